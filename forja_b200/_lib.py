@@ -1,0 +1,116 @@
+"""ctypes declarations for libforja_cuda.so (see include/forja_cuda.h)."""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+from . import build as _build
+
+
+class FjTensor(C.Structure):
+    _fields_ = [("buffer", C.c_uint64), ("dtype", C.c_uint32), ("rank", C.c_uint32), ("offset", C.c_uint64),
+                ("shape", C.c_uint32 * 8), ("strides", C.c_uint64 * 8)]
+
+
+class FjDispatch(C.Structure):
+    _fields_ = [("op", C.c_uint32), ("n_inputs", C.c_uint32), ("n_outputs", C.c_uint32), ("u0", C.c_uint32), ("u1", C.c_uint32),
+                ("u2", C.c_uint32), ("u3", C.c_uint32), ("f0", C.c_float), ("program", C.c_uint64),
+                ("inputs", C.POINTER(FjTensor)), ("outputs", C.POINTER(FjTensor))]
+
+
+class FjDeviceError(C.Structure):
+    _fields_ = [("submission", C.c_uint64), ("dispatch", C.c_uint32), ("op", C.c_uint32), ("flag", C.c_uint32),
+                ("value", C.c_uint32), ("code", C.c_int64)]
+
+
+class FjDeviceInfo(C.Structure):
+    _fields_ = [("name", C.c_char * 128), ("sm_count", C.c_uint32), ("cc_major", C.c_uint32), ("cc_minor", C.c_uint32),
+                ("total_memory", C.c_uint64), ("l2_bytes", C.c_uint64), ("max_smem_per_block", C.c_uint32)]
+
+
+class FjDispatchProfile(C.Structure):
+    _fields_ = [("op", C.c_uint32), ("kernels", C.c_uint32), ("ns", C.c_uint64)]
+
+
+class FjPackView(C.Structure):
+    _fields_ = [("rows", C.c_uint32), ("lanes", C.c_uint32), ("logical_lengths", C.c_uint64), ("query_starts", C.c_uint64),
+                ("absolute_positions", C.c_uint64), ("activity", C.c_uint64), ("cu_seqlens", C.c_uint64), ("positions", C.c_uint64),
+                ("slot_mapping", C.c_uint64), ("row_lane", C.c_uint64)]
+
+
+class FjDenseConfig(C.Structure):
+    _fields_ = [("dtype", C.c_uint32), ("layers", C.c_uint32), ("hidden", C.c_uint32), ("q_heads", C.c_uint32), ("kv_heads", C.c_uint32),
+                ("head_dim", C.c_uint32), ("intermediate", C.c_uint32), ("vocab", C.c_uint32), ("qk_norm", C.c_uint32),
+                ("eps", C.c_float), ("theta", C.c_float), ("max_rows", C.c_uint32)]
+
+
+class FjDenseLayerWeights(C.Structure):
+    _fields_ = [(n, C.c_uint64) for n in ("input_norm", "wq", "wk", "wv", "q_norm", "k_norm", "wo", "post_norm", "w_gate", "w_up", "w_down")]
+
+
+# Every symbol include/forja_cuda.h declares; the loader test checks that the library exports them all.
+EXPORTS = [
+    "fj_backend_create", "fj_backend_destroy", "fj_device_info", "fj_set_memory_limit", "fj_memory_usage", "fj_alloc",
+    "fj_import_readonly", "fj_release", "fj_write", "fj_read", "fj_read_strided", "fj_buffer_device_ptr", "fj_program_prepare",
+    "fj_program_info", "fj_submit", "fj_sub_wait", "fj_sub_gpu_time_ns", "fj_sub_completion_serial", "fj_sub_error",
+    "fj_sub_kernel_launches", "fj_sub_profile", "fj_sub_destroy", "fj_synchronize", "fj_kernel_launch_count", "fj_timer_create",
+    "fj_timer_record", "fj_timer_elapsed_ns", "fj_kvpool_create", "fj_kvpool_destroy", "fj_kvpool_reserve", "fj_kvpool_release",
+    "fj_kvpool_read_table", "fj_kvpool_read_generations", "fj_kvpool_read_free", "fj_kvpool_tables_buffer",
+    "fj_kvpool_generations_buffer", "fj_pack_step", "fj_dense_model_create", "fj_dense_model_destroy", "fj_dense_step",
+    "fj_dense_step_stats",
+]
+
+_lib = None
+
+
+def library_path() -> str:
+    return _build.OUTPUT
+
+
+def load():
+    """Loads the in-tree library, building it first when sources are newer. Raises when it cannot
+    be built or loaded: there is no fallback implementation."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    path = _build.OUTPUT
+    if _build.needs_build():
+        if os.environ.get("FORJA_B200_NO_BUILD"):
+            if not os.path.exists(path):
+                raise RuntimeError(f"{path} is missing and FORJA_B200_NO_BUILD is set")
+        else:
+            _build.build()
+    lib = C.CDLL(path)
+    for name in EXPORTS:
+        getattr(lib, name)
+    lib.fj_sub_completion_serial.restype = C.c_uint64
+    lib.fj_kernel_launch_count.restype = C.c_uint64
+    lib.fj_sub_kernel_launches.restype = C.c_uint32
+    lib.fj_kvpool_tables_buffer.restype = C.c_uint64
+    lib.fj_kvpool_generations_buffer.restype = C.c_uint64
+    lib.fj_backend_destroy.restype = None
+    lib.fj_sub_destroy.restype = None
+    lib.fj_kvpool_destroy.restype = None
+    lib.fj_dense_model_destroy.restype = None
+    for name in ("fj_backend_destroy", "fj_sub_destroy", "fj_kvpool_destroy", "fj_dense_model_destroy", "fj_sub_completion_serial",
+                 "fj_kernel_launch_count", "fj_sub_kernel_launches", "fj_kvpool_tables_buffer", "fj_kvpool_generations_buffer"):
+        getattr(lib, name).argtypes = [C.c_void_p]
+    P, U32, U64, I32 = C.c_void_p, C.c_uint32, C.c_uint64, C.c_int32
+    argtypes = {
+        "fj_backend_create": [I32, U64, P], "fj_device_info": [P, P], "fj_set_memory_limit": [P, U64], "fj_memory_usage": [P, P, P],
+        "fj_alloc": [P, U64, P], "fj_import_readonly": [P, P, U64, P], "fj_release": [P, U64], "fj_write": [P, U64, U64, P, U64],
+        "fj_read": [P, U64, U64, P, U64], "fj_read_strided": [P, P, P], "fj_buffer_device_ptr": [P, U64, P, P],
+        "fj_program_prepare": [P, U32, P, U32, P, U32, P], "fj_program_info": [P, U64, P, P], "fj_submit": [P, P, U32, U32, P],
+        "fj_sub_wait": [P, U64], "fj_sub_gpu_time_ns": [P, P], "fj_sub_error": [P, P], "fj_sub_profile": [P, P, U32, P],
+        "fj_synchronize": [P], "fj_timer_create": [P, P], "fj_timer_record": [P, U64], "fj_timer_elapsed_ns": [P, U64, U64, P],
+        "fj_kvpool_create": [P, U32, U32, U32, U32, P], "fj_kvpool_reserve": [P, P, P, U32, P], "fj_kvpool_release": [P, P, U32],
+        "fj_kvpool_read_table": [P, U32, P], "fj_kvpool_read_generations": [P, P], "fj_kvpool_read_free": [P, P, U32, P],
+        "fj_pack_step": [P, P, P, U32, P], "fj_dense_model_create": [P, P, U64, U64, P, P, P], "fj_dense_step": [P, P, P, U64],
+        "fj_dense_step_stats": [P, P, P],
+    }
+    for name, types in argtypes.items():
+        fn = getattr(lib, name)
+        fn.argtypes = types
+        fn.restype = C.c_int32
+    _lib = lib
+    return lib

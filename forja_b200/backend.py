@@ -1,0 +1,482 @@
+"""Host-side mirror of forja's backend interface over the C ABI of libforja_cuda.so.
+
+Names and semantics follow ``forja_core`` (crates/forja-core/src/backend.rs:650-984, ops.rs:163-302,
+layout.rs): ``CudaBackend.alloc/view/write/read/release/submit``, ``Tensor`` + ``Layout`` views,
+``CommandList.dispatch`` with the reference's operand orders, ``Submission.wait``. This module is a
+test and benchmark harness; the product is the library behind it. There is no CPU path: creating a
+backend without a CUDA device raises.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass, field
+from typing import List, Optional, Sequence, Tuple
+
+import numpy as np
+
+from . import _lib
+
+F32, F16, BF16, I32, U32 = 0, 1, 2, 3, 4
+DTYPE_SIZE = {F32: 4, F16: 2, BF16: 2, I32: 4, U32: 4}
+NP_OF = {F32: np.float32, F16: np.float16, BF16: np.uint16, I32: np.int32, U32: np.uint32}
+
+STATUS_NAMES = ["Ok", "QuotaExceeded", "AllocationFailed", "ExecutionFailed", "DeviceExecutionFailed", "DeviceErrorFlag",
+                "Timeout", "InvalidInput", "UnsupportedOperation", "IndexOutOfRange"]
+OK, QUOTA_EXCEEDED, ALLOCATION_FAILED, EXECUTION_FAILED, DEVICE_EXECUTION_FAILED, DEVICE_ERROR_FLAG, TIMEOUT, INVALID_INPUT, \
+    UNSUPPORTED_OPERATION, INDEX_OUT_OF_RANGE = range(10)
+
+
+class BackendError(RuntimeError):
+    """forja_core::BackendError (crates/forja-core/src/backend.rs:362-426)."""
+
+    def __init__(self, status: int, index: Optional[int] = None, dispatch: Optional[int] = None, flag: Optional[int] = None):
+        name = STATUS_NAMES[status] if 0 <= status < len(STATUS_NAMES) else str(status)
+        super().__init__(f"BackendError::{name}" + (f" index={index}" if index is not None else ""))
+        self.status, self.index, self.dispatch, self.flag = status, index, dispatch, flag
+
+
+def _check(status: int):
+    if status != OK:
+        raise BackendError(status)
+
+
+@dataclass(frozen=True)
+class Layout:
+    """Strided view metadata in elements (crates/forja-core/src/layout.rs)."""
+    dtype: int
+    offset: int
+    shape: Tuple[int, ...]
+    strides: Tuple[int, ...]
+
+    @staticmethod
+    def contiguous(dtype: int, shape: Sequence[int], offset: int = 0) -> "Layout":
+        strides, acc = [], 1
+        for extent in reversed(shape):
+            strides.append(acc)
+            acc *= extent
+        return Layout(dtype, offset, tuple(shape), tuple(reversed(strides)))
+
+    def element_count(self) -> int:
+        n = 1
+        for s in self.shape:
+            n *= s
+        return n
+
+    def is_contiguous(self) -> bool:
+        return self.strides == Layout.contiguous(self.dtype, self.shape).strides or self.element_count() <= 1
+
+    def slice(self, specs: Sequence[Tuple[int, int, int]]) -> "Layout":
+        """specs: (start, len, step) per axis, like ViewOp::Slice."""
+        if len(specs) != len(self.shape):
+            raise BackendError(INVALID_INPUT)
+        offset, shape, strides = self.offset, [], []
+        for (start, length, step), extent, stride in zip(specs, self.shape, self.strides):
+            if step == 0 or (length and start + (length - 1) * step >= extent):
+                raise BackendError(INVALID_INPUT)
+            offset += start * stride
+            shape.append(length)
+            strides.append(stride * step)
+        return Layout(self.dtype, offset, tuple(shape), tuple(strides))
+
+    def reshape(self, shape: Sequence[int]) -> "Layout":
+        if not self.is_contiguous():
+            raise BackendError(INVALID_INPUT)
+        new = Layout.contiguous(self.dtype, shape, self.offset)
+        if new.element_count() != self.element_count():
+            raise BackendError(INVALID_INPUT)
+        return new
+
+    def permute(self, axes: Sequence[int]) -> "Layout":
+        if sorted(axes) != list(range(len(self.shape))):
+            raise BackendError(INVALID_INPUT)
+        return Layout(self.dtype, self.offset, tuple(self.shape[a] for a in axes), tuple(self.strides[a] for a in axes))
+
+    def broadcast(self, shape: Sequence[int]) -> "Layout":
+        if len(shape) < len(self.shape):
+            raise BackendError(INVALID_INPUT)
+        pad = len(shape) - len(self.shape)
+        old_shape, old_strides = (1,) * pad + self.shape, (0,) * pad + self.strides
+        strides = []
+        for want, have, stride in zip(shape, old_shape, old_strides):
+            if have == want:
+                strides.append(stride)
+            elif have == 1:
+                strides.append(0)
+            else:
+                raise BackendError(INVALID_INPUT)
+        return Layout(self.dtype, self.offset, tuple(shape), tuple(strides))
+
+
+@dataclass(frozen=True)
+class Tensor:
+    """Validated view into a backend allocation (crates/forja-core/src/ops.rs:90-159)."""
+    buffer: int
+    layout: Layout
+    byte_len: int
+    writable: bool = True
+
+    @property
+    def shape(self):
+        return self.layout.shape
+
+    @property
+    def dtype(self):
+        return self.layout.dtype
+
+    def slice(self, specs): return Tensor(self.buffer, self.layout.slice(specs), self.byte_len, self.writable)
+    def reshape(self, shape): return Tensor(self.buffer, self.layout.reshape(shape), self.byte_len, self.writable)
+    def permute(self, axes): return Tensor(self.buffer, self.layout.permute(axes), self.byte_len, self.writable)
+    def broadcast(self, shape): return Tensor(self.buffer, self.layout.broadcast(shape), self.byte_len, self.writable)
+
+    def narrow(self, axis: int, start: int, length: int) -> "Tensor":
+        specs = [(0, s, 1) for s in self.shape]
+        specs[axis] = (start, length, 1)
+        return self.slice(specs)
+
+    def to_c(self) -> _lib.FjTensor:
+        t = _lib.FjTensor()
+        t.buffer, t.dtype, t.rank, t.offset = self.buffer, self.layout.dtype, len(self.layout.shape), self.layout.offset
+        for i, (s, st) in enumerate(zip(self.layout.shape, self.layout.strides)):
+            t.shape[i], t.strides[i] = s, st
+        return t
+
+
+# fj_op codes (include/forja_cuda.h)
+OP_PROGRAM, OP_COPY, OP_PAGED_COPY, OP_RMS_NORM, OP_ARGMAX, OP_TOP_K, OP_ROPE, OP_EMBED, OP_QUANT_EMBED, OP_MATMUL, OP_QUANT_MATMUL, \
+    OP_GATHER_QUANT_MATMUL, OP_PAGED_SDPA, OP_PAGED_SDPA_APPEND, OP_SDPA, OP_SAMPLE = range(1, 17)
+
+
+@dataclass(frozen=True)
+class Op:
+    """forja_core::Op (crates/forja-core/src/ops.rs:163-302) with its scalar parameters."""
+    code: int
+    u0: int = 0
+    u1: int = 0
+    u2: int = 0
+    u3: int = 0
+    f0: float = 0.0
+    program: int = 0
+
+    @staticmethod
+    def Copy(): return Op(OP_COPY)
+    @staticmethod
+    def PagedCopy(into_pages: bool, start: int, page_tokens: int): return Op(OP_PAGED_COPY, u0=0 if into_pages else 1, u1=start, u2=page_tokens)
+    @staticmethod
+    def RmsNorm(eps: float): return Op(OP_RMS_NORM, f0=eps)
+    @staticmethod
+    def Argmax(chunk_width: int = 2048): return Op(OP_ARGMAX)
+    @staticmethod
+    def TopK(k: int, normalize: bool, chunk_width: int = 2048): return Op(OP_TOP_K, u0=k, u1=int(normalize))
+    @staticmethod
+    def Rope(theta: float): return Op(OP_ROPE, f0=theta)
+    @staticmethod
+    def Embed(): return Op(OP_EMBED)
+    @staticmethod
+    def QuantEmbed(bits: int, group_size: int): return Op(OP_QUANT_EMBED, u0=bits, u1=group_size)
+    @staticmethod
+    def Matmul(): return Op(OP_MATMUL)
+    @staticmethod
+    def QuantMatmul(bits: int, group_size: int): return Op(OP_QUANT_MATMUL, u0=bits, u1=group_size)
+    @staticmethod
+    def GatherQuantMatmul(bits: int, group_size: int, epilogue: int = 0): return Op(OP_GATHER_QUANT_MATMUL, u0=bits, u1=group_size, program=epilogue)
+    @staticmethod
+    def PagedSdpa(scale: float, causal: bool, q_start: int, key_length: int, page_tokens: int):
+        return Op(OP_PAGED_SDPA, u0=int(causal), u1=q_start, u2=key_length, u3=page_tokens, f0=scale)
+    @staticmethod
+    def PagedSdpaAppend(scale: float, q_start: int, page_tokens: int): return Op(OP_PAGED_SDPA_APPEND, u1=q_start, u3=page_tokens, f0=scale)
+    @staticmethod
+    def Program(handle: int): return Op(OP_PROGRAM, program=handle)
+
+
+@dataclass
+class Dispatch:
+    op: Op
+    inputs: List[Tensor]
+    outputs: List[Tensor]
+
+
+@dataclass
+class CommandList:
+    """Ordered validated dispatches (crates/forja-core/src/ops.rs CommandList)."""
+    dispatches: List[Dispatch] = field(default_factory=list)
+
+    def dispatch(self, op: Op, inputs: Sequence[Tensor], output: Tensor):
+        self.dispatches.append(Dispatch(op, list(inputs), [output]))
+        return self
+
+    def dispatch_many(self, op: Op, inputs: Sequence[Tensor], outputs: Sequence[Tensor]):
+        self.dispatches.append(Dispatch(op, list(inputs), list(outputs)))
+        return self
+
+
+class Submission:
+    """forja_core::Submission (crates/forja-core/src/backend.rs:609-647)."""
+
+    def __init__(self, lib, handle, keepalive):
+        self._lib, self._h, self._keep = lib, handle, keepalive
+
+    def wait(self, timeout_ns: int = 0):
+        status = self._lib.fj_sub_wait(self._h, timeout_ns)
+        if status in (INDEX_OUT_OF_RANGE, DEVICE_ERROR_FLAG, DEVICE_EXECUTION_FAILED):
+            err = _lib.FjDeviceError()
+            self._lib.fj_sub_error(self._h, C.byref(err))
+            raise BackendError(status, index=err.value, dispatch=err.dispatch, flag=err.flag)
+        _check(status)
+
+    def gpu_time_ns(self) -> int:
+        out = C.c_uint64(0)
+        _check(self._lib.fj_sub_gpu_time_ns(self._h, C.byref(out)))
+        return out.value
+
+    def completion_serial(self) -> int:
+        return self._lib.fj_sub_completion_serial(self._h)
+
+    def kernel_launches(self) -> int:
+        return self._lib.fj_sub_kernel_launches(self._h)
+
+    def profile(self):
+        n = C.c_uint32(0)
+        self._lib.fj_sub_profile(self._h, None, 0, C.byref(n))
+        arr = (_lib.FjDispatchProfile * max(n.value, 1))()
+        self._lib.fj_sub_profile(self._h, arr, n.value, C.byref(n))
+        return [(arr[i].op, arr[i].kernels, arr[i].ns) for i in range(n.value)]
+
+    def __del__(self):
+        if getattr(self, "_h", None):
+            self._lib.fj_sub_destroy(self._h)
+            self._h = None
+
+
+class CudaBackend:
+    """The `forja-cuda` backend: one CUDA device, one stream, hand-written sm_100a kernels."""
+
+    def __init__(self, device: int = 0, memory_limit: int = 0):
+        self._lib = _lib.load()
+        handle = C.c_void_p()
+        status = self._lib.fj_backend_create(device, memory_limit, C.byref(handle))
+        if status != OK:
+            raise BackendError(status)
+        self._h = handle
+        self.device = device
+
+    def close(self):
+        if getattr(self, "_h", None):
+            self._lib.fj_backend_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        self.close()
+
+    # -- Backend trait ----------------------------------------------------------------------
+    def device_info(self):
+        info = _lib.FjDeviceInfo()
+        _check(self._lib.fj_device_info(self._h, C.byref(info)))
+        return {"name": info.name.decode(), "sm_count": info.sm_count, "cc": (info.cc_major, info.cc_minor),
+                "total_memory": info.total_memory, "l2_bytes": info.l2_bytes, "max_smem_per_block": info.max_smem_per_block}
+
+    def memory_usage(self):
+        used, limit = C.c_uint64(0), C.c_uint64(0)
+        _check(self._lib.fj_memory_usage(self._h, C.byref(used), C.byref(limit)))
+        return used.value, limit.value
+
+    def set_memory_limit(self, nbytes: int):
+        _check(self._lib.fj_set_memory_limit(self._h, nbytes))
+
+    def alloc(self, dtype: int, shape: Sequence[int]) -> Tensor:
+        layout = Layout.contiguous(dtype, tuple(int(s) for s in shape))
+        nbytes = layout.element_count() * DTYPE_SIZE[dtype]
+        buf = C.c_uint64(0)
+        _check(self._lib.fj_alloc(self._h, nbytes, C.byref(buf)))
+        return Tensor(buf.value, layout, nbytes, True)
+
+    def import_readonly(self, array: np.ndarray, dtype: int) -> Tensor:
+        array = np.ascontiguousarray(array)
+        buf = C.c_uint64(0)
+        _check(self._lib.fj_import_readonly(self._h, array.ctypes.data_as(C.c_void_p), array.nbytes, C.byref(buf)))
+        return Tensor(buf.value, Layout.contiguous(dtype, array.shape), array.nbytes, False)
+
+    def view(self, tensor: Tensor, kind: str, arg) -> Tensor:
+        return getattr(tensor, kind)(arg)
+
+    def write(self, tensor: Tensor, data) -> None:
+        if not tensor.writable or not tensor.layout.is_contiguous():
+            raise BackendError(INVALID_INPUT)
+        data = np.ascontiguousarray(data)
+        if data.nbytes != tensor.layout.element_count() * DTYPE_SIZE[tensor.dtype]:
+            raise BackendError(INVALID_INPUT)
+        _check(self._lib.fj_write(self._h, tensor.buffer, tensor.layout.offset * DTYPE_SIZE[tensor.dtype], data.ctypes.data_as(C.c_void_p), data.nbytes))
+
+    def read(self, tensor: Tensor) -> np.ndarray:
+        out = np.empty(tensor.shape, NP_OF[tensor.dtype])
+        if out.size == 0:
+            return out
+        t = tensor.to_c()
+        _check(self._lib.fj_read_strided(self._h, C.byref(t), out.ctypes.data_as(C.c_void_p)))
+        return out
+
+    def release(self, tensor: Tensor) -> None:
+        _check(self._lib.fj_release(self._h, tensor.buffer))
+
+    def prepare_program(self, kind: int, insts: np.ndarray, outputs: np.ndarray) -> int:
+        insts = np.ascontiguousarray(insts, np.uint32)
+        outputs = np.ascontiguousarray(outputs, np.uint32)
+        handle = C.c_uint64(0)
+        _check(self._lib.fj_program_prepare(self._h, kind, insts.ctypes.data_as(C.c_void_p), insts.shape[0], outputs.ctypes.data_as(C.c_void_p), outputs.shape[0], C.byref(handle)))
+        return handle.value
+
+    def program_info(self, handle: int):
+        kernel = C.c_uint32(0)
+        consts = (C.c_float * 4)()
+        _check(self._lib.fj_program_info(self._h, handle, C.byref(kernel), consts))
+        return kernel.value, tuple(consts)
+
+    def submit(self, commands: CommandList, profiled: bool = False) -> Submission:
+        n = len(commands.dispatches)
+        arr = (_lib.FjDispatch * max(n, 1))()
+        keep = []
+        for i, d in enumerate(commands.dispatches):
+            ins = (_lib.FjTensor * max(len(d.inputs), 1))(*[t.to_c() for t in d.inputs])
+            outs = (_lib.FjTensor * max(len(d.outputs), 1))(*[t.to_c() for t in d.outputs])
+            keep += [ins, outs]
+            arr[i].op, arr[i].n_inputs, arr[i].n_outputs = d.op.code, len(d.inputs), len(d.outputs)
+            arr[i].u0, arr[i].u1, arr[i].u2, arr[i].u3, arr[i].f0, arr[i].program = d.op.u0, d.op.u1, d.op.u2, d.op.u3, d.op.f0, d.op.program
+            arr[i].inputs, arr[i].outputs = ins, outs
+        handle = C.c_void_p()
+        _check(self._lib.fj_submit(self._h, arr, n, int(profiled), C.byref(handle)))
+        return Submission(self._lib, handle, keep)
+
+    # -- helpers for tests and benchmarks -----------------------------------------------------
+    def tensor_from(self, array: np.ndarray, dtype: int) -> Tensor:
+        t = self.alloc(dtype, array.shape)
+        self.write(t, array)
+        return t
+
+    def run(self, op: Op, inputs: Sequence[Tensor], outputs: Sequence[Tensor]):
+        cl = CommandList()
+        cl.dispatch_many(op, inputs, outputs)
+        sub = self.submit(cl)
+        sub.wait()
+        return sub
+
+    def synchronize(self):
+        _check(self._lib.fj_synchronize(self._h))
+
+    def kernel_launch_count(self) -> int:
+        return self._lib.fj_kernel_launch_count(self._h)
+
+    def timer(self) -> int:
+        t = C.c_uint64(0)
+        _check(self._lib.fj_timer_create(self._h, C.byref(t)))
+        return t.value
+
+    def timer_record(self, timer: int):
+        _check(self._lib.fj_timer_record(self._h, timer))
+
+    def timer_elapsed_ns(self, start: int, stop: int) -> int:
+        out = C.c_uint64(0)
+        _check(self._lib.fj_timer_elapsed_ns(self._h, start, stop, C.byref(out)))
+        return out.value
+
+
+class KvPool:
+    """Device-resident paged-KV allocator and ragged-batch packer (fj_kvpool_*, fj_pack_step)."""
+
+    def __init__(self, backend: CudaBackend, page_tokens: int, physical_pages: int, lanes: int, table_pages: int):
+        self.backend, self._lib = backend, backend._lib
+        self.page_tokens, self.physical_pages, self.lanes, self.table_pages = page_tokens, physical_pages, lanes, table_pages
+        handle = C.c_void_p()
+        _check(self._lib.fj_kvpool_create(backend._h, page_tokens, physical_pages, lanes, table_pages, C.byref(handle)))
+        self._h = handle
+
+    def close(self):
+        if getattr(self, "_h", None) and getattr(self.backend, "_h", None):
+            self._lib.fj_kvpool_destroy(self._h)
+        self._h = None
+
+    def reserve(self, lanes: Sequence[int], tokens: Sequence[int], want_status: bool = True):
+        la, to = np.ascontiguousarray(lanes, np.uint32), np.ascontiguousarray(tokens, np.uint32)
+        status = np.zeros(la.size, np.int32)
+        _check(self._lib.fj_kvpool_reserve(self._h, la.ctypes.data_as(C.c_void_p), to.ctypes.data_as(C.c_void_p), la.size,
+                                           status.ctypes.data_as(C.c_void_p) if want_status else None))
+        return status.tolist() if want_status else None
+
+    def release(self, lanes: Sequence[int]):
+        la = np.ascontiguousarray(lanes, np.uint32)
+        _check(self._lib.fj_kvpool_release(self._h, la.ctypes.data_as(C.c_void_p), la.size))
+
+    def table(self, lane: int) -> np.ndarray:
+        out = np.zeros((self.table_pages, 2), np.uint32)
+        _check(self._lib.fj_kvpool_read_table(self._h, lane, out.ctypes.data_as(C.c_void_p)))
+        return out
+
+    def generations(self) -> np.ndarray:
+        out = np.zeros(self.physical_pages, np.uint32)
+        _check(self._lib.fj_kvpool_read_generations(self._h, out.ctypes.data_as(C.c_void_p)))
+        return out
+
+    def free_list(self) -> np.ndarray:
+        out = np.zeros(self.physical_pages, np.uint32)
+        n = C.c_uint32(0)
+        _check(self._lib.fj_kvpool_read_free(self._h, out.ctypes.data_as(C.c_void_p), self.physical_pages, C.byref(n)))
+        return out[:n.value]
+
+    def tables_tensor(self) -> Tensor:
+        return Tensor(self._lib.fj_kvpool_tables_buffer(self._h), Layout.contiguous(U32, (self.lanes, self.table_pages, 2)), self.lanes * self.table_pages * 8)
+
+    def generations_tensor(self) -> Tensor:
+        return Tensor(self._lib.fj_kvpool_generations_buffer(self._h), Layout.contiguous(U32, (self.physical_pages,)), self.physical_pages * 4)
+
+    def pack_step(self, starts: Sequence[int], tokens: Sequence[int], read_back: bool = False):
+        st, to = np.ascontiguousarray(starts, np.uint32), np.ascontiguousarray(tokens, np.uint32)
+        view = _lib.FjPackView()
+        _check(self._lib.fj_pack_step(self._h, st.ctypes.data_as(C.c_void_p), to.ctypes.data_as(C.c_void_p), st.size, C.byref(view)))
+        if not read_back:
+            return view.rows
+        out = {"rows": view.rows}
+        lanes = st.size
+
+        def rd(buf, n):
+            a = np.zeros(max(n, 1), np.uint32)
+            if n:
+                _check(self._lib.fj_read(self.backend._h, buf, 0, a.ctypes.data_as(C.c_void_p), n * 4))
+            return a[:n]
+        for name in ("logical_lengths", "query_starts", "absolute_positions", "activity"):
+            out[name] = rd(getattr(view, name), lanes)
+        out["cu_seqlens"] = rd(view.cu_seqlens, lanes + 1)
+        for name in ("positions", "slot_mapping", "row_lane"):
+            out[name] = rd(getattr(view, name), view.rows)
+        return out
+
+
+class DenseModel:
+    """Dense decoder on the fast path (fj_dense_model_create / fj_dense_step)."""
+
+    def __init__(self, backend: CudaBackend, pool: KvPool, config: dict, embed: Tensor, final_norm: Tensor, layers: Sequence[dict]):
+        self.backend, self.pool, self._lib, self.config = backend, pool, backend._lib, dict(config)
+        cfg = _lib.FjDenseConfig()
+        for key in ("dtype", "layers", "hidden", "q_heads", "kv_heads", "head_dim", "intermediate", "vocab", "qk_norm", "eps", "theta", "max_rows"):
+            setattr(cfg, key, config[key])
+        arr = (_lib.FjDenseLayerWeights * len(layers))()
+        for i, layer in enumerate(layers):
+            for name, _ in _lib.FjDenseLayerWeights._fields_:
+                setattr(arr[i], name, layer[name].buffer if layer.get(name) is not None else 0)
+        handle = C.c_void_p()
+        _check(self._lib.fj_dense_model_create(backend._h, C.byref(cfg), embed.buffer, final_norm.buffer, arr, pool._h, C.byref(handle)))
+        self._h = handle
+
+    def close(self):
+        if getattr(self, "_h", None) and getattr(self.backend, "_h", None):
+            self._lib.fj_dense_model_destroy(self._h)
+        self._h = None
+
+    def step(self, token_ids=None, want_tokens: bool = True, logits: Optional[Tensor] = None, lanes: Optional[int] = None):
+        ids = None if token_ids is None else np.ascontiguousarray(token_ids, np.uint32)
+        out = np.zeros(lanes if lanes is not None else self.pool.lanes, np.uint32) if want_tokens else None
+        _check(self._lib.fj_dense_step(self._h, None if ids is None else ids.ctypes.data_as(C.c_void_p),
+                                       None if out is None else out.ctypes.data_as(C.c_void_p), logits.buffer if logits is not None else 0))
+        return out
+
+    def stats(self):
+        k, w = C.c_uint64(0), C.c_uint64(0)
+        _check(self._lib.fj_dense_step_stats(self._h, C.byref(k), C.byref(w)))
+        return {"kernels": k.value, "attn_work_items": w.value}

@@ -1,0 +1,126 @@
+// Shared device helpers for the forja sm_100a kernels: storage <-> f32 conversion with the
+// reference's rounding (round to nearest even on every store, crates/forja-cpu/src/lib.rs:1836-1847),
+// IEEE total-order keys, warp/block reductions and the per-dispatch error record.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace fj {
+
+enum DType : int { F32 = 0, F16 = 1, BF16 = 2, I32 = 3, U32 = 4 };
+
+__host__ __device__ inline size_t dtype_size(int dt) { return (dt == F16 || dt == BF16) ? 2 : 4; }
+
+// Per-dispatch error record written by kernels: never a trap, always a flag the host reads after
+// completion (the reference's device contract: crates/forja-metal/src/paged.metal:39-55).
+struct ErrorRecord {
+  unsigned int flag;   // 0 ok, 1 index out of range, 2 page entry refused, 3 wait gave up
+  unsigned int value;  // lowest offending value (initialised to 0xFFFFFFFF)
+};
+enum : unsigned int { ERR_INDEX = 1, ERR_PAGE = 2, ERR_WAIT = 3 };
+
+__device__ inline void report_error(ErrorRecord* rec, unsigned int flag, unsigned int value) {
+  if (rec == nullptr) return;
+  atomicMax(&rec->flag, flag);
+  atomicMin(&rec->value, value);
+}
+
+template <typename T> __device__ inline float to_f32(T v);
+template <> __device__ inline float to_f32<float>(float v) { return v; }
+template <> __device__ inline float to_f32<__half>(__half v) { return __half2float(v); }
+template <> __device__ inline float to_f32<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+template <typename T> __device__ inline T from_f32(float v);
+template <> __device__ inline float from_f32<float>(float v) { return v; }
+template <> __device__ inline __half from_f32<__half>(float v) { return __float2half_rn(v); }
+template <> __device__ inline __nv_bfloat16 from_f32<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+
+// Runtime-dtype element access (cold paths and generic kernels).
+__device__ inline float load_as_f32(const void* base, int dt, size_t index) {
+  switch (dt) {
+    case F32: return static_cast<const float*>(base)[index];
+    case F16: return __half2float(static_cast<const __half*>(base)[index]);
+    default: return __bfloat162float(static_cast<const __nv_bfloat16*>(base)[index]);
+  }
+}
+__device__ inline void store_from_f32(void* base, int dt, size_t index, float v) {
+  switch (dt) {
+    case F32: static_cast<float*>(base)[index] = v; break;
+    case F16: static_cast<__half*>(base)[index] = __float2half_rn(v); break;
+    default: static_cast<__nv_bfloat16*>(base)[index] = __float2bfloat16_rn(v); break;
+  }
+}
+// Rounds an f32 value through a storage dtype (re-inserts the rounding of a materialised tensor).
+__device__ inline float round_through(float v, int dt) {
+  switch (dt) {
+    case F16: return __half2float(__float2half_rn(v));
+    case BF16: return __bfloat162float(__float2bfloat16_rn(v));
+    default: return v;
+  }
+}
+
+// f32::total_cmp as an unsigned key: larger key = greater under IEEE total order.
+__device__ inline unsigned int total_order_key(float v) {
+  int b = __float_as_int(v);
+  b ^= static_cast<int>(static_cast<unsigned int>(b >> 31) >> 1);
+  return static_cast<unsigned int>(b) ^ 0x80000000u;
+}
+__device__ inline float key_to_float(unsigned int key) {
+  int b = static_cast<int>(key ^ 0x80000000u);
+  b ^= static_cast<int>(static_cast<unsigned int>(b >> 31) >> 1);
+  return __int_as_float(b);
+}
+
+__device__ inline float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ inline float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+__device__ inline unsigned long long warp_max_u64(unsigned long long v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    unsigned long long other = __shfl_xor_sync(0xffffffffu, v, o);
+    v = other > v ? other : v;
+  }
+  return v;
+}
+// Block-wide sum; `scratch` holds 32 floats of shared memory. All threads get the result.
+__device__ inline float block_sum(float v, float* scratch) {
+  v = warp_sum(v);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  __syncthreads();
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  const int warps = (blockDim.x + 31) >> 5;
+  float total = lane < warps ? scratch[lane] : 0.0f;
+  total = warp_sum(total);
+  return total;
+}
+
+// Strided view descriptor passed by value to generic kernels.
+struct View {
+  void* base;          // allocation base pointer (already offset by the view's element offset)
+  int dtype;
+  int rank;
+  unsigned int shape[8];
+  unsigned long long strides[8];
+};
+__device__ inline size_t view_offset(const View& v, size_t linear) {
+  size_t off = 0;
+#pragma unroll 1
+  for (int a = v.rank - 1; a >= 0; --a) {
+    off += (linear % v.shape[a]) * v.strides[a];
+    linear /= v.shape[a];
+  }
+  return off;
+}
+
+}  // namespace fj

@@ -1,0 +1,150 @@
+// Host-side launch interface of the forja sm_100a kernels. Every launcher enqueues on ctx.stream
+// and bumps ctx.launches by the number of kernels it started; none of them allocates.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "fj_common.cuh"
+
+namespace fj {
+
+struct Ctx {
+  cudaStream_t stream;
+  unsigned long long launches;  // kernels started through this context
+  int sm_count;
+};
+
+// ---- fj_elementwise.cu ----------------------------------------------------------------------
+void launch_copy(Ctx& ctx, const View& in, const View& out, size_t elements);
+void launch_fill_zero(Ctx& ctx, void* ptr, size_t bytes);
+// Map programs over `shape` (views broadcast to it): add, silu_mul, rope_pairs.
+void launch_add(Ctx& ctx, const View& a, const View& b, const View& out, size_t elements);
+void launch_silu_mul(Ctx& ctx, const View& gate, const View& up, const View& out, size_t elements);
+// Row programs: rows = elements / width, reductions over the last axis.
+void launch_rms_norm(Ctx& ctx, const View& x, const View& w, const View& out, size_t rows, unsigned width, float eps);
+void launch_residual_norm(Ctx& ctx, const View& residual, const View& update, const View& w, const View& sum_out,
+                          const View& norm_out, size_t rows, unsigned width, float eps);
+// qk_norm_rope over the half row: inputs lo, hi, weight_lo, weight_hi, positions (all views of the
+// iteration shape [.., half]); inv_freq[i] = powf(theta, i * (-2/head_dim)) precomputed on the host.
+void launch_qk_norm_rope(Ctx& ctx, const View& lo, const View& hi, const View& wlo, const View& whi, const View& pos,
+                         const View& out_lo, const View& out_hi, size_t rows, unsigned half, float head_dim, float eps,
+                         const float* inv_freq);
+// rope_pairs map program / Op::Rope: first, second halves; positions view (float or u32 dtype).
+void launch_rope_pairs(Ctx& ctx, const View& first, const View& second, const View& pos, const View& out_first,
+                       const View& out_second, size_t elements, unsigned half, const float* inv_freq);
+void launch_embed(Ctx& ctx, const void* table, int t_dt, const unsigned* ids, void* out, int out_dt, unsigned vocab,
+                  unsigned width, unsigned count, ErrorRecord* err);
+void launch_quant_embed(Ctx& ctx, const unsigned* packed, const void* scales, const void* biases, int p_dt,
+                        const unsigned* ids, void* out, int out_dt, unsigned vocab, unsigned packed_width, unsigned count,
+                        unsigned bits, unsigned group_size, ErrorRecord* err);
+// argmax under IEEE total order, ties -> highest index. scratch: rows * chunks u64.
+size_t argmax_scratch_bytes(unsigned rows, unsigned width);
+void launch_argmax(Ctx& ctx, const void* x, int x_dt, size_t row_stride, unsigned* out, unsigned rows, unsigned width,
+                   void* scratch);
+// top-k: descending total order, ties -> lower index; optional softmax over the selected set.
+void launch_top_k(Ctx& ctx, const void* x, int x_dt, void* values, int v_dt, unsigned* indices, unsigned rows,
+                  unsigned width, unsigned k, bool normalize);
+// Fused q/k RMS-norm + RoPE + KV append for the dense step. qkv [rows, (hq + 2 kvh) * d] in `dt`;
+// q_out [rows, hq, d]; K/V rows go to the planes at slot_mapping[row] (slot 0xFFFFFFFF = skip).
+// qk_norm == 0: plain half-split RoPE with inv_freq (Op::Rope semantics, u32 positions).
+void launch_qknorm_rope_append(Ctx& ctx, const void* qkv, int dt, const void* q_norm_w, const void* k_norm_w,
+                               const unsigned* positions, const unsigned* slot_mapping, void* q_out, void* k_plane,
+                               void* v_plane, unsigned rows, unsigned q_heads, unsigned kv_heads, unsigned head_dim,
+                               float eps, const float* inv_freq, int qk_norm, unsigned plane_slots);
+
+// ---- fj_paged.cu ----------------------------------------------------------------------------
+// One sequence (lane) of a ragged attention launch. Pointers are device addresses.
+struct AttnSeq {
+  const void* q;                // first query row of the lane
+  void* out;
+  const unsigned* table;        // [table_pages][2] {page, generation}
+  const unsigned* activity;     // one word or nullptr (= active)
+  unsigned q_len, q_start, key_length, table_pages;
+  unsigned long long q_tok_stride, q_head_stride, o_tok_stride, o_head_stride;  // elements
+  unsigned causal;
+  unsigned pad;
+};
+struct AttnWork {
+  unsigned seq, kv_head, t_begin, t_end, split, n_splits, slot, group_index;
+};
+struct AttnGeometry {
+  unsigned q_heads, kv_heads, head_dim, value_dim, page_tokens, physical_pages;
+  int q_dtype, kv_dtype, out_dtype;
+  float scale;
+};
+// Scratch layout for split-K partials (device memory owned by the caller).
+struct AttnScratch {
+  float* part_o;        // [slots][16][head_dim]
+  float* part_ml;       // [slots][2][16]
+  unsigned* counters;   // [groups] (zero before first use; kernels leave them zero)
+};
+size_t attn_part_o_bytes(unsigned slots, unsigned head_dim);
+size_t attn_part_ml_bytes(unsigned slots);
+// Decode / short-query attention on tensor cores: requires q_len * (q_heads / kv_heads) <= 16,
+// head_dim == value_dim == 128, page_tokens == 16, 16-bit q/kv dtypes (same type).
+bool attn_decode_mma_supported(const AttnGeometry& g, unsigned max_q_len);
+void launch_attn_decode_mma(Ctx& ctx, const AttnGeometry& g, const AttnSeq* seqs, const AttnWork* work, unsigned n_work,
+                            const void* kpool, const void* vpool, const unsigned* generations, const AttnScratch& scratch,
+                            ErrorRecord* err);
+// Generic f32-math attention for any float dtypes, head_dim <= 256, any q_len (one CTA per
+// (sequence, head, query row)); used for f32 models and odd shapes.
+void launch_attn_generic(Ctx& ctx, const AttnGeometry& g, const AttnSeq* seqs, unsigned n_seqs, unsigned max_q_len,
+                         const void* kpool, const void* vpool, const unsigned* generations, ErrorRecord* err);
+// Paged copy of `tokens` rows between an ordinary [tokens, elements] tensor and a plane.
+void launch_paged_copy(Ctx& ctx, bool into_pages, void* ordinary, int o_dt, size_t o_row_stride, void* pool, int p_dt,
+                       const unsigned* table, unsigned table_pages, const unsigned* generations, unsigned physical_pages,
+                       unsigned start, unsigned tokens, unsigned page_tokens, unsigned elements, const unsigned* activity,
+                       ErrorRecord* err);
+
+// ---- fj_gemm.cu -----------------------------------------------------------------------------
+// C[M,N] = A[M,K] * W[N,K]^T ("NT": both operands K-major), f32 accumulation, output rounded once.
+// lda/ldw/ldc in elements. 16-bit path: mma.sync tiles for M > 16, warp-per-column GEMV below.
+size_t gemm_scratch_bytes(unsigned m, unsigned n, unsigned k);
+void launch_gemm_nt(Ctx& ctx, const void* a, int a_dt, size_t lda, const void* w, int w_dt, size_t ldw, void* c, int c_dt,
+                    size_t ldc, unsigned m, unsigned n, unsigned k, void* scratch, size_t scratch_bytes);
+// Fully strided fallback (any layout, batch): one thread per output element.
+void launch_matmul_generic(Ctx& ctx, const View& a, const View& b, const View& c, unsigned batch, unsigned m, unsigned n,
+                           unsigned k);
+
+// ---- fj_quant.cu ----------------------------------------------------------------------------
+// y[m,n] = sum_k x[m,k] * (scale[n,k/g] * q[n,k] + bias[n,k/g]); packed u32 [N, K*bits/32], LSB first.
+void launch_quant_matmul(Ctx& ctx, const void* x, int x_dt, const unsigned* packed, const void* scales, const void* biases,
+                         int p_dt, void* out, int out_dt, unsigned m, unsigned k, unsigned n, unsigned bits,
+                         unsigned group_size);
+// epilogue: 0 none; 1 silu(acc0) * acc1 (pair form); 2 acc0 + extra (weighted-sum form)
+void launch_gather_quant_matmul(Ctx& ctx, const void* x, int x_dt, const unsigned* packed, const void* scales,
+                                const void* biases, int p_dt, const unsigned* packed2, const void* scales2,
+                                const void* biases2, const unsigned* indices, void* out, int out_dt, unsigned rows,
+                                unsigned k, unsigned experts, unsigned n, unsigned routes, unsigned bits, unsigned group_size,
+                                int epilogue, ErrorRecord* err);
+void launch_gather_quant_weighted_sum(Ctx& ctx, const void* act, int a_dt, const unsigned* packed, const void* scales,
+                                      const void* biases, int p_dt, const unsigned* indices, const void* weights, int w_dt,
+                                      const void* extra, int e_dt, void* out, int out_dt, unsigned rows, unsigned routes,
+                                      unsigned k, unsigned experts, unsigned n, unsigned bits, unsigned group_size,
+                                      int epilogue, ErrorRecord* err);
+
+// ---- fj_pack.cu -----------------------------------------------------------------------------
+struct KvPoolDevice {
+  unsigned* free_stack;   // [physical_pages]; top at free_count - 1
+  unsigned* free_count;   // [1]
+  unsigned* generations;  // [physical_pages]
+  unsigned* tables;       // [lanes][table_pages][2]
+  unsigned* lane_pages;   // [lanes] pages bound to each lane
+  unsigned physical_pages, lanes, table_pages, page_tokens;
+};
+void launch_kvpool_init(Ctx& ctx, const KvPoolDevice& pool);
+void launch_kvpool_reserve(Ctx& ctx, const KvPoolDevice& pool, const unsigned* lanes, const unsigned* tokens, unsigned count,
+                           int* status);
+void launch_kvpool_release(Ctx& ctx, const KvPoolDevice& pool, const unsigned* lanes, unsigned count);
+struct PackOutputs {
+  unsigned *logical_lengths, *query_starts, *absolute_positions, *activity, *cu_seqlens, *positions, *slot_mapping, *row_lane;
+};
+void launch_pack_step(Ctx& ctx, const KvPoolDevice& pool, const unsigned* starts, const unsigned* tokens, unsigned lanes,
+                      const PackOutputs& out, unsigned rows_cap);
+// Builds AttnSeq / AttnWork lists for the dense step from packed metadata (one CTA).
+void launch_build_attn_lists(Ctx& ctx, const KvPoolDevice& pool, const PackOutputs& pack, unsigned lanes, unsigned kv_heads,
+                             unsigned chunk_tokens, const void* q_base, void* out_base, unsigned q_heads, unsigned head_dim,
+                             int elem_bytes, AttnSeq* seqs, AttnWork* work, unsigned* n_work, unsigned work_cap);
+
+}  // namespace fj

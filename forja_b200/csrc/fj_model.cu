@@ -1,0 +1,476 @@
+// Device-resident fast path of the continuous-batching forward step: the paged-KV pool with its
+// on-device allocator and packer, and the dense decoder step that strings the kernels together
+// without returning to the host between operators.
+//
+// Reference op order: Qwen3 dense, engines/qwen3/src/lib.rs:391-452 (layer) and :734-811 (sequence);
+// SmolLM2, engines/smollm2/src/optimized.rs:97-245. Every intermediate the reference materialises
+// is materialised here in the same dtype, so rounding points coincide.
+#include "fj_backend.h"
+
+#include <string.h>
+
+#include <algorithm>
+
+using namespace fjb;
+
+struct fj_kvpool {
+  fj_backend* be = nullptr;
+  fj::KvPoolDevice dev{};
+  uint64_t buf_free = 0, buf_count = 0, buf_gens = 0, buf_tables = 0, buf_lane_pages = 0;
+  // packer state
+  uint64_t buf_lane_meta[5] = {0, 0, 0, 0, 0};  // logical_lengths, query_starts, absolute_positions, activity, cu_seqlens
+  uint64_t buf_rows[3] = {0, 0, 0};             // positions, slot_mapping, row_lane
+  uint64_t buf_stage = 0;                       // starts | tokens staged on the device
+  uint32_t rows_cap = 0;
+  fj::PackOutputs pack{};
+  std::vector<uint32_t> host_starts, host_tokens;  // last packed step (host copy for grid sizing)
+  uint32_t rows = 0, lanes_packed = 0;
+};
+
+namespace {
+
+void* buf_ptr(fj_backend* be, uint64_t id) {
+  fj_buffer_rec* r = find_buffer(be, id);
+  return r ? r->ptr : nullptr;
+}
+
+bool ensure_row_buffers(fj_kvpool* pool, uint32_t rows) {
+  if (rows <= pool->rows_cap) return true;
+  fj_backend* be = pool->be;
+  cudaStreamSynchronize(be->stream);
+  uint32_t cap = std::max<uint32_t>(rows, std::max<uint32_t>(pool->rows_cap * 2, 256));
+  for (int i = 0; i < 3; ++i) {
+    if (pool->buf_rows[i]) {
+      fj_buffer_rec* r = find_buffer(be, pool->buf_rows[i]);
+      cudaFree(r->ptr);
+      be->used_bytes -= r->bytes;
+      be->buffers.erase(pool->buf_rows[i]);
+      pool->buf_rows[i] = 0;
+    }
+    if (alloc_buffer(be, static_cast<uint64_t>(cap) * 4, &pool->buf_rows[i]) != FJ_OK) return false;
+  }
+  pool->rows_cap = cap;
+  pool->pack.positions = static_cast<unsigned*>(buf_ptr(be, pool->buf_rows[0]));
+  pool->pack.slot_mapping = static_cast<unsigned*>(buf_ptr(be, pool->buf_rows[1]));
+  pool->pack.row_lane = static_cast<unsigned*>(buf_ptr(be, pool->buf_rows[2]));
+  return true;
+}
+
+}  // namespace
+
+extern "C" {
+
+int32_t fj_kvpool_create(fj_backend* be, uint32_t page_tokens, uint32_t physical_pages, uint32_t lanes, uint32_t table_pages, fj_kvpool** out) {
+  if (!be || !out || page_tokens == 0 || page_tokens > 4096 || physical_pages == 0 || lanes == 0 || table_pages == 0) return FJ_INVALID_INPUT;
+  std::lock_guard<std::mutex> lock(be->mutex);
+  cudaSetDevice(be->device);
+  auto* pool = new fj_kvpool();
+  pool->be = be;
+  int32_t st = FJ_OK;
+  auto need = [&](uint64_t bytes, uint64_t* id) { if (st == FJ_OK) st = alloc_buffer(be, bytes, id); };
+  need(static_cast<uint64_t>(physical_pages) * 4, &pool->buf_free);
+  need(16, &pool->buf_count);
+  need(static_cast<uint64_t>(physical_pages) * 4, &pool->buf_gens);
+  need(static_cast<uint64_t>(lanes) * table_pages * 8, &pool->buf_tables);
+  need(static_cast<uint64_t>(lanes) * 4, &pool->buf_lane_pages);
+  for (int i = 0; i < 4; ++i) need(static_cast<uint64_t>(lanes) * 4, &pool->buf_lane_meta[i]);
+  need(static_cast<uint64_t>(lanes + 1) * 4, &pool->buf_lane_meta[4]);
+  need(static_cast<uint64_t>(lanes) * 8, &pool->buf_stage);
+  if (st != FJ_OK) { delete pool; return st; }
+  pool->dev.free_stack = static_cast<unsigned*>(buf_ptr(be, pool->buf_free));
+  pool->dev.free_count = static_cast<unsigned*>(buf_ptr(be, pool->buf_count));
+  pool->dev.generations = static_cast<unsigned*>(buf_ptr(be, pool->buf_gens));
+  pool->dev.tables = static_cast<unsigned*>(buf_ptr(be, pool->buf_tables));
+  pool->dev.lane_pages = static_cast<unsigned*>(buf_ptr(be, pool->buf_lane_pages));
+  pool->dev.physical_pages = physical_pages; pool->dev.lanes = lanes; pool->dev.table_pages = table_pages; pool->dev.page_tokens = page_tokens;
+  pool->pack.logical_lengths = static_cast<unsigned*>(buf_ptr(be, pool->buf_lane_meta[0]));
+  pool->pack.query_starts = static_cast<unsigned*>(buf_ptr(be, pool->buf_lane_meta[1]));
+  pool->pack.absolute_positions = static_cast<unsigned*>(buf_ptr(be, pool->buf_lane_meta[2]));
+  pool->pack.activity = static_cast<unsigned*>(buf_ptr(be, pool->buf_lane_meta[3]));
+  pool->pack.cu_seqlens = static_cast<unsigned*>(buf_ptr(be, pool->buf_lane_meta[4]));
+  if (!ensure_row_buffers(pool, 256)) { delete pool; return FJ_ALLOCATION_FAILED; }
+  fj::launch_kvpool_init(be->ctx, pool->dev);
+  *out = pool;
+  return cuda_status(cudaStreamSynchronize(be->stream));
+}
+
+void fj_kvpool_destroy(fj_kvpool* pool) {
+  if (!pool) return;
+  fj_backend* be = pool->be;
+  std::lock_guard<std::mutex> lock(be->mutex);
+  cudaSetDevice(be->device);
+  cudaStreamSynchronize(be->stream);
+  uint64_t ids[] = {pool->buf_free, pool->buf_count, pool->buf_gens, pool->buf_tables, pool->buf_lane_pages, pool->buf_lane_meta[0], pool->buf_lane_meta[1],
+                    pool->buf_lane_meta[2], pool->buf_lane_meta[3], pool->buf_lane_meta[4], pool->buf_rows[0], pool->buf_rows[1], pool->buf_rows[2], pool->buf_stage};
+  for (uint64_t id : ids) {
+    fj_buffer_rec* r = id ? find_buffer(be, id) : nullptr;
+    if (r) { cudaFree(r->ptr); be->used_bytes -= r->bytes; be->buffers.erase(id); }
+  }
+  delete pool;
+}
+
+int32_t fj_kvpool_reserve(fj_kvpool* pool, const uint32_t* lanes, const uint32_t* tokens, uint32_t count, int32_t* status) {
+  if (!pool || (count && (!lanes || !tokens))) return FJ_INVALID_INPUT;
+  if (count == 0) return FJ_OK;
+  fj_backend* be = pool->be;
+  std::lock_guard<std::mutex> lock(be->mutex);
+  cudaSetDevice(be->device);
+  unsigned* staged = nullptr;
+  if (cudaMallocAsync(reinterpret_cast<void**>(&staged), static_cast<size_t>(count) * 12, be->stream) != cudaSuccess) { cudaGetLastError(); return FJ_ALLOCATION_FAILED; }
+  cudaMemcpyAsync(staged, lanes, count * 4, cudaMemcpyHostToDevice, be->stream);
+  cudaMemcpyAsync(staged + count, tokens, count * 4, cudaMemcpyHostToDevice, be->stream);
+  int* dev_status = reinterpret_cast<int*>(staged + 2 * count);
+  fj::launch_kvpool_reserve(be->ctx, pool->dev, staged, staged + count, count, dev_status);
+  int32_t result = FJ_OK;
+  if (status) {
+    cudaMemcpyAsync(status, dev_status, count * 4, cudaMemcpyDeviceToHost, be->stream);
+    result = cuda_status(cudaStreamSynchronize(be->stream));
+  }
+  cudaFreeAsync(staged, be->stream);
+  return result;
+}
+
+int32_t fj_kvpool_release(fj_kvpool* pool, const uint32_t* lanes, uint32_t count) {
+  if (!pool || (count && !lanes)) return FJ_INVALID_INPUT;
+  if (count == 0) return FJ_OK;
+  fj_backend* be = pool->be;
+  std::lock_guard<std::mutex> lock(be->mutex);
+  cudaSetDevice(be->device);
+  unsigned* staged = nullptr;
+  if (cudaMallocAsync(reinterpret_cast<void**>(&staged), static_cast<size_t>(count) * 4, be->stream) != cudaSuccess) { cudaGetLastError(); return FJ_ALLOCATION_FAILED; }
+  cudaMemcpyAsync(staged, lanes, count * 4, cudaMemcpyHostToDevice, be->stream);
+  fj::launch_kvpool_release(be->ctx, pool->dev, staged, count);
+  cudaFreeAsync(staged, be->stream);
+  return FJ_OK;
+}
+
+int32_t fj_kvpool_read_table(fj_kvpool* pool, uint32_t lane, uint32_t* entries) {
+  if (!pool || !entries || lane >= pool->dev.lanes) return FJ_INVALID_INPUT;
+  return fj_read(pool->be, pool->buf_tables, static_cast<uint64_t>(lane) * pool->dev.table_pages * 8, entries, static_cast<uint64_t>(pool->dev.table_pages) * 8);
+}
+int32_t fj_kvpool_read_generations(fj_kvpool* pool, uint32_t* generations) {
+  if (!pool || !generations) return FJ_INVALID_INPUT;
+  return fj_read(pool->be, pool->buf_gens, 0, generations, static_cast<uint64_t>(pool->dev.physical_pages) * 4);
+}
+int32_t fj_kvpool_read_free(fj_kvpool* pool, uint32_t* pages, uint32_t cap, uint32_t* count) {
+  if (!pool || !count) return FJ_INVALID_INPUT;
+  uint32_t n = 0;
+  int32_t st = fj_read(pool->be, pool->buf_count, 0, &n, 4);
+  if (st != FJ_OK) return st;
+  *count = n;
+  if (pages && n) return fj_read(pool->be, pool->buf_free, 0, pages, static_cast<uint64_t>(std::min(n, cap)) * 4);
+  return FJ_OK;
+}
+uint64_t fj_kvpool_tables_buffer(fj_kvpool* pool) { return pool ? pool->buf_tables : 0; }
+uint64_t fj_kvpool_generations_buffer(fj_kvpool* pool) { return pool ? pool->buf_gens : 0; }
+
+int32_t fj_pack_step(fj_kvpool* pool, const uint32_t* starts, const uint32_t* tokens, uint32_t lanes, fj_pack_view* out) {
+  if (!pool || !starts || !tokens || lanes == 0 || lanes > pool->dev.lanes) return FJ_INVALID_INPUT;
+  fj_backend* be = pool->be;
+  std::lock_guard<std::mutex> lock(be->mutex);
+  cudaSetDevice(be->device);
+  uint64_t rows = 0;
+  for (uint32_t i = 0; i < lanes; ++i) {
+    if (tokens[i] && static_cast<uint64_t>(starts[i]) + tokens[i] - 1 > 0xFFFFFFFFull) return FJ_INVALID_INPUT;  // "batch absolute position overflowed"
+    rows += tokens[i];
+  }
+  if (rows > 0x7FFFFFFFull || !ensure_row_buffers(pool, static_cast<uint32_t>(rows))) return FJ_ALLOCATION_FAILED;
+  unsigned* staged = static_cast<unsigned*>(buf_ptr(be, pool->buf_stage));
+  cudaMemcpyAsync(staged, starts, lanes * 4, cudaMemcpyHostToDevice, be->stream);
+  cudaMemcpyAsync(staged + pool->dev.lanes, tokens, lanes * 4, cudaMemcpyHostToDevice, be->stream);
+  fj::launch_pack_step(be->ctx, pool->dev, staged, staged + pool->dev.lanes, lanes, pool->pack, pool->rows_cap);
+  pool->host_starts.assign(starts, starts + lanes);
+  pool->host_tokens.assign(tokens, tokens + lanes);
+  pool->rows = static_cast<uint32_t>(rows);
+  pool->lanes_packed = lanes;
+  if (out) {
+    out->rows = pool->rows; out->lanes = lanes;
+    out->logical_lengths = pool->buf_lane_meta[0]; out->query_starts = pool->buf_lane_meta[1]; out->absolute_positions = pool->buf_lane_meta[2];
+    out->activity = pool->buf_lane_meta[3]; out->cu_seqlens = pool->buf_lane_meta[4];
+    out->positions = pool->buf_rows[0]; out->slot_mapping = pool->buf_rows[1]; out->row_lane = pool->buf_rows[2];
+  }
+  return FJ_OK;
+}
+
+}  // extern "C"
+
+// ---------------------------------------------------------------------------------------------
+// dense decoder
+// ---------------------------------------------------------------------------------------------
+
+struct fj_dense_model {
+  fj_backend* be = nullptr;
+  fj_kvpool* pool = nullptr;
+  fj_dense_config cfg{};
+  const void* embed = nullptr;
+  const void* final_norm = nullptr;
+  struct Layer { const void *input_norm, *q_norm, *k_norm, *wo, *post_norm, *w_down; void *wqkv, *w_gate_up, *k_plane, *v_plane; };
+  std::vector<Layer> layers;
+  std::vector<void*> owned;  // device allocations of the model
+  // workspace
+  void *hidden = nullptr, *hidden2 = nullptr, *normed = nullptr, *qkv = nullptr, *q = nullptr, *attn = nullptr, *proj = nullptr, *gate_up = nullptr, *act = nullptr;
+  void *last_hidden = nullptr, *last_normed = nullptr, *logits = nullptr, *argmax_scratch = nullptr;
+  unsigned *tokens_in = nullptr, *tokens_out = nullptr;
+  fj::AttnSeq* seqs = nullptr;
+  fj::AttnWork* work = nullptr;
+  unsigned* n_work_dev = nullptr;
+  uint32_t work_cap = 0;
+  const float* inv_freq = nullptr;
+  uint64_t last_kernels = 0, last_work_items = 0;
+};
+
+namespace {
+
+__global__ void feedback_tokens_kernel(const unsigned* __restrict__ cu_seqlens, const unsigned* __restrict__ previous, unsigned* tokens, unsigned lanes) {
+  unsigned lane = blockIdx.x * blockDim.x + threadIdx.x;
+  if (lane >= lanes) return;
+  unsigned begin = cu_seqlens[lane], end = cu_seqlens[lane + 1];
+  if (end > begin) tokens[end - 1] = previous[lane];
+}
+
+// last row of each lane -> [lanes, hidden]; inactive lanes get zeros
+template <typename T>
+__global__ void gather_last_rows_kernel(const T* __restrict__ hidden, const unsigned* __restrict__ cu_seqlens, T* out, unsigned lanes, unsigned width) {
+  for (unsigned lane = blockIdx.x; lane < lanes; lane += gridDim.x) {
+    unsigned begin = cu_seqlens[lane], end = cu_seqlens[lane + 1];
+    for (unsigned i = threadIdx.x; i < width; i += blockDim.x)
+      out[static_cast<size_t>(lane) * width + i] = end > begin ? hidden[static_cast<size_t>(end - 1) * width + i] : T{};
+  }
+}
+
+fj::View dense_view(void* base, int dtype, unsigned rows, unsigned width, size_t row_stride) {
+  fj::View v;
+  v.base = base; v.dtype = dtype; v.rank = 2;
+  for (int a = 0; a < 8; ++a) { v.shape[a] = 1; v.strides[a] = 0; }
+  v.shape[0] = rows; v.shape[1] = width; v.strides[0] = row_stride; v.strides[1] = 1;
+  return v;
+}
+fj::View weight_view(const void* base, int dtype, unsigned rows, unsigned width) {
+  fj::View v = dense_view(const_cast<void*>(base), dtype, rows, width, 0);
+  return v;
+}
+
+}  // namespace
+
+extern "C" {
+
+int32_t fj_dense_model_create(fj_backend* be, const fj_dense_config* config, uint64_t embed, uint64_t final_norm, const fj_dense_layer_weights* layers,
+                              fj_kvpool* pool, fj_dense_model** out) {
+  if (!be || !config || !layers || !pool || !out || pool->be != be) return FJ_INVALID_INPUT;
+  const fj_dense_config& c = *config;
+  if ((c.dtype != FJ_F32 && c.dtype != FJ_BF16 && c.dtype != FJ_F16) || c.layers == 0 || c.kv_heads == 0 || c.q_heads % c.kv_heads != 0 || c.head_dim % 2 != 0 || c.head_dim > 256 ||
+      c.max_rows == 0 || c.hidden == 0 || c.vocab == 0 || c.intermediate == 0)
+    return FJ_INVALID_INPUT;
+  std::lock_guard<std::mutex> lock(be->mutex);
+  cudaSetDevice(be->device);
+  const size_t esz = fj::dtype_size(c.dtype);
+  auto* m = new fj_dense_model();
+  m->be = be; m->pool = pool; m->cfg = c;
+  bool ok = true;
+  auto dev_alloc = [&](size_t bytes) -> void* {
+    void* p = nullptr;
+    if (!ok) return nullptr;
+    if (be->limit_bytes && be->used_bytes + bytes > be->limit_bytes) { ok = false; return nullptr; }
+    if (cudaMalloc(&p, std::max<size_t>(bytes, 16)) != cudaSuccess) { cudaGetLastError(); ok = false; return nullptr; }
+    cudaMemsetAsync(p, 0, std::max<size_t>(bytes, 16), be->stream);
+    be->used_bytes += bytes;
+    m->owned.push_back(p);
+    return p;
+  };
+  auto weight = [&](uint64_t id, uint64_t elements) -> const void* {
+    fj_buffer_rec* r = find_buffer(be, id);
+    if (!r || r->bytes < elements * esz) { ok = false; return nullptr; }
+    return r->ptr;
+  };
+  const uint64_t qd = static_cast<uint64_t>(c.q_heads) * c.head_dim, kd = static_cast<uint64_t>(c.kv_heads) * c.head_dim;
+  m->embed = weight(embed, static_cast<uint64_t>(c.vocab) * c.hidden);
+  m->final_norm = weight(final_norm, c.hidden);
+  const size_t plane_bytes = static_cast<size_t>(pool->dev.physical_pages) * pool->dev.page_tokens * kd * esz;
+  m->layers.resize(c.layers);
+  for (uint32_t l = 0; l < c.layers && ok; ++l) {
+    const fj_dense_layer_weights& w = layers[l];
+    auto& L = m->layers[l];
+    L.input_norm = weight(w.input_norm, c.hidden);
+    L.post_norm = weight(w.post_norm, c.hidden);
+    L.wo = weight(w.wo, static_cast<uint64_t>(c.hidden) * qd);
+    L.w_down = weight(w.w_down, static_cast<uint64_t>(c.hidden) * c.intermediate);
+    L.q_norm = c.qk_norm ? weight(w.q_norm, c.head_dim) : nullptr;
+    L.k_norm = c.qk_norm ? weight(w.k_norm, c.head_dim) : nullptr;
+    const void *wq = weight(w.wq, qd * c.hidden), *wk = weight(w.wk, kd * c.hidden), *wv = weight(w.wv, kd * c.hidden);
+    const void *wg = weight(w.w_gate, static_cast<uint64_t>(c.intermediate) * c.hidden), *wu = weight(w.w_up, static_cast<uint64_t>(c.intermediate) * c.hidden);
+    // stacked projection weights: one GEMM for q|k|v and one for gate|up (same per-element arithmetic)
+    L.wqkv = dev_alloc((qd + 2 * kd) * c.hidden * esz);
+    L.w_gate_up = dev_alloc(2ull * c.intermediate * c.hidden * esz);
+    L.k_plane = dev_alloc(plane_bytes);
+    L.v_plane = dev_alloc(plane_bytes);
+    if (!ok) break;
+    char* dst = static_cast<char*>(L.wqkv);
+    cudaMemcpyAsync(dst, wq, qd * c.hidden * esz, cudaMemcpyDeviceToDevice, be->stream);
+    cudaMemcpyAsync(dst + qd * c.hidden * esz, wk, kd * c.hidden * esz, cudaMemcpyDeviceToDevice, be->stream);
+    cudaMemcpyAsync(dst + (qd + kd) * c.hidden * esz, wv, kd * c.hidden * esz, cudaMemcpyDeviceToDevice, be->stream);
+    dst = static_cast<char*>(L.w_gate_up);
+    cudaMemcpyAsync(dst, wg, static_cast<size_t>(c.intermediate) * c.hidden * esz, cudaMemcpyDeviceToDevice, be->stream);
+    cudaMemcpyAsync(dst + static_cast<size_t>(c.intermediate) * c.hidden * esz, wu, static_cast<size_t>(c.intermediate) * c.hidden * esz, cudaMemcpyDeviceToDevice, be->stream);
+  }
+  const size_t R = c.max_rows, Lanes = pool->dev.lanes;
+  m->hidden = dev_alloc(R * c.hidden * esz);
+  m->hidden2 = dev_alloc(R * c.hidden * esz);
+  m->normed = dev_alloc(R * c.hidden * esz);
+  m->qkv = dev_alloc(R * (qd + 2 * kd) * esz);
+  m->q = dev_alloc(R * qd * esz);
+  m->attn = dev_alloc(R * qd * esz);
+  m->proj = dev_alloc(R * c.hidden * esz);
+  m->gate_up = dev_alloc(R * 2 * c.intermediate * esz);
+  m->act = dev_alloc(R * c.intermediate * esz);
+  m->last_hidden = dev_alloc(Lanes * c.hidden * esz);
+  m->last_normed = dev_alloc(Lanes * c.hidden * esz);
+  m->logits = dev_alloc(Lanes * c.vocab * esz);
+  m->argmax_scratch = dev_alloc(fj::argmax_scratch_bytes(static_cast<unsigned>(Lanes), c.vocab));
+  m->tokens_in = static_cast<unsigned*>(dev_alloc(R * 4));
+  m->tokens_out = static_cast<unsigned*>(dev_alloc(Lanes * 4));
+  m->seqs = static_cast<fj::AttnSeq*>(dev_alloc(Lanes * sizeof(fj::AttnSeq)));
+  // work items: every lane may be split into table_pages * page_tokens / 64 chunks in the worst case;
+  // the list is sized for the pool's token capacity instead, which bounds the sum over lanes
+  const uint64_t token_capacity = static_cast<uint64_t>(pool->dev.physical_pages) * pool->dev.page_tokens;
+  m->work_cap = static_cast<uint32_t>(std::min<uint64_t>((token_capacity / 64 + Lanes) * c.kv_heads, 1u << 22));
+  m->work = static_cast<fj::AttnWork*>(dev_alloc(static_cast<size_t>(m->work_cap) * sizeof(fj::AttnWork)));
+  m->n_work_dev = static_cast<unsigned*>(dev_alloc(16));
+  if (ok) {
+    m->inv_freq = c.qk_norm ? freq_table(be, c.theta, -2.0f / static_cast<float>(c.head_dim), c.head_dim / 2, false)
+                            : freq_table(be, c.theta, 0.0f, c.head_dim / 2, true);
+    ok = m->inv_freq != nullptr;
+  }
+  if (ok) ok = ensure_gemm_scratch(be, fj::gemm_scratch_bytes(static_cast<unsigned>(R), std::max<unsigned>({2 * c.intermediate, static_cast<unsigned>(qd + 2 * kd), c.hidden}), c.hidden));
+  if (!ok || cudaStreamSynchronize(be->stream) != cudaSuccess) {
+    for (void* p : m->owned) cudaFree(p);
+    delete m;
+    return FJ_ALLOCATION_FAILED;
+  }
+  *out = m;
+  return FJ_OK;
+}
+
+void fj_dense_model_destroy(fj_dense_model* m) {
+  if (!m) return;
+  std::lock_guard<std::mutex> lock(m->be->mutex);
+  cudaSetDevice(m->be->device);
+  cudaStreamSynchronize(m->be->stream);
+  for (void* p : m->owned) cudaFree(p);
+  delete m;
+}
+
+int32_t fj_dense_step(fj_dense_model* m, const uint32_t* token_ids, uint32_t* out_tokens, uint64_t logits_out) {
+  if (!m) return FJ_INVALID_INPUT;
+  fj_backend* be = m->be;
+  fj_kvpool* pool = m->pool;
+  std::lock_guard<std::mutex> lock(be->mutex);
+  cudaSetDevice(be->device);
+  const fj_dense_config& c = m->cfg;
+  const unsigned rows = pool->rows, lanes = pool->lanes_packed;
+  if (rows == 0 || lanes == 0) return FJ_INVALID_INPUT;
+  if (rows > c.max_rows) return FJ_INVALID_INPUT;
+  const int dt = static_cast<int>(c.dtype);
+  const size_t esz = fj::dtype_size(dt);
+  const unsigned qd = c.q_heads * c.head_dim, kd = c.kv_heads * c.head_dim, H = c.hidden, I = c.intermediate;
+  fj::Ctx& ctx = be->ctx;
+  const unsigned long long launches_before = ctx.launches;
+
+  if (token_ids) cudaMemcpyAsync(m->tokens_in, token_ids, static_cast<size_t>(rows) * 4, cudaMemcpyHostToDevice, be->stream);
+  else { feedback_tokens_kernel<<<(lanes + 127) / 128, 128, 0, be->stream>>>(pool->pack.cu_seqlens, m->tokens_out, m->tokens_in, lanes); ctx.launches++; }
+
+  // attention plan for this step (shared by all layers: q and attn buffers do not move)
+  const unsigned group = c.q_heads / c.kv_heads;
+  unsigned max_q_len = 0;
+  uint64_t total_keys = 0;
+  for (unsigned l = 0; l < lanes; ++l) {
+    max_q_len = std::max(max_q_len, pool->host_tokens[l]);
+    if (pool->host_tokens[l]) total_keys += static_cast<uint64_t>(pool->host_starts[l]) + pool->host_tokens[l];
+  }
+  fj::AttnGeometry g;
+  g.q_heads = c.q_heads; g.kv_heads = c.kv_heads; g.head_dim = c.head_dim; g.value_dim = c.head_dim; g.page_tokens = pool->dev.page_tokens;
+  g.physical_pages = pool->dev.physical_pages; g.q_dtype = dt; g.kv_dtype = dt; g.out_dtype = dt;
+  g.scale = 1.0f / sqrtf(static_cast<float>(c.head_dim));
+  const bool mma = fj::attn_decode_mma_supported(g, max_q_len) && max_q_len * group <= 16;
+  uint64_t chunk = 64, n_work = 0;
+  if (mma) {
+    const uint64_t target_items = static_cast<uint64_t>(ctx.sm_count) * 2 * 4;
+    chunk = (total_keys * c.kv_heads + target_items - 1) / std::max<uint64_t>(target_items, 1);
+    chunk = std::min<uint64_t>(std::max<uint64_t>((chunk + 63) / 64 * 64, 64), 1024);
+    for (unsigned l = 0; l < lanes; ++l)
+      if (pool->host_tokens[l]) n_work += ((static_cast<uint64_t>(pool->host_starts[l]) + pool->host_tokens[l] + chunk - 1) / chunk) * c.kv_heads;
+    if (n_work > m->work_cap) return FJ_QUOTA_EXCEEDED;
+  }
+  fj::launch_build_attn_lists(ctx, pool->dev, pool->pack, lanes, c.kv_heads, static_cast<unsigned>(chunk), m->q, m->attn, c.q_heads, c.head_dim, static_cast<int>(esz), m->seqs,
+                              m->work, m->n_work_dev, m->work_cap);
+  fj::AttnScratch scratch{nullptr, nullptr, nullptr};
+  if (mma) {
+    const size_t groups = static_cast<size_t>(lanes) * c.kv_heads;
+    const size_t counter_bytes = (groups * sizeof(unsigned) + 255) / 256 * 256;
+    const size_t o_bytes = fj::attn_part_o_bytes(static_cast<unsigned>(n_work), c.head_dim), ml_bytes = fj::attn_part_ml_bytes(static_cast<unsigned>(n_work));
+    if (!ensure_attn_scratch(be, counter_bytes + o_bytes + ml_bytes)) return FJ_ALLOCATION_FAILED;
+    scratch.counters = static_cast<unsigned*>(be->attn_scratch);
+    scratch.part_o = reinterpret_cast<float*>(static_cast<char*>(be->attn_scratch) + counter_bytes);
+    scratch.part_ml = reinterpret_cast<float*>(static_cast<char*>(be->attn_scratch) + counter_bytes + o_bytes);
+  }
+
+  fj::launch_embed(ctx, m->embed, dt, m->tokens_in, m->hidden, dt, c.vocab, H, rows, nullptr);
+  void* hidden = m->hidden;
+  void* other = m->hidden2;
+  fj::launch_rms_norm(ctx, dense_view(hidden, dt, rows, H, H), weight_view(m->layers[0].input_norm, dt, rows, H), dense_view(m->normed, dt, rows, H, H), rows, H, c.eps);
+  const unsigned plane_slots = pool->dev.physical_pages * pool->dev.page_tokens;
+  for (uint32_t l = 0; l < c.layers; ++l) {
+    const auto& L = m->layers[l];
+    fj::launch_gemm_nt(ctx, m->normed, dt, H, L.wqkv, dt, H, m->qkv, dt, qd + 2 * kd, rows, qd + 2 * kd, H, be->gemm_scratch, be->gemm_scratch_bytes);
+    fj::launch_qknorm_rope_append(ctx, m->qkv, dt, L.q_norm, L.k_norm, pool->pack.positions, pool->pack.slot_mapping, m->q, L.k_plane, L.v_plane, rows, c.q_heads, c.kv_heads,
+                                  c.head_dim, c.eps, m->inv_freq, c.qk_norm ? 1 : 0, plane_slots);
+    if (mma) fj::launch_attn_decode_mma(ctx, g, m->seqs, m->work, static_cast<unsigned>(n_work), L.k_plane, L.v_plane, pool->dev.generations, scratch, nullptr);
+    else fj::launch_attn_generic(ctx, g, m->seqs, lanes, max_q_len, L.k_plane, L.v_plane, pool->dev.generations, nullptr);
+    fj::launch_gemm_nt(ctx, m->attn, dt, qd, L.wo, dt, qd, m->proj, dt, H, rows, H, qd, be->gemm_scratch, be->gemm_scratch_bytes);
+    // hidden' = hidden + attention ; normed = rms(hidden') * post_norm
+    fj::launch_residual_norm(ctx, dense_view(hidden, dt, rows, H, H), dense_view(m->proj, dt, rows, H, H), weight_view(L.post_norm, dt, rows, H), dense_view(other, dt, rows, H, H),
+                             dense_view(m->normed, dt, rows, H, H), rows, H, c.eps);
+    std::swap(hidden, other);
+    fj::launch_gemm_nt(ctx, m->normed, dt, H, L.w_gate_up, dt, H, m->gate_up, dt, 2 * I, rows, 2 * I, H, be->gemm_scratch, be->gemm_scratch_bytes);
+    fj::launch_silu_mul(ctx, dense_view(m->gate_up, dt, rows, I, 2 * I), dense_view(static_cast<char*>(m->gate_up) + static_cast<size_t>(I) * esz, dt, rows, I, 2 * I),
+                        dense_view(m->act, dt, rows, I, I), static_cast<size_t>(rows) * I);
+    fj::launch_gemm_nt(ctx, m->act, dt, I, L.w_down, dt, I, m->proj, dt, H, rows, H, I, be->gemm_scratch, be->gemm_scratch_bytes);
+    if (l + 1 < c.layers) {
+      fj::launch_residual_norm(ctx, dense_view(hidden, dt, rows, H, H), dense_view(m->proj, dt, rows, H, H), weight_view(m->layers[l + 1].input_norm, dt, rows, H),
+                               dense_view(other, dt, rows, H, H), dense_view(m->normed, dt, rows, H, H), rows, H, c.eps);
+    } else {
+      fj::launch_add(ctx, dense_view(hidden, dt, rows, H, H), dense_view(m->proj, dt, rows, H, H), dense_view(other, dt, rows, H, H), static_cast<size_t>(rows) * H);
+    }
+    std::swap(hidden, other);
+  }
+  // last row of every lane -> final norm -> tied lm_head -> greedy token
+  if (dt == FJ_F32) gather_last_rows_kernel<float><<<std::min(lanes, 1024u), 256, 0, be->stream>>>(static_cast<const float*>(hidden), pool->pack.cu_seqlens, static_cast<float*>(m->last_hidden), lanes, H);
+  else gather_last_rows_kernel<unsigned short><<<std::min(lanes, 1024u), 256, 0, be->stream>>>(static_cast<const unsigned short*>(hidden), pool->pack.cu_seqlens, static_cast<unsigned short*>(m->last_hidden), lanes, H);
+  ctx.launches++;
+  fj::launch_rms_norm(ctx, dense_view(m->last_hidden, dt, lanes, H, H), weight_view(m->final_norm, dt, lanes, H), dense_view(m->last_normed, dt, lanes, H, H), lanes, H, c.eps);
+  void* logits = m->logits;
+  if (logits_out) {
+    fj_buffer_rec* r = find_buffer(be, logits_out);
+    if (!r || r->readonly || r->bytes < static_cast<uint64_t>(lanes) * c.vocab * esz) return FJ_INVALID_INPUT;
+    logits = r->ptr;
+  }
+  fj::launch_gemm_nt(ctx, m->last_normed, dt, H, m->embed, dt, H, logits, dt, c.vocab, lanes, c.vocab, H, be->gemm_scratch, be->gemm_scratch_bytes);
+  fj::launch_argmax(ctx, logits, dt, c.vocab, m->tokens_out, lanes, c.vocab, m->argmax_scratch);
+  m->last_kernels = ctx.launches - launches_before;
+  m->last_work_items = n_work;
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return FJ_DEVICE_EXECUTION_FAILED;
+  if (out_tokens) {
+    cudaMemcpyAsync(out_tokens, m->tokens_out, static_cast<size_t>(lanes) * 4, cudaMemcpyDeviceToHost, be->stream);
+    return cuda_status(cudaStreamSynchronize(be->stream));
+  }
+  return FJ_OK;
+}
+
+int32_t fj_dense_step_stats(fj_dense_model* m, uint64_t* kernels, uint64_t* attn_work_items) {
+  if (!m) return FJ_INVALID_INPUT;
+  if (kernels) *kernels = m->last_kernels;
+  if (attn_work_items) *attn_work_items = m->last_work_items;
+  return FJ_OK;
+}
+
+}  // extern "C"

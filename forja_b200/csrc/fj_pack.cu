@@ -1,0 +1,236 @@
+// Device-resident bookkeeping of the continuous-batching step: the paged-KV page allocator and the
+// ragged-batch packer. All of it is integer work that must equal the host reference bit for bit:
+//  * allocator: LIFO free stack with page 0 on top after initialisation, generation + 1 on every
+//    allocation and never 0xFFFFFFFF, refusals change nothing (PagePool::reserve / release /
+//    add_slab / allocate_pages, crates/forja-core/src/paged_pool.rs:204-232, 308-327, 1229-1326);
+//  * packer: per-lane logical_length / query_start / absolute_position / activity
+//    (write_paged_lane_metadata, crates/forja-host/src/lib.rs:4977-5065) plus cu_seqlens, per-row
+//    positions, slot_mapping (= physical page * page_tokens + offset) and row_lane.
+// One CTA per call keeps request order deterministic; these kernels are latency-bound (a few
+// microseconds) and replace host loops plus several small host-to-device copies per step.
+#include "fj_kernels.h"
+
+namespace fj {
+
+namespace {
+
+constexpr unsigned POISON = 0xFFFFFFFFu;
+constexpr int kPackThreads = 256;
+
+__global__ void kvpool_init_kernel(KvPoolDevice pool) {
+  for (unsigned i = threadIdx.x; i < pool.physical_pages; i += blockDim.x) {
+    pool.free_stack[i] = pool.physical_pages - 1 - i;  // (start..end).rev(): page 0 pops first
+    pool.generations[i] = 0;
+  }
+  for (size_t i = threadIdx.x; i < static_cast<size_t>(pool.lanes) * pool.table_pages; i += blockDim.x) {
+    pool.tables[2 * i] = 0;
+    pool.tables[2 * i + 1] = POISON;
+  }
+  for (unsigned i = threadIdx.x; i < pool.lanes; i += blockDim.x) pool.lane_pages[i] = 0;
+  if (threadIdx.x == 0) *pool.free_count = pool.physical_pages;
+}
+
+__global__ void kvpool_reserve_kernel(KvPoolDevice pool, const unsigned* __restrict__ lanes, const unsigned* __restrict__ tokens,
+                                      unsigned count, int* status) {
+  __shared__ int s_status;
+  __shared__ unsigned s_free;
+  for (unsigned i = 0; i < count; ++i) {
+    const unsigned lane = lanes[i];
+    const unsigned need = tokens[i] == 0 ? 0 : (tokens[i] + pool.page_tokens - 1) / pool.page_tokens;
+    if (threadIdx.x == 0) {
+      s_free = *pool.free_count;
+      int st = 0;  // FJ_OK
+      if (lane >= pool.lanes || need > pool.table_pages || pool.lane_pages[lane] != 0) st = 7;  // FJ_INVALID_INPUT
+      else if (need > s_free) st = 1;                                                         // FJ_QUOTA_EXCEEDED
+      s_status = st;
+    }
+    __syncthreads();
+    if (s_status == 0) {
+      // preflight: no page of the request may step onto the poison generation
+      int overflow = 0;
+      for (unsigned j = threadIdx.x; j < need; j += blockDim.x) {
+        unsigned g = pool.generations[pool.free_stack[s_free - 1 - j]];
+        if (g >= POISON - 1) overflow = 1;
+      }
+      overflow = __syncthreads_or(overflow);
+      if (overflow) {
+        if (threadIdx.x == 0) s_status = 3;  // FJ_EXECUTION_FAILED (arithmetic overflow in the reference)
+      } else {
+        for (unsigned j = threadIdx.x; j < need; j += blockDim.x) {
+          const unsigned page = pool.free_stack[s_free - 1 - j];
+          const unsigned g = pool.generations[page] + 1;
+          pool.generations[page] = g;
+          pool.tables[(static_cast<size_t>(lane) * pool.table_pages + j) * 2] = page;
+          pool.tables[(static_cast<size_t>(lane) * pool.table_pages + j) * 2 + 1] = g;
+        }
+        if (threadIdx.x == 0) { *pool.free_count = s_free - need; pool.lane_pages[lane] = need; }
+      }
+    }
+    __syncthreads();
+    if (threadIdx.x == 0 && status != nullptr) status[i] = s_status;
+    __syncthreads();
+  }
+}
+
+__global__ void kvpool_release_kernel(KvPoolDevice pool, const unsigned* __restrict__ lanes, unsigned count) {
+  __shared__ unsigned s_free, s_pages;
+  for (unsigned i = 0; i < count; ++i) {
+    const unsigned lane = lanes[i];
+    if (lane >= pool.lanes) continue;
+    if (threadIdx.x == 0) { s_free = *pool.free_count; s_pages = pool.lane_pages[lane]; }
+    __syncthreads();
+    const unsigned pages = s_pages;
+    for (unsigned j = threadIdx.x; j < pages; j += blockDim.x) {
+      const size_t e = (static_cast<size_t>(lane) * pool.table_pages + j) * 2;
+      pool.free_stack[s_free + j] = pool.tables[e];  // sequence order: the last page ends on top
+      pool.tables[e] = 0;
+      pool.tables[e + 1] = POISON;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) { *pool.free_count = s_free + pages; pool.lane_pages[lane] = 0; }
+    __syncthreads();
+  }
+}
+
+// Exclusive scan of per-lane values over one CTA (lanes processed in chunks of blockDim.x).
+__device__ inline unsigned block_exclusive_scan(unsigned value, unsigned* total, unsigned* warp_sums) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  unsigned inclusive = value;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    unsigned n = __shfl_up_sync(0xffffffffu, inclusive, o);
+    if (lane >= o) inclusive += n;
+  }
+  __syncthreads();
+  if (lane == 31) warp_sums[warp] = inclusive;
+  __syncthreads();
+  unsigned offset = 0;
+  const int warps = blockDim.x >> 5;
+  for (int w = 0; w < warps; ++w) {
+    if (w < warp) offset += warp_sums[w];
+  }
+  unsigned sum_all = 0;
+  for (int w = 0; w < warps; ++w) sum_all += warp_sums[w];
+  *total = sum_all;
+  return offset + inclusive - value;
+}
+
+__global__ void pack_step_kernel(KvPoolDevice pool, const unsigned* __restrict__ starts, const unsigned* __restrict__ tokens,
+                                 unsigned lanes, PackOutputs out, unsigned rows_cap) {
+  __shared__ unsigned warp_sums[kPackThreads / 32];
+  __shared__ unsigned s_base;
+  if (threadIdx.x == 0) { s_base = 0; out.cu_seqlens[0] = 0; }
+  __syncthreads();
+  for (unsigned l0 = 0; l0 < lanes; l0 += blockDim.x) {
+    const unsigned lane = l0 + threadIdx.x;
+    const unsigned t = lane < lanes ? tokens[lane] : 0;
+    unsigned total;
+    const unsigned offset = block_exclusive_scan(t, &total, warp_sums) + s_base;
+    if (lane < lanes) {
+      const unsigned start = starts[lane];
+      out.cu_seqlens[lane + 1] = offset + t;
+      out.logical_lengths[lane] = t ? start : 0;
+      out.query_starts[lane] = t ? start : 0;
+      out.absolute_positions[lane] = t ? start + t - 1 : 0;
+      out.activity[lane] = t ? 1 : 0;
+      for (unsigned i = 0; i < t; ++i) {
+        const unsigned row = offset + i;
+        if (row >= rows_cap) break;
+        const unsigned position = start + i, lp = position / pool.page_tokens;
+        unsigned slot = POISON;
+        if (lp < pool.table_pages) {
+          const size_t e = (static_cast<size_t>(lane) * pool.table_pages + lp) * 2;
+          if (pool.tables[e + 1] != POISON) slot = pool.tables[e] * pool.page_tokens + position % pool.page_tokens;
+        }
+        out.positions[row] = position;
+        out.slot_mapping[row] = slot;
+        out.row_lane[row] = lane;
+      }
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) s_base += total;
+    __syncthreads();
+  }
+}
+
+__global__ void build_attn_lists_kernel(KvPoolDevice pool, PackOutputs pack, unsigned lanes, unsigned kv_heads, unsigned chunk_tokens,
+                                        const char* q_base, char* out_base, unsigned q_heads, unsigned head_dim, int elem_bytes,
+                                        AttnSeq* seqs, AttnWork* work, unsigned* n_work, unsigned work_cap) {
+  __shared__ unsigned warp_sums[kPackThreads / 32];
+  __shared__ unsigned s_item_base, s_group_base;
+  if (threadIdx.x == 0) { s_item_base = 0; s_group_base = 0; }
+  __syncthreads();
+  const size_t row_elems = static_cast<size_t>(q_heads) * head_dim;
+  for (unsigned l0 = 0; l0 < lanes; l0 += blockDim.x) {
+    const unsigned lane = l0 + threadIdx.x;
+    unsigned q_len = 0, start = 0, key_length = 0, splits = 0;
+    if (lane < lanes) {
+      q_len = pack.cu_seqlens[lane + 1] - pack.cu_seqlens[lane];
+      start = pack.query_starts[lane];
+      key_length = q_len ? start + q_len : 0;
+      splits = key_length ? (key_length + chunk_tokens - 1) / chunk_tokens : 0;
+      AttnSeq s;
+      s.q = q_base + static_cast<size_t>(pack.cu_seqlens[lane]) * row_elems * elem_bytes;
+      s.out = out_base + static_cast<size_t>(pack.cu_seqlens[lane]) * row_elems * elem_bytes;
+      s.table = pool.tables + static_cast<size_t>(lane) * pool.table_pages * 2;
+      s.activity = nullptr;
+      s.q_len = q_len; s.q_start = start; s.key_length = key_length; s.table_pages = pool.table_pages;
+      s.q_tok_stride = row_elems; s.q_head_stride = head_dim; s.o_tok_stride = row_elems; s.o_head_stride = head_dim;
+      s.causal = 1; s.pad = 0;
+      seqs[lane] = s;
+    }
+    unsigned total_items, total_groups;
+    const unsigned item_off = block_exclusive_scan(splits * kv_heads, &total_items, warp_sums) + s_item_base;
+    const unsigned group_off = block_exclusive_scan(splits ? kv_heads : 0, &total_groups, warp_sums) + s_group_base;
+    if (lane < lanes && splits) {
+      for (unsigned h = 0; h < kv_heads; ++h) {
+        for (unsigned sp = 0; sp < splits; ++sp) {
+          const unsigned idx = item_off + h * splits + sp;
+          if (idx >= work_cap) continue;
+          AttnWork w;
+          w.seq = lane; w.kv_head = h;
+          w.t_begin = sp * chunk_tokens;
+          w.t_end = min(key_length, (sp + 1) * chunk_tokens);
+          w.split = sp; w.n_splits = splits; w.slot = idx; w.group_index = group_off + h;
+          work[idx] = w;
+        }
+      }
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) { s_item_base += total_items; s_group_base += total_groups; }
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) *n_work = min(s_item_base, work_cap);
+}
+
+}  // namespace
+
+void launch_kvpool_init(Ctx& ctx, const KvPoolDevice& pool) {
+  kvpool_init_kernel<<<1, 1024, 0, ctx.stream>>>(pool);
+  ctx.launches++;
+}
+void launch_kvpool_reserve(Ctx& ctx, const KvPoolDevice& pool, const unsigned* lanes, const unsigned* tokens, unsigned count,
+                           int* status) {
+  if (count == 0) return;
+  kvpool_reserve_kernel<<<1, 256, 0, ctx.stream>>>(pool, lanes, tokens, count, status);
+  ctx.launches++;
+}
+void launch_kvpool_release(Ctx& ctx, const KvPoolDevice& pool, const unsigned* lanes, unsigned count) {
+  if (count == 0) return;
+  kvpool_release_kernel<<<1, 256, 0, ctx.stream>>>(pool, lanes, count);
+  ctx.launches++;
+}
+void launch_pack_step(Ctx& ctx, const KvPoolDevice& pool, const unsigned* starts, const unsigned* tokens, unsigned lanes,
+                      const PackOutputs& out, unsigned rows_cap) {
+  pack_step_kernel<<<1, kPackThreads, 0, ctx.stream>>>(pool, starts, tokens, lanes, out, rows_cap);
+  ctx.launches++;
+}
+void launch_build_attn_lists(Ctx& ctx, const KvPoolDevice& pool, const PackOutputs& pack, unsigned lanes, unsigned kv_heads,
+                             unsigned chunk_tokens, const void* q_base, void* out_base, unsigned q_heads, unsigned head_dim,
+                             int elem_bytes, AttnSeq* seqs, AttnWork* work, unsigned* n_work, unsigned work_cap) {
+  build_attn_lists_kernel<<<1, kPackThreads, 0, ctx.stream>>>(pool, pack, lanes, kv_heads, chunk_tokens, static_cast<const char*>(q_base),
+                                                             static_cast<char*>(out_base), q_heads, head_dim, elem_bytes, seqs, work, n_work, work_cap);
+  ctx.launches++;
+}
+
+}  // namespace fj

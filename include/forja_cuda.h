@@ -1,0 +1,255 @@
+/*
+ * forja_cuda.h - C ABI of libforja_cuda.so, the sm_100a backend library behind forja's
+ * `forja_core::Backend` / `Submission` traits (reference: crates/forja-core/src/backend.rs:609-984).
+ *
+ * A Rust `forja-cuda` crate implements `Backend` by forwarding to these entry points; views stay
+ * pure layout arithmetic on the caller's side (crates/forja-core/src/layout.rs) and cross the
+ * boundary as `fj_tensor` descriptors. Every function returns an `fj_status`; results come back
+ * through out-parameters. There is no CPU fallback: a backend cannot be created without a CUDA
+ * device, and unsupported operations answer FJ_UNSUPPORTED_OPERATION.
+ *
+ * Threading: one backend may be used from several host threads; calls serialise on an internal
+ * mutex (the reference CPU backend does the same, crates/forja-cpu/src/lib.rs:22-24).
+ * Submissions of one backend execute in submission order on one CUDA stream.
+ */
+#ifndef FORJA_CUDA_H
+#define FORJA_CUDA_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- enums -------------------------------------------------------------------------------- */
+
+/* BackendError, crates/forja-core/src/backend.rs:362-426 */
+typedef enum fj_status {
+  FJ_OK = 0,
+  FJ_QUOTA_EXCEEDED = 1,
+  FJ_ALLOCATION_FAILED = 2,
+  FJ_EXECUTION_FAILED = 3,
+  FJ_DEVICE_EXECUTION_FAILED = 4, /* fj_device_error.code = cudaError_t */
+  FJ_DEVICE_ERROR_FLAG = 5,       /* data-dependent error reported by a kernel, see fj_sub_error */
+  FJ_TIMEOUT = 6,
+  FJ_INVALID_INPUT = 7,
+  FJ_UNSUPPORTED_OPERATION = 8,
+  FJ_INDEX_OUT_OF_RANGE = 9       /* fj_device_error.value = lowest offending index */
+} fj_status;
+
+/* dtype, wit/compute.wit:4-10 */
+typedef enum fj_dtype { FJ_F32 = 0, FJ_F16 = 1, FJ_BF16 = 2, FJ_I32 = 3, FJ_U32 = 4 } fj_dtype;
+
+/* Op, crates/forja-core/src/ops.rs:163-302 (State, Sample* and GatherMatmul are not on this path) */
+typedef enum fj_op {
+  FJ_OP_PROGRAM = 1,            /* program = handle from fj_program_prepare */
+  FJ_OP_COPY = 2,
+  FJ_OP_PAGED_COPY = 3,         /* u0 = direction (0 into pages, 1 out of pages), u1 = start, u2 = page_tokens */
+  FJ_OP_RMS_NORM = 4,           /* f0 = eps */
+  FJ_OP_ARGMAX = 5,
+  FJ_OP_TOP_K = 6,              /* u0 = k, u1 = normalize */
+  FJ_OP_ROPE = 7,               /* f0 = theta */
+  FJ_OP_EMBED = 8,
+  FJ_OP_QUANT_EMBED = 9,        /* u0 = bits, u1 = group_size */
+  FJ_OP_MATMUL = 10,
+  FJ_OP_QUANT_MATMUL = 11,      /* u0 = bits, u1 = group_size */
+  FJ_OP_GATHER_QUANT_MATMUL = 12, /* u0 = bits, u1 = group_size; 5-, 8- or 6-input form; program = epilogue or 0 */
+  FJ_OP_PAGED_SDPA = 13,        /* f0 = scale, u0 = causal, u1 = q_start, u2 = key_length, u3 = page_tokens */
+  FJ_OP_PAGED_SDPA_APPEND = 14, /* f0 = scale, u1 = q_start, u3 = page_tokens */
+  FJ_OP_SDPA = 15,              /* f0 = scale, u0 = causal, u1 = q_start (contiguous cache) */
+  FJ_OP_SAMPLE = 16             /* u0 = position; inputs [logits, params(5 x u32), (allow mask)] */
+} fj_op;
+
+/* ---- plain data ---------------------------------------------------------------------------- */
+
+/* Tensor = BufferId + Layout, crates/forja-core/src/ops.rs:20-159, layout.rs:165-175 */
+typedef struct fj_tensor {
+  uint64_t buffer;     /* allocation id returned by fj_alloc / fj_import_readonly */
+  uint32_t dtype;      /* fj_dtype */
+  uint32_t rank;       /* <= 8 */
+  uint64_t offset;     /* elements from the start of the allocation */
+  uint32_t shape[8];
+  uint64_t strides[8]; /* elements; 0 for broadcast axes */
+} fj_tensor;
+
+/* Dispatch, crates/forja-core/src/ops.rs:664-782: already validated by the caller (arity, dtype,
+ * shape, aliasing); the library re-checks what it needs to stay memory-safe. Operand orders are
+ * those of the reference: PagedCopy [ordinary-or-pool, table, generations, (activity)] -> out;
+ * PagedSdpa [q, kpool, vpool, table, generations, (activity)] -> out; PagedSdpaAppend
+ * [q, k_new, v_new, table, generations, (activity)] -> [out, kpool, vpool]; QuantMatmul
+ * [x, packed, scales, biases]; GatherQuantMatmul [x, packed, scales, biases, idx] /
+ * [x, p1, s1, b1, p2, s2, b2, idx] / [act, packed, scales, biases, idx, weights] (+ epilogue
+ * extras); TopK [logits] -> [values, indices]. */
+typedef struct fj_dispatch {
+  uint32_t op; /* fj_op */
+  uint32_t n_inputs;
+  uint32_t n_outputs;
+  uint32_t u0, u1, u2, u3;
+  float f0;
+  uint64_t program; /* Op::Program / epilogue handle, else 0 */
+  const fj_tensor* inputs;
+  const fj_tensor* outputs;
+} fj_dispatch;
+
+typedef struct fj_device_error {
+  uint64_t submission; /* completion serial of the failing submission */
+  uint32_t dispatch;   /* index within the submission */
+  uint32_t op;         /* fj_op of that dispatch */
+  uint32_t flag;       /* 1 = index out of range, 2 = page-table entry refused, 3 = internal wait gave up */
+  uint32_t value;      /* lowest offending index / logical page */
+  int64_t code;        /* cudaError_t for FJ_DEVICE_EXECUTION_FAILED */
+} fj_device_error;
+
+typedef struct fj_device_info_t {
+  char name[128];
+  uint32_t sm_count;
+  uint32_t cc_major, cc_minor;
+  uint64_t total_memory;
+  uint64_t l2_bytes;
+  uint32_t max_smem_per_block;
+} fj_device_info_t;
+
+typedef struct fj_dispatch_profile {
+  uint32_t op;
+  uint32_t kernels;   /* kernel launches issued for this dispatch */
+  uint64_t ns;        /* device time, 0 when the submission was not profiled */
+} fj_dispatch_profile;
+
+typedef struct fj_backend fj_backend;
+typedef struct fj_submission fj_submission;
+
+/* ---- backend: Backend trait, crates/forja-core/src/backend.rs:650-984 ------------------------ */
+
+/* CudaBackend::new. memory_limit 0 = no quota. Fails with FJ_ALLOCATION_FAILED when no CUDA
+ * device can be opened (there is no fallback). */
+int32_t fj_backend_create(int32_t device, uint64_t memory_limit, fj_backend** out);
+void fj_backend_destroy(fj_backend* be);
+int32_t fj_device_info(fj_backend* be, fj_device_info_t* out);                     /* backend.rs:679 */
+int32_t fj_set_memory_limit(fj_backend* be, uint64_t bytes);                      /* backend.rs:684 */
+int32_t fj_memory_usage(fj_backend* be, uint64_t* used, uint64_t* limit);         /* backend.rs:669 */
+/* alloc: zero-initialised device allocation (backend.rs:713). */
+int32_t fj_alloc(fj_backend* be, uint64_t bytes, uint64_t* buffer);
+/* import_readonly (backend.rs:719): copies `bytes` from host memory into a read-only buffer. */
+int32_t fj_import_readonly(fj_backend* be, const void* host, uint64_t bytes, uint64_t* buffer);
+int32_t fj_release(fj_backend* be, uint64_t buffer);                              /* backend.rs:777 */
+/* write (backend.rs:756): contiguous bytes at a byte offset; refused on read-only buffers. */
+int32_t fj_write(fj_backend* be, uint64_t buffer, uint64_t byte_offset, const void* src, uint64_t len);
+/* read_buffer_range (backend.rs:728). */
+int32_t fj_read(fj_backend* be, uint64_t buffer, uint64_t byte_offset, void* dst, uint64_t len);
+/* read (backend.rs:762): gathers a strided view into contiguous logical bytes at dst. */
+int32_t fj_read_strided(fj_backend* be, const fj_tensor* view, void* dst);
+/* Device address of a buffer, for callers that stage data with their own copies or kernels. */
+int32_t fj_buffer_device_ptr(fj_backend* be, uint64_t buffer, void** ptr, uint64_t* bytes);
+
+/* prepare_program (backend.rs:693): structural recognition of the scalar programs the engines
+ * submit (crates/forja-sdk/src/nn/blocks.rs:380-444, engines/qwen3-coder/src/lib.rs:26-54) with
+ * their constants captured; anything else is FJ_UNSUPPORTED_OPERATION (no interpreter fallback).
+ * kind: 0 Map, 1 Row. insts: n_insts x 4 words {tag, a, b, c} with tags 0 Input(slot),
+ * 1 Const(f32 bits), 2 Index(axis), 3 Extent(axis), 4 Unary(op, x), 5 Binary(op, l, r),
+ * 6 Select(c, t, f), 7 Cast(type, x), 8 Reduce(op, x); opcode numbering follows the declaration
+ * order of UnOp/BinOp/RedOp/ValueType in crates/forja-core/src/program.rs:43-126.
+ * outputs: n_outputs x {slot, inst}. */
+int32_t fj_program_prepare(fj_backend* be, uint32_t kind, const uint32_t* insts, uint32_t n_insts,
+                           const uint32_t* outputs, uint32_t n_outputs, uint64_t* handle);
+/* Which fused kernel a prepared program maps to: 1 add, 2 silu_mul, 3 rms_norm, 4 residual_norm,
+ * 5 qk_norm_rope, 6 rope_pairs; consts receives the captured constants (eps, theta, head_dim). */
+int32_t fj_program_info(fj_backend* be, uint64_t handle, uint32_t* kernel, float consts[4]);
+
+/* submit (backend.rs:783) / submit_profiled (backend.rs:800). Work is enqueued and the call
+ * returns; runs of per-lane paged-attention dispatches over the same planes are executed as one
+ * ragged launch. */
+int32_t fj_submit(fj_backend* be, const fj_dispatch* dispatches, uint32_t count, uint32_t profiled,
+                  fj_submission** out);
+/* Submission, backend.rs:609-647 */
+int32_t fj_sub_wait(fj_submission* sub, uint64_t timeout_ns); /* 0 = wait forever; FJ_TIMEOUT leaves the submission alive */
+int32_t fj_sub_gpu_time_ns(fj_submission* sub, uint64_t* ns);
+uint64_t fj_sub_completion_serial(fj_submission* sub);
+int32_t fj_sub_error(fj_submission* sub, fj_device_error* out);
+uint32_t fj_sub_kernel_launches(fj_submission* sub);
+int32_t fj_sub_profile(fj_submission* sub, fj_dispatch_profile* out, uint32_t cap, uint32_t* count);
+void fj_sub_destroy(fj_submission* sub);
+
+/* Device-wide synchronisation of the backend's stream (tests and benchmarks). */
+int32_t fj_synchronize(fj_backend* be);
+/* Number of kernels this backend has launched since creation. */
+uint64_t fj_kernel_launch_count(fj_backend* be);
+
+/* Timers on the backend's stream (CUDA events): benchmarks time the stream the kernels run on. */
+int32_t fj_timer_create(fj_backend* be, uint64_t* timer);
+int32_t fj_timer_record(fj_backend* be, uint64_t timer);
+int32_t fj_timer_elapsed_ns(fj_backend* be, uint64_t start_timer, uint64_t stop_timer, uint64_t* ns);
+
+/* ---- fast path: device-resident ragged batching -------------------------------------------- */
+
+/* Paged-KV allocator on the device (replaces the host mutex of PagePool::reserve/release,
+ * crates/forja-core/src/paged_pool.rs:204-232, 308-327, 1229-1326, for fixed-capacity pools).
+ * One pool owns: free stack (LIFO, page 0 on top), generations[physical_pages], and
+ * `lanes` page tables of `table_pages` entries {page, generation}, poisoned when unbound. */
+typedef struct fj_kvpool fj_kvpool;
+int32_t fj_kvpool_create(fj_backend* be, uint32_t page_tokens, uint32_t physical_pages, uint32_t lanes,
+                         uint32_t table_pages, fj_kvpool** out);
+void fj_kvpool_destroy(fj_kvpool* pool);
+/* reserve: lane <- ceil(tokens/page_tokens) pages popped from the stack, generation bumped
+ * (never 0xFFFFFFFF); refusal (not enough pages, lane bound, table too small) changes nothing and
+ * is reported in status[i] (FJ_OK / FJ_QUOTA_EXCEEDED / FJ_INVALID_INPUT) after the call.
+ * Requests are applied in order by one CTA so page ids equal the host allocator's. */
+int32_t fj_kvpool_reserve(fj_kvpool* pool, const uint32_t* lanes, const uint32_t* tokens, uint32_t count,
+                          int32_t* status);
+/* release: pages of the lane return to the stack in table order; table re-poisoned. */
+int32_t fj_kvpool_release(fj_kvpool* pool, const uint32_t* lanes, uint32_t count);
+/* Snapshots for parity checks: table [table_pages x 2] of one lane, generations, free stack. */
+int32_t fj_kvpool_read_table(fj_kvpool* pool, uint32_t lane, uint32_t* entries);
+int32_t fj_kvpool_read_generations(fj_kvpool* pool, uint32_t* generations);
+int32_t fj_kvpool_read_free(fj_kvpool* pool, uint32_t* pages, uint32_t cap, uint32_t* count);
+uint64_t fj_kvpool_tables_buffer(fj_kvpool* pool);      /* buffer id: [lanes, table_pages, 2] u32 */
+uint64_t fj_kvpool_generations_buffer(fj_kvpool* pool); /* buffer id: [physical_pages] u32 */
+
+/* Ragged-batch packer on the device: lane descriptors -> the metadata of
+ * write_paged_lane_metadata (crates/forja-host/src/lib.rs:4977-5065) plus cu_seqlens, positions,
+ * slot_mapping and row_lane. starts/tokens are host arrays [lanes] (tokens 0 = inactive lane);
+ * logical lengths are taken as start (the lane's committed length when the step begins).
+ * All outputs are u32 device buffers owned by the pool; read them back with fj_kvpool_read_pack. */
+typedef struct fj_pack_view {
+  uint32_t rows;
+  uint32_t lanes;
+  uint64_t logical_lengths, query_starts, absolute_positions, activity; /* buffer ids, [lanes] */
+  uint64_t cu_seqlens;                                                  /* [lanes + 1] */
+  uint64_t positions, slot_mapping, row_lane;                           /* [rows] */
+} fj_pack_view;
+int32_t fj_pack_step(fj_kvpool* pool, const uint32_t* starts, const uint32_t* tokens, uint32_t lanes,
+                     fj_pack_view* out);
+
+/* Dense decoder (SmolLM2 / Qwen3-dense shapes; reference op order: engines/qwen3/src/lib.rs:391-452,
+ * 734-811 and engines/smollm2/src/optimized.rs:97-245). Weights are buffers of this backend in the
+ * activation dtype: embed [vocab, hidden] (tied lm_head), per layer wq [hq*d, hidden],
+ * wk/wv [kvh*d, hidden], wo [hidden, hq*d], w_gate/w_up [inter, hidden], w_down [hidden, inter],
+ * norms [hidden], optional q_norm/k_norm [d]. */
+typedef struct fj_dense_config {
+  uint32_t dtype;        /* FJ_F32 or FJ_BF16: activations, weights and KV planes */
+  uint32_t layers, hidden, q_heads, kv_heads, head_dim, intermediate, vocab;
+  uint32_t qk_norm;      /* 1: per-head RMSNorm on q and k before RoPE (guest program), 0: plain Op::Rope */
+  float eps, theta;
+  uint32_t max_rows;     /* largest number of token rows in one step */
+} fj_dense_config;
+typedef struct fj_dense_layer_weights {
+  uint64_t input_norm, wq, wk, wv, q_norm, k_norm, wo, post_norm, w_gate, w_up, w_down;
+} fj_dense_layer_weights;
+typedef struct fj_dense_model fj_dense_model;
+int32_t fj_dense_model_create(fj_backend* be, const fj_dense_config* config, uint64_t embed, uint64_t final_norm,
+                              const fj_dense_layer_weights* layers, fj_kvpool* pool, fj_dense_model** out);
+void fj_dense_model_destroy(fj_dense_model* model);
+/* One continuous-batching forward step over the lanes packed by the last fj_pack_step:
+ * embed -> layers (qkv, qk-norm+rope+KV append, paged attention, o, residual+norm, MLP) -> final
+ * norm -> lm_head on each lane's last row -> greedy argmax. token_ids: host u32 [rows] or NULL to
+ * feed back each lane's previous greedy token (device-resident). out_tokens: host u32 [lanes] or
+ * NULL. logits_out: buffer id receiving [lanes, vocab] in the activation dtype, or 0. The call
+ * returns after the step completed when out_tokens != NULL, else it only enqueues. */
+int32_t fj_dense_step(fj_dense_model* model, const uint32_t* token_ids, uint32_t* out_tokens, uint64_t logits_out);
+/* Device time and launch count of the last completed step; attention split statistics. */
+int32_t fj_dense_step_stats(fj_dense_model* model, uint64_t* kernels, uint64_t* attn_work_items);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FORJA_CUDA_H */
