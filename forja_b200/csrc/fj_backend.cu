@@ -955,6 +955,15 @@ int32_t fj_program_prepare(fj_backend* be, uint32_t kind, const uint32_t* insts,
   return FJ_OK;
 }
 
+int32_t fj_program_classify(uint32_t kind, const uint32_t* insts, uint32_t n_insts, const uint32_t* outputs, uint32_t n_outputs, uint32_t* kernel, float consts[4]) {
+  if (!insts || !outputs || kind > 1 || n_insts == 0 || n_insts > 256 || n_outputs == 0 || n_outputs > 4) return FJ_INVALID_INPUT;
+  fj_program_rec r;
+  if (!recognise(kind, insts, n_insts, outputs, n_outputs, &r)) return FJ_UNSUPPORTED_OPERATION;
+  if (kernel) *kernel = r.kernel;
+  if (consts) { consts[0] = r.eps; consts[1] = r.theta; consts[2] = r.head_dim; consts[3] = r.exponent_scale; }
+  return FJ_OK;
+}
+
 int32_t fj_program_info(fj_backend* be, uint64_t handle, uint32_t* kernel, float consts[4]) {
   if (!be) return FJ_INVALID_INPUT;
   std::lock_guard<std::mutex> lock(be->mutex);

@@ -72,7 +72,7 @@ __global__ void rms_norm_kernel(View x, View w, View out, size_t rows, unsigned 
   }
 }
 
-__global__ void residual_norm_kernel(View residual, View update, View w, View sum_out, View norm_out, size_t rows,
+__global__ void residual_norm_kernel(View residual, View update, View w, View sum_out, View norm_out, size_t rows, int round_sum,
                                      unsigned width, float eps) {
   const int lane = threadIdx.x & 31;
   const size_t warps_per_block = blockDim.x >> 5;
@@ -82,15 +82,18 @@ __global__ void residual_norm_kernel(View residual, View update, View w, View su
       size_t e = row * width + i;
       float v = load_as_f32(residual.base, residual.dtype, view_offset(residual, e)) +
                 load_as_f32(update.base, update.dtype, view_offset(update, e));
+      if (round_sum) v = round_through(v, sum_out.dtype);
       sum += v * v;
     }
     sum = warp_sum(sum);
     const float inverse = 1.0f / sqrtf(sum / static_cast<float>(width) + eps);
     for (unsigned i = lane; i < width; i += 32) {
       size_t e = row * width + i;
-      // the normalised output uses the unrounded f32 sum, as the row program does
+      // the row program normalises the unrounded f32 sum; the unfused add + rms_norm pair of the
+      // SmolLM2 graph normalises the sum after it was stored (round_sum)
       float v = load_as_f32(residual.base, residual.dtype, view_offset(residual, e)) +
                 load_as_f32(update.base, update.dtype, view_offset(update, e));
+      if (round_sum) v = round_through(v, sum_out.dtype);
       float g = load_as_f32(w.base, w.dtype, view_offset(w, e));
       store_from_f32(norm_out.base, norm_out.dtype, view_offset(norm_out, e), v * inverse * g);
       store_from_f32(sum_out.base, sum_out.dtype, view_offset(sum_out, e), v);
@@ -172,7 +175,8 @@ __global__ void quant_embed_kernel(const unsigned* __restrict__ packed, const vo
         unsigned word = packed[static_cast<size_t>(id) * packed_width + c / vpw];
         unsigned q = (word >> ((c % vpw) * bits)) & mask;
         size_t g = static_cast<size_t>(id) * groups + c / group_size;
-        v = load_as_f32(scales, p_dt, g) * static_cast<float>(q) + load_as_f32(biases, p_dt, g);
+        // separate multiply and add (no FMA contraction): same two roundings as the reference
+        v = __fadd_rn(__fmul_rn(load_as_f32(scales, p_dt, g), static_cast<float>(q)), load_as_f32(biases, p_dt, g));
       }
       store_from_f32(out, out_dt, static_cast<size_t>(row) * width + c, v);
     }
@@ -341,9 +345,9 @@ void launch_rms_norm(Ctx& ctx, const View& x, const View& w, const View& out, si
   ctx.launches++;
 }
 void launch_residual_norm(Ctx& ctx, const View& residual, const View& update, const View& w, const View& sum_out,
-                          const View& norm_out, size_t rows, unsigned width, float eps) {
+                          const View& norm_out, size_t rows, unsigned width, float eps, int round_sum) {
   if (rows == 0) return;
-  residual_norm_kernel<<<grid_for(rows * 32, kThreads, ctx.sm_count), kThreads, 0, ctx.stream>>>(residual, update, w, sum_out, norm_out, rows, width, eps);
+  residual_norm_kernel<<<grid_for(rows * 32, kThreads, ctx.sm_count), kThreads, 0, ctx.stream>>>(residual, update, w, sum_out, norm_out, rows, round_sum, width, eps);
   ctx.launches++;
 }
 void launch_qk_norm_rope(Ctx& ctx, const View& lo, const View& hi, const View& wlo, const View& whi, const View& pos,

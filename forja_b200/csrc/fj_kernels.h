@@ -24,7 +24,7 @@ void launch_silu_mul(Ctx& ctx, const View& gate, const View& up, const View& out
 // Row programs: rows = elements / width, reductions over the last axis.
 void launch_rms_norm(Ctx& ctx, const View& x, const View& w, const View& out, size_t rows, unsigned width, float eps);
 void launch_residual_norm(Ctx& ctx, const View& residual, const View& update, const View& w, const View& sum_out,
-                          const View& norm_out, size_t rows, unsigned width, float eps);
+                          const View& norm_out, size_t rows, unsigned width, float eps, int round_sum = 0);
 // qk_norm_rope over the half row: inputs lo, hi, weight_lo, weight_hi, positions (all views of the
 // iteration shape [.., half]); inv_freq[i] = powf(theta, i * (-2/head_dim)) precomputed on the host.
 void launch_qk_norm_rope(Ctx& ctx, const View& lo, const View& hi, const View& wlo, const View& whi, const View& pos,

@@ -428,7 +428,7 @@ int32_t fj_dense_step(fj_dense_model* m, const uint32_t* token_ids, uint32_t* ou
     fj::launch_gemm_nt(ctx, m->attn, dt, qd, L.wo, dt, qd, m->proj, dt, H, rows, H, qd, be->gemm_scratch, be->gemm_scratch_bytes);
     // hidden' = hidden + attention ; normed = rms(hidden') * post_norm
     fj::launch_residual_norm(ctx, dense_view(hidden, dt, rows, H, H), dense_view(m->proj, dt, rows, H, H), weight_view(L.post_norm, dt, rows, H), dense_view(other, dt, rows, H, H),
-                             dense_view(m->normed, dt, rows, H, H), rows, H, c.eps);
+                             dense_view(m->normed, dt, rows, H, H), rows, H, c.eps, c.qk_norm ? 0 : 1);
     std::swap(hidden, other);
     fj::launch_gemm_nt(ctx, m->normed, dt, H, L.w_gate_up, dt, H, m->gate_up, dt, 2 * I, rows, 2 * I, H, be->gemm_scratch, be->gemm_scratch_bytes);
     fj::launch_silu_mul(ctx, dense_view(m->gate_up, dt, rows, I, 2 * I), dense_view(static_cast<char*>(m->gate_up) + static_cast<size_t>(I) * esz, dt, rows, I, 2 * I),
@@ -436,7 +436,7 @@ int32_t fj_dense_step(fj_dense_model* m, const uint32_t* token_ids, uint32_t* ou
     fj::launch_gemm_nt(ctx, m->act, dt, I, L.w_down, dt, I, m->proj, dt, H, rows, H, I, be->gemm_scratch, be->gemm_scratch_bytes);
     if (l + 1 < c.layers) {
       fj::launch_residual_norm(ctx, dense_view(hidden, dt, rows, H, H), dense_view(m->proj, dt, rows, H, H), weight_view(m->layers[l + 1].input_norm, dt, rows, H),
-                               dense_view(other, dt, rows, H, H), dense_view(m->normed, dt, rows, H, H), rows, H, c.eps);
+                               dense_view(other, dt, rows, H, H), dense_view(m->normed, dt, rows, H, H), rows, H, c.eps, c.qk_norm ? 0 : 1);
     } else {
       fj::launch_add(ctx, dense_view(hidden, dt, rows, H, H), dense_view(m->proj, dt, rows, H, H), dense_view(other, dt, rows, H, H), static_cast<size_t>(rows) * H);
     }

@@ -152,6 +152,10 @@ int32_t fj_buffer_device_ptr(fj_backend* be, uint64_t buffer, void** ptr, uint64
  * outputs: n_outputs x {slot, inst}. */
 int32_t fj_program_prepare(fj_backend* be, uint32_t kind, const uint32_t* insts, uint32_t n_insts,
                            const uint32_t* outputs, uint32_t n_outputs, uint64_t* handle);
+/* The recognition step alone (host logic, needs no device): FJ_OK and *kernel / consts filled as
+ * for fj_program_info, or FJ_UNSUPPORTED_OPERATION. */
+int32_t fj_program_classify(uint32_t kind, const uint32_t* insts, uint32_t n_insts, const uint32_t* outputs,
+                            uint32_t n_outputs, uint32_t* kernel, float consts[4]);
 /* Which fused kernel a prepared program maps to: 1 add, 2 silu_mul, 3 rms_norm, 4 residual_norm,
  * 5 qk_norm_rope, 6 rope_pairs; consts receives the captured constants (eps, theta, head_dim). */
 int32_t fj_program_info(fj_backend* be, uint64_t handle, uint32_t* kernel, float consts[4]);
