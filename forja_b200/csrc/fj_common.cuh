@@ -68,6 +68,26 @@ __device__ inline unsigned int total_order_key(float v) {
   b ^= static_cast<int>(static_cast<unsigned int>(b >> 31) >> 1);
   return static_cast<unsigned int>(b) ^ 0x80000000u;
 }
+// Bits of element `index` widened to f32 with integer arithmetic only, so NaN sign and payload
+// reach the ordering key untouched (the reference decodes f16/bf16 NaNs as sign | quiet | payload).
+__device__ inline unsigned int load_f32_bits(const void* base, int dt, size_t index) {
+  if (dt == F32) return static_cast<const unsigned int*>(base)[index];
+  const unsigned int h = static_cast<const unsigned short*>(base)[index];
+  if (dt == BF16) return ((h & 0x7FFFu) > 0x7F80u) ? ((h | 0x0040u) << 16) : (h << 16);
+  const unsigned int sign = (h & 0x8000u) << 16, exp = h & 0x7C00u, man = h & 0x03FFu;
+  if (exp == 0x7C00u) return man == 0 ? (sign | 0x7F800000u) : (sign | 0x7FC00000u | (man << 13));
+  return static_cast<unsigned int>(__float_as_int(__half2float(__ushort_as_half(static_cast<unsigned short>(h)))));
+}
+__device__ inline unsigned int total_order_key_bits(unsigned int bits) {
+  int b = static_cast<int>(bits);
+  b ^= static_cast<int>(static_cast<unsigned int>(b >> 31) >> 1);
+  return static_cast<unsigned int>(b) ^ 0x80000000u;
+}
+__device__ inline unsigned int key_to_bits(unsigned int key) {
+  int b = static_cast<int>(key ^ 0x80000000u);
+  b ^= static_cast<int>(static_cast<unsigned int>(b >> 31) >> 1);
+  return static_cast<unsigned int>(b);
+}
 __device__ inline float key_to_float(unsigned int key) {
   int b = static_cast<int>(key ^ 0x80000000u);
   b ^= static_cast<int>(static_cast<unsigned int>(b >> 31) >> 1);

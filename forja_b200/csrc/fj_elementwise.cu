@@ -194,8 +194,8 @@ __global__ void argmax_partial_kernel(const void* x, int dt, size_t row_stride, 
   const unsigned end = min(width, begin + kArgmaxChunk);
   unsigned long long best = 0;
   for (unsigned i = begin + threadIdx.x; i < end; i += blockDim.x) {
-    float v = load_as_f32(x, dt, static_cast<size_t>(row) * row_stride + i);
-    unsigned long long key = (static_cast<unsigned long long>(total_order_key(v)) << 32) | i;
+    const unsigned bits = load_f32_bits(x, dt, static_cast<size_t>(row) * row_stride + i);
+    unsigned long long key = (static_cast<unsigned long long>(total_order_key_bits(bits)) << 32) | i;
     best = key > best ? key : best;
   }
   best = warp_max_u64(best);
@@ -230,8 +230,8 @@ __global__ void top_k_kernel(const void* x, int dt, void* values, int v_dt, unsi
   __shared__ float chosen[64];
   const unsigned row = blockIdx.x;
   for (unsigned i = threadIdx.x; i < width; i += blockDim.x) {
-    float v = load_as_f32(x, dt, static_cast<size_t>(row) * width + i);
-    keys[i] = (static_cast<unsigned long long>(total_order_key(v)) << 32) | (0xFFFFFFFFu - i);
+    const unsigned bits = load_f32_bits(x, dt, static_cast<size_t>(row) * width + i);
+    keys[i] = (static_cast<unsigned long long>(total_order_key_bits(bits)) << 32) | (0xFFFFFFFFu - i);
   }
   __syncthreads();
   for (unsigned j = 0; j < k; ++j) {
@@ -246,9 +246,10 @@ __global__ void top_k_kernel(const void* x, int dt, void* values, int v_dt, unsi
       selected = best;
       keys[index] = 0;  // below every real key (real keys have a nonzero low word or high word)
       indices[static_cast<size_t>(row) * k + j] = index;
-      float v = key_to_float(static_cast<unsigned>(best >> 32));
-      if (normalize) chosen[j] = v;
-      else store_from_f32(values, v_dt, static_cast<size_t>(row) * k + j, v);
+      const unsigned bits = key_to_bits(static_cast<unsigned>(best >> 32));
+      if (normalize) chosen[j] = __uint_as_float(bits);
+      else if (v_dt == F32) static_cast<unsigned*>(values)[static_cast<size_t>(row) * k + j] = bits;  // NaN payloads survive
+      else store_from_f32(values, v_dt, static_cast<size_t>(row) * k + j, __uint_as_float(bits));
     }
     __syncthreads();
   }
