@@ -1,0 +1,469 @@
+"""Benchmark of the continuous-batching decode step (the hot path) on B200.
+
+Workload (fits one GPU): Qwen3-0.6B architecture, bf16, random-init weights; 128 sequences whose
+context lengths are log-uniform over 128..8192 tokens, page size 16, greedy decode; a sequence that
+reaches its token budget leaves and a new request takes its lane (continuous batching). Contexts
+are synthetic: the KV planes are pre-filled with seeded N(0, 1) values, so a newly admitted
+request finds its context rows already in its pages and the timed region is pure decode.
+
+One "step" = one forward step over every active lane. `value` is decode tokens per second with
+all inputs resident on the device (tokens fed back on the device, no host synchronisation inside
+the timed region); `e2e` is the same loop driven through the C ABI with host buffers: every step
+uploads token ids and lane descriptors and reads the greedy tokens back before the next step.
+
+usage: python bench.py [--gpus N] [--steps K] [--warmup W] [--impl native|reference]
+For N > 1 launch with torch.distributed.run: each rank owns one GPU, runs its own 128 lanes
+(independent replicas over sequences, no data-path collective) and rank 0 prints one JSON line.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+BF16, U32 = 2, 4
+QWEN3_06B = dict(dtype=BF16, layers=28, hidden=1024, q_heads=16, kv_heads=8, head_dim=128, intermediate=3072, vocab=151936, qk_norm=1,
+                 eps=1e-6, theta=1e6, max_rows=128)
+PAGE = 16
+CTX_MIN, CTX_MAX = 128, 8192
+BUDGET_MIN, BUDGET_MAX = 64, 256
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=256)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--impl", default="native", choices=["native", "reference"])
+    ap.add_argument("--lanes", type=int, default=128)
+    ap.add_argument("--seed", type=int, default=0)
+    ap.add_argument("--pool-pages", type=int, default=36000, help="physical KV pages per GPU (36000 pages = 66 GB of planes)")
+    ap.add_argument("--ctx-max", type=int, default=CTX_MAX, help="largest context length (lower it for profiler captures)")
+    ap.add_argument("--layers", type=int, default=0, help="override the layer count (profiler captures only; 0 = the model's 28)")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    return ap.parse_args()
+
+
+def f32_to_bf16_bits(x: np.ndarray) -> np.ndarray:
+    """Round-to-nearest-even f32 -> bf16 bit patterns (finite inputs)."""
+    u = np.ascontiguousarray(x, np.float32).view(np.uint32)
+    return ((u + 0x7FFF + ((u >> 16) & 1)) >> 16).astype(np.uint16)
+
+
+class Requests:
+    """Seeded stream of synthetic requests: (context length, new-token budget)."""
+
+    def __init__(self, seed, ctx_max):
+        self.rng = np.random.default_rng(seed)
+        self.ctx_max = ctx_max
+
+    def next(self):
+        ctx = int(round(float(np.exp(self.rng.uniform(np.log(CTX_MIN), np.log(self.ctx_max))))))
+        budget = int(self.rng.integers(BUDGET_MIN, BUDGET_MAX + 1))
+        return ctx, budget
+
+
+class Lanes:
+    """Host bookkeeping of the continuous batch: which request sits in which lane, its current
+    length and remaining budget, and the free-page count (the device allocator is deterministic,
+    so the host knows it without reading anything back)."""
+
+    def __init__(self, pool, requests, lanes, pool_pages):
+        self.pool, self.requests, self.n = pool, requests, lanes
+        self.free_pages = pool_pages
+        self.length = np.zeros(lanes, np.uint32)
+        self.remaining = np.zeros(lanes, np.int64)
+        self.pages = np.zeros(lanes, np.int64)
+        self.waiting = [None] * lanes
+        self.admitted = 0
+        for lane in range(lanes):
+            self.waiting[lane] = requests.next()
+        self.admit()
+
+    def admit(self):
+        lanes, tokens = [], []
+        for lane in range(self.n):
+            req = self.waiting[lane]
+            if req is None:
+                continue
+            ctx, budget = req
+            need = (ctx + budget + PAGE - 1) // PAGE
+            if need > self.free_pages:
+                continue  # page reservation does not fit yet: the lane idles this step
+            self.free_pages -= need
+            self.pages[lane], self.length[lane], self.remaining[lane] = need, ctx, budget
+            self.waiting[lane] = None
+            lanes.append(lane)
+            tokens.append(ctx + budget)
+            self.admitted += 1
+        if lanes:
+            self.pool.reserve(lanes, tokens, want_status=False)
+
+    def descriptors(self):
+        active = self.remaining > 0
+        return self.length.copy(), active.astype(np.uint32)
+
+    def advance(self):
+        """After a step: every active lane grew by one token; finished lanes release their pages."""
+        active = self.remaining > 0
+        self.length[active] += 1
+        self.remaining[active] -= 1
+        done = np.nonzero(active & (self.remaining == 0))[0]
+        if done.size:
+            self.pool.release(done.tolist())
+            for lane in done.tolist():
+                self.free_pages += int(self.pages[lane])
+                self.pages[lane] = 0
+                self.waiting[lane] = self.requests.next()
+            self.admit()
+        return int(active.sum())
+
+
+def attention_bytes(lengths, cfg):
+    """Algorithmic bytes of one paged decode-attention launch (one layer): q rows + K/V rows of
+    every attended token + 12 B per page of table/generation reads + 4 B + output rows
+    (the reference's KernelCost, crates/forja-core/src/cost/attention.rs:38-90)."""
+    hq, kvh, d, esz = cfg["q_heads"], cfg["kv_heads"], cfg["head_dim"], 2
+    total = 0
+    for L in lengths:
+        total += hq * d * esz + kvh * int(L) * 2 * d * esz + 12 * ((int(L) + PAGE - 1) // PAGE) + 4 + hq * d * esz
+    return total
+
+
+def start_clock_sampler(path, device):
+    query = "index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown," \
+            "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap"
+    try:
+        return subprocess.Popen(["nvidia-smi", "-i", str(device), f"--query-gpu={query}", "--format=csv,noheader,nounits", "-lms", "200"],
+                                stdout=open(path, "w"), stderr=subprocess.DEVNULL)
+    except OSError:
+        return None
+
+
+def read_clock_samples(path):
+    sm, sm_max, reasons = [], 0.0, set()
+    try:
+        for line in open(path):
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 9:
+                continue
+            try:
+                sm.append(float(parts[1]))
+                sm_max = max(sm_max, float(parts[2]))
+            except ValueError:
+                continue
+            for name, value in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), parts[5:9]):
+                if value.lower().startswith("active"):
+                    reasons.add(name)
+    except OSError:
+        pass
+    busy = sorted(s for s in sm if s > 0)
+    top = busy[len(busy) // 2:] if busy else []  # samples under load: upper half
+    return {"sm_mhz": float(np.median(top)) if top else None, "sm_max_mhz": sm_max or None, "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def random_weights_bf16(cfg, seed):
+    """Random-init N(0, 0.02) weights, norm gains 1 + N(0, 0.02), as bf16 bit patterns."""
+    rng = np.random.default_rng(seed)
+    H, I, V, d = cfg["hidden"], cfg["intermediate"], cfg["vocab"], cfg["head_dim"]
+    qd, kd = cfg["q_heads"] * d, cfg["kv_heads"] * d
+    mat = lambda r, c: f32_to_bf16_bits(rng.standard_normal((r, c), dtype=np.float32) * np.float32(0.02))
+    gain = lambda n: f32_to_bf16_bits(np.float32(1.0) + rng.standard_normal(n, dtype=np.float32) * np.float32(0.02))
+    weights = {"embed": mat(V, H), "final_norm": gain(H), "layers": []}
+    for _ in range(cfg["layers"]):
+        weights["layers"].append({"input_norm": gain(H), "wq": mat(qd, H), "wk": mat(kd, H), "wv": mat(kd, H), "q_norm": gain(d), "k_norm": gain(d),
+                                  "wo": mat(H, qd), "post_norm": gain(H), "w_gate": mat(I, H), "w_up": mat(I, H), "w_down": mat(H, I)})
+    return weights
+
+
+def dist_setup(n_gpus):
+    """torch.distributed is plumbing only: rendezvous, barrier and the max over ranks."""
+    rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    dist = None
+    if world > 1:
+        import torch
+        import torch.distributed as dist
+        torch.cuda.set_device(local)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    return rank, world, local, dist
+
+
+def reduce_max_sum(dist, local, elapsed_s, tokens, extra):
+    """max of elapsed over ranks, sums of the token counts and of each entry of `extra`."""
+    if dist is None:
+        return elapsed_s, tokens, extra
+    import torch
+    t = torch.tensor([elapsed_s], dtype=torch.float64, device=f"cuda:{local}")
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    s = torch.tensor([float(tokens)] + [float(v) for v in extra], dtype=torch.float64, device=f"cuda:{local}")
+    dist.all_reduce(s, op=dist.ReduceOp.SUM)
+    vals = s.tolist()
+    return float(t.item()), vals[0], vals[1:]
+
+
+def barrier(dist, be):
+    be.synchronize()
+    if dist is not None:
+        dist.barrier()
+
+
+def run_native(args):
+    import forja_b200 as fb
+    rank, world, local, dist = dist_setup(args.gpus)
+    be = fb.CudaBackend(local)  # raises when the CUDA library or device is missing: no fallback
+    cfg = dict(QWEN3_06B)
+    if args.layers:
+        cfg["layers"] = args.layers
+    cfg["max_rows"] = args.lanes
+    table_pages = (args.ctx_max + BUDGET_MAX + PAGE - 1) // PAGE
+    pool = fb.KvPool(be, PAGE, args.pool_pages, args.lanes, table_pages)
+    weights = random_weights_bf16(cfg, args.seed)
+    up = lambda a: be.tensor_from(a, fb.BF16)
+    model = fb.DenseModel(be, pool, cfg, up(weights["embed"]), up(weights["final_norm"]), [{k: up(v) for k, v in layer.items()} for layer in weights["layers"]])
+    del weights
+    model.fill_kv(args.seed + 17 * rank)
+    lanes = Lanes(pool, Requests(args.seed * 1000 + rank, args.ctx_max), args.lanes, args.pool_pages)
+
+    def step_device():
+        starts, tokens = lanes.descriptors()
+        pool.pack_step(starts, tokens)
+        model.step(None, want_tokens=False)
+        return starts, tokens
+
+    # first token of every lane comes from the host once; afterwards tokens feed back on the device
+    starts, tokens = lanes.descriptors()
+    pool.pack_step(starts, tokens)
+    seed_tokens = np.random.default_rng(args.seed).integers(0, cfg["vocab"], int(tokens.sum())).astype(np.uint32)
+    model.step(seed_tokens, want_tokens=False)
+    lanes.advance()
+    for _ in range(max(args.warmup - 1, 0)):
+        step_device()
+        lanes.advance()
+
+    # ---- timed region 1: device-resident decode --------------------------------------------
+    t_begin, t_end = be.timer(), be.timer()
+    clocks_path = os.path.join(ROOT, "gpurun_out", f"clocks_rank{rank}.csv")
+    os.makedirs(os.path.dirname(clocks_path), exist_ok=True)
+    sampler = start_clock_sampler(clocks_path, local)
+    model.attention_time()
+    barrier(dist, be)
+    launches0 = be.kernel_launch_count()
+    be.timer_record(t_begin)
+    total_tokens, attn_bytes, kv_tokens, profiled_steps = 0, 0, 0, 0
+    for step in range(args.steps):
+        # the attention launches of every 8th step are bracketed by CUDA events on the kernel's
+        # stream; bracketing all of them costs about a millisecond per step in pipeline bubbles
+        sampled = step % 8 == 0
+        model.profile_attention(sampled)
+        starts, tokens = step_device()
+        active = starts[tokens > 0] + 1
+        if sampled:
+            attn_bytes += attention_bytes(active, cfg)
+            profiled_steps += 1
+        kv_tokens += int(active.sum())
+        total_tokens += lanes.advance()
+    be.timer_record(t_end)
+    barrier(dist, be)
+    elapsed = be.timer_elapsed_ns(t_begin, t_end) * 1e-9
+    launches = be.kernel_launch_count() - launches0
+    attn_ns, attn_launches = model.attention_time()
+    model.profile_attention(False)
+    stats = model.stats()
+
+    # ---- timed region 2: end to end through the C ABI with host buffers ----------------------
+    e2e_steps = args.steps
+    host_tokens = np.zeros(args.lanes, np.uint32)
+    barrier(dist, be)
+    h2d = d2h = 0
+    e2e_tokens = 0
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        starts, tokens = lanes.descriptors()
+        pool.pack_step(starts, tokens)                       # host -> device: 2 x lanes x 4 B lane descriptors
+        ids = host_tokens[tokens > 0]
+        out = model.step(ids, want_tokens=True, lanes=args.lanes)  # host -> device ids, device -> host greedy tokens (synchronises)
+        host_tokens = out
+        h2d += starts.nbytes + tokens.nbytes + ids.nbytes
+        d2h += out.nbytes
+        e2e_tokens += lanes.advance()
+    be.synchronize()
+    e2e_elapsed = time.perf_counter() - t0
+    if sampler is not None:
+        sampler.terminate()
+        sampler.wait()
+    clocks = read_clock_samples(clocks_path)
+
+    elapsed, total_tokens, (e2e_tok_sum, attn_bytes_sum) = reduce_max_sum(dist, local, elapsed, total_tokens, [e2e_tokens, attn_bytes])
+    e2e_elapsed, _, _ = reduce_max_sum(dist, local, e2e_elapsed, 0, [])
+    if rank != 0:
+        return None
+    peaks = load_peaks()
+    # attn_bytes sums one launch per step; every step launches the kernel once per layer on the same lanes
+    achieved = (attn_bytes * cfg["layers"] / 1e9) / (attn_ns * 1e-9) if attn_ns else None
+    per_launch_bytes = attn_bytes / max(profiled_steps, 1)
+    result = {
+        "metric": "ragged decode tok/s", "value": total_tokens / elapsed, "unit": "tok/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": elapsed / args.steps * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": "qwen3-0.6b-arch bf16 continuous-batching decode, 128 lanes, ctx log-uniform 128-%d, page 16" % args.ctx_max,
+                   "lanes_per_gpu": args.lanes, "layers": cfg["layers"], "pool_pages": args.pool_pages, "admitted_requests": lanes.admitted,
+                   "mean_kv_tokens_per_step": kv_tokens / args.steps, "parallelism": "independent replicas over sequences (no collective)",
+                   "l2": "inputs larger than L2: each step streams the KV of every lane (tens of GB) and 1.19 GB of weights"},
+        "clocks": clocks,
+        "e2e": {"value": e2e_tok_sum / e2e_elapsed, "unit": "tok/s", "h2d_bytes_per_step": h2d / e2e_steps, "d2h_bytes_per_step": d2h / e2e_steps,
+                "ms_per_step": e2e_elapsed / e2e_steps * 1e3},
+        "gpu_launches": int(launches),
+        "roofline": {"kernel": "attn_decode_mma_kernel (paged GQA decode attention, split-K)", "bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"],
+                     "unit": "GB/s", "frac": (achieved / peaks["hbm_gbs"]) if achieved else None, "peak_source": peaks["source"],
+                     "algorithmic_bytes_per_launch": per_launch_bytes, "launches": int(attn_launches), "avg_launch_us": attn_ns / max(attn_launches, 1) * 1e-3,
+                     "attention_share_of_step": (attn_ns * 1e-9 / max(profiled_steps, 1)) / (elapsed / args.steps) if elapsed else None, "profiled_steps": profiled_steps, "work_items_last_step": stats["attn_work_items"],
+                     "traffic": ncu_traffic_per_launch(per_launch_bytes)},
+    }
+    step_bytes = 2 * sum_weight_params(cfg) + (kv_tokens / args.steps) * cfg["layers"] * cfg["kv_heads"] * cfg["head_dim"] * 2 * 2
+    result["step_roofline"] = {"algorithmic_gb_per_step": step_bytes / 1e9, "achieved_gbs": step_bytes / 1e9 / (elapsed / args.steps),
+                               "frac_of_hbm_peak": step_bytes / 1e9 / (elapsed / args.steps) / peaks["hbm_gbs"]}
+    if world == 1 and not args.no_cpu_baseline:
+        result["cpu_baseline"] = cpu_baseline(args, cfg, budget_s=20.0)
+    model.close()
+    pool.close()
+    return result
+
+
+def sum_weight_params(cfg):
+    qd, kd = cfg["q_heads"] * cfg["head_dim"], cfg["kv_heads"] * cfg["head_dim"]
+    per_layer = cfg["hidden"] * (qd + 2 * kd) + cfg["hidden"] * qd + 3 * cfg["hidden"] * cfg["intermediate"]
+    return cfg["layers"] * per_layer + cfg["vocab"] * cfg["hidden"]
+
+
+def load_peaks():
+    """Roofline denominators: the driver-measured copy bandwidth of this pool's B200s, else the
+    earlier pool measurement."""
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        data = json.load(open(path))
+        return {"hbm_gbs": float(data["hbm_gbs"]), "source": "measured (MEASURED_PEAKS.json)"}
+    except (OSError, KeyError, ValueError):
+        return {"hbm_gbs": 6650.0, "source": "fallback (earlier pool measurement)"}
+
+
+# DRAM traffic of the decode-attention kernel relative to its algorithmic bytes, from the ncu
+# capture summarised in profiles/attn_decode_mma_c2_decode.md (dram__bytes_read.sum +
+# dram__bytes_write.sum over the algorithmic bytes of the captured launch). None until captured.
+NCU_TRAFFIC_RATIO = None
+
+
+def ncu_traffic_per_launch(algorithmic_bytes):
+    return None if NCU_TRAFFIC_RATIO is None else algorithmic_bytes * NCU_TRAFFIC_RATIO
+
+
+def cpu_sample(args, cfg, n_lanes, threads):
+    """Builds the CPU port (the oracle engine, test infrastructure) on a sample of the workload:
+    `n_lanes` requests drawn from the same length distribution, synthetic N(0,1) KV contexts."""
+    from oracle import engine, fjo
+    fjo.set_threads(threads)
+    requests = Requests(args.seed * 1000, args.ctx_max)
+    sample = [requests.next() for _ in range(args.lanes)]
+    pick = [sample[i] for i in np.linspace(0, args.lanes - 1, n_lanes).astype(int)]
+    pages = [(ctx + 2 + PAGE - 1) // PAGE for ctx, _ in pick]
+    physical = sum(pages) + 1
+    weights = engine.random_dense_weights(cfg, args.seed)
+    ref = engine.DenseOracle(cfg, weights, physical, PAGE)
+    rng = np.random.default_rng(args.seed)
+    block = f32_to_bf16_bits(rng.standard_normal(1 << 20, dtype=np.float32))
+    for plane in ref.k_planes + ref.v_planes:
+        flat = plane.reshape(-1)
+        flat[:] = np.resize(block, flat.size)
+    generations = np.ones(physical, np.uint32)
+    tables, cursor = [], 0
+    for n in pages:
+        t = np.zeros((n, 2), np.uint32)
+        t[:, 0] = np.arange(cursor, cursor + n)
+        t[:, 1] = 1
+        tables.append(t)
+        cursor += n
+    return ref, pick, tables, generations
+
+
+def cpu_decode_step(ref, pick, tables, generations, offset):
+    tokens = 0
+    for (ctx, _), table in zip(pick, tables):
+        ref.forward_lane([(ctx * 7 + offset) % ref.cfg["vocab"]], ctx + offset, table, generations)
+        tokens += 1
+    return tokens
+
+
+def cpu_baseline(args, cfg, budget_s):
+    """Times the CPU port on this box's host cores on a bounded sample (one decode step of a few
+    lanes of the same workload). A reported baseline, not the optimisation target."""
+    from oracle import fjo
+    threads = fjo.max_threads()
+    n_lanes = 2
+    ref, pick, tables, generations = cpu_sample(args, cfg, n_lanes, threads)
+    t0 = time.perf_counter()
+    tokens = cpu_decode_step(ref, pick, tables, generations, 0)
+    first = time.perf_counter() - t0
+    steps = 1
+    if first < budget_s / 2:
+        t0 = time.perf_counter()
+        tokens = cpu_decode_step(ref, pick, tables, generations, 1)
+        first = time.perf_counter() - t0
+    fjo.set_threads(1)
+    return {"value": tokens / first, "unit": "tok/s", "cores": threads, "kind": "port",
+            "sample": f"{steps} decode step of {n_lanes} lanes (contexts {[c for c, _ in pick]}) of the same request stream, all {cfg['layers']} layers, "
+                      f"C++ restatement of forja-cpu with OpenMP over rows/columns"}
+
+
+def run_reference(args):
+    """Reference arm: forja's own CPU backend cannot be built here (Rust, no toolchain), so the CPU
+    port (oracle restatement of crates/forja-cpu) is timed on the host cores with every thread it
+    can use. Each step decodes a bounded sample of lanes of the same workload."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return None
+    from oracle import fjo
+    cfg = dict(QWEN3_06B)
+    if args.layers:
+        cfg["layers"] = args.layers
+    threads = fjo.max_threads()
+    n_lanes = 1
+    ref, pick, tables, generations = cpu_sample(args, cfg, n_lanes, threads)
+    budget = 150.0
+    t0 = time.perf_counter()
+    cpu_decode_step(ref, pick, tables, generations, 0)
+    one = time.perf_counter() - t0
+    steps = max(1, min(args.steps, int(budget / max(one, 1e-3)) - args.warmup))
+    warmup = min(args.warmup, max(0, int(budget / max(one, 1e-3)) - steps))
+    for w in range(warmup):
+        cpu_decode_step(ref, pick, tables, generations, 1 + w)
+    t0 = time.perf_counter()
+    tokens = 0
+    for s in range(steps):
+        tokens += cpu_decode_step(ref, pick, tables, generations, 1 + warmup + s)
+    elapsed = time.perf_counter() - t0
+    fjo.set_threads(1)
+    value = tokens / elapsed
+    sample = f"each step decodes {n_lanes} lane (context {pick[0][0]}) of the same request stream through all {cfg['layers']} layers; {steps} timed steps"
+    return {"impl": "reference", "metric": "ragged decode tok/s", "value": value, "unit": "tok/s", "n_gpus": args.gpus, "steps": steps, "warmup": warmup,
+            "ms_per_step": elapsed / steps * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": "qwen3-0.6b-arch bf16 continuous-batching decode, 128 lanes, ctx log-uniform 128-%d, page 16" % args.ctx_max,
+                       "note": "forja-cpu restated in C++ (the Rust reference cannot be compiled on this box); steps requested %d" % args.steps},
+            "cpu_baseline": {"value": value, "unit": "tok/s", "cores": threads, "kind": "port", "sample": sample},
+            "e2e": {"value": value, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}, "gpu_launches": 0}
+
+
+def main():
+    args = parse_args()
+    result = run_reference(args) if args.impl == "reference" else run_native(args)
+    if result is not None:
+        print(json.dumps(result))
+
+
+if __name__ == "__main__":
+    main()

@@ -57,7 +57,7 @@ EXPORTS = [
     "fj_timer_record", "fj_timer_elapsed_ns", "fj_kvpool_create", "fj_kvpool_destroy", "fj_kvpool_reserve", "fj_kvpool_release",
     "fj_kvpool_read_table", "fj_kvpool_read_generations", "fj_kvpool_read_free", "fj_kvpool_tables_buffer",
     "fj_kvpool_generations_buffer", "fj_pack_step", "fj_dense_model_create", "fj_dense_model_destroy", "fj_dense_step",
-    "fj_dense_step_stats",
+    "fj_dense_step_stats", "fj_dense_fill_kv", "fj_dense_profile_attention", "fj_dense_attention_time",
 ]
 
 _lib = None
@@ -106,7 +106,8 @@ def load():
         "fj_kvpool_create": [P, U32, U32, U32, U32, P], "fj_kvpool_reserve": [P, P, P, U32, P], "fj_kvpool_release": [P, P, U32],
         "fj_kvpool_read_table": [P, U32, P], "fj_kvpool_read_generations": [P, P], "fj_kvpool_read_free": [P, P, U32, P],
         "fj_pack_step": [P, P, P, U32, P], "fj_dense_model_create": [P, P, U64, U64, P, P, P], "fj_dense_step": [P, P, P, U64],
-        "fj_dense_step_stats": [P, P, P],
+        "fj_dense_step_stats": [P, P, P], "fj_dense_fill_kv": [P, U64], "fj_dense_profile_attention": [P, U32],
+        "fj_dense_attention_time": [P, P, P],
     }
     for name, types in argtypes.items():
         fn = getattr(lib, name)

@@ -476,6 +476,17 @@ class DenseModel:
                                        None if out is None else out.ctypes.data_as(C.c_void_p), logits.buffer if logits is not None else 0))
         return out
 
+    def fill_kv(self, seed: int = 0):
+        _check(self._lib.fj_dense_fill_kv(self._h, seed))
+
+    def profile_attention(self, enabled: bool):
+        _check(self._lib.fj_dense_profile_attention(self._h, int(enabled)))
+
+    def attention_time(self):
+        ns, n = C.c_uint64(0), C.c_uint64(0)
+        _check(self._lib.fj_dense_attention_time(self._h, C.byref(ns), C.byref(n)))
+        return ns.value, n.value
+
     def stats(self):
         k, w = C.c_uint64(0), C.c_uint64(0)
         _check(self._lib.fj_dense_step_stats(self._h, C.byref(k), C.byref(w)))

@@ -62,12 +62,9 @@ __device__ inline float round_through(float v, int dt) {
   }
 }
 
-// f32::total_cmp as an unsigned key: larger key = greater under IEEE total order.
-__device__ inline unsigned int total_order_key(float v) {
-  int b = __float_as_int(v);
-  b ^= static_cast<int>(static_cast<unsigned int>(b >> 31) >> 1);
-  return static_cast<unsigned int>(b) ^ 0x80000000u;
-}
+// f32::total_cmp as an unsigned key (larger key = greater under IEEE total order). Keys are built
+// from raw bits: routing a NaN through a float register before taking its bits lost the ordering
+// of positive NaNs on sm_100a builds, so no float value is involved.
 // Bits of element `index` widened to f32 with integer arithmetic only, so NaN sign and payload
 // reach the ordering key untouched (the reference decodes f16/bf16 NaNs as sign | quiet | payload).
 __device__ inline unsigned int load_f32_bits(const void* base, int dt, size_t index) {
@@ -87,11 +84,6 @@ __device__ inline unsigned int key_to_bits(unsigned int key) {
   int b = static_cast<int>(key ^ 0x80000000u);
   b ^= static_cast<int>(static_cast<unsigned int>(b >> 31) >> 1);
   return static_cast<unsigned int>(b);
-}
-__device__ inline float key_to_float(unsigned int key) {
-  int b = static_cast<int>(key ^ 0x80000000u);
-  b ^= static_cast<int>(static_cast<unsigned int>(b >> 31) >> 1);
-  return __int_as_float(b);
 }
 
 __device__ inline float warp_sum(float v) {
@@ -134,6 +126,7 @@ struct View {
   unsigned long long strides[8];
 };
 __device__ inline size_t view_offset(const View& v, size_t linear) {
+  if (v.rank == 1) return linear * v.strides[0];
   size_t off = 0;
 #pragma unroll 1
   for (int a = v.rank - 1; a >= 0; --a) {

@@ -320,6 +320,134 @@ __global__ void qknorm_rope_append_kernel(const T* __restrict__ qkv, const T* __
   }
 }
 
+// ---- dense fast paths: rows of 16-bit elements, 16-byte vector accesses, one CTA per row -------
+// Same arithmetic as the generic kernels above; chosen by the launchers when every operand is a
+// plain row-major matrix (last stride 1, 16-byte aligned rows, width a multiple of 8).
+
+struct DenseRow {
+  bool ok;
+  char* base;
+  size_t row_stride;  // elements
+};
+
+inline DenseRow dense_rows(const View& v, size_t rows, unsigned width, bool broadcast_rows) {
+  DenseRow d{false, static_cast<char*>(v.base), 0};
+  if (v.dtype != BF16 && v.dtype != F16) return d;
+  if (v.rank < 1 || v.shape[v.rank - 1] != width || v.strides[v.rank - 1] != 1) return d;
+  // leading axes must collapse to one row index
+  size_t expect = 0;
+  for (int a = v.rank - 2; a >= 0; --a) {
+    if (v.shape[a] == 1) continue;
+    if (expect == 0) { d.row_stride = v.strides[a]; expect = v.strides[a] * v.shape[a]; }
+    else if (v.strides[a] != expect) return d;
+    else expect *= v.shape[a];
+  }
+  if (broadcast_rows ? d.row_stride != 0 : (rows > 1 && d.row_stride < width)) return d;
+  if (width % 8 != 0 || d.row_stride % 8 != 0 || reinterpret_cast<size_t>(v.base) % 16 != 0) return d;
+  d.ok = true;
+  return d;
+}
+
+template <typename T> __device__ inline void unpack8(const uint4& v, float* out) {
+  const T* p = reinterpret_cast<const T*>(&v);
+#pragma unroll
+  for (int i = 0; i < 8; ++i) out[i] = to_f32(p[i]);
+}
+template <typename T> __device__ inline uint4 pack8(const float* in) {
+  uint4 v;
+  T* p = reinterpret_cast<T*>(&v);
+#pragma unroll
+  for (int i = 0; i < 8; ++i) p[i] = from_f32<T>(in[i]);
+  return v;
+}
+
+// residual == nullptr: plain rms_norm of `update`.
+template <typename T>
+__global__ void __launch_bounds__(128) norm_dense_kernel(const T* residual, size_t r_stride, const T* update, size_t u_stride, const T* __restrict__ w,
+                                                         T* sum_out, size_t s_stride, T* norm_out, size_t n_stride, unsigned width, float eps,
+                                                         int round_sum) {
+  __shared__ float red[32];
+  const size_t row = blockIdx.x;
+  const unsigned vecs = width / 8;
+  float sum = 0.0f;
+  for (unsigned v = threadIdx.x; v < vecs; v += blockDim.x) {
+    float x[8];
+    unpack8<T>(*reinterpret_cast<const uint4*>(update + row * u_stride + v * 8), x);
+    if (residual) {
+      float r[8];
+      unpack8<T>(*reinterpret_cast<const uint4*>(residual + row * r_stride + v * 8), r);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) { x[i] = r[i] + x[i]; if (round_sum) x[i] = to_f32(from_f32<T>(x[i])); }
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) sum += x[i] * x[i];
+  }
+  sum = block_sum(sum, red);
+  const float inverse = 1.0f / sqrtf(sum / static_cast<float>(width) + eps);
+  for (unsigned v = threadIdx.x; v < vecs; v += blockDim.x) {
+    float x[8], g[8], y[8];
+    unpack8<T>(*reinterpret_cast<const uint4*>(update + row * u_stride + v * 8), x);
+    if (residual) {
+      float r[8];
+      unpack8<T>(*reinterpret_cast<const uint4*>(residual + row * r_stride + v * 8), r);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) { x[i] = r[i] + x[i]; if (round_sum) x[i] = to_f32(from_f32<T>(x[i])); }
+      *reinterpret_cast<uint4*>(sum_out + row * s_stride + v * 8) = pack8<T>(x);
+    }
+    unpack8<T>(*reinterpret_cast<const uint4*>(w + v * 8), g);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) y[i] = x[i] * inverse * g[i];
+    *reinterpret_cast<uint4*>(norm_out + row * n_stride + v * 8) = pack8<T>(y);
+  }
+}
+
+// mode 0: a + b; mode 1: a * sigmoid(a) * b
+template <typename T>
+__global__ void map2_dense_kernel(const T* a, size_t a_stride, const T* b, size_t b_stride, T* out, size_t o_stride, size_t rows, unsigned width, int mode) {
+  const unsigned vecs = width / 8;
+  const size_t total = rows * vecs;
+  for (size_t idx = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; idx < total; idx += static_cast<size_t>(gridDim.x) * blockDim.x) {
+    const size_t row = idx / vecs, v = idx % vecs;
+    float x[8], y[8], z[8];
+    unpack8<T>(*reinterpret_cast<const uint4*>(a + row * a_stride + v * 8), x);
+    unpack8<T>(*reinterpret_cast<const uint4*>(b + row * b_stride + v * 8), y);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) z[i] = mode == 0 ? x[i] + y[i] : x[i] * sigmoid_ref(x[i]) * y[i];
+    *reinterpret_cast<uint4*>(out + row * o_stride + v * 8) = pack8<T>(z);
+  }
+}
+
+template <typename T>
+bool try_norm_dense(Ctx& ctx, const View* residual, const View& update, const View& w, const View* sum_out, const View& norm_out, size_t rows, unsigned width,
+                    float eps, int round_sum) {
+  const int dt = update.dtype;
+  if (w.dtype != dt || norm_out.dtype != dt || (residual && (residual->dtype != dt || sum_out->dtype != dt))) return false;
+  DenseRow u = dense_rows(update, rows, width, false), g = dense_rows(w, rows, width, true), n = dense_rows(norm_out, rows, width, false);
+  DenseRow r{true, nullptr, 0}, s{true, nullptr, 0};
+  if (residual) { r = dense_rows(*residual, rows, width, false); s = dense_rows(*sum_out, rows, width, false); }
+  if (!u.ok || !g.ok || !n.ok || !r.ok || !s.ok || rows > 0x7FFFFFFFull) return false;
+  norm_dense_kernel<T><<<static_cast<unsigned>(rows), 128, 0, ctx.stream>>>(reinterpret_cast<const T*>(r.base), r.row_stride, reinterpret_cast<const T*>(u.base), u.row_stride,
+                                                                          reinterpret_cast<const T*>(g.base), reinterpret_cast<T*>(s.base), s.row_stride,
+                                                                          reinterpret_cast<T*>(n.base), n.row_stride, width, eps, round_sum);
+  ctx.launches++;
+  return true;
+}
+
+template <typename T>
+bool try_map2_dense(Ctx& ctx, const View& a, const View& b, const View& out, size_t n, int mode) {
+  if (a.rank < 1 || a.dtype != b.dtype || a.dtype != out.dtype) return false;
+  const unsigned width = a.shape[a.rank - 1];
+  if (width == 0 || n % width != 0) return false;
+  const size_t rows = n / width;
+  DenseRow x = dense_rows(a, rows, width, false), y = dense_rows(b, rows, width, false), o = dense_rows(out, rows, width, false);
+  if (!x.ok || !y.ok || !o.ok) return false;
+  const size_t total = rows * (width / 8);
+  map2_dense_kernel<T><<<grid_for(total, kThreads, ctx.sm_count), kThreads, 0, ctx.stream>>>(reinterpret_cast<const T*>(x.base), x.row_stride, reinterpret_cast<const T*>(y.base),
+                                                                                           y.row_stride, reinterpret_cast<T*>(o.base), o.row_stride, rows, width, mode);
+  ctx.launches++;
+  return true;
+}
+
 }  // namespace
 
 void launch_copy(Ctx& ctx, const View& in, const View& out, size_t n) {
@@ -332,22 +460,30 @@ void launch_fill_zero(Ctx& ctx, void* ptr, size_t bytes) {
 }
 void launch_add(Ctx& ctx, const View& a, const View& b, const View& out, size_t n) {
   if (n == 0) return;
+  if (a.dtype == BF16 && try_map2_dense<__nv_bfloat16>(ctx, a, b, out, n, 0)) return;
+  if (a.dtype == F16 && try_map2_dense<__half>(ctx, a, b, out, n, 0)) return;
   add_kernel<<<grid_for(n, kThreads, ctx.sm_count), kThreads, 0, ctx.stream>>>(a, b, out, n);
   ctx.launches++;
 }
 void launch_silu_mul(Ctx& ctx, const View& gate, const View& up, const View& out, size_t n) {
   if (n == 0) return;
+  if (gate.dtype == BF16 && try_map2_dense<__nv_bfloat16>(ctx, gate, up, out, n, 1)) return;
+  if (gate.dtype == F16 && try_map2_dense<__half>(ctx, gate, up, out, n, 1)) return;
   silu_mul_kernel<<<grid_for(n, kThreads, ctx.sm_count), kThreads, 0, ctx.stream>>>(gate, up, out, n);
   ctx.launches++;
 }
 void launch_rms_norm(Ctx& ctx, const View& x, const View& w, const View& out, size_t rows, unsigned width, float eps) {
   if (rows == 0) return;
+  if (x.dtype == BF16 && try_norm_dense<__nv_bfloat16>(ctx, nullptr, x, w, nullptr, out, rows, width, eps, 0)) return;
+  if (x.dtype == F16 && try_norm_dense<__half>(ctx, nullptr, x, w, nullptr, out, rows, width, eps, 0)) return;
   rms_norm_kernel<<<grid_for(rows * 32, kThreads, ctx.sm_count), kThreads, 0, ctx.stream>>>(x, w, out, rows, width, eps);
   ctx.launches++;
 }
 void launch_residual_norm(Ctx& ctx, const View& residual, const View& update, const View& w, const View& sum_out,
                           const View& norm_out, size_t rows, unsigned width, float eps, int round_sum) {
   if (rows == 0) return;
+  if (residual.dtype == BF16 && try_norm_dense<__nv_bfloat16>(ctx, &residual, update, w, &sum_out, norm_out, rows, width, eps, round_sum)) return;
+  if (residual.dtype == F16 && try_norm_dense<__half>(ctx, &residual, update, w, &sum_out, norm_out, rows, width, eps, round_sum)) return;
   residual_norm_kernel<<<grid_for(rows * 32, kThreads, ctx.sm_count), kThreads, 0, ctx.stream>>>(residual, update, w, sum_out, norm_out, rows, round_sum, width, eps);
   ctx.launches++;
 }

@@ -228,10 +228,20 @@ __global__ void __launch_bounds__(GEMM_THREADS) gemm_nt_mma_kernel(GemmParams p)
 #pragma unroll
       for (int j = 0; j < NT; ++j)
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
+        for (int e = 0; e < 4; e += 2) {
           const unsigned r = row0 + warp_m * WM + i * 16 + gr + (e >> 1) * 8;
-          const unsigned c = col0 + warp_n * WN + j * 8 + gc + (e & 1);
-          if (r < p.m && c < p.n) store_from_f32(p.c, p.c_dt, static_cast<size_t>(r) * p.ldc + c, acc[i][j][e]);
+          const unsigned c = col0 + warp_n * WN + j * 8 + gc;
+          if (r >= p.m) continue;
+          const size_t off = static_cast<size_t>(r) * p.ldc + c;
+          if (c + 1 < p.n && p.c_dt != F32 && (p.ldc & 1) == 0 && (reinterpret_cast<size_t>(p.c) & 3) == 0) {
+            unsigned packed;
+            if (p.c_dt == BF16) { __nv_bfloat162 v = __floats2bfloat162_rn(acc[i][j][e], acc[i][j][e + 1]); packed = *reinterpret_cast<unsigned*>(&v); }
+            else { __half2 v = __floats2half2_rn(acc[i][j][e], acc[i][j][e + 1]); packed = *reinterpret_cast<unsigned*>(&v); }
+            *reinterpret_cast<unsigned*>(static_cast<unsigned short*>(p.c) + off) = packed;
+          } else {
+            if (c < p.n) store_from_f32(p.c, p.c_dt, off, acc[i][j][e]);
+            if (c + 1 < p.n) store_from_f32(p.c, p.c_dt, off + 1, acc[i][j][e + 1]);
+          }
         }
     return;
   }
@@ -242,10 +252,15 @@ __global__ void __launch_bounds__(GEMM_THREADS) gemm_nt_mma_kernel(GemmParams p)
 #pragma unroll
     for (int j = 0; j < NT; ++j)
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
+      for (int e = 0; e < 4; e += 2) {
         const unsigned r = row0 + warp_m * WM + i * 16 + gr + (e >> 1) * 8;
-        const unsigned c = col0 + warp_n * WN + j * 8 + gc + (e & 1);
-        if (r < p.m && c < p.n) mine[static_cast<size_t>(r) * p.n + c] = acc[i][j][e];
+        const unsigned c = col0 + warp_n * WN + j * 8 + gc;
+        if (r < p.m && c + 1 < p.n && (p.n & 1) == 0) {
+          *reinterpret_cast<float2*>(mine + static_cast<size_t>(r) * p.n + c) = make_float2(acc[i][j][e], acc[i][j][e + 1]);
+        } else if (r < p.m) {
+          if (c < p.n) mine[static_cast<size_t>(r) * p.n + c] = acc[i][j][e];
+          if (c + 1 < p.n) mine[static_cast<size_t>(r) * p.n + c + 1] = acc[i][j][e + 1];
+        }
       }
   __threadfence();
   __syncthreads();
@@ -254,12 +269,38 @@ __global__ void __launch_bounds__(GEMM_THREADS) gemm_nt_mma_kernel(GemmParams p)
   __syncthreads();
   if (s_ticket != p.splits - 1) return;
   __threadfence();
-  for (unsigned idx = threadIdx.x; idx < BM * BN; idx += GEMM_THREADS) {
-    const unsigned r = row0 + idx / BN, c = col0 + idx % BN;
-    if (r < p.m && c < p.n) {
-      float sum = 0.0f;
-      for (unsigned s = 0; s < p.splits; ++s) sum += __ldcg(p.partial + (static_cast<size_t>(s) * p.m + r) * p.n + c);
-      store_from_f32(p.c, p.c_dt, static_cast<size_t>(r) * p.ldc + c, sum);
+  const bool vec4 = (p.n % 4 == 0) && (p.ldc % 4 == 0) && (reinterpret_cast<size_t>(p.c) % 8 == 0) && p.c_dt != F32;
+  if (vec4) {
+    // four columns per thread, all splits' loads of an element group issued back to back
+    for (unsigned idx = threadIdx.x; idx < BM * (BN / 4); idx += GEMM_THREADS) {
+      const unsigned r = row0 + idx / (BN / 4), c = col0 + (idx % (BN / 4)) * 4;
+      if (r < p.m && c < p.n) {
+        float4 sum = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+#pragma unroll 4
+        for (unsigned s = 0; s < p.splits; ++s) {
+          const float4 v = __ldcg(reinterpret_cast<const float4*>(p.partial + (static_cast<size_t>(s) * p.m + r) * p.n + c));
+          sum.x += v.x; sum.y += v.y; sum.z += v.z; sum.w += v.w;
+        }
+        unsigned short h[4];
+        if (p.c_dt == BF16) {
+          h[0] = __bfloat16_as_ushort(__float2bfloat16_rn(sum.x)); h[1] = __bfloat16_as_ushort(__float2bfloat16_rn(sum.y));
+          h[2] = __bfloat16_as_ushort(__float2bfloat16_rn(sum.z)); h[3] = __bfloat16_as_ushort(__float2bfloat16_rn(sum.w));
+        } else {
+          h[0] = __half_as_ushort(__float2half_rn(sum.x)); h[1] = __half_as_ushort(__float2half_rn(sum.y));
+          h[2] = __half_as_ushort(__float2half_rn(sum.z)); h[3] = __half_as_ushort(__float2half_rn(sum.w));
+        }
+        uint2 packed = make_uint2(h[0] | (static_cast<unsigned>(h[1]) << 16), h[2] | (static_cast<unsigned>(h[3]) << 16));
+        *reinterpret_cast<uint2*>(static_cast<unsigned short*>(p.c) + static_cast<size_t>(r) * p.ldc + c) = packed;
+      }
+    }
+  } else {
+    for (unsigned idx = threadIdx.x; idx < BM * BN; idx += GEMM_THREADS) {
+      const unsigned r = row0 + idx / BN, c = col0 + idx % BN;
+      if (r < p.m && c < p.n) {
+        float sum = 0.0f;
+        for (unsigned s = 0; s < p.splits; ++s) sum += __ldcg(p.partial + (static_cast<size_t>(s) * p.m + r) * p.n + c);
+        store_from_f32(p.c, p.c_dt, static_cast<size_t>(r) * p.ldc + c, sum);
+      }
     }
   }
   if (threadIdx.x == 0) p.counters[tile] = 0;

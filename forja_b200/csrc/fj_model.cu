@@ -217,6 +217,18 @@ struct fj_dense_model {
   uint32_t work_cap = 0;
   const float* inv_freq = nullptr;
   uint64_t last_kernels = 0, last_work_items = 0;
+  // attention timing (CUDA event pairs on the backend's stream)
+  bool profile_attention = false;
+  std::vector<cudaEvent_t> event_pool;                         // reusable events
+  std::vector<std::pair<cudaEvent_t, cudaEvent_t>> pending;    // recorded, not yet measured
+  uint64_t attention_ns = 0, attention_launches = 0;
+  size_t plane_bytes = 0;
+  cudaEvent_t take_event() {
+    if (!event_pool.empty()) { cudaEvent_t e = event_pool.back(); event_pool.pop_back(); return e; }
+    cudaEvent_t e = nullptr;
+    cudaEventCreate(&e);
+    return e;
+  }
 };
 
 namespace {
@@ -235,6 +247,27 @@ __global__ void gather_last_rows_kernel(const T* __restrict__ hidden, const unsi
     unsigned begin = cu_seqlens[lane], end = cu_seqlens[lane + 1];
     for (unsigned i = threadIdx.x; i < width; i += blockDim.x)
       out[static_cast<size_t>(lane) * width + i] = end > begin ? hidden[static_cast<size_t>(end - 1) * width + i] : T{};
+  }
+}
+
+// Seeded pseudo-random N(0, 1) fill (counter hash + Box-Muller), two values per thread iteration.
+__device__ inline unsigned long long mix64(unsigned long long z) {
+  z += 0x9e3779b97f4a7c15ull;
+  z = (z ^ (z >> 30)) * 0xbf58476d1ce4e5b9ull;
+  z = (z ^ (z >> 27)) * 0x94d049bb133111ebull;
+  return z ^ (z >> 31);
+}
+__global__ void fill_normal_kernel(void* out, int dt, size_t elements, unsigned long long seed) {
+  const size_t pairs = (elements + 1) / 2;
+  for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < pairs; i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+    const unsigned long long r = mix64(seed ^ (i * 0xD1342543DE82EF95ull));
+    const float u1 = (static_cast<float>(static_cast<unsigned>(r >> 40)) + 0.5f) * (1.0f / 16777216.0f);
+    const float u2 = (static_cast<float>(static_cast<unsigned>(r & 0xFFFFFFu)) + 0.5f) * (1.0f / 16777216.0f);
+    const float radius = sqrtf(-2.0f * logf(u1));
+    float s, c;
+    sincospif(2.0f * u2, &s, &c);
+    fj::store_from_f32(out, dt, 2 * i, radius * c);
+    if (2 * i + 1 < elements) fj::store_from_f32(out, dt, 2 * i + 1, radius * s);
   }
 }
 
@@ -286,6 +319,7 @@ int32_t fj_dense_model_create(fj_backend* be, const fj_dense_config* config, uin
   m->embed = weight(embed, static_cast<uint64_t>(c.vocab) * c.hidden);
   m->final_norm = weight(final_norm, c.hidden);
   const size_t plane_bytes = static_cast<size_t>(pool->dev.physical_pages) * pool->dev.page_tokens * kd * esz;
+  m->plane_bytes = plane_bytes;
   m->layers.resize(c.layers);
   for (uint32_t l = 0; l < c.layers && ok; ++l) {
     const fj_dense_layer_weights& w = layers[l];
@@ -356,6 +390,8 @@ void fj_dense_model_destroy(fj_dense_model* m) {
   cudaSetDevice(m->be->device);
   cudaStreamSynchronize(m->be->stream);
   for (void* p : m->owned) cudaFree(p);
+  for (auto& pair : m->pending) { cudaEventDestroy(pair.first); cudaEventDestroy(pair.second); }
+  for (auto e : m->event_pool) cudaEventDestroy(e);
   delete m;
 }
 
@@ -423,8 +459,11 @@ int32_t fj_dense_step(fj_dense_model* m, const uint32_t* token_ids, uint32_t* ou
     fj::launch_gemm_nt(ctx, m->normed, dt, H, L.wqkv, dt, H, m->qkv, dt, qd + 2 * kd, rows, qd + 2 * kd, H, be->gemm_scratch, be->gemm_scratch_bytes);
     fj::launch_qknorm_rope_append(ctx, m->qkv, dt, L.q_norm, L.k_norm, pool->pack.positions, pool->pack.slot_mapping, m->q, L.k_plane, L.v_plane, rows, c.q_heads, c.kv_heads,
                                   c.head_dim, c.eps, m->inv_freq, c.qk_norm ? 1 : 0, plane_slots);
+    cudaEvent_t attn_begin = nullptr, attn_end = nullptr;
+    if (m->profile_attention) { attn_begin = m->take_event(); attn_end = m->take_event(); cudaEventRecord(attn_begin, be->stream); }
     if (mma) fj::launch_attn_decode_mma(ctx, g, m->seqs, m->work, static_cast<unsigned>(n_work), L.k_plane, L.v_plane, pool->dev.generations, scratch, nullptr);
     else fj::launch_attn_generic(ctx, g, m->seqs, lanes, max_q_len, L.k_plane, L.v_plane, pool->dev.generations, nullptr);
+    if (m->profile_attention) { cudaEventRecord(attn_end, be->stream); m->pending.emplace_back(attn_begin, attn_end); }
     fj::launch_gemm_nt(ctx, m->attn, dt, qd, L.wo, dt, qd, m->proj, dt, H, rows, H, qd, be->gemm_scratch, be->gemm_scratch_bytes);
     // hidden' = hidden + attention ; normed = rms(hidden') * post_norm
     fj::launch_residual_norm(ctx, dense_view(hidden, dt, rows, H, H), dense_view(m->proj, dt, rows, H, H), weight_view(L.post_norm, dt, rows, H), dense_view(other, dt, rows, H, H),
@@ -470,6 +509,49 @@ int32_t fj_dense_step_stats(fj_dense_model* m, uint64_t* kernels, uint64_t* attn
   if (!m) return FJ_INVALID_INPUT;
   if (kernels) *kernels = m->last_kernels;
   if (attn_work_items) *attn_work_items = m->last_work_items;
+  return FJ_OK;
+}
+
+int32_t fj_dense_fill_kv(fj_dense_model* m, uint64_t seed) {
+  if (!m) return FJ_INVALID_INPUT;
+  fj_backend* be = m->be;
+  std::lock_guard<std::mutex> lock(be->mutex);
+  cudaSetDevice(be->device);
+  const size_t elements = m->plane_bytes / fj::dtype_size(static_cast<int>(m->cfg.dtype));
+  const unsigned grid = static_cast<unsigned>(be->ctx.sm_count) * 16;
+  for (size_t l = 0; l < m->layers.size(); ++l) {
+    fill_normal_kernel<<<grid, 256, 0, be->stream>>>(m->layers[l].k_plane, static_cast<int>(m->cfg.dtype), elements, seed * 131 + 2 * l);
+    fill_normal_kernel<<<grid, 256, 0, be->stream>>>(m->layers[l].v_plane, static_cast<int>(m->cfg.dtype), elements, seed * 131 + 2 * l + 1);
+    be->ctx.launches += 2;
+  }
+  return cuda_status(cudaStreamSynchronize(be->stream));
+}
+
+int32_t fj_dense_profile_attention(fj_dense_model* m, uint32_t enabled) {
+  if (!m) return FJ_INVALID_INPUT;
+  std::lock_guard<std::mutex> lock(m->be->mutex);
+  m->profile_attention = enabled != 0;
+  return FJ_OK;
+}
+
+int32_t fj_dense_attention_time(fj_dense_model* m, uint64_t* total_ns, uint64_t* launches) {
+  if (!m) return FJ_INVALID_INPUT;
+  std::lock_guard<std::mutex> lock(m->be->mutex);
+  cudaSetDevice(m->be->device);
+  for (auto& pair : m->pending) {
+    float ms = 0.0f;
+    if (cudaEventSynchronize(pair.second) == cudaSuccess && cudaEventElapsedTime(&ms, pair.first, pair.second) == cudaSuccess) {
+      m->attention_ns += static_cast<uint64_t>(static_cast<double>(ms) * 1.0e6);
+      m->attention_launches += 1;
+    } else {
+      cudaGetLastError();
+    }
+    m->event_pool.push_back(pair.first);
+    m->event_pool.push_back(pair.second);
+  }
+  m->pending.clear();
+  if (total_ns) *total_ns = m->attention_ns;
+  if (launches) *launches = m->attention_launches;
   return FJ_OK;
 }
 

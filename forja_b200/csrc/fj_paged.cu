@@ -190,20 +190,39 @@ __global__ void __launch_bounds__(kWarps * 32, 2) attn_decode_mma_kernel(DecodeP
   const unsigned smem_base = static_cast<unsigned>(__cvta_generic_to_shared(smem)) + warp * kStages * kStageBytes;
   const size_t plane_row_bytes = static_cast<size_t>(p.kv_heads) * kRowBytes;
 
-  auto issue = [&](unsigned j) {
+  // Page-table entries are authenticated 32 pages at a time (lane l owns the warp's page base + l)
+  // so the dependent table -> generation loads stay out of the steady-state loop.
+  unsigned ent_page = 0;
+  int ent_ok = 0;
+  auto fetch_entries = [&](unsigned base_j) {
+    const unsigned j = base_j + lane;
+    ent_page = 0;
+    ent_ok = 0;
     if (j < n_mine) {
       const unsigned lp = my_first + j * kWarps;
-      unsigned page = 0;
       bool ok = lp < seq.table_pages;
+      unsigned page = 0;
       if (ok) {
         page = seq.table[2 * lp];
         ok = authenticate(page, seq.table[2 * lp + 1], p.generations, p.physical_pages);
       }
       if (!ok) {
         bad = 1;
-        if (lane == 0) report_error(p.err, ERR_PAGE, lp);
+        report_error(p.err, ERR_PAGE, lp);
         page = 0;
       }
+      ent_page = page;
+      ent_ok = ok ? 1 : 0;
+    }
+  };
+  fetch_entries(0);
+
+  auto issue = [&](unsigned j) {
+    if (j < n_mine) {
+      if (j != 0 && (j & 31) == 0) fetch_entries(j);
+      const unsigned lp = my_first + j * kWarps;
+      const unsigned page = __shfl_sync(0xffffffffu, ent_page, j & 31);
+      const bool ok = __shfl_sync(0xffffffffu, ent_ok, j & 31) != 0;
       const unsigned stage = smem_base + (j % kStages) * kStageBytes;
       const size_t page_off = (static_cast<size_t>(page) * kPageTokens * p.kv_heads + kv_head) * kRowBytes;
 #pragma unroll
@@ -311,15 +330,16 @@ __global__ void __launch_bounds__(kWarps * 32, 2) attn_decode_mma_kernel(DecodeP
   }
   const int any_bad = __syncthreads_or(bad);  // also: every warp is done with the pipeline buffers
 
-  // combine the four warps through shared memory
+  // combine the four warps through shared memory; only the n_rows valid rows of the tile matter
   float* o_buf = reinterpret_cast<float*>(smem);                       // [4][16][128]
-  float* ml_buf = o_buf + kWarps * 16 * kHeadDim;                      // [4][2][16]
+  float* ml_buf = o_buf + kWarps * 16 * kHeadDim;                      // [4][2][16] running max, denominator
+  float* f_buf = ml_buf + kWarps * 2 * 16;                             // [4][16] warp factors, [16] row max, [16] row denominator
 #pragma unroll
   for (int nt = 0; nt < 16; ++nt) {
-    const unsigned col = nt * 8 + (lane & 3) * 2;
-    float* base = o_buf + (warp * 16) * kHeadDim + col;
-    *reinterpret_cast<float2*>(base + r0 * kHeadDim) = make_float2(o[nt][0], o[nt][1]);
-    *reinterpret_cast<float2*>(base + r1 * kHeadDim) = make_float2(o[nt][2], o[nt][3]);
+    const unsigned c = nt * 8 + (lane & 3) * 2;
+    float* base = o_buf + (warp * 16) * kHeadDim + c;
+    if (r0 < n_rows) *reinterpret_cast<float2*>(base + r0 * kHeadDim) = make_float2(o[nt][0], o[nt][1]);
+    if (r1 < n_rows) *reinterpret_cast<float2*>(base + r1 * kHeadDim) = make_float2(o[nt][2], o[nt][3]);
   }
   if ((lane & 3) == 0) {
     ml_buf[(warp * 2 + 0) * 16 + r0] = m[0];
@@ -328,36 +348,45 @@ __global__ void __launch_bounds__(kWarps * 32, 2) attn_decode_mma_kernel(DecodeP
     ml_buf[(warp * 2 + 1) * 16 + r1] = l[1];
   }
   __syncthreads();
-
-  const unsigned col = threadIdx.x;  // 128 threads = 128 columns
-  float acc[16], den[16], top[16];
-#pragma unroll
-  for (int r = 0; r < 16; ++r) {
+  if (threadIdx.x < 16) {
+    const int r = threadIdx.x;
     float big = -INFINITY;
 #pragma unroll
     for (int w = 0; w < kWarps; ++w) big = fmaxf(big, ml_buf[(w * 2) * 16 + r]);
-    float a = 0.0f, d = 0.0f;
+    float d = 0.0f;
 #pragma unroll
     for (int w = 0; w < kWarps; ++w) {
       const float mw = ml_buf[(w * 2) * 16 + r];
       const float f = mw == -INFINITY ? 0.0f : expf(mw - big);
-      a += f * o_buf[(w * 16 + r) * kHeadDim + col];
+      f_buf[w * 16 + r] = f;
       d += f * ml_buf[(w * 2 + 1) * 16 + r];
     }
-    acc[r] = a; den[r] = d; top[r] = big;
+    f_buf[kWarps * 16 + r] = big;
+    f_buf[kWarps * 16 + 16 + r] = d;
   }
+  __syncthreads();
 
-  if (work.n_splits == 1) {
-    store_rows(seq, p, kv_head, col, acc, den, any_bad != 0);
-    return;
-  }
-
-  // split-K: publish this CTA's partial, the last CTA of the (sequence, kv head) group merges
+  const unsigned col = threadIdx.x;  // 128 threads = 128 columns
+  const bool single = work.n_splits == 1;
   float* po = p.part_o + static_cast<size_t>(work.slot) * 16 * kHeadDim;
   float* pml = p.part_ml + static_cast<size_t>(work.slot) * 32;
+  for (unsigned r = 0; r < n_rows; ++r) {
+    float a = 0.0f;
 #pragma unroll
-  for (int r = 0; r < 16; ++r) po[r * kHeadDim + col] = acc[r];
-  if (col < 16) { pml[col] = top[col]; pml[16 + col] = den[col]; }
+    for (int w = 0; w < kWarps; ++w) a += f_buf[w * 16 + r] * o_buf[(w * 16 + r) * kHeadDim + col];
+    if (single) {
+      const float d = f_buf[kWarps * 16 + 16 + r];
+      const unsigned tok = r / p.group, head = kv_head * p.group + r % p.group;
+      const float v = (any_bad || d <= 0.0f) ? 0.0f : a / d;
+      store_from_f32(seq.out, p.out_dtype, static_cast<size_t>(tok) * seq.o_tok_stride + static_cast<size_t>(head) * seq.o_head_stride + col, v);
+    } else {
+      po[r * kHeadDim + col] = a;
+    }
+  }
+  if (single) return;
+
+  // split-K: publish this CTA's partial, the last CTA of the (sequence, kv head) group merges
+  if (col < 16) { pml[col] = f_buf[kWarps * 16 + col]; pml[16 + col] = f_buf[kWarps * 16 + 16 + col]; }
   __threadfence();
   __syncthreads();
   if (threadIdx.x == 0) s_ticket = atomicAdd(&p.counters[work.group_index], 1u + (any_bad ? 0x10000u : 0u)) + 1u + (any_bad ? 0x10000u : 0u);
@@ -366,8 +395,8 @@ __global__ void __launch_bounds__(kWarps * 32, 2) attn_decode_mma_kernel(DecodeP
   if ((ticket & 0xFFFFu) != work.n_splits) return;
   __threadfence();
   const unsigned slot_base = work.slot - work.split;
-#pragma unroll 1
-  for (int r = 0; r < 16; ++r) {
+  const bool zero = (ticket >> 16) != 0;
+  for (unsigned r = 0; r < n_rows; ++r) {
     float big = -INFINITY;
     for (unsigned sp = 0; sp < work.n_splits; ++sp) big = fmaxf(big, __ldcg(p.part_ml + static_cast<size_t>(slot_base + sp) * 32 + r));
     float a = 0.0f, d = 0.0f;
@@ -377,9 +406,10 @@ __global__ void __launch_bounds__(kWarps * 32, 2) attn_decode_mma_kernel(DecodeP
       a += f * __ldcg(p.part_o + (static_cast<size_t>(slot_base + sp) * 16 + r) * kHeadDim + col);
       d += f * __ldcg(p.part_ml + static_cast<size_t>(slot_base + sp) * 32 + 16 + r);
     }
-    acc[r] = a; den[r] = d;
+    const unsigned tok = r / p.group, head = kv_head * p.group + r % p.group;
+    const float v = (zero || d <= 0.0f) ? 0.0f : a / d;
+    store_from_f32(seq.out, p.out_dtype, static_cast<size_t>(tok) * seq.o_tok_stride + static_cast<size_t>(head) * seq.o_head_stride + col, v);
   }
-  store_rows(seq, p, kv_head, col, acc, den, (ticket >> 16) != 0);
   if (threadIdx.x == 0) p.counters[work.group_index] = 0;  // leave the counter ready for the next launch
 }
 

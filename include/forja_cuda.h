@@ -250,8 +250,16 @@ void fj_dense_model_destroy(fj_dense_model* model);
  * NULL. logits_out: buffer id receiving [lanes, vocab] in the activation dtype, or 0. The call
  * returns after the step completed when out_tokens != NULL, else it only enqueues. */
 int32_t fj_dense_step(fj_dense_model* model, const uint32_t* token_ids, uint32_t* out_tokens, uint64_t logits_out);
-/* Device time and launch count of the last completed step; attention split statistics. */
+/* Launch count of the last step and the number of split-K work items of its attention launches. */
 int32_t fj_dense_step_stats(fj_dense_model* model, uint64_t* kernels, uint64_t* attn_work_items);
+/* Fills every K/V plane of the model with seeded pseudo-random N(0, 1) values in the plane dtype
+ * (synthetic contexts for benchmarks: any page a lane is given already holds finite random rows). */
+int32_t fj_dense_fill_kv(fj_dense_model* model, uint64_t seed);
+/* Attention timing: when enabled, every paged-attention launch of fj_dense_step is bracketed by
+ * CUDA events on the backend's stream. fj_dense_attention_time drains the recorded pairs
+ * (synchronising on them), adds their durations and launch count to the totals and returns them. */
+int32_t fj_dense_profile_attention(fj_dense_model* model, uint32_t enabled);
+int32_t fj_dense_attention_time(fj_dense_model* model, uint64_t* total_ns, uint64_t* launches);
 
 #ifdef __cplusplus
 }
