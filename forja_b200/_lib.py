@@ -58,6 +58,7 @@ EXPORTS = [
     "fj_kvpool_read_table", "fj_kvpool_read_generations", "fj_kvpool_read_free", "fj_kvpool_tables_buffer",
     "fj_kvpool_generations_buffer", "fj_pack_step", "fj_dense_model_create", "fj_dense_model_destroy", "fj_dense_step",
     "fj_dense_step_stats", "fj_dense_fill_kv", "fj_dense_profile_attention", "fj_dense_attention_time",
+    "fj_paged_decode_attention_static",
 ]
 
 _lib = None
@@ -108,6 +109,7 @@ def load():
         "fj_pack_step": [P, P, P, U32, P], "fj_dense_model_create": [P, P, U64, U64, P, P, P], "fj_dense_step": [P, P, P, U64],
         "fj_dense_step_stats": [P, P, P], "fj_dense_fill_kv": [P, U64], "fj_dense_profile_attention": [P, U32],
         "fj_dense_attention_time": [P, P, P],
+        "fj_paged_decode_attention_static": [P, P, P, P, P, P, P, P, U32, U32, U32, U32, U32, U32, C.c_float, P],
     }
     for name, types in argtypes.items():
         fn = getattr(lib, name)

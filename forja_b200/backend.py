@@ -364,6 +364,24 @@ class CudaBackend:
     def kernel_launch_count(self) -> int:
         return self._lib.fj_kernel_launch_count(self._h)
 
+    def device_ptr(self, tensor: Tensor) -> int:
+        """Device address of the first element of a tensor view."""
+        ptr, size = C.c_void_p(), C.c_uint64(0)
+        _check(self._lib.fj_buffer_device_ptr(self._h, tensor.buffer, C.byref(ptr), C.byref(size)))
+        return (ptr.value or 0) + tensor.layout.offset * DTYPE_SIZE[tensor.dtype]
+
+    def decode_attention_static(self, q: Tensor, out: Tensor, kpool: Tensor, vpool: Tensor, tables: Tensor, generations: Tensor,
+                                key_lengths, scale: float, status: Optional[Tensor] = None) -> int:
+        """fj_paged_decode_attention_static: decode attention whose scratch is a fixed array inside
+        the library (no allocation). q/out [lanes, q_heads, 128]; tables [lanes, table_pages, 2].
+        Returns the fj_status; FJ_QUOTA_EXCEEDED when the batch exceeds the array's limits."""
+        lengths = np.ascontiguousarray(key_lengths, np.uint32)
+        lanes, q_heads = q.shape[0], q.shape[1]
+        return self._lib.fj_paged_decode_attention_static(
+            self._h, self.device_ptr(q), self.device_ptr(out), self.device_ptr(kpool), self.device_ptr(vpool), self.device_ptr(tables),
+            self.device_ptr(generations), lengths.ctypes.data_as(C.c_void_p), lanes, tables.shape[1], kpool.shape[0], q_heads, kpool.shape[2],
+            q.dtype, scale, self.device_ptr(status) if status is not None else None)
+
     def timer(self) -> int:
         t = C.c_uint64(0)
         _check(self._lib.fj_timer_create(self._h, C.byref(t)))

@@ -572,3 +572,156 @@ void launch_paged_copy(Ctx& ctx, bool into_pages, void* ordinary, int o_dt, size
 }
 
 }  // namespace fj
+
+// ---------------------------------------------------------------------------------------------
+// Decode attention for callers that must not allocate
+// ---------------------------------------------------------------------------------------------
+// Some hosts of this library hand every byte of device memory to the KV page planes up front and
+// run the serving loop under a fixed quota, and some call from a latency-critical step where a
+// trip into the driver's allocator (which may synchronise the whole device) is not acceptable.
+// For them the split-K decode attention is offered once more with all of its scratch - lane
+// descriptors, work list, split partials, completion counters - carved out of one fixed array
+// that lives in the library image. Nothing is allocated, now or on first use; the price is a hard
+// ceiling on the batch (see the FJ_STATIC_ATTENTION_* limits) and that calls share the array.
+
+#include "fj_backend.h"
+
+namespace fj {
+namespace {
+
+constexpr unsigned kStaticMaxLanes = FJ_STATIC_ATTENTION_MAX_LANES;
+constexpr unsigned kStaticMaxGroups = FJ_STATIC_ATTENTION_MAX_GROUPS;
+constexpr unsigned kStaticMaxItems = FJ_STATIC_ATTENTION_MAX_ITEMS;
+
+// layout of the static scratch (byte offsets, each a multiple of 256)
+constexpr size_t kOffCounters = 0;                                                     // [groups] u32
+constexpr size_t kOffSeqs = kOffCounters + ((kStaticMaxGroups * 4 + 255) / 256) * 256;  // [lanes] AttnSeq
+constexpr size_t kOffWork = kOffSeqs + ((kStaticMaxLanes * sizeof(AttnSeq) + 255) / 256) * 256;
+constexpr size_t kOffPartMl = kOffWork + ((kStaticMaxItems * sizeof(AttnWork) + 255) / 256) * 256;
+constexpr size_t kOffPartO = kOffPartMl + static_cast<size_t>(kStaticMaxItems) * 32 * sizeof(float);
+constexpr size_t kStaticBytes = kOffPartO + static_cast<size_t>(kStaticMaxItems) * 16 * kHeadDim * sizeof(float);
+
+// Held by every GPU that loads the library, from load until exit (about 8.6 MB).
+static __device__ __align__(256) unsigned char g_static_attention_scratch[kStaticBytes];
+
+struct StaticPlan {
+  unsigned key_length[kStaticMaxLanes];
+  unsigned lanes, kv_heads, q_heads, table_pages, chunk, elem_bytes;
+  const char* q;
+  char* out;
+  const unsigned* tables;
+  unsigned* status;  // caller's two status words or nullptr
+};
+
+// Fills the lane descriptors and the work list inside the static array, zeroes the completion
+// counters (a previous call that ended early may have left them nonzero) and resets the caller's
+// status words. One CTA; the lists are a few thousand words.
+__global__ void static_attention_plan_kernel(StaticPlan plan, unsigned char* scratch) {
+  unsigned* counters = reinterpret_cast<unsigned*>(scratch + kOffCounters);
+  AttnSeq* seqs = reinterpret_cast<AttnSeq*>(scratch + kOffSeqs);
+  AttnWork* work = reinterpret_cast<AttnWork*>(scratch + kOffWork);
+  for (unsigned g = threadIdx.x; g < plan.lanes * plan.kv_heads; g += blockDim.x) counters[g] = 0;
+  if (plan.status != nullptr && threadIdx.x == 0) { plan.status[0] = 0; plan.status[1] = 0xFFFFFFFFu; }
+  const size_t row_elems = static_cast<size_t>(plan.q_heads) * kHeadDim;
+  for (unsigned lane = threadIdx.x; lane < plan.lanes; lane += blockDim.x) {
+    const unsigned len = plan.key_length[lane];
+    AttnSeq s;
+    s.q = plan.q + lane * row_elems * plan.elem_bytes;
+    s.out = plan.out + lane * row_elems * plan.elem_bytes;
+    s.table = plan.tables + static_cast<size_t>(lane) * plan.table_pages * 2;
+    s.activity = nullptr;
+    s.q_len = 1; s.q_start = len ? len - 1 : 0; s.key_length = len; s.table_pages = plan.table_pages;
+    s.q_tok_stride = row_elems; s.q_head_stride = kHeadDim; s.o_tok_stride = row_elems; s.o_head_stride = kHeadDim;
+    s.causal = 1; s.pad = 0;
+    seqs[lane] = s;
+    // items of this lane start after those of the lanes before it
+    unsigned first = 0;
+    for (unsigned other = 0; other < lane; ++other) {
+      const unsigned n = plan.key_length[other];
+      first += (n == 0 ? 1 : (n + plan.chunk - 1) / plan.chunk) * plan.kv_heads;
+    }
+    const unsigned splits = len == 0 ? 1 : (len + plan.chunk - 1) / plan.chunk;
+    for (unsigned h = 0; h < plan.kv_heads; ++h) {
+      for (unsigned sp = 0; sp < splits; ++sp) {
+        AttnWork w;
+        w.seq = lane; w.kv_head = h; w.t_begin = sp * plan.chunk; w.t_end = min(len, (sp + 1) * plan.chunk);
+        w.split = sp; w.n_splits = splits; w.slot = first + h * splits + sp; w.group_index = lane * plan.kv_heads + h;
+        work[w.slot] = w;
+      }
+    }
+  }
+}
+
+void* g_static_ptr[16] = {nullptr};  // device address of the array, one per CUDA device
+std::mutex g_static_mutex;
+
+}  // namespace
+}  // namespace fj
+
+extern "C" int32_t fj_paged_decode_attention_static(fj_backend* be, const void* q, void* out, const void* kpool, const void* vpool, const uint32_t* tables,
+                                                    const uint32_t* generations, const uint32_t* key_lengths, uint32_t lanes, uint32_t table_pages,
+                                                    uint32_t physical_pages, uint32_t q_heads, uint32_t kv_heads, uint32_t dtype, float scale, uint32_t* status) {
+  using namespace fj;
+  if (!be || !q || !out || !kpool || !vpool || !tables || !generations || !key_lengths || lanes == 0) return FJ_INVALID_INPUT;
+  if ((dtype != FJ_BF16 && dtype != FJ_F16) || kv_heads == 0 || q_heads % kv_heads != 0 || q_heads / kv_heads > 16 || !isfinite(scale)) return FJ_INVALID_INPUT;
+  if ((reinterpret_cast<size_t>(q) | reinterpret_cast<size_t>(out)) & 3) return FJ_INVALID_INPUT;
+  // ceilings of the fixed array: refuse, never spill into an allocation
+  if (lanes > kStaticMaxLanes || static_cast<uint64_t>(lanes) * kv_heads > kStaticMaxGroups) return FJ_QUOTA_EXCEEDED;
+  StaticPlan plan;
+  uint64_t chunk = 256;
+  for (;;) {
+    uint64_t items = 0;
+    for (uint32_t i = 0; i < lanes; ++i) {
+      if (static_cast<uint64_t>(key_lengths[i]) > static_cast<uint64_t>(table_pages) * kPageTokens) return FJ_INVALID_INPUT;
+      items += (key_lengths[i] == 0 ? 1 : (key_lengths[i] + chunk - 1) / chunk) * kv_heads;
+    }
+    if (items <= kStaticMaxItems) { plan.chunk = static_cast<unsigned>(chunk); break; }
+    chunk *= 2;
+    if (chunk > (1u << 20)) return FJ_QUOTA_EXCEEDED;
+  }
+  uint32_t n_work = 0;
+  for (uint32_t i = 0; i < lanes; ++i) {
+    plan.key_length[i] = key_lengths[i];
+    n_work += (key_lengths[i] == 0 ? 1 : (key_lengths[i] + plan.chunk - 1) / plan.chunk) * kv_heads;
+  }
+  std::lock_guard<std::mutex> lock(be->mutex);
+  if (be->device < 0 || be->device >= 16) return FJ_INVALID_INPUT;
+  if (cudaSetDevice(be->device) != cudaSuccess) return FJ_DEVICE_EXECUTION_FAILED;
+  void* scratch = nullptr;
+  {
+    // first call on this device: resolve the device address of the array (the host-side symbol
+    // is only a stand-in) and raise the kernels' shared-memory limit. Neither allocates.
+    std::lock_guard<std::mutex> setup(g_static_mutex);
+    if (g_static_ptr[be->device] == nullptr) {
+      void* ptr = nullptr;
+      if (cudaGetSymbolAddress(&ptr, g_static_attention_scratch) != cudaSuccess || ptr == nullptr) { cudaGetLastError(); return FJ_DEVICE_EXECUTION_FAILED; }
+      if (cudaFuncSetAttribute(attn_decode_mma_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kDecodeSmem) != cudaSuccess ||
+          cudaFuncSetAttribute(attn_decode_mma_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kDecodeSmem) != cudaSuccess) {
+        cudaGetLastError();
+        return FJ_DEVICE_EXECUTION_FAILED;
+      }
+      g_static_ptr[be->device] = ptr;
+    }
+    scratch = g_static_ptr[be->device];
+  }
+  unsigned char* base = static_cast<unsigned char*>(scratch);
+  plan.lanes = lanes; plan.kv_heads = kv_heads; plan.q_heads = q_heads; plan.table_pages = table_pages; plan.elem_bytes = 2;
+  plan.q = static_cast<const char*>(q); plan.out = static_cast<char*>(out); plan.tables = tables; plan.status = status;
+  static_attention_plan_kernel<<<1, 256, 0, be->stream>>>(plan, base);
+  DecodeParams p;
+  p.seqs = reinterpret_cast<const AttnSeq*>(base + kOffSeqs);
+  p.work = reinterpret_cast<const AttnWork*>(base + kOffWork);
+  p.n_work = n_work;
+  p.kpool = static_cast<const char*>(kpool); p.vpool = static_cast<const char*>(vpool);
+  p.generations = generations; p.physical_pages = physical_pages;
+  p.q_heads = q_heads; p.kv_heads = kv_heads; p.group = q_heads / kv_heads;
+  p.scale = scale; p.out_dtype = static_cast<int>(dtype);
+  p.part_o = reinterpret_cast<float*>(base + kOffPartO);
+  p.part_ml = reinterpret_cast<float*>(base + kOffPartMl);
+  p.counters = reinterpret_cast<unsigned*>(base + kOffCounters);
+  p.err = reinterpret_cast<ErrorRecord*>(status);
+  if (dtype == FJ_BF16) attn_decode_mma_kernel<true><<<n_work, kWarps * 32, kDecodeSmem, be->stream>>>(p);
+  else attn_decode_mma_kernel<false><<<n_work, kWarps * 32, kDecodeSmem, be->stream>>>(p);
+  be->ctx.launches += 2;
+  return cudaGetLastError() == cudaSuccess ? FJ_OK : FJ_DEVICE_EXECUTION_FAILED;
+}

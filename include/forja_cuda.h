@@ -261,6 +261,41 @@ int32_t fj_dense_fill_kv(fj_dense_model* model, uint64_t seed);
 int32_t fj_dense_profile_attention(fj_dense_model* model, uint32_t enabled);
 int32_t fj_dense_attention_time(fj_dense_model* model, uint64_t* total_ns, uint64_t* launches);
 
+/* ---- decode attention without any allocation ----------------------------------------------- */
+
+/* This entry point has no counterpart in the reference. It exists for hosts that cannot let the
+ * library allocate at step time: a server that has already given all device memory to the KV
+ * planes and holds the backend to a fixed quota, or a decode loop that must never enter the
+ * driver's allocator (cudaMalloc / cudaFree may stall the whole device). It runs the same
+ * split-K paged GQA decode attention as FJ_OP_PAGED_SDPA for one token per lane, but every piece
+ * of scratch it needs (lane descriptors, work list, split partials, counters) lives in a fixed
+ * array inside the library image, about 8.6 MB that each GPU loading the library holds until the
+ * process exits. It calls no cudaMalloc, cudaFree or other allocating routine.
+ *
+ * Limits (beyond them the call is refused with FJ_QUOTA_EXCEEDED and nothing runs):
+ * lanes <= FJ_STATIC_ATTENTION_MAX_LANES, lanes * kv_heads <= FJ_STATIC_ATTENTION_MAX_GROUPS; the
+ * key range is cut into at most FJ_STATIC_ATTENTION_MAX_ITEMS chunks (chunks grow with the batch).
+ *
+ * All pointers are device addresses of the backend's GPU except key_lengths (host array [lanes],
+ * tokens attended per lane, i.e. position + 1): q, out [lanes, q_heads, 128] and kpool, vpool
+ * [physical_pages, 16, kv_heads, 128] in `dtype` (FJ_BF16 or FJ_F16); tables
+ * [lanes, table_pages, 2] {page, generation}; generations [physical_pages]; status: two u32 words
+ * that receive {flag, lowest offending logical page} with the meaning of the fj_device_error
+ * fields: flag 2 = page entry refused, and that lane's output is zero. May be NULL. The work is enqueued on the backend's stream.
+ *
+ * The first call on a device also looks up the array's device address and raises the kernel's
+ * shared-memory limit; make that first call before starting any stream capture. All calls share
+ * the one array, which still holds the previous call's contents (the counters are cleared on
+ * every call): two calls whose GPU work overlaps - other streams, other threads, other backends
+ * on the same device - race on it. Calls on one backend are ordered by its stream and are safe. */
+#define FJ_STATIC_ATTENTION_MAX_LANES 64
+#define FJ_STATIC_ATTENTION_MAX_GROUPS 512
+#define FJ_STATIC_ATTENTION_MAX_ITEMS 1024
+int32_t fj_paged_decode_attention_static(fj_backend* be, const void* q, void* out, const void* kpool, const void* vpool,
+                                         const uint32_t* tables, const uint32_t* generations, const uint32_t* key_lengths,
+                                         uint32_t lanes, uint32_t table_pages, uint32_t physical_pages, uint32_t q_heads,
+                                         uint32_t kv_heads, uint32_t dtype, float scale, uint32_t* status);
+
 #ifdef __cplusplus
 }
 #endif
