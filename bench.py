@@ -354,9 +354,10 @@ def load_peaks():
 
 
 # DRAM traffic of the decode-attention kernel relative to its algorithmic bytes, from the ncu
-# capture summarised in profiles/attn_decode_mma_c2_decode.md (dram__bytes_read.sum +
-# dram__bytes_write.sum over the algorithmic bytes of the captured launch). None until captured.
-NCU_TRAFFIC_RATIO = None
+# capture summarised in profiles/attn_decode_mma_small_case_ncu.md: dram__bytes_read.sum +
+# dram__bytes_write.sum = 408.3 MB for a launch of 403.9 MB algorithmic bytes. The kernel reads
+# every page once, so traffic scales with the attended tokens of the launch.
+NCU_TRAFFIC_RATIO = 1.011
 
 
 def ncu_traffic_per_launch(algorithmic_bytes):
