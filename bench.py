@@ -283,7 +283,7 @@ def run_native(args):
     host_tokens = np.zeros(args.lanes, np.uint32)
     barrier(dist, be)
     h2d = d2h = 0
-    e2e_tokens = 0
+    e2e_tokens = e2e_kv_tokens = 0
     t0 = time.perf_counter()
     for _ in range(e2e_steps):
         starts, tokens = lanes.descriptors()
@@ -291,6 +291,7 @@ def run_native(args):
         ids = host_tokens[tokens > 0]
         out = model.step(ids, want_tokens=True, lanes=args.lanes)  # host -> device ids, device -> host greedy tokens (synchronises)
         host_tokens = out
+        e2e_kv_tokens += int((starts[tokens > 0] + 1).sum())
         h2d += starts.nbytes + tokens.nbytes + ids.nbytes
         d2h += out.nbytes
         e2e_tokens += lanes.advance()
@@ -318,7 +319,7 @@ def run_native(args):
                    "l2": "inputs larger than L2: each step streams the KV of every lane (tens of GB) and 1.19 GB of weights"},
         "clocks": clocks,
         "e2e": {"value": e2e_tok_sum / e2e_elapsed, "unit": "tok/s", "h2d_bytes_per_step": h2d / e2e_steps, "d2h_bytes_per_step": d2h / e2e_steps,
-                "ms_per_step": e2e_elapsed / e2e_steps * 1e3},
+                "ms_per_step": e2e_elapsed / e2e_steps * 1e3, "mean_kv_tokens_per_step": e2e_kv_tokens / e2e_steps},
         "gpu_launches": int(launches),
         "roofline": {"kernel": "attn_decode_mma_kernel (paged GQA decode attention, split-K)", "bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"],
                      "unit": "GB/s", "frac": (achieved / peaks["hbm_gbs"]) if achieved else None, "peak_source": peaks["source"],

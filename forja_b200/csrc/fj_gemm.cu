@@ -103,7 +103,10 @@ __global__ void __launch_bounds__(F32_TILE* F32_TILE) gemm_nt_f32_kernel(const f
 // 16-bit tensor-core GEMM (mma.sync), NT
 // ---------------------------------------------------------------------------------------------
 
-constexpr int BM = 128, BK = 64, GEMM_STAGES = 3, GEMM_THREADS = 256;
+constexpr int BM = 128, BK = 64, GEMM_THREADS = 256;
+// cp.async pipeline depth: decode-sized grids leave one CTA per SM, so the tile stream itself has
+// to keep enough bytes in flight (BN 64: 6 x 24 KB, BN 128: 4 x 32 KB).
+template <int BN> constexpr int kPipelineDepth = BN == 128 ? 4 : 6;
 
 __device__ inline void cp_async_16(unsigned smem_addr, const void* gmem, unsigned src_bytes) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(smem_addr), "l"(gmem), "r"(src_bytes) : "memory");
@@ -161,7 +164,7 @@ __global__ void __launch_bounds__(GEMM_THREADS) gemm_nt_mma_kernel(GemmParams p)
 
   auto issue = [&](unsigned it) {
     if (it < k_iters) {
-      const unsigned stage = smem_base + (it % GEMM_STAGES) * STAGE_BYTES;
+      const unsigned stage = smem_base + (it % kPipelineDepth<BN>) * STAGE_BYTES;
       const unsigned kk = k_begin + it * BK;
       // A tile: BM rows x 8 chunks; W tile: BN rows x 8 chunks (16 B = 8 elements each)
 #pragma unroll
@@ -185,13 +188,13 @@ __global__ void __launch_bounds__(GEMM_THREADS) gemm_nt_mma_kernel(GemmParams p)
   };
 
 #pragma unroll
-  for (int s = 0; s < GEMM_STAGES - 1; ++s) issue(s);
+  for (int s = 0; s < kPipelineDepth<BN> - 1; ++s) issue(s);
 
   for (unsigned it = 0; it < k_iters; ++it) {
-    cp_async_wait<GEMM_STAGES - 2>();
+    cp_async_wait<kPipelineDepth<BN> - 2>();
     __syncthreads();  // stage `it` has landed for every thread; stage it-1 is free for refill
-    issue(it + GEMM_STAGES - 1);
-    const unsigned stage = smem_base + (it % GEMM_STAGES) * STAGE_BYTES;
+    issue(it + kPipelineDepth<BN> - 1);
+    const unsigned stage = smem_base + (it % kPipelineDepth<BN>) * STAGE_BYTES;
 #pragma unroll
     for (int ks = 0; ks < BK / 16; ++ks) {
       unsigned af[MT][4];
@@ -325,14 +328,19 @@ struct SplitPlan { unsigned bn, splits, k_per_split, tiles; };
 
 SplitPlan plan_gemm(unsigned m, unsigned n, unsigned k, int sm_count) {
   SplitPlan s;
-  s.bn = (n >= 4096) ? 128 : 64;
-  unsigned tiles_m = (m + BM - 1) / BM, tiles_n = (n + s.bn - 1) / s.bn;
+  // Wide tiles only when they alone fill the GPU (lm_head); otherwise BN 64 gives twice the CTAs.
+  unsigned tiles_m = (m + BM - 1) / BM;
+  s.bn = (tiles_m * ((n + 127) / 128) >= 2u * static_cast<unsigned>(sm_count)) ? 128 : 64;
+  unsigned tiles_n = (n + s.bn - 1) / s.bn;
   s.tiles = tiles_m * tiles_n;
   unsigned k_iters = (k + BK - 1) / BK;
   unsigned splits = 1;
-  if (s.tiles < static_cast<unsigned>(sm_count)) {
-    splits = static_cast<unsigned>(sm_count) / s.tiles;
-    unsigned max_by_k = k_iters / 4;  // at least 4 k-iterations per split
+  // Split K only for grids that would leave most SMs idle: every split costs an f32 partial
+  // round trip and a serial reduction by the last CTA of the tile.
+  const unsigned want_ctas = static_cast<unsigned>(sm_count) / 2;
+  if (s.tiles < want_ctas) {
+    splits = (want_ctas + s.tiles - 1) / s.tiles;
+    unsigned max_by_k = k_iters / 8;  // at least 8 k-iterations per split
     if (splits > max_by_k) splits = max_by_k;
     if (splits > 16) splits = 16;
     if (splits < 1) splits = 1;
@@ -345,7 +353,7 @@ SplitPlan plan_gemm(unsigned m, unsigned n, unsigned k, int sm_count) {
 
 template <int BN, bool kBF16>
 void run_mma(Ctx& ctx, const GemmParams& p, unsigned tiles_m, unsigned tiles_n) {
-  constexpr int smem = GEMM_STAGES * (BM * BK * 2 + BN * BK * 2);
+  constexpr int smem = kPipelineDepth<BN> * (BM * BK * 2 + BN * BK * 2);
   static bool configured = false;
   if (!configured) {
     cudaFuncSetAttribute(gemm_nt_mma_kernel<BN, kBF16>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
