@@ -324,7 +324,8 @@ struct fj_submission {
   std::vector<uint32_t> ops;
   std::vector<uint32_t> kernels;
   std::vector<cudaEvent_t> marks;  // count + 1 events when profiled
-  fj::ErrorRecord* host_err = nullptr;  // pinned, count entries
+  fj::ErrorRecord* host_err = nullptr;  // pinned, count entries (recycled through the backend)
+  size_t host_err_capacity = 0;
   bool done = false;
   int32_t result = FJ_OK;
   fj_device_error error{};
@@ -555,7 +556,22 @@ int32_t exec_quant_matmul(Exec& x, const fj_dispatch& d) {
   const void *xp = x.input(xt), *pp = x.input(pk), *sp = x.input(d.inputs[2]), *bp = x.input(d.inputs[3]);
   void* out = x.output(d.outputs[0]);
   if (!xp || !pp || !sp || !bp || !out) return FJ_INVALID_INPUT;
-  fj::launch_quant_matmul(x.be->ctx, xp, xt.dtype, static_cast<const unsigned*>(pp), sp, bp, d.inputs[2].dtype, out, d.outputs[0].dtype, m, k, n, d.u0, d.u1);
+  void* workspace = nullptr;
+  size_t workspace_bytes = 0;
+  void* gemm_scratch = nullptr;
+  size_t gemm_scratch_bytes = 0;
+  if (m > 16 && xt.dtype != FJ_F32) {
+    // slab of dequantised weights for the tensor-core path (at most 64 MiB) + split-K scratch
+    workspace_bytes = std::min<size_t>(static_cast<size_t>(n) * k * 2, size_t(64) << 20);
+    workspace_bytes = std::max<size_t>(workspace_bytes, static_cast<size_t>(k) * 64 * 2);
+    workspace = x.temp(workspace_bytes);
+    if (!workspace) return FJ_ALLOCATION_FAILED;
+    const unsigned slab_cols = static_cast<unsigned>(std::min<size_t>(n, workspace_bytes / (static_cast<size_t>(k) * 2)));
+    size_t need = fj::gemm_scratch_bytes(m, slab_cols, k);
+    if (need <= (size_t(1) << 30) && ensure_gemm_scratch(x.be, need)) { gemm_scratch = x.be->gemm_scratch; gemm_scratch_bytes = x.be->gemm_scratch_bytes; }
+  }
+  fj::launch_quant_matmul(x.be->ctx, xp, xt.dtype, static_cast<const unsigned*>(pp), sp, bp, d.inputs[2].dtype, out, d.outputs[0].dtype, m, k, n, d.u0, d.u1, workspace,
+                          workspace_bytes, gemm_scratch, gemm_scratch_bytes);
   return FJ_OK;
 }
 
@@ -831,6 +847,7 @@ void fj_backend_destroy(fj_backend* be) {
   for (auto& kv : be->buffers) cudaFree(kv.second.ptr);
   for (auto& kv : be->freq_tables) cudaFree(kv.second);
   for (auto e : be->timers) cudaEventDestroy(e);
+  for (auto& block : be->pinned_pool) cudaFreeHost(block.first);
   if (be->gemm_scratch) cudaFree(be->gemm_scratch);
   if (be->attn_scratch) cudaFree(be->attn_scratch);
   cudaStreamDestroy(be->stream);
@@ -989,7 +1006,21 @@ int32_t fj_submit(fj_backend* be, const fj_dispatch* dispatches, uint32_t count,
   Exec x{be};
   const unsigned long long launches_before = be->ctx.launches;
   if (count) {
-    if (cudaMallocHost(reinterpret_cast<void**>(&sub->host_err), count * sizeof(fj::ErrorRecord)) != cudaSuccess) { cudaGetLastError(); sub->host_err = nullptr; }
+    {
+      std::lock_guard<std::mutex> pinned(be->pinned_mutex);
+      for (size_t i = 0; i < be->pinned_pool.size(); ++i) {
+        if (be->pinned_pool[i].second >= count) {
+          sub->host_err = static_cast<fj::ErrorRecord*>(be->pinned_pool[i].first);
+          sub->host_err_capacity = be->pinned_pool[i].second;
+          be->pinned_pool.erase(be->pinned_pool.begin() + i);
+          break;
+        }
+      }
+    }
+    if (!sub->host_err) {
+      sub->host_err_capacity = std::max<size_t>(count, 64);
+      if (cudaMallocHost(reinterpret_cast<void**>(&sub->host_err), sub->host_err_capacity * sizeof(fj::ErrorRecord)) != cudaSuccess) { cudaGetLastError(); sub->host_err = nullptr; }
+    }
     x.dev_err = static_cast<fj::ErrorRecord*>(x.temp(count * sizeof(fj::ErrorRecord)));
     if (!sub->host_err || !x.dev_err) { fj_sub_destroy(sub); return FJ_ALLOCATION_FAILED; }
     for (uint32_t i = 0; i < count; ++i) { sub->host_err[i].flag = 0; sub->host_err[i].value = 0xFFFFFFFFu; }
@@ -1148,7 +1179,11 @@ void fj_sub_destroy(fj_submission* sub) {
   if (sub->start) cudaEventDestroy(sub->start);
   if (sub->stop) cudaEventDestroy(sub->stop);
   for (auto e : sub->marks) cudaEventDestroy(e);
-  if (sub->host_err) cudaFreeHost(sub->host_err);
+  if (sub->host_err) {
+    std::lock_guard<std::mutex> pinned(sub->be->pinned_mutex);
+    if (sub->be->pinned_pool.size() < 64) sub->be->pinned_pool.emplace_back(sub->host_err, sub->host_err_capacity);
+    else cudaFreeHost(sub->host_err);
+  }
   delete sub;
 }
 

@@ -43,6 +43,9 @@ struct fj_backend {
   size_t gemm_scratch_bytes = 0;
   void* attn_scratch = nullptr;
   size_t attn_scratch_bytes = 0;
+  // recycled pinned blocks for the per-submission error records (pointer, capacity in records)
+  std::vector<std::pair<void*, size_t>> pinned_pool;
+  std::mutex pinned_mutex;
 };
 
 namespace fjb {

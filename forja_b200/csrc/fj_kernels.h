@@ -111,7 +111,8 @@ void launch_matmul_generic(Ctx& ctx, const View& a, const View& b, const View& c
 // y[m,n] = sum_k x[m,k] * (scale[n,k/g] * q[n,k] + bias[n,k/g]); packed u32 [N, K*bits/32], LSB first.
 void launch_quant_matmul(Ctx& ctx, const void* x, int x_dt, const unsigned* packed, const void* scales, const void* biases,
                          int p_dt, void* out, int out_dt, unsigned m, unsigned k, unsigned n, unsigned bits,
-                         unsigned group_size);
+                         unsigned group_size, void* workspace = nullptr, size_t workspace_bytes = 0, void* gemm_scratch = nullptr,
+                         size_t gemm_scratch_bytes = 0);
 // epilogue: 0 none; 1 silu(acc0) * acc1 (pair form); 2 acc0 + extra (weighted-sum form)
 void launch_gather_quant_matmul(Ctx& ctx, const void* x, int x_dt, const unsigned* packed, const void* scales,
                                 const void* biases, int p_dt, const unsigned* packed2, const void* scales2,

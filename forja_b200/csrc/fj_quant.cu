@@ -10,6 +10,8 @@
 // so the inner loop is one multiply-add per weight plus one running sum of x.
 #include "fj_kernels.h"
 
+#include <algorithm>
+
 namespace fj {
 
 namespace {
@@ -125,6 +127,449 @@ __global__ void __launch_bounds__(256) quant_matmul_kernel(QuantArgs a, void* ou
   }
 }
 
+// ---------------------------------------------------------------------------------------------
+// q4 decode projection on tensor cores (M <= 16 rows, 16-bit activations, group 64 or 128)
+// ---------------------------------------------------------------------------------------------
+// At HBM speed a B200 delivers ~13 T nibbles/s, more than its FP32 lanes can unpack and multiply
+// one by one, so the weights go through mma.sync m16n8k16 with the roles swapped: the 16 rows of
+// the A operand are 16 output columns of W, the 8 columns of the B operand are up to 8 activation
+// rows. Nibbles become exact bf16/f16 values by OR-ing them into the mantissa of 128.0 / 1024.0
+// (value = offset + q); the mma accumulates sum_k x (offset + q) in f32 per 64-k group and the
+// affine part is applied per group afterwards:
+//   y += s * acc + (b - offset * s) * sum_k x.
+// Inside a group the k order seen by the mma is permuted (lane t of a quad owns 16 consecutive k,
+// and a register pairs k = i with k = i + 4 so that one mask extracts two nibbles), which is
+// harmless because both operands use the same permutation. The per-group sum of x comes from a
+// second mma against an all-ones A operand. One warp owns 16 columns over
+// a slice of K; the 4 warps of a CTA split K and combine through shared memory. Per 64-k block a
+// lane issues two 8-byte weight loads, 4 mma per 8 activation rows and ~1 integer op per nibble.
+
+template <bool kBF16>
+__device__ inline void mma_q4(float (&d)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3, unsigned b0, unsigned b1) {
+  if (kBF16) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+  } else {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+  }
+}
+
+struct Q4MmaArgs {
+  const unsigned short* x; size_t x_row_stride;   // activations, 16-bit
+  const unsigned* packed; const unsigned short* scales; const unsigned short* biases;  // one matrix [n, k/8], [n, k/group]
+  void* out; int out_dt; size_t out_row_stride;
+  unsigned m, k, n, group_size;
+};
+
+constexpr int Q4_UNROLL = 4;  // 64-k blocks whose weight loads are in flight together per lane
+
+// NB = number of 8-row activation tiles (1: m <= 8, 2: m <= 16); WARPS split K inside the CTA.
+// A B200 needs ~5 MB in flight to cover DRAM latency at full bandwidth, about the size of one
+// decode projection, so every lane issues the loads of all its blocks (up to Q4_UNROLL at a
+// time, 16 bytes of weights each) before it touches the first one.
+template <bool kBF16, int NB, int WARPS>
+__global__ void __launch_bounds__(WARPS * 32, 768 / (WARPS * 32)) q4_mma_gemv_kernel(Q4MmaArgs a) {
+  __shared__ float partial[WARPS][16][8 * NB];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const unsigned g = lane >> 2, t = lane & 3;
+  const unsigned col0 = blockIdx.x * 16;
+  const unsigned blocks = a.k / 64, per_warp = (blocks + WARPS - 1) / WARPS;
+  const unsigned b_begin = min(blocks, warp * per_warp), b_end = min(blocks, b_begin + per_warp);
+  const unsigned words_per_row = a.k / 8, groups_per_row = a.k / a.group_size;
+  const unsigned group_shift = a.group_size == 64 ? 0 : 1;  // blocks per group: 1 or 2
+  const float offset = kBF16 ? 128.0f : 1024.0f;
+  // this lane's two weight columns (rows g and g + 8 of the A operand); out-of-range columns read column 0 and are dropped at the end
+  const unsigned ca = col0 + g < a.n ? col0 + g : 0, cb = col0 + g + 8 < a.n ? col0 + g + 8 : 0;
+  const unsigned* wa = a.packed + static_cast<size_t>(ca) * words_per_row + 2 * t;
+  const unsigned* wb = a.packed + static_cast<size_t>(cb) * words_per_row + 2 * t;
+  const unsigned short* sa = a.scales + static_cast<size_t>(ca) * groups_per_row;
+  const unsigned short* sb = a.scales + static_cast<size_t>(cb) * groups_per_row;
+  const unsigned short* ba = a.biases + static_cast<size_t>(ca) * groups_per_row;
+  const unsigned short* bb = a.biases + static_cast<size_t>(cb) * groups_per_row;
+  // activation rows supplied by this lane to the B operand: row g of each 8-row tile
+  const unsigned short* xr[NB];
+  bool xok[NB];
+#pragma unroll
+  for (int nb = 0; nb < NB; ++nb) { xok[nb] = g + 8 * nb < a.m; xr[nb] = a.x + static_cast<size_t>(xok[nb] ? g + 8 * nb : 0) * a.x_row_stride + 16 * t; }
+
+  float y[NB][4];
+#pragma unroll
+  for (int nb = 0; nb < NB; ++nb) y[nb][0] = y[nb][1] = y[nb][2] = y[nb][3] = 0.0f;
+
+  auto to_f = [](unsigned short h) { return kBF16 ? __bfloat162float(__ushort_as_bfloat16(h)) : __half2float(__ushort_as_half(h)); };
+
+  // scale/bias pairs of 4 consecutive groups come in one 8-byte load when the warp's block range is 4-aligned
+  const bool vec_params = group_shift == 0 && per_warp % 4 == 0 && groups_per_row % 4 == 0 && Q4_UNROLL == 4;
+  const unsigned ones = kBF16 ? 0x3F803F80u : 0x3C003C00u, magic = kBF16 ? 0x43004300u : 0x64006400u;
+
+  for (unsigned blk0 = b_begin; blk0 < b_end; blk0 += Q4_UNROLL) {
+    uint2 qa[Q4_UNROLL], qb[Q4_UNROLL];
+    unsigned short hs_a[Q4_UNROLL], hs_b[Q4_UNROLL], hb_a[Q4_UNROLL], hb_b[Q4_UNROLL];
+#pragma unroll
+    for (int u = 0; u < Q4_UNROLL; ++u) {
+      const unsigned blk = min(blk0 + u, b_end - 1);  // the tail re-reads the last block and is skipped below
+      qa[u] = __ldg(reinterpret_cast<const uint2*>(wa + blk * 8));
+      qb[u] = __ldg(reinterpret_cast<const uint2*>(wb + blk * 8));
+    }
+    if (vec_params) {
+      const uint2 v0 = __ldg(reinterpret_cast<const uint2*>(sa + blk0)), v1 = __ldg(reinterpret_cast<const uint2*>(sb + blk0));
+      const uint2 v2 = __ldg(reinterpret_cast<const uint2*>(ba + blk0)), v3 = __ldg(reinterpret_cast<const uint2*>(bb + blk0));
+      hs_a[0] = v0.x & 0xFFFFu; hs_a[1] = v0.x >> 16; hs_a[2] = v0.y & 0xFFFFu; hs_a[3] = v0.y >> 16;
+      hs_b[0] = v1.x & 0xFFFFu; hs_b[1] = v1.x >> 16; hs_b[2] = v1.y & 0xFFFFu; hs_b[3] = v1.y >> 16;
+      hb_a[0] = v2.x & 0xFFFFu; hb_a[1] = v2.x >> 16; hb_a[2] = v2.y & 0xFFFFu; hb_a[3] = v2.y >> 16;
+      hb_b[0] = v3.x & 0xFFFFu; hb_b[1] = v3.x >> 16; hb_b[2] = v3.y & 0xFFFFu; hb_b[3] = v3.y >> 16;
+    } else {
+#pragma unroll
+      for (int u = 0; u < Q4_UNROLL; ++u) {
+        const unsigned grp = min(blk0 + u, b_end - 1) >> group_shift;
+        hs_a[u] = __ldg(sa + grp); hs_b[u] = __ldg(sb + grp);
+        hb_a[u] = __ldg(ba + grp); hb_b[u] = __ldg(bb + grp);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < Q4_UNROLL; ++u) {
+      const unsigned blk = blk0 + u;
+      if (blk >= b_end) break;  // uniform across the warp
+      const float s_a = to_f(hs_a[u]), s_b = to_f(hs_b[u]);
+      const float o_a = to_f(hb_a[u]) - offset * s_a, o_b = to_f(hb_b[u]) - offset * s_b;
+      // A fragments: one mask per register yields nibbles i and i + 4 of a word as {offset + q_i, offset + q_(i+4)},
+      // so a register pairs k = i with k = i + 4; the activations below are paired the same way.
+      unsigned fa[2][4], fb[2][4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        fa[0][i] = ((qa[u].x >> (4 * i)) & 0x000F000Fu) | magic; fa[1][i] = ((qa[u].y >> (4 * i)) & 0x000F000Fu) | magic;
+        fb[0][i] = ((qb[u].x >> (4 * i)) & 0x000F000Fu) | magic; fb[1][i] = ((qb[u].y >> (4 * i)) & 0x000F000Fu) | magic;
+      }
+#pragma unroll
+      for (int nb = 0; nb < NB; ++nb) {
+        // 16 activations of row g for this lane's k slice: 32 bytes, re-paired as (x_i, x_(i+4)) per 8
+        uint4 x0 = make_uint4(0, 0, 0, 0), x1 = make_uint4(0, 0, 0, 0);
+        if (xok[nb]) {
+          x0 = *reinterpret_cast<const uint4*>(xr[nb] + blk * 64);
+          x1 = *reinterpret_cast<const uint4*>(xr[nb] + blk * 64 + 8);
+        }
+        const unsigned p0 = __byte_perm(x0.x, x0.z, 0x5410), p1 = __byte_perm(x0.x, x0.z, 0x7632);
+        const unsigned p2 = __byte_perm(x0.y, x0.w, 0x5410), p3 = __byte_perm(x0.y, x0.w, 0x7632);
+        const unsigned p4 = __byte_perm(x1.x, x1.z, 0x5410), p5 = __byte_perm(x1.x, x1.z, 0x7632);
+        const unsigned p6 = __byte_perm(x1.y, x1.w, 0x5410), p7 = __byte_perm(x1.y, x1.w, 0x7632);
+        float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f}, sum[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        mma_q4<kBF16>(acc, fa[0][0], fb[0][0], fa[0][1], fb[0][1], p0, p1);
+        mma_q4<kBF16>(acc, fa[0][2], fb[0][2], fa[0][3], fb[0][3], p2, p3);
+        mma_q4<kBF16>(acc, fa[1][0], fb[1][0], fa[1][1], fb[1][1], p4, p5);
+        mma_q4<kBF16>(acc, fa[1][2], fb[1][2], fa[1][3], fb[1][3], p6, p7);
+        // sum of the block's activations per row through the same pipe: A = all ones, so every
+        // accumulator row holds sum_k x[row 2t / 2t+1][k], already in this lane's output layout
+        mma_q4<kBF16>(sum, ones, ones, ones, ones, p0, p1);
+        mma_q4<kBF16>(sum, ones, ones, ones, ones, p2, p3);
+        mma_q4<kBF16>(sum, ones, ones, ones, ones, p4, p5);
+        mma_q4<kBF16>(sum, ones, ones, ones, ones, p6, p7);
+        y[nb][0] += s_a * acc[0] + o_a * sum[0];
+        y[nb][1] += s_a * acc[1] + o_a * sum[1];
+        y[nb][2] += s_b * acc[2] + o_b * sum[0];
+        y[nb][3] += s_b * acc[3] + o_b * sum[1];
+      }
+    }
+  }
+  // combine the K slices of the warps; layout [warp][column in tile][activation row]
+#pragma unroll
+  for (int nb = 0; nb < NB; ++nb) {
+    partial[warp][g][8 * nb + 2 * t] = y[nb][0];
+    partial[warp][g][8 * nb + 2 * t + 1] = y[nb][1];
+    partial[warp][g + 8][8 * nb + 2 * t] = y[nb][2];
+    partial[warp][g + 8][8 * nb + 2 * t + 1] = y[nb][3];
+  }
+  __syncthreads();
+  for (unsigned idx = threadIdx.x; idx < 16 * 8 * NB; idx += blockDim.x) {
+    const unsigned row = idx / 16, c = idx % 16;  // consecutive threads write consecutive columns
+    if (row < a.m && col0 + c < a.n) {
+      float v = 0.0f;
+#pragma unroll
+      for (int w = 0; w < WARPS; ++w) v += partial[w][c][row];
+      store_from_f32(a.out, a.out_dt, static_cast<size_t>(row) * a.out_row_stride + col0 + c, v);
+    }
+  }
+}
+
+bool q4_mma_supported(int x_dt, int p_dt, unsigned m, unsigned k, unsigned bits, unsigned group_size, const void* x, size_t x_row_stride,
+                      const void* packed) {
+  return bits == 4 && (x_dt == BF16 || x_dt == F16) && p_dt == x_dt && m >= 1 && m <= 16 && (group_size == 64 || group_size == 128) &&
+         k % 64 == 0 && k >= 64 && x_row_stride % 8 == 0 && reinterpret_cast<size_t>(x) % 16 == 0 && reinterpret_cast<size_t>(packed) % 8 == 0;
+}
+
+template <bool kBF16, int NB>
+void run_q4_mma_warps(Ctx& ctx, const Q4MmaArgs& a) {
+  const unsigned grid = (a.n + 15) / 16, blocks = a.k / 64;
+  if (blocks >= 64) q4_mma_gemv_kernel<kBF16, NB, 16><<<grid, 16 * 32, 0, ctx.stream>>>(a);
+  else if (blocks >= 32) q4_mma_gemv_kernel<kBF16, NB, 8><<<grid, 8 * 32, 0, ctx.stream>>>(a);
+  else q4_mma_gemv_kernel<kBF16, NB, 4><<<grid, 4 * 32, 0, ctx.stream>>>(a);
+  ctx.launches++;
+}
+
+void run_q4_mma(Ctx& ctx, const Q4MmaArgs& a, int x_dt) {
+  const bool bf = x_dt == BF16;
+  if (a.m <= 8) {
+    if (bf) run_q4_mma_warps<true, 1>(ctx, a); else run_q4_mma_warps<false, 1>(ctx, a);
+  } else {
+    if (bf) run_q4_mma_warps<true, 2>(ctx, a); else run_q4_mma_warps<false, 2>(ctx, a);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Streaming form of the q4 decode projection: persistent CTAs, one cp.async pipeline per warp
+// ---------------------------------------------------------------------------------------------
+// The register-prefetch kernel above keeps a CTA alive for one DRAM round trip only and spends
+// most of its instructions on address arithmetic and activation handling. Here:
+//  * the activations are permuted into mma fragment order once per CTA and kept in shared memory
+//    together with their per-block sums (K * 16 bytes per 8 rows), so the steady state touches
+//    them with two 16-byte shared loads per block;
+//  * every warp owns whole 16-column tiles (or a 1/ksplit slice of K when there are too few
+//    tiles to go round) and streams them in units of 256 k = 2 KB of nibbles + 256 B of scales
+//    and biases through its own ring of cp.async stages, so the steady state has no CTA barrier;
+//  * a unit's rows are 128 bytes apart in memory and 160 bytes apart in shared memory, which
+//    keeps the copies coalesced and the 8-byte fragment reads of 4 rows x 4 lanes conflict-free.
+constexpr int Q4W_WARPS = 8;
+constexpr int Q4W_ROW_STRIDE = 160;
+constexpr int Q4W_PARAM_OFFSET = 16 * Q4W_ROW_STRIDE;
+constexpr int Q4W_UNIT_BYTES = Q4W_PARAM_OFFSET + 256;  // scales [16][4] u16, biases [16][4] u16
+
+struct Q4WarpArgs {
+  Q4MmaArgs base;
+  unsigned tiles, ksplit, rounds;  // 16-column tiles; warps sharing a tile (1, 2, 4, 8); tile rounds per CTA
+};
+
+template <bool kBF16, int NB, int STAGES>
+__global__ void __launch_bounds__(Q4W_WARPS * 32, 1) q4_warp_stream_kernel(Q4WarpArgs args) {
+  extern __shared__ __align__(128) unsigned char q4_smem[];
+  const Q4MmaArgs& a = args.base;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const unsigned g = lane >> 2, t = lane & 3;
+  const unsigned blocks = a.k / 64, groups_per_row = a.k / a.group_size;
+  const bool g64 = a.group_size == 64;
+  const float offset = kBF16 ? 128.0f : 1024.0f;
+  const unsigned ones = kBF16 ? 0x3F803F80u : 0x3C003C00u, magic = kBF16 ? 0x43004300u : 0x64006400u;
+  auto to_f = [](unsigned h) { return kBF16 ? __uint_as_float(h << 16) : __half2float(__ushort_as_half(static_cast<unsigned short>(h))); };
+
+  uint4* xperm = reinterpret_cast<uint4*>(q4_smem);                                   // [blocks][NB][2][32]
+  float2* xsum = reinterpret_cast<float2*>(q4_smem + static_cast<size_t>(blocks) * NB * 1024);  // [blocks][NB][4]
+  unsigned char* ring = q4_smem + static_cast<size_t>(blocks) * NB * (1024 + 32) + warp * (STAGES * Q4W_UNIT_BYTES);
+  float* partial = reinterpret_cast<float*>(q4_smem + static_cast<size_t>(blocks) * NB * (1024 + 32) + Q4W_WARPS * STAGES * Q4W_UNIT_BYTES);  // [warp][16][8 NB]
+  const unsigned ring_base = static_cast<unsigned>(__cvta_generic_to_shared(ring));
+
+  // ---- activations: fragment order + block sums, once per CTA ----
+  for (unsigned b = warp; b < blocks; b += Q4W_WARPS) {
+#pragma unroll
+    for (int nb = 0; nb < NB; ++nb) {
+      uint4 x0 = make_uint4(0, 0, 0, 0), x1 = make_uint4(0, 0, 0, 0);
+      if (g + 8 * nb < a.m) {
+        const unsigned short* xr = a.x + static_cast<size_t>(g + 8 * nb) * a.x_row_stride + b * 64 + 16 * t;
+        x0 = *reinterpret_cast<const uint4*>(xr);
+        x1 = *reinterpret_cast<const uint4*>(xr + 8);
+      }
+      // a register pairs k = i with k = i + 4 (see the nibble masks below)
+      const uint4 pa = make_uint4(__byte_perm(x0.x, x0.z, 0x5410), __byte_perm(x0.x, x0.z, 0x7632), __byte_perm(x0.y, x0.w, 0x5410), __byte_perm(x0.y, x0.w, 0x7632));
+      const uint4 pb = make_uint4(__byte_perm(x1.x, x1.z, 0x5410), __byte_perm(x1.x, x1.z, 0x7632), __byte_perm(x1.y, x1.w, 0x5410), __byte_perm(x1.y, x1.w, 0x7632));
+      float s4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+      mma_q4<kBF16>(s4, ones, ones, ones, ones, pa.x, pa.y);
+      mma_q4<kBF16>(s4, ones, ones, ones, ones, pa.z, pa.w);
+      mma_q4<kBF16>(s4, ones, ones, ones, ones, pb.x, pb.y);
+      mma_q4<kBF16>(s4, ones, ones, ones, ones, pb.z, pb.w);
+      xperm[((b * NB + nb) * 2 + 0) * 32 + lane] = pa;
+      xperm[((b * NB + nb) * 2 + 1) * 32 + lane] = pb;
+      if (g == 0) xsum[(b * NB + nb) * 4 + t] = make_float2(s4[0], s4[1]);  // rows 2t, 2t+1 of this 8-row tile
+    }
+  }
+  __syncthreads();
+
+  const unsigned ksplit = args.ksplit, group = warp / ksplit, ks = warp % ksplit, tile_groups = Q4W_WARPS / ksplit;
+  const unsigned upt = (a.k / 256) / ksplit;  // units of this warp per tile
+  const unsigned items = args.rounds * upt;
+  const unsigned char* wbase = reinterpret_cast<const unsigned char*>(a.packed);
+  const size_t row_bytes = a.k / 2;
+  const unsigned copy_row = lane >> 3, copy_col = (lane & 7) * 16;
+  const unsigned param_which = lane >> 4, param_col = lane & 15;
+
+  auto tile_of = [&](unsigned q) { return ((q / upt) * tile_groups + group) * gridDim.x + blockIdx.x; };
+
+  auto issue = [&](unsigned q) {
+    if (q < items) {
+      const unsigned tile = tile_of(q);
+      if (tile < args.tiles) {
+        const unsigned k0 = (ks * upt + q % upt) * 256;
+        const unsigned stage = ring_base + (q % STAGES) * Q4W_UNIT_BYTES;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const unsigned r = copy_row + 4 * i, col = min(tile * 16 + r, a.n - 1);
+          const unsigned char* src = wbase + col * row_bytes + k0 / 2 + copy_col;
+          asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(stage + r * Q4W_ROW_STRIDE + copy_col), "l"(src) : "memory");
+        }
+        const unsigned col = min(tile * 16 + param_col, a.n - 1);
+        const unsigned short* src = (param_which ? a.biases : a.scales) + static_cast<size_t>(col) * groups_per_row + k0 / a.group_size;
+        const unsigned dst = stage + Q4W_PARAM_OFFSET + param_which * 128 + param_col * 8;
+        if (g64) asm volatile("cp.async.ca.shared.global [%0], [%1], 8;\n" ::"r"(dst), "l"(src) : "memory");
+        else asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"(dst), "l"(src) : "memory");
+      }
+    }
+    asm volatile("cp.async.commit_group;\n" ::: "memory");
+  };
+
+  for (unsigned q = 0; q + 1 < STAGES; ++q) issue(q);
+
+  float y[NB][4];
+  for (unsigned q = 0; q < items; ++q) {
+    asm volatile("cp.async.wait_group %0;\n" ::"n"(STAGES - 2) : "memory");
+    __syncwarp();  // unit q is visible to the whole warp, and the warp is done with unit q - 1
+    issue(q + STAGES - 1);
+    const unsigned tile = tile_of(q), u = q % upt;
+    const bool live = tile < args.tiles;
+    if (u == 0) {
+#pragma unroll
+      for (int nb = 0; nb < NB; ++nb) y[nb][0] = y[nb][1] = y[nb][2] = y[nb][3] = 0.0f;
+    }
+    if (live) {
+      const unsigned char* stage = ring + (q % STAGES) * Q4W_UNIT_BYTES;
+      const uint2 sa = *reinterpret_cast<const uint2*>(stage + Q4W_PARAM_OFFSET + g * 8);
+      const uint2 sb = *reinterpret_cast<const uint2*>(stage + Q4W_PARAM_OFFSET + (g + 8) * 8);
+      const uint2 ba = *reinterpret_cast<const uint2*>(stage + Q4W_PARAM_OFFSET + 128 + g * 8);
+      const uint2 bb = *reinterpret_cast<const uint2*>(stage + Q4W_PARAM_OFFSET + 128 + (g + 8) * 8);
+      const unsigned block0 = (ks * upt + u) * 4;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const uint2 qa = *reinterpret_cast<const uint2*>(stage + g * Q4W_ROW_STRIDE + j * 32 + t * 8);
+        const uint2 qb = *reinterpret_cast<const uint2*>(stage + (g + 8) * Q4W_ROW_STRIDE + j * 32 + t * 8);
+        const int slot = g64 ? j : j >> 1;  // parameter slot of this block inside the unit
+        auto pick = [&](const uint2& v) { const unsigned w = slot & 2 ? v.y : v.x; return slot & 1 ? w >> 16 : w & 0xFFFFu; };
+        const float s_a = to_f(pick(sa)), s_b = to_f(pick(sb));
+        const float o_a = to_f(pick(ba)) - offset * s_a, o_b = to_f(pick(bb)) - offset * s_b;
+        unsigned fa[2][4], fb[2][4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          fa[0][i] = ((qa.x >> (4 * i)) & 0x000F000Fu) | magic; fa[1][i] = ((qa.y >> (4 * i)) & 0x000F000Fu) | magic;
+          fb[0][i] = ((qb.x >> (4 * i)) & 0x000F000Fu) | magic; fb[1][i] = ((qb.y >> (4 * i)) & 0x000F000Fu) | magic;
+        }
+#pragma unroll
+        for (int nb = 0; nb < NB; ++nb) {
+          const uint4 pa = xperm[(((block0 + j) * NB + nb) * 2 + 0) * 32 + lane];
+          const uint4 pb = xperm[(((block0 + j) * NB + nb) * 2 + 1) * 32 + lane];
+          const float2 sum = xsum[((block0 + j) * NB + nb) * 4 + t];
+          float acc0[4] = {0.0f, 0.0f, 0.0f, 0.0f}, acc1[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+          mma_q4<kBF16>(acc0, fa[0][0], fb[0][0], fa[0][1], fb[0][1], pa.x, pa.y);
+          mma_q4<kBF16>(acc1, fa[0][2], fb[0][2], fa[0][3], fb[0][3], pa.z, pa.w);
+          mma_q4<kBF16>(acc0, fa[1][0], fb[1][0], fa[1][1], fb[1][1], pb.x, pb.y);
+          mma_q4<kBF16>(acc1, fa[1][2], fb[1][2], fa[1][3], fb[1][3], pb.z, pb.w);
+          y[nb][0] += s_a * (acc0[0] + acc1[0]) + o_a * sum.x;
+          y[nb][1] += s_a * (acc0[1] + acc1[1]) + o_a * sum.y;
+          y[nb][2] += s_b * (acc0[2] + acc1[2]) + o_b * sum.x;
+          y[nb][3] += s_b * (acc0[3] + acc1[3]) + o_b * sum.y;
+        }
+      }
+    }
+    if (u + 1 == upt) {
+      if (ksplit == 1) {
+        if (live) {
+#pragma unroll
+          for (int nb = 0; nb < NB; ++nb) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const unsigned row = 8 * nb + 2 * t + (i & 1), col = tile * 16 + g + (i >> 1) * 8;
+              if (row < a.m && col < a.n) store_from_f32(a.out, a.out_dt, static_cast<size_t>(row) * a.out_row_stride + col, y[nb][i]);
+            }
+          }
+        }
+      } else {
+        // the warps sharing a tile combine their K slices; every warp of the CTA reaches both barriers
+        float* mine = partial + warp * (16 * 8 * NB);
+#pragma unroll
+        for (int nb = 0; nb < NB; ++nb) {
+          mine[g * (8 * NB) + 8 * nb + 2 * t] = y[nb][0];
+          mine[g * (8 * NB) + 8 * nb + 2 * t + 1] = y[nb][1];
+          mine[(g + 8) * (8 * NB) + 8 * nb + 2 * t] = y[nb][2];
+          mine[(g + 8) * (8 * NB) + 8 * nb + 2 * t + 1] = y[nb][3];
+        }
+        __syncthreads();
+        if (live) {
+          const float* first = partial + (group * ksplit) * (16 * 8 * NB);
+          for (unsigned idx = ks * 32 + lane; idx < 16 * 8 * NB; idx += ksplit * 32) {
+            const unsigned row = idx / 16, c = idx % 16;
+            if (row < a.m && tile * 16 + c < a.n) {
+              float v = 0.0f;
+              for (unsigned w = 0; w < ksplit; ++w) v += first[w * (16 * 8 * NB) + c * (8 * NB) + row];
+              store_from_f32(a.out, a.out_dt, static_cast<size_t>(row) * a.out_row_stride + tile * 16 + c, v);
+            }
+          }
+        }
+        __syncthreads();
+      }
+    }
+  }
+  asm volatile("cp.async.wait_group 0;\n" ::: "memory");
+}
+
+template <bool kBF16, int NB, int STAGES>
+bool launch_q4_warp_stream(Ctx& ctx, const Q4WarpArgs& args, unsigned grid, size_t smem) {
+  static bool configured[64] = {};
+  int device = 0;
+  cudaGetDevice(&device);
+  if (device < 0 || device >= 64) return false;
+  if (!configured[device]) {
+    if (cudaFuncSetAttribute(q4_warp_stream_kernel<kBF16, NB, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) != cudaSuccess) { cudaGetLastError(); return false; }
+    configured[device] = true;
+  }
+  q4_warp_stream_kernel<kBF16, NB, STAGES><<<grid, Q4W_WARPS * 32, smem, ctx.stream>>>(args);
+  ctx.launches++;
+  return true;
+}
+
+// Tries the streaming kernel; false when shape or alignment rule it out (the caller falls back).
+bool run_q4_stream(Ctx& ctx, const Q4MmaArgs& a, int x_dt) {
+  const unsigned param_align = a.group_size == 64 ? 8 : 4;
+  if (a.k % 256 != 0 || reinterpret_cast<size_t>(a.packed) % 16 != 0 || reinterpret_cast<size_t>(a.scales) % param_align != 0 ||
+      reinterpret_cast<size_t>(a.biases) % param_align != 0) return false;
+  const unsigned nb = a.m <= 8 ? 1 : 2, blocks = a.k / 64, units = a.k / 256;
+  const unsigned sms = static_cast<unsigned>(ctx.sm_count > 0 ? ctx.sm_count : 148);
+  Q4WarpArgs args{a, (a.n + 15) / 16, 1, 1};
+  const unsigned grid = std::min(args.tiles, sms);
+  // too few tiles for every warp to own one: let 2, 4 or 8 warps share a tile along K
+  const unsigned per_cta = (args.tiles + grid - 1) / grid;
+  unsigned tile_groups = 1;
+  while (tile_groups < Q4W_WARPS && tile_groups < per_cta) tile_groups *= 2;
+  args.ksplit = Q4W_WARPS / tile_groups;
+  while (args.ksplit > 1 && units % args.ksplit != 0) args.ksplit /= 2;
+  tile_groups = Q4W_WARPS / args.ksplit;
+  args.rounds = (args.tiles + tile_groups * grid - 1) / (tile_groups * grid);
+  const size_t fixed = static_cast<size_t>(blocks) * nb * (1024 + 32) + (args.ksplit > 1 ? Q4W_WARPS * 16 * 8 * nb * sizeof(float) : 0);
+  const size_t limit = 227 * 1024;
+  const bool bf = x_dt == BF16;
+  if (fixed + Q4W_WARPS * 6 * Q4W_UNIT_BYTES <= limit) {
+    const size_t smem = fixed + Q4W_WARPS * 6 * Q4W_UNIT_BYTES;
+    if (nb == 1) return bf ? launch_q4_warp_stream<true, 1, 6>(ctx, args, grid, smem) : launch_q4_warp_stream<false, 1, 6>(ctx, args, grid, smem);
+    return bf ? launch_q4_warp_stream<true, 2, 6>(ctx, args, grid, smem) : launch_q4_warp_stream<false, 2, 6>(ctx, args, grid, smem);
+  }
+  if (fixed + Q4W_WARPS * 3 * Q4W_UNIT_BYTES <= limit) {
+    const size_t smem = fixed + Q4W_WARPS * 3 * Q4W_UNIT_BYTES;
+    if (nb == 1) return bf ? launch_q4_warp_stream<true, 1, 3>(ctx, args, grid, smem) : launch_q4_warp_stream<false, 1, 3>(ctx, args, grid, smem);
+    return bf ? launch_q4_warp_stream<true, 2, 3>(ctx, args, grid, smem) : launch_q4_warp_stream<false, 2, 3>(ctx, args, grid, smem);
+  }
+  return false;
+}
+
+
+// Dequantises `cols` weight rows (columns of the projection) starting at absolute row `row0` of
+// the scale/bias tables into a dense [cols, k] matrix of dtype out_dt; one thread per packed word.
+__global__ void dequant_rows_kernel(const unsigned* __restrict__ packed, const void* scales, const void* biases, int p_dt, void* out, int out_dt,
+                                    unsigned cols, unsigned k, unsigned bits, unsigned group_size, unsigned row0) {
+  const unsigned vpw = 32 / bits, mask = (1u << bits) - 1, words_per_row = k / vpw, groups = k / group_size;
+  const size_t total = static_cast<size_t>(cols) * words_per_row;
+  for (size_t idx = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; idx < total; idx += static_cast<size_t>(gridDim.x) * blockDim.x) {
+    const unsigned row = static_cast<unsigned>(idx / words_per_row), wi = static_cast<unsigned>(idx % words_per_row);
+    const unsigned word = packed[idx];
+    const size_t g = static_cast<size_t>(row0 + row) * groups + (wi * vpw) / group_size;
+    const float s = load_as_f32(scales, p_dt, g), b = load_as_f32(biases, p_dt, g);
+    for (unsigned i = 0; i < vpw; ++i)
+      store_from_f32(out, out_dt, static_cast<size_t>(row) * k + wi * vpw + i, __fadd_rn(__fmul_rn(s, static_cast<float>((word >> (i * bits)) & mask)), b));
+  }
+}
+
 __device__ inline float sigmoid_ref(float v) { return 1.0f / (1.0f + expf(-v)); }
 
 // Gathered projection: grid.y = rows * routes; each route uses the expert named by indices.
@@ -200,8 +645,31 @@ __global__ void __launch_bounds__(256) gather_weighted_kernel(QuantArgs a, const
 
 void launch_quant_matmul(Ctx& ctx, const void* x, int x_dt, const unsigned* packed, const void* scales, const void* biases,
                          int p_dt, void* out, int out_dt, unsigned m, unsigned k, unsigned n, unsigned bits,
-                         unsigned group_size) {
+                         unsigned group_size, void* workspace, size_t workspace_bytes, void* gemm_scratch, size_t gemm_scratch_bytes) {
   if (m == 0 || n == 0) return;
+  if (q4_mma_supported(x_dt, p_dt, m, k, bits, group_size, x, k, packed)) {
+    Q4MmaArgs a{static_cast<const unsigned short*>(x), k, packed, static_cast<const unsigned short*>(scales), static_cast<const unsigned short*>(biases),
+                out, out_dt, n, m, k, n, group_size};
+    if (!run_q4_stream(ctx, a, x_dt)) run_q4_mma(ctx, a, x_dt);
+    return;
+  }
+  // More than 16 rows of 16-bit activations: dequantise a slab of columns into the workspace in
+  // the activation dtype and run the dense tensor-core GEMM on it (the weights are rounded to
+  // 16 bits once, which stays inside the quantised tolerance).
+  const size_t esz = 2;
+  if (m > 16 && (x_dt == BF16 || x_dt == F16) && out_dt == x_dt && workspace != nullptr && k % 8 == 0 && workspace_bytes >= static_cast<size_t>(k) * 64 * esz) {
+    unsigned slab = static_cast<unsigned>(std::min<size_t>(n, workspace_bytes / (static_cast<size_t>(k) * esz)));
+    if (slab < n) slab = slab / 64 * 64;
+    for (unsigned n0 = 0; n0 < n; n0 += slab) {
+      const unsigned cols = std::min(slab, n - n0);
+      const size_t total = static_cast<size_t>(cols) * k / 8;
+      dequant_rows_kernel<<<static_cast<unsigned>(std::min<size_t>((total + 255) / 256, 65535u * 8)), 256, 0, ctx.stream>>>(
+          packed + static_cast<size_t>(n0) * (k * bits / 32), scales, biases, p_dt, workspace, x_dt, cols, k, bits, group_size, n0);
+      ctx.launches++;
+      launch_gemm_nt(ctx, x, x_dt, k, workspace, x_dt, k, static_cast<char*>(out) + static_cast<size_t>(n0) * esz, out_dt, n, m, cols, k, gemm_scratch, gemm_scratch_bytes);
+    }
+    return;
+  }
   QuantArgs a{x, x_dt, k, packed, scales, biases, p_dt, k, n, bits, group_size};
   unsigned row_groups = (m + QM - 1) / QM;
   dim3 grid((n + 7) / 8, min(row_groups, 65535u));

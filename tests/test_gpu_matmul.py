@@ -105,9 +105,9 @@ def test_quant_matmul_known_answer_in_mlx_order(bits, p_dt, rows):
     assert np.all(np.abs(got - expected) <= 1e-5 * np.maximum(1.0, np.abs(expected)))
 
 
-@pytest.mark.parametrize("x_dt", [fb.BF16, fb.F32])
+@pytest.mark.parametrize("x_dt", [fb.BF16, fb.F16, fb.F32])
 @pytest.mark.parametrize("bits,group", [(4, 64), (8, 64), (4, 32), (4, 128)])
-@pytest.mark.parametrize("m,k,n", [(1, 2048, 768), (8, 4096, 512), (7, 768, 2048), (33, 2048, 130), (64, 2048, 384)])
+@pytest.mark.parametrize("m,k,n", [(1, 2048, 768), (8, 4096, 512), (7, 768, 2048), (33, 2048, 130), (64, 2048, 384), (12, 4096, 264), (16, 1024, 6144), (300, 1024, 2048)])
 def test_quant_matmul_matches_oracle(x_dt, bits, group, m, k, n):
     rng = np.random.default_rng(m + k + n + bits + group)
     be = backend()
