@@ -7,6 +7,7 @@ fallback: every compute entry point needs the compiled library and a CUDA device
 """
 from .backend import (BF16, F16, F32, I32, U32, BackendError, CommandList, CudaBackend, DenseModel, KvPool, Layout, Op,
                       Submission, Tensor)
+from .scheduler import SchedulerPolicy, chunk_merged_work, chunk_work, prefill_plan, reservations_fit
 
 __all__ = ["BF16", "F16", "F32", "I32", "U32", "BackendError", "CommandList", "CudaBackend", "DenseModel", "KvPool", "Layout",
-           "Op", "Submission", "Tensor"]
+           "Op", "Submission", "Tensor", "SchedulerPolicy", "chunk_work", "chunk_merged_work", "prefill_plan", "reservations_fit"]

@@ -48,6 +48,8 @@ class FjDenseLayerWeights(C.Structure):
     _fields_ = [(n, C.c_uint64) for n in ("input_norm", "wq", "wk", "wv", "q_norm", "k_norm", "wo", "post_norm", "w_gate", "w_up", "w_down")]
 
 
+SCHED_RESERVE_FN = C.CFUNCTYPE(C.c_int32, C.c_void_p, C.c_uint64, C.c_uint64)
+
 # Every symbol include/forja_cuda.h declares; the loader test checks that the library exports them all.
 EXPORTS = [
     "fj_backend_create", "fj_backend_destroy", "fj_device_info", "fj_set_memory_limit", "fj_memory_usage", "fj_alloc",
@@ -58,7 +60,10 @@ EXPORTS = [
     "fj_kvpool_read_table", "fj_kvpool_read_generations", "fj_kvpool_read_free", "fj_kvpool_tables_buffer",
     "fj_kvpool_generations_buffer", "fj_pack_step", "fj_dense_model_create", "fj_dense_model_destroy", "fj_dense_step",
     "fj_dense_step_stats", "fj_dense_fill_kv", "fj_dense_profile_attention", "fj_dense_attention_time",
-    "fj_paged_decode_attention_static",
+    "fj_paged_decode_attention_static", "fj_sched_create", "fj_sched_destroy", "fj_sched_set_prompt_chunk_multiple", "fj_sched_enqueue",
+    "fj_sched_reconcile_active", "fj_sched_complete", "fj_sched_retry_admission", "fj_sched_admit", "fj_sched_admit_pages",
+    "fj_sched_decode_bucket", "fj_sched_ready_prompt", "fj_sched_prompt_batch", "fj_sched_waiting", "fj_sched_active",
+    "fj_prompt_chunk_work", "fj_prompt_chunk_merged_work", "fj_reservations_fit", "fj_prefill_plan",
 ]
 
 _lib = None
@@ -115,5 +120,21 @@ def load():
         fn = getattr(lib, name)
         fn.argtypes = types
         fn.restype = C.c_int32
+    # host scheduler: (argtypes, restype)
+    sched = {
+        "fj_sched_create": ([P, U32, U64, U64, U32, U32, P], I32), "fj_sched_destroy": ([P], None),
+        "fj_sched_set_prompt_chunk_multiple": ([P, U32], None), "fj_sched_enqueue": ([P, U64, U64], None),
+        "fj_sched_reconcile_active": ([P, U64], None), "fj_sched_complete": ([P, U64], None),
+        "fj_sched_retry_admission": ([P, U64, U64], None), "fj_sched_admit": ([P, SCHED_RESERVE_FN, P, P, U64], U64),
+        "fj_sched_admit_pages": ([P, U32, P, P, U64], U64), "fj_sched_decode_bucket": ([P, P, U64], C.c_int64),
+        "fj_sched_ready_prompt": ([P, U64, U32], None), "fj_sched_prompt_batch": ([P, I32, P, P, U64], U64),
+        "fj_sched_waiting": ([P], U64), "fj_sched_active": ([P], U64),
+        "fj_prompt_chunk_work": ([U32, U32, U32], U32), "fj_prompt_chunk_merged_work": ([U32, U32, U32], U32),
+        "fj_reservations_fit": ([U32, U32, P, U64], I32), "fj_prefill_plan": ([U32, U32, U32, P, U64], U64),
+    }
+    for name, (types, restype) in sched.items():
+        fn = getattr(lib, name)
+        fn.argtypes = types
+        fn.restype = restype
     _lib = lib
     return lib

@@ -12,14 +12,14 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 INCLUDE = os.path.join(os.path.dirname(HERE), "include")
 OUTPUT = os.path.join(HERE, "libforja_cuda.so")
-SOURCES = ["fj_backend.cu", "fj_model.cu", "fj_elementwise.cu", "fj_paged.cu", "fj_gemm.cu", "fj_quant.cu", "fj_pack.cu"]
+SOURCES = ["fj_backend.cu", "fj_model.cu", "fj_elementwise.cu", "fj_paged.cu", "fj_gemm.cu", "fj_quant.cu", "fj_pack.cu", "fj_sched.cpp"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-Xcompiler", "-fPIC",
               "--expt-relaxed-constexpr", "-I", INCLUDE, "-I", CSRC]
 
 
 def _deps():
     files = [os.path.join(CSRC, f) for f in os.listdir(CSRC)] + [os.path.join(INCLUDE, "forja_cuda.h")]
-    return [f for f in files if f.endswith((".cu", ".cuh", ".h"))]
+    return [f for f in files if f.endswith((".cu", ".cuh", ".h", ".cpp"))]
 
 
 def needs_build() -> bool:
@@ -30,7 +30,7 @@ def needs_build() -> bool:
 
 
 def _compile(src: str, verbose: bool) -> str:
-    obj = os.path.join(CSRC, src.replace(".cu", ".o"))
+    obj = os.path.join(CSRC, os.path.splitext(src)[0] + ".o")
     deps_newer = not os.path.exists(obj) or any(os.path.getmtime(f) > os.path.getmtime(obj) for f in _deps() if f.endswith((".cuh", ".h")) or f.endswith(src))
     if deps_newer:
         cmd = ["nvcc", *NVCC_FLAGS, "-c", os.path.join(CSRC, src), "-o", obj]
@@ -49,7 +49,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
         return OUTPUT
     if force:
         for s in SOURCES:
-            obj = os.path.join(CSRC, s.replace(".cu", ".o"))
+            obj = os.path.join(CSRC, os.path.splitext(s)[0] + ".o")
             if os.path.exists(obj):
                 os.remove(obj)
     with ThreadPoolExecutor(max_workers=8) as pool:

@@ -316,48 +316,106 @@ void run_q4_mma(Ctx& ctx, const Q4MmaArgs& a, int x_dt) {
 }
 
 // ---------------------------------------------------------------------------------------------
-// Streaming form of the q4 decode projection: persistent CTAs, one cp.async pipeline per warp
+// Streaming q4 decode projection: persistent CTAs, per-warp cp.async rings, integer tensor cores
 // ---------------------------------------------------------------------------------------------
-// The register-prefetch kernel above keeps a CTA alive for one DRAM round trip only and spends
-// most of its instructions on address arithmetic and activation handling. Here:
-//  * the activations are permuted into mma fragment order once per CTA and kept in shared memory
-//    together with their per-block sums (K * 16 bytes per 8 rows), so the steady state touches
-//    them with two 16-byte shared loads per block;
-//  * every warp owns whole 16-column tiles (or a 1/ksplit slice of K when there are too few
-//    tiles to go round) and streams them in units of 256 k = 2 KB of nibbles + 256 B of scales
-//    and biases through its own ring of cp.async stages, so the steady state has no CTA barrier;
+// Unpacking nibbles into 16-bit floats costs 7 integer instructions per packed word, and the
+// integer pipe (16 lanes per scheduler) then caps the kernel near a third of HBM bandwidth. Here
+// the nibbles stay integers: `w & 0x0F0F0F0F` and `(w >> 4) & 0x0F0F0F0F` are already the u8 A
+// operands of mma.sync m16n8k32 (3 instructions per word). The activations are turned, once per
+// CTA, into block fixed point: per (row, 64-k block) a power-of-two step S = 2^(E-11) with E the
+// exponent of the block's largest |x|, and x / S rounded to a 13-bit integer that is split into a
+// signed high byte and an unsigned low byte. A bf16 activation has 8 significant bits, so every
+// element within 2^4 of the block maximum is represented exactly and the rest to within S/2,
+// i.e. 2^-12 of the block maximum. The integer dot products are exact and, with 64 terms of at
+// most 15 * 4095, stay below 2^22; the low accumulator starts at 0x4B400000 so that the bit
+// pattern of 256 * hi + lo read as f32 is 12582912 + sum, which makes the int -> float
+// conversion a single subtraction. Per block:
+//   y += (s * S) * (256 * hi + lo) + b * sum_k x        (sum_k x is taken from the original values)
+// Layout and pipeline:
+//  * activations (fixed-point bytes in fragment order, block sums and steps) live in shared
+//    memory for the whole kernel: K * 17 bytes per 8 rows;
+//  * every warp owns whole 16-column tiles (or a 1/ksplit slice of K when there are too few tiles
+//    to go round) and streams them in units of 256 k = 2 KB of nibbles + 256 B of scales and
+//    biases through its own ring of cp.async stages, so the steady state has no CTA barrier;
 //  * a unit's rows are 128 bytes apart in memory and 160 bytes apart in shared memory, which
 //    keeps the copies coalesced and the 8-byte fragment reads of 4 rows x 4 lanes conflict-free.
-constexpr int Q4W_WARPS = 8;
 constexpr int Q4W_ROW_STRIDE = 160;
 constexpr int Q4W_PARAM_OFFSET = 16 * Q4W_ROW_STRIDE;
 constexpr int Q4W_UNIT_BYTES = Q4W_PARAM_OFFSET + 256;  // scales [16][4] u16, biases [16][4] u16
+constexpr int Q4W_X_BYTES = 1024 + 64;                  // per (64-k block, 8-row tile): fragments + {sum, step} per row
 
 struct Q4WarpArgs {
   Q4MmaArgs base;
-  unsigned tiles, ksplit, rounds;  // 16-column tiles; warps sharing a tile (1, 2, 4, 8); tile rounds per CTA
+  unsigned tiles, ksplit, rounds;  // 16-column tiles; warps sharing a tile (power of two); tile rounds per CTA
 };
 
-template <bool kBF16, int NB, int STAGES>
-__global__ void __launch_bounds__(Q4W_WARPS * 32, 1) q4_warp_stream_kernel(Q4WarpArgs args) {
+template <bool kSignedB>
+__device__ inline void mma_u8(int (&d)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3, unsigned b0, unsigned b1) {
+  if (kSignedB) {
+    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+  } else {
+    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.u8.u8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+  }
+}
+
+// bf16 activations and parameters only (f16 callers use the mantissa-offset kernel above).
+template <bool kG64, int NB, int STAGES, int WARPS>
+__global__ void __launch_bounds__(WARPS * 32, 1) q4_i8_stream_kernel(Q4WarpArgs args) {
   extern __shared__ __align__(128) unsigned char q4_smem[];
   const Q4MmaArgs& a = args.base;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const unsigned g = lane >> 2, t = lane & 3;
   const unsigned blocks = a.k / 64, groups_per_row = a.k / a.group_size;
-  const bool g64 = a.group_size == 64;
-  const float offset = kBF16 ? 128.0f : 1024.0f;
-  const unsigned ones = kBF16 ? 0x3F803F80u : 0x3C003C00u, magic = kBF16 ? 0x43004300u : 0x64006400u;
-  auto to_f = [](unsigned h) { return kBF16 ? __uint_as_float(h << 16) : __half2float(__ushort_as_half(static_cast<unsigned short>(h))); };
+  constexpr bool g64 = kG64;
+  auto half_to_f = [](unsigned h) { return __uint_as_float(h << 16); };
 
-  uint4* xperm = reinterpret_cast<uint4*>(q4_smem);                                   // [blocks][NB][2][32]
-  float2* xsum = reinterpret_cast<float2*>(q4_smem + static_cast<size_t>(blocks) * NB * 1024);  // [blocks][NB][4]
-  unsigned char* ring = q4_smem + static_cast<size_t>(blocks) * NB * (1024 + 32) + warp * (STAGES * Q4W_UNIT_BYTES);
-  float* partial = reinterpret_cast<float*>(q4_smem + static_cast<size_t>(blocks) * NB * (1024 + 32) + Q4W_WARPS * STAGES * Q4W_UNIT_BYTES);  // [warp][16][8 NB]
+  uint4* xq = reinterpret_cast<uint4*>(q4_smem);                                                  // [blocks][NB][2][32]
+  float2* xmeta = reinterpret_cast<float2*>(q4_smem + static_cast<size_t>(blocks) * NB * 1024);    // [blocks][NB][8] {sum, step}
+  unsigned char* ring = q4_smem + static_cast<size_t>(blocks) * NB * Q4W_X_BYTES + warp * (STAGES * Q4W_UNIT_BYTES);
+  float* partial = reinterpret_cast<float*>(q4_smem + static_cast<size_t>(blocks) * NB * Q4W_X_BYTES + WARPS * STAGES * Q4W_UNIT_BYTES);  // [warp][16][8 NB]
   const unsigned ring_base = static_cast<unsigned>(__cvta_generic_to_shared(ring));
 
-  // ---- activations: fragment order + block sums, once per CTA ----
-  for (unsigned b = warp; b < blocks; b += Q4W_WARPS) {
+  const unsigned ksplit = args.ksplit, group = warp / ksplit, ks = warp % ksplit, tile_groups = WARPS / ksplit;
+  const unsigned upt = (a.k / 256) / ksplit;  // units of this warp per tile
+  const unsigned items = args.rounds * upt;
+  const unsigned tile_step = tile_groups * gridDim.x, tile_first = group * gridDim.x + blockIdx.x;
+  const unsigned char* wbase = reinterpret_cast<const unsigned char*>(a.packed);
+  const size_t row_bytes = a.k / 2;
+  const unsigned copy_row = lane >> 3, copy_col = (lane & 7) * 16;
+  const unsigned param_which = lane >> 4, param_col = lane & 15;
+  const unsigned copy_dst = copy_row * Q4W_ROW_STRIDE + copy_col, param_dst = Q4W_PARAM_OFFSET + param_which * 128 + param_col * 8;
+  const unsigned short* param_base = param_which ? a.biases : a.scales;
+
+  // ---- producer side: the unit after the last one issued (tile, unit in tile, stage), advanced without divisions ----
+  unsigned in_tile = tile_first, in_u = 0, in_stage = 0, in_count = 0;
+  const unsigned char* in_rows[4];
+  const unsigned short* in_param = nullptr;
+  auto issue = [&]() {
+    if (in_count < items && in_tile < args.tiles) {
+      if (in_u == 0) {  // new tile: row pointers of this lane's 4 copies and of its parameter slot
+#pragma unroll
+        for (int i = 0; i < 4; ++i) in_rows[i] = wbase + min(in_tile * 16 + copy_row + 4 * i, a.n - 1) * row_bytes + (ks * upt) * 128 + copy_col;
+        in_param = param_base + static_cast<size_t>(min(in_tile * 16 + param_col, a.n - 1)) * groups_per_row + (ks * upt) * (256 / (g64 ? 64 : 128));
+      }
+      const unsigned stage = ring_base + in_stage * Q4W_UNIT_BYTES;
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(stage + copy_dst + i * (4 * Q4W_ROW_STRIDE)), "l"(in_rows[i] + in_u * 128) : "memory");
+      if (g64) asm volatile("cp.async.ca.shared.global [%0], [%1], 8;\n" ::"r"(stage + param_dst), "l"(in_param + in_u * 4) : "memory");
+      else asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"(stage + param_dst), "l"(in_param + in_u * 2) : "memory");
+    }
+    asm volatile("cp.async.commit_group;\n" ::: "memory");
+    ++in_count;
+    in_stage = in_stage + 1 == STAGES ? 0 : in_stage + 1;
+    if (++in_u == upt) { in_u = 0; in_tile += tile_step; }
+  };
+
+  for (int q = 0; q + 1 < STAGES; ++q) issue();  // the first weight units are already on their way while the activations are converted
+
+  // ---- activations -> block fixed point in fragment order, once per CTA ----
+  for (unsigned b = warp; b < blocks; b += WARPS) {
 #pragma unroll
     for (int nb = 0; nb < NB; ++nb) {
       uint4 x0 = make_uint4(0, 0, 0, 0), x1 = make_uint4(0, 0, 0, 0);
@@ -366,104 +424,112 @@ __global__ void __launch_bounds__(Q4W_WARPS * 32, 1) q4_warp_stream_kernel(Q4War
         x0 = *reinterpret_cast<const uint4*>(xr);
         x1 = *reinterpret_cast<const uint4*>(xr + 8);
       }
-      // a register pairs k = i with k = i + 4 (see the nibble masks below)
-      const uint4 pa = make_uint4(__byte_perm(x0.x, x0.z, 0x5410), __byte_perm(x0.x, x0.z, 0x7632), __byte_perm(x0.y, x0.w, 0x5410), __byte_perm(x0.y, x0.w, 0x7632));
-      const uint4 pb = make_uint4(__byte_perm(x1.x, x1.z, 0x5410), __byte_perm(x1.x, x1.z, 0x7632), __byte_perm(x1.y, x1.w, 0x5410), __byte_perm(x1.y, x1.w, 0x7632));
-      float s4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-      mma_q4<kBF16>(s4, ones, ones, ones, ones, pa.x, pa.y);
-      mma_q4<kBF16>(s4, ones, ones, ones, ones, pa.z, pa.w);
-      mma_q4<kBF16>(s4, ones, ones, ones, ones, pb.x, pb.y);
-      mma_q4<kBF16>(s4, ones, ones, ones, ones, pb.z, pb.w);
-      xperm[((b * NB + nb) * 2 + 0) * 32 + lane] = pa;
-      xperm[((b * NB + nb) * 2 + 1) * 32 + lane] = pb;
-      if (g == 0) xsum[(b * NB + nb) * 4 + t] = make_float2(s4[0], s4[1]);  // rows 2t, 2t+1 of this 8-row tile
+      const unsigned raw[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
+      float f[16];
+      float sum = 0.0f, biggest = 0.0f;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        f[2 * i] = half_to_f(raw[i] & 0xFFFFu);
+        f[2 * i + 1] = half_to_f(raw[i] >> 16);
+        sum += f[2 * i] + f[2 * i + 1];
+        biggest = fmaxf(biggest, fmaxf(fabsf(f[2 * i]), fabsf(f[2 * i + 1])));
+      }
+      sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+      sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+      biggest = fmaxf(biggest, __shfl_xor_sync(0xffffffffu, biggest, 1));
+      biggest = fmaxf(biggest, __shfl_xor_sync(0xffffffffu, biggest, 2));
+      // step = 2^(E - 11); blocks of zeros, subnormals, infinities or NaNs keep a harmless step of 1
+      const unsigned exponent = __float_as_uint(biggest) & 0x7F800000u;
+      const bool usable = exponent >= (12u << 23) && exponent < (255u << 23);
+      const float step = usable ? __uint_as_float(exponent - (11u << 23)) : 1.0f;
+      const float inv_step = usable ? __uint_as_float((254u << 23) - (exponent - (11u << 23))) : 1.0f;
+      int fixed[16];
+#pragma unroll
+      for (int i = 0; i < 16; ++i) fixed[i] = usable ? __float2int_rn(f[i] * inv_step) : 0;
+      // byte order of a B register: k = 0,2,4,6 | 1,3,5,7 | 8,10,12,14 | 9,11,13,15 (matches the nibble masks)
+      unsigned hi[4], lo[4];
+#pragma unroll
+      for (int r = 0; r < 4; ++r) {
+        const int base = (r >> 1) * 8 + (r & 1);
+        hi[r] = lo[r] = 0;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int v = fixed[base + 2 * j];
+          hi[r] |= (static_cast<unsigned>(v >> 8) & 0xFFu) << (8 * j);
+          lo[r] |= (static_cast<unsigned>(v) & 0xFFu) << (8 * j);
+        }
+      }
+      xq[((b * NB + nb) * 2 + 0) * 32 + lane] = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+      xq[((b * NB + nb) * 2 + 1) * 32 + lane] = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+      // a block without a usable step (all zeros, or values below 2^-115) keeps only its b * sum term
+      if (t == 0) xmeta[(b * NB + nb) * 8 + g] = make_float2(sum, usable ? step : 0.0f);
     }
   }
   __syncthreads();
 
-  const unsigned ksplit = args.ksplit, group = warp / ksplit, ks = warp % ksplit, tile_groups = Q4W_WARPS / ksplit;
-  const unsigned upt = (a.k / 256) / ksplit;  // units of this warp per tile
-  const unsigned items = args.rounds * upt;
-  const unsigned char* wbase = reinterpret_cast<const unsigned char*>(a.packed);
-  const size_t row_bytes = a.k / 2;
-  const unsigned copy_row = lane >> 3, copy_col = (lane & 7) * 16;
-  const unsigned param_which = lane >> 4, param_col = lane & 15;
-
-  auto tile_of = [&](unsigned q) { return ((q / upt) * tile_groups + group) * gridDim.x + blockIdx.x; };
-
-  auto issue = [&](unsigned q) {
-    if (q < items) {
-      const unsigned tile = tile_of(q);
-      if (tile < args.tiles) {
-        const unsigned k0 = (ks * upt + q % upt) * 256;
-        const unsigned stage = ring_base + (q % STAGES) * Q4W_UNIT_BYTES;
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const unsigned r = copy_row + 4 * i, col = min(tile * 16 + r, a.n - 1);
-          const unsigned char* src = wbase + col * row_bytes + k0 / 2 + copy_col;
-          asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(stage + r * Q4W_ROW_STRIDE + copy_col), "l"(src) : "memory");
-        }
-        const unsigned col = min(tile * 16 + param_col, a.n - 1);
-        const unsigned short* src = (param_which ? a.biases : a.scales) + static_cast<size_t>(col) * groups_per_row + k0 / a.group_size;
-        const unsigned dst = stage + Q4W_PARAM_OFFSET + param_which * 128 + param_col * 8;
-        if (g64) asm volatile("cp.async.ca.shared.global [%0], [%1], 8;\n" ::"r"(dst), "l"(src) : "memory");
-        else asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"(dst), "l"(src) : "memory");
-      }
-    }
-    asm volatile("cp.async.commit_group;\n" ::: "memory");
-  };
-
-  for (unsigned q = 0; q + 1 < STAGES; ++q) issue(q);
-
+  constexpr int kMagic = 0x4B400000;        // bit pattern of 12582912.0f
+  constexpr float kMagicF = 12582912.0f;
   float y[NB][4];
+  unsigned tile = tile_first, u = 0, out_stage = 0;
   for (unsigned q = 0; q < items; ++q) {
     asm volatile("cp.async.wait_group %0;\n" ::"n"(STAGES - 2) : "memory");
     __syncwarp();  // unit q is visible to the whole warp, and the warp is done with unit q - 1
-    issue(q + STAGES - 1);
-    const unsigned tile = tile_of(q), u = q % upt;
+    issue();
     const bool live = tile < args.tiles;
     if (u == 0) {
 #pragma unroll
       for (int nb = 0; nb < NB; ++nb) y[nb][0] = y[nb][1] = y[nb][2] = y[nb][3] = 0.0f;
     }
     if (live) {
-      const unsigned char* stage = ring + (q % STAGES) * Q4W_UNIT_BYTES;
+      const unsigned char* stage = ring + out_stage * Q4W_UNIT_BYTES;
+      // scales and biases of this lane's two columns for the unit's 4 blocks (group 128: 2 slots used)
       const uint2 sa = *reinterpret_cast<const uint2*>(stage + Q4W_PARAM_OFFSET + g * 8);
       const uint2 sb = *reinterpret_cast<const uint2*>(stage + Q4W_PARAM_OFFSET + (g + 8) * 8);
       const uint2 ba = *reinterpret_cast<const uint2*>(stage + Q4W_PARAM_OFFSET + 128 + g * 8);
       const uint2 bb = *reinterpret_cast<const uint2*>(stage + Q4W_PARAM_OFFSET + 128 + (g + 8) * 8);
-      const unsigned block0 = (ks * upt + u) * 4;
+      float s_a[4], s_b[4], b_a[4], b_b[4];
+      {
+        const unsigned w[8] = {sa.x, sa.y, sb.x, sb.y, ba.x, ba.y, bb.x, bb.y};
+        float v[8][2];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) { v[i][0] = __uint_as_float(w[i] << 16); v[i][1] = __uint_as_float(w[i] & 0xFFFF0000u); }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int slot = g64 ? j : j >> 1;
+          s_a[j] = v[0 + (slot >> 1)][slot & 1]; s_b[j] = v[2 + (slot >> 1)][slot & 1];
+          b_a[j] = v[4 + (slot >> 1)][slot & 1]; b_b[j] = v[6 + (slot >> 1)][slot & 1];
+        }
+      }
+      const uint4* xq_unit = xq + static_cast<size_t>((ks * upt + u) * 4) * (NB * 2 * 32) + lane;
+      const float2* meta_unit = xmeta + static_cast<size_t>((ks * upt + u) * 4) * (NB * 8) + 2 * t;
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
         const uint2 qa = *reinterpret_cast<const uint2*>(stage + g * Q4W_ROW_STRIDE + j * 32 + t * 8);
         const uint2 qb = *reinterpret_cast<const uint2*>(stage + (g + 8) * Q4W_ROW_STRIDE + j * 32 + t * 8);
-        const int slot = g64 ? j : j >> 1;  // parameter slot of this block inside the unit
-        auto pick = [&](const uint2& v) { const unsigned w = slot & 2 ? v.y : v.x; return slot & 1 ? w >> 16 : w & 0xFFFFu; };
-        const float s_a = to_f(pick(sa)), s_b = to_f(pick(sb));
-        const float o_a = to_f(pick(ba)) - offset * s_a, o_b = to_f(pick(bb)) - offset * s_b;
-        unsigned fa[2][4], fb[2][4];
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          fa[0][i] = ((qa.x >> (4 * i)) & 0x000F000Fu) | magic; fa[1][i] = ((qa.y >> (4 * i)) & 0x000F000Fu) | magic;
-          fb[0][i] = ((qb.x >> (4 * i)) & 0x000F000Fu) | magic; fb[1][i] = ((qb.y >> (4 * i)) & 0x000F000Fu) | magic;
-        }
+        const unsigned ea0 = qa.x & 0x0F0F0F0Fu, oa0 = (qa.x >> 4) & 0x0F0F0F0Fu, ea1 = qa.y & 0x0F0F0F0Fu, oa1 = (qa.y >> 4) & 0x0F0F0F0Fu;
+        const unsigned eb0 = qb.x & 0x0F0F0F0Fu, ob0 = (qb.x >> 4) & 0x0F0F0F0Fu, eb1 = qb.y & 0x0F0F0F0Fu, ob1 = (qb.y >> 4) & 0x0F0F0F0Fu;
 #pragma unroll
         for (int nb = 0; nb < NB; ++nb) {
-          const uint4 pa = xperm[(((block0 + j) * NB + nb) * 2 + 0) * 32 + lane];
-          const uint4 pb = xperm[(((block0 + j) * NB + nb) * 2 + 1) * 32 + lane];
-          const float2 sum = xsum[((block0 + j) * NB + nb) * 4 + t];
-          float acc0[4] = {0.0f, 0.0f, 0.0f, 0.0f}, acc1[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-          mma_q4<kBF16>(acc0, fa[0][0], fb[0][0], fa[0][1], fb[0][1], pa.x, pa.y);
-          mma_q4<kBF16>(acc1, fa[0][2], fb[0][2], fa[0][3], fb[0][3], pa.z, pa.w);
-          mma_q4<kBF16>(acc0, fa[1][0], fb[1][0], fa[1][1], fb[1][1], pb.x, pb.y);
-          mma_q4<kBF16>(acc1, fa[1][2], fb[1][2], fa[1][3], fb[1][3], pb.z, pb.w);
-          y[nb][0] += s_a * (acc0[0] + acc1[0]) + o_a * sum.x;
-          y[nb][1] += s_a * (acc0[1] + acc1[1]) + o_a * sum.y;
-          y[nb][2] += s_b * (acc0[2] + acc1[2]) + o_b * sum.x;
-          y[nb][3] += s_b * (acc0[3] + acc1[3]) + o_b * sum.y;
+          const uint4 xh = xq_unit[((j * NB + nb) * 2 + 0) * 32];
+          const uint4 xl = xq_unit[((j * NB + nb) * 2 + 1) * 32];
+          const float4 meta = *reinterpret_cast<const float4*>(meta_unit + (j * NB + nb) * 8);  // rows 2t, 2t+1: {sum, step} x 2
+          int hi[4] = {0, 0, 0, 0}, lo[4] = {kMagic, kMagic, kMagic, kMagic};
+          mma_u8<true>(hi, ea0, eb0, oa0, ob0, xh.x, xh.y);
+          mma_u8<false>(lo, ea0, eb0, oa0, ob0, xl.x, xl.y);
+          mma_u8<true>(hi, ea1, eb1, oa1, ob1, xh.z, xh.w);
+          mma_u8<false>(lo, ea1, eb1, oa1, ob1, xl.z, xl.w);
+          // |256 * hi + lo| < 2^22, so the combined integer keeps the magic exponent
+          float v[4];
+#pragma unroll
+          for (int i = 0; i < 4; ++i) v[i] = __int_as_float(hi[i] * 256 + lo[i]) - kMagicF;
+          y[nb][0] += (s_a[j] * meta.y) * v[0] + b_a[j] * meta.x;
+          y[nb][1] += (s_a[j] * meta.w) * v[1] + b_a[j] * meta.z;
+          y[nb][2] += (s_b[j] * meta.y) * v[2] + b_b[j] * meta.x;
+          y[nb][3] += (s_b[j] * meta.w) * v[3] + b_b[j] * meta.z;
         }
       }
     }
+    out_stage = out_stage + 1 == STAGES ? 0 : out_stage + 1;
     if (u + 1 == upt) {
       if (ksplit == 1) {
         if (live) {
@@ -501,58 +567,65 @@ __global__ void __launch_bounds__(Q4W_WARPS * 32, 1) q4_warp_stream_kernel(Q4War
         __syncthreads();
       }
     }
+    if (++u == upt) { u = 0; tile += tile_step; }
   }
   asm volatile("cp.async.wait_group 0;\n" ::: "memory");
 }
 
-template <bool kBF16, int NB, int STAGES>
-bool launch_q4_warp_stream(Ctx& ctx, const Q4WarpArgs& args, unsigned grid, size_t smem) {
+template <bool kG64, int NB, int STAGES, int WARPS>
+bool launch_q4_i8_stream(Ctx& ctx, const Q4WarpArgs& args, unsigned grid, size_t smem) {
   static bool configured[64] = {};
   int device = 0;
   cudaGetDevice(&device);
   if (device < 0 || device >= 64) return false;
   if (!configured[device]) {
-    if (cudaFuncSetAttribute(q4_warp_stream_kernel<kBF16, NB, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) != cudaSuccess) { cudaGetLastError(); return false; }
+    if (cudaFuncSetAttribute(q4_i8_stream_kernel<kG64, NB, STAGES, WARPS>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) != cudaSuccess) { cudaGetLastError(); return false; }
     configured[device] = true;
   }
-  q4_warp_stream_kernel<kBF16, NB, STAGES><<<grid, Q4W_WARPS * 32, smem, ctx.stream>>>(args);
+  q4_i8_stream_kernel<kG64, NB, STAGES, WARPS><<<grid, WARPS * 32, smem, ctx.stream>>>(args);
   ctx.launches++;
   return true;
 }
 
-// Tries the streaming kernel; false when shape or alignment rule it out (the caller falls back).
-bool run_q4_stream(Ctx& ctx, const Q4MmaArgs& a, int x_dt) {
-  const unsigned param_align = a.group_size == 64 ? 8 : 4;
-  if (a.k % 256 != 0 || reinterpret_cast<size_t>(a.packed) % 16 != 0 || reinterpret_cast<size_t>(a.scales) % param_align != 0 ||
-      reinterpret_cast<size_t>(a.biases) % param_align != 0) return false;
-  const unsigned nb = a.m <= 8 ? 1 : 2, blocks = a.k / 64, units = a.k / 256;
-  const unsigned sms = static_cast<unsigned>(ctx.sm_count > 0 ? ctx.sm_count : 148);
-  Q4WarpArgs args{a, (a.n + 15) / 16, 1, 1};
-  const unsigned grid = std::min(args.tiles, sms);
-  // too few tiles for every warp to own one: let 2, 4 or 8 warps share a tile along K
-  const unsigned per_cta = (args.tiles + grid - 1) / grid;
+// Shared-memory need of one CTA and the tile split for a given warp count; false when it cannot run.
+template <int STAGES, int WARPS>
+bool plan_q4_i8(const Q4MmaArgs& a, unsigned sms, unsigned nb, Q4WarpArgs* args, unsigned* grid, size_t* smem) {
+  const unsigned blocks = a.k / 64, units = a.k / 256;
+  args->tiles = (a.n + 15) / 16;
+  *grid = std::min(args->tiles, sms);
+  // too few tiles for every warp to own one: let 2, 4, ... warps share a tile along K
+  const unsigned per_cta = (args->tiles + *grid - 1) / *grid;
   unsigned tile_groups = 1;
-  while (tile_groups < Q4W_WARPS && tile_groups < per_cta) tile_groups *= 2;
-  args.ksplit = Q4W_WARPS / tile_groups;
-  while (args.ksplit > 1 && units % args.ksplit != 0) args.ksplit /= 2;
-  tile_groups = Q4W_WARPS / args.ksplit;
-  args.rounds = (args.tiles + tile_groups * grid - 1) / (tile_groups * grid);
-  const size_t fixed = static_cast<size_t>(blocks) * nb * (1024 + 32) + (args.ksplit > 1 ? Q4W_WARPS * 16 * 8 * nb * sizeof(float) : 0);
-  const size_t limit = 227 * 1024;
-  const bool bf = x_dt == BF16;
-  if (fixed + Q4W_WARPS * 6 * Q4W_UNIT_BYTES <= limit) {
-    const size_t smem = fixed + Q4W_WARPS * 6 * Q4W_UNIT_BYTES;
-    if (nb == 1) return bf ? launch_q4_warp_stream<true, 1, 6>(ctx, args, grid, smem) : launch_q4_warp_stream<false, 1, 6>(ctx, args, grid, smem);
-    return bf ? launch_q4_warp_stream<true, 2, 6>(ctx, args, grid, smem) : launch_q4_warp_stream<false, 2, 6>(ctx, args, grid, smem);
-  }
-  if (fixed + Q4W_WARPS * 3 * Q4W_UNIT_BYTES <= limit) {
-    const size_t smem = fixed + Q4W_WARPS * 3 * Q4W_UNIT_BYTES;
-    if (nb == 1) return bf ? launch_q4_warp_stream<true, 1, 3>(ctx, args, grid, smem) : launch_q4_warp_stream<false, 1, 3>(ctx, args, grid, smem);
-    return bf ? launch_q4_warp_stream<true, 2, 3>(ctx, args, grid, smem) : launch_q4_warp_stream<false, 2, 3>(ctx, args, grid, smem);
-  }
+  while (tile_groups < WARPS && tile_groups < per_cta) tile_groups *= 2;
+  args->ksplit = WARPS / tile_groups;
+  while (args->ksplit > 1 && units % args->ksplit != 0) args->ksplit /= 2;
+  tile_groups = WARPS / args->ksplit;
+  args->rounds = (args->tiles + tile_groups * *grid - 1) / (tile_groups * *grid);
+  *smem = static_cast<size_t>(blocks) * nb * Q4W_X_BYTES + static_cast<size_t>(WARPS) * STAGES * Q4W_UNIT_BYTES +
+          (args->ksplit > 1 ? static_cast<size_t>(WARPS) * 16 * 8 * nb * sizeof(float) : 0);
+  return *smem <= 227 * 1024;
+}
+
+template <bool kG64, int NB>
+bool run_q4_i8_config(Ctx& ctx, const Q4MmaArgs& a, unsigned sms) {
+  Q4WarpArgs args{a, 0, 1, 1};
+  unsigned grid = 0;
+  size_t smem = 0;
+  if (plan_q4_i8<4, 16>(a, sms, NB, &args, &grid, &smem)) return launch_q4_i8_stream<kG64, NB, 4, 16>(ctx, args, grid, smem);
+  if (plan_q4_i8<3, 16>(a, sms, NB, &args, &grid, &smem)) return launch_q4_i8_stream<kG64, NB, 3, 16>(ctx, args, grid, smem);
+  if (plan_q4_i8<3, 8>(a, sms, NB, &args, &grid, &smem)) return launch_q4_i8_stream<kG64, NB, 3, 8>(ctx, args, grid, smem);
   return false;
 }
 
+// Tries the streaming kernel; false when dtype, shape or alignment rule it out (the caller falls back).
+bool run_q4_stream(Ctx& ctx, const Q4MmaArgs& a, int x_dt) {
+  const unsigned param_align = a.group_size == 64 ? 8 : 4;
+  if (x_dt != BF16 || a.k % 256 != 0 || reinterpret_cast<size_t>(a.packed) % 16 != 0 || reinterpret_cast<size_t>(a.scales) % param_align != 0 ||
+      reinterpret_cast<size_t>(a.biases) % param_align != 0) return false;
+  const unsigned sms = static_cast<unsigned>(ctx.sm_count > 0 ? ctx.sm_count : 148);
+  if (a.group_size == 64) return a.m <= 8 ? run_q4_i8_config<true, 1>(ctx, a, sms) : run_q4_i8_config<true, 2>(ctx, a, sms);
+  return a.m <= 8 ? run_q4_i8_config<false, 1>(ctx, a, sms) : run_q4_i8_config<false, 2>(ctx, a, sms);
+}
 
 // Dequantises `cols` weight rows (columns of the projection) starting at absolute row `row0` of
 // the scale/bias tables into a dense [cols, k] matrix of dtype out_dt; one thread per packed word.

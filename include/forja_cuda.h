@@ -224,6 +224,50 @@ typedef struct fj_pack_view {
 int32_t fj_pack_step(fj_kvpool* pool, const uint32_t* starts, const uint32_t* tokens, uint32_t lanes,
                      fj_pack_view* out);
 
+/* Continuous-batching policy on the host; replaces SchedulerPolicy
+ * (crates/forja-serve/src/scheduler.rs:16-196). Integer bookkeeping, bit-exact with the reference:
+ *   create            SchedulerPolicy::new :30-66 (buckets sorted + deduplicated, must start at 1 and
+ *                     reach active_limit; limits and budgets positive, else FJ_INVALID_INPUT)
+ *   set_prompt_chunk_multiple  with_prompt_chunk_multiple :67-76 (switches to merged chunking)
+ *   enqueue / reconcile_active / complete / retry_admission   :78-107
+ *   admit             :109-152: FIFO; a head that cannot be reserved may be overtaken at most 8 times
+ *                     by the first strictly smaller request that can; `reserve` returns nonzero when
+ *                     it has reserved room for (id, reserved_tokens). Returns how many were admitted
+ *                     and writes up to cap ids in admission order.
+ *   admit_pages       admit with the page arithmetic of the continuous engine: a request needs
+ *                     ceil(reserved_tokens / page_tokens) pages out of *free_pages (decremented).
+ *   decode_bucket     :89-95: smallest bucket >= max(slot) + 1 (saturating), -1 when none / empty
+ *   ready_prompt / prompt_batch  :154-195: round-robin over ascending ids starting after the id
+ *                     served last, at most prefill_limit entries, spending prompt_budget (decoding)
+ *                     or idle_prompt_budget through PromptChunking::work / merged_work
+ *                     (crates/forja-host/src/prompt.rs:20-41). */
+typedef struct fj_sched fj_sched;
+typedef int32_t (*fj_sched_reserve_fn)(void* user, uint64_t id, uint64_t reserved_tokens);
+int32_t fj_sched_create(const uint32_t* buckets, uint32_t bucket_count, uint64_t active_limit, uint64_t prefill_limit,
+                        uint32_t prompt_budget, uint32_t idle_prompt_budget, fj_sched** out);
+void fj_sched_destroy(fj_sched* sched);
+void fj_sched_set_prompt_chunk_multiple(fj_sched* sched, uint32_t multiple);
+void fj_sched_enqueue(fj_sched* sched, uint64_t id, uint64_t reserved_tokens);
+void fj_sched_reconcile_active(fj_sched* sched, uint64_t active);
+void fj_sched_complete(fj_sched* sched, uint64_t id);
+void fj_sched_retry_admission(fj_sched* sched, uint64_t id, uint64_t reserved_tokens);
+uint64_t fj_sched_admit(fj_sched* sched, fj_sched_reserve_fn reserve, void* user, uint64_t* ids, uint64_t cap);
+uint64_t fj_sched_admit_pages(fj_sched* sched, uint32_t page_tokens, uint64_t* free_pages, uint64_t* ids, uint64_t cap);
+int64_t fj_sched_decode_bucket(const fj_sched* sched, const uint32_t* slots, uint64_t count);
+void fj_sched_ready_prompt(fj_sched* sched, uint64_t id, uint32_t tokens);
+uint64_t fj_sched_prompt_batch(fj_sched* sched, int32_t decoding, uint64_t* ids, uint32_t* spend, uint64_t cap);
+uint64_t fj_sched_waiting(const fj_sched* sched);
+uint64_t fj_sched_active(const fj_sched* sched);
+/* PromptChunking::work / merged_work (crates/forja-host/src/prompt.rs:20-41). */
+uint32_t fj_prompt_chunk_work(uint32_t piece, uint32_t remaining, uint32_t allowance);
+uint32_t fj_prompt_chunk_merged_work(uint32_t piece, uint32_t remaining, uint32_t allowance);
+/* reservations_fit (crates/forja-serve/src/engine/continuous/batch.rs:1139-1152): 1 when the pages of
+ * all reservations fit ceil(max_context / page_tokens), 0 otherwise or on overflow. */
+int32_t fj_reservations_fit(uint32_t page_tokens, uint32_t max_context, const uint64_t* reservations, uint64_t count);
+/* Chunk lengths of a chunked prefill (crates/forja-sdk/src/nn/blocks.rs:892-911): full chunks, then
+ * tail_chunk-sized pieces; returns the number of pieces (0 = no valid plan). */
+uint64_t fj_prefill_plan(uint32_t sequence, uint32_t chunk, uint32_t tail_chunk, uint32_t* out, uint64_t cap);
+
 /* Dense decoder (SmolLM2 / Qwen3-dense shapes; reference op order: engines/qwen3/src/lib.rs:391-452,
  * 734-811 and engines/smollm2/src/optimized.rs:97-245). Weights are buffers of this backend in the
  * activation dtype: embed [vocab, hidden] (tied lm_head), per layer wq [hq*d, hidden],
