@@ -344,9 +344,15 @@ constexpr int Q4W_PARAM_OFFSET = 16 * Q4W_ROW_STRIDE;
 constexpr int Q4W_UNIT_BYTES = Q4W_PARAM_OFFSET + 256;  // scales [16][4] u16, biases [16][4] u16
 constexpr int Q4W_X_BYTES = 1024 + 64;                  // per (64-k block, 8-row tile): fragments + {sum, step} per row
 
+// Tiles [tile_base, tile_end) are dealt out in `rounds` rounds of (WARPS / ksplit) tiles per CTA, each tile
+// shared by ksplit warps along K. Phase 0 gives every warp of the grid the same number of whole tiles;
+// phase 1 spreads the remainder over as many warps as possible so that the tail costs a fraction of a tile.
+struct Q4Phase {
+  unsigned ksplit, rounds, tile_base, tile_end;
+};
 struct Q4WarpArgs {
   Q4MmaArgs base;
-  unsigned tiles, ksplit, rounds;  // 16-column tiles; warps sharing a tile (power of two); tile rounds per CTA
+  Q4Phase phase[2];
 };
 
 template <bool kSignedB>
@@ -377,10 +383,14 @@ __global__ void __launch_bounds__(WARPS * 32, 1) q4_i8_stream_kernel(Q4WarpArgs 
   float* partial = reinterpret_cast<float*>(q4_smem + static_cast<size_t>(blocks) * NB * Q4W_X_BYTES + WARPS * STAGES * Q4W_UNIT_BYTES);  // [warp][16][8 NB]
   const unsigned ring_base = static_cast<unsigned>(__cvta_generic_to_shared(ring));
 
-  const unsigned ksplit = args.ksplit, group = warp / ksplit, ks = warp % ksplit, tile_groups = WARPS / ksplit;
+  bool x_ready = false;
+  for (int phase_index = 0; phase_index < 2; ++phase_index) {
+  const Q4Phase ph = phase_index == 0 ? args.phase[0] : args.phase[1];
+  if (ph.rounds == 0) continue;  // uniform across the grid
+  const unsigned ksplit = ph.ksplit, group = warp / ksplit, ks = warp % ksplit, tile_groups = WARPS / ksplit;
   const unsigned upt = (a.k / 256) / ksplit;  // units of this warp per tile
-  const unsigned items = args.rounds * upt;
-  const unsigned tile_step = tile_groups * gridDim.x, tile_first = group * gridDim.x + blockIdx.x;
+  const unsigned items = ph.rounds * upt;
+  const unsigned tile_step = tile_groups * gridDim.x, tile_first = ph.tile_base + group * gridDim.x + blockIdx.x;
   const unsigned char* wbase = reinterpret_cast<const unsigned char*>(a.packed);
   const size_t row_bytes = a.k / 2;
   const unsigned copy_row = lane >> 3, copy_col = (lane & 7) * 16;
@@ -393,7 +403,7 @@ __global__ void __launch_bounds__(WARPS * 32, 1) q4_i8_stream_kernel(Q4WarpArgs 
   const unsigned char* in_rows[4];
   const unsigned short* in_param = nullptr;
   auto issue = [&]() {
-    if (in_count < items && in_tile < args.tiles) {
+    if (in_count < items && in_tile < ph.tile_end) {
       if (in_u == 0) {  // new tile: row pointers of this lane's 4 copies and of its parameter slot
 #pragma unroll
         for (int i = 0; i < 4; ++i) in_rows[i] = wbase + min(in_tile * 16 + copy_row + 4 * i, a.n - 1) * row_bytes + (ks * upt) * 128 + copy_col;
@@ -415,7 +425,7 @@ __global__ void __launch_bounds__(WARPS * 32, 1) q4_i8_stream_kernel(Q4WarpArgs 
   for (int q = 0; q + 1 < STAGES; ++q) issue();  // the first weight units are already on their way while the activations are converted
 
   // ---- activations -> block fixed point in fragment order, once per CTA ----
-  for (unsigned b = warp; b < blocks; b += WARPS) {
+  for (unsigned b = x_ready ? blocks : warp; b < blocks; b += WARPS) {
 #pragma unroll
     for (int nb = 0; nb < NB; ++nb) {
       uint4 x0 = make_uint4(0, 0, 0, 0), x1 = make_uint4(0, 0, 0, 0);
@@ -465,6 +475,7 @@ __global__ void __launch_bounds__(WARPS * 32, 1) q4_i8_stream_kernel(Q4WarpArgs 
       if (t == 0) xmeta[(b * NB + nb) * 8 + g] = make_float2(sum, usable ? step : 0.0f);
     }
   }
+  x_ready = true;
   __syncthreads();
 
   constexpr int kMagic = 0x4B400000;        // bit pattern of 12582912.0f
@@ -475,7 +486,7 @@ __global__ void __launch_bounds__(WARPS * 32, 1) q4_i8_stream_kernel(Q4WarpArgs 
     asm volatile("cp.async.wait_group %0;\n" ::"n"(STAGES - 2) : "memory");
     __syncwarp();  // unit q is visible to the whole warp, and the warp is done with unit q - 1
     issue();
-    const bool live = tile < args.tiles;
+    const bool live = tile < ph.tile_end;
     if (u == 0) {
 #pragma unroll
       for (int nb = 0; nb < NB; ++nb) y[nb][0] = y[nb][1] = y[nb][2] = y[nb][3] = 0.0f;
@@ -570,6 +581,8 @@ __global__ void __launch_bounds__(WARPS * 32, 1) q4_i8_stream_kernel(Q4WarpArgs 
     if (++u == upt) { u = 0; tile += tile_step; }
   }
   asm volatile("cp.async.wait_group 0;\n" ::: "memory");
+  __syncwarp();
+  }  // phase
 }
 
 template <bool kG64, int NB, int STAGES, int WARPS>
@@ -587,28 +600,34 @@ bool launch_q4_i8_stream(Ctx& ctx, const Q4WarpArgs& args, unsigned grid, size_t
   return true;
 }
 
-// Shared-memory need of one CTA and the tile split for a given warp count; false when it cannot run.
+// Shared-memory need of one CTA and the two-phase tile split for a given warp count; false when it cannot run.
 template <int STAGES, int WARPS>
 bool plan_q4_i8(const Q4MmaArgs& a, unsigned sms, unsigned nb, Q4WarpArgs* args, unsigned* grid, size_t* smem) {
-  const unsigned blocks = a.k / 64, units = a.k / 256;
-  args->tiles = (a.n + 15) / 16;
-  *grid = std::min(args->tiles, sms);
-  // too few tiles for every warp to own one: let 2, 4, ... warps share a tile along K
-  const unsigned per_cta = (args->tiles + *grid - 1) / *grid;
-  unsigned tile_groups = 1;
-  while (tile_groups < WARPS && tile_groups < per_cta) tile_groups *= 2;
-  args->ksplit = WARPS / tile_groups;
-  while (args->ksplit > 1 && units % args->ksplit != 0) args->ksplit /= 2;
-  tile_groups = WARPS / args->ksplit;
-  args->rounds = (args->tiles + tile_groups * *grid - 1) / (tile_groups * *grid);
+  const unsigned blocks = a.k / 64, units = a.k / 256, tiles = (a.n + 15) / 16;
+  *grid = std::min(tiles, sms);
+  const unsigned warps_total = *grid * WARPS, whole = tiles / warps_total;
+  args->phase[0] = Q4Phase{1, whole, 0, whole * warps_total};
+  args->phase[1] = Q4Phase{1, 0, whole * warps_total, tiles};
+  const unsigned rest = tiles - whole * warps_total;
+  if (rest != 0) {
+    // too few tiles left for every warp to own one: let 2, 4, ... warps share a tile along K
+    const unsigned per_cta = (rest + *grid - 1) / *grid;
+    unsigned tile_groups = 1;
+    while (tile_groups < WARPS && tile_groups < per_cta) tile_groups *= 2;
+    unsigned ksplit = WARPS / tile_groups;
+    while (ksplit > 1 && units % ksplit != 0) ksplit /= 2;
+    tile_groups = WARPS / ksplit;
+    args->phase[1].ksplit = ksplit;
+    args->phase[1].rounds = (rest + tile_groups * *grid - 1) / (tile_groups * *grid);
+  }
   *smem = static_cast<size_t>(blocks) * nb * Q4W_X_BYTES + static_cast<size_t>(WARPS) * STAGES * Q4W_UNIT_BYTES +
-          (args->ksplit > 1 ? static_cast<size_t>(WARPS) * 16 * 8 * nb * sizeof(float) : 0);
+          (args->phase[1].ksplit > 1 ? static_cast<size_t>(WARPS) * 16 * 8 * nb * sizeof(float) : 0);
   return *smem <= 227 * 1024;
 }
 
 template <bool kG64, int NB>
 bool run_q4_i8_config(Ctx& ctx, const Q4MmaArgs& a, unsigned sms) {
-  Q4WarpArgs args{a, 0, 1, 1};
+  Q4WarpArgs args{a, {}};
   unsigned grid = 0;
   size_t smem = 0;
   if (plan_q4_i8<4, 16>(a, sms, NB, &args, &grid, &smem)) return launch_q4_i8_stream<kG64, NB, 4, 16>(ctx, args, grid, smem);
