@@ -5,9 +5,9 @@ The product is the C-ABI shared library ``libforja_cuda.so`` (sources in ``csrc/
 reference's backend interface used by tests and benchmarks. Importing it never touches a CPU
 fallback: every compute entry point needs the compiled library and a CUDA device.
 """
-from .backend import (BF16, F16, F32, I32, U32, BackendError, CommandList, CudaBackend, DenseModel, KvPool, Layout, Op,
-                      Submission, Tensor)
+from .backend import (BF16, F16, F32, I32, U32, BackendError, CommandList, CudaBackend, DenseModel, ExpertParallel, KvPool, Layout,
+                      MoeModel, Op, Submission, Tensor)
 from .scheduler import SchedulerPolicy, chunk_merged_work, chunk_work, prefill_plan, reservations_fit
 
 __all__ = ["BF16", "F16", "F32", "I32", "U32", "BackendError", "CommandList", "CudaBackend", "DenseModel", "KvPool", "Layout",
-           "Op", "Submission", "Tensor", "SchedulerPolicy", "chunk_work", "chunk_merged_work", "prefill_plan", "reservations_fit"]
+           "Op", "Submission", "Tensor", "ExpertParallel", "MoeModel", "SchedulerPolicy", "chunk_work", "chunk_merged_work", "prefill_plan", "reservations_fit"]

@@ -48,6 +48,20 @@ class FjDenseLayerWeights(C.Structure):
     _fields_ = [(n, C.c_uint64) for n in ("input_norm", "wq", "wk", "wv", "q_norm", "k_norm", "wo", "post_norm", "w_gate", "w_up", "w_down")]
 
 
+class FjQuantWeight(C.Structure):
+    _fields_ = [("packed", C.c_uint64), ("scales", C.c_uint64), ("biases", C.c_uint64)]
+
+
+class FjMoeConfig(C.Structure):
+    _fields_ = [(n, C.c_uint32) for n in ("layers", "hidden", "q_heads", "kv_heads", "head_dim", "experts", "top_k", "expert_intermediate", "vocab",
+                                          "group_size", "router_bits")] + [("eps", C.c_float), ("theta", C.c_float), ("max_rows", C.c_uint32)]
+
+
+class FjMoeLayerWeights(C.Structure):
+    _fields_ = [(n, C.c_uint64) for n in ("input_norm", "q_norm", "k_norm", "post_norm")] + \
+               [(n, FjQuantWeight) for n in ("qkv", "o", "router", "gate", "up", "down")]
+
+
 SCHED_RESERVE_FN = C.CFUNCTYPE(C.c_int32, C.c_void_p, C.c_uint64, C.c_uint64)
 
 # Every symbol include/forja_cuda.h declares; the loader test checks that the library exports them all.
@@ -64,6 +78,8 @@ EXPORTS = [
     "fj_sched_reconcile_active", "fj_sched_complete", "fj_sched_retry_admission", "fj_sched_admit", "fj_sched_admit_pages",
     "fj_sched_decode_bucket", "fj_sched_ready_prompt", "fj_sched_prompt_batch", "fj_sched_waiting", "fj_sched_active",
     "fj_prompt_chunk_work", "fj_prompt_chunk_merged_work", "fj_reservations_fit", "fj_prefill_plan",
+    "fj_ep_load", "fj_ep_unique_id", "fj_ep_create", "fj_ep_destroy", "fj_ep_all_to_all", "fj_moe_model_create", "fj_moe_model_destroy",
+    "fj_moe_step", "fj_moe_step_stats",
 ]
 
 _lib = None
@@ -131,6 +147,9 @@ def load():
         "fj_sched_waiting": ([P], U64), "fj_sched_active": ([P], U64),
         "fj_prompt_chunk_work": ([U32, U32, U32], U32), "fj_prompt_chunk_merged_work": ([U32, U32, U32], U32),
         "fj_reservations_fit": ([U32, U32, P, U64], I32), "fj_prefill_plan": ([U32, U32, U32, P, U64], U64),
+        "fj_ep_load": ([C.c_char_p], I32), "fj_ep_unique_id": ([P], I32), "fj_ep_create": ([P, P, U32, U32, P], I32), "fj_ep_destroy": ([P], None),
+        "fj_ep_all_to_all": ([P, U64, U64, U64], I32), "fj_moe_model_create": ([P, P, P, U64, P, P, P, P, P], I32),
+        "fj_moe_model_destroy": ([P], None), "fj_moe_step": ([P, P, P, U64], I32), "fj_moe_step_stats": ([P, P, P], I32),
     }
     for name, (types, restype) in sched.items():
         fn = getattr(lib, name)

@@ -9,6 +9,7 @@ backend without a CUDA device raises.
 from __future__ import annotations
 
 import ctypes as C
+import os
 from dataclasses import dataclass, field
 from typing import List, Optional, Sequence, Tuple
 
@@ -508,4 +509,90 @@ class DenseModel:
     def stats(self):
         k, w = C.c_uint64(0), C.c_uint64(0)
         _check(self._lib.fj_dense_step_stats(self._h, C.byref(k), C.byref(w)))
+        return {"kernels": k.value, "attn_work_items": w.value}
+
+
+def nccl_library_path() -> Optional[str]:
+    """Path of the NCCL library bundled with PyTorch's wheels, when there is one."""
+    try:
+        import nvidia.nccl  # type: ignore
+        root = os.path.dirname(nvidia.nccl.__file__) if getattr(nvidia.nccl, "__file__", None) else list(nvidia.nccl.__path__)[0]
+        path = os.path.join(root, "lib", "libnccl.so.2")
+        return path if os.path.exists(path) else None
+    except Exception:
+        return None
+
+
+class ExpertParallel:
+    """Group of ranks (one per GPU) that share the experts of a sparse-MoE model (fj_ep_*).
+    ``exchange`` moves the 128-byte group id from rank 0 to every rank (e.g. a torch.distributed
+    broadcast): it receives rank 0's bytes (None elsewhere) and returns the agreed bytes."""
+
+    def __init__(self, backend: CudaBackend, rank: int, world: int, exchange):
+        self.backend, self._lib, self.rank, self.world = backend, backend._lib, rank, world
+        path = nccl_library_path()
+        _check(self._lib.fj_ep_load(path.encode() if path else None))
+        mine = None
+        if rank == 0:
+            buf = (C.c_uint8 * 128)()
+            _check(self._lib.fj_ep_unique_id(buf))
+            mine = bytes(buf)
+        agreed = exchange(mine)
+        handle = C.c_void_p()
+        _check(self._lib.fj_ep_create(backend._h, (C.c_uint8 * 128).from_buffer_copy(agreed), rank, world, C.byref(handle)))
+        self._h = handle
+
+    def all_to_all(self, send: Tensor, recv: Tensor, bytes_per_peer: int):
+        _check(self._lib.fj_ep_all_to_all(self._h, send.buffer, recv.buffer, bytes_per_peer))
+
+    def close(self):
+        if getattr(self, "_h", None) and getattr(self.backend, "_h", None):
+            self._lib.fj_ep_destroy(self._h)
+        self._h = None
+
+
+def _quant_weight(triple) -> "_lib.FjQuantWeight":
+    w = _lib.FjQuantWeight()
+    w.packed, w.scales, w.biases = (t.buffer for t in triple)
+    return w
+
+
+class MoeModel:
+    """Sparse-MoE decoder on the fast path (fj_moe_model_create / fj_moe_step). Quantised weights
+    are (packed, scales, biases) tensor triples; ``layers`` entries carry input_norm, q_norm,
+    k_norm, post_norm and the triples qkv, o, router, gate, up, down."""
+
+    def __init__(self, backend: CudaBackend, pool: KvPool, config: dict, embed, final_norm: Tensor, lm_head, layers: Sequence[dict],
+                 ep: Optional[ExpertParallel] = None):
+        self.backend, self.pool, self._lib, self.config = backend, pool, backend._lib, dict(config)
+        cfg = _lib.FjMoeConfig()
+        for name, _ in _lib.FjMoeConfig._fields_:
+            setattr(cfg, name, config[name])
+        arr = (_lib.FjMoeLayerWeights * len(layers))()
+        for i, layer in enumerate(layers):
+            for name in ("input_norm", "q_norm", "k_norm", "post_norm"):
+                setattr(arr[i], name, layer[name].buffer)
+            for name in ("qkv", "o", "router", "gate", "up", "down"):
+                setattr(arr[i], name, _quant_weight(layer[name]))
+        e, h = _quant_weight(embed), _quant_weight(lm_head)
+        handle = C.c_void_p()
+        _check(self._lib.fj_moe_model_create(backend._h, C.byref(cfg), C.byref(e), final_norm.buffer, C.byref(h), arr, pool._h, ep._h if ep is not None else None,
+                                             C.byref(handle)))
+        self._h = handle
+
+    def close(self):
+        if getattr(self, "_h", None) and getattr(self.backend, "_h", None):
+            self._lib.fj_moe_model_destroy(self._h)
+        self._h = None
+
+    def step(self, token_ids=None, want_tokens: bool = True, logits: Optional[Tensor] = None, lanes: Optional[int] = None):
+        ids = None if token_ids is None else np.ascontiguousarray(token_ids, np.uint32)
+        out = np.zeros(lanes if lanes is not None else self.pool.lanes, np.uint32) if want_tokens else None
+        _check(self._lib.fj_moe_step(self._h, None if ids is None else ids.ctypes.data_as(C.c_void_p),
+                                     None if out is None else out.ctypes.data_as(C.c_void_p), logits.buffer if logits is not None else 0))
+        return out
+
+    def stats(self):
+        k, w = C.c_uint64(0), C.c_uint64(0)
+        _check(self._lib.fj_moe_step_stats(self._h, C.byref(k), C.byref(w)))
         return {"kernels": k.value, "attn_work_items": w.value}

@@ -48,7 +48,39 @@ struct fj_backend {
   std::mutex pinned_mutex;
 };
 
+// Paged-KV pool: device allocator state, page tables and the metadata of the last packed step.
+struct fj_kvpool {
+  fj_backend* be = nullptr;
+  fj::KvPoolDevice dev{};
+  uint64_t buf_free = 0, buf_count = 0, buf_gens = 0, buf_tables = 0, buf_lane_pages = 0;
+  // packer state
+  uint64_t buf_lane_meta[5] = {0, 0, 0, 0, 0};  // logical_lengths, query_starts, absolute_positions, activity, cu_seqlens
+  uint64_t buf_rows[3] = {0, 0, 0};             // positions, slot_mapping, row_lane
+  uint64_t buf_stage = 0;                       // starts | tokens staged on the device
+  uint32_t rows_cap = 0;
+  fj::PackOutputs pack{};
+  std::vector<uint32_t> host_starts, host_tokens;  // last packed step (host copy for grid sizing)
+  uint32_t rows = 0, lanes_packed = 0;
+};
+
 namespace fjb {
+
+// Row-major [rows, width] view with the given row stride (elements), and its broadcast form for a
+// [width] weight vector shared by every row.
+inline fj::View dense_view(void* base, int dtype, unsigned rows, unsigned width, size_t row_stride) {
+  fj::View v;
+  v.base = base; v.dtype = dtype; v.rank = 2;
+  for (int a = 0; a < 8; ++a) { v.shape[a] = 1; v.strides[a] = 0; }
+  v.shape[0] = rows; v.shape[1] = width; v.strides[0] = row_stride; v.strides[1] = 1;
+  return v;
+}
+inline fj::View weight_view(const void* base, int dtype, unsigned rows, unsigned width) {
+  return dense_view(const_cast<void*>(base), dtype, rows, width, 0);
+}
+// Tokens of the previous step fed back as this step's inputs (last row of each lane), and the
+// gather of every lane's last row into [lanes, width] (inactive lanes: zeros).
+void launch_feedback_tokens(fj::Ctx& ctx, const unsigned* cu_seqlens, const unsigned* previous, unsigned* tokens, unsigned lanes);
+void launch_gather_last_rows(fj::Ctx& ctx, const void* hidden, int dtype, const unsigned* cu_seqlens, void* out, unsigned lanes, unsigned width);
 
 // Looks up a buffer; nullptr when unknown.
 fj_buffer_rec* find_buffer(fj_backend* be, uint64_t id);

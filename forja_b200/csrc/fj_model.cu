@@ -13,20 +13,6 @@
 
 using namespace fjb;
 
-struct fj_kvpool {
-  fj_backend* be = nullptr;
-  fj::KvPoolDevice dev{};
-  uint64_t buf_free = 0, buf_count = 0, buf_gens = 0, buf_tables = 0, buf_lane_pages = 0;
-  // packer state
-  uint64_t buf_lane_meta[5] = {0, 0, 0, 0, 0};  // logical_lengths, query_starts, absolute_positions, activity, cu_seqlens
-  uint64_t buf_rows[3] = {0, 0, 0};             // positions, slot_mapping, row_lane
-  uint64_t buf_stage = 0;                       // starts | tokens staged on the device
-  uint32_t rows_cap = 0;
-  fj::PackOutputs pack{};
-  std::vector<uint32_t> host_starts, host_tokens;  // last packed step (host copy for grid sizing)
-  uint32_t rows = 0, lanes_packed = 0;
-};
-
 namespace {
 
 void* buf_ptr(fj_backend* be, uint64_t id) {
@@ -271,19 +257,19 @@ __global__ void fill_normal_kernel(void* out, int dt, size_t elements, unsigned 
   }
 }
 
-fj::View dense_view(void* base, int dtype, unsigned rows, unsigned width, size_t row_stride) {
-  fj::View v;
-  v.base = base; v.dtype = dtype; v.rank = 2;
-  for (int a = 0; a < 8; ++a) { v.shape[a] = 1; v.strides[a] = 0; }
-  v.shape[0] = rows; v.shape[1] = width; v.strides[0] = row_stride; v.strides[1] = 1;
-  return v;
-}
-fj::View weight_view(const void* base, int dtype, unsigned rows, unsigned width) {
-  fj::View v = dense_view(const_cast<void*>(base), dtype, rows, width, 0);
-  return v;
-}
-
 }  // namespace
+
+namespace fjb {
+void launch_feedback_tokens(fj::Ctx& ctx, const unsigned* cu_seqlens, const unsigned* previous, unsigned* tokens, unsigned lanes) {
+  feedback_tokens_kernel<<<(lanes + 127) / 128, 128, 0, ctx.stream>>>(cu_seqlens, previous, tokens, lanes);
+  ctx.launches++;
+}
+void launch_gather_last_rows(fj::Ctx& ctx, const void* hidden, int dtype, const unsigned* cu_seqlens, void* out, unsigned lanes, unsigned width) {
+  if (dtype == FJ_F32) gather_last_rows_kernel<float><<<std::min(lanes, 1024u), 256, 0, ctx.stream>>>(static_cast<const float*>(hidden), cu_seqlens, static_cast<float*>(out), lanes, width);
+  else gather_last_rows_kernel<unsigned short><<<std::min(lanes, 1024u), 256, 0, ctx.stream>>>(static_cast<const unsigned short*>(hidden), cu_seqlens, static_cast<unsigned short*>(out), lanes, width);
+  ctx.launches++;
+}
+}  // namespace fjb
 
 extern "C" {
 
@@ -412,7 +398,7 @@ int32_t fj_dense_step(fj_dense_model* m, const uint32_t* token_ids, uint32_t* ou
   const unsigned long long launches_before = ctx.launches;
 
   if (token_ids) cudaMemcpyAsync(m->tokens_in, token_ids, static_cast<size_t>(rows) * 4, cudaMemcpyHostToDevice, be->stream);
-  else { feedback_tokens_kernel<<<(lanes + 127) / 128, 128, 0, be->stream>>>(pool->pack.cu_seqlens, m->tokens_out, m->tokens_in, lanes); ctx.launches++; }
+  else launch_feedback_tokens(ctx, pool->pack.cu_seqlens, m->tokens_out, m->tokens_in, lanes);
 
   // attention plan for this step (shared by all layers: q and attn buffers do not move)
   const unsigned group = c.q_heads / c.kv_heads;
@@ -482,9 +468,7 @@ int32_t fj_dense_step(fj_dense_model* m, const uint32_t* token_ids, uint32_t* ou
     std::swap(hidden, other);
   }
   // last row of every lane -> final norm -> tied lm_head -> greedy token
-  if (dt == FJ_F32) gather_last_rows_kernel<float><<<std::min(lanes, 1024u), 256, 0, be->stream>>>(static_cast<const float*>(hidden), pool->pack.cu_seqlens, static_cast<float*>(m->last_hidden), lanes, H);
-  else gather_last_rows_kernel<unsigned short><<<std::min(lanes, 1024u), 256, 0, be->stream>>>(static_cast<const unsigned short*>(hidden), pool->pack.cu_seqlens, static_cast<unsigned short*>(m->last_hidden), lanes, H);
-  ctx.launches++;
+  launch_gather_last_rows(ctx, hidden, dt, pool->pack.cu_seqlens, m->last_hidden, lanes, H);
   fj::launch_rms_norm(ctx, dense_view(m->last_hidden, dt, lanes, H, H), weight_view(m->final_norm, dt, lanes, H), dense_view(m->last_normed, dt, lanes, H, H), lanes, H, c.eps);
   void* logits = m->logits;
   if (logits_out) {

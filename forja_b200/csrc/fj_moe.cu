@@ -1,0 +1,515 @@
+// Device-resident forward step of the sparse-MoE decoder (Qwen3-Coder-30B-A3B shape family) and
+// expert parallelism over several GPUs.
+//
+// Reference op order (engines/qwen3-coder/src/lib.rs:886-947 forward_batch, :505-603 SparseMoe,
+// crates/forja-sdk/src/nn.rs:29-45 moe_router_with):
+//   QuantEmbed(q4) -> RmsNorm -> per layer { QuantMatmul qkv -> qk_norm_rope -> PagedSdpaAppend ->
+//   QuantMatmul o -> residual_norm -> QuantMatmul(q8) router -> TopK{k, normalize} ->
+//   GatherQuantMatmul pair (gate, up) + silu(gate)*up -> GatherQuantMatmul weighted sum (down)
+//   + residual -> rms_norm } -> QuantMatmul lm_head -> Argmax.
+// Activations are bf16 (the reference engine keeps f32 tensors); router logits, routing weights and
+// the per-route down projections stay f32, as the fused epilogues of the reference see them.
+//
+// Expert parallelism (no reference counterpart: the reference is single-GPU). Experts are sharded
+// contiguously, expert e lives on rank e / (experts / world); attention, router and the dense
+// projections are replicated and every rank runs its own lanes. Per MoE layer:
+//   1. route locally; one CTA packs each route's activation row into the slab of the rank that owns
+//      its expert (fixed capacity rows * top_k per peer, so no size has to reach the host);
+//   2. all-to-all of the slabs (NCCL send/recv over NVLink) with the local expert id of every row;
+//   3. the owner runs gate/up/silu and down for the rows it received (f32 results);
+//   4. all-to-all back; the origin adds  residual + sum_j w_j * down_j  in ascending j.
+// Each route's arithmetic is the same kernel code as in the single-GPU path, so both paths give
+// identical bits. Received rows land in local memory before any kernel reads them.
+#include "fj_backend.h"
+
+#include <dlfcn.h>
+#include <string.h>
+
+#include <algorithm>
+
+using namespace fjb;
+
+// ---- NCCL through dlopen: the library keeps no link-time dependency on it ----------------------
+namespace {
+
+struct NcclApi {
+  void* handle = nullptr;
+  int (*GetUniqueId)(void* id) = nullptr;
+  int (*CommInitRank)(void** comm, int nranks, const void* id_by_value_128, int rank) = nullptr;
+  int (*CommDestroy)(void* comm) = nullptr;
+  int (*Send)(const void* buf, size_t count, int dtype, int peer, void* comm, cudaStream_t stream) = nullptr;
+  int (*Recv)(void* buf, size_t count, int dtype, int peer, void* comm, cudaStream_t stream) = nullptr;
+  int (*GroupStart)() = nullptr;
+  int (*GroupEnd)() = nullptr;
+};
+NcclApi g_nccl;
+std::mutex g_nccl_mutex;
+
+// ncclUniqueId is a 128-byte struct passed by value to ncclCommInitRank.
+struct UniqueId { char bytes[128]; };
+using CommInitRankFn = int (*)(void** comm, int nranks, UniqueId id, int rank);
+constexpr int kNcclInt8 = 0;  // ncclInt8 / ncclChar
+
+}  // namespace
+
+struct fj_ep {
+  fj_backend* be = nullptr;
+  void* comm = nullptr;
+  uint32_t rank = 0, world = 1;
+};
+
+extern "C" {
+
+int32_t fj_ep_load(const char* libnccl_path) {
+  std::lock_guard<std::mutex> lock(g_nccl_mutex);
+  if (g_nccl.handle) return FJ_OK;
+  void* h = dlopen(libnccl_path && libnccl_path[0] ? libnccl_path : "libnccl.so.2", RTLD_NOW | RTLD_GLOBAL);
+  if (!h) return FJ_UNSUPPORTED_OPERATION;
+  NcclApi api;
+  api.handle = h;
+  api.GetUniqueId = reinterpret_cast<int (*)(void*)>(dlsym(h, "ncclGetUniqueId"));
+  api.CommInitRank = reinterpret_cast<int (*)(void**, int, const void*, int)>(dlsym(h, "ncclCommInitRank"));
+  api.CommDestroy = reinterpret_cast<int (*)(void*)>(dlsym(h, "ncclCommDestroy"));
+  api.Send = reinterpret_cast<int (*)(const void*, size_t, int, int, void*, cudaStream_t)>(dlsym(h, "ncclSend"));
+  api.Recv = reinterpret_cast<int (*)(void*, size_t, int, int, void*, cudaStream_t)>(dlsym(h, "ncclRecv"));
+  api.GroupStart = reinterpret_cast<int (*)()>(dlsym(h, "ncclGroupStart"));
+  api.GroupEnd = reinterpret_cast<int (*)()>(dlsym(h, "ncclGroupEnd"));
+  if (!api.GetUniqueId || !api.CommInitRank || !api.CommDestroy || !api.Send || !api.Recv || !api.GroupStart || !api.GroupEnd) { dlclose(h); return FJ_UNSUPPORTED_OPERATION; }
+  g_nccl = api;
+  return FJ_OK;
+}
+
+int32_t fj_ep_unique_id(uint8_t* out128) {
+  if (!out128 || !g_nccl.handle) return FJ_INVALID_INPUT;
+  UniqueId id;
+  memset(&id, 0, sizeof(id));
+  if (g_nccl.GetUniqueId(&id) != 0) return FJ_DEVICE_EXECUTION_FAILED;
+  memcpy(out128, id.bytes, 128);
+  return FJ_OK;
+}
+
+int32_t fj_ep_create(fj_backend* be, const uint8_t* id128, uint32_t rank, uint32_t world, fj_ep** out) {
+  if (!be || !id128 || !out || world == 0 || rank >= world || !g_nccl.handle) return FJ_INVALID_INPUT;
+  std::lock_guard<std::mutex> lock(be->mutex);
+  cudaSetDevice(be->device);
+  UniqueId id;
+  memcpy(id.bytes, id128, 128);
+  void* comm = nullptr;
+  if (reinterpret_cast<CommInitRankFn>(g_nccl.CommInitRank)(&comm, static_cast<int>(world), id, static_cast<int>(rank)) != 0) return FJ_DEVICE_EXECUTION_FAILED;
+  auto* ep = new fj_ep();
+  ep->be = be; ep->comm = comm; ep->rank = rank; ep->world = world;
+  *out = ep;
+  return FJ_OK;
+}
+
+void fj_ep_destroy(fj_ep* ep) {
+  if (!ep) return;
+  {
+    std::lock_guard<std::mutex> lock(ep->be->mutex);
+    cudaSetDevice(ep->be->device);
+    cudaStreamSynchronize(ep->be->stream);
+    if (ep->comm) g_nccl.CommDestroy(ep->comm);
+  }
+  delete ep;
+}
+
+}  // extern "C"
+
+namespace {
+
+// Every rank sends bytes_per_peer to each peer and receives as much from each, on the backend's
+// stream; the block for the rank itself is a device copy. Caller holds the backend mutex.
+int32_t ep_all_to_all(fj_ep* ep, const void* send, void* recv, size_t bytes_per_peer) {
+  cudaStream_t stream = ep->be->stream;
+  if (g_nccl.GroupStart() != 0) return FJ_DEVICE_EXECUTION_FAILED;
+  int failed = 0;
+  for (uint32_t peer = 0; peer < ep->world; ++peer) {
+    const char* s = static_cast<const char*>(send) + static_cast<size_t>(peer) * bytes_per_peer;
+    char* r = static_cast<char*>(recv) + static_cast<size_t>(peer) * bytes_per_peer;
+    if (peer == ep->rank) { cudaMemcpyAsync(r, s, bytes_per_peer, cudaMemcpyDeviceToDevice, stream); continue; }
+    failed |= g_nccl.Send(s, bytes_per_peer, kNcclInt8, static_cast<int>(peer), ep->comm, stream);
+    failed |= g_nccl.Recv(r, bytes_per_peer, kNcclInt8, static_cast<int>(peer), ep->comm, stream);
+  }
+  if (g_nccl.GroupEnd() != 0 || failed) return FJ_DEVICE_EXECUTION_FAILED;
+  return FJ_OK;
+}
+
+// ---- expert-parallel dispatch / combine kernels -------------------------------------------------
+// One thread walks the routes in (row, j) order and hands each the next slot of its destination's slab,
+// so slot numbers are deterministic. Unused slots keep expert id `experts_local` (out of range: the
+// expert kernels write zeros for them without touching any weight).
+__global__ void ep_plan_kernel(const unsigned* __restrict__ indices, unsigned routes, unsigned experts_local, unsigned world, unsigned capacity,
+                               unsigned* send_experts, unsigned* route_slot) {
+  extern __shared__ unsigned ep_smem[];
+  unsigned* next = ep_smem;  // [world] running slot per destination
+  for (unsigned i = threadIdx.x; i < world; i += blockDim.x) next[i] = 0;
+  for (unsigned i = threadIdx.x; i < world * capacity; i += blockDim.x) send_experts[i] = experts_local;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (unsigned r = 0; r < routes; ++r) {
+      const unsigned expert = indices[r];
+      const unsigned dest = expert / experts_local;
+      if (dest >= world) { route_slot[r] = 0xFFFFFFFFu; continue; }  // bad expert id: contributes nothing
+      const unsigned slot = dest * capacity + next[dest]++;
+      route_slot[r] = slot;
+      send_experts[slot] = expert - dest * experts_local;
+    }
+  }
+}
+
+// Copies each route's activation row (bf16, width % 8 == 0) into its slot, 16 bytes per thread step.
+__global__ void ep_scatter_rows_kernel(const unsigned short* __restrict__ normed, const unsigned* __restrict__ route_slot, unsigned routes, unsigned top_k,
+                                       unsigned width, unsigned short* send_rows) {
+  const unsigned vecs = width / 8;
+  for (unsigned r = blockIdx.x; r < routes; r += gridDim.x) {
+    const unsigned slot = route_slot[r];
+    if (slot == 0xFFFFFFFFu) continue;
+    const uint4* src = reinterpret_cast<const uint4*>(normed + static_cast<size_t>(r / top_k) * width);
+    uint4* dst = reinterpret_cast<uint4*>(send_rows + static_cast<size_t>(slot) * width);
+    for (unsigned i = threadIdx.x; i < vecs; i += blockDim.x) dst[i] = src[i];
+  }
+}
+
+// out[row] = bf16(residual[row] + sum_j weights[row, j] * returned[route_slot[row, j]]), j ascending,
+// f32 accumulation: the arithmetic of the fused weighted-sum projection.
+__global__ void ep_combine_kernel(const float* __restrict__ returned, const unsigned* __restrict__ route_slot, const float* __restrict__ weights,
+                                  const unsigned short* __restrict__ residual, unsigned short* out, unsigned rows, unsigned top_k, unsigned width) {
+  for (unsigned row = blockIdx.x; row < rows; row += gridDim.x) {
+    for (unsigned c = threadIdx.x; c < width; c += blockDim.x) {
+      float total = 0.0f;
+      for (unsigned j = 0; j < top_k; ++j) {
+        const unsigned slot = route_slot[row * top_k + j];
+        if (slot == 0xFFFFFFFFu) continue;
+        total = __fadd_rn(total, __fmul_rn(weights[row * top_k + j], returned[static_cast<size_t>(slot) * width + c]));
+      }
+      const size_t o = static_cast<size_t>(row) * width + c;
+      total = total + fj::load_as_f32(residual, fj::BF16, o);
+      fj::store_from_f32(out, fj::BF16, o, total);
+    }
+  }
+}
+
+}  // namespace
+
+// ---- the model ------------------------------------------------------------------------------------
+namespace {
+struct QuantW {
+  const unsigned* packed = nullptr;
+  const void* scales = nullptr;
+  const void* biases = nullptr;
+};
+}  // namespace
+
+struct fj_moe_model {
+  fj_backend* be = nullptr;
+  fj_kvpool* pool = nullptr;
+  fj_ep* ep = nullptr;
+  fj_moe_config cfg{};
+  uint32_t experts_local = 0, world = 1, capacity = 0;
+  QuantW embed, lm_head;
+  const void* final_norm = nullptr;
+  struct Layer {
+    const void *input_norm, *q_norm, *k_norm, *post_norm;
+    QuantW qkv, o, router, gate, up, down;
+    void *k_plane, *v_plane;
+  };
+  std::vector<Layer> layers;
+  std::vector<void*> owned;
+  // workspace (bf16 unless noted)
+  void *hidden = nullptr, *hidden2 = nullptr, *normed = nullptr, *qkv = nullptr, *q = nullptr, *attn = nullptr, *proj = nullptr, *act = nullptr;
+  float *router_logits = nullptr, *route_weights = nullptr;
+  unsigned* route_experts = nullptr;
+  void *last_hidden = nullptr, *last_normed = nullptr, *logits = nullptr, *argmax_scratch = nullptr, *dequant = nullptr;
+  size_t dequant_bytes = 0;
+  unsigned *tokens_in = nullptr, *tokens_out = nullptr;
+  // expert parallelism: slabs of `capacity` slots per peer
+  unsigned short *send_rows = nullptr, *recv_rows = nullptr, *act_ep = nullptr;
+  unsigned *send_experts = nullptr, *recv_experts = nullptr, *route_slot = nullptr;
+  float *down_ep = nullptr, *returned = nullptr;
+  fj::AttnSeq* seqs = nullptr;
+  fj::AttnWork* work = nullptr;
+  unsigned* n_work_dev = nullptr;
+  uint32_t work_cap = 0;
+  const float* inv_freq = nullptr;
+  uint64_t last_kernels = 0, last_work_items = 0;
+};
+
+extern "C" {
+
+int32_t fj_ep_all_to_all(fj_ep* ep, uint64_t send, uint64_t recv, uint64_t bytes_per_peer) {
+  if (!ep) return FJ_INVALID_INPUT;
+  fj_backend* be = ep->be;
+  std::lock_guard<std::mutex> lock(be->mutex);
+  cudaSetDevice(be->device);
+  fj_buffer_rec *s = find_buffer(be, send), *r = find_buffer(be, recv);
+  const uint64_t total = bytes_per_peer * ep->world;
+  if (!s || !r || r->readonly || s->bytes < total || r->bytes < total || s == r) return FJ_INVALID_INPUT;
+  return ep_all_to_all(ep, s->ptr, r->ptr, bytes_per_peer);
+}
+
+int32_t fj_moe_model_create(fj_backend* be, const fj_moe_config* config, const fj_quant_weight* embed, uint64_t final_norm, const fj_quant_weight* lm_head,
+                            const fj_moe_layer_weights* layers, fj_kvpool* pool, fj_ep* ep, fj_moe_model** out) {
+  if (!be || !config || !embed || !lm_head || !layers || !pool || !out || pool->be != be || (ep && ep->be != be)) return FJ_INVALID_INPUT;
+  const fj_moe_config& c = *config;
+  const uint32_t world = ep ? ep->world : 1;
+  if (c.layers == 0 || c.kv_heads == 0 || c.q_heads % c.kv_heads != 0 || c.head_dim % 2 != 0 || c.head_dim > 256 || c.max_rows == 0 || c.hidden % 8 != 0 || c.vocab == 0 ||
+      c.experts == 0 || c.experts % world != 0 || c.top_k == 0 || c.top_k > c.experts || c.expert_intermediate == 0 || (c.group_size != 32 && c.group_size != 64 && c.group_size != 128) ||
+      (c.router_bits != 4 && c.router_bits != 8) || c.hidden % c.group_size != 0 || c.expert_intermediate % c.group_size != 0 || (c.q_heads * c.head_dim) % c.group_size != 0)
+    return FJ_INVALID_INPUT;
+  std::lock_guard<std::mutex> lock(be->mutex);
+  cudaSetDevice(be->device);
+  auto* m = new fj_moe_model();
+  m->be = be; m->pool = pool; m->ep = ep; m->cfg = c; m->world = world;
+  m->experts_local = c.experts / world;
+  m->capacity = c.max_rows * c.top_k;
+  bool ok = true;
+  auto dev_alloc = [&](size_t bytes) -> void* {
+    void* p = nullptr;
+    if (!ok) return nullptr;
+    if (be->limit_bytes && be->used_bytes + bytes > be->limit_bytes) { ok = false; return nullptr; }
+    if (cudaMalloc(&p, std::max<size_t>(bytes, 16)) != cudaSuccess) { cudaGetLastError(); ok = false; return nullptr; }
+    cudaMemsetAsync(p, 0, std::max<size_t>(bytes, 16), be->stream);
+    be->used_bytes += bytes;
+    m->owned.push_back(p);
+    return p;
+  };
+  auto vec = [&](uint64_t id, uint64_t elements) -> const void* {
+    fj_buffer_rec* r = find_buffer(be, id);
+    if (!r || r->bytes < elements * 2) { ok = false; return nullptr; }
+    return r->ptr;
+  };
+  // a quantised tensor of `count` stacked [n, k] matrices
+  auto quant = [&](const fj_quant_weight& w, uint64_t count, uint64_t n, uint64_t k, uint32_t bits) -> QuantW {
+    QuantW q;
+    fj_buffer_rec *p = find_buffer(be, w.packed), *s = find_buffer(be, w.scales), *b = find_buffer(be, w.biases);
+    const uint64_t groups = count * n * (k / c.group_size);
+    if (!p || !s || !b || p->bytes < count * n * (k * bits / 32) * 4 || s->bytes < groups * 2 || b->bytes < groups * 2) { ok = false; return q; }
+    q.packed = static_cast<const unsigned*>(p->ptr); q.scales = s->ptr; q.biases = b->ptr;
+    return q;
+  };
+  const uint64_t H = c.hidden, I = c.expert_intermediate, qd = static_cast<uint64_t>(c.q_heads) * c.head_dim, kd = static_cast<uint64_t>(c.kv_heads) * c.head_dim;
+  m->embed = quant(*embed, 1, c.vocab, H, 4);
+  m->lm_head = quant(*lm_head, 1, c.vocab, H, 4);
+  m->final_norm = vec(final_norm, H);
+  const size_t plane_bytes = static_cast<size_t>(pool->dev.physical_pages) * pool->dev.page_tokens * kd * 2;
+  m->layers.resize(c.layers);
+  for (uint32_t l = 0; l < c.layers && ok; ++l) {
+    const fj_moe_layer_weights& w = layers[l];
+    auto& L = m->layers[l];
+    L.input_norm = vec(w.input_norm, H);
+    L.post_norm = vec(w.post_norm, H);
+    L.q_norm = vec(w.q_norm, c.head_dim);
+    L.k_norm = vec(w.k_norm, c.head_dim);
+    L.qkv = quant(w.qkv, 1, qd + 2 * kd, H, 4);
+    L.o = quant(w.o, 1, H, qd, 4);
+    L.router = quant(w.router, 1, c.experts, H, c.router_bits);
+    L.gate = quant(w.gate, m->experts_local, I, H, 4);
+    L.up = quant(w.up, m->experts_local, I, H, 4);
+    L.down = quant(w.down, m->experts_local, H, I, 4);
+    L.k_plane = dev_alloc(plane_bytes);
+    L.v_plane = dev_alloc(plane_bytes);
+  }
+  const size_t R = c.max_rows, Lanes = pool->dev.lanes, K = c.top_k;
+  m->hidden = dev_alloc(R * H * 2);
+  m->hidden2 = dev_alloc(R * H * 2);
+  m->normed = dev_alloc(R * H * 2);
+  m->qkv = dev_alloc(R * (qd + 2 * kd) * 2);
+  m->q = dev_alloc(R * qd * 2);
+  m->attn = dev_alloc(R * qd * 2);
+  m->proj = dev_alloc(R * H * 2);
+  m->act = dev_alloc(R * K * I * 2);
+  m->router_logits = static_cast<float*>(dev_alloc(R * c.experts * 4));
+  m->route_weights = static_cast<float*>(dev_alloc(R * K * 4));
+  m->route_experts = static_cast<unsigned*>(dev_alloc(R * K * 4));
+  m->last_hidden = dev_alloc(Lanes * H * 2);
+  m->last_normed = dev_alloc(Lanes * H * 2);
+  m->logits = dev_alloc(Lanes * c.vocab * 2);
+  m->argmax_scratch = dev_alloc(fj::argmax_scratch_bytes(static_cast<unsigned>(Lanes), c.vocab));
+  m->tokens_in = static_cast<unsigned*>(dev_alloc(R * 4));
+  m->tokens_out = static_cast<unsigned*>(dev_alloc(Lanes * 4));
+  m->seqs = static_cast<fj::AttnSeq*>(dev_alloc(Lanes * sizeof(fj::AttnSeq)));
+  const uint64_t token_capacity = static_cast<uint64_t>(pool->dev.physical_pages) * pool->dev.page_tokens;
+  m->work_cap = static_cast<uint32_t>(std::min<uint64_t>((token_capacity / 64 + Lanes) * c.kv_heads, 1u << 22));
+  m->work = static_cast<fj::AttnWork*>(dev_alloc(static_cast<size_t>(m->work_cap) * sizeof(fj::AttnWork)));
+  m->n_work_dev = static_cast<unsigned*>(dev_alloc(16));
+  if (std::max(R, Lanes) > 16) {
+    // slab of dequantised weights for projections with more than 16 rows (tensor-core GEMM path)
+    const uint64_t widest = std::max<uint64_t>({qd + 2 * kd, H, static_cast<uint64_t>(c.vocab)});
+    m->dequant_bytes = static_cast<size_t>(std::min<uint64_t>(widest * std::max<uint64_t>(H, qd) * 2, uint64_t(64) << 20));
+    m->dequant = dev_alloc(m->dequant_bytes);
+  }
+  if (world > 1) {
+    const size_t slots = static_cast<size_t>(world) * m->capacity;
+    m->send_rows = static_cast<unsigned short*>(dev_alloc(slots * H * 2));
+    m->recv_rows = static_cast<unsigned short*>(dev_alloc(slots * H * 2));
+    m->act_ep = static_cast<unsigned short*>(dev_alloc(slots * I * 2));
+    m->send_experts = static_cast<unsigned*>(dev_alloc(slots * 4));
+    m->recv_experts = static_cast<unsigned*>(dev_alloc(slots * 4));
+    m->route_slot = static_cast<unsigned*>(dev_alloc(R * K * 4));
+    m->down_ep = static_cast<float*>(dev_alloc(slots * H * 4));
+    m->returned = static_cast<float*>(dev_alloc(slots * H * 4));
+  }
+  if (ok) {
+    m->inv_freq = freq_table(be, c.theta, -2.0f / static_cast<float>(c.head_dim), c.head_dim / 2, false);
+    ok = m->inv_freq != nullptr;
+  }
+  if (ok) ok = ensure_gemm_scratch(be, fj::gemm_scratch_bytes(static_cast<unsigned>(std::max(R, Lanes)), static_cast<unsigned>(std::max<uint64_t>(qd + 2 * kd, H)), static_cast<unsigned>(std::max<uint64_t>(H, qd))));
+  if (!ok || cudaStreamSynchronize(be->stream) != cudaSuccess) {
+    for (void* p : m->owned) { cudaFree(p); }
+    delete m;
+    return ok ? FJ_ALLOCATION_FAILED : FJ_INVALID_INPUT;
+  }
+  *out = m;
+  return FJ_OK;
+}
+
+void fj_moe_model_destroy(fj_moe_model* m) {
+  if (!m) return;
+  std::lock_guard<std::mutex> lock(m->be->mutex);
+  cudaSetDevice(m->be->device);
+  cudaStreamSynchronize(m->be->stream);
+  for (void* p : m->owned) cudaFree(p);
+  delete m;
+}
+
+int32_t fj_moe_step_stats(fj_moe_model* m, uint64_t* kernels, uint64_t* attn_work_items) {
+  if (!m) return FJ_INVALID_INPUT;
+  if (kernels) *kernels = m->last_kernels;
+  if (attn_work_items) *attn_work_items = m->last_work_items;
+  return FJ_OK;
+}
+
+}  // extern "C"
+
+extern "C" int32_t fj_moe_step(fj_moe_model* m, const uint32_t* token_ids, uint32_t* out_tokens, uint64_t logits_out) {
+  if (!m) return FJ_INVALID_INPUT;
+  fj_backend* be = m->be;
+  fj_kvpool* pool = m->pool;
+  std::lock_guard<std::mutex> lock(be->mutex);
+  cudaSetDevice(be->device);
+  const fj_moe_config& c = m->cfg;
+  const unsigned rows = pool->rows, lanes = pool->lanes_packed;
+  if (lanes == 0 || rows > c.max_rows) return FJ_INVALID_INPUT;
+  if (rows == 0 && m->world == 1) return FJ_INVALID_INPUT;
+  const int dt = FJ_BF16;
+  const unsigned qd = c.q_heads * c.head_dim, kd = c.kv_heads * c.head_dim, H = c.hidden, I = c.expert_intermediate, K = c.top_k, G = c.group_size;
+  fj::Ctx& ctx = be->ctx;
+  const unsigned long long launches_before = ctx.launches;
+  auto q4 = [&](const void* x, const QuantW& w, void* out, int out_dt, unsigned m_rows, unsigned k, unsigned n, unsigned bits) {
+    fj::launch_quant_matmul(ctx, x, dt, w.packed, w.scales, w.biases, dt, out, out_dt, m_rows, k, n, bits, G, m_rows > 16 ? m->dequant : nullptr,
+                            m_rows > 16 ? m->dequant_bytes : 0, be->gemm_scratch, be->gemm_scratch_bytes);
+  };
+
+  // attention plan for this step (shared by all layers)
+  const unsigned group = c.q_heads / c.kv_heads;
+  unsigned max_q_len = 0;
+  uint64_t total_keys = 0;
+  for (unsigned l = 0; l < lanes; ++l) {
+    max_q_len = std::max(max_q_len, pool->host_tokens[l]);
+    if (pool->host_tokens[l]) total_keys += static_cast<uint64_t>(pool->host_starts[l]) + pool->host_tokens[l];
+  }
+  fj::AttnGeometry g;
+  g.q_heads = c.q_heads; g.kv_heads = c.kv_heads; g.head_dim = c.head_dim; g.value_dim = c.head_dim; g.page_tokens = pool->dev.page_tokens;
+  g.physical_pages = pool->dev.physical_pages; g.q_dtype = dt; g.kv_dtype = dt; g.out_dtype = dt;
+  g.scale = 1.0f / sqrtf(static_cast<float>(c.head_dim));
+  const bool mma = rows != 0 && fj::attn_decode_mma_supported(g, max_q_len) && max_q_len * group <= 16;
+  uint64_t chunk = 64, n_work = 0;
+  fj::AttnScratch scratch{nullptr, nullptr, nullptr};
+  if (rows != 0) {
+    if (mma) {
+      const uint64_t target_items = static_cast<uint64_t>(ctx.sm_count) * 2 * 4;
+      chunk = (total_keys * c.kv_heads + target_items - 1) / std::max<uint64_t>(target_items, 1);
+      chunk = std::min<uint64_t>(std::max<uint64_t>((chunk + 63) / 64 * 64, 64), 1024);
+      for (unsigned l = 0; l < lanes; ++l)
+        if (pool->host_tokens[l]) n_work += ((static_cast<uint64_t>(pool->host_starts[l]) + pool->host_tokens[l] + chunk - 1) / chunk) * c.kv_heads;
+      if (n_work > m->work_cap) return FJ_QUOTA_EXCEEDED;
+    }
+    fj::launch_build_attn_lists(ctx, pool->dev, pool->pack, lanes, c.kv_heads, static_cast<unsigned>(chunk), m->q, m->attn, c.q_heads, c.head_dim, 2, m->seqs, m->work,
+                                m->n_work_dev, m->work_cap);
+    if (mma) {
+      const size_t groups = static_cast<size_t>(lanes) * c.kv_heads;
+      const size_t counter_bytes = (groups * sizeof(unsigned) + 255) / 256 * 256;
+      const size_t o_bytes = fj::attn_part_o_bytes(static_cast<unsigned>(n_work), c.head_dim), ml_bytes = fj::attn_part_ml_bytes(static_cast<unsigned>(n_work));
+      if (!ensure_attn_scratch(be, counter_bytes + o_bytes + ml_bytes)) return FJ_ALLOCATION_FAILED;
+      scratch.counters = static_cast<unsigned*>(be->attn_scratch);
+      scratch.part_o = reinterpret_cast<float*>(static_cast<char*>(be->attn_scratch) + counter_bytes);
+      scratch.part_ml = reinterpret_cast<float*>(static_cast<char*>(be->attn_scratch) + counter_bytes + o_bytes);
+    }
+    if (token_ids) cudaMemcpyAsync(m->tokens_in, token_ids, static_cast<size_t>(rows) * 4, cudaMemcpyHostToDevice, be->stream);
+    else launch_feedback_tokens(ctx, pool->pack.cu_seqlens, m->tokens_out, m->tokens_in, lanes);
+    fj::launch_quant_embed(ctx, m->embed.packed, m->embed.scales, m->embed.biases, dt, m->tokens_in, m->hidden, dt, c.vocab, H / 8, rows, 4, G, nullptr);
+    fj::launch_rms_norm(ctx, dense_view(m->hidden, dt, rows, H, H), weight_view(m->layers[0].input_norm, dt, rows, H), dense_view(m->normed, dt, rows, H, H), rows, H, c.eps);
+  }
+  void* hidden = m->hidden;
+  void* other = m->hidden2;
+  const unsigned plane_slots = pool->dev.physical_pages * pool->dev.page_tokens;
+  int32_t status = FJ_OK;
+  for (uint32_t l = 0; l < c.layers && status == FJ_OK; ++l) {
+    const auto& L = m->layers[l];
+    if (rows != 0) {
+      q4(m->normed, L.qkv, m->qkv, dt, rows, H, qd + 2 * kd, 4);
+      fj::launch_qknorm_rope_append(ctx, m->qkv, dt, L.q_norm, L.k_norm, pool->pack.positions, pool->pack.slot_mapping, m->q, L.k_plane, L.v_plane, rows, c.q_heads, c.kv_heads,
+                                    c.head_dim, c.eps, m->inv_freq, 1, plane_slots);
+      if (mma) fj::launch_attn_decode_mma(ctx, g, m->seqs, m->work, static_cast<unsigned>(n_work), L.k_plane, L.v_plane, pool->dev.generations, scratch, nullptr);
+      else fj::launch_attn_generic(ctx, g, m->seqs, lanes, max_q_len, L.k_plane, L.v_plane, pool->dev.generations, nullptr);
+      q4(m->attn, L.o, m->proj, dt, rows, qd, H, 4);
+      fj::launch_residual_norm(ctx, dense_view(hidden, dt, rows, H, H), dense_view(m->proj, dt, rows, H, H), weight_view(L.post_norm, dt, rows, H), dense_view(other, dt, rows, H, H),
+                               dense_view(m->normed, dt, rows, H, H), rows, H, c.eps, 0);
+      std::swap(hidden, other);  // `hidden` is now the post-attention residual stream
+      q4(m->normed, L.router, m->router_logits, FJ_F32, rows, H, c.experts, c.router_bits);
+      fj::launch_top_k(ctx, m->router_logits, FJ_F32, m->route_weights, FJ_F32, m->route_experts, rows, c.experts, K, true);
+    }
+    if (m->world == 1) {
+      fj::launch_gather_quant_matmul(ctx, m->normed, dt, L.gate.packed, L.gate.scales, L.gate.biases, dt, L.up.packed, L.up.scales, L.up.biases, m->route_experts, m->act, dt, rows, H,
+                                     c.experts, I, K, 4, G, 1, nullptr);
+      fj::launch_gather_quant_weighted_sum(ctx, m->act, dt, L.down.packed, L.down.scales, L.down.biases, dt, m->route_experts, m->route_weights, FJ_F32, hidden, dt, other, dt, rows, K,
+                                           I, c.experts, H, 4, G, 2, nullptr);
+    } else {
+      const unsigned cap = m->capacity, slots = m->world * cap, routes = rows * K;
+      ep_plan_kernel<<<1, 256, m->world * sizeof(unsigned), be->stream>>>(m->route_experts, routes, m->experts_local, m->world, cap, m->send_experts, m->route_slot);
+      ctx.launches++;
+      if (routes) { ep_scatter_rows_kernel<<<std::min(routes, 4096u), 128, 0, be->stream>>>(static_cast<const unsigned short*>(m->normed), m->route_slot, routes, K, H, m->send_rows); ctx.launches++; }
+      status = ep_all_to_all(m->ep, m->send_rows, m->recv_rows, static_cast<size_t>(cap) * H * 2);
+      if (status == FJ_OK) status = ep_all_to_all(m->ep, m->send_experts, m->recv_experts, static_cast<size_t>(cap) * 4);
+      if (status != FJ_OK) break;
+      // rows received for this rank's experts: one route each, expert id per slot (padding: out of range -> zeros)
+      fj::launch_gather_quant_matmul(ctx, m->recv_rows, dt, L.gate.packed, L.gate.scales, L.gate.biases, dt, L.up.packed, L.up.scales, L.up.biases, m->recv_experts, m->act_ep, dt, slots, H,
+                                     m->experts_local, I, 1, 4, G, 1, nullptr);
+      fj::launch_gather_quant_matmul(ctx, m->act_ep, dt, L.down.packed, L.down.scales, L.down.biases, dt, nullptr, nullptr, nullptr, m->recv_experts, m->down_ep, FJ_F32, slots, I,
+                                     m->experts_local, H, 1, 4, G, 0, nullptr);
+      status = ep_all_to_all(m->ep, m->down_ep, m->returned, static_cast<size_t>(cap) * H * 4);
+      if (status != FJ_OK) break;
+      if (rows) {
+        ep_combine_kernel<<<std::min(rows, 1024u), 256, 0, be->stream>>>(m->returned, m->route_slot, m->route_weights, static_cast<const unsigned short*>(hidden),
+                                                                         static_cast<unsigned short*>(other), rows, K, H);
+        ctx.launches++;
+      }
+    }
+    std::swap(hidden, other);
+    if (rows != 0) {
+      const void* next_norm = l + 1 < c.layers ? m->layers[l + 1].input_norm : m->final_norm;
+      fj::launch_rms_norm(ctx, dense_view(hidden, dt, rows, H, H), weight_view(next_norm, dt, rows, H), dense_view(m->normed, dt, rows, H, H), rows, H, c.eps);
+    }
+  }
+  if (status != FJ_OK) { cudaStreamSynchronize(be->stream); return status; }
+  if (rows != 0) {
+    // the final norm ran on every row; the greedy token comes from each lane's last row
+    launch_gather_last_rows(ctx, m->normed, dt, pool->pack.cu_seqlens, m->last_normed, lanes, H);
+    void* logits = m->logits;
+    if (logits_out) {
+      fj_buffer_rec* r = find_buffer(be, logits_out);
+      if (!r || r->readonly || r->bytes < static_cast<uint64_t>(lanes) * c.vocab * 2) return FJ_INVALID_INPUT;
+      logits = r->ptr;
+    }
+    q4(m->last_normed, m->lm_head, logits, dt, lanes, H, c.vocab, 4);
+    fj::launch_argmax(ctx, logits, dt, c.vocab, m->tokens_out, lanes, c.vocab, m->argmax_scratch);
+  }
+  m->last_kernels = ctx.launches - launches_before;
+  m->last_work_items = n_work;
+  if (cudaGetLastError() != cudaSuccess) return FJ_DEVICE_EXECUTION_FAILED;
+  if (out_tokens && rows != 0) {
+    cudaMemcpyAsync(out_tokens, m->tokens_out, static_cast<size_t>(lanes) * 4, cudaMemcpyDeviceToHost, be->stream);
+    return cuda_status(cudaStreamSynchronize(be->stream));
+  }
+  return FJ_OK;
+}

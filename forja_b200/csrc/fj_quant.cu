@@ -723,7 +723,7 @@ __global__ void __launch_bounds__(256) gather_weighted_kernel(QuantArgs a, const
 #pragma unroll
     for (int r = 0; r < QM; ++r) acc[r] = 0.0f;
     quant_column<BITS>(a, route * a.x_row_stride, 1, packed_base, group_base, col, lane, acc);
-    total += load_as_f32(weights, w_dt, route) * acc[0];
+    total = __fadd_rn(total, __fmul_rn(load_as_f32(weights, w_dt, route), acc[0]));  // product rounded, then added (lib.rs:1153-1199)
   }
   if (lane == 0) {
     const size_t o = static_cast<size_t>(row) * a.n + col;

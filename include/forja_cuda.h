@@ -340,6 +340,55 @@ int32_t fj_paged_decode_attention_static(fj_backend* be, const void* q, void* ou
                                          uint32_t lanes, uint32_t table_pages, uint32_t physical_pages, uint32_t q_heads,
                                          uint32_t kv_heads, uint32_t dtype, float scale, uint32_t* status);
 
+/* Expert parallelism over the GPUs of one node. The reference is single-GPU, so these entry points
+ * have no counterpart there; they carry the all-to-all of the sparse-MoE step below. NCCL is opened
+ * at run time (path of libnccl.so.2, or NULL for the loader's search path); one rank creates the
+ * 128-byte id, every rank of the group passes the same id to the create call. */
+typedef struct fj_ep fj_ep;
+int32_t fj_ep_load(const char* libnccl_path);
+int32_t fj_ep_unique_id(uint8_t* out128);
+int32_t fj_ep_create(fj_backend* be, const uint8_t* id128, uint32_t rank, uint32_t world, fj_ep** out);
+void fj_ep_destroy(fj_ep* ep);
+/* Every rank sends bytes_per_peer bytes of `send` to each rank and receives as many from each into
+ * `recv` (buffer ids; world * bytes_per_peer bytes each), ordered on the backend's stream. */
+int32_t fj_ep_all_to_all(fj_ep* ep, uint64_t send, uint64_t recv, uint64_t bytes_per_peer);
+
+/* Sparse-MoE decoder (Qwen3-Coder-30B-A3B shape family; reference op order:
+ * engines/qwen3-coder/src/lib.rs:886-947 forward_batch, :505-603 SparseMoe::route / forward_decode,
+ * crates/forja-sdk/src/nn.rs:29-45 moe_router_with). All projections are MLX affine-quantised
+ * (packed u32 [N, K * bits / 32], scales and biases bf16 [N, K / group]): q4 everywhere except the
+ * router (router_bits, 8 in the reference). Expert tensors are stacked [experts_local, N, ...].
+ * Activations and KV are bf16; router logits, routing weights and per-route down projections f32.
+ * With an fj_ep the experts are sharded: this rank holds experts
+ * [rank * experts / world, (rank + 1) * experts / world) and runs its own lanes. */
+typedef struct fj_quant_weight {
+  uint64_t packed, scales, biases; /* buffer ids */
+} fj_quant_weight;
+typedef struct fj_moe_config {
+  uint32_t layers, hidden, q_heads, kv_heads, head_dim, experts, top_k, expert_intermediate, vocab;
+  uint32_t group_size, router_bits;
+  float eps, theta;
+  uint32_t max_rows; /* largest number of token rows in one step */
+} fj_moe_config;
+typedef struct fj_moe_layer_weights {
+  uint64_t input_norm, q_norm, k_norm, post_norm; /* bf16 [hidden], [head_dim], [head_dim], [hidden] */
+  fj_quant_weight qkv;                            /* [(q_heads + 2 kv_heads) * head_dim, hidden] */
+  fj_quant_weight o;                              /* [hidden, q_heads * head_dim] */
+  fj_quant_weight router;                         /* [experts, hidden], router_bits */
+  fj_quant_weight gate, up;                       /* [experts_local, expert_intermediate, hidden] */
+  fj_quant_weight down;                           /* [experts_local, hidden, expert_intermediate] */
+} fj_moe_layer_weights;
+typedef struct fj_moe_model fj_moe_model;
+int32_t fj_moe_model_create(fj_backend* be, const fj_moe_config* config, const fj_quant_weight* embed, uint64_t final_norm,
+                            const fj_quant_weight* lm_head, const fj_moe_layer_weights* layers, fj_kvpool* pool, fj_ep* ep,
+                            fj_moe_model** out);
+void fj_moe_model_destroy(fj_moe_model* model);
+/* One forward step over the lanes packed by the last fj_pack_step; arguments as fj_dense_step
+ * (logits_out, when nonzero, receives [lanes, vocab] bf16). Under expert parallelism every rank of
+ * the group must call it for the same step, even with no active lane of its own (pack zero tokens). */
+int32_t fj_moe_step(fj_moe_model* model, const uint32_t* token_ids, uint32_t* out_tokens, uint64_t logits_out);
+int32_t fj_moe_step_stats(fj_moe_model* model, uint64_t* kernels, uint64_t* attn_work_items);
+
 #ifdef __cplusplus
 }
 #endif

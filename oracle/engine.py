@@ -103,3 +103,138 @@ class DenseOracle:
         logits = self._linear(final, self.w["embed"])
         token = int(fjo.argmax(logits, dt)[0])
         return fjo.decode(logits, dt)[0], token
+
+
+def random_moe_weights(cfg: dict, seed: int = 0):
+    """Random MLX-affine weights for the sparse-MoE decoder: uniformly random codes, positive scales
+    and biases that centre every group near zero. Returns numpy arrays: quantised tensors as
+    (packed u32, scales bf16 bits, biases bf16 bits) triples, norm gains as bf16 bit arrays."""
+    rng = np.random.default_rng(seed)
+    H, I, V, d, E = cfg["hidden"], cfg["expert_intermediate"], cfg["vocab"], cfg["head_dim"], cfg["experts"]
+    qd, kd, G = cfg["q_heads"] * d, cfg["kv_heads"] * d, cfg["group_size"]
+
+    def quant(shape_n, k, bits=4, spread=0.006):
+        lead = shape_n if isinstance(shape_n, tuple) else (shape_n,)
+        packed = rng.integers(0, 2 ** 32, lead + (k * bits // 32,), dtype=np.uint64).astype(np.uint32)
+        scales = (np.abs(rng.standard_normal(lead + (k // G,))) * spread + spread * 0.25).astype(np.float32)
+        if bits == 8:
+            scales = scales / 16.0
+        centre = (2 ** bits - 1) / 2.0
+        biases = (-centre * scales + rng.standard_normal(lead + (k // G,)) * spread * 0.5).astype(np.float32)
+        return packed, fjo.encode(scales, fjo.BF16), fjo.encode(biases, fjo.BF16)
+
+    def gain(n):
+        return fjo.encode((1.0 + rng.standard_normal(n) * 0.02).astype(np.float32), fjo.BF16)
+
+    weights = {"embed": quant(V, H, spread=0.02), "final_norm": gain(H), "lm_head": quant(V, H), "layers": []}
+    for _ in range(cfg["layers"]):
+        weights["layers"].append({
+            "input_norm": gain(H), "q_norm": gain(d), "k_norm": gain(d), "post_norm": gain(H),
+            "qkv": quant(qd + 2 * kd, H), "o": quant(H, qd), "router": quant(E, H, bits=cfg["router_bits"], spread=0.02),
+            "gate": quant((E, I), H), "up": quant((E, I), H), "down": quant((E, H), I)})
+    return weights
+
+
+class MoeOracle:
+    """Reference-order forward step of the sparse-MoE decoder over paged KV (Qwen3-Coder,
+    engines/qwen3-coder/src/lib.rs:886-947 and :505-603), one lane at a time. Activations bf16;
+    router logits, routing weights and the inputs of the fused epilogues f32 (an epilogue of the
+    reference sees the f32 accumulator and its output is rounded once)."""
+
+    def __init__(self, cfg: dict, weights: dict, physical_pages: int, page_tokens: int):
+        self.cfg, self.w, self.page_tokens = cfg, weights, page_tokens
+        kd = cfg["kv_heads"] * cfg["head_dim"]
+        self.k_planes = [np.zeros((physical_pages, page_tokens, kd), np.uint16) for _ in range(cfg["layers"])]
+        self.v_planes = [np.zeros((physical_pages, page_tokens, kd), np.uint16) for _ in range(cfg["layers"])]
+        self.scale = float(np.float32(1.0) / np.sqrt(np.float32(cfg["head_dim"])))
+
+    def _q(self, x, triple, bits=4, out_dt=None):
+        return fjo.quant_matmul(x, fjo.BF16, triple[0], triple[1], triple[2], fjo.BF16, bits, self.cfg["group_size"], fjo.BF16 if out_dt is None else out_dt)
+
+    def moe(self, normed, residual, L):
+        """Returns (new residual stream, router logits f32, expert ids, routing weights)."""
+        cfg, G = self.cfg, self.cfg["group_size"]
+        logits = self._q(normed, L["router"], bits=cfg["router_bits"], out_dt=fjo.F32)
+        weights, experts = fjo.top_k(logits, fjo.F32, cfg["top_k"], True)
+        gate = fjo.gather_quant_matmul(normed, fjo.BF16, *L["gate"], fjo.BF16, experts, 4, G, out_dt=fjo.F32)
+        up = fjo.gather_quant_matmul(normed, fjo.BF16, *L["up"], fjo.BF16, experts, 4, G, out_dt=fjo.F32)
+        act = fjo.prog_silu_mul(gate, up, fjo.F32, out_dt=fjo.BF16)
+        mixed = fjo.gather_quant_weighted_sum(act, fjo.BF16, *L["down"], fjo.BF16, experts, weights, fjo.F32, 4, G, fjo.F32)
+        out = fjo.prog_add(mixed, fjo.decode(residual, fjo.BF16), fjo.F32, out_dt=fjo.BF16)
+        return out, logits, experts, weights
+
+    def forward_lane(self, token_ids, start: int, table: np.ndarray, generations: np.ndarray):
+        cfg, dt = self.cfg, fjo.BF16
+        T, d, hq, kvh = len(token_ids), cfg["head_dim"], cfg["q_heads"], cfg["kv_heads"]
+        eps, theta, G = cfg["eps"], cfg["theta"], cfg["group_size"]
+        hidden = fjo.quant_embed(*self.w["embed"], fjo.BF16, np.asarray(token_ids, np.uint32), 4, G, dt)
+        positions = np.arange(start, start + T, dtype=np.uint32).astype(np.float32)
+        normed = fjo.rms_norm(hidden, dt, self.w["layers"][0]["input_norm"], dt, eps)
+        for li, L in enumerate(self.w["layers"]):
+            qkv = self._q(normed, L["qkv"])
+            q = np.ascontiguousarray(qkv[:, :hq * d]).reshape(T, hq, d)
+            k = np.ascontiguousarray(qkv[:, hq * d:(hq + kvh) * d]).reshape(T, kvh, d)
+            v = np.ascontiguousarray(qkv[:, (hq + kvh) * d:]).reshape(T, kvh, d)
+            q = fjo.prog_qk_norm_rope(q, dt, L["q_norm"], dt, positions, eps, theta)
+            k = fjo.prog_qk_norm_rope(k, dt, L["k_norm"], dt, positions, eps, theta)
+            fjo.paged_copy_in(k.reshape(T, kvh * d), dt, self.k_planes[li], dt, table, generations, start, self.page_tokens)
+            fjo.paged_copy_in(v.reshape(T, kvh * d), dt, self.v_planes[li], dt, table, generations, start, self.page_tokens)
+            P = self.k_planes[li].shape[0]
+            attended = fjo.paged_sdpa(np.ascontiguousarray(q.transpose(1, 0, 2)), dt, self.k_planes[li].reshape(P, self.page_tokens, kvh, d), dt,
+                                      self.v_planes[li].reshape(P, self.page_tokens, kvh, d), dt, table, generations, start + T, start, self.scale, True,
+                                      self.page_tokens)
+            attended = np.ascontiguousarray(attended.transpose(1, 0, 2)).reshape(T, hq * d)
+            hidden, normed = fjo.prog_residual_norm(hidden, self._q(attended, L["o"]), dt, L["post_norm"], dt, eps)
+            hidden, _, _, _ = self.moe(normed, hidden, L)
+            nxt = self.w["layers"][li + 1]["input_norm"] if li + 1 < len(self.w["layers"]) else self.w["final_norm"]
+            normed = fjo.prog_rms_norm(hidden, dt, nxt, dt, eps)
+        logits = self._q(normed[T - 1:T], self.w["lm_head"])
+        return fjo.decode(logits, dt)[0], int(fjo.argmax(logits, dt)[0])
+
+
+def ep_moe_layer(rank: int, world: int, cfg: dict, normed, residual, L_local: dict, router, exchange):
+    """Expert-parallel form of MoeOracle.moe for one rank, restating the device algorithm in numpy:
+    slots are handed out per destination in (row, j) order, slabs of capacity rows * top_k are
+    exchanged, the owner computes gate/up/silu/down for every received slot, results return as f32
+    and the origin adds residual + sum_j w_j * down_j in ascending j (product rounded, then added).
+    ``L_local`` holds this rank's expert slice; ``exchange(array)`` takes [world, ...] slabs and
+    returns the slabs addressed to this rank, [world, ...] indexed by source."""
+    G, K, H, I = cfg["group_size"], cfg["top_k"], cfg["hidden"], cfg["expert_intermediate"]
+    per = cfg["experts"] // world
+    rows = normed.shape[0]
+    cap = cfg["max_rows"] * K
+    logits = fjo.quant_matmul(normed, fjo.BF16, *router, fjo.BF16, cfg["router_bits"], G, fjo.F32)
+    weights, experts = fjo.top_k(logits, fjo.F32, K, True) if rows else (np.zeros((0, K), np.float32), np.zeros((0, K), np.uint32))
+    send_rows = np.zeros((world, cap, H), np.uint16)
+    send_experts = np.full((world, cap), per, np.uint32)
+    next_slot = [0] * world
+    route_slot = np.zeros((rows, K), np.int64)
+    for r in range(rows):
+        for j in range(K):
+            dest = int(experts[r, j]) // per
+            slot = next_slot[dest]
+            next_slot[dest] += 1
+            route_slot[r, j] = dest * cap + slot
+            send_rows[dest, slot] = normed[r]
+            send_experts[dest, slot] = int(experts[r, j]) - dest * per
+    recv_rows, recv_experts = exchange(send_rows), exchange(send_experts)
+    down = np.zeros((world, cap, H), np.float32)
+    for src in range(world):
+        live = np.nonzero(recv_experts[src] < per)[0]
+        if live.size == 0:
+            continue
+        x = np.ascontiguousarray(recv_rows[src, live])
+        ids = np.ascontiguousarray(recv_experts[src, live]).reshape(-1, 1)
+        gate = fjo.gather_quant_matmul(x, fjo.BF16, *L_local["gate"], fjo.BF16, ids, 4, G, out_dt=fjo.F32)
+        up = fjo.gather_quant_matmul(x, fjo.BF16, *L_local["up"], fjo.BF16, ids, 4, G, out_dt=fjo.F32)
+        act = fjo.prog_silu_mul(gate, up, fjo.F32, out_dt=fjo.BF16).reshape(live.size, I)
+        down[src, live] = fjo.gather_quant_matmul(act, fjo.BF16, *L_local["down"], fjo.BF16, ids, 4, G, out_dt=fjo.F32).reshape(live.size, H)
+    returned = exchange(down).reshape(world * cap, H)
+    out = np.zeros((rows, H), np.uint16)
+    res = fjo.decode(residual, fjo.BF16) if rows else np.zeros((0, H), np.float32)
+    for r in range(rows):
+        total = np.zeros(H, np.float32)
+        for j in range(K):
+            total = (total + (weights[r, j] * returned[route_slot[r, j]]).astype(np.float32)).astype(np.float32)
+        out[r] = fjo.encode((total + res[r]).astype(np.float32), fjo.BF16)
+    return out

@@ -1,0 +1,112 @@
+"""Sparse-MoE decoder step (fj_moe_*) against the CPU oracle's replay of the reference op order
+(engines/qwen3-coder/src/lib.rs:886-947, :505-603), and expert parallelism over two GPUs against the
+single-GPU path. Tolerance: bf16 / 4-bit logits within max-abs rel 2e-2; greedy tokens equal or a
+near-tie (reduced-precision rule of the reference, docs/engines.md:108-111)."""
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+
+import forja_b200 as fb
+from oracle import engine, fjo
+from tests.gpu_util import backend, down, max_abs_rel
+
+pytestmark = pytest.mark.gpu
+
+TINY = dict(layers=2, hidden=256, q_heads=4, kv_heads=2, head_dim=64, experts=8, top_k=2, expert_intermediate=128, vocab=512,
+            group_size=64, router_bits=8, eps=1e-6, theta=1e7, max_rows=96)
+# head_dim 128 with 8 query heads per KV head: the decode steps run the tensor-core attention and,
+# with at most 16 rows, the streaming q4 projection kernels
+CODER_LIKE = dict(layers=2, hidden=512, q_heads=8, kv_heads=1, head_dim=128, experts=16, top_k=4, expert_intermediate=192, vocab=1024,
+                  group_size=64, router_bits=8, eps=1e-6, theta=1e7, max_rows=64)
+
+
+def upload_moe(be, weights):
+    def triple(t):
+        return (be.tensor_from(t[0], fb.U32), be.tensor_from(t[1], fb.BF16), be.tensor_from(t[2], fb.BF16))
+
+    layers = []
+    for layer in weights["layers"]:
+        entry = {k: be.tensor_from(layer[k], fb.BF16) for k in ("input_norm", "q_norm", "k_norm", "post_norm")}
+        entry.update({k: triple(layer[k]) for k in ("qkv", "o", "router", "gate", "up", "down")})
+        layers.append(entry)
+    return triple(weights["embed"]), be.tensor_from(weights["final_norm"], fb.BF16), triple(weights["lm_head"]), layers
+
+
+def near_tie_flips(tokens, ref_tokens, got_logits):
+    flips = 0
+    for lane, (got, want) in enumerate(zip(tokens.tolist(), ref_tokens)):
+        if got != want:
+            row = got_logits[lane]
+            assert abs(row[got] - row[want]) <= 2e-2 * np.max(np.abs(row)), "token differs without a near-tie"
+            flips += 1
+    return flips
+
+
+@pytest.mark.parametrize("cfg,prompts,steps", [(TINY, [5, 23, 9], 5), (CODER_LIKE, [3, 17, 1, 8], 6)])
+def test_moe_step_matches_oracle(cfg, prompts, steps):
+    rng = np.random.default_rng(3)
+    be = backend()
+    page, lanes = 16, len(prompts)
+    table_pages = max((n + steps + page - 1) // page for n in prompts) + 1
+    physical = sum((n + steps + page - 1) // page for n in prompts) + 3
+    pool = fb.KvPool(be, page, physical, lanes, table_pages)
+    assert all(s == 0 for s in pool.reserve(list(range(lanes)), [n + steps for n in prompts]))
+    weights = engine.random_moe_weights(cfg, 11)
+    embed, final_norm, lm_head, layers = upload_moe(be, weights)
+    model = fb.MoeModel(be, pool, cfg, embed, final_norm, lm_head, layers)
+    ref = engine.MoeOracle(cfg, weights, physical, page)
+    tables = [pool.table(lane) for lane in range(lanes)]
+    generations = pool.generations()
+    ids = [rng.integers(0, cfg["vocab"], n).astype(np.uint32) for n in prompts]
+    logits = be.alloc(fb.BF16, (lanes, cfg["vocab"]))
+    fjo.set_threads(fjo.max_threads())
+    pool.pack_step([0] * lanes, prompts)
+    tokens = model.step(np.concatenate(ids), lanes=lanes, logits=logits)
+    got = down(logits)
+    ref_tokens, flips = [], 0
+    for lane in range(lanes):
+        want, tok = ref.forward_lane(ids[lane], 0, tables[lane], generations)
+        ref_tokens.append(tok)
+        assert max_abs_rel(got[lane], want) <= 2e-2, f"prefill lane {lane}"
+    flips += near_tie_flips(tokens, ref_tokens, got)
+    positions = list(prompts)
+    for step in range(steps):
+        pool.pack_step(positions, [1] * lanes)
+        tokens = model.step(np.array(ref_tokens, np.uint32), lanes=lanes, logits=logits)  # teacher-forced
+        got = down(logits)
+        for lane in range(lanes):
+            want, tok = ref.forward_lane([ref_tokens[lane]], positions[lane], tables[lane], generations)
+            ref_tokens[lane] = tok
+            assert max_abs_rel(got[lane], want) <= 2e-2, f"step {step} lane {lane}"
+        flips += near_tie_flips(tokens, ref_tokens, got)
+        positions = [p + 1 for p in positions]
+    fjo.set_threads(1)
+    assert flips <= max(1, int(0.05 * lanes * (steps + 1)))
+    assert model.stats()["kernels"] > 0
+    model.close()
+    pool.close()
+
+
+def test_expert_parallel_step_equals_single_gpu_bits():
+    """Two ranks, one GPU each, experts split in half: every rank's logits must equal, bit for bit,
+    what one GPU computes for the same lanes (each route runs the same arithmetic either way)."""
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", MASTER_ADDR="127.0.0.1", MASTER_PORT="29741")
+    script = os.path.join(os.path.dirname(__file__), "ep_child.py")
+    procs = [subprocess.Popen([sys.executable, script, str(rank), "2"], env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True) for rank in range(2)]
+    outputs = []
+    for p in procs:
+        try:
+            out, _ = p.communicate(timeout=600)
+        except subprocess.TimeoutExpired:
+            p.kill()
+            out, _ = p.communicate()
+        outputs.append(out)
+    for rank, (p, out) in enumerate(zip(procs, outputs)):
+        assert p.returncode == 0, f"rank {rank} failed:\n{out[-4000:]}"
+        assert "EP_OK" in out, out[-2000:]
