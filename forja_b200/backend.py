@@ -359,6 +359,10 @@ class CudaBackend:
         sub.wait()
         return sub
 
+    def fill_random(self, tensor: Tensor, seed: int, mean: float = 0.0, std: float = 1.0):
+        """Synthetic contents for a whole contiguous tensor (normal for floats, random words for u32)."""
+        _check(self._lib.fj_fill_random(self._h, tensor.buffer, tensor.layout.offset * DTYPE_SIZE[tensor.dtype], tensor.layout.element_count(), tensor.dtype, seed, mean, std))
+
     def synchronize(self):
         _check(self._lib.fj_synchronize(self._h))
 
@@ -567,7 +571,7 @@ class MoeModel:
         self.backend, self.pool, self._lib, self.config = backend, pool, backend._lib, dict(config)
         cfg = _lib.FjMoeConfig()
         for name, _ in _lib.FjMoeConfig._fields_:
-            setattr(cfg, name, config[name])
+            setattr(cfg, name, config.get(name, 0))
         arr = (_lib.FjMoeLayerWeights * len(layers))()
         for i, layer in enumerate(layers):
             for name in ("input_norm", "q_norm", "k_norm", "post_norm"):

@@ -1,0 +1,286 @@
+// Grouped expert projections for many routed rows (reference counterparts: the sorted MoE path of
+// crates/forja-metal/kernels/quant_matmul.metal: count_expert_routes :1217, plan_expert_routes
+// :1255, arrange_expert_routes :1312, grouped_quantized_pair_32x32_2x2_blocked :1615; operator
+// semantics: Op::GatherQuantMatmul, crates/forja-cpu/src/lib.rs:964-1204).
+//
+// The per-route kernels read an expert's whole matrix for every route, which is right for a few
+// decode rows and hopeless for prefill chunks. Here the routes are bucketed by expert (histogram,
+// scan, arrange; one CTA, like the reference), cut into tiles of 64 rows of one expert, and every
+// tile runs a 64 x 64 x K tensor-core GEMM whose B operand is dequantised on the fly: per 64-k
+// step (= one quantisation group) the CTA copies 64 columns x 32 bytes of nibbles with cp.async,
+// expands them to bf16 (w = s * q + b in f32, rounded once) into a swizzled shared tile and feeds
+// mma.sync m16n8k16 through ldmatrix. Rows of A are gathered through the sorted route list.
+//  pair mode: gate and up tiles share the A tile; epilogue silu(gate) * up -> act[route] (bf16)
+//  single mode: f32 result per route (the weighted combine adds them in route order afterwards)
+// The order of rows inside an expert's bucket is whatever the atomics give; it only decides which
+// tile a row lands in, never its value.
+#include "fj_kernels.h"
+
+namespace fj {
+
+namespace {
+
+constexpr int GT_BM = 64, GT_BN = 64, GT_BK = 64, GT_THREADS = 128;
+
+struct RouteTile {
+  unsigned expert, first, count;
+};
+
+// One CTA: histogram of routes per expert, exclusive scan, arrange, tile list.
+__global__ void __launch_bounds__(1024) route_plan_kernel(const unsigned* __restrict__ indices, unsigned total, unsigned experts, unsigned* offsets /*[experts + 1]*/,
+                                                          unsigned* sorted /*[total]*/, RouteTile* tiles, unsigned* n_tiles, unsigned tiles_cap) {
+  extern __shared__ unsigned plan_smem[];
+  unsigned* count = plan_smem;           // [experts]
+  unsigned* cursor = plan_smem + experts;  // [experts]
+  for (unsigned e = threadIdx.x; e < experts; e += blockDim.x) count[e] = 0;
+  __syncthreads();
+  for (unsigned r = threadIdx.x; r < total; r += blockDim.x) {
+    const unsigned e = indices[r];
+    if (e < experts) atomicAdd(&count[e], 1u);
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    unsigned running = 0, made = 0;
+    for (unsigned e = 0; e < experts; ++e) {
+      offsets[e] = running;
+      cursor[e] = running;
+      for (unsigned f = 0; f < count[e]; f += GT_BM) {
+        if (made < tiles_cap) tiles[made] = RouteTile{e, running + f, min(static_cast<unsigned>(GT_BM), count[e] - f)};
+        ++made;
+      }
+      running += count[e];
+    }
+    offsets[experts] = running;
+    *n_tiles = min(made, tiles_cap);
+  }
+  __syncthreads();
+  for (unsigned r = threadIdx.x; r < total; r += blockDim.x) {
+    const unsigned e = indices[r];
+    if (e < experts) sorted[atomicAdd(&cursor[e], 1u)] = r;
+  }
+}
+
+__device__ inline void g_cp_async_16(unsigned smem_addr, const void* gmem, unsigned src_bytes) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(smem_addr), "l"(gmem), "r"(src_bytes) : "memory");
+}
+__device__ inline void g_ldmatrix_x4(unsigned& r0, unsigned& r1, unsigned& r2, unsigned& r3, unsigned addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ inline void g_mma(float (&d)[4], const unsigned (&a)[4], unsigned b0, unsigned b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3]) : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ inline unsigned pack_bf16(float lo, float hi) {
+  return static_cast<unsigned>(__bfloat16_as_ushort(__float2bfloat16_rn(lo))) | (static_cast<unsigned>(__bfloat16_as_ushort(__float2bfloat16_rn(hi))) << 16);
+}
+
+struct GroupedArgs {
+  const unsigned short* x;          // A source rows, bf16 [*, k]
+  const unsigned* packed[2];        // [experts][n][k / 8]
+  const unsigned short* scales[2];  // [experts][n][k / 64] bf16
+  const unsigned short* biases[2];
+  const unsigned* sorted;           // route ids bucketed by expert
+  const RouteTile* tiles;
+  const unsigned* n_tiles;
+  void* out;                        // pair: bf16 [routes][n]; single: f32 [routes][n]
+  unsigned k, n, src_div;           // A row of a route = route / src_div
+};
+
+template <bool kPair>
+__global__ void __launch_bounds__(GT_THREADS) grouped_q4_gemm_kernel(GroupedArgs p) {
+  constexpr int NW = kPair ? 2 : 1;
+  __shared__ __align__(128) unsigned char s_a[2][GT_BM * 128];
+  __shared__ __align__(128) unsigned char s_b[NW][GT_BN * 128];
+  __shared__ __align__(16) unsigned char s_q[2][NW][GT_BN * 32];
+  __shared__ unsigned short s_scale[2][NW][GT_BN], s_bias[2][NW][GT_BN];
+  __shared__ unsigned s_route[GT_BM];
+  if (blockIdx.y >= *p.n_tiles) return;
+  const RouteTile tile = p.tiles[blockIdx.y];
+  const unsigned col0 = blockIdx.x * GT_BN;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int warp_m = warp >> 1, warp_n = warp & 1;  // 2 x 2 warps of 32 x 32
+  const unsigned k_iters = p.k / GT_BK, words_per_row = p.k / 8, groups_per_row = p.k / 64;
+  for (unsigned i = threadIdx.x; i < GT_BM; i += GT_THREADS) s_route[i] = i < tile.count ? p.sorted[tile.first + i] : 0xFFFFFFFFu;
+  __syncthreads();
+  const unsigned a_base = static_cast<unsigned>(__cvta_generic_to_shared(&s_a[0][0]));
+  const unsigned b_base = static_cast<unsigned>(__cvta_generic_to_shared(&s_b[0][0]));
+  const unsigned q_base = static_cast<unsigned>(__cvta_generic_to_shared(&s_q[0][0][0]));
+  const size_t expert_rows = static_cast<size_t>(tile.expert) * p.n;
+
+  float acc[NW][2][4][4];
+#pragma unroll
+  for (int w = 0; w < NW; ++w)
+#pragma unroll
+    for (int i = 0; i < 2; ++i)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) acc[w][i][j][0] = acc[w][i][j][1] = acc[w][i][j][2] = acc[w][i][j][3] = 0.0f;
+
+  auto issue = [&](unsigned it) {
+    if (it < k_iters) {
+      const unsigned stage = it & 1, kk = it * GT_BK;
+      // A: 64 rows x 8 chunks of 16 bytes, gathered through the route list
+#pragma unroll
+      for (int i = 0; i < (GT_BM * 8) / GT_THREADS; ++i) {
+        const unsigned chunk = threadIdx.x + i * GT_THREADS, r = chunk >> 3, c8 = chunk & 7;
+        const unsigned route = s_route[r];
+        const bool ok = route != 0xFFFFFFFFu;
+        const void* src = ok ? static_cast<const void*>(p.x + static_cast<size_t>(route / p.src_div) * p.k + kk + c8 * 8) : static_cast<const void*>(p.x);
+        g_cp_async_16(a_base + stage * (GT_BM * 128) + r * 128 + ((c8 ^ (r & 7)) << 4), src, ok ? 16u : 0u);
+      }
+      // packed weights: 64 columns x 2 chunks of 16 bytes per matrix; scales / biases: one u16 each
+#pragma unroll
+      for (int w = 0; w < NW; ++w) {
+        const unsigned c = threadIdx.x >> 1, half = threadIdx.x & 1;
+        const bool ok = col0 + c < p.n;
+        const size_t row = expert_rows + (ok ? col0 + c : 0);
+        g_cp_async_16(q_base + ((stage * NW + w) * GT_BN + c) * 32 + half * 16, p.packed[w] + row * words_per_row + (kk / 8) + half * 4, ok ? 16u : 0u);
+        if (half == 0) s_scale[stage][w][c] = ok ? p.scales[w][row * groups_per_row + it] : static_cast<unsigned short>(0);
+        else s_bias[stage][w][c] = ok ? p.biases[w][row * groups_per_row + it] : static_cast<unsigned short>(0);
+      }
+    }
+    asm volatile("cp.async.commit_group;\n" ::: "memory");
+  };
+
+  issue(0);
+  for (unsigned it = 0; it < k_iters; ++it) {
+    asm volatile("cp.async.wait_group 0;\n" ::: "memory");
+    __syncthreads();  // stage `it` landed; everyone finished the previous step's mma (s_b and the other stage are free)
+    issue(it + 1);
+    const unsigned stage = it & 1;
+    // expand this step's nibbles: thread -> (column, half of the 64-k step) = 32 weights per matrix
+#pragma unroll
+    for (int w = 0; w < NW; ++w) {
+      const unsigned c = threadIdx.x >> 1, half = threadIdx.x & 1;
+      const uint4 q = *reinterpret_cast<const uint4*>(&s_q[stage][w][c * 32 + half * 16]);
+      const float s = __uint_as_float(static_cast<unsigned>(s_scale[stage][w][c]) << 16), b = __uint_as_float(static_cast<unsigned>(s_bias[stage][w][c]) << 16);
+      const unsigned words[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        float v[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          // exact int -> float through the 2^23 mantissa trick, then w = s * q + b, product rounded first
+          const float qf = __uint_as_float(0x4B000000u | ((words[i] >> (4 * j)) & 0xFu)) - 8388608.0f;
+          v[j] = __fadd_rn(__fmul_rn(s, qf), b);
+        }
+        const uint4 packed = make_uint4(pack_bf16(v[0], v[1]), pack_bf16(v[2], v[3]), pack_bf16(v[4], v[5]), pack_bf16(v[6], v[7]));
+        const unsigned chunk = half * 4 + i;
+        *reinterpret_cast<uint4*>(&s_b[w][c * 128 + ((chunk ^ (c & 7)) << 4)]) = packed;
+      }
+    }
+    __syncthreads();
+#pragma unroll
+    for (int ks = 0; ks < GT_BK / 16; ++ks) {
+      unsigned af[2][4];
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
+        const unsigned mi = lane >> 3, rr = lane & 7;
+        const unsigned r = warp_m * 32 + i * 16 + (mi & 1) * 8 + rr;
+        const unsigned chunk = ks * 2 + (mi >> 1);
+        g_ldmatrix_x4(af[i][0], af[i][1], af[i][2], af[i][3], a_base + stage * (GT_BM * 128) + r * 128 + ((chunk ^ (r & 7)) << 4));
+      }
+#pragma unroll
+      for (int w = 0; w < NW; ++w)
+#pragma unroll
+        for (int j = 0; j < 4; j += 2) {
+          const unsigned mi = lane >> 3, rr = lane & 7;
+          const unsigned r = warp_n * 32 + j * 8 + (mi >> 1) * 8 + rr;
+          const unsigned chunk = ks * 2 + (mi & 1);
+          unsigned b0, b1, b2, b3;
+          g_ldmatrix_x4(b0, b1, b2, b3, b_base + w * (GT_BN * 128) + r * 128 + ((chunk ^ (r & 7)) << 4));
+#pragma unroll
+          for (int i = 0; i < 2; ++i) {
+            g_mma(acc[w][i][j], af[i], b0, b1);
+            g_mma(acc[w][i][j + 1], af[i], b2, b3);
+          }
+        }
+    }
+  }
+  asm volatile("cp.async.wait_group 0;\n" ::: "memory");
+
+  const unsigned gr = lane >> 2, gc = (lane & 3) * 2;
+#pragma unroll
+  for (int i = 0; i < 2; ++i)
+#pragma unroll
+    for (int e = 0; e < 4; e += 2) {
+      const unsigned r = warp_m * 32 + i * 16 + gr + (e >> 1) * 8;
+      const unsigned route = s_route[r];
+      if (route == 0xFFFFFFFFu) continue;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const unsigned col = col0 + warp_n * 32 + j * 8 + gc;
+        if (col >= p.n) continue;
+        float v0 = acc[0][i][j][e], v1 = acc[0][i][j][e + 1];
+        if (kPair) {
+          v0 = v0 * (1.0f / (1.0f + expf(-v0))) * acc[NW - 1][i][j][e];
+          v1 = v1 * (1.0f / (1.0f + expf(-v1))) * acc[NW - 1][i][j][e + 1];
+          unsigned short* o = static_cast<unsigned short*>(p.out) + static_cast<size_t>(route) * p.n + col;
+          if (col + 1 < p.n) *reinterpret_cast<unsigned*>(o) = pack_bf16(v0, v1);
+          else *o = __bfloat16_as_ushort(__float2bfloat16_rn(v0));
+        } else {
+          float* o = static_cast<float*>(p.out) + static_cast<size_t>(route) * p.n + col;
+          if (col + 1 < p.n) *reinterpret_cast<float2*>(o) = make_float2(v0, v1);
+          else *o = v0;
+        }
+      }
+    }
+}
+
+}  // namespace
+
+size_t route_plan_bytes(unsigned total_routes, unsigned experts) {
+  const size_t tiles_cap = total_routes / GT_BM + experts + 1;
+  return (static_cast<size_t>(experts) + 1 + total_routes + 4) * sizeof(unsigned) + tiles_cap * sizeof(RouteTile) + 64;
+}
+
+namespace {
+struct PlanLayout {
+  unsigned *offsets, *sorted, *n_tiles;
+  RouteTile* tiles;
+  unsigned tiles_cap;
+};
+PlanLayout plan_layout(void* plan, unsigned total_routes, unsigned experts) {
+  PlanLayout l;
+  unsigned* base = static_cast<unsigned*>(plan);
+  l.n_tiles = base;  // 4 words reserved
+  l.offsets = base + 4;
+  l.sorted = l.offsets + experts + 1;
+  size_t words = 4 + static_cast<size_t>(experts) + 1 + total_routes;
+  words = (words + 3) / 4 * 4;
+  l.tiles = reinterpret_cast<RouteTile*>(base + words);
+  l.tiles_cap = total_routes / GT_BM + experts + 1;
+  return l;
+}
+}  // namespace
+
+void launch_route_plan(Ctx& ctx, const unsigned* indices, unsigned total_routes, unsigned experts, void* plan) {
+  const PlanLayout l = plan_layout(plan, total_routes, experts);
+  route_plan_kernel<<<1, 1024, 2 * experts * sizeof(unsigned), ctx.stream>>>(indices, total_routes, experts, l.offsets, l.sorted, l.tiles, l.n_tiles, l.tiles_cap);
+  ctx.launches++;
+}
+
+bool grouped_q4_supported(unsigned k, unsigned n, unsigned bits, unsigned group_size, unsigned experts, const void* x, const void* packed) {
+  return bits == 4 && group_size == 64 && k % 64 == 0 && n % 2 == 0 && experts <= 4096 && reinterpret_cast<size_t>(x) % 16 == 0 && reinterpret_cast<size_t>(packed) % 16 == 0;
+}
+
+void launch_grouped_q4_pair(Ctx& ctx, const void* x, const unsigned* gate, const void* gate_scales, const void* gate_biases, const unsigned* up, const void* up_scales,
+                            const void* up_biases, const void* plan, unsigned total_routes, unsigned experts, unsigned src_div, void* act_out, unsigned k, unsigned n) {
+  const PlanLayout l = plan_layout(const_cast<void*>(plan), total_routes, experts);
+  GroupedArgs a{static_cast<const unsigned short*>(x), {gate, up}, {static_cast<const unsigned short*>(gate_scales), static_cast<const unsigned short*>(up_scales)},
+                {static_cast<const unsigned short*>(gate_biases), static_cast<const unsigned short*>(up_biases)}, l.sorted, l.tiles, l.n_tiles, act_out, k, n, src_div};
+  dim3 grid((n + GT_BN - 1) / GT_BN, l.tiles_cap);
+  grouped_q4_gemm_kernel<true><<<grid, GT_THREADS, 0, ctx.stream>>>(a);
+  ctx.launches++;
+}
+
+void launch_grouped_q4_single(Ctx& ctx, const void* x, const unsigned* packed, const void* scales, const void* biases, const void* plan, unsigned total_routes, unsigned experts,
+                              unsigned src_div, float* out, unsigned k, unsigned n) {
+  const PlanLayout l = plan_layout(const_cast<void*>(plan), total_routes, experts);
+  GroupedArgs a{static_cast<const unsigned short*>(x), {packed, packed}, {static_cast<const unsigned short*>(scales), static_cast<const unsigned short*>(scales)},
+                {static_cast<const unsigned short*>(biases), static_cast<const unsigned short*>(biases)}, l.sorted, l.tiles, l.n_tiles, out, k, n, src_div};
+  dim3 grid((n + GT_BN - 1) / GT_BN, l.tiles_cap);
+  grouped_q4_gemm_kernel<false><<<grid, GT_THREADS, 0, ctx.stream>>>(a);
+  ctx.launches++;
+}
+
+}  // namespace fj

@@ -243,7 +243,11 @@ __device__ inline unsigned long long mix64(unsigned long long z) {
   z = (z ^ (z >> 27)) * 0x94d049bb133111ebull;
   return z ^ (z >> 31);
 }
-__global__ void fill_normal_kernel(void* out, int dt, size_t elements, unsigned long long seed) {
+__global__ void fill_words_kernel(unsigned* out, size_t elements, unsigned long long seed) {
+  for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < elements; i += static_cast<size_t>(gridDim.x) * blockDim.x)
+    out[i] = static_cast<unsigned>(mix64(seed ^ (i * 0xD1342543DE82EF95ull)) >> 16);
+}
+__global__ void fill_normal_kernel(void* out, int dt, size_t elements, unsigned long long seed, float mean = 0.0f, float std = 1.0f) {
   const size_t pairs = (elements + 1) / 2;
   for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < pairs; i += static_cast<size_t>(gridDim.x) * blockDim.x) {
     const unsigned long long r = mix64(seed ^ (i * 0xD1342543DE82EF95ull));
@@ -252,8 +256,8 @@ __global__ void fill_normal_kernel(void* out, int dt, size_t elements, unsigned 
     const float radius = sqrtf(-2.0f * logf(u1));
     float s, c;
     sincospif(2.0f * u2, &s, &c);
-    fj::store_from_f32(out, dt, 2 * i, radius * c);
-    if (2 * i + 1 < elements) fj::store_from_f32(out, dt, 2 * i + 1, radius * s);
+    fj::store_from_f32(out, dt, 2 * i, mean + std * (radius * c));
+    if (2 * i + 1 < elements) fj::store_from_f32(out, dt, 2 * i + 1, mean + std * (radius * s));
   }
 }
 
@@ -509,6 +513,22 @@ int32_t fj_dense_fill_kv(fj_dense_model* m, uint64_t seed) {
     be->ctx.launches += 2;
   }
   return cuda_status(cudaStreamSynchronize(be->stream));
+}
+
+int32_t fj_fill_random(fj_backend* be, uint64_t buffer, uint64_t offset_bytes, uint64_t elements, uint32_t dtype, uint64_t seed, float mean, float std) {
+  if (!be || dtype > FJ_U32) return FJ_INVALID_INPUT;
+  std::lock_guard<std::mutex> lock(be->mutex);
+  cudaSetDevice(be->device);
+  fj_buffer_rec* r = find_buffer(be, buffer);
+  const uint64_t esz = fj::dtype_size(static_cast<int>(dtype));
+  if (!r || r->readonly || offset_bytes % esz != 0 || offset_bytes > r->bytes || elements > (r->bytes - offset_bytes) / esz) return FJ_INVALID_INPUT;
+  if (elements == 0) return FJ_OK;
+  const unsigned grid = static_cast<unsigned>(be->ctx.sm_count) * 16;
+  char* base = static_cast<char*>(r->ptr) + offset_bytes;
+  if (dtype == FJ_U32 || dtype == FJ_I32) fill_words_kernel<<<grid, 256, 0, be->stream>>>(reinterpret_cast<unsigned*>(base), elements, seed);
+  else fill_normal_kernel<<<grid, 256, 0, be->stream>>>(base, static_cast<int>(dtype), elements, seed, mean, std);
+  be->ctx.launches++;
+  return cuda_status(cudaGetLastError());
 }
 
 int32_t fj_dense_profile_attention(fj_dense_model* m, uint32_t enabled) {

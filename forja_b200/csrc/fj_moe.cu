@@ -13,9 +13,10 @@
 // Expert parallelism (no reference counterpart: the reference is single-GPU). Experts are sharded
 // contiguously, expert e lives on rank e / (experts / world); attention, router and the dense
 // projections are replicated and every rank runs its own lanes. Per MoE layer:
-//   1. route locally; one CTA packs each route's activation row into the slab of the rank that owns
-//      its expert (fixed capacity rows * top_k per peer, so no size has to reach the host);
-//   2. all-to-all of the slabs (NCCL send/recv over NVLink) with the local expert id of every row;
+//   1. route locally; each route's activation row goes into the slab of the rank that owns its
+//      expert, slots handed out in (row, j) order; the per-peer row counts are exchanged and read
+//      back by the host (one small copy per layer) so that only live rows travel;
+//   2. all-to-all of the rows (NCCL send/recv over NVLink) with the local expert id of every row;
 //   3. the owner runs gate/up/silu and down for the rows it received (f32 results);
 //   4. all-to-all back; the origin adds  residual + sum_j w_j * down_j  in ascending j.
 // Each route's arithmetic is the same kernel code as in the single-GPU path, so both paths give
@@ -26,6 +27,7 @@
 #include <string.h>
 
 #include <algorithm>
+#include <vector>
 
 using namespace fjb;
 
@@ -134,12 +136,33 @@ int32_t ep_all_to_all(fj_ep* ep, const void* send, void* recv, size_t bytes_per_
   return FJ_OK;
 }
 
+// Variable-size form: rank p gets send_counts[p] rows of row_bytes from send + send_rows_at[p] rows, and
+// its recv_counts[p] rows land at recv + recv_rows_at[p] rows. Counts are host values.
+int32_t ep_all_to_all_rows(fj_ep* ep, const void* send, const unsigned* send_rows_at, const unsigned* send_counts, void* recv, const unsigned* recv_rows_at,
+                           const unsigned* recv_counts, size_t row_bytes) {
+  cudaStream_t stream = ep->be->stream;
+  if (g_nccl.GroupStart() != 0) return FJ_DEVICE_EXECUTION_FAILED;
+  int failed = 0;
+  for (uint32_t peer = 0; peer < ep->world; ++peer) {
+    const char* s = static_cast<const char*>(send) + static_cast<size_t>(send_rows_at[peer]) * row_bytes;
+    char* r = static_cast<char*>(recv) + static_cast<size_t>(recv_rows_at[peer]) * row_bytes;
+    if (peer == ep->rank) {
+      if (send_counts[peer]) cudaMemcpyAsync(r, s, static_cast<size_t>(send_counts[peer]) * row_bytes, cudaMemcpyDeviceToDevice, stream);
+      continue;
+    }
+    if (send_counts[peer]) failed |= g_nccl.Send(s, static_cast<size_t>(send_counts[peer]) * row_bytes, kNcclInt8, static_cast<int>(peer), ep->comm, stream);
+    if (recv_counts[peer]) failed |= g_nccl.Recv(r, static_cast<size_t>(recv_counts[peer]) * row_bytes, kNcclInt8, static_cast<int>(peer), ep->comm, stream);
+  }
+  if (g_nccl.GroupEnd() != 0 || failed) return FJ_DEVICE_EXECUTION_FAILED;
+  return FJ_OK;
+}
+
 // ---- expert-parallel dispatch / combine kernels -------------------------------------------------
 // One thread walks the routes in (row, j) order and hands each the next slot of its destination's slab,
 // so slot numbers are deterministic. Unused slots keep expert id `experts_local` (out of range: the
 // expert kernels write zeros for them without touching any weight).
 __global__ void ep_plan_kernel(const unsigned* __restrict__ indices, unsigned routes, unsigned experts_local, unsigned world, unsigned capacity,
-                               unsigned* send_experts, unsigned* route_slot) {
+                               unsigned* send_experts, unsigned* route_slot, unsigned* send_counts) {
   extern __shared__ unsigned ep_smem[];
   unsigned* next = ep_smem;  // [world] running slot per destination
   for (unsigned i = threadIdx.x; i < world; i += blockDim.x) next[i] = 0;
@@ -154,6 +177,7 @@ __global__ void ep_plan_kernel(const unsigned* __restrict__ indices, unsigned ro
       route_slot[r] = slot;
       send_experts[slot] = expert - dest * experts_local;
     }
+    for (unsigned d = 0; d < world; ++d) send_counts[d] = next[d];
   }
 }
 
@@ -172,13 +196,15 @@ __global__ void ep_scatter_rows_kernel(const unsigned short* __restrict__ normed
 
 // out[row] = bf16(residual[row] + sum_j weights[row, j] * returned[route_slot[row, j]]), j ascending,
 // f32 accumulation: the arithmetic of the fused weighted-sum projection.
-__global__ void ep_combine_kernel(const float* __restrict__ returned, const unsigned* __restrict__ route_slot, const float* __restrict__ weights,
-                                  const unsigned short* __restrict__ residual, unsigned short* out, unsigned rows, unsigned top_k, unsigned width) {
+// route_slot == nullptr: the result of route r sits in row r and routes whose expert id is out of range are skipped.
+__global__ void ep_combine_kernel(const float* __restrict__ returned, const unsigned* __restrict__ route_slot, const unsigned* __restrict__ expert_ids, unsigned experts,
+                                  const float* __restrict__ weights, const unsigned short* __restrict__ residual, unsigned short* out, unsigned rows, unsigned top_k,
+                                  unsigned width) {
   for (unsigned row = blockIdx.x; row < rows; row += gridDim.x) {
     for (unsigned c = threadIdx.x; c < width; c += blockDim.x) {
       float total = 0.0f;
       for (unsigned j = 0; j < top_k; ++j) {
-        const unsigned slot = route_slot[row * top_k + j];
+        const unsigned slot = route_slot ? route_slot[row * top_k + j] : (expert_ids[row * top_k + j] < experts ? row * top_k + j : 0xFFFFFFFFu);
         if (slot == 0xFFFFFFFFu) continue;
         total = __fadd_rn(total, __fmul_rn(weights[row * top_k + j], returned[static_cast<size_t>(slot) * width + c]));
       }
@@ -226,6 +252,11 @@ struct fj_moe_model {
   unsigned short *send_rows = nullptr, *recv_rows = nullptr, *act_ep = nullptr;
   unsigned *send_experts = nullptr, *recv_experts = nullptr, *route_slot = nullptr;
   float *down_ep = nullptr, *returned = nullptr;
+  unsigned *ep_counts = nullptr;       // device: send counts [world] | receive counts [world]
+  unsigned* ep_counts_host = nullptr;  // pinned copy of both
+  // grouped expert path (many routes): route plan and per-route f32 down projections
+  void* route_plan = nullptr;
+  float* down_routes = nullptr;
   fj::AttnSeq* seqs = nullptr;
   fj::AttnWork* work = nullptr;
   unsigned* n_work_dev = nullptr;
@@ -348,6 +379,12 @@ int32_t fj_moe_model_create(fj_backend* be, const fj_moe_config* config, const f
     m->route_slot = static_cast<unsigned*>(dev_alloc(R * K * 4));
     m->down_ep = static_cast<float*>(dev_alloc(slots * H * 4));
     m->returned = static_cast<float*>(dev_alloc(slots * H * 4));
+    m->ep_counts = static_cast<unsigned*>(dev_alloc(2 * world * 4));
+    if (cudaMallocHost(reinterpret_cast<void**>(&m->ep_counts_host), 2 * world * 4) != cudaSuccess) { cudaGetLastError(); ok = false; }
+    m->route_plan = dev_alloc(fj::route_plan_bytes(static_cast<unsigned>(slots), m->experts_local));
+  } else {
+    m->route_plan = dev_alloc(fj::route_plan_bytes(static_cast<unsigned>(R * K), c.experts));
+    m->down_routes = static_cast<float*>(dev_alloc(R * K * H * 4));
   }
   if (ok) {
     m->inv_freq = freq_table(be, c.theta, -2.0f / static_cast<float>(c.head_dim), c.head_dim / 2, false);
@@ -356,6 +393,7 @@ int32_t fj_moe_model_create(fj_backend* be, const fj_moe_config* config, const f
   if (ok) ok = ensure_gemm_scratch(be, fj::gemm_scratch_bytes(static_cast<unsigned>(std::max(R, Lanes)), static_cast<unsigned>(std::max<uint64_t>(qd + 2 * kd, H)), static_cast<unsigned>(std::max<uint64_t>(H, qd))));
   if (!ok || cudaStreamSynchronize(be->stream) != cudaSuccess) {
     for (void* p : m->owned) { cudaFree(p); }
+    if (m->ep_counts_host) cudaFreeHost(m->ep_counts_host);
     delete m;
     return ok ? FJ_ALLOCATION_FAILED : FJ_INVALID_INPUT;
   }
@@ -369,6 +407,7 @@ void fj_moe_model_destroy(fj_moe_model* m) {
   cudaSetDevice(m->be->device);
   cudaStreamSynchronize(m->be->stream);
   for (void* p : m->owned) cudaFree(p);
+  if (m->ep_counts_host) cudaFreeHost(m->ep_counts_host);
   delete m;
 }
 
@@ -459,28 +498,62 @@ extern "C" int32_t fj_moe_step(fj_moe_model* m, const uint32_t* token_ids, uint3
       q4(m->normed, L.router, m->router_logits, FJ_F32, rows, H, c.experts, c.router_bits);
       fj::launch_top_k(ctx, m->router_logits, FJ_F32, m->route_weights, FJ_F32, m->route_experts, rows, c.experts, K, true);
     }
+    // Few routes: one GEMV-style pass per route. Many: bucket by expert and run tile GEMMs (weights rounded to bf16).
+    const unsigned kGroupedRoutes = c.grouped_min_routes ? c.grouped_min_routes : 128;
     if (m->world == 1) {
-      fj::launch_gather_quant_matmul(ctx, m->normed, dt, L.gate.packed, L.gate.scales, L.gate.biases, dt, L.up.packed, L.up.scales, L.up.biases, m->route_experts, m->act, dt, rows, H,
-                                     c.experts, I, K, 4, G, 1, nullptr);
-      fj::launch_gather_quant_weighted_sum(ctx, m->act, dt, L.down.packed, L.down.scales, L.down.biases, dt, m->route_experts, m->route_weights, FJ_F32, hidden, dt, other, dt, rows, K,
-                                           I, c.experts, H, 4, G, 2, nullptr);
+      const unsigned routes = rows * K;
+      if (routes >= kGroupedRoutes && G == 64 && fj::grouped_q4_supported(H, I, 4, G, c.experts, m->normed, L.gate.packed) &&
+          fj::grouped_q4_supported(I, H, 4, G, c.experts, m->act, L.down.packed)) {
+        fj::launch_route_plan(ctx, m->route_experts, routes, c.experts, m->route_plan);
+        fj::launch_grouped_q4_pair(ctx, m->normed, L.gate.packed, L.gate.scales, L.gate.biases, L.up.packed, L.up.scales, L.up.biases, m->route_plan, routes, c.experts, K, m->act, H, I);
+        fj::launch_grouped_q4_single(ctx, m->act, L.down.packed, L.down.scales, L.down.biases, m->route_plan, routes, c.experts, 1, m->down_routes, I, H);
+        ep_combine_kernel<<<std::min(rows, 1024u), 256, 0, be->stream>>>(m->down_routes, nullptr, m->route_experts, c.experts, m->route_weights,
+                                                                         static_cast<const unsigned short*>(hidden), static_cast<unsigned short*>(other), rows, K, H);
+        ctx.launches++;
+      } else {
+        fj::launch_gather_quant_matmul(ctx, m->normed, dt, L.gate.packed, L.gate.scales, L.gate.biases, dt, L.up.packed, L.up.scales, L.up.biases, m->route_experts, m->act, dt, rows, H,
+                                       c.experts, I, K, 4, G, 1, nullptr);
+        fj::launch_gather_quant_weighted_sum(ctx, m->act, dt, L.down.packed, L.down.scales, L.down.biases, dt, m->route_experts, m->route_weights, FJ_F32, hidden, dt, other, dt, rows, K,
+                                             I, c.experts, H, 4, G, 2, nullptr);
+      }
     } else {
-      const unsigned cap = m->capacity, slots = m->world * cap, routes = rows * K;
-      ep_plan_kernel<<<1, 256, m->world * sizeof(unsigned), be->stream>>>(m->route_experts, routes, m->experts_local, m->world, cap, m->send_experts, m->route_slot);
+      const unsigned cap = m->capacity, routes = rows * K, W = m->world;
+      ep_plan_kernel<<<1, 256, W * sizeof(unsigned), be->stream>>>(m->route_experts, routes, m->experts_local, W, cap, m->send_experts, m->route_slot, m->ep_counts);
       ctx.launches++;
       if (routes) { ep_scatter_rows_kernel<<<std::min(routes, 4096u), 128, 0, be->stream>>>(static_cast<const unsigned short*>(m->normed), m->route_slot, routes, K, H, m->send_rows); ctx.launches++; }
-      status = ep_all_to_all(m->ep, m->send_rows, m->recv_rows, static_cast<size_t>(cap) * H * 2);
-      if (status == FJ_OK) status = ep_all_to_all(m->ep, m->send_experts, m->recv_experts, static_cast<size_t>(cap) * 4);
+      // how many rows every peer will send here: one 4-byte exchange, then both count vectors go to the host
+      status = ep_all_to_all(m->ep, m->ep_counts, m->ep_counts + W, 4);
       if (status != FJ_OK) break;
-      // rows received for this rank's experts: one route each, expert id per slot (padding: out of range -> zeros)
-      fj::launch_gather_quant_matmul(ctx, m->recv_rows, dt, L.gate.packed, L.gate.scales, L.gate.biases, dt, L.up.packed, L.up.scales, L.up.biases, m->recv_experts, m->act_ep, dt, slots, H,
-                                     m->experts_local, I, 1, 4, G, 1, nullptr);
-      fj::launch_gather_quant_matmul(ctx, m->act_ep, dt, L.down.packed, L.down.scales, L.down.biases, dt, nullptr, nullptr, nullptr, m->recv_experts, m->down_ep, FJ_F32, slots, I,
-                                     m->experts_local, H, 1, 4, G, 0, nullptr);
-      status = ep_all_to_all(m->ep, m->down_ep, m->returned, static_cast<size_t>(cap) * H * 4);
+      cudaMemcpyAsync(m->ep_counts_host, m->ep_counts, 2 * W * 4, cudaMemcpyDeviceToHost, be->stream);
+      if (cudaStreamSynchronize(be->stream) != cudaSuccess) { status = FJ_DEVICE_EXECUTION_FAILED; break; }
+      const unsigned* send_counts = m->ep_counts_host;
+      const unsigned* recv_counts = m->ep_counts_host + W;
+      std::vector<unsigned> slab_at(W), packed_at(W);
+      unsigned received = 0;
+      for (unsigned p = 0; p < W; ++p) { slab_at[p] = p * cap; packed_at[p] = received; received += recv_counts[p]; }
+      if (received > W * cap) { status = FJ_EXECUTION_FAILED; break; }
+      status = ep_all_to_all_rows(m->ep, m->send_rows, slab_at.data(), send_counts, m->recv_rows, packed_at.data(), recv_counts, static_cast<size_t>(H) * 2);
+      if (status == FJ_OK) status = ep_all_to_all_rows(m->ep, m->send_experts, slab_at.data(), send_counts, m->recv_experts, packed_at.data(), recv_counts, 4);
+      if (status != FJ_OK) break;
+      if (received) {
+        // rows received for this rank's experts, densely packed by source: one route each
+        if (received >= kGroupedRoutes && G == 64 && fj::grouped_q4_supported(H, I, 4, G, m->experts_local, m->recv_rows, L.gate.packed) &&
+            fj::grouped_q4_supported(I, H, 4, G, m->experts_local, m->act_ep, L.down.packed)) {
+          fj::launch_route_plan(ctx, m->recv_experts, received, m->experts_local, m->route_plan);
+          fj::launch_grouped_q4_pair(ctx, m->recv_rows, L.gate.packed, L.gate.scales, L.gate.biases, L.up.packed, L.up.scales, L.up.biases, m->route_plan, received, m->experts_local, 1,
+                                     m->act_ep, H, I);
+          fj::launch_grouped_q4_single(ctx, m->act_ep, L.down.packed, L.down.scales, L.down.biases, m->route_plan, received, m->experts_local, 1, m->down_ep, I, H);
+        } else {
+          fj::launch_gather_quant_matmul(ctx, m->recv_rows, dt, L.gate.packed, L.gate.scales, L.gate.biases, dt, L.up.packed, L.up.scales, L.up.biases, m->recv_experts, m->act_ep, dt,
+                                         received, H, m->experts_local, I, 1, 4, G, 1, nullptr);
+          fj::launch_gather_quant_matmul(ctx, m->act_ep, dt, L.down.packed, L.down.scales, L.down.biases, dt, nullptr, nullptr, nullptr, m->recv_experts, m->down_ep, FJ_F32, received, I,
+                                         m->experts_local, H, 1, 4, G, 0, nullptr);
+        }
+      }
+      status = ep_all_to_all_rows(m->ep, m->down_ep, packed_at.data(), recv_counts, m->returned, slab_at.data(), send_counts, static_cast<size_t>(H) * 4);
       if (status != FJ_OK) break;
       if (rows) {
-        ep_combine_kernel<<<std::min(rows, 1024u), 256, 0, be->stream>>>(m->returned, m->route_slot, m->route_weights, static_cast<const unsigned short*>(hidden),
+        ep_combine_kernel<<<std::min(rows, 1024u), 256, 0, be->stream>>>(m->returned, m->route_slot, nullptr, 0, m->route_weights, static_cast<const unsigned short*>(hidden),
                                                                          static_cast<unsigned short*>(other), rows, K, H);
         ctx.launches++;
       }

@@ -340,6 +340,12 @@ int32_t fj_paged_decode_attention_static(fj_backend* be, const void* q, void* ou
                                          uint32_t lanes, uint32_t table_pages, uint32_t physical_pages, uint32_t q_heads,
                                          uint32_t kv_heads, uint32_t dtype, float scale, uint32_t* status);
 
+/* Synthetic contents for benchmarks (no counterpart in the reference, whose weights come from
+ * checkpoints): fills `elements` values of a buffer starting at offset_bytes with a counter-based
+ * generator: normal(mean, std) for float dtypes, uniform 32-bit words for FJ_U32 / FJ_I32. */
+int32_t fj_fill_random(fj_backend* be, uint64_t buffer, uint64_t offset_bytes, uint64_t elements, uint32_t dtype, uint64_t seed,
+                       float mean, float std);
+
 /* Expert parallelism over the GPUs of one node. The reference is single-GPU, so these entry points
  * have no counterpart there; they carry the all-to-all of the sparse-MoE step below. NCCL is opened
  * at run time (path of libnccl.so.2, or NULL for the loader's search path); one rank creates the
@@ -369,6 +375,9 @@ typedef struct fj_moe_config {
   uint32_t group_size, router_bits;
   float eps, theta;
   uint32_t max_rows; /* largest number of token rows in one step */
+  /* Expert projections switch from one pass per route to expert-bucketed tile GEMMs (weights rounded
+   * to bf16) at this many routes; 0 = 128. A value above max_rows * top_k keeps the per-route path. */
+  uint32_t grouped_min_routes;
 } fj_moe_config;
 typedef struct fj_moe_layer_weights {
   uint64_t input_norm, q_norm, k_norm, post_norm; /* bf16 [hidden], [head_dim], [head_dim], [hidden] */

@@ -15,7 +15,8 @@ from oracle import engine  # noqa: E402  (weight generator only)
 from tests.test_gpu_moe import upload_moe  # noqa: E402
 
 CFG = dict(layers=2, hidden=512, q_heads=8, kv_heads=1, head_dim=128, experts=16, top_k=4, expert_intermediate=192, vocab=1024,
-           group_size=64, router_bits=8, eps=1e-6, theta=1e7, max_rows=64)
+           group_size=64, router_bits=8, eps=1e-6, theta=1e7, max_rows=64,
+           grouped_min_routes=1 << 30)  # per-route projections on both sides: the comparison below is bit for bit
 
 
 def main():
