@@ -1,0 +1,214 @@
+"""Benchmarks of the rows next to the headline decode path: the sparse-MoE step with expert
+parallelism (Qwen3-30B-A3B shape), the isolated q4 projection and the isolated paged attention.
+`python -m forja_b200.benchmarks moe --gpus N` (under torch.distributed.run for N > 1, one rank per
+GPU) prints one JSON line on rank 0. Weights and KV contents are synthetic (counter-based generator
+on the device); timing is CUDA events on the backend's stream, maximum over ranks.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import time
+
+import numpy as np
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+import forja_b200 as fb  # noqa: E402
+
+PAGE = 16
+MOE = dict(layers=48, hidden=2048, q_heads=32, kv_heads=4, head_dim=128, experts=128, top_k=8, expert_intermediate=768, vocab=151936,
+           group_size=64, router_bits=8, eps=1e-6, theta=1e7)
+
+
+def quant_tensor(be, shape_n, k, bits, seed):
+    """Random MLX-affine tensor on the device: uniform codes, scales near 0.006, biases centring the groups."""
+    lead = tuple(shape_n) if isinstance(shape_n, (tuple, list)) else (shape_n,)
+    packed = be.alloc(fb.U32, lead + (k * bits // 32,))
+    scales = be.alloc(fb.BF16, lead + (k // 64,))
+    biases = be.alloc(fb.BF16, lead + (k // 64,))
+    spread = 0.006 if bits == 4 else 0.006 / 16
+    centre = (2 ** bits - 1) / 2.0
+    be.fill_random(packed, seed)
+    be.fill_random(scales, seed + 1, mean=spread, std=spread * 0.15)
+    be.fill_random(biases, seed + 2, mean=-centre * spread, std=spread * 0.5)
+    return packed, scales, biases
+
+
+def gain(be, n, seed):
+    t = be.alloc(fb.BF16, (n,))
+    be.fill_random(t, seed, mean=1.0, std=0.02)
+    return t
+
+
+def build_moe(be, pool, cfg, ep, rank, world):
+    per = cfg["experts"] // world
+    H, I, d = cfg["hidden"], cfg["expert_intermediate"], cfg["head_dim"]
+    qd, kd = cfg["q_heads"] * d, cfg["kv_heads"] * d
+    seed = 1000  # replicated tensors use the same seeds on every rank; expert slices differ by rank
+    embed = quant_tensor(be, cfg["vocab"], H, 4, seed)
+    lm_head = quant_tensor(be, cfg["vocab"], H, 4, seed + 10)
+    final_norm = gain(be, H, seed + 20)
+    layers = []
+    for layer in range(cfg["layers"]):
+        s = seed + 100 * (layer + 1)
+        layers.append({
+            "input_norm": gain(be, H, s), "q_norm": gain(be, d, s + 1), "k_norm": gain(be, d, s + 2), "post_norm": gain(be, H, s + 3),
+            "qkv": quant_tensor(be, qd + 2 * kd, H, 4, s + 10), "o": quant_tensor(be, H, qd, 4, s + 20),
+            "router": quant_tensor(be, cfg["experts"], H, cfg["router_bits"], s + 30),
+            "gate": quant_tensor(be, (per, I), H, 4, s + 40 + 7919 * rank), "up": quant_tensor(be, (per, I), H, 4, s + 50 + 7919 * rank),
+            "down": quant_tensor(be, (per, H), I, 4, s + 60 + 7919 * rank)})
+    return fb.MoeModel(be, pool, cfg, embed, final_norm, lm_head, layers, ep=ep)
+
+
+class MoeLanes:
+    """Continuous batch of one rank: prompts uniform 512-4096 prefilled in 512-token pieces under a
+    per-step prompt budget (the library's scheduler policy), then 64-256 decode steps; a finished
+    lane is refilled with the next request."""
+
+    def __init__(self, pool, lanes, seed, prompt_budget, prefill_limit, prompt_range, decode_only):
+        self.pool, self.n = pool, lanes
+        self.rng = np.random.default_rng(seed)
+        self.prompt_range, self.decode_only = prompt_range, decode_only
+        self.policy = fb.SchedulerPolicy([1, lanes] if lanes > 1 else [1], lanes, prefill_limit, prompt_budget, prompt_budget).with_prompt_chunk_multiple(512)
+        self.length = np.zeros(lanes, np.int64)       # tokens already in the cache
+        self.prompt_left = np.zeros(lanes, np.int64)
+        self.decode_left = np.zeros(lanes, np.int64)
+        for lane in range(lanes):
+            self.refill(lane)
+
+    def refill(self, lane):
+        prompt = int(self.rng.integers(self.prompt_range[0], self.prompt_range[1] + 1))
+        budget = int(self.rng.integers(64, 257))
+        self.pool.reserve([lane], [prompt + budget + 1], want_status=False)
+        if self.decode_only:  # the prompt is taken as already cached (KV planes hold random contents)
+            self.length[lane], self.prompt_left[lane] = prompt, 0
+        else:
+            self.length[lane], self.prompt_left[lane] = 0, prompt
+            self.policy.ready_prompt(lane, prompt)
+        self.decode_left[lane] = budget
+
+    def plan(self):
+        """(starts, tokens) of this step."""
+        tokens = np.zeros(self.n, np.uint32)
+        decoding = (self.prompt_left == 0) & (self.decode_left > 0)
+        tokens[decoding] = 1
+        for lane, spend in self.policy.prompt_batch(bool(decoding.any())):
+            tokens[lane] = spend
+        return self.length.astype(np.uint32), tokens
+
+    def advance(self, tokens):
+        done = []
+        for lane in np.nonzero(tokens)[0].tolist():
+            t = int(tokens[lane])
+            self.length[lane] += t
+            if self.prompt_left[lane] > 0:
+                self.prompt_left[lane] -= t
+            else:
+                self.decode_left[lane] -= 1
+                if self.decode_left[lane] == 0:
+                    done.append(lane)
+        if done:
+            self.pool.release(done)
+            for lane in done:
+                self.refill(lane)
+
+
+def run_moe(args):
+    rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
+    local_rank = int(os.environ.get("LOCAL_RANK", 0))
+    dist = None
+    if world > 1:
+        import torch.distributed as dist_mod
+        dist = dist_mod
+        dist.init_process_group("gloo", rank=rank, world_size=world)
+    cfg = dict(MOE)
+    if args.layers:
+        cfg["layers"] = args.layers
+    lanes = args.lanes // world
+    cfg["max_rows"] = lanes + (0 if args.decode_only else args.prompt_budget)
+    be = fb.CudaBackend(local_rank)
+    ep = None
+    if world > 1:
+        def exchange(mine):
+            box = [mine]
+            dist.broadcast_object_list(box, src=0)
+            return box[0]
+        ep = fb.ExpertParallel(be, rank, world, exchange)
+    table_pages = (args.prompt_max + 256 + 1 + PAGE - 1) // PAGE + 1
+    pool = fb.KvPool(be, PAGE, lanes * table_pages + 8, lanes, table_pages)
+    model = build_moe(be, pool, cfg, ep, rank, world)
+    state = MoeLanes(pool, lanes, args.seed + rank, args.prompt_budget, args.prefill_limit, (args.prompt_min, args.prompt_max), args.decode_only)
+    rng = np.random.default_rng(args.seed + 77 + rank)
+    t0, t1 = be.timer(), be.timer()
+    processed = 0
+    kernels = 0
+    for step in range(args.warmup + args.steps):
+        if step == args.warmup:
+            be.synchronize()
+            if dist is not None:
+                dist.barrier()
+            be.timer_record(t0)
+            processed, kernels = 0, 0
+        starts, tokens = state.plan()
+        rows = int(tokens.sum())
+        pool.pack_step(starts, tokens)
+        ids = rng.integers(0, cfg["vocab"], rows).astype(np.uint32) if rows else None
+        model.step(ids, want_tokens=rows > 0, lanes=lanes)
+        kernels += model.stats()["kernels"]
+        state.advance(tokens)
+        processed += rows
+    be.timer_record(t1)
+    be.synchronize()
+    elapsed = be.timer_elapsed_ns(t0, t1) * 1e-9
+    total = processed
+    if dist is not None:
+        import torch
+        box = torch.tensor([elapsed, float(processed), float(kernels)], dtype=torch.float64)
+        gathered = [torch.zeros_like(box) for _ in range(world)]
+        dist.all_gather(gathered, box)
+        elapsed = max(float(g[0]) for g in gathered)
+        total = int(sum(float(g[1]) for g in gathered))
+        kernels = int(sum(float(g[2]) for g in gathered))
+        dist.barrier()
+    if rank == 0:
+        print(json.dumps({
+            "metric": "moe step tok/s (prompt + generated tokens)", "value": total / elapsed, "unit": "tok/s", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": elapsed / args.steps * 1e3, "higher_is_better": True, "scaling": "strong", "dtype": "bf16 activations, q4 weights",
+            "data": "synthetic", "gpu_launches": kernels,
+            "config": {"workload": "qwen3-30b-a3b-arch q4 sparse-MoE continuous batching" + (" (decode only)" if args.decode_only else " (chunked prefill + decode)"),
+                       "lanes_total": args.lanes, "lanes_per_gpu": lanes, "layers": cfg["layers"], "prompt_tokens": [args.prompt_min, args.prompt_max],
+                       "prompt_budget_per_gpu_step": 0 if args.decode_only else args.prompt_budget,
+                       "parallelism": "experts sharded over %d GPUs, NCCL send/recv all-to-all per MoE layer; lanes data-parallel" % world if world > 1 else "single GPU"}}))
+    model.close()
+    pool.close()
+    if ep is not None:
+        ep.close()
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser(description=__doc__)
+    sub = ap.add_subparsers(dest="command", required=True)
+    moe = sub.add_parser("moe")
+    moe.add_argument("--gpus", type=int, default=1, help="informational; the rank count comes from the launcher's environment")
+    moe.add_argument("--lanes", type=int, default=256)
+    moe.add_argument("--steps", type=int, default=16)
+    moe.add_argument("--warmup", type=int, default=3)
+    moe.add_argument("--layers", type=int, default=0)
+    moe.add_argument("--seed", type=int, default=0)
+    moe.add_argument("--prompt-min", type=int, default=512)
+    moe.add_argument("--prompt-max", type=int, default=4096)
+    moe.add_argument("--prompt-budget", type=int, default=2048)
+    moe.add_argument("--prefill-limit", type=int, default=4)
+    moe.add_argument("--decode-only", action="store_true")
+    args = ap.parse_args()
+    if args.command == "moe":
+        run_moe(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -724,6 +724,21 @@ int32_t exec_paged_attention_run(Exec& x, const fj_dispatch* ds, uint32_t count,
     }
   }
   if (!mma) {
+    // longer query runs (prefill chunks): 64-row tensor-core blocks when the shape allows, else the f32 kernel
+    bool blocks = fj::attn_prefill_mma_supported(g);
+    for (auto& s : seqs) {
+      if ((reinterpret_cast<size_t>(s.q) & 3) || (s.q_tok_stride & 1) || (s.q_head_stride & 1)) blocks = false;
+    }
+    if (blocks) {
+      const unsigned per_block = fj::attn_prefill_tokens_per_block(g);
+      std::vector<uint2> items;
+      for (uint32_t i = 0; i < count; ++i)
+        for (unsigned t = 0; t < seqs[i].q_len; t += per_block) items.push_back(make_uint2(i, t));
+      uint2* dev_items = x.upload(items);
+      if (!dev_items) return FJ_ALLOCATION_FAILED;
+      fj::launch_attn_prefill_mma(x.be->ctx, g, dev_seqs, dev_items, static_cast<unsigned>(items.size()), kp, vp, gp, err);
+      return FJ_OK;
+    }
     fj::launch_attn_generic(x.be->ctx, g, dev_seqs, count, max_q_len, kp, vp, gp, err);
     return FJ_OK;
   }

@@ -87,6 +87,13 @@ bool attn_decode_mma_supported(const AttnGeometry& g, unsigned max_q_len);
 void launch_attn_decode_mma(Ctx& ctx, const AttnGeometry& g, const AttnSeq* seqs, const AttnWork* work, unsigned n_work,
                             const void* kpool, const void* vpool, const unsigned* generations, const AttnScratch& scratch,
                             ErrorRecord* err);
+// Chunked-prefill attention on tensor cores for any q_len: same shape limits as the decode kernel and
+// q_heads / kv_heads in {1, 2, 4, 8, 16}. One CTA per item {sequence, first token of a block of
+// attn_prefill_tokens_per_block tokens} and KV head; the caller lists every block of every sequence.
+bool attn_prefill_mma_supported(const AttnGeometry& g);
+unsigned attn_prefill_tokens_per_block(const AttnGeometry& g);
+void launch_attn_prefill_mma(Ctx& ctx, const AttnGeometry& g, const AttnSeq* seqs, const uint2* items, unsigned n_items, const void* kpool, const void* vpool,
+                             const unsigned* generations, ErrorRecord* err);
 // Generic f32-math attention for any float dtypes, head_dim <= 256, any q_len (one CTA per
 // (sequence, head, query row)); used for f32 models and odd shapes.
 void launch_attn_generic(Ctx& ctx, const AttnGeometry& g, const AttnSeq* seqs, unsigned n_seqs, unsigned max_q_len,

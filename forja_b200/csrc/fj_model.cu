@@ -10,6 +10,7 @@
 #include <string.h>
 
 #include <algorithm>
+#include <vector>
 
 using namespace fjb;
 
@@ -201,6 +202,8 @@ struct fj_dense_model {
   fj::AttnWork* work = nullptr;
   unsigned* n_work_dev = nullptr;
   uint32_t work_cap = 0;
+  uint2* prefill_items = nullptr;  // {lane, first token} blocks of the chunked-prefill attention
+  uint32_t prefill_items_cap = 0;
   const float* inv_freq = nullptr;
   uint64_t last_kernels = 0, last_work_items = 0;
   // attention timing (CUDA event pairs on the backend's stream)
@@ -359,6 +362,8 @@ int32_t fj_dense_model_create(fj_backend* be, const fj_dense_config* config, uin
   m->work_cap = static_cast<uint32_t>(std::min<uint64_t>((token_capacity / 64 + Lanes) * c.kv_heads, 1u << 22));
   m->work = static_cast<fj::AttnWork*>(dev_alloc(static_cast<size_t>(m->work_cap) * sizeof(fj::AttnWork)));
   m->n_work_dev = static_cast<unsigned*>(dev_alloc(16));
+  m->prefill_items_cap = static_cast<uint32_t>(R + Lanes);
+  m->prefill_items = static_cast<uint2*>(dev_alloc(static_cast<size_t>(m->prefill_items_cap) * sizeof(uint2)));
   if (ok) {
     m->inv_freq = c.qk_norm ? freq_table(be, c.theta, -2.0f / static_cast<float>(c.head_dim), c.head_dim / 2, false)
                             : freq_table(be, c.theta, 0.0f, c.head_dim / 2, true);
@@ -428,6 +433,17 @@ int32_t fj_dense_step(fj_dense_model* m, const uint32_t* token_ids, uint32_t* ou
   }
   fj::launch_build_attn_lists(ctx, pool->dev, pool->pack, lanes, c.kv_heads, static_cast<unsigned>(chunk), m->q, m->attn, c.q_heads, c.head_dim, static_cast<int>(esz), m->seqs,
                               m->work, m->n_work_dev, m->work_cap);
+  // query runs too long for the decode kernel: 64-row tensor-core blocks, listed by the host from the packed step
+  unsigned n_blocks = 0;
+  if (!mma && fj::attn_prefill_mma_supported(g)) {
+    const unsigned per_block = fj::attn_prefill_tokens_per_block(g);
+    std::vector<uint2> items;
+    for (unsigned l = 0; l < lanes; ++l)
+      for (unsigned t = 0; t < pool->host_tokens[l]; t += per_block) items.push_back(make_uint2(l, t));
+    if (items.size() > m->prefill_items_cap) return FJ_QUOTA_EXCEEDED;
+    n_blocks = static_cast<unsigned>(items.size());
+    cudaMemcpyAsync(m->prefill_items, items.data(), items.size() * sizeof(uint2), cudaMemcpyHostToDevice, be->stream);  // pageable source: staged before the call returns
+  }
   fj::AttnScratch scratch{nullptr, nullptr, nullptr};
   if (mma) {
     const size_t groups = static_cast<size_t>(lanes) * c.kv_heads;
@@ -452,6 +468,7 @@ int32_t fj_dense_step(fj_dense_model* m, const uint32_t* token_ids, uint32_t* ou
     cudaEvent_t attn_begin = nullptr, attn_end = nullptr;
     if (m->profile_attention) { attn_begin = m->take_event(); attn_end = m->take_event(); cudaEventRecord(attn_begin, be->stream); }
     if (mma) fj::launch_attn_decode_mma(ctx, g, m->seqs, m->work, static_cast<unsigned>(n_work), L.k_plane, L.v_plane, pool->dev.generations, scratch, nullptr);
+    else if (n_blocks) fj::launch_attn_prefill_mma(ctx, g, m->seqs, m->prefill_items, n_blocks, L.k_plane, L.v_plane, pool->dev.generations, nullptr);
     else fj::launch_attn_generic(ctx, g, m->seqs, lanes, max_q_len, L.k_plane, L.v_plane, pool->dev.generations, nullptr);
     if (m->profile_attention) { cudaEventRecord(attn_end, be->stream); m->pending.emplace_back(attn_begin, attn_end); }
     fj::launch_gemm_nt(ctx, m->attn, dt, qd, L.wo, dt, qd, m->proj, dt, H, rows, H, qd, be->gemm_scratch, be->gemm_scratch_bytes);

@@ -261,6 +261,8 @@ struct fj_moe_model {
   fj::AttnWork* work = nullptr;
   unsigned* n_work_dev = nullptr;
   uint32_t work_cap = 0;
+  uint2* prefill_items = nullptr;  // {lane, first token} blocks of the chunked-prefill attention
+  uint32_t prefill_items_cap = 0;
   const float* inv_freq = nullptr;
   uint64_t last_kernels = 0, last_work_items = 0;
 };
@@ -363,6 +365,8 @@ int32_t fj_moe_model_create(fj_backend* be, const fj_moe_config* config, const f
   m->work_cap = static_cast<uint32_t>(std::min<uint64_t>((token_capacity / 64 + Lanes) * c.kv_heads, 1u << 22));
   m->work = static_cast<fj::AttnWork*>(dev_alloc(static_cast<size_t>(m->work_cap) * sizeof(fj::AttnWork)));
   m->n_work_dev = static_cast<unsigned*>(dev_alloc(16));
+  m->prefill_items_cap = static_cast<uint32_t>(R + Lanes);
+  m->prefill_items = static_cast<uint2*>(dev_alloc(static_cast<size_t>(m->prefill_items_cap) * sizeof(uint2)));
   if (std::max(R, Lanes) > 16) {
     // slab of dequantised weights for projections with more than 16 rows (tensor-core GEMM path)
     const uint64_t widest = std::max<uint64_t>({qd + 2 * kd, H, static_cast<uint64_t>(c.vocab)});
@@ -454,6 +458,7 @@ extern "C" int32_t fj_moe_step(fj_moe_model* m, const uint32_t* token_ids, uint3
   const bool mma = rows != 0 && fj::attn_decode_mma_supported(g, max_q_len) && max_q_len * group <= 16;
   uint64_t chunk = 64, n_work = 0;
   fj::AttnScratch scratch{nullptr, nullptr, nullptr};
+  unsigned n_blocks = 0;
   if (rows != 0) {
     if (mma) {
       const uint64_t target_items = static_cast<uint64_t>(ctx.sm_count) * 2 * 4;
@@ -474,6 +479,15 @@ extern "C" int32_t fj_moe_step(fj_moe_model* m, const uint32_t* token_ids, uint3
       scratch.part_o = reinterpret_cast<float*>(static_cast<char*>(be->attn_scratch) + counter_bytes);
       scratch.part_ml = reinterpret_cast<float*>(static_cast<char*>(be->attn_scratch) + counter_bytes + o_bytes);
     }
+    if (!mma && fj::attn_prefill_mma_supported(g)) {
+      const unsigned per_block = fj::attn_prefill_tokens_per_block(g);
+      std::vector<uint2> items;
+      for (unsigned l = 0; l < lanes; ++l)
+        for (unsigned t = 0; t < pool->host_tokens[l]; t += per_block) items.push_back(make_uint2(l, t));
+      if (items.size() > m->prefill_items_cap) return FJ_QUOTA_EXCEEDED;
+      n_blocks = static_cast<unsigned>(items.size());
+      cudaMemcpyAsync(m->prefill_items, items.data(), items.size() * sizeof(uint2), cudaMemcpyHostToDevice, be->stream);  // pageable source: staged before the call returns
+    }
     if (token_ids) cudaMemcpyAsync(m->tokens_in, token_ids, static_cast<size_t>(rows) * 4, cudaMemcpyHostToDevice, be->stream);
     else launch_feedback_tokens(ctx, pool->pack.cu_seqlens, m->tokens_out, m->tokens_in, lanes);
     fj::launch_quant_embed(ctx, m->embed.packed, m->embed.scales, m->embed.biases, dt, m->tokens_in, m->hidden, dt, c.vocab, H / 8, rows, 4, G, nullptr);
@@ -490,6 +504,7 @@ extern "C" int32_t fj_moe_step(fj_moe_model* m, const uint32_t* token_ids, uint3
       fj::launch_qknorm_rope_append(ctx, m->qkv, dt, L.q_norm, L.k_norm, pool->pack.positions, pool->pack.slot_mapping, m->q, L.k_plane, L.v_plane, rows, c.q_heads, c.kv_heads,
                                     c.head_dim, c.eps, m->inv_freq, 1, plane_slots);
       if (mma) fj::launch_attn_decode_mma(ctx, g, m->seqs, m->work, static_cast<unsigned>(n_work), L.k_plane, L.v_plane, pool->dev.generations, scratch, nullptr);
+      else if (n_blocks) fj::launch_attn_prefill_mma(ctx, g, m->seqs, m->prefill_items, n_blocks, L.k_plane, L.v_plane, pool->dev.generations, nullptr);
       else fj::launch_attn_generic(ctx, g, m->seqs, lanes, max_q_len, L.k_plane, L.v_plane, pool->dev.generations, nullptr);
       q4(m->attn, L.o, m->proj, dt, rows, qd, H, 4);
       fj::launch_residual_norm(ctx, dense_view(hidden, dt, rows, H, H), dense_view(m->proj, dt, rows, H, H), weight_view(L.post_norm, dt, rows, H), dense_view(other, dt, rows, H, H),

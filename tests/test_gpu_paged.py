@@ -280,3 +280,56 @@ def test_long_context_split_k_matches_oracle():
     want = fjo.paged_sdpa(np.ascontiguousarray(qh.transpose(1, 0, 2)), dt, kh, dt, vh, dt, table, generations, length, length - 1, scale, True, page)
     fjo.set_threads(1)
     assert_close(down(out).transpose(1, 0, 2), fjo.decode(want, dt), TOL[dt])
+
+
+@pytest.mark.parametrize("hq,kvh", [(32, 4), (16, 8), (8, 8), (16, 1)])
+@pytest.mark.parametrize("q_len,q_start", [(512, 0), (512, 1536), (70, 33), (9, 1000), (257, 15)])
+def test_chunked_prefill_attention_on_tensor_cores_matches_oracle(hq, kvh, q_len, q_start):
+    """Prefill chunks (config 3: 32 q / 4 kv heads, d 128, 512-token chunks) and ragged tails through
+    the 64-row tensor-core blocks: permuted pages, causal limit per row, chunk start inside a page."""
+    rng = np.random.default_rng(q_len * 7 + q_start + hq)
+    be = backend()
+    dt, page, d = fb.BF16, 16, 128
+    key_length = q_start + q_len
+    physical = (key_length + page - 1) // page + 3
+    table, generations = random_table(rng, key_length, page, physical)
+    kt, kh, vt, vh = fill_pools(rng, physical, page, kvh, d, dt)
+    q, qh = up(rng.standard_normal((q_len, hq, d)), dt)
+    out = be.alloc(dt, (q_len, hq, d))
+    scale = float(np.float32(1.0) / np.sqrt(np.float32(d)))
+    be.run(Op.PagedSdpa(scale, True, q_start, key_length, page), [q.permute([1, 0, 2]), kt, vt, up_u32(table)[0], up_u32(generations)[0]], [out.permute([1, 0, 2])])
+    fjo.set_threads(fjo.max_threads())
+    want = fjo.paged_sdpa(np.ascontiguousarray(qh.transpose(1, 0, 2)), dt, kh, dt, vh, dt, table, generations, key_length, q_start, scale, True, page)
+    fjo.set_threads(1)
+    got = down(out).transpose(1, 0, 2)
+    assert_close(got, fjo.decode(want, dt), TOL[dt])
+    assert max_abs_rel(got, fjo.decode(want, dt)) <= 2e-2
+
+
+def test_prefill_attention_non_causal_inactive_and_corrupt_lanes():
+    rng = np.random.default_rng(77)
+    be = backend()
+    dt, page, d, hq, kvh, q_len, key_length = fb.BF16, 16, 128, 16, 8, 40, 100
+    physical = key_length // page + 4
+    table, generations = random_table(rng, key_length, page, physical)
+    kt, kh, vt, vh = fill_pools(rng, physical, page, kvh, d, dt)
+    q, qh = up(rng.standard_normal((q_len, hq, d)), dt)
+    scale = 0.088388346
+    # non-causal: every row attends to all 100 keys
+    out = be.alloc(dt, (q_len, hq, d))
+    be.run(Op.PagedSdpa(scale, False, 0, key_length, page), [q.permute([1, 0, 2]), kt, vt, up_u32(table)[0], up_u32(generations)[0]], [out.permute([1, 0, 2])])
+    want = fjo.paged_sdpa(np.ascontiguousarray(qh.transpose(1, 0, 2)), dt, kh, dt, vh, dt, table, generations, key_length, 0, scale, False, page)
+    assert_close(down(out).transpose(1, 0, 2), fjo.decode(want, dt), TOL[dt])
+    # inactive lane: zeros, whatever the output held before
+    out2, _ = up(np.ones((q_len, hq, d)), dt)
+    idle, _ = up_u32(np.zeros(1, np.uint32))
+    be.run(Op.PagedSdpa(scale, True, 60, key_length, page), [q.permute([1, 0, 2]), kt, vt, up_u32(table)[0], up_u32(generations)[0], idle], [out2.permute([1, 0, 2])])
+    assert np.all(down(out2) == 0.0)
+    # a stale generation in a page the chunk needs: error flag with the logical page, zero rows
+    bad = table.copy()
+    bad[2, 1] += 1
+    out3 = be.alloc(dt, (q_len, hq, d))
+    with pytest.raises(fb.BackendError) as info:
+        be.run(Op.PagedSdpa(scale, True, 60, key_length, page), [q.permute([1, 0, 2]), kt, vt, up_u32(bad)[0], up_u32(generations)[0]], [out3.permute([1, 0, 2])])
+    assert info.value.flag == 2 and info.value.index == 2
+    assert np.all(down(out3) == 0.0)
