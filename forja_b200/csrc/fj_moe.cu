@@ -158,26 +158,17 @@ int32_t ep_all_to_all_rows(fj_ep* ep, const void* send, const unsigned* send_row
 }
 
 // ---- expert-parallel dispatch / combine kernels -------------------------------------------------
-// One thread walks the routes in (row, j) order and hands each the next slot of its destination's slab,
-// so slot numbers are deterministic. Unused slots keep expert id `experts_local` (out of range: the
-// expert kernels write zeros for them without touching any weight).
+// Every route takes the next free slot of its destination's slab (atomic counter per destination,
+// zeroed by the caller). Which slot a route gets does not matter: results come back by slot.
 __global__ void ep_plan_kernel(const unsigned* __restrict__ indices, unsigned routes, unsigned experts_local, unsigned world, unsigned capacity,
                                unsigned* send_experts, unsigned* route_slot, unsigned* send_counts) {
-  extern __shared__ unsigned ep_smem[];
-  unsigned* next = ep_smem;  // [world] running slot per destination
-  for (unsigned i = threadIdx.x; i < world; i += blockDim.x) next[i] = 0;
-  for (unsigned i = threadIdx.x; i < world * capacity; i += blockDim.x) send_experts[i] = experts_local;
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    for (unsigned r = 0; r < routes; ++r) {
-      const unsigned expert = indices[r];
-      const unsigned dest = expert / experts_local;
-      if (dest >= world) { route_slot[r] = 0xFFFFFFFFu; continue; }  // bad expert id: contributes nothing
-      const unsigned slot = dest * capacity + next[dest]++;
-      route_slot[r] = slot;
-      send_experts[slot] = expert - dest * experts_local;
-    }
-    for (unsigned d = 0; d < world; ++d) send_counts[d] = next[d];
+  for (unsigned r = blockIdx.x * blockDim.x + threadIdx.x; r < routes; r += gridDim.x * blockDim.x) {
+    const unsigned expert = indices[r];
+    const unsigned dest = expert / experts_local;
+    if (dest >= world) { route_slot[r] = 0xFFFFFFFFu; continue; }  // bad expert id: contributes nothing
+    const unsigned slot = dest * capacity + atomicAdd(&send_counts[dest], 1u);
+    route_slot[r] = slot;
+    send_experts[slot] = expert - dest * experts_local;
   }
 }
 
@@ -533,20 +524,34 @@ extern "C" int32_t fj_moe_step(fj_moe_model* m, const uint32_t* token_ids, uint3
       }
     } else {
       const unsigned cap = m->capacity, routes = rows * K, W = m->world;
-      ep_plan_kernel<<<1, 256, W * sizeof(unsigned), be->stream>>>(m->route_experts, routes, m->experts_local, W, cap, m->send_experts, m->route_slot, m->ep_counts);
-      ctx.launches++;
-      if (routes) { ep_scatter_rows_kernel<<<std::min(routes, 4096u), 128, 0, be->stream>>>(static_cast<const unsigned short*>(m->normed), m->route_slot, routes, K, H, m->send_rows); ctx.launches++; }
-      // how many rows every peer will send here: one 4-byte exchange, then both count vectors go to the host
-      status = ep_all_to_all(m->ep, m->ep_counts, m->ep_counts + W, 4);
-      if (status != FJ_OK) break;
-      cudaMemcpyAsync(m->ep_counts_host, m->ep_counts, 2 * W * 4, cudaMemcpyDeviceToHost, be->stream);
-      if (cudaStreamSynchronize(be->stream) != cudaSuccess) { status = FJ_DEVICE_EXECUTION_FAILED; break; }
-      const unsigned* send_counts = m->ep_counts_host;
-      const unsigned* recv_counts = m->ep_counts_host + W;
-      std::vector<unsigned> slab_at(W), packed_at(W);
+      // Small steps (decode): whole slabs of `cap` slots travel, padded with an out-of-range expert id, and
+      // nothing has to come back to the host. Large steps: the row counts are exchanged and read back first
+      // so that only live rows travel. The choice depends on the model's capacity only, so all ranks agree.
+      const bool padded = cap <= 1024;
+      cudaMemsetAsync(m->ep_counts, 0, 2 * W * 4, be->stream);
+      if (padded) cudaMemsetAsync(m->send_experts, 0xFF, static_cast<size_t>(W) * cap * 4, be->stream);
+      if (routes) {
+        ep_plan_kernel<<<std::min((routes + 255) / 256, 256u), 256, 0, be->stream>>>(m->route_experts, routes, m->experts_local, W, cap, m->send_experts, m->route_slot, m->ep_counts);
+        ep_scatter_rows_kernel<<<std::min(routes, 4096u), 128, 0, be->stream>>>(static_cast<const unsigned short*>(m->normed), m->route_slot, routes, K, H, m->send_rows);
+        ctx.launches += 2;
+      }
+      std::vector<unsigned> slab_at(W), packed_at(W), slab_counts(W, cap);
+      const unsigned *send_counts = slab_counts.data(), *recv_counts = slab_counts.data();
       unsigned received = 0;
-      for (unsigned p = 0; p < W; ++p) { slab_at[p] = p * cap; packed_at[p] = received; received += recv_counts[p]; }
-      if (received > W * cap) { status = FJ_EXECUTION_FAILED; break; }
+      if (padded) {
+        for (unsigned p = 0; p < W; ++p) { slab_at[p] = p * cap; packed_at[p] = p * cap; }
+        received = W * cap;
+      } else {
+        // how many rows every peer will send here: one 4-byte exchange, then both count vectors go to the host
+        status = ep_all_to_all(m->ep, m->ep_counts, m->ep_counts + W, 4);
+        if (status != FJ_OK) break;
+        cudaMemcpyAsync(m->ep_counts_host, m->ep_counts, 2 * W * 4, cudaMemcpyDeviceToHost, be->stream);
+        if (cudaStreamSynchronize(be->stream) != cudaSuccess) { status = FJ_DEVICE_EXECUTION_FAILED; break; }
+        send_counts = m->ep_counts_host;
+        recv_counts = m->ep_counts_host + W;
+        for (unsigned p = 0; p < W; ++p) { slab_at[p] = p * cap; packed_at[p] = received; received += recv_counts[p]; }
+        if (received > W * cap) { status = FJ_EXECUTION_FAILED; break; }
+      }
       status = ep_all_to_all_rows(m->ep, m->send_rows, slab_at.data(), send_counts, m->recv_rows, packed_at.data(), recv_counts, static_cast<size_t>(H) * 2);
       if (status == FJ_OK) status = ep_all_to_all_rows(m->ep, m->send_experts, slab_at.data(), send_counts, m->recv_experts, packed_at.data(), recv_counts, 4);
       if (status != FJ_OK) break;

@@ -46,15 +46,24 @@ def main():
     rng = np.random.default_rng(100 + rank)
     ids = [rng.integers(0, CFG["vocab"], n).astype(np.uint32) for n in prompts]
 
+    for max_rows in (64, 300):  # slab capacity 256 (padded exchange, no host round trip) and 1200 (row counts exchanged first)
+        run_case(be, ep, rank, dict(CFG, max_rows=max_rows), weights, local, prompts, steps, page, lanes, table_pages, physical, ids)
+    dist.barrier()
+    ep.close()
+    dist.destroy_process_group()
+    print("EP_OK", rank)
+
+
+def run_case(be, ep, rank, cfg, weights, local, prompts, steps, page, lanes, table_pages, physical, ids):
     def build(w, group):
         pool = fb.KvPool(be, page, physical, lanes, table_pages)
         assert all(s == 0 for s in pool.reserve(list(range(lanes)), [n + steps + 1 for n in prompts]))
         embed, final_norm, lm_head, layers = upload_moe(be, w)
-        return pool, fb.MoeModel(be, pool, CFG, embed, final_norm, lm_head, layers, ep=group)
+        return pool, fb.MoeModel(be, pool, cfg, embed, final_norm, lm_head, layers, ep=group)
 
     pool_ep, model_ep = build(local, ep)
     pool_one, model_one = build(weights, None)
-    logits_ep, logits_one = be.alloc(fb.BF16, (lanes, CFG["vocab"])), be.alloc(fb.BF16, (lanes, CFG["vocab"]))
+    logits_ep, logits_one = be.alloc(fb.BF16, (lanes, cfg["vocab"])), be.alloc(fb.BF16, (lanes, cfg["vocab"]))
 
     def both(starts, counts, tokens):
         pool_ep.pack_step(starts, counts)
@@ -79,9 +88,7 @@ def main():
         model_ep.step(None, want_tokens=False, lanes=lanes)
     be.synchronize()
     dist.barrier()
-    model_ep.close(); model_one.close(); pool_ep.close(); pool_one.close(); ep.close()
-    dist.destroy_process_group()
-    print("EP_OK", rank)
+    model_ep.close(); model_one.close(); pool_ep.close(); pool_one.close()
 
 
 if __name__ == "__main__":
