@@ -363,6 +363,11 @@ class CudaBackend:
         """Synthetic contents for a whole contiguous tensor (normal for floats, random words for u32)."""
         _check(self._lib.fj_fill_random(self._h, tensor.buffer, tensor.layout.offset * DTYPE_SIZE[tensor.dtype], tensor.layout.element_count(), tensor.dtype, seed, mean, std))
 
+    def tcgen05_wait_giveups(self) -> int:
+        out = C.c_uint32(0)
+        _check(self._lib.fj_tcgen05_wait_giveups(self._h, C.byref(out)))
+        return out.value
+
     def synchronize(self):
         _check(self._lib.fj_synchronize(self._h))
 

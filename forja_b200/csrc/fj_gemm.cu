@@ -394,6 +394,11 @@ void launch_gemm_nt(Ctx& ctx, const void* a, int a_dt, size_t lda, const void* w
     }
     return;
   }
+  // enough 128 x 128 tiles to go round: TMEM-accumulator tiles; smaller grids keep the split-K mma.sync kernel
+  if (gemm_nt_tcgen05_supported(a_dt, w_dt, m, n, k, lda, ldw, a, w) && static_cast<size_t>((m + 127) / 128) * ((n + 127) / 128) >= 64) {
+    launch_gemm_nt_tcgen05(ctx, a, a_dt, lda, w, ldw, c, c_dt, ldc, m, n, k);
+    return;
+  }
   SplitPlan plan = plan_gemm(m, n, k, ctx.sm_count);
   const size_t need = static_cast<size_t>(plan.splits) * m * n * sizeof(float) + static_cast<size_t>(plan.tiles) * sizeof(unsigned);
   if (plan.splits > 1 && (scratch == nullptr || scratch_bytes < need || plan.tiles > 4096)) {

@@ -110,6 +110,10 @@ void launch_paged_copy(Ctx& ctx, bool into_pages, void* ordinary, int o_dt, size
 size_t gemm_scratch_bytes(unsigned m, unsigned n, unsigned k);
 void launch_gemm_nt(Ctx& ctx, const void* a, int a_dt, size_t lda, const void* w, int w_dt, size_t ldw, void* c, int c_dt,
                     size_t ldc, unsigned m, unsigned n, unsigned k, void* scratch, size_t scratch_bytes);
+// tcgen05 form (TMEM accumulators, 128 x 128 x 64 tiles, no split-K): bf16/f16, K % 64 == 0, 16-byte aligned rows.
+bool gemm_nt_tcgen05_supported(int a_dt, int w_dt, unsigned m, unsigned n, unsigned k, size_t lda, size_t ldw, const void* a, const void* w);
+void launch_gemm_nt_tcgen05(Ctx& ctx, const void* a, int a_dt, size_t lda, const void* w, size_t ldw, void* c, int c_dt, size_t ldc, unsigned m, unsigned n, unsigned k);
+unsigned gemm_tcgen05_giveups();  // bounded waits that ran out since the library was loaded (0 in a healthy run)
 // Fully strided fallback (any layout, batch): one thread per output element.
 void launch_matmul_generic(Ctx& ctx, const View& a, const View& b, const View& c, unsigned batch, unsigned m, unsigned n,
                            unsigned k);

@@ -532,6 +532,15 @@ int32_t fj_dense_fill_kv(fj_dense_model* m, uint64_t seed) {
   return cuda_status(cudaStreamSynchronize(be->stream));
 }
 
+int32_t fj_tcgen05_wait_giveups(fj_backend* be, uint32_t* out) {
+  if (!be || !out) return FJ_INVALID_INPUT;
+  std::lock_guard<std::mutex> lock(be->mutex);
+  cudaSetDevice(be->device);
+  cudaStreamSynchronize(be->stream);
+  *out = fj::gemm_tcgen05_giveups();
+  return FJ_OK;
+}
+
 int32_t fj_fill_random(fj_backend* be, uint64_t buffer, uint64_t offset_bytes, uint64_t elements, uint32_t dtype, uint64_t seed, float mean, float std) {
   if (!be || dtype > FJ_U32) return FJ_INVALID_INPUT;
   std::lock_guard<std::mutex> lock(be->mutex);

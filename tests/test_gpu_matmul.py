@@ -37,6 +37,24 @@ def test_matmul_with_transposed_weight_view(dt, m, k, n):
         assert_close(down(out), fjo.decode(want, dt), TOL[dt])
 
 
+@pytest.mark.parametrize("dt", [fb.BF16, fb.F16])
+@pytest.mark.parametrize("m,k,n", [(1024, 256, 1024), (300, 128, 4000), (128, 1024, 8200), (2048, 64, 520), (777, 1984, 1333)])
+def test_large_grids_run_on_tensor_memory_tiles(dt, m, k, n):
+    """At least 64 output tiles of 128 x 128 and K a multiple of 64: the tcgen05 kernel (TMEM accumulators);
+    ragged M and N edges, one to 31 k steps. None of its bounded waits may run out."""
+    rng = np.random.default_rng(m + k + n)
+    be = backend()
+    x, xh = up(rng.standard_normal((m, k)), dt)
+    w, wh = up(rng.standard_normal((n, k)) * 0.05, dt)
+    out = be.alloc(dt, (m, n))
+    be.run(Op.Matmul(), [x, w.permute([1, 0])], [out])
+    assert be.tcgen05_wait_giveups() == 0
+    fjo.set_threads(fjo.max_threads())
+    want = fjo.matmul(xh, dt, wh, dt, dt, right_transposed=True)
+    fjo.set_threads(1)
+    assert_close(down(out), fjo.decode(want, dt), TOL[dt])
+
+
 def test_matmul_generic_layouts_and_batches():
     rng = np.random.default_rng(2)
     be = backend()
