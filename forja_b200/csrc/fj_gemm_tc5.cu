@@ -6,7 +6,7 @@
 // One CTA owns a 128 x 128 output tile. Operand tiles of 128 rows x 64 k (128 bytes per row) are
 // copied with cp.async into shared memory in the 128-byte-swizzle layout the tensor core expects
 // for K-major operands (16-byte chunk c of row r at chunk c ^ (r & 7), 8-row groups 1024 bytes
-// apart), four stages deep. When a stage has landed, one elected thread issues four
+// apart), three stages deep with two CTAs per SM. When a stage has landed, one elected thread issues four
 // tcgen05.mma.cta_group::1.kind::f16 (M 128, N 128, K 16 each) whose accumulator is a 128-lane x
 // 128-column f32 block of TMEM, then tcgen05.commit arrives on that stage's mbarrier once the
 // tensor core is done reading it, which is what lets the stage be refilled. After the last k step
@@ -21,7 +21,7 @@ namespace fj {
 
 namespace {
 
-constexpr int T5_BM = 128, T5_BN = 128, T5_BK = 64, T5_STAGES = 4, T5_THREADS = 128;
+constexpr int T5_BM = 128, T5_BN = 128, T5_BK = 64, T5_STAGES = 3, T5_THREADS = 128;  // 3 stages = 97 KB: two CTAs per SM
 constexpr int T5_TILE_BYTES = 128 * 128;                       // 128 rows x 128 bytes
 constexpr int T5_STAGE_BYTES = 2 * T5_TILE_BYTES;              // A then W
 constexpr int T5_SMEM = T5_STAGES * T5_STAGE_BYTES + 1024;     // + slack to align the base to 1024 bytes
@@ -67,7 +67,7 @@ struct Tc5Params {
   int bf16;
 };
 
-__global__ void __launch_bounds__(T5_THREADS) gemm_nt_tcgen05_kernel(Tc5Params p) {
+__global__ void __launch_bounds__(T5_THREADS, 2) gemm_nt_tcgen05_kernel(Tc5Params p) {
   extern __shared__ unsigned char t5_smem_raw[];
   __shared__ __align__(8) unsigned long long s_bar[T5_STAGES + 1];  // stage released by the tensor core; [STAGES]: all MMAs done
   __shared__ unsigned s_tmem;
@@ -119,17 +119,10 @@ __global__ void __launch_bounds__(T5_THREADS) gemm_nt_tcgen05_kernel(Tc5Params p
 
   const unsigned idesc = instr_desc(p.bf16 != 0);
   bool failed = false;
-  for (unsigned it = 0; it < k_iters && !failed; ++it) {
-    // the stage that iteration it + STAGES - 1 refills was read by the MMAs of iteration it - 1
-    if (it >= 1) {
-      const unsigned prev = it - 1;
-      if (!mbar_wait(bar_base + 8 * (prev % T5_STAGES), (prev / T5_STAGES) & 1u)) failed = true;
-    }
-    if (__syncthreads_or(failed ? 1 : 0)) { failed = true; break; }
-    issue_loads(it + T5_STAGES - 1);
-    asm volatile("cp.async.wait_group %0;\n" ::"n"(T5_STAGES - 1) : "memory");
+  for (unsigned it = 0; it < k_iters; ++it) {
+    asm volatile("cp.async.wait_group %0;\n" ::"n"(T5_STAGES - 2) : "memory");
     asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");  // cp.async wrote through the generic proxy; the tensor core reads through the async proxy
-    __syncthreads();
+    if (__syncthreads_or(failed ? 1 : 0)) { failed = true; break; }  // stage `it` has landed for every thread
     if (threadIdx.x == 0) {
       asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
       const unsigned stage = smem_base + (it % T5_STAGES) * T5_STAGE_BYTES;
@@ -145,6 +138,13 @@ __global__ void __launch_bounds__(T5_THREADS) gemm_nt_tcgen05_kernel(Tc5Params p
       asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(bar_base + 8 * (it % T5_STAGES)) : "memory");
       if (it + 1 == k_iters) asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(bar_base + 8 * T5_STAGES) : "memory");
     }
+    // With this step's MMAs queued, refill the stage the previous step read, once the tensor core has released it.
+    if (it >= 1) {
+      const unsigned prev = it - 1;
+      if (!mbar_wait(bar_base + 8 * (prev % T5_STAGES), (prev / T5_STAGES) & 1u)) failed = true;
+    }
+    if (!failed) issue_loads(it + T5_STAGES - 1);
+    else asm volatile("cp.async.commit_group;\n" ::: "memory");
   }
   asm volatile("cp.async.wait_group 0;\n" ::: "memory");
   if (!failed && k_iters != 0 && !mbar_wait(bar_base + 8 * T5_STAGES, 0)) failed = true;
@@ -170,9 +170,31 @@ __global__ void __launch_bounds__(T5_THREADS) gemm_nt_tcgen05_kernel(Tc5Params p
       asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
       if (row < p.m) {
         const unsigned c_first = col0 + cb * 32;
+        const size_t base = static_cast<size_t>(row) * p.ldc + c_first;
+        if (p.c_dt != F32 && c_first + 32 <= p.n && base % 8 == 0 && reinterpret_cast<size_t>(p.c) % 16 == 0) {
+          // 32 columns of one row = 64 bytes: four 16-byte stores
+          unsigned short* dst = static_cast<unsigned short*>(p.c) + base;
 #pragma unroll
-        for (int j = 0; j < 32; ++j)
-          if (c_first + j < p.n) store_from_f32(p.c, p.c_dt, static_cast<size_t>(row) * p.ldc + c_first + j, __uint_as_float(v[j]));
+          for (int q = 0; q < 4; ++q) {
+            unsigned packed[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const float lo = __uint_as_float(v[q * 8 + 2 * j]), hi = __uint_as_float(v[q * 8 + 2 * j + 1]);
+              if (p.c_dt == BF16) {
+                __nv_bfloat162 t = __floats2bfloat162_rn(lo, hi);
+                packed[j] = *reinterpret_cast<unsigned*>(&t);
+              } else {
+                __half2 t = __floats2half2_rn(lo, hi);
+                packed[j] = *reinterpret_cast<unsigned*>(&t);
+              }
+            }
+            *reinterpret_cast<uint4*>(dst + q * 8) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j)
+            if (c_first + j < p.n) store_from_f32(p.c, p.c_dt, base + j, __uint_as_float(v[j]));
+        }
       }
     }
   }
