@@ -238,6 +238,17 @@ def run_native(args):
         model.step(None, want_tokens=False)
         return starts, tokens
 
+    # The clock sampler starts before the warm-up: nvidia-smi's own start-up (NVML initialisation) can stall
+    # kernel launches for about a second, which must not land inside a timed region. It keeps sampling
+    # through both timed regions.
+    clocks_path = os.path.join(ROOT, "gpurun_out", f"clocks_rank{rank}.csv")
+    os.makedirs(os.path.dirname(clocks_path), exist_ok=True)
+    sampler = start_clock_sampler(clocks_path, local)
+    if sampler is not None:
+        deadline = time.perf_counter() + 5.0
+        while time.perf_counter() < deadline and not (os.path.exists(clocks_path) and os.path.getsize(clocks_path) > 200):
+            time.sleep(0.05)
+
     # first token of every lane comes from the host once; afterwards tokens feed back on the device
     starts, tokens = lanes.descriptors()
     pool.pack_step(starts, tokens)
@@ -250,9 +261,6 @@ def run_native(args):
 
     # ---- timed region 1: device-resident decode --------------------------------------------
     t_begin, t_end = be.timer(), be.timer()
-    clocks_path = os.path.join(ROOT, "gpurun_out", f"clocks_rank{rank}.csv")
-    os.makedirs(os.path.dirname(clocks_path), exist_ok=True)
-    sampler = start_clock_sampler(clocks_path, local)
     model.attention_time()
     barrier(dist, be)
     launches0 = be.kernel_launch_count()
@@ -321,6 +329,7 @@ def run_native(args):
         "e2e": {"value": e2e_tok_sum / e2e_elapsed, "unit": "tok/s", "h2d_bytes_per_step": h2d / e2e_steps, "d2h_bytes_per_step": d2h / e2e_steps,
                 "ms_per_step": e2e_elapsed / e2e_steps * 1e3, "mean_kv_tokens_per_step": e2e_kv_tokens / e2e_steps},
         "gpu_launches": int(launches),
+        "health": {"tcgen05_wait_giveups": int(be.tcgen05_wait_giveups())},
         "roofline": {"kernel": "attn_decode_mma_kernel (paged GQA decode attention, split-K)", "bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"],
                      "unit": "GB/s", "frac": (achieved / peaks["hbm_gbs"]) if achieved else None, "peak_source": peaks["source"],
                      "algorithmic_bytes_per_launch": per_launch_bytes, "launches": int(attn_launches), "avg_launch_us": attn_ns / max(attn_launches, 1) * 1e-3,
