@@ -190,6 +190,125 @@ def run_moe(args):
         dist.destroy_process_group()
 
 
+def load_peaks():
+    try:
+        with open(os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "MEASURED_PEAKS.json")) as f:
+            peaks = json.load(f)
+        return float(peaks.get("hbm_gbs", 6650.0)), float(peaks.get("bf16_tflops", 1590.0)), "measured"
+    except (OSError, ValueError):
+        return 6650.0, 1590.0, "fallback"
+
+
+def timed(be, commands, dispatches, reps=3):
+    """Best device time per dispatch over `reps` submissions of a command list (CUDA events around the submission)."""
+    be.submit(commands).wait()
+    best = float("inf")
+    for _ in range(reps):
+        sub = be.submit(commands)
+        sub.wait()
+        best = min(best, sub.gpu_time_ns() / dispatches)
+    return best
+
+
+def run_q4(args):
+    """Isolated MLX q4 projection (config 4): weights uniform nibbles, scales/biases N(0, 0.01), activations N(0, 1).
+    Each dispatch uses its own copy of the weights so that every launch streams them from HBM."""
+    from forja_b200.backend import CommandList, Op
+    be = fb.CudaBackend(0)
+    hbm, tflops, source = load_peaks()
+    shapes = {"qkv": (2048, 6144), "o": (4096, 2048), "expert": (2048, 768), "lm_head": (2048, 151936)}
+    for name in args.shapes.split(","):
+        k, n = shapes[name]
+        wbytes = 0.5625 * n * k
+        copies = max(2, min(args.copies, int((768 << 20) // wbytes) + 1))
+        packed = be.alloc(fb.U32, (copies, n, k // 8)); be.fill_random(packed, 1)
+        scales = be.alloc(fb.BF16, (copies, n, k // 64)); be.fill_random(scales, 2, std=0.01)
+        biases = be.alloc(fb.BF16, (copies, n, k // 64)); be.fill_random(biases, 3, std=0.01)
+        for m in [int(v) for v in args.m.split(",")]:
+            x = be.alloc(fb.BF16, (m, k)); be.fill_random(x, 4)
+            out = be.alloc(fb.BF16, (m, n))
+            cl = CommandList()
+            used = copies if m <= 64 else min(copies, 4)
+            for c in range(used):
+                cl.dispatch(Op.QuantMatmul(4, 64), [x, packed.narrow(0, c, 1).reshape((n, k // 8)), scales.narrow(0, c, 1).reshape((n, k // 64)),
+                                                    biases.narrow(0, c, 1).reshape((n, k // 64))], out)
+            ns = timed(be, cl, used)
+            print(json.dumps({"workload": "q4 projection", "shape": name, "k": k, "n": n, "m": m, "us_per_launch": ns / 1e3, "weight_gbs": wbytes / ns,
+                              "frac_of_hbm_peak": wbytes / ns / hbm, "tflops": 2.0 * m * k * n / ns / 1e3, "frac_of_bf16_peak": 2.0 * m * k * n / ns / 1e3 / tflops,
+                              "peak_source": source}), flush=True)
+            be.release(x); be.release(out)
+        for t in (packed, scales, biases):
+            be.release(t)
+
+
+def run_gemm(args):
+    from forja_b200.backend import CommandList, Op
+    be = fb.CudaBackend(0)
+    _, tflops, source = load_peaks()
+    for shape in args.shapes.split(","):
+        m, k, n = (int(v) for v in shape.split("x"))
+        x = be.alloc(fb.BF16, (m, k)); w = be.alloc(fb.BF16, (n, k)); out = be.alloc(fb.BF16, (m, n))
+        be.fill_random(x, 1); be.fill_random(w, 2, std=0.05)
+        cl = CommandList()
+        for _ in range(args.reps):
+            cl.dispatch(Op.Matmul(), [x, w.permute([1, 0])], out)
+        ns = timed(be, cl, args.reps)
+        print(json.dumps({"workload": "bf16 matmul (weight [n, k] through a transposed view)", "m": m, "k": k, "n": n, "us_per_launch": ns / 1e3,
+                          "tflops": 2.0 * m * k * n / ns / 1e3, "frac_of_bf16_peak": 2.0 * m * k * n / ns / 1e3 / tflops, "peak_source": source,
+                          "tcgen05_wait_giveups": be.tcgen05_wait_giveups()}), flush=True)
+        for t in (x, w, out):
+            be.release(t)
+
+
+def run_attention(args):
+    """Isolated paged GQA attention (config 3): 32 q / 4 kv heads, head_dim 128, page 16, permuted page tables, bf16 N(0, 1).
+    decode: `lanes` sequences with kv lengths log-uniform 64-32768, one query token each (one ragged launch);
+    prefill: one 512-token chunk per sequence at a random chunk-aligned start."""
+    from forja_b200.backend import CommandList, Op
+    be = fb.CudaBackend(0)
+    hbm, tflops, source = load_peaks()
+    rng = np.random.default_rng(args.seed)
+    hq, kvh, d, page = 32, 4, 128, PAGE
+    scale = float(1.0 / np.sqrt(d))
+    if args.mode == "decode":
+        lengths = np.round(np.exp(rng.uniform(np.log(64), np.log(args.kv_max), args.lanes))).astype(np.int64)
+        q_lens = np.ones(args.lanes, np.int64)
+        starts = lengths - 1
+    else:
+        chunks = rng.integers(0, max(args.kv_max // 512, 1), args.lanes)
+        starts = chunks * 512
+        q_lens = np.full(args.lanes, 512, np.int64)
+        lengths = starts + q_lens
+    pages = (lengths + page - 1) // page
+    physical = int(pages.sum()) + 8
+    kpool = be.alloc(fb.BF16, (physical, page, kvh, d)); be.fill_random(kpool, 11)
+    vpool = be.alloc(fb.BF16, (physical, page, kvh, d)); be.fill_random(vpool, 12)
+    generations = be.tensor_from(np.ones(physical, np.uint32), fb.U32)
+    order = rng.permutation(physical)
+    cl = CommandList()
+    cursor = 0
+    keep = []
+    for lane in range(args.lanes):
+        table = np.zeros((int(pages[lane]), 2), np.uint32)
+        table[:, 0] = order[cursor:cursor + int(pages[lane])]
+        table[:, 1] = 1
+        cursor += int(pages[lane])
+        t = be.tensor_from(table, fb.U32)
+        q = be.alloc(fb.BF16, (int(q_lens[lane]), hq, d)); be.fill_random(q, 100 + lane)
+        out = be.alloc(fb.BF16, (int(q_lens[lane]), hq, d))
+        keep += [t, q, out]
+        cl.dispatch(Op.PagedSdpa(scale, True, int(starts[lane]), int(lengths[lane]), page), [q.permute([1, 0, 2]), kpool, vpool, t, generations], out.permute([1, 0, 2]))
+    ns = timed(be, cl, 1)
+    kv_bytes = float((lengths * kvh * d * 2 * 2).sum())
+    qo_bytes = float((q_lens * hq * d * 2 * 2).sum())
+    # causal flops: every query row attends min(key_length, q_start + row + 1) keys, 4 d flops per (row, key, head)
+    attended = sum(float(np.minimum(lengths[i], starts[i] + np.arange(q_lens[i]) + 1).sum()) for i in range(args.lanes))
+    flops = attended * hq * d * 4.0
+    print(json.dumps({"workload": "paged GQA attention " + args.mode, "lanes": args.lanes, "q_heads": hq, "kv_heads": kvh, "head_dim": d, "kv_tokens": int(lengths.sum()),
+                      "us": ns / 1e3, "algorithmic_gbs": (kv_bytes + qo_bytes) / ns, "frac_of_hbm_peak": (kv_bytes + qo_bytes) / ns / hbm,
+                      "tflops": flops / ns / 1e3, "frac_of_bf16_peak": flops / ns / 1e3 / tflops, "peak_source": source, "kernel_launches": be.kernel_launch_count()}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser(description=__doc__)
     sub = ap.add_subparsers(dest="command", required=True)
@@ -205,9 +324,20 @@ def main():
     moe.add_argument("--prompt-budget", type=int, default=2048)
     moe.add_argument("--prefill-limit", type=int, default=4)
     moe.add_argument("--decode-only", action="store_true")
+    q4 = sub.add_parser("q4")
+    q4.add_argument("--shapes", default="qkv,o,expert,lm_head")
+    q4.add_argument("--m", default="1,8,64,512,4096")
+    q4.add_argument("--copies", type=int, default=64)
+    gemm = sub.add_parser("gemm")
+    gemm.add_argument("--shapes", default="2048x2048x5120,4096x4096x4096,8192x2048x8192")
+    gemm.add_argument("--reps", type=int, default=10)
+    attn = sub.add_parser("attention")
+    attn.add_argument("--mode", default="decode", choices=["decode", "prefill"])
+    attn.add_argument("--lanes", type=int, default=256)
+    attn.add_argument("--kv-max", type=int, default=32768)
+    attn.add_argument("--seed", type=int, default=0)
     args = ap.parse_args()
-    if args.command == "moe":
-        run_moe(args)
+    {"moe": run_moe, "q4": run_q4, "gemm": run_gemm, "attention": run_attention}[args.command](args)
 
 
 if __name__ == "__main__":
