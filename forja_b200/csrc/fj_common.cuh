@@ -22,6 +22,16 @@ struct ErrorRecord {
 };
 enum : unsigned int { ERR_INDEX = 1, ERR_PAGE = 2, ERR_WAIT = 3 };
 
+// Programmatic dependent launch: a kernel started with the stream-serialisation attribute may begin
+// while its predecessor in the stream is still draining. `griddepcontrol.wait` blocks until that
+// predecessor has completed and its writes are visible, so it must come before the first access to
+// anything the predecessor wrote (or still reads); `launch_dependents` lets the successor start its
+// own launch early. Both are no-ops for kernels started without the attribute.
+__device__ inline void pdl_sync() {
+  asm volatile("griddepcontrol.wait;\n" ::: "memory");
+  asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
+}
+
 __device__ inline void report_error(ErrorRecord* rec, unsigned int flag, unsigned int value) {
   if (rec == nullptr) return;
   atomicMax(&rec->flag, flag);

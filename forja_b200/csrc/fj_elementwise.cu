@@ -270,6 +270,7 @@ __global__ void qknorm_rope_append_kernel(const T* __restrict__ qkv, const T* __
                                           T* __restrict__ q_out, T* __restrict__ k_plane, T* __restrict__ v_plane, unsigned rows,
                                           unsigned q_heads, unsigned kv_heads, unsigned head_dim, float eps,
                                           const float* __restrict__ inv_freq, int qk_norm, unsigned plane_slots) {
+  pdl_sync();
   const unsigned heads_total = q_heads + 2 * kv_heads;
   const unsigned half = head_dim / 2;
   const int lane = threadIdx.x & 31;
@@ -367,6 +368,7 @@ __global__ void __launch_bounds__(128) norm_dense_kernel(const T* residual, size
                                                          T* sum_out, size_t s_stride, T* norm_out, size_t n_stride, unsigned width, float eps,
                                                          int round_sum) {
   __shared__ float red[32];
+  pdl_sync();
   const size_t row = blockIdx.x;
   const unsigned vecs = width / 8;
   float sum = 0.0f;
@@ -404,6 +406,7 @@ __global__ void __launch_bounds__(128) norm_dense_kernel(const T* residual, size
 // mode 0: a + b; mode 1: a * sigmoid(a) * b
 template <typename T>
 __global__ void map2_dense_kernel(const T* a, size_t a_stride, const T* b, size_t b_stride, T* out, size_t o_stride, size_t rows, unsigned width, int mode) {
+  pdl_sync();
   const unsigned vecs = width / 8;
   const size_t total = rows * vecs;
   for (size_t idx = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; idx < total; idx += static_cast<size_t>(gridDim.x) * blockDim.x) {
@@ -426,9 +429,8 @@ bool try_norm_dense(Ctx& ctx, const View* residual, const View& update, const Vi
   DenseRow r{true, nullptr, 0}, s{true, nullptr, 0};
   if (residual) { r = dense_rows(*residual, rows, width, false); s = dense_rows(*sum_out, rows, width, false); }
   if (!u.ok || !g.ok || !n.ok || !r.ok || !s.ok || rows > 0x7FFFFFFFull) return false;
-  norm_dense_kernel<T><<<static_cast<unsigned>(rows), 128, 0, ctx.stream>>>(reinterpret_cast<const T*>(r.base), r.row_stride, reinterpret_cast<const T*>(u.base), u.row_stride,
-                                                                          reinterpret_cast<const T*>(g.base), reinterpret_cast<T*>(s.base), s.row_stride,
-                                                                          reinterpret_cast<T*>(n.base), n.row_stride, width, eps, round_sum);
+  launch_pdl(norm_dense_kernel<T>, dim3(static_cast<unsigned>(rows)), dim3(128), 0, ctx.stream, reinterpret_cast<const T*>(r.base), r.row_stride, reinterpret_cast<const T*>(u.base),
+             u.row_stride, reinterpret_cast<const T*>(g.base), reinterpret_cast<T*>(s.base), s.row_stride, reinterpret_cast<T*>(n.base), n.row_stride, width, eps, round_sum);
   ctx.launches++;
   return true;
 }
@@ -442,8 +444,8 @@ bool try_map2_dense(Ctx& ctx, const View& a, const View& b, const View& out, siz
   DenseRow x = dense_rows(a, rows, width, false), y = dense_rows(b, rows, width, false), o = dense_rows(out, rows, width, false);
   if (!x.ok || !y.ok || !o.ok) return false;
   const size_t total = rows * (width / 8);
-  map2_dense_kernel<T><<<grid_for(total, kThreads, ctx.sm_count), kThreads, 0, ctx.stream>>>(reinterpret_cast<const T*>(x.base), x.row_stride, reinterpret_cast<const T*>(y.base),
-                                                                                           y.row_stride, reinterpret_cast<T*>(o.base), o.row_stride, rows, width, mode);
+  launch_pdl(map2_dense_kernel<T>, dim3(grid_for(total, kThreads, ctx.sm_count)), dim3(kThreads), 0, ctx.stream, reinterpret_cast<const T*>(x.base), x.row_stride,
+             reinterpret_cast<const T*>(y.base), y.row_stride, reinterpret_cast<T*>(o.base), o.row_stride, rows, width, mode);
   ctx.launches++;
   return true;
 }
@@ -547,17 +549,17 @@ void launch_qknorm_rope_append(Ctx& ctx, const void* qkv, int dt, const void* q_
   size_t items = static_cast<size_t>(rows) * (q_heads + 2 * kv_heads);
   unsigned grid = grid_for(items * 32, kThreads, ctx.sm_count);
   if (dt == BF16)
-    qknorm_rope_append_kernel<__nv_bfloat16><<<grid, kThreads, 0, ctx.stream>>>(
+    launch_pdl(qknorm_rope_append_kernel<__nv_bfloat16>, dim3(grid), dim3(kThreads), 0, ctx.stream,
         static_cast<const __nv_bfloat16*>(qkv), static_cast<const __nv_bfloat16*>(q_norm_w), static_cast<const __nv_bfloat16*>(k_norm_w),
         positions, slot_mapping, static_cast<__nv_bfloat16*>(q_out), static_cast<__nv_bfloat16*>(k_plane), static_cast<__nv_bfloat16*>(v_plane),
         rows, q_heads, kv_heads, head_dim, eps, inv_freq, qk_norm, plane_slots);
   else if (dt == F16)
-    qknorm_rope_append_kernel<__half><<<grid, kThreads, 0, ctx.stream>>>(
+    launch_pdl(qknorm_rope_append_kernel<__half>, dim3(grid), dim3(kThreads), 0, ctx.stream,
         static_cast<const __half*>(qkv), static_cast<const __half*>(q_norm_w), static_cast<const __half*>(k_norm_w), positions, slot_mapping,
         static_cast<__half*>(q_out), static_cast<__half*>(k_plane), static_cast<__half*>(v_plane), rows, q_heads, kv_heads, head_dim, eps,
         inv_freq, qk_norm, plane_slots);
   else
-    qknorm_rope_append_kernel<float><<<grid, kThreads, 0, ctx.stream>>>(
+    launch_pdl(qknorm_rope_append_kernel<float>, dim3(grid), dim3(kThreads), 0, ctx.stream,
         static_cast<const float*>(qkv), static_cast<const float*>(q_norm_w), static_cast<const float*>(k_norm_w), positions, slot_mapping,
         static_cast<float*>(q_out), static_cast<float*>(k_plane), static_cast<float*>(v_plane), rows, q_heads, kv_heads, head_dim, eps,
         inv_freq, qk_norm, plane_slots);

@@ -148,6 +148,7 @@ __global__ void __launch_bounds__(GEMM_THREADS) gemm_nt_mma_kernel(GemmParams p)
   constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
   extern __shared__ __align__(128) unsigned char smem[];
   __shared__ unsigned s_ticket;
+  pdl_sync();
   const unsigned smem_base = static_cast<unsigned>(__cvta_generic_to_shared(smem));
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int warp_m = warp / WARPS_N, warp_n = warp % WARPS_N;
@@ -359,7 +360,7 @@ void run_mma(Ctx& ctx, const GemmParams& p, unsigned tiles_m, unsigned tiles_n) 
     cudaFuncSetAttribute(gemm_nt_mma_kernel<BN, kBF16>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     configured = true;
   }
-  gemm_nt_mma_kernel<BN, kBF16><<<dim3(tiles_n, tiles_m, p.splits), GEMM_THREADS, smem, ctx.stream>>>(p);
+  launch_pdl(gemm_nt_mma_kernel<BN, kBF16>, dim3(tiles_n, tiles_m, p.splits), dim3(GEMM_THREADS), smem, ctx.stream, p);
   ctx.launches++;
 }
 

@@ -15,6 +15,23 @@ struct Ctx {
   int sm_count;
 };
 
+// Launch with the programmatic stream-serialisation attribute (see pdl_sync in fj_common.cuh): only
+// for kernels whose first statement is pdl_sync().
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {
+  cudaLaunchConfig_t config = {};
+  config.gridDim = grid;
+  config.blockDim = block;
+  config.dynamicSmemBytes = smem;
+  config.stream = stream;
+  cudaLaunchAttribute attribute[1];
+  attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attribute[0].val.programmaticStreamSerializationAllowed = 1;
+  config.attrs = attribute;
+  config.numAttrs = 1;
+  return cudaLaunchKernelEx(&config, kernel, KArgs(args)...);
+}
+
 // ---- fj_elementwise.cu ----------------------------------------------------------------------
 void launch_copy(Ctx& ctx, const View& in, const View& out, size_t elements);
 void launch_fill_zero(Ctx& ctx, void* ptr, size_t bytes);

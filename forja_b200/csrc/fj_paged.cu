@@ -131,6 +131,7 @@ template <bool kBF16>
 __global__ void __launch_bounds__(kWarps * 32, 2) attn_decode_mma_kernel(DecodeParams p) {
   extern __shared__ __align__(128) unsigned char smem[];
   __shared__ unsigned s_ticket;
+  pdl_sync();
   const unsigned item = blockIdx.x;
   if (item >= p.n_work) return;
   const AttnWork work = p.work[item];
@@ -791,8 +792,8 @@ void launch_attn_decode_mma(Ctx& ctx, const AttnGeometry& g, const AttnSeq* seqs
     cudaFuncSetAttribute(attn_decode_mma_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kDecodeSmem);
     configured = true;
   }
-  if (g.kv_dtype == BF16) attn_decode_mma_kernel<true><<<n_work, kWarps * 32, kDecodeSmem, ctx.stream>>>(p);
-  else attn_decode_mma_kernel<false><<<n_work, kWarps * 32, kDecodeSmem, ctx.stream>>>(p);
+  if (g.kv_dtype == BF16) launch_pdl(attn_decode_mma_kernel<true>, dim3(n_work), dim3(kWarps * 32), kDecodeSmem, ctx.stream, p);
+  else launch_pdl(attn_decode_mma_kernel<false>, dim3(n_work), dim3(kWarps * 32), kDecodeSmem, ctx.stream, p);
   ctx.launches++;
 }
 
