@@ -601,6 +601,16 @@ class MoeModel:
                                      None if out is None else out.ctypes.data_as(C.c_void_p), logits.buffer if logits is not None else 0))
         return out
 
+    def capture_routes(self, enabled: bool = True):
+        _check(self._lib.fj_moe_capture_routes(self._h, int(enabled)))
+
+    def routes(self, layer: int, rows: int):
+        """(expert ids u32 [rows, top_k], weights f32 [rows, top_k]) of one layer of the last step."""
+        k = self.config["top_k"]
+        experts, weights = np.zeros((rows, k), np.uint32), np.zeros((rows, k), np.float32)
+        _check(self._lib.fj_moe_read_routes(self._h, layer, rows, experts.ctypes.data_as(C.c_void_p), weights.ctypes.data_as(C.c_void_p)))
+        return experts, weights
+
     def stats(self):
         k, w = C.c_uint64(0), C.c_uint64(0)
         _check(self._lib.fj_moe_step_stats(self._h, C.byref(k), C.byref(w)))

@@ -189,6 +189,7 @@ constexpr unsigned kArgmaxChunk = 4096;
 
 __global__ void argmax_partial_kernel(const void* x, int dt, size_t row_stride, unsigned width, unsigned chunks,
                                       unsigned long long* partial) {
+  pdl_sync();
   const unsigned row = blockIdx.y, chunk = blockIdx.x;
   const unsigned begin = chunk * kArgmaxChunk;
   const unsigned end = min(width, begin + kArgmaxChunk);
@@ -209,6 +210,7 @@ __global__ void argmax_partial_kernel(const void* x, int dt, size_t row_stride, 
 }
 
 __global__ void argmax_final_kernel(const unsigned long long* partial, unsigned chunks, unsigned* out, unsigned rows) {
+  pdl_sync();
   unsigned row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (row >= rows) return;
   unsigned long long best = 0;
@@ -224,6 +226,7 @@ __global__ void argmax_final_kernel(const unsigned long long* partial, unsigned 
 // values select the lower index first (crates/forja-cpu/src/lib.rs:572-584).
 __global__ void top_k_kernel(const void* x, int dt, void* values, int v_dt, unsigned* indices, unsigned width, unsigned k,
                              int normalize) {
+  pdl_sync();
   extern __shared__ unsigned long long keys[];  // width entries
   __shared__ unsigned long long warp_best[8];
   __shared__ unsigned long long selected;
@@ -537,7 +540,7 @@ void launch_top_k(Ctx& ctx, const void* x, int x_dt, void* values, int v_dt, uns
   if (rows == 0) return;
   size_t smem = static_cast<size_t>(width) * sizeof(unsigned long long);
   int threads = width >= 1024 ? 256 : (width >= 128 ? 128 : 32);
-  top_k_kernel<<<rows, threads, smem, ctx.stream>>>(x, x_dt, values, v_dt, indices, width, k, normalize ? 1 : 0);
+  launch_pdl(top_k_kernel, dim3(rows), dim3(threads), smem, ctx.stream, x, x_dt, values, v_dt, indices, width, k, normalize ? 1 : 0);
   ctx.launches++;
 }
 

@@ -395,8 +395,8 @@ void launch_gemm_nt(Ctx& ctx, const void* a, int a_dt, size_t lda, const void* w
     }
     return;
   }
-  // enough 128 x 128 tiles to go round: TMEM-accumulator tiles; smaller grids keep the split-K mma.sync kernel
-  if (gemm_nt_tcgen05_supported(a_dt, w_dt, m, n, k, lda, ldw, a, w) && static_cast<size_t>((m + 127) / 128) * ((n + 127) / 128) >= 64) {
+  // at least one 128 x 128 tile per SM: TMEM-accumulator tiles; smaller grids keep the split-K mma.sync kernel
+  if (gemm_nt_tcgen05_supported(a_dt, w_dt, m, n, k, lda, ldw, a, w) && static_cast<size_t>((m + 127) / 128) * ((n + 127) / 128) >= static_cast<size_t>(ctx.sm_count > 0 ? ctx.sm_count : 148)) {
     launch_gemm_nt_tcgen05(ctx, a, a_dt, lda, w, ldw, c, c_dt, ldc, m, n, k);
     return;
   }

@@ -91,6 +91,7 @@ __global__ void __launch_bounds__(T5_THREADS, 2) gemm_nt_tcgen05_kernel(Tc5Param
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
   const unsigned tmem = s_tmem;
+  pdl_sync();  // barriers and tensor memory are set up while the previous kernel drains; its results are read from here on
 
   auto issue_loads = [&](unsigned it) {
     if (it < k_iters) {
@@ -220,7 +221,7 @@ void launch_gemm_nt_tcgen05(Ctx& ctx, const void* a, int a_dt, size_t lda, const
   }
   Tc5Params p{static_cast<const unsigned short*>(a), lda, static_cast<const unsigned short*>(w), ldw, c, c_dt, ldc, m, n, k, a_dt == BF16 ? 1 : 0};
   dim3 grid((n + T5_BN - 1) / T5_BN, (m + T5_BM - 1) / T5_BM);
-  gemm_nt_tcgen05_kernel<<<grid, T5_THREADS, T5_SMEM, ctx.stream>>>(p);
+  launch_pdl(gemm_nt_tcgen05_kernel, grid, dim3(T5_THREADS), T5_SMEM, ctx.stream, p);
   ctx.launches++;
 }
 

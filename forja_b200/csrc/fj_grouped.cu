@@ -30,6 +30,7 @@ struct RouteTile {
 __global__ void __launch_bounds__(1024) route_plan_kernel(const unsigned* __restrict__ indices, unsigned total, unsigned experts, unsigned* offsets /*[experts + 1]*/,
                                                           unsigned* sorted /*[total]*/, RouteTile* tiles, unsigned* n_tiles, unsigned tiles_cap) {
   extern __shared__ unsigned plan_smem[];
+  pdl_sync();
   unsigned* count = plan_smem;           // [experts]
   unsigned* cursor = plan_smem + experts;  // [experts]
   for (unsigned e = threadIdx.x; e < experts; e += blockDim.x) count[e] = 0;
@@ -94,6 +95,7 @@ __global__ void __launch_bounds__(GT_THREADS) grouped_q4_gemm_kernel(GroupedArgs
   __shared__ __align__(16) unsigned char s_q[2][NW][GT_BN * 32];
   __shared__ unsigned short s_scale[2][NW][GT_BN], s_bias[2][NW][GT_BN];
   __shared__ unsigned s_route[GT_BM];
+  pdl_sync();
   if (blockIdx.y >= *p.n_tiles) return;
   const RouteTile tile = p.tiles[blockIdx.y];
   const unsigned col0 = blockIdx.x * GT_BN;
@@ -255,7 +257,7 @@ PlanLayout plan_layout(void* plan, unsigned total_routes, unsigned experts) {
 
 void launch_route_plan(Ctx& ctx, const unsigned* indices, unsigned total_routes, unsigned experts, void* plan) {
   const PlanLayout l = plan_layout(plan, total_routes, experts);
-  route_plan_kernel<<<1, 1024, 2 * experts * sizeof(unsigned), ctx.stream>>>(indices, total_routes, experts, l.offsets, l.sorted, l.tiles, l.n_tiles, l.tiles_cap);
+  launch_pdl(route_plan_kernel, dim3(1), dim3(1024), 2 * experts * sizeof(unsigned), ctx.stream, indices, total_routes, experts, l.offsets, l.sorted, l.tiles, l.n_tiles, l.tiles_cap);
   ctx.launches++;
 }
 
@@ -269,7 +271,7 @@ void launch_grouped_q4_pair(Ctx& ctx, const void* x, const unsigned* gate, const
   GroupedArgs a{static_cast<const unsigned short*>(x), {gate, up}, {static_cast<const unsigned short*>(gate_scales), static_cast<const unsigned short*>(up_scales)},
                 {static_cast<const unsigned short*>(gate_biases), static_cast<const unsigned short*>(up_biases)}, l.sorted, l.tiles, l.n_tiles, act_out, k, n, src_div};
   dim3 grid((n + GT_BN - 1) / GT_BN, l.tiles_cap);
-  grouped_q4_gemm_kernel<true><<<grid, GT_THREADS, 0, ctx.stream>>>(a);
+  launch_pdl(grouped_q4_gemm_kernel<true>, grid, dim3(GT_THREADS), 0, ctx.stream, a);
   ctx.launches++;
 }
 
@@ -279,7 +281,7 @@ void launch_grouped_q4_single(Ctx& ctx, const void* x, const unsigned* packed, c
   GroupedArgs a{static_cast<const unsigned short*>(x), {packed, packed}, {static_cast<const unsigned short*>(scales), static_cast<const unsigned short*>(scales)},
                 {static_cast<const unsigned short*>(biases), static_cast<const unsigned short*>(biases)}, l.sorted, l.tiles, l.n_tiles, out, k, n, src_div};
   dim3 grid((n + GT_BN - 1) / GT_BN, l.tiles_cap);
-  grouped_q4_gemm_kernel<false><<<grid, GT_THREADS, 0, ctx.stream>>>(a);
+  launch_pdl(grouped_q4_gemm_kernel<false>, grid, dim3(GT_THREADS), 0, ctx.stream, a);
   ctx.launches++;
 }
 

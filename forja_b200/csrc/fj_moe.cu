@@ -256,6 +256,9 @@ struct fj_moe_model {
   uint32_t prefill_items_cap = 0;
   const float* inv_freq = nullptr;
   uint64_t last_kernels = 0, last_work_items = 0;
+  // optional record of every layer's routing of the last step (parity checks): [layers][max_rows * top_k]
+  unsigned* captured_experts = nullptr;
+  float* captured_weights = nullptr;
 };
 
 extern "C" {
@@ -406,6 +409,35 @@ void fj_moe_model_destroy(fj_moe_model* m) {
   delete m;
 }
 
+int32_t fj_moe_capture_routes(fj_moe_model* m, uint32_t enabled) {
+  if (!m) return FJ_INVALID_INPUT;
+  fj_backend* be = m->be;
+  std::lock_guard<std::mutex> lock(be->mutex);
+  cudaSetDevice(be->device);
+  if (enabled && !m->captured_experts) {
+    const size_t bytes = static_cast<size_t>(m->cfg.layers) * m->cfg.max_rows * m->cfg.top_k * 4;
+    void *a = nullptr, *b = nullptr;
+    if (cudaMalloc(&a, bytes) != cudaSuccess || cudaMalloc(&b, bytes) != cudaSuccess) { cudaGetLastError(); if (a) cudaFree(a); return FJ_ALLOCATION_FAILED; }
+    m->owned.push_back(a);
+    m->owned.push_back(b);
+    m->captured_experts = static_cast<unsigned*>(a);
+    m->captured_weights = static_cast<float*>(b);
+  }
+  if (!enabled) { m->captured_experts = nullptr; m->captured_weights = nullptr; }  // the buffers stay owned by the model
+  return FJ_OK;
+}
+
+int32_t fj_moe_read_routes(fj_moe_model* m, uint32_t layer, uint32_t rows, uint32_t* experts, float* weights) {
+  if (!m || !m->captured_experts || layer >= m->cfg.layers || rows > m->cfg.max_rows || !experts || !weights) return FJ_INVALID_INPUT;
+  fj_backend* be = m->be;
+  std::lock_guard<std::mutex> lock(be->mutex);
+  cudaSetDevice(be->device);
+  const size_t at = static_cast<size_t>(layer) * m->cfg.max_rows * m->cfg.top_k, count = static_cast<size_t>(rows) * m->cfg.top_k;
+  cudaMemcpyAsync(experts, m->captured_experts + at, count * 4, cudaMemcpyDeviceToHost, be->stream);
+  cudaMemcpyAsync(weights, m->captured_weights + at, count * 4, cudaMemcpyDeviceToHost, be->stream);
+  return cuda_status(cudaStreamSynchronize(be->stream));
+}
+
 int32_t fj_moe_step_stats(fj_moe_model* m, uint64_t* kernels, uint64_t* attn_work_items) {
   if (!m) return FJ_INVALID_INPUT;
   if (kernels) *kernels = m->last_kernels;
@@ -503,6 +535,11 @@ extern "C" int32_t fj_moe_step(fj_moe_model* m, const uint32_t* token_ids, uint3
       std::swap(hidden, other);  // `hidden` is now the post-attention residual stream
       q4(m->normed, L.router, m->router_logits, FJ_F32, rows, H, c.experts, c.router_bits);
       fj::launch_top_k(ctx, m->router_logits, FJ_F32, m->route_weights, FJ_F32, m->route_experts, rows, c.experts, K, true);
+      if (m->captured_experts) {
+        const size_t at = static_cast<size_t>(l) * c.max_rows * K;
+        cudaMemcpyAsync(m->captured_experts + at, m->route_experts, static_cast<size_t>(rows) * K * 4, cudaMemcpyDeviceToDevice, be->stream);
+        cudaMemcpyAsync(m->captured_weights + at, m->route_weights, static_cast<size_t>(rows) * K * 4, cudaMemcpyDeviceToDevice, be->stream);
+      }
     }
     // Few routes: one GEMV-style pass per route. Many: bucket by expert and run tile GEMMs (weights rounded to bf16).
     const unsigned kGroupedRoutes = c.grouped_min_routes ? c.grouped_min_routes : 128;

@@ -445,6 +445,7 @@ struct PrefillParams {
 template <bool kBF16>
 __global__ void __launch_bounds__(kWarps * 32, 2) attn_prefill_mma_kernel(PrefillParams p) {
   extern __shared__ __align__(128) unsigned char smem[];
+  pdl_sync();
   if (blockIdx.x >= p.n_items) return;
   const uint2 item = p.items[blockIdx.x];
   const AttnSeq seq = p.seqs[item.x];
@@ -819,8 +820,8 @@ void launch_attn_prefill_mma(Ctx& ctx, const AttnGeometry& g, const AttnSeq* seq
   PrefillParams p{seqs, items, n_items, static_cast<const char*>(kpool), static_cast<const char*>(vpool), generations, g.physical_pages, g.q_heads, g.kv_heads,
                   g.q_heads / g.kv_heads, g.scale, g.out_dtype, err};
   dim3 grid(n_items, g.kv_heads);
-  if (g.kv_dtype == BF16) attn_prefill_mma_kernel<true><<<grid, kWarps * 32, kPrefillSmem, ctx.stream>>>(p);
-  else attn_prefill_mma_kernel<false><<<grid, kWarps * 32, kPrefillSmem, ctx.stream>>>(p);
+  if (g.kv_dtype == BF16) launch_pdl(attn_prefill_mma_kernel<true>, grid, dim3(kWarps * 32), kPrefillSmem, ctx.stream, p);
+  else launch_pdl(attn_prefill_mma_kernel<false>, grid, dim3(kWarps * 32), kPrefillSmem, ctx.stream, p);
   ctx.launches++;
 }
 

@@ -113,6 +113,7 @@ __device__ inline void quant_column(const QuantArgs& a, size_t x_index, unsigned
 
 template <int BITS>
 __global__ void __launch_bounds__(256) quant_matmul_kernel(QuantArgs a, void* out, int out_dt, unsigned m) {
+  pdl_sync();
   const int lane = threadIdx.x & 31;
   const unsigned col = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (col >= a.n) return;
@@ -170,6 +171,7 @@ constexpr int Q4_UNROLL = 4;  // 64-k blocks whose weight loads are in flight to
 // time, 16 bytes of weights each) before it touches the first one.
 template <bool kBF16, int NB, int WARPS>
 __global__ void __launch_bounds__(WARPS * 32, 768 / (WARPS * 32)) q4_mma_gemv_kernel(Q4MmaArgs a) {
+  pdl_sync();
   __shared__ float partial[WARPS][16][8 * NB];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const unsigned g = lane >> 2, t = lane & 3;
@@ -300,9 +302,9 @@ bool q4_mma_supported(int x_dt, int p_dt, unsigned m, unsigned k, unsigned bits,
 template <bool kBF16, int NB>
 void run_q4_mma_warps(Ctx& ctx, const Q4MmaArgs& a) {
   const unsigned grid = (a.n + 15) / 16, blocks = a.k / 64;
-  if (blocks >= 64) q4_mma_gemv_kernel<kBF16, NB, 16><<<grid, 16 * 32, 0, ctx.stream>>>(a);
-  else if (blocks >= 32) q4_mma_gemv_kernel<kBF16, NB, 8><<<grid, 8 * 32, 0, ctx.stream>>>(a);
-  else q4_mma_gemv_kernel<kBF16, NB, 4><<<grid, 4 * 32, 0, ctx.stream>>>(a);
+  if (blocks >= 64) launch_pdl(q4_mma_gemv_kernel<kBF16, NB, 16>, dim3(grid), dim3(16 * 32), 0, ctx.stream, a);
+  else if (blocks >= 32) launch_pdl(q4_mma_gemv_kernel<kBF16, NB, 8>, dim3(grid), dim3(8 * 32), 0, ctx.stream, a);
+  else launch_pdl(q4_mma_gemv_kernel<kBF16, NB, 4>, dim3(grid), dim3(4 * 32), 0, ctx.stream, a);
   ctx.launches++;
 }
 
@@ -369,6 +371,7 @@ __device__ inline void mma_u8(int (&d)[4], unsigned a0, unsigned a1, unsigned a2
 // bf16 activations and parameters only (f16 callers use the mantissa-offset kernel above).
 template <bool kG64, int NB, int STAGES, int WARPS>
 __global__ void __launch_bounds__(WARPS * 32, 1) q4_i8_stream_kernel(Q4WarpArgs args) {
+  asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
   extern __shared__ __align__(128) unsigned char q4_smem[];
   const Q4MmaArgs& a = args.base;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -425,6 +428,8 @@ __global__ void __launch_bounds__(WARPS * 32, 1) q4_i8_stream_kernel(Q4WarpArgs 
   for (int q = 0; q + 1 < STAGES; ++q) issue();  // the first weight units are already on their way while the activations are converted
 
   // ---- activations -> block fixed point in fragment order, once per CTA ----
+  // (programmatic dependent launch: the weight copies above do not depend on the previous kernel; the activations do)
+  if (!x_ready) asm volatile("griddepcontrol.wait;\n" ::: "memory");
   for (unsigned b = x_ready ? blocks : warp; b < blocks; b += WARPS) {
 #pragma unroll
     for (int nb = 0; nb < NB; ++nb) {
@@ -595,7 +600,7 @@ bool launch_q4_i8_stream(Ctx& ctx, const Q4WarpArgs& args, unsigned grid, size_t
     if (cudaFuncSetAttribute(q4_i8_stream_kernel<kG64, NB, STAGES, WARPS>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) != cudaSuccess) { cudaGetLastError(); return false; }
     configured[device] = true;
   }
-  q4_i8_stream_kernel<kG64, NB, STAGES, WARPS><<<grid, WARPS * 32, smem, ctx.stream>>>(args);
+  launch_pdl(q4_i8_stream_kernel<kG64, NB, STAGES, WARPS>, dim3(grid), dim3(WARPS * 32), smem, ctx.stream, args);
   ctx.launches++;
   return true;
 }
@@ -650,6 +655,7 @@ bool run_q4_stream(Ctx& ctx, const Q4MmaArgs& a, int x_dt) {
 // the scale/bias tables into a dense [cols, k] matrix of dtype out_dt; one thread per packed word.
 __global__ void dequant_rows_kernel(const unsigned* __restrict__ packed, const void* scales, const void* biases, int p_dt, void* out, int out_dt,
                                     unsigned cols, unsigned k, unsigned bits, unsigned group_size, unsigned row0) {
+  pdl_sync();
   const unsigned vpw = 32 / bits, mask = (1u << bits) - 1, words_per_row = k / vpw, groups = k / group_size;
   const size_t total = static_cast<size_t>(cols) * words_per_row;
   for (size_t idx = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; idx < total; idx += static_cast<size_t>(gridDim.x) * blockDim.x) {
@@ -669,6 +675,7 @@ template <int BITS>
 __global__ void __launch_bounds__(256) gather_quant_kernel(QuantArgs a, QuantArgs b, int paired, const unsigned* __restrict__ indices,
                                                            void* out, int out_dt, unsigned routes, size_t total_routes, unsigned experts,
                                                            int epilogue, ErrorRecord* err) {
+  pdl_sync();
   const int lane = threadIdx.x & 31;
   const unsigned col = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (col >= a.n) return;
@@ -705,6 +712,7 @@ template <int BITS>
 __global__ void __launch_bounds__(256) gather_weighted_kernel(QuantArgs a, const unsigned* __restrict__ indices, const void* weights,
                                                               int w_dt, const void* extra, int e_dt, void* out, int out_dt,
                                                               unsigned rows, unsigned routes, unsigned experts, int epilogue, ErrorRecord* err) {
+  pdl_sync();
   const int lane = threadIdx.x & 31;
   const unsigned col = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (col >= a.n) return;
@@ -739,6 +747,17 @@ void launch_quant_matmul(Ctx& ctx, const void* x, int x_dt, const unsigned* pack
                          int p_dt, void* out, int out_dt, unsigned m, unsigned k, unsigned n, unsigned bits,
                          unsigned group_size, void* workspace, size_t workspace_bytes, void* gemm_scratch, size_t gemm_scratch_bytes) {
   if (m == 0 || n == 0) return;
+  // 17 to 64 rows: passes of 16 rows through the decode kernels (the weights of the later passes come from L2 for
+  // all but the largest matrices), cheaper than expanding the matrix for a GEMM of so few rows
+  if (m > 16 && m <= 64 && out_dt == x_dt && q4_mma_supported(x_dt, p_dt, 16, k, bits, group_size, x, k, packed) && (k * 2) % 16 == 0) {
+    for (unsigned r0 = 0; r0 < m; r0 += 16) {
+      const unsigned rows = std::min(16u, m - r0);
+      Q4MmaArgs a{static_cast<const unsigned short*>(x) + static_cast<size_t>(r0) * k, k, packed, static_cast<const unsigned short*>(scales), static_cast<const unsigned short*>(biases),
+                  static_cast<char*>(out) + static_cast<size_t>(r0) * n * 2, out_dt, n, rows, k, n, group_size};
+      if (!run_q4_stream(ctx, a, x_dt)) run_q4_mma(ctx, a, x_dt);
+    }
+    return;
+  }
   if (q4_mma_supported(x_dt, p_dt, m, k, bits, group_size, x, k, packed)) {
     Q4MmaArgs a{static_cast<const unsigned short*>(x), k, packed, static_cast<const unsigned short*>(scales), static_cast<const unsigned short*>(biases),
                 out, out_dt, n, m, k, n, group_size};
@@ -765,8 +784,8 @@ void launch_quant_matmul(Ctx& ctx, const void* x, int x_dt, const unsigned* pack
   QuantArgs a{x, x_dt, k, packed, scales, biases, p_dt, k, n, bits, group_size};
   unsigned row_groups = (m + QM - 1) / QM;
   dim3 grid((n + 7) / 8, min(row_groups, 65535u));
-  if (bits == 4) quant_matmul_kernel<4><<<grid, 256, 0, ctx.stream>>>(a, out, out_dt, m);
-  else quant_matmul_kernel<8><<<grid, 256, 0, ctx.stream>>>(a, out, out_dt, m);
+  if (bits == 4) launch_pdl(quant_matmul_kernel<4>, grid, dim3(256), 0, ctx.stream, a, out, out_dt, m);
+  else launch_pdl(quant_matmul_kernel<8>, grid, dim3(256), 0, ctx.stream, a, out, out_dt, m);
   ctx.launches++;
 }
 
@@ -781,8 +800,8 @@ void launch_gather_quant_matmul(Ctx& ctx, const void* x, int x_dt, const unsigne
   const int paired = packed2 != nullptr;
   const size_t total_routes = static_cast<size_t>(rows) * routes;
   dim3 grid((n + 7) / 8, static_cast<unsigned>(total_routes < 65535 ? total_routes : 65535));
-  if (bits == 4) gather_quant_kernel<4><<<grid, 256, 0, ctx.stream>>>(a, b, paired, indices, out, out_dt, routes, total_routes, experts, epilogue, err);
-  else gather_quant_kernel<8><<<grid, 256, 0, ctx.stream>>>(a, b, paired, indices, out, out_dt, routes, total_routes, experts, epilogue, err);
+  if (bits == 4) launch_pdl(gather_quant_kernel<4>, grid, dim3(256), 0, ctx.stream, a, b, paired, indices, out, out_dt, routes, total_routes, experts, epilogue, err);
+  else launch_pdl(gather_quant_kernel<8>, grid, dim3(256), 0, ctx.stream, a, b, paired, indices, out, out_dt, routes, total_routes, experts, epilogue, err);
   ctx.launches++;
 }
 
@@ -794,8 +813,8 @@ void launch_gather_quant_weighted_sum(Ctx& ctx, const void* act, int a_dt, const
   if (rows == 0 || n == 0) return;
   QuantArgs a{act, a_dt, k, packed, scales, biases, p_dt, k, n, bits, group_size};
   dim3 grid((n + 7) / 8, min(rows, 65535u));
-  if (bits == 4) gather_weighted_kernel<4><<<grid, 256, 0, ctx.stream>>>(a, indices, weights, w_dt, extra, e_dt, out, out_dt, rows, routes, experts, epilogue, err);
-  else gather_weighted_kernel<8><<<grid, 256, 0, ctx.stream>>>(a, indices, weights, w_dt, extra, e_dt, out, out_dt, rows, routes, experts, epilogue, err);
+  if (bits == 4) launch_pdl(gather_weighted_kernel<4>, grid, dim3(256), 0, ctx.stream, a, indices, weights, w_dt, extra, e_dt, out, out_dt, rows, routes, experts, epilogue, err);
+  else launch_pdl(gather_weighted_kernel<8>, grid, dim3(256), 0, ctx.stream, a, indices, weights, w_dt, extra, e_dt, out, out_dt, rows, routes, experts, epilogue, err);
   ctx.launches++;
 }
 

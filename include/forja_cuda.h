@@ -402,6 +402,10 @@ void fj_moe_model_destroy(fj_moe_model* model);
  * the group must call it for the same step, even with no active lane of its own (pack zero tokens). */
 int32_t fj_moe_step(fj_moe_model* model, const uint32_t* token_ids, uint32_t* out_tokens, uint64_t logits_out);
 int32_t fj_moe_step_stats(fj_moe_model* model, uint64_t* kernels, uint64_t* attn_work_items);
+/* Parity aid: while enabled, every layer's routing of a step (TopK output: expert ids and normalised
+ * weights, [rows, top_k] in packed row order) is kept and can be read back after the step. */
+int32_t fj_moe_capture_routes(fj_moe_model* model, uint32_t enabled);
+int32_t fj_moe_read_routes(fj_moe_model* model, uint32_t layer, uint32_t rows, uint32_t* experts, float* weights);
 
 #ifdef __cplusplus
 }

@@ -151,11 +151,19 @@ class MoeOracle:
     def _q(self, x, triple, bits=4, out_dt=None):
         return fjo.quant_matmul(x, fjo.BF16, triple[0], triple[1], triple[2], fjo.BF16, bits, self.cfg["group_size"], fjo.BF16 if out_dt is None else out_dt)
 
-    def moe(self, normed, residual, L):
-        """Returns (new residual stream, router logits f32, expert ids, routing weights)."""
+    def moe(self, normed, residual, L, forced_experts=None):
+        """Returns (new residual stream, router logits f32, expert ids, routing weights). With
+        ``forced_experts`` [rows, top_k] the block uses that routing (weights from its own logits:
+        exp(v_i - v_first) / sum over the forced set) and keeps its own choice in ``self.own_experts``."""
         cfg, G = self.cfg, self.cfg["group_size"]
         logits = self._q(normed, L["router"], bits=cfg["router_bits"], out_dt=fjo.F32)
         weights, experts = fjo.top_k(logits, fjo.F32, cfg["top_k"], True)
+        self.own_experts = experts
+        if forced_experts is not None:
+            experts = np.ascontiguousarray(forced_experts, np.uint32)
+            picked = np.take_along_axis(logits.astype(np.float32), experts.astype(np.int64), axis=-1)
+            e = np.exp((picked - picked[:, :1]).astype(np.float32)).astype(np.float32)
+            weights = (e / e.sum(axis=-1, keepdims=True, dtype=np.float32)).astype(np.float32)
         gate = fjo.gather_quant_matmul(normed, fjo.BF16, *L["gate"], fjo.BF16, experts, 4, G, out_dt=fjo.F32)
         up = fjo.gather_quant_matmul(normed, fjo.BF16, *L["up"], fjo.BF16, experts, 4, G, out_dt=fjo.F32)
         act = fjo.prog_silu_mul(gate, up, fjo.F32, out_dt=fjo.BF16)
@@ -163,11 +171,18 @@ class MoeOracle:
         out = fjo.prog_add(mixed, fjo.decode(residual, fjo.BF16), fjo.F32, out_dt=fjo.BF16)
         return out, logits, experts, weights
 
-    def forward_lane(self, token_ids, start: int, table: np.ndarray, generations: np.ndarray):
+    def forward_lane(self, token_ids, start: int, table: np.ndarray, generations: np.ndarray, forced_routes=None):
+        """``forced_routes``: per layer, expert ids [T, top_k] to use instead of the oracle's own top-k.
+        ``self.route_disagreements`` then lists (layer, row, relative margin of the oracle's own decision)
+        for every row whose forced expert set differs from the oracle's."""
         cfg, dt = self.cfg, fjo.BF16
+        self.route_disagreements = []
         T, d, hq, kvh = len(token_ids), cfg["head_dim"], cfg["q_heads"], cfg["kv_heads"]
         eps, theta, G = cfg["eps"], cfg["theta"], cfg["group_size"]
         hidden = fjo.quant_embed(*self.w["embed"], fjo.BF16, np.asarray(token_ids, np.uint32), 4, G, dt)
+        # smallest gap, relative to the largest |logit| of the row, between the last routed expert and the first one
+        # left out, over all rows and layers of this call: tells a caller how close the routing was to a tie
+        self.last_min_margin = float("inf")
         positions = np.arange(start, start + T, dtype=np.uint32).astype(np.float32)
         normed = fjo.rms_norm(hidden, dt, self.w["layers"][0]["input_norm"], dt, eps)
         for li, L in enumerate(self.w["layers"]):
@@ -185,7 +200,16 @@ class MoeOracle:
                                       self.page_tokens)
             attended = np.ascontiguousarray(attended.transpose(1, 0, 2)).reshape(T, hq * d)
             hidden, normed = fjo.prog_residual_norm(hidden, self._q(attended, L["o"]), dt, L["post_norm"], dt, eps)
-            hidden, _, _, _ = self.moe(normed, hidden, L)
+            forced = None if forced_routes is None else forced_routes[li]
+            hidden, router_logits, _, _ = self.moe(normed, hidden, L, forced)
+            ranked = np.sort(router_logits.astype(np.float32), axis=-1)[:, ::-1]
+            k = cfg["top_k"]
+            gaps = (ranked[:, k - 1] - ranked[:, k]) / np.maximum(np.abs(ranked).max(axis=-1), 1e-30)
+            self.last_min_margin = min(self.last_min_margin, float(gaps.min()))
+            if forced is not None:
+                for row in range(T):
+                    if set(int(v) for v in forced[row]) != set(int(v) for v in self.own_experts[row]):
+                        self.route_disagreements.append((li, row, float(gaps[row])))
             nxt = self.w["layers"][li + 1]["input_norm"] if li + 1 < len(self.w["layers"]) else self.w["final_norm"]
             normed = fjo.prog_rms_norm(hidden, dt, nxt, dt, eps)
         logits = self._q(normed[T - 1:T], self.w["lm_head"])

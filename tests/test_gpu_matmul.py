@@ -38,9 +38,9 @@ def test_matmul_with_transposed_weight_view(dt, m, k, n):
 
 
 @pytest.mark.parametrize("dt", [fb.BF16, fb.F16])
-@pytest.mark.parametrize("m,k,n", [(1024, 256, 1024), (300, 128, 4000), (128, 1024, 8200), (2048, 64, 520), (777, 1984, 1333)])
+@pytest.mark.parametrize("m,k,n", [(2048, 256, 1280), (300, 128, 8000), (128, 1024, 19000), (4096, 64, 600), (1500, 1984, 1666)])
 def test_large_grids_run_on_tensor_memory_tiles(dt, m, k, n):
-    """At least 64 output tiles of 128 x 128 and K a multiple of 64: the tcgen05 kernel (TMEM accumulators);
+    """At least one 128 x 128 output tile per SM and K a multiple of 64: the tcgen05 kernel (TMEM accumulators);
     ragged M and N edges, one to 31 k steps. None of its bounded waits may run out."""
     rng = np.random.default_rng(m + k + n)
     be = backend()

@@ -48,6 +48,12 @@ def near_tie_flips(tokens, ref_tokens, got_logits):
 # the long prompts put more than 128 routes into one step: expert-bucketed tile GEMMs; the rest: one pass per route
 @pytest.mark.parametrize("cfg,prompts,steps", [(TINY, [5, 23, 9], 5), (CODER_LIKE, [3, 17, 1, 8], 6), (TINY, [70, 40, 9], 3), (CODER_LIKE, [40, 33], 2)])
 def test_moe_step_matches_oracle(cfg, prompts, steps):
+    """Two claims, checked separately. (1) Routing: every layer's top-k expert set on the GPU equals the oracle's,
+    except where the oracle's own decision was a near-tie (the last routed expert ahead of the first one left out
+    by less than 3 % of the row's largest router logit): the q8 router sums in another order on the GPU and its
+    input is bf16, so such ties may resolve the other way (the reference documents the effect,
+    engines/olmoe/README.md:157-165). (2) Values: with the GPU's routing handed to the oracle, logits agree within
+    max-abs rel 2e-2 and greedy tokens are equal or a near-tie of the logits."""
     rng = np.random.default_rng(3)
     be = backend()
     page, lanes = 16, len(prompts)
@@ -58,34 +64,51 @@ def test_moe_step_matches_oracle(cfg, prompts, steps):
     weights = engine.random_moe_weights(cfg, 11)
     embed, final_norm, lm_head, layers = upload_moe(be, weights)
     model = fb.MoeModel(be, pool, cfg, embed, final_norm, lm_head, layers)
+    model.capture_routes(True)
     ref = engine.MoeOracle(cfg, weights, physical, page)
     tables = [pool.table(lane) for lane in range(lanes)]
     generations = pool.generations()
     ids = [rng.integers(0, cfg["vocab"], n).astype(np.uint32) for n in prompts]
     logits = be.alloc(fb.BF16, (lanes, cfg["vocab"]))
     fjo.set_threads(fjo.max_threads())
+    decisions = disagreements = flips = 0
+
+    def replay(step_tokens, starts, counts, where):
+        """Runs the oracle for every lane of the step that just ran on the GPU, with the GPU's routing."""
+        nonlocal decisions, disagreements
+        rows = int(sum(counts))
+        routes = [model.routes(layer, rows)[0] for layer in range(cfg["layers"])]
+        got = down(logits)
+        out_tokens, offset = [], 0
+        for lane in range(lanes):
+            n = counts[lane]
+            forced = [r[offset:offset + n] for r in routes]
+            want, tok = ref.forward_lane(step_tokens[lane], starts[lane], tables[lane], generations, forced_routes=forced)
+            offset += n
+            decisions += n * cfg["layers"]
+            for layer, row, margin in ref.route_disagreements:
+                assert margin < 0.03, f"{where} lane {lane} layer {layer} row {row}: experts differ although the oracle's margin was {margin:.3f}"
+            disagreements += len(ref.route_disagreements)
+            err = max_abs_rel(got[lane], want)
+            assert err <= 2e-2, f"{where} lane {lane}: logits max-abs rel {err:.3e}"
+            out_tokens.append(tok)
+        return got, out_tokens
+
     pool.pack_step([0] * lanes, prompts)
     tokens = model.step(np.concatenate(ids), lanes=lanes, logits=logits)
-    got = down(logits)
-    ref_tokens, flips = [], 0
-    for lane in range(lanes):
-        want, tok = ref.forward_lane(ids[lane], 0, tables[lane], generations)
-        ref_tokens.append(tok)
-        assert max_abs_rel(got[lane], want) <= 2e-2, f"prefill lane {lane}"
+    got, ref_tokens = replay(ids, [0] * lanes, prompts, "prefill")
     flips += near_tie_flips(tokens, ref_tokens, got)
     positions = list(prompts)
     for step in range(steps):
         pool.pack_step(positions, [1] * lanes)
         tokens = model.step(np.array(ref_tokens, np.uint32), lanes=lanes, logits=logits)  # teacher-forced
-        got = down(logits)
-        for lane in range(lanes):
-            want, tok = ref.forward_lane([ref_tokens[lane]], positions[lane], tables[lane], generations)
-            ref_tokens[lane] = tok
-            assert max_abs_rel(got[lane], want) <= 2e-2, f"step {step} lane {lane}"
+        got, ref_tokens = replay([[t] for t in ref_tokens], positions, [1] * lanes, f"step {step}")
         flips += near_tie_flips(tokens, ref_tokens, got)
         positions = [p + 1 for p in positions]
     fjo.set_threads(1)
     assert flips <= max(1, int(0.05 * lanes * (steps + 1)))
+    assert disagreements <= max(2, int(0.02 * decisions)), f"{disagreements} of {decisions} routing decisions differ"
+    print(f"routing decisions {decisions}, resolved differently at near-ties {disagreements}, token near-tie flips {flips}")
     assert model.stats()["kernels"] > 0
     model.close()
     pool.close()
