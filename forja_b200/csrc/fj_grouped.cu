@@ -28,7 +28,7 @@ struct RouteTile {
 
 // One CTA: histogram of routes per expert, exclusive scan, arrange, tile list.
 __global__ void __launch_bounds__(1024) route_plan_kernel(const unsigned* __restrict__ indices, unsigned total, unsigned experts, unsigned* offsets /*[experts + 1]*/,
-                                                          unsigned* sorted /*[total]*/, RouteTile* tiles, unsigned* n_tiles, unsigned tiles_cap) {
+                                                          unsigned* sorted /*[total]*/, RouteTile* tiles, unsigned* n_tiles, unsigned tiles_cap, ErrorRecord* err) {
   extern __shared__ unsigned plan_smem[];
   pdl_sync();
   unsigned* count = plan_smem;           // [experts]
@@ -38,6 +38,7 @@ __global__ void __launch_bounds__(1024) route_plan_kernel(const unsigned* __rest
   for (unsigned r = threadIdx.x; r < total; r += blockDim.x) {
     const unsigned e = indices[r];
     if (e < experts) atomicAdd(&count[e], 1u);
+    else report_error(err, ERR_INDEX, e);  // left out of every bucket; the lowest bad id is reported (lib.rs:1078-1088)
   }
   __syncthreads();
   if (threadIdx.x == 0) {
@@ -83,8 +84,9 @@ struct GroupedArgs {
   const unsigned* sorted;           // route ids bucketed by expert
   const RouteTile* tiles;
   const unsigned* n_tiles;
-  void* out;                        // pair: bf16 [routes][n]; single: f32 [routes][n]
+  void* out;                        // pair: bf16 [routes][n]; single: f32 (or bf16 when out_bf16) [routes][n]
   unsigned k, n, src_div;           // A row of a route = route / src_div
+  int out_bf16;
 };
 
 template <bool kPair>
@@ -219,6 +221,10 @@ __global__ void __launch_bounds__(GT_THREADS) grouped_q4_gemm_kernel(GroupedArgs
           unsigned short* o = static_cast<unsigned short*>(p.out) + static_cast<size_t>(route) * p.n + col;
           if (col + 1 < p.n) *reinterpret_cast<unsigned*>(o) = pack_bf16(v0, v1);
           else *o = __bfloat16_as_ushort(__float2bfloat16_rn(v0));
+        } else if (p.out_bf16) {
+          unsigned short* o = static_cast<unsigned short*>(p.out) + static_cast<size_t>(route) * p.n + col;
+          if (col + 1 < p.n) *reinterpret_cast<unsigned*>(o) = pack_bf16(v0, v1);
+          else *o = __bfloat16_as_ushort(__float2bfloat16_rn(v0));
         } else {
           float* o = static_cast<float*>(p.out) + static_cast<size_t>(route) * p.n + col;
           if (col + 1 < p.n) *reinterpret_cast<float2*>(o) = make_float2(v0, v1);
@@ -255,9 +261,9 @@ PlanLayout plan_layout(void* plan, unsigned total_routes, unsigned experts) {
 }
 }  // namespace
 
-void launch_route_plan(Ctx& ctx, const unsigned* indices, unsigned total_routes, unsigned experts, void* plan) {
+void launch_route_plan(Ctx& ctx, const unsigned* indices, unsigned total_routes, unsigned experts, void* plan, ErrorRecord* err) {
   const PlanLayout l = plan_layout(plan, total_routes, experts);
-  launch_pdl(route_plan_kernel, dim3(1), dim3(1024), 2 * experts * sizeof(unsigned), ctx.stream, indices, total_routes, experts, l.offsets, l.sorted, l.tiles, l.n_tiles, l.tiles_cap);
+  launch_pdl(route_plan_kernel, dim3(1), dim3(1024), 2 * experts * sizeof(unsigned), ctx.stream, indices, total_routes, experts, l.offsets, l.sorted, l.tiles, l.n_tiles, l.tiles_cap, err);
   ctx.launches++;
 }
 
@@ -269,19 +275,51 @@ void launch_grouped_q4_pair(Ctx& ctx, const void* x, const unsigned* gate, const
                             const void* up_biases, const void* plan, unsigned total_routes, unsigned experts, unsigned src_div, void* act_out, unsigned k, unsigned n) {
   const PlanLayout l = plan_layout(const_cast<void*>(plan), total_routes, experts);
   GroupedArgs a{static_cast<const unsigned short*>(x), {gate, up}, {static_cast<const unsigned short*>(gate_scales), static_cast<const unsigned short*>(up_scales)},
-                {static_cast<const unsigned short*>(gate_biases), static_cast<const unsigned short*>(up_biases)}, l.sorted, l.tiles, l.n_tiles, act_out, k, n, src_div};
+                {static_cast<const unsigned short*>(gate_biases), static_cast<const unsigned short*>(up_biases)}, l.sorted, l.tiles, l.n_tiles, act_out, k, n, src_div, 1};
   dim3 grid((n + GT_BN - 1) / GT_BN, l.tiles_cap);
   launch_pdl(grouped_q4_gemm_kernel<true>, grid, dim3(GT_THREADS), 0, ctx.stream, a);
   ctx.launches++;
 }
 
 void launch_grouped_q4_single(Ctx& ctx, const void* x, const unsigned* packed, const void* scales, const void* biases, const void* plan, unsigned total_routes, unsigned experts,
-                              unsigned src_div, float* out, unsigned k, unsigned n) {
+                              unsigned src_div, void* out, bool out_bf16, unsigned k, unsigned n) {
   const PlanLayout l = plan_layout(const_cast<void*>(plan), total_routes, experts);
   GroupedArgs a{static_cast<const unsigned short*>(x), {packed, packed}, {static_cast<const unsigned short*>(scales), static_cast<const unsigned short*>(scales)},
-                {static_cast<const unsigned short*>(biases), static_cast<const unsigned short*>(biases)}, l.sorted, l.tiles, l.n_tiles, out, k, n, src_div};
+                {static_cast<const unsigned short*>(biases), static_cast<const unsigned short*>(biases)}, l.sorted, l.tiles, l.n_tiles, out, k, n, src_div, out_bf16 ? 1 : 0};
   dim3 grid((n + GT_BN - 1) / GT_BN, l.tiles_cap);
   launch_pdl(grouped_q4_gemm_kernel<false>, grid, dim3(GT_THREADS), 0, ctx.stream, a);
+  ctx.launches++;
+}
+
+namespace {
+// out[row] = (extra[row] +) sum_j weights[row, j] * per_route[slot(row, j)], j ascending, f32, each product rounded
+// before it is added: the arithmetic of the fused weighted-sum projection (lib.rs:1153-1199). route_slot == nullptr:
+// the result of route r sits in row r and routes whose expert id is out of range are skipped.
+__global__ void routes_combine_kernel(const float* __restrict__ per_route, const unsigned* __restrict__ route_slot, const unsigned* __restrict__ expert_ids, unsigned experts,
+                                      const void* __restrict__ weights, int w_dt, const void* __restrict__ extra, int e_dt, void* out, int out_dt, unsigned rows, unsigned top_k,
+                                      unsigned width) {
+  pdl_sync();
+  for (unsigned row = blockIdx.x; row < rows; row += gridDim.x) {
+    for (unsigned c = threadIdx.x; c < width; c += blockDim.x) {
+      float total = 0.0f;
+      for (unsigned j = 0; j < top_k; ++j) {
+        const unsigned slot = route_slot ? route_slot[row * top_k + j] : (expert_ids[row * top_k + j] < experts ? row * top_k + j : 0xFFFFFFFFu);
+        if (slot == 0xFFFFFFFFu) continue;
+        total = __fadd_rn(total, __fmul_rn(load_as_f32(weights, w_dt, row * top_k + j), per_route[static_cast<size_t>(slot) * width + c]));
+      }
+      const size_t o = static_cast<size_t>(row) * width + c;
+      if (extra) total = total + load_as_f32(extra, e_dt, o);
+      store_from_f32(out, out_dt, o, total);
+    }
+  }
+}
+}  // namespace
+
+void launch_routes_combine(Ctx& ctx, const float* per_route, const unsigned* route_slot, const unsigned* expert_ids, unsigned experts, const void* weights, int w_dt, const void* extra,
+                           int e_dt, void* out, int out_dt, unsigned rows, unsigned top_k, unsigned width) {
+  if (rows == 0) return;
+  launch_pdl(routes_combine_kernel, dim3(rows < 1024u ? rows : 1024u), dim3(256), 0, ctx.stream, per_route, route_slot, expert_ids, experts, weights, w_dt, extra, e_dt, out, out_dt, rows,
+             top_k, width);
   ctx.launches++;
 }
 

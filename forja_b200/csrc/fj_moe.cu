@@ -185,27 +185,6 @@ __global__ void ep_scatter_rows_kernel(const unsigned short* __restrict__ normed
   }
 }
 
-// out[row] = bf16(residual[row] + sum_j weights[row, j] * returned[route_slot[row, j]]), j ascending,
-// f32 accumulation: the arithmetic of the fused weighted-sum projection.
-// route_slot == nullptr: the result of route r sits in row r and routes whose expert id is out of range are skipped.
-__global__ void ep_combine_kernel(const float* __restrict__ returned, const unsigned* __restrict__ route_slot, const unsigned* __restrict__ expert_ids, unsigned experts,
-                                  const float* __restrict__ weights, const unsigned short* __restrict__ residual, unsigned short* out, unsigned rows, unsigned top_k,
-                                  unsigned width) {
-  for (unsigned row = blockIdx.x; row < rows; row += gridDim.x) {
-    for (unsigned c = threadIdx.x; c < width; c += blockDim.x) {
-      float total = 0.0f;
-      for (unsigned j = 0; j < top_k; ++j) {
-        const unsigned slot = route_slot ? route_slot[row * top_k + j] : (expert_ids[row * top_k + j] < experts ? row * top_k + j : 0xFFFFFFFFu);
-        if (slot == 0xFFFFFFFFu) continue;
-        total = __fadd_rn(total, __fmul_rn(weights[row * top_k + j], returned[static_cast<size_t>(slot) * width + c]));
-      }
-      const size_t o = static_cast<size_t>(row) * width + c;
-      total = total + fj::load_as_f32(residual, fj::BF16, o);
-      fj::store_from_f32(out, fj::BF16, o, total);
-    }
-  }
-}
-
 }  // namespace
 
 // ---- the model ------------------------------------------------------------------------------------
@@ -547,12 +526,10 @@ extern "C" int32_t fj_moe_step(fj_moe_model* m, const uint32_t* token_ids, uint3
       const unsigned routes = rows * K;
       if (routes >= kGroupedRoutes && G == 64 && fj::grouped_q4_supported(H, I, 4, G, c.experts, m->normed, L.gate.packed) &&
           fj::grouped_q4_supported(I, H, 4, G, c.experts, m->act, L.down.packed)) {
-        fj::launch_route_plan(ctx, m->route_experts, routes, c.experts, m->route_plan);
+        fj::launch_route_plan(ctx, m->route_experts, routes, c.experts, m->route_plan, nullptr);
         fj::launch_grouped_q4_pair(ctx, m->normed, L.gate.packed, L.gate.scales, L.gate.biases, L.up.packed, L.up.scales, L.up.biases, m->route_plan, routes, c.experts, K, m->act, H, I);
-        fj::launch_grouped_q4_single(ctx, m->act, L.down.packed, L.down.scales, L.down.biases, m->route_plan, routes, c.experts, 1, m->down_routes, I, H);
-        ep_combine_kernel<<<std::min(rows, 1024u), 256, 0, be->stream>>>(m->down_routes, nullptr, m->route_experts, c.experts, m->route_weights,
-                                                                         static_cast<const unsigned short*>(hidden), static_cast<unsigned short*>(other), rows, K, H);
-        ctx.launches++;
+        fj::launch_grouped_q4_single(ctx, m->act, L.down.packed, L.down.scales, L.down.biases, m->route_plan, routes, c.experts, 1, m->down_routes, false, I, H);
+        fj::launch_routes_combine(ctx, m->down_routes, nullptr, m->route_experts, c.experts, m->route_weights, FJ_F32, hidden, dt, other, dt, rows, K, H);
       } else {
         fj::launch_gather_quant_matmul(ctx, m->normed, dt, L.gate.packed, L.gate.scales, L.gate.biases, dt, L.up.packed, L.up.scales, L.up.biases, m->route_experts, m->act, dt, rows, H,
                                        c.experts, I, K, 4, G, 1, nullptr);
@@ -596,10 +573,10 @@ extern "C" int32_t fj_moe_step(fj_moe_model* m, const uint32_t* token_ids, uint3
         // rows received for this rank's experts, densely packed by source: one route each
         if (received >= kGroupedRoutes && G == 64 && fj::grouped_q4_supported(H, I, 4, G, m->experts_local, m->recv_rows, L.gate.packed) &&
             fj::grouped_q4_supported(I, H, 4, G, m->experts_local, m->act_ep, L.down.packed)) {
-          fj::launch_route_plan(ctx, m->recv_experts, received, m->experts_local, m->route_plan);
+          fj::launch_route_plan(ctx, m->recv_experts, received, m->experts_local, m->route_plan, nullptr);
           fj::launch_grouped_q4_pair(ctx, m->recv_rows, L.gate.packed, L.gate.scales, L.gate.biases, L.up.packed, L.up.scales, L.up.biases, m->route_plan, received, m->experts_local, 1,
                                      m->act_ep, H, I);
-          fj::launch_grouped_q4_single(ctx, m->act_ep, L.down.packed, L.down.scales, L.down.biases, m->route_plan, received, m->experts_local, 1, m->down_ep, I, H);
+          fj::launch_grouped_q4_single(ctx, m->act_ep, L.down.packed, L.down.scales, L.down.biases, m->route_plan, received, m->experts_local, 1, m->down_ep, false, I, H);
         } else {
           fj::launch_gather_quant_matmul(ctx, m->recv_rows, dt, L.gate.packed, L.gate.scales, L.gate.biases, dt, L.up.packed, L.up.scales, L.up.biases, m->recv_experts, m->act_ep, dt,
                                          received, H, m->experts_local, I, 1, 4, G, 1, nullptr);
@@ -610,9 +587,7 @@ extern "C" int32_t fj_moe_step(fj_moe_model* m, const uint32_t* token_ids, uint3
       status = ep_all_to_all_rows(m->ep, m->down_ep, packed_at.data(), recv_counts, m->returned, slab_at.data(), send_counts, static_cast<size_t>(H) * 4);
       if (status != FJ_OK) break;
       if (rows) {
-        ep_combine_kernel<<<std::min(rows, 1024u), 256, 0, be->stream>>>(m->returned, m->route_slot, nullptr, 0, m->route_weights, static_cast<const unsigned short*>(hidden),
-                                                                         static_cast<unsigned short*>(other), rows, K, H);
-        ctx.launches++;
+        fj::launch_routes_combine(ctx, m->returned, m->route_slot, nullptr, 0, m->route_weights, FJ_F32, hidden, dt, other, dt, rows, K, H);
       }
     }
     std::swap(hidden, other);

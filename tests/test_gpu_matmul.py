@@ -183,7 +183,8 @@ def test_gather_quant_weighted_sum_known_answer():
     assert down(out).ravel().tolist() == [473.5, 582.0]
 
 
-@pytest.mark.parametrize("rows", [1, 8, 33])
+# 33 and 200 rows x 8 routes cross the 128-route threshold: expert-bucketed tile GEMMs instead of one pass per route
+@pytest.mark.parametrize("rows", [1, 8, 33, 200])
 def test_moe_expert_projections_match_oracle(rows):
     """Qwen3-30B-A3B expert shapes at a reduced expert count: gate/up pair 2048 -> 768 with the
     gate*sigmoid(gate)*up epilogue, then the weighted down projection 768 -> 2048 plus residual
@@ -216,3 +217,29 @@ def test_moe_expert_projections_match_oracle(rows):
     want = fjo.prog_add(acc, fjo.decode(resh, dt), fjo.F32, dt)
     fjo.set_threads(1)
     assert_close(down(out), fjo.decode(want, dt), QUANT_TOL)
+
+
+def test_bucketed_expert_path_zeroes_bad_routes_and_reports_the_lowest_id():
+    """More than 128 routes with two out-of-range expert ids: their rows are zero, every other row is computed,
+    and the submission fails with the lowest offending id (crates/forja-cpu/src/lib.rs:1078-1088)."""
+    rng = np.random.default_rng(5)
+    be = backend()
+    experts, hidden, inter, top_k, rows = 8, 512, 128, 4, 40
+    dt = fb.BF16
+    pk, sc, bi = quant_weights(rng, inter, hidden, 4, 64, fb.BF16, experts)
+    x, xh = up(rng.standard_normal((rows, hidden)), dt)
+    ids = rng.integers(0, experts, (rows, top_k)).astype(np.uint32)
+    ids[3, 1], ids[17, 0] = 99, 77
+    idx, _ = up_u32(ids)
+    out = be.alloc(dt, (rows, top_k, inter))
+    with pytest.raises(fb.BackendError) as info:
+        be.run(Op.GatherQuantMatmul(4, 64), [x, be.tensor_from(pk, fb.U32), be.tensor_from(sc, fb.BF16), be.tensor_from(bi, fb.BF16), idx], [out])
+    assert info.value.index == 77
+    got = down(out)
+    assert np.all(got[3, 1] == 0.0) and np.all(got[17, 0] == 0.0)
+    good = ids.copy()
+    good[3, 1], good[17, 0] = 0, 0
+    want = fjo.decode(fjo.gather_quant_matmul(xh, dt, pk, sc, bi, fjo.BF16, good, 4, 64, dt), dt)
+    mask = np.ones((rows, top_k), bool)
+    mask[3, 1] = mask[17, 0] = False
+    assert_close(got[mask], want[mask], QUANT_TOL)
