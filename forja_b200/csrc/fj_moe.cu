@@ -139,10 +139,13 @@ int32_t ep_all_to_all(fj_ep* ep, const void* send, void* recv, size_t bytes_per_
 // Variable-size form: rank p gets send_counts[p] rows of row_bytes from send + send_rows_at[p] rows, and
 // its recv_counts[p] rows land at recv + recv_rows_at[p] rows. Counts are host values.
 int32_t ep_all_to_all_rows(fj_ep* ep, const void* send, const unsigned* send_rows_at, const unsigned* send_counts, void* recv, const unsigned* recv_rows_at,
-                           const unsigned* recv_counts, size_t row_bytes) {
+                           const unsigned* recv_counts, size_t row_bytes, const void* send2 = nullptr, void* recv2 = nullptr, size_t row_bytes2 = 0) {
   cudaStream_t stream = ep->be->stream;
   if (g_nccl.GroupStart() != 0) return FJ_DEVICE_EXECUTION_FAILED;
   int failed = 0;
+  // a second array with the same row layout (the expert id of every row) travels in the same group
+  for (int pass = 0; pass < (send2 ? 2 : 1); ++pass) {
+  if (pass == 1) { send = send2; recv = recv2; row_bytes = row_bytes2; }
   for (uint32_t peer = 0; peer < ep->world; ++peer) {
     const char* s = static_cast<const char*>(send) + static_cast<size_t>(send_rows_at[peer]) * row_bytes;
     char* r = static_cast<char*>(recv) + static_cast<size_t>(recv_rows_at[peer]) * row_bytes;
@@ -152,6 +155,7 @@ int32_t ep_all_to_all_rows(fj_ep* ep, const void* send, const unsigned* send_row
     }
     if (send_counts[peer]) failed |= g_nccl.Send(s, static_cast<size_t>(send_counts[peer]) * row_bytes, kNcclInt8, static_cast<int>(peer), ep->comm, stream);
     if (recv_counts[peer]) failed |= g_nccl.Recv(r, static_cast<size_t>(recv_counts[peer]) * row_bytes, kNcclInt8, static_cast<int>(peer), ep->comm, stream);
+  }
   }
   if (g_nccl.GroupEnd() != 0 || failed) return FJ_DEVICE_EXECUTION_FAILED;
   return FJ_OK;
@@ -566,8 +570,8 @@ extern "C" int32_t fj_moe_step(fj_moe_model* m, const uint32_t* token_ids, uint3
         for (unsigned p = 0; p < W; ++p) { slab_at[p] = p * cap; packed_at[p] = received; received += recv_counts[p]; }
         if (received > W * cap) { status = FJ_EXECUTION_FAILED; break; }
       }
-      status = ep_all_to_all_rows(m->ep, m->send_rows, slab_at.data(), send_counts, m->recv_rows, packed_at.data(), recv_counts, static_cast<size_t>(H) * 2);
-      if (status == FJ_OK) status = ep_all_to_all_rows(m->ep, m->send_experts, slab_at.data(), send_counts, m->recv_experts, packed_at.data(), recv_counts, 4);
+      status = ep_all_to_all_rows(m->ep, m->send_rows, slab_at.data(), send_counts, m->recv_rows, packed_at.data(), recv_counts, static_cast<size_t>(H) * 2, m->send_experts,
+                                  m->recv_experts, 4);
       if (status != FJ_OK) break;
       if (received) {
         // rows received for this rank's experts, densely packed by source: one route each
