@@ -129,6 +129,8 @@ def run_moe(args):
         cfg["layers"] = args.layers
     lanes = args.lanes // world
     cfg["max_rows"] = lanes + (0 if args.decode_only else args.prompt_budget)
+    cfg["grouped_min_routes"] = args.grouped_min_routes
+    cfg["stream_rows_per_expert"] = args.stream_rows_per_expert
     be = fb.CudaBackend(local_rank)
     ep = None
     if world > 1:
@@ -324,6 +326,8 @@ def main():
     moe.add_argument("--prompt-budget", type=int, default=2048)
     moe.add_argument("--prefill-limit", type=int, default=4)
     moe.add_argument("--decode-only", action="store_true")
+    moe.add_argument("--grouped-min-routes", type=int, default=0, help="0 = library default")
+    moe.add_argument("--stream-rows-per-expert", type=int, default=0, help="0 = library default")
     q4 = sub.add_parser("q4")
     q4.add_argument("--shapes", default="qkv,o,expert,lm_head")
     q4.add_argument("--m", default="1,8,64,512,4096")

@@ -575,8 +575,11 @@ int32_t exec_quant_matmul(Exec& x, const fj_dispatch& d) {
   return FJ_OK;
 }
 
-// From this many routes on, GatherQuantMatmul buckets the routes by expert and runs tile GEMMs (weights rounded to bf16).
-constexpr uint64_t kGroupedRoutes = 128;
+// From this many routes on, GatherQuantMatmul buckets the routes by expert: 16-row tiles that stream each active
+// expert once while the average expert has fewer than kStreamRowsPerExpert rows, 64-row tile GEMMs (weights rounded
+// to bf16) beyond that.
+constexpr uint64_t kGroupedRoutes = 64;
+constexpr uint64_t kStreamRowsPerExpert = 24;
 
 int32_t exec_gather_quant(Exec& x, const fj_dispatch& d, fj::ErrorRecord* err) {
   if (d.n_outputs != 1 || !quant_params_ok(d.u0, d.u1)) return FJ_INVALID_INPUT;
@@ -601,12 +604,17 @@ int32_t exec_gather_quant(Exec& x, const fj_dispatch& d, fj::ErrorRecord* err) {
     if (epilogue == 2 && element_count(d.inputs[6]) != element_count(d.outputs[0])) return FJ_INVALID_INPUT;
     // many routes: bucket by expert, tile GEMMs into per-route f32 rows, then the ordered weighted sum
     const uint64_t total = static_cast<uint64_t>(rows) * routes;
-    if (total >= kGroupedRoutes && total < (1u << 30) && act.dtype == FJ_BF16 && d.inputs[2].dtype == FJ_BF16 && fj::grouped_q4_supported(k, n, d.u0, d.u1, experts, ap, pp)) {
+    const bool bucket_ok = total >= kGroupedRoutes && total < (1u << 30) && act.dtype == FJ_BF16 && d.inputs[2].dtype == FJ_BF16;
+    const bool stream = bucket_ok && total < kStreamRowsPerExpert * experts && fj::expert_stream_supported(k, n, d.u0, d.u1, experts, ap, pp, sp, bp);
+    if (stream || (bucket_ok && fj::grouped_q4_supported(k, n, d.u0, d.u1, experts, ap, pp))) {
       void* plan = x.temp(fj::route_plan_bytes(static_cast<unsigned>(total), experts));
       float* per_route = static_cast<float*>(x.temp(total * n * sizeof(float)));
       if (!plan || !per_route) return FJ_ALLOCATION_FAILED;
-      fj::launch_route_plan(x.be->ctx, static_cast<const unsigned*>(ip), static_cast<unsigned>(total), experts, plan, err);
-      fj::launch_grouped_q4_single(x.be->ctx, ap, static_cast<const unsigned*>(pp), sp, bp, plan, static_cast<unsigned>(total), experts, 1, per_route, false, k, n);
+      fj::launch_route_plan(x.be->ctx, static_cast<const unsigned*>(ip), static_cast<unsigned>(total), experts, plan, err, stream ? 16 : 64);
+      if (stream) {
+        if (!fj::launch_expert_stream_single(x.be->ctx, ap, static_cast<const unsigned*>(pp), sp, bp, plan, static_cast<unsigned>(total), experts, 1, per_route, false, k, n))
+          return FJ_DEVICE_EXECUTION_FAILED;
+      } else fj::launch_grouped_q4_single(x.be->ctx, ap, static_cast<const unsigned*>(pp), sp, bp, plan, static_cast<unsigned>(total), experts, 1, per_route, false, k, n);
       fj::launch_routes_combine(x.be->ctx, per_route, nullptr, static_cast<const unsigned*>(ip), experts, wp, wt.dtype, ex, epilogue == 2 ? d.inputs[6].dtype : 0, out,
                                 d.outputs[0].dtype, rows, routes, n);
       return FJ_OK;
@@ -628,14 +636,22 @@ int32_t exec_gather_quant(Exec& x, const fj_dispatch& d, fj::ErrorRecord* err) {
   void* out = x.output(d.outputs[0]);
   if (!xp || !pp || !sp || !bp || !ip || !out) return FJ_INVALID_INPUT;
   const uint64_t total = static_cast<uint64_t>(rows) * routes;
-  if (total >= kGroupedRoutes && total < (1u << 30) && xt.dtype == FJ_BF16 && d.outputs[0].dtype == FJ_BF16 && d.inputs[2].dtype == FJ_BF16 &&
-      (!paired || d.inputs[5].dtype == FJ_BF16) && fj::grouped_q4_supported(k, n, d.u0, d.u1, experts, xp, pp) && (!paired || reinterpret_cast<size_t>(pp2) % 16 == 0)) {
+  const bool bucket_ok = total >= kGroupedRoutes && total < (1u << 30) && xt.dtype == FJ_BF16 && d.outputs[0].dtype == FJ_BF16 && d.inputs[2].dtype == FJ_BF16 &&
+                         (!paired || d.inputs[5].dtype == FJ_BF16);
+  const bool stream = bucket_ok && total < kStreamRowsPerExpert * experts && fj::expert_stream_supported(k, n, d.u0, d.u1, experts, xp, pp, sp, bp) &&
+                      (!paired || fj::expert_stream_supported(k, n, d.u0, d.u1, experts, xp, pp2, sp2, bp2));
+  if (stream || (bucket_ok && fj::grouped_q4_supported(k, n, d.u0, d.u1, experts, xp, pp) && (!paired || reinterpret_cast<size_t>(pp2) % 16 == 0))) {
     // routes with an out-of-range expert id belong to no bucket: their rows stay zero and the lowest id is reported
     void* plan = x.temp(fj::route_plan_bytes(static_cast<unsigned>(total), experts));
     if (!plan) return FJ_ALLOCATION_FAILED;
     cudaMemsetAsync(out, 0, total * n * 2, x.be->stream);
-    fj::launch_route_plan(x.be->ctx, static_cast<const unsigned*>(ip), static_cast<unsigned>(total), experts, plan, err);
-    if (paired)
+    fj::launch_route_plan(x.be->ctx, static_cast<const unsigned*>(ip), static_cast<unsigned>(total), experts, plan, err, stream ? 16 : 64);
+    if (stream) {
+      const bool ok = paired ? fj::launch_expert_stream_pair(x.be->ctx, xp, static_cast<const unsigned*>(pp), sp, bp, static_cast<const unsigned*>(pp2), sp2, bp2, plan,
+                                                             static_cast<unsigned>(total), experts, routes, out, k, n)
+                             : fj::launch_expert_stream_single(x.be->ctx, xp, static_cast<const unsigned*>(pp), sp, bp, plan, static_cast<unsigned>(total), experts, routes, out, true, k, n);
+      if (!ok) return FJ_DEVICE_EXECUTION_FAILED;
+    } else if (paired)
       fj::launch_grouped_q4_pair(x.be->ctx, xp, static_cast<const unsigned*>(pp), sp, bp, static_cast<const unsigned*>(pp2), sp2, bp2, plan, static_cast<unsigned>(total), experts, routes,
                                  out, k, n);
     else

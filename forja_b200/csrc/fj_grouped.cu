@@ -15,6 +15,9 @@
 // The order of rows inside an expert's bucket is whatever the atomics give; it only decides which
 // tile a row lands in, never its value.
 #include "fj_kernels.h"
+#include "fj_q4_i8.cuh"
+
+#include <algorithm>
 
 namespace fj {
 
@@ -28,7 +31,7 @@ struct RouteTile {
 
 // One CTA: histogram of routes per expert, exclusive scan, arrange, tile list.
 __global__ void __launch_bounds__(1024) route_plan_kernel(const unsigned* __restrict__ indices, unsigned total, unsigned experts, unsigned* offsets /*[experts + 1]*/,
-                                                          unsigned* sorted /*[total]*/, RouteTile* tiles, unsigned* n_tiles, unsigned tiles_cap, ErrorRecord* err) {
+                                                          unsigned* sorted /*[total]*/, RouteTile* tiles, unsigned* n_tiles, unsigned tiles_cap, unsigned tile_rows, ErrorRecord* err) {
   extern __shared__ unsigned plan_smem[];
   pdl_sync();
   unsigned* count = plan_smem;           // [experts]
@@ -46,8 +49,8 @@ __global__ void __launch_bounds__(1024) route_plan_kernel(const unsigned* __rest
     for (unsigned e = 0; e < experts; ++e) {
       offsets[e] = running;
       cursor[e] = running;
-      for (unsigned f = 0; f < count[e]; f += GT_BM) {
-        if (made < tiles_cap) tiles[made] = RouteTile{e, running + f, min(static_cast<unsigned>(GT_BM), count[e] - f)};
+      for (unsigned f = 0; f < count[e]; f += tile_rows) {
+        if (made < tiles_cap) tiles[made] = RouteTile{e, running + f, min(tile_rows, count[e] - f)};
         ++made;
       }
       running += count[e];
@@ -234,10 +237,174 @@ __global__ void __launch_bounds__(GT_THREADS) grouped_q4_gemm_kernel(GroupedArgs
     }
 }
 
+// ---- streaming form for few rows per expert (decode) ----
+// With a handful of rows per expert the projections are bound by reading every active expert's
+// nibbles once. The routes are bucketed as above but cut into tiles of 16 rows; CTA (chunk, tile)
+// converts the tile's rows to block fixed point in shared memory once and its warps stream
+// 16-column weight tiles of that expert (units of 256 k through a per-warp cp.async ring) into
+// int8 tensor-core products, exactly like the plain decode projections. Pair mode streams the
+// gate tile and then the up tile of the same columns and stores silu(gate) * up.
+struct ExpertStreamArgs {
+  const unsigned short* x;
+  const unsigned* packed[2];
+  const unsigned short* scales[2];
+  const unsigned short* biases[2];
+  const unsigned* sorted;
+  const RouteTile* tiles;
+  const unsigned* n_tiles;
+  void* out;  // [routes][n]: pair bf16; single f32 (bf16 when out_bf16)
+  unsigned k, n, src_div, cols_per_cta;  // cols_per_cta: 16-column tiles per chunk
+  int out_bf16;
+};
+
+template <bool kPair, int NB, int STAGES, int WARPS>
+__device__ __forceinline__ void expert_stream_body(const ExpertStreamArgs& a, const RouteTile tile, unsigned char* smem, const unsigned* s_route) {
+  constexpr int MATS = kPair ? 2 : 1;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const unsigned g = lane >> 2, t = lane & 3;
+  const unsigned blocks = a.k / 64, upt = a.k / 256;
+  uint4* xq = reinterpret_cast<uint4*>(smem);                                              // [blocks][NB][2][32]
+  float2* xmeta = reinterpret_cast<float2*>(smem + static_cast<size_t>(blocks) * NB * 1024);  // [blocks][NB][8] {sum, step}
+  unsigned char* ring = smem + static_cast<size_t>(blocks) * 2 * Q4W_X_BYTES + warp * (STAGES * Q4W_UNIT_BYTES);
+  const unsigned ring_base = static_cast<unsigned>(__cvta_generic_to_shared(ring));
+
+  const unsigned col_tiles = (a.n + 15) / 16, c_begin = blockIdx.x * a.cols_per_cta, c_end = min(c_begin + a.cols_per_cta, col_tiles);
+  const unsigned c_first = c_begin + warp;
+  const unsigned my_cols = c_first < c_end ? (c_end - c_first + WARPS - 1) / WARPS : 0;
+  const unsigned items = my_cols * MATS * upt;
+  const size_t row_bytes = a.k / 2, expert_row0 = static_cast<size_t>(tile.expert) * a.n;
+  const unsigned copy_row = lane >> 3, copy_col = (lane & 7) * 16;
+  const unsigned param_which = lane >> 4, param_col = lane & 15;
+  const unsigned copy_dst = copy_row * Q4W_ROW_STRIDE + copy_col, param_dst = Q4W_PARAM_OFFSET + param_which * 128 + param_col * 8;
+
+  unsigned in_c = c_first, in_mat = 0, in_u = 0, in_stage = 0, in_count = 0;
+  const unsigned char* in_rows[4];
+  const unsigned short* in_param = nullptr;
+  auto issue = [&]() {
+    if (in_count < items) {
+      if (in_u == 0) {
+        const unsigned char* wbase = reinterpret_cast<const unsigned char*>(in_mat == 0 ? a.packed[0] : a.packed[MATS - 1]);
+        const unsigned short* pbase = param_which ? (in_mat == 0 ? a.biases[0] : a.biases[MATS - 1]) : (in_mat == 0 ? a.scales[0] : a.scales[MATS - 1]);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) in_rows[i] = wbase + (expert_row0 + min(in_c * 16 + copy_row + 4 * i, a.n - 1)) * row_bytes + copy_col;
+        in_param = pbase + (expert_row0 + min(in_c * 16 + param_col, a.n - 1)) * blocks;
+      }
+      const unsigned stage = ring_base + in_stage * Q4W_UNIT_BYTES;
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(stage + copy_dst + i * (4 * Q4W_ROW_STRIDE)), "l"(in_rows[i] + in_u * 128) : "memory");
+      asm volatile("cp.async.ca.shared.global [%0], [%1], 8;\n" ::"r"(stage + param_dst), "l"(in_param + in_u * 4) : "memory");
+    }
+    asm volatile("cp.async.commit_group;\n" ::: "memory");
+    ++in_count;
+    in_stage = in_stage + 1 == STAGES ? 0 : in_stage + 1;
+    if (++in_u == upt) {
+      in_u = 0;
+      if (++in_mat == MATS) { in_mat = 0; in_c += WARPS; }
+    }
+  };
+  for (int q = 0; q + 1 < STAGES; ++q) issue();  // weights are on their way while the rows are converted
+
+  const unsigned short* x_row[NB];
+#pragma unroll
+  for (int nb = 0; nb < NB; ++nb) {
+    const unsigned route = s_route[g + 8 * nb];
+    x_row[nb] = route == 0xFFFFFFFFu ? nullptr : a.x + static_cast<size_t>(route / a.src_div) * a.k + 16 * t;
+  }
+  for (unsigned b = warp; b < blocks; b += WARPS) {
+#pragma unroll
+    for (int nb = 0; nb < NB; ++nb)
+      q4_i8_convert_block(x_row[nb] ? x_row[nb] + b * 64 : nullptr, xq + ((b * NB + nb) * 2 + 0) * 32, xq + ((b * NB + nb) * 2 + 1) * 32, xmeta + (b * NB + nb) * 8, lane);
+  }
+  __syncthreads();
+
+  float y[NB][4], gate[NB][4];
+  unsigned c = c_first, mat = 0, u = 0, out_stage = 0;
+  for (unsigned q = 0; q < items; ++q) {
+    asm volatile("cp.async.wait_group %0;\n" ::"n"(STAGES - 2) : "memory");
+    __syncwarp();  // unit q is visible to the whole warp, and the warp is done with unit q - 1
+    issue();
+    if (u == 0) {
+#pragma unroll
+      for (int nb = 0; nb < NB; ++nb) y[nb][0] = y[nb][1] = y[nb][2] = y[nb][3] = 0.0f;
+    }
+    q4_i8_unit_g64<NB>(ring + out_stage * Q4W_UNIT_BYTES, xq + static_cast<size_t>(u * 4) * (NB * 2 * 32), xmeta + static_cast<size_t>(u * 4) * (NB * 8), lane, y);
+    out_stage = out_stage + 1 == STAGES ? 0 : out_stage + 1;
+    if (++u == upt) {
+      u = 0;
+      if (kPair && mat == 0) {
+#pragma unroll
+        for (int nb = 0; nb < NB; ++nb)
+#pragma unroll
+          for (int i = 0; i < 4; ++i) gate[nb][i] = y[nb][i];
+        mat = 1;
+      } else {
+#pragma unroll
+        for (int nb = 0; nb < NB; ++nb)
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const unsigned route = s_route[8 * nb + 2 * t + (i & 1)], col = c * 16 + g + (i >> 1) * 8;
+            if (route == 0xFFFFFFFFu || col >= a.n) continue;
+            const size_t o = static_cast<size_t>(route) * a.n + col;
+            float v = y[nb][i];
+            if (kPair) v = gate[nb][i] * (1.0f / (1.0f + expf(-gate[nb][i]))) * v;
+            if (kPair || a.out_bf16) static_cast<unsigned short*>(a.out)[o] = __bfloat16_as_ushort(__float2bfloat16_rn(v));
+            else static_cast<float*>(a.out)[o] = v;
+          }
+        mat = 0;
+        c += WARPS;
+      }
+    }
+  }
+  asm volatile("cp.async.wait_group 0;\n" ::: "memory");
+}
+
+template <bool kPair, int STAGES, int WARPS>
+__global__ void __launch_bounds__(WARPS * 32, 1) expert_q4_stream_kernel(ExpertStreamArgs a) {
+  extern __shared__ __align__(128) unsigned char es_smem[];
+  unsigned* s_route = reinterpret_cast<unsigned*>(es_smem + static_cast<size_t>(a.k / 64) * 2 * Q4W_X_BYTES + static_cast<size_t>(WARPS) * STAGES * Q4W_UNIT_BYTES);  // [16]
+  pdl_sync();  // the plan and the rows come from the kernels before
+  if (blockIdx.y >= *a.n_tiles) return;
+  const RouteTile tile = a.tiles[blockIdx.y];
+  if (threadIdx.x < 16) s_route[threadIdx.x] = threadIdx.x < tile.count ? a.sorted[tile.first + threadIdx.x] : 0xFFFFFFFFu;
+  __syncthreads();
+  if (tile.count <= 8) expert_stream_body<kPair, 1, STAGES, WARPS>(a, tile, es_smem, s_route);
+  else expert_stream_body<kPair, 2, STAGES, WARPS>(a, tile, es_smem, s_route);
+}
+
+template <bool kPair, int STAGES, int WARPS>
+bool launch_expert_stream(Ctx& ctx, ExpertStreamArgs a, unsigned tiles_cap, unsigned est_tiles) {
+  const size_t smem = static_cast<size_t>(a.k / 64) * 2 * Q4W_X_BYTES + static_cast<size_t>(WARPS) * STAGES * Q4W_UNIT_BYTES + 64;  // + the tile's 16 route ids
+  if (smem > 227 * 1024) return false;
+  static bool configured[64] = {};
+  int device = 0;
+  cudaGetDevice(&device);
+  if (device < 0 || device >= 64) return false;
+  if (!configured[device]) {
+    if (cudaFuncSetAttribute(expert_q4_stream_kernel<kPair, STAGES, WARPS>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) != cudaSuccess) { cudaGetLastError(); return false; }
+    configured[device] = true;
+  }
+  // enough CTAs for about three per SM, never less than one 16-column tile per warp
+  const unsigned sms = static_cast<unsigned>(ctx.sm_count > 0 ? ctx.sm_count : 148), col_tiles = (a.n + 15) / 16;
+  unsigned chunks = (3 * sms + est_tiles - 1) / std::max(est_tiles, 1u);
+  chunks = std::max(1u, std::min(chunks, std::max(1u, col_tiles / WARPS)));
+  a.cols_per_cta = (col_tiles + chunks - 1) / chunks;
+  chunks = (col_tiles + a.cols_per_cta - 1) / a.cols_per_cta;
+  launch_pdl(expert_q4_stream_kernel<kPair, STAGES, WARPS>, dim3(chunks, tiles_cap), dim3(WARPS * 32), smem, ctx.stream, a);
+  ctx.launches++;
+  return true;
+}
+
+template <bool kPair>
+bool run_expert_stream(Ctx& ctx, const ExpertStreamArgs& a, unsigned tiles_cap, unsigned est_tiles) {
+  return launch_expert_stream<kPair, 4, 16>(ctx, a, tiles_cap, est_tiles) || launch_expert_stream<kPair, 3, 16>(ctx, a, tiles_cap, est_tiles) ||
+         launch_expert_stream<kPair, 3, 8>(ctx, a, tiles_cap, est_tiles);
+}
+
 }  // namespace
 
 size_t route_plan_bytes(unsigned total_routes, unsigned experts) {
-  const size_t tiles_cap = total_routes / GT_BM + experts + 1;
+  const size_t tiles_cap = total_routes / 16 + experts + 1;  // sized for the smallest tile height (16 rows)
   return (static_cast<size_t>(experts) + 1 + total_routes + 4) * sizeof(unsigned) + tiles_cap * sizeof(RouteTile) + 64;
 }
 
@@ -256,14 +423,15 @@ PlanLayout plan_layout(void* plan, unsigned total_routes, unsigned experts) {
   size_t words = 4 + static_cast<size_t>(experts) + 1 + total_routes;
   words = (words + 3) / 4 * 4;
   l.tiles = reinterpret_cast<RouteTile*>(base + words);
-  l.tiles_cap = total_routes / GT_BM + experts + 1;
+  l.tiles_cap = total_routes / 16 + experts + 1;
   return l;
 }
 }  // namespace
 
-void launch_route_plan(Ctx& ctx, const unsigned* indices, unsigned total_routes, unsigned experts, void* plan, ErrorRecord* err) {
+void launch_route_plan(Ctx& ctx, const unsigned* indices, unsigned total_routes, unsigned experts, void* plan, ErrorRecord* err, unsigned tile_rows) {
   const PlanLayout l = plan_layout(plan, total_routes, experts);
-  launch_pdl(route_plan_kernel, dim3(1), dim3(1024), 2 * experts * sizeof(unsigned), ctx.stream, indices, total_routes, experts, l.offsets, l.sorted, l.tiles, l.n_tiles, l.tiles_cap, err);
+  launch_pdl(route_plan_kernel, dim3(1), dim3(1024), 2 * experts * sizeof(unsigned), ctx.stream, indices, total_routes, experts, l.offsets, l.sorted, l.tiles, l.n_tiles, l.tiles_cap,
+             tile_rows, err);
   ctx.launches++;
 }
 
@@ -289,6 +457,31 @@ void launch_grouped_q4_single(Ctx& ctx, const void* x, const unsigned* packed, c
   dim3 grid((n + GT_BN - 1) / GT_BN, l.tiles_cap);
   launch_pdl(grouped_q4_gemm_kernel<false>, grid, dim3(GT_THREADS), 0, ctx.stream, a);
   ctx.launches++;
+}
+
+bool expert_stream_supported(unsigned k, unsigned n, unsigned bits, unsigned group_size, unsigned experts, const void* x, const void* packed, const void* scales, const void* biases) {
+  return bits == 4 && group_size == 64 && k % 256 == 0 && k <= 4096 && n >= 1 && experts <= 4096 && reinterpret_cast<size_t>(x) % 16 == 0 && reinterpret_cast<size_t>(packed) % 16 == 0 &&
+         reinterpret_cast<size_t>(scales) % 8 == 0 && reinterpret_cast<size_t>(biases) % 8 == 0;
+}
+
+// The plan must have been made with 16-row tiles. live_routes: how many of the routes are expected to carry a valid
+// expert id (padded exchanges); it only sizes the grid.
+bool launch_expert_stream_pair(Ctx& ctx, const void* x, const unsigned* gate, const void* gate_scales, const void* gate_biases, const unsigned* up, const void* up_scales,
+                               const void* up_biases, const void* plan, unsigned total_routes, unsigned experts, unsigned src_div, void* act_out, unsigned k, unsigned n, unsigned live_routes) {
+  const PlanLayout l = plan_layout(const_cast<void*>(plan), total_routes, experts);
+  live_routes = std::min(live_routes, total_routes);
+  ExpertStreamArgs a{static_cast<const unsigned short*>(x), {gate, up}, {static_cast<const unsigned short*>(gate_scales), static_cast<const unsigned short*>(up_scales)},
+                     {static_cast<const unsigned short*>(gate_biases), static_cast<const unsigned short*>(up_biases)}, l.sorted, l.tiles, l.n_tiles, act_out, k, n, src_div, 0, 1};
+  return run_expert_stream<true>(ctx, a, l.tiles_cap, std::min(experts, live_routes) + live_routes / 16);
+}
+
+bool launch_expert_stream_single(Ctx& ctx, const void* x, const unsigned* packed, const void* scales, const void* biases, const void* plan, unsigned total_routes, unsigned experts,
+                                 unsigned src_div, void* out, bool out_bf16, unsigned k, unsigned n, unsigned live_routes) {
+  const PlanLayout l = plan_layout(const_cast<void*>(plan), total_routes, experts);
+  live_routes = std::min(live_routes, total_routes);
+  ExpertStreamArgs a{static_cast<const unsigned short*>(x), {packed, packed}, {static_cast<const unsigned short*>(scales), static_cast<const unsigned short*>(scales)},
+                     {static_cast<const unsigned short*>(biases), static_cast<const unsigned short*>(biases)}, l.sorted, l.tiles, l.n_tiles, out, k, n, src_div, 0, out_bf16 ? 1 : 0};
+  return run_expert_stream<false>(ctx, a, l.tiles_cap, std::min(experts, live_routes) + live_routes / 16);
 }
 
 namespace {

@@ -154,10 +154,10 @@ void launch_gather_quant_weighted_sum(Ctx& ctx, const void* act, int a_dt, const
                                       int epilogue, ErrorRecord* err);
 
 // ---- fj_grouped.cu --------------------------------------------------------------------------
-// Routes bucketed by expert and cut into 64-row tiles; `plan` is caller-owned device memory of
+// Routes bucketed by expert and cut into tiles of tile_rows rows (64 for the tile GEMMs, 16 for the streaming form); `plan` is caller-owned device memory of
 // route_plan_bytes(total_routes, experts). Ids >= experts are left out of every bucket.
 size_t route_plan_bytes(unsigned total_routes, unsigned experts);
-void launch_route_plan(Ctx& ctx, const unsigned* indices, unsigned total_routes, unsigned experts, void* plan, ErrorRecord* err);
+void launch_route_plan(Ctx& ctx, const unsigned* indices, unsigned total_routes, unsigned experts, void* plan, ErrorRecord* err, unsigned tile_rows = 64);
 bool grouped_q4_supported(unsigned k, unsigned n, unsigned bits, unsigned group_size, unsigned experts, const void* x, const void* packed);
 // act_out[route, :] = silu(x_r . gate_e) * (x_r . up_e) in bf16, x_r = x[route / src_div]; bf16 x, bf16 scales/biases, group 64.
 void launch_grouped_q4_pair(Ctx& ctx, const void* x, const unsigned* gate, const void* gate_scales, const void* gate_biases, const unsigned* up, const void* up_scales,
@@ -165,6 +165,15 @@ void launch_grouped_q4_pair(Ctx& ctx, const void* x, const unsigned* gate, const
 // out[route, :] = x[route / src_div] . W_e, f32 or (out_bf16) bf16.
 void launch_grouped_q4_single(Ctx& ctx, const void* x, const unsigned* packed, const void* scales, const void* biases, const void* plan, unsigned total_routes, unsigned experts,
                               unsigned src_div, void* out, bool out_bf16, unsigned k, unsigned n);
+// Streaming form of the two launchers above for few rows per expert; the plan must have been made with tile_rows = 16.
+// live_routes (only a hint for the grid): how many of the routes are expected to carry a valid expert id.
+// false: the kernel could not be configured on this device and nothing was launched.
+bool expert_stream_supported(unsigned k, unsigned n, unsigned bits, unsigned group_size, unsigned experts, const void* x, const void* packed, const void* scales, const void* biases);
+bool launch_expert_stream_pair(Ctx& ctx, const void* x, const unsigned* gate, const void* gate_scales, const void* gate_biases, const unsigned* up, const void* up_scales,
+                               const void* up_biases, const void* plan, unsigned total_routes, unsigned experts, unsigned src_div, void* act_out, unsigned k, unsigned n,
+                               unsigned live_routes = 0xFFFFFFFFu);
+bool launch_expert_stream_single(Ctx& ctx, const void* x, const unsigned* packed, const void* scales, const void* biases, const void* plan, unsigned total_routes, unsigned experts,
+                                 unsigned src_div, void* out, bool out_bf16, unsigned k, unsigned n, unsigned live_routes = 0xFFFFFFFFu);
 // out[row] = (extra[row] +) sum_j weights[row, j] * per_route[slot], j ascending (slot = route_slot[row, j], or the route itself).
 void launch_routes_combine(Ctx& ctx, const float* per_route, const unsigned* route_slot, const unsigned* expert_ids, unsigned experts, const void* weights, int w_dt, const void* extra,
                            int e_dt, void* out, int out_dt, unsigned rows, unsigned top_k, unsigned width);

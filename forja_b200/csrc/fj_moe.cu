@@ -524,15 +524,35 @@ extern "C" int32_t fj_moe_step(fj_moe_model* m, const uint32_t* token_ids, uint3
         cudaMemcpyAsync(m->captured_weights + at, m->route_weights, static_cast<size_t>(rows) * K * 4, cudaMemcpyDeviceToDevice, be->stream);
       }
     }
-    // Few routes: one GEMV-style pass per route. Many: bucket by expert and run tile GEMMs (weights rounded to bf16).
-    const unsigned kGroupedRoutes = c.grouped_min_routes ? c.grouped_min_routes : 128;
+    // Few routes: one GEMV-style pass per route. More: bucket by expert; while the average expert has few rows the
+    // 16-row tiles stream each active expert's nibbles once (int8 tensor cores), beyond that 64-row tile GEMMs
+    // (weights rounded to bf16) take over.
+    const unsigned kGroupedRoutes = c.grouped_min_routes ? c.grouped_min_routes : 64;
+    const unsigned kStreamRows = c.stream_rows_per_expert ? c.stream_rows_per_expert : 24;
+    // `live`: how many of the n_routes ids are expected to be valid (a padded exchange carries whole slabs)
+    auto bucketed = [&](const void* x, unsigned src_div, const unsigned* ids, unsigned n_routes, unsigned live, unsigned n_experts, void* act, float* down_out) -> bool {
+      if (live < kGroupedRoutes || G != 64) return false;
+      const bool stream = live < static_cast<uint64_t>(kStreamRows) * n_experts &&
+                          fj::expert_stream_supported(H, I, 4, G, n_experts, x, L.gate.packed, L.gate.scales, L.gate.biases) &&
+                          fj::expert_stream_supported(H, I, 4, G, n_experts, x, L.up.packed, L.up.scales, L.up.biases) &&
+                          fj::expert_stream_supported(I, H, 4, G, n_experts, act, L.down.packed, L.down.scales, L.down.biases);
+      if (stream) {
+        fj::launch_route_plan(ctx, ids, n_routes, n_experts, m->route_plan, nullptr, 16);
+        if (!fj::launch_expert_stream_pair(ctx, x, L.gate.packed, L.gate.scales, L.gate.biases, L.up.packed, L.up.scales, L.up.biases, m->route_plan, n_routes, n_experts, src_div, act, H,
+                                           I, live) ||
+            !fj::launch_expert_stream_single(ctx, act, L.down.packed, L.down.scales, L.down.biases, m->route_plan, n_routes, n_experts, 1, down_out, false, I, H, live))
+          status = FJ_DEVICE_EXECUTION_FAILED;
+        return true;
+      }
+      if (!fj::grouped_q4_supported(H, I, 4, G, n_experts, x, L.gate.packed) || !fj::grouped_q4_supported(I, H, 4, G, n_experts, act, L.down.packed)) return false;
+      fj::launch_route_plan(ctx, ids, n_routes, n_experts, m->route_plan, nullptr);
+      fj::launch_grouped_q4_pair(ctx, x, L.gate.packed, L.gate.scales, L.gate.biases, L.up.packed, L.up.scales, L.up.biases, m->route_plan, n_routes, n_experts, src_div, act, H, I);
+      fj::launch_grouped_q4_single(ctx, act, L.down.packed, L.down.scales, L.down.biases, m->route_plan, n_routes, n_experts, 1, down_out, false, I, H);
+      return true;
+    };
     if (m->world == 1) {
       const unsigned routes = rows * K;
-      if (routes >= kGroupedRoutes && G == 64 && fj::grouped_q4_supported(H, I, 4, G, c.experts, m->normed, L.gate.packed) &&
-          fj::grouped_q4_supported(I, H, 4, G, c.experts, m->act, L.down.packed)) {
-        fj::launch_route_plan(ctx, m->route_experts, routes, c.experts, m->route_plan, nullptr);
-        fj::launch_grouped_q4_pair(ctx, m->normed, L.gate.packed, L.gate.scales, L.gate.biases, L.up.packed, L.up.scales, L.up.biases, m->route_plan, routes, c.experts, K, m->act, H, I);
-        fj::launch_grouped_q4_single(ctx, m->act, L.down.packed, L.down.scales, L.down.biases, m->route_plan, routes, c.experts, 1, m->down_routes, false, I, H);
+      if (bucketed(m->normed, K, m->route_experts, routes, routes, c.experts, m->act, m->down_routes)) {
         fj::launch_routes_combine(ctx, m->down_routes, nullptr, m->route_experts, c.experts, m->route_weights, FJ_F32, hidden, dt, other, dt, rows, K, H);
       } else {
         fj::launch_gather_quant_matmul(ctx, m->normed, dt, L.gate.packed, L.gate.scales, L.gate.biases, dt, L.up.packed, L.up.scales, L.up.biases, m->route_experts, m->act, dt, rows, H,
@@ -575,19 +595,14 @@ extern "C" int32_t fj_moe_step(fj_moe_model* m, const uint32_t* token_ids, uint3
       if (status != FJ_OK) break;
       if (received) {
         // rows received for this rank's experts, densely packed by source: one route each
-        if (received >= kGroupedRoutes && G == 64 && fj::grouped_q4_supported(H, I, 4, G, m->experts_local, m->recv_rows, L.gate.packed) &&
-            fj::grouped_q4_supported(I, H, 4, G, m->experts_local, m->act_ep, L.down.packed)) {
-          fj::launch_route_plan(ctx, m->recv_experts, received, m->experts_local, m->route_plan, nullptr);
-          fj::launch_grouped_q4_pair(ctx, m->recv_rows, L.gate.packed, L.gate.scales, L.gate.biases, L.up.packed, L.up.scales, L.up.biases, m->route_plan, received, m->experts_local, 1,
-                                     m->act_ep, H, I);
-          fj::launch_grouped_q4_single(ctx, m->act_ep, L.down.packed, L.down.scales, L.down.biases, m->route_plan, received, m->experts_local, 1, m->down_ep, false, I, H);
-        } else {
+        if (!bucketed(m->recv_rows, 1, m->recv_experts, received, padded ? cap : received, m->experts_local, m->act_ep, m->down_ep)) {
           fj::launch_gather_quant_matmul(ctx, m->recv_rows, dt, L.gate.packed, L.gate.scales, L.gate.biases, dt, L.up.packed, L.up.scales, L.up.biases, m->recv_experts, m->act_ep, dt,
                                          received, H, m->experts_local, I, 1, 4, G, 1, nullptr);
           fj::launch_gather_quant_matmul(ctx, m->act_ep, dt, L.down.packed, L.down.scales, L.down.biases, dt, nullptr, nullptr, nullptr, m->recv_experts, m->down_ep, FJ_F32, received, I,
                                          m->experts_local, H, 1, 4, G, 0, nullptr);
         }
       }
+      if (status != FJ_OK) break;
       status = ep_all_to_all_rows(m->ep, m->down_ep, packed_at.data(), recv_counts, m->returned, slab_at.data(), send_counts, static_cast<size_t>(H) * 4);
       if (status != FJ_OK) break;
       if (rows) {

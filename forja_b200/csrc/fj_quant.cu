@@ -9,6 +9,7 @@
 //   sum_k x (s q + b) = s * sum_k x q + b * sum_k x   per group,
 // so the inner loop is one multiply-add per weight plus one running sum of x.
 #include "fj_kernels.h"
+#include "fj_q4_i8.cuh"
 
 #include <algorithm>
 
@@ -341,11 +342,6 @@ void run_q4_mma(Ctx& ctx, const Q4MmaArgs& a, int x_dt) {
 //    biases through its own ring of cp.async stages, so the steady state has no CTA barrier;
 //  * a unit's rows are 128 bytes apart in memory and 160 bytes apart in shared memory, which
 //    keeps the copies coalesced and the 8-byte fragment reads of 4 rows x 4 lanes conflict-free.
-constexpr int Q4W_ROW_STRIDE = 160;
-constexpr int Q4W_PARAM_OFFSET = 16 * Q4W_ROW_STRIDE;
-constexpr int Q4W_UNIT_BYTES = Q4W_PARAM_OFFSET + 256;  // scales [16][4] u16, biases [16][4] u16
-constexpr int Q4W_X_BYTES = 1024 + 64;                  // per (64-k block, 8-row tile): fragments + {sum, step} per row
-
 // Tiles [tile_base, tile_end) are dealt out in `rounds` rounds of (WARPS / ksplit) tiles per CTA, each tile
 // shared by ksplit warps along K. Phase 0 gives every warp of the grid the same number of whole tiles;
 // phase 1 spreads the remainder over as many warps as possible so that the tail costs a fraction of a tile.
@@ -356,17 +352,6 @@ struct Q4WarpArgs {
   Q4MmaArgs base;
   Q4Phase phase[2];
 };
-
-template <bool kSignedB>
-__device__ inline void mma_u8(int (&d)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3, unsigned b0, unsigned b1) {
-  if (kSignedB) {
-    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
-                 : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-  } else {
-    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.u8.u8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
-                 : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-  }
-}
 
 // bf16 activations and parameters only (f16 callers use the mantissa-offset kernel above).
 template <bool kG64, int NB, int STAGES, int WARPS>

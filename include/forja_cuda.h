@@ -380,9 +380,12 @@ typedef struct fj_moe_config {
   uint32_t group_size, router_bits;
   float eps, theta;
   uint32_t max_rows; /* largest number of token rows in one step */
-  /* Expert projections switch from one pass per route to expert-bucketed tile GEMMs (weights rounded
-   * to bf16) at this many routes; 0 = 128. A value above max_rows * top_k keeps the per-route path. */
+  /* Expert projections switch from one pass per route to expert-bucketed forms at this many routes
+   * (0 = 64); a value above max_rows * top_k keeps the per-route path. Bucketed routes run as 16-row
+   * tiles that stream each active expert once (int8 tensor cores) while routes < stream_rows_per_expert
+   * * experts (0 = 24), and as 64-row tile GEMMs (weights rounded to bf16) from there on. */
   uint32_t grouped_min_routes;
+  uint32_t stream_rows_per_expert;
 } fj_moe_config;
 typedef struct fj_moe_layer_weights {
   uint64_t input_norm, q_norm, k_norm, post_norm; /* bf16 [hidden], [head_dim], [head_dim], [hidden] */

@@ -183,8 +183,10 @@ def test_gather_quant_weighted_sum_known_answer():
     assert down(out).ravel().tolist() == [473.5, 582.0]
 
 
-# 33 and 200 rows x 8 routes cross the 128-route threshold: expert-bucketed tile GEMMs instead of one pass per route
-@pytest.mark.parametrize("rows", [1, 8, 33, 200])
+# 1 and 7 rows x 8 routes: one pass per route. 8 to 47 rows (64 to 376 routes, fewer than 24 per expert): routes bucketed by
+# expert into 16-row tiles that stream each expert once (8-row and 16-row forms, experts with more than one tile).
+# 200 rows: 64-row tile GEMMs.
+@pytest.mark.parametrize("rows", [1, 7, 8, 16, 33, 47, 200])
 def test_moe_expert_projections_match_oracle(rows):
     """Qwen3-30B-A3B expert shapes at a reduced expert count: gate/up pair 2048 -> 768 with the
     gate*sigmoid(gate)*up epilogue, then the weighted down projection 768 -> 2048 plus residual
@@ -219,12 +221,13 @@ def test_moe_expert_projections_match_oracle(rows):
     assert_close(down(out), fjo.decode(want, dt), QUANT_TOL)
 
 
-def test_bucketed_expert_path_zeroes_bad_routes_and_reports_the_lowest_id():
-    """More than 128 routes with two out-of-range expert ids: their rows are zero, every other row is computed,
+@pytest.mark.parametrize("rows", [40, 80])  # 160 routes: streamed 16-row tiles; 320 routes: 64-row tile GEMMs
+def test_bucketed_expert_path_zeroes_bad_routes_and_reports_the_lowest_id(rows):
+    """Bucketed routes with two out-of-range expert ids: their rows are zero, every other row is computed,
     and the submission fails with the lowest offending id (crates/forja-cpu/src/lib.rs:1078-1088)."""
     rng = np.random.default_rng(5)
     be = backend()
-    experts, hidden, inter, top_k, rows = 8, 512, 128, 4, 40
+    experts, hidden, inter, top_k = 8, 512, 128, 4
     dt = fb.BF16
     pk, sc, bi = quant_weights(rng, inter, hidden, 4, 64, fb.BF16, experts)
     x, xh = up(rng.standard_normal((rows, hidden)), dt)
