@@ -169,6 +169,8 @@ class Op:
     @staticmethod
     def TopK(k: int, normalize: bool, chunk_width: int = 2048): return Op(OP_TOP_K, u0=k, u1=int(normalize))
     @staticmethod
+    def Sample(position: int): return Op(OP_SAMPLE, u0=position)  # inputs [logits, params(5 x u32)] or, masked, [logits, params, allow]
+    @staticmethod
     def Rope(theta: float): return Op(OP_ROPE, f0=theta)
     @staticmethod
     def Embed(): return Op(OP_EMBED)

@@ -447,6 +447,25 @@ int32_t exec_argmax(Exec& x, const fj_dispatch& d) {
   return FJ_OK;
 }
 
+// Op::Sample (2 inputs) and Op::SampleMasked (3 inputs), crates/forja-core/src/ops.rs:1546-1592.
+int32_t exec_sample(Exec& x, const fj_dispatch& d, fj::ErrorRecord* err) {
+  if ((d.n_inputs != 2 && d.n_inputs != 3) || d.n_outputs != 1 || d.inputs[0].rank == 0 || !is_float(d.inputs[0].dtype) || d.outputs[0].dtype != FJ_U32) return FJ_INVALID_INPUT;
+  if (d.inputs[1].dtype != FJ_U32 || d.inputs[1].rank != 1 || d.inputs[1].shape[0] != 5) return FJ_INVALID_INPUT;
+  const unsigned width = d.inputs[0].shape[d.inputs[0].rank - 1];
+  if (width == 0) return FJ_EXECUTION_FAILED;
+  const uint64_t rows = element_count(d.inputs[0]) / width;
+  if (element_count(d.outputs[0]) != rows || rows > 0x7FFFFFFFu) return FJ_INVALID_INPUT;
+  const bool masked = d.n_inputs == 3;
+  if (masked && (d.inputs[2].dtype != FJ_U32 || d.inputs[2].rank != 1 || d.inputs[2].shape[0] != (width + 31) / 32 || !is_contiguous(d.inputs[2]))) return FJ_INVALID_INPUT;
+  const void* in = x.input(d.inputs[0]);
+  const void* params = x.input(d.inputs[1]);
+  const void* allow = masked ? x.input(d.inputs[2]) : nullptr;
+  unsigned* out = static_cast<unsigned*>(x.output(d.outputs[0]));
+  if (!in || !params || !out || (masked && !allow)) return FJ_INVALID_INPUT;
+  fj::launch_sample(x.be->ctx, in, d.inputs[0].dtype, width, static_cast<const unsigned*>(params), static_cast<const unsigned*>(allow), out, static_cast<unsigned>(rows), width, d.u0, err);
+  return FJ_OK;
+}
+
 int32_t exec_top_k(Exec& x, const fj_dispatch& d) {
   if (d.n_inputs != 1 || d.n_outputs != 2 || d.inputs[0].rank == 0 || !is_float(d.inputs[0].dtype) || d.outputs[1].dtype != FJ_U32) return FJ_INVALID_INPUT;
   const unsigned width = d.inputs[0].shape[d.inputs[0].rank - 1], k = d.u0;
@@ -1112,6 +1131,7 @@ int32_t fj_submit(fj_backend* be, const fj_dispatch* dispatches, uint32_t count,
       case FJ_OP_RMS_NORM: status = exec_rms_norm(x, d); break;
       case FJ_OP_ARGMAX: status = exec_argmax(x, d); break;
       case FJ_OP_TOP_K: status = exec_top_k(x, d); break;
+      case FJ_OP_SAMPLE: status = exec_sample(x, d, err); break;
       case FJ_OP_ROPE: status = exec_rope(x, d); break;
       case FJ_OP_EMBED: status = exec_embed(x, d, err); break;
       case FJ_OP_QUANT_EMBED: status = exec_quant_embed(x, d, err); break;
@@ -1195,7 +1215,7 @@ int32_t fj_sub_wait(fj_submission* sub, uint64_t timeout_ns) {
       sub->error.op = sub->ops[i];
       sub->error.flag = sub->host_err[i].flag;
       sub->error.value = sub->host_err[i].value;
-      sub->result = sub->host_err[i].flag == fj::ERR_INDEX ? FJ_INDEX_OUT_OF_RANGE : FJ_DEVICE_ERROR_FLAG;
+      sub->result = sub->host_err[i].flag == fj::ERR_INDEX ? FJ_INDEX_OUT_OF_RANGE : sub->host_err[i].flag == fj::ERR_INVALID ? FJ_INVALID_INPUT : FJ_DEVICE_ERROR_FLAG;
       break;
     }
   }

@@ -20,7 +20,7 @@ struct ErrorRecord {
   unsigned int flag;   // 0 ok, 1 index out of range, 2 page entry refused, 3 wait gave up
   unsigned int value;  // lowest offending value (initialised to 0xFFFFFFFF)
 };
-enum : unsigned int { ERR_INDEX = 1, ERR_PAGE = 2, ERR_WAIT = 3 };
+enum : unsigned int { ERR_INDEX = 1, ERR_PAGE = 2, ERR_WAIT = 3, ERR_INVALID = 4 };  // ERR_INVALID: a device-resident parameter failed validation
 
 // Programmatic dependent launch: a kernel started with the stream-serialisation attribute may begin
 // while its predecessor in the stream is still draining. `griddepcontrol.wait` blocks until that

@@ -493,7 +493,7 @@ __global__ void routes_combine_kernel(const float* __restrict__ per_route, const
                                       unsigned width) {
   pdl_sync();
   for (unsigned row = blockIdx.x; row < rows; row += gridDim.x) {
-    for (unsigned c = threadIdx.x; c < width; c += blockDim.x) {
+    for (unsigned c = blockIdx.y * blockDim.x + threadIdx.x; c < width; c += gridDim.y * blockDim.x) {
       float total = 0.0f;
       for (unsigned j = 0; j < top_k; ++j) {
         const unsigned slot = route_slot ? route_slot[row * top_k + j] : (expert_ids[row * top_k + j] < experts ? row * top_k + j : 0xFFFFFFFFu);
@@ -511,7 +511,9 @@ __global__ void routes_combine_kernel(const float* __restrict__ per_route, const
 void launch_routes_combine(Ctx& ctx, const float* per_route, const unsigned* route_slot, const unsigned* expert_ids, unsigned experts, const void* weights, int w_dt, const void* extra,
                            int e_dt, void* out, int out_dt, unsigned rows, unsigned top_k, unsigned width) {
   if (rows == 0) return;
-  launch_pdl(routes_combine_kernel, dim3(rows < 1024u ? rows : 1024u), dim3(256), 0, ctx.stream, per_route, route_slot, expert_ids, experts, weights, w_dt, extra, e_dt, out, out_dt, rows,
+  // few rows: spread the columns of a row over several CTAs so that the grid still fills the GPU
+  const unsigned col_ctas = rows >= 1024u ? 1u : std::min((width + 255u) / 256u, (1024u + rows - 1) / rows);
+  launch_pdl(routes_combine_kernel, dim3(rows < 1024u ? rows : 1024u, col_ctas), dim3(256), 0, ctx.stream, per_route, route_slot, expert_ids, experts, weights, w_dt, extra, e_dt, out, out_dt, rows,
              top_k, width);
   ctx.launches++;
 }

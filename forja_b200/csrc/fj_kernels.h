@@ -59,6 +59,10 @@ void launch_quant_embed(Ctx& ctx, const unsigned* packed, const void* scales, co
 size_t argmax_scratch_bytes(unsigned rows, unsigned width);
 void launch_argmax(Ctx& ctx, const void* x, int x_dt, size_t row_stride, unsigned* out, unsigned rows, unsigned width,
                    void* scratch);
+// Op::Sample / SampleMasked: params = 5 device words (temperature, top_k, top_p, seed lo, seed hi), allow = bit mask or nullptr.
+// Invalid parameters or mask: ERR_INVALID in err (value = row) and token 0.
+void launch_sample(Ctx& ctx, const void* x, int x_dt, size_t row_stride, const unsigned* params, const unsigned* allow, unsigned* out, unsigned rows, unsigned width,
+                   unsigned position, ErrorRecord* err);
 // top-k: descending total order, ties -> lower index; optional softmax over the selected set.
 void launch_top_k(Ctx& ctx, const void* x, int x_dt, void* values, int v_dt, unsigned* indices, unsigned rows,
                   unsigned width, unsigned k, bool normalize);

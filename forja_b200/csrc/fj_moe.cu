@@ -176,6 +176,39 @@ __global__ void ep_plan_kernel(const unsigned* __restrict__ indices, unsigned ro
   }
 }
 
+// Router logits for many rows on the tensor cores without giving up f32 weights: every dequantised
+// router weight w = s * q + b (f32, rounded like the reference, crates/forja-cpu/src/lib.rs:878-962)
+// is split into hi = bf16(w) and lo = bf16(w - hi), stacked as 2 * experts rows; x . hi and x . lo
+// come out of one dense GEMM with f32 accumulators and are added afterwards (|w - hi - lo| <= 2^-17 |w|).
+__global__ void router_split_kernel(const unsigned* __restrict__ packed, const unsigned short* __restrict__ scales, const unsigned short* __restrict__ biases, unsigned experts,
+                                    unsigned k, unsigned bits, unsigned group_size, unsigned short* __restrict__ out /*[2 * experts][k]*/) {
+  fj::pdl_sync();
+  const unsigned vpw = 32 / bits, mask = (1u << bits) - 1, words_per_row = k / vpw, groups = k / group_size;
+  const size_t total = static_cast<size_t>(experts) * words_per_row;
+  for (size_t idx = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; idx < total; idx += static_cast<size_t>(gridDim.x) * blockDim.x) {
+    const unsigned row = static_cast<unsigned>(idx / words_per_row), wi = static_cast<unsigned>(idx % words_per_row);
+    const unsigned word = packed[idx];
+    const size_t g = static_cast<size_t>(row) * groups + (wi * vpw) / group_size;
+    const float s = __uint_as_float(static_cast<unsigned>(scales[g]) << 16), b = __uint_as_float(static_cast<unsigned>(biases[g]) << 16);
+    for (unsigned i = 0; i < vpw; ++i) {
+      const float w = __fadd_rn(__fmul_rn(s, static_cast<float>((word >> (i * bits)) & mask)), b);
+      const __nv_bfloat16 hi = __float2bfloat16_rn(w);
+      const __nv_bfloat16 lo = __float2bfloat16_rn(w - __bfloat162float(hi));
+      out[static_cast<size_t>(row) * k + wi * vpw + i] = __bfloat16_as_ushort(hi);
+      out[static_cast<size_t>(experts + row) * k + wi * vpw + i] = __bfloat16_as_ushort(lo);
+    }
+  }
+}
+
+__global__ void router_sum_kernel(const float* __restrict__ halves /*[rows][2 * experts]*/, float* __restrict__ logits, unsigned rows, unsigned experts) {
+  fj::pdl_sync();
+  const size_t total = static_cast<size_t>(rows) * experts;
+  for (size_t idx = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; idx < total; idx += static_cast<size_t>(gridDim.x) * blockDim.x) {
+    const size_t row = idx / experts, e = idx % experts;
+    logits[idx] = halves[row * 2 * experts + e] + halves[row * 2 * experts + experts + e];
+  }
+}
+
 // Copies each route's activation row (bf16, width % 8 == 0) into its slot, 16 bytes per thread step.
 __global__ void ep_scatter_rows_kernel(const unsigned short* __restrict__ normed, const unsigned* __restrict__ route_slot, unsigned routes, unsigned top_k,
                                        unsigned width, unsigned short* send_rows) {
@@ -218,6 +251,8 @@ struct fj_moe_model {
   // workspace (bf16 unless noted)
   void *hidden = nullptr, *hidden2 = nullptr, *normed = nullptr, *qkv = nullptr, *q = nullptr, *attn = nullptr, *proj = nullptr, *act = nullptr;
   float *router_logits = nullptr, *route_weights = nullptr;
+  float* router_halves = nullptr;          // [max_rows][2 * experts] f32: x . hi | x . lo
+  unsigned short* router_split = nullptr;  // [2 * experts][hidden] bf16, rebuilt per layer
   unsigned* route_experts = nullptr;
   void *last_hidden = nullptr, *last_normed = nullptr, *logits = nullptr, *argmax_scratch = nullptr, *dequant = nullptr;
   size_t dequant_bytes = 0;
@@ -329,6 +364,10 @@ int32_t fj_moe_model_create(fj_backend* be, const fj_moe_config* config, const f
   m->proj = dev_alloc(R * H * 2);
   m->act = dev_alloc(R * K * I * 2);
   m->router_logits = static_cast<float*>(dev_alloc(R * c.experts * 4));
+  if (R > 16) {
+    m->router_halves = static_cast<float*>(dev_alloc(R * 2 * c.experts * 4));
+    m->router_split = static_cast<unsigned short*>(dev_alloc(2 * static_cast<size_t>(c.experts) * H * 2));
+  }
   m->route_weights = static_cast<float*>(dev_alloc(R * K * 4));
   m->route_experts = static_cast<unsigned*>(dev_alloc(R * K * 4));
   m->last_hidden = dev_alloc(Lanes * H * 2);
@@ -516,7 +555,20 @@ extern "C" int32_t fj_moe_step(fj_moe_model* m, const uint32_t* token_ids, uint3
       fj::launch_residual_norm(ctx, dense_view(hidden, dt, rows, H, H), dense_view(m->proj, dt, rows, H, H), weight_view(L.post_norm, dt, rows, H), dense_view(other, dt, rows, H, H),
                                dense_view(m->normed, dt, rows, H, H), rows, H, c.eps, 0);
       std::swap(hidden, other);  // `hidden` is now the post-attention residual stream
-      q4(m->normed, L.router, m->router_logits, FJ_F32, rows, H, c.experts, c.router_bits);
+      if (rows > 16 && m->router_split != nullptr) {
+        const size_t words = static_cast<size_t>(c.experts) * (H * c.router_bits / 32);
+        fj::launch_pdl(router_split_kernel, dim3(static_cast<unsigned>(std::min<size_t>((words + 255) / 256, 4096))), dim3(256), 0, be->stream, L.router.packed,
+                       static_cast<const unsigned short*>(L.router.scales), static_cast<const unsigned short*>(L.router.biases), c.experts, H, c.router_bits, G,
+                       m->router_split);
+        ctx.launches++;
+        fj::launch_gemm_nt(ctx, m->normed, dt, H, m->router_split, dt, H, m->router_halves, FJ_F32, 2 * c.experts, rows, 2 * c.experts, H, be->gemm_scratch,
+                           be->gemm_scratch_bytes);
+        fj::launch_pdl(router_sum_kernel, dim3(static_cast<unsigned>(std::min<size_t>((static_cast<size_t>(rows) * c.experts + 255) / 256, 2048))), dim3(256), 0, be->stream,
+                       static_cast<const float*>(m->router_halves), m->router_logits, rows, c.experts);
+        ctx.launches++;
+      } else {
+        q4(m->normed, L.router, m->router_logits, FJ_F32, rows, H, c.experts, c.router_bits);
+      }
       fj::launch_top_k(ctx, m->router_logits, FJ_F32, m->route_weights, FJ_F32, m->route_experts, rows, c.experts, K, true);
       if (m->captured_experts) {
         const size_t at = static_cast<size_t>(l) * c.max_rows * K;

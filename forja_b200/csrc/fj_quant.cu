@@ -643,11 +643,24 @@ __global__ void dequant_rows_kernel(const unsigned* __restrict__ packed, const v
   pdl_sync();
   const unsigned vpw = 32 / bits, mask = (1u << bits) - 1, words_per_row = k / vpw, groups = k / group_size;
   const size_t total = static_cast<size_t>(cols) * words_per_row;
+  // 4-bit weights into a 16-bit slab: one packed word becomes one 16-byte store
+  const bool wide = bits == 4 && (out_dt == BF16 || out_dt == F16) && reinterpret_cast<size_t>(out) % 16 == 0;
   for (size_t idx = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; idx < total; idx += static_cast<size_t>(gridDim.x) * blockDim.x) {
     const unsigned row = static_cast<unsigned>(idx / words_per_row), wi = static_cast<unsigned>(idx % words_per_row);
-    const unsigned word = packed[idx];
+    const unsigned word = __ldg(packed + idx);
     const size_t g = static_cast<size_t>(row0 + row) * groups + (wi * vpw) / group_size;
     const float s = load_as_f32(scales, p_dt, g), b = load_as_f32(biases, p_dt, g);
+    if (wide) {
+      unsigned o[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float lo = __fadd_rn(__fmul_rn(s, static_cast<float>((word >> (8 * i)) & 15u)), b), hi = __fadd_rn(__fmul_rn(s, static_cast<float>((word >> (8 * i + 4)) & 15u)), b);
+        o[i] = out_dt == BF16 ? (static_cast<unsigned>(__bfloat16_as_ushort(__float2bfloat16_rn(lo))) | (static_cast<unsigned>(__bfloat16_as_ushort(__float2bfloat16_rn(hi))) << 16))
+                              : (static_cast<unsigned>(__half_as_ushort(__float2half_rn(lo))) | (static_cast<unsigned>(__half_as_ushort(__float2half_rn(hi))) << 16));
+      }
+      *reinterpret_cast<uint4*>(static_cast<unsigned short*>(out) + idx * 8) = make_uint4(o[0], o[1], o[2], o[3]);
+      continue;
+    }
     for (unsigned i = 0; i < vpw; ++i)
       store_from_f32(out, out_dt, static_cast<size_t>(row) * k + wi * vpw + i, __fadd_rn(__fmul_rn(s, static_cast<float>((word >> (i * bits)) & mask)), b));
   }

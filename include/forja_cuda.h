@@ -58,7 +58,8 @@ typedef enum fj_op {
   FJ_OP_PAGED_SDPA = 13,        /* f0 = scale, u0 = causal, u1 = q_start, u2 = key_length, u3 = page_tokens */
   FJ_OP_PAGED_SDPA_APPEND = 14, /* f0 = scale, u1 = q_start, u3 = page_tokens */
   FJ_OP_SDPA = 15,              /* f0 = scale, u0 = causal, u1 = q_start (contiguous cache) */
-  FJ_OP_SAMPLE = 16             /* u0 = position; inputs [logits, params(5 x u32), (allow mask)] */
+  FJ_OP_SAMPLE = 16             /* Op::Sample / Op::SampleMasked (crates/forja-core/src/ops.rs:202-239): u0 = position; inputs [logits, params(5 x u32),
+                                   (allow mask, (width + 31) / 32 x u32)]; invalid parameter words or mask fail the submission with FJ_INVALID_INPUT */
 } fj_op;
 
 /* ---- plain data ---------------------------------------------------------------------------- */
