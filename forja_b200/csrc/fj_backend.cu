@@ -629,11 +629,12 @@ int32_t exec_gather_quant(Exec& x, const fj_dispatch& d, fj::ErrorRecord* err) {
       void* plan = x.temp(fj::route_plan_bytes(static_cast<unsigned>(total), experts));
       float* per_route = static_cast<float*>(x.temp(total * n * sizeof(float)));
       if (!plan || !per_route) return FJ_ALLOCATION_FAILED;
-      fj::launch_route_plan(x.be->ctx, static_cast<const unsigned*>(ip), static_cast<unsigned>(total), experts, plan, err, stream ? 16 : 64);
+      const unsigned tile_rows = stream ? 16 : fj::grouped_tile_rows(static_cast<unsigned>(total), experts);
+      fj::launch_route_plan(x.be->ctx, static_cast<const unsigned*>(ip), static_cast<unsigned>(total), experts, plan, err, tile_rows);
       if (stream) {
         if (!fj::launch_expert_stream_single(x.be->ctx, ap, static_cast<const unsigned*>(pp), sp, bp, plan, static_cast<unsigned>(total), experts, 1, per_route, false, k, n))
           return FJ_DEVICE_EXECUTION_FAILED;
-      } else fj::launch_grouped_q4_single(x.be->ctx, ap, static_cast<const unsigned*>(pp), sp, bp, plan, static_cast<unsigned>(total), experts, 1, per_route, false, k, n);
+      } else fj::launch_grouped_q4_single(x.be->ctx, ap, static_cast<const unsigned*>(pp), sp, bp, plan, static_cast<unsigned>(total), experts, 1, per_route, false, k, n, tile_rows);
       fj::launch_routes_combine(x.be->ctx, per_route, nullptr, static_cast<const unsigned*>(ip), experts, wp, wt.dtype, ex, epilogue == 2 ? d.inputs[6].dtype : 0, out,
                                 d.outputs[0].dtype, rows, routes, n);
       return FJ_OK;
@@ -664,7 +665,8 @@ int32_t exec_gather_quant(Exec& x, const fj_dispatch& d, fj::ErrorRecord* err) {
     void* plan = x.temp(fj::route_plan_bytes(static_cast<unsigned>(total), experts));
     if (!plan) return FJ_ALLOCATION_FAILED;
     cudaMemsetAsync(out, 0, total * n * 2, x.be->stream);
-    fj::launch_route_plan(x.be->ctx, static_cast<const unsigned*>(ip), static_cast<unsigned>(total), experts, plan, err, stream ? 16 : 64);
+    const unsigned tile_rows = stream ? 16 : fj::grouped_tile_rows(static_cast<unsigned>(total), experts);
+    fj::launch_route_plan(x.be->ctx, static_cast<const unsigned*>(ip), static_cast<unsigned>(total), experts, plan, err, tile_rows);
     if (stream) {
       const bool ok = paired ? fj::launch_expert_stream_pair(x.be->ctx, xp, static_cast<const unsigned*>(pp), sp, bp, static_cast<const unsigned*>(pp2), sp2, bp2, plan,
                                                              static_cast<unsigned>(total), experts, routes, out, k, n)
@@ -672,9 +674,9 @@ int32_t exec_gather_quant(Exec& x, const fj_dispatch& d, fj::ErrorRecord* err) {
       if (!ok) return FJ_DEVICE_EXECUTION_FAILED;
     } else if (paired)
       fj::launch_grouped_q4_pair(x.be->ctx, xp, static_cast<const unsigned*>(pp), sp, bp, static_cast<const unsigned*>(pp2), sp2, bp2, plan, static_cast<unsigned>(total), experts, routes,
-                                 out, k, n);
+                                 out, k, n, tile_rows);
     else
-      fj::launch_grouped_q4_single(x.be->ctx, xp, static_cast<const unsigned*>(pp), sp, bp, plan, static_cast<unsigned>(total), experts, routes, out, true, k, n);
+      fj::launch_grouped_q4_single(x.be->ctx, xp, static_cast<const unsigned*>(pp), sp, bp, plan, static_cast<unsigned>(total), experts, routes, out, true, k, n, tile_rows);
     return FJ_OK;
   }
   fj::launch_gather_quant_matmul(x.be->ctx, xp, xt.dtype, static_cast<const unsigned*>(pp), sp, bp, d.inputs[2].dtype, static_cast<const unsigned*>(pp2), sp2, bp2,

@@ -23,7 +23,7 @@ namespace fj {
 
 namespace {
 
-constexpr int GT_BM = 64, GT_BN = 64, GT_BK = 64, GT_THREADS = 128;
+constexpr int GT_BN = 64, GT_BK = 64;  // columns and k per tile step; rows per tile: 64 or 128 (template parameter)
 
 struct RouteTile {
   unsigned expert, first, count;
@@ -92,26 +92,36 @@ struct GroupedArgs {
   int out_bf16;
 };
 
-template <bool kPair>
-__global__ void __launch_bounds__(GT_THREADS) grouped_q4_gemm_kernel(GroupedArgs p) {
-  constexpr int NW = kPair ? 2 : 1;
-  __shared__ __align__(128) unsigned char s_a[2][GT_BM * 128];
-  __shared__ __align__(128) unsigned char s_b[NW][GT_BN * 128];
-  __shared__ __align__(16) unsigned char s_q[2][NW][GT_BN * 32];
-  __shared__ unsigned short s_scale[2][NW][GT_BN], s_bias[2][NW][GT_BN];
-  __shared__ unsigned s_route[GT_BM];
+// Shared memory of one CTA: A stages, the expanded B tile(s), nibble stages, scales and biases, route ids.
+template <bool kPair, int BM>
+constexpr size_t grouped_smem_bytes() {
+  return 2 * BM * 128 + (kPair ? 2 : 1) * (GT_BN * 128 + 2 * GT_BN * 32 + 2 * GT_BN * 2 * 2) + BM * 4;
+}
+
+// BM rows of one expert x 64 columns per CTA, BM / 32 x 2 warps of 32 x 32.
+template <bool kPair, int BM>
+__global__ void __launch_bounds__(BM * 2) grouped_q4_gemm_kernel(GroupedArgs p) {
+  constexpr int NW = kPair ? 2 : 1, THREADS = BM * 2, PARTS = THREADS / GT_BN, WORDS = 8 / PARTS;  // a thread expands WORDS packed words of one column per matrix
+  extern __shared__ __align__(128) unsigned char g_smem[];
+  unsigned char* s_a = g_smem;                                   // [2][BM * 128]
+  unsigned char* s_b = s_a + 2 * BM * 128;                        // [NW][GT_BN * 128]
+  unsigned char* s_q = s_b + NW * GT_BN * 128;                    // [2][NW][GT_BN * 32]
+  unsigned short* s_scale = reinterpret_cast<unsigned short*>(s_q + 2 * NW * GT_BN * 32);  // [2][NW][GT_BN]
+  unsigned short* s_bias = s_scale + 2 * NW * GT_BN;              // [2][NW][GT_BN]
+  unsigned* s_route = reinterpret_cast<unsigned*>(s_bias + 2 * NW * GT_BN);  // [BM]
   pdl_sync();
   if (blockIdx.y >= *p.n_tiles) return;
   const RouteTile tile = p.tiles[blockIdx.y];
   const unsigned col0 = blockIdx.x * GT_BN;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int warp_m = warp >> 1, warp_n = warp & 1;  // 2 x 2 warps of 32 x 32
+  const int warp_m = warp >> 1, warp_n = warp & 1;
+  const bool rows_live = static_cast<unsigned>(warp_m) * 32 < tile.count;  // a warp whose 32 rows are all padding only helps with the copies
   const unsigned k_iters = p.k / GT_BK, words_per_row = p.k / 8, groups_per_row = p.k / 64;
-  for (unsigned i = threadIdx.x; i < GT_BM; i += GT_THREADS) s_route[i] = i < tile.count ? p.sorted[tile.first + i] : 0xFFFFFFFFu;
+  for (unsigned i = threadIdx.x; i < BM; i += THREADS) s_route[i] = i < tile.count ? p.sorted[tile.first + i] : 0xFFFFFFFFu;
   __syncthreads();
-  const unsigned a_base = static_cast<unsigned>(__cvta_generic_to_shared(&s_a[0][0]));
-  const unsigned b_base = static_cast<unsigned>(__cvta_generic_to_shared(&s_b[0][0]));
-  const unsigned q_base = static_cast<unsigned>(__cvta_generic_to_shared(&s_q[0][0][0]));
+  const unsigned a_base = static_cast<unsigned>(__cvta_generic_to_shared(s_a));
+  const unsigned b_base = static_cast<unsigned>(__cvta_generic_to_shared(s_b));
+  const unsigned q_base = static_cast<unsigned>(__cvta_generic_to_shared(s_q));
   const size_t expert_rows = static_cast<size_t>(tile.expert) * p.n;
 
   float acc[NW][2][4][4];
@@ -122,27 +132,36 @@ __global__ void __launch_bounds__(GT_THREADS) grouped_q4_gemm_kernel(GroupedArgs
 #pragma unroll
       for (int j = 0; j < 4; ++j) acc[w][i][j][0] = acc[w][i][j][1] = acc[w][i][j][2] = acc[w][i][j][3] = 0.0f;
 
+  // source row of this thread's A chunks (4 chunks of 16 bytes per thread and stage: rows r, r + THREADS / 8, ...)
+  const unsigned a_c8 = threadIdx.x & 7;
+  const unsigned short* a_src[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const unsigned route = s_route[(threadIdx.x >> 3) + i * (THREADS / 8)];
+    a_src[i] = route != 0xFFFFFFFFu ? p.x + static_cast<size_t>(route / p.src_div) * p.k + a_c8 * 8 : nullptr;
+  }
+
   auto issue = [&](unsigned it) {
     if (it < k_iters) {
       const unsigned stage = it & 1, kk = it * GT_BK;
-      // A: 64 rows x 8 chunks of 16 bytes, gathered through the route list
+      // A: BM rows x 8 chunks of 16 bytes, gathered through the route list
 #pragma unroll
-      for (int i = 0; i < (GT_BM * 8) / GT_THREADS; ++i) {
-        const unsigned chunk = threadIdx.x + i * GT_THREADS, r = chunk >> 3, c8 = chunk & 7;
-        const unsigned route = s_route[r];
-        const bool ok = route != 0xFFFFFFFFu;
-        const void* src = ok ? static_cast<const void*>(p.x + static_cast<size_t>(route / p.src_div) * p.k + kk + c8 * 8) : static_cast<const void*>(p.x);
-        g_cp_async_16(a_base + stage * (GT_BM * 128) + r * 128 + ((c8 ^ (r & 7)) << 4), src, ok ? 16u : 0u);
+      for (int i = 0; i < 4; ++i) {
+        const unsigned r = (threadIdx.x >> 3) + i * (THREADS / 8);
+        const bool ok = a_src[i] != nullptr;
+        g_cp_async_16(a_base + stage * (BM * 128) + r * 128 + ((a_c8 ^ (r & 7)) << 4), ok ? static_cast<const void*>(a_src[i] + kk) : static_cast<const void*>(p.x), ok ? 16u : 0u);
       }
       // packed weights: 64 columns x 2 chunks of 16 bytes per matrix; scales / biases: one u16 each
+      if (threadIdx.x < 128) {
 #pragma unroll
-      for (int w = 0; w < NW; ++w) {
-        const unsigned c = threadIdx.x >> 1, half = threadIdx.x & 1;
-        const bool ok = col0 + c < p.n;
-        const size_t row = expert_rows + (ok ? col0 + c : 0);
-        g_cp_async_16(q_base + ((stage * NW + w) * GT_BN + c) * 32 + half * 16, p.packed[w] + row * words_per_row + (kk / 8) + half * 4, ok ? 16u : 0u);
-        if (half == 0) s_scale[stage][w][c] = ok ? p.scales[w][row * groups_per_row + it] : static_cast<unsigned short>(0);
-        else s_bias[stage][w][c] = ok ? p.biases[w][row * groups_per_row + it] : static_cast<unsigned short>(0);
+        for (int w = 0; w < NW; ++w) {
+          const unsigned c = threadIdx.x >> 1, half = threadIdx.x & 1;
+          const bool ok = col0 + c < p.n;
+          const size_t row = expert_rows + (ok ? col0 + c : 0);
+          g_cp_async_16(q_base + ((stage * NW + w) * GT_BN + c) * 32 + half * 16, p.packed[w] + row * words_per_row + (kk / 8) + half * 4, ok ? 16u : 0u);
+          if (half == 0) s_scale[(stage * NW + w) * GT_BN + c] = ok ? p.scales[w][row * groups_per_row + it] : static_cast<unsigned short>(0);
+          else s_bias[(stage * NW + w) * GT_BN + c] = ok ? p.biases[w][row * groups_per_row + it] : static_cast<unsigned short>(0);
+        }
       }
     }
     asm volatile("cp.async.commit_group;\n" ::: "memory");
@@ -154,28 +173,35 @@ __global__ void __launch_bounds__(GT_THREADS) grouped_q4_gemm_kernel(GroupedArgs
     __syncthreads();  // stage `it` landed; everyone finished the previous step's mma (s_b and the other stage are free)
     issue(it + 1);
     const unsigned stage = it & 1;
-    // expand this step's nibbles: thread -> (column, half of the 64-k step) = 32 weights per matrix
+    // expand this step's nibbles: thread -> (column, part of the 64-k step). Nibbles j and j + 4 of a word are OR-ed
+    // into the mantissa of bf16 128.0, 128 is subtracted (exact), one bf16x2 fma gives bf16(s * q + b) with a
+    // single rounding, and two byte permutes put the eight results back in k order.
 #pragma unroll
     for (int w = 0; w < NW; ++w) {
-      const unsigned c = threadIdx.x >> 1, half = threadIdx.x & 1;
-      const uint4 q = *reinterpret_cast<const uint4*>(&s_q[stage][w][c * 32 + half * 16]);
-      const float s = __uint_as_float(static_cast<unsigned>(s_scale[stage][w][c]) << 16), b = __uint_as_float(static_cast<unsigned>(s_bias[stage][w][c]) << 16);
-      const unsigned words[4] = {q.x, q.y, q.z, q.w};
+      const unsigned c = threadIdx.x / PARTS, part = threadIdx.x % PARTS;
+      const unsigned sc = s_scale[(stage * NW + w) * GT_BN + c], bi = s_bias[(stage * NW + w) * GT_BN + c];
+      const unsigned s2 = sc | (sc << 16), b2 = bi | (bi << 16);
+      const __nv_bfloat162 scale2 = *reinterpret_cast<const __nv_bfloat162*>(&s2), bias2 = *reinterpret_cast<const __nv_bfloat162*>(&b2);
+      const unsigned offset_bits = 0x43004300u;
+      const __nv_bfloat162 offset2 = *reinterpret_cast<const __nv_bfloat162*>(&offset_bits);
+      const unsigned* q = reinterpret_cast<const unsigned*>(s_q + ((stage * NW + w) * GT_BN + c) * 32 + part * (WORDS * 4));
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        float v[8];
+      for (int i = 0; i < WORDS; ++i) {
+        const unsigned word = q[i];
+        unsigned r[4];
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          // exact int -> float through the 2^23 mantissa trick, then w = s * q + b, product rounded first
-          const float qf = __uint_as_float(0x4B000000u | ((words[i] >> (4 * j)) & 0xFu)) - 8388608.0f;
-          v[j] = __fadd_rn(__fmul_rn(s, qf), b);
+        for (int j = 0; j < 4; ++j) {
+          const unsigned pair_bits = ((word >> (4 * j)) & 0x000F000Fu) | 0x43004300u;  // {128 + nibble j, 128 + nibble j + 4}
+          const __nv_bfloat162 value = __hfma2(__hsub2(*reinterpret_cast<const __nv_bfloat162*>(&pair_bits), offset2), scale2, bias2);
+          r[j] = *reinterpret_cast<const unsigned*>(&value);
         }
-        const uint4 packed = make_uint4(pack_bf16(v[0], v[1]), pack_bf16(v[2], v[3]), pack_bf16(v[4], v[5]), pack_bf16(v[6], v[7]));
-        const unsigned chunk = half * 4 + i;
-        *reinterpret_cast<uint4*>(&s_b[w][c * 128 + ((chunk ^ (c & 7)) << 4)]) = packed;
+        const uint4 packed = make_uint4(__byte_perm(r[0], r[1], 0x5410), __byte_perm(r[2], r[3], 0x5410), __byte_perm(r[0], r[1], 0x7632), __byte_perm(r[2], r[3], 0x7632));
+        const unsigned chunk = part * WORDS + i;
+        *reinterpret_cast<uint4*>(s_b + w * (GT_BN * 128) + c * 128 + ((chunk ^ (c & 7)) << 4)) = packed;
       }
     }
     __syncthreads();
+    if (!rows_live) continue;
 #pragma unroll
     for (int ks = 0; ks < GT_BK / 16; ++ks) {
       unsigned af[2][4];
@@ -184,7 +210,7 @@ __global__ void __launch_bounds__(GT_THREADS) grouped_q4_gemm_kernel(GroupedArgs
         const unsigned mi = lane >> 3, rr = lane & 7;
         const unsigned r = warp_m * 32 + i * 16 + (mi & 1) * 8 + rr;
         const unsigned chunk = ks * 2 + (mi >> 1);
-        g_ldmatrix_x4(af[i][0], af[i][1], af[i][2], af[i][3], a_base + stage * (GT_BM * 128) + r * 128 + ((chunk ^ (r & 7)) << 4));
+        g_ldmatrix_x4(af[i][0], af[i][1], af[i][2], af[i][3], a_base + stage * (BM * 128) + r * 128 + ((chunk ^ (r & 7)) << 4));
       }
 #pragma unroll
       for (int w = 0; w < NW; ++w)
@@ -435,28 +461,50 @@ void launch_route_plan(Ctx& ctx, const unsigned* indices, unsigned total_routes,
   ctx.launches++;
 }
 
+// 128-row tiles once the average expert fills most of one (the nibble expansion is shared by twice the rows), else 64.
+unsigned grouped_tile_rows(unsigned total_routes, unsigned experts) { return total_routes >= 96ull * experts ? 128u : 64u; }
+
 bool grouped_q4_supported(unsigned k, unsigned n, unsigned bits, unsigned group_size, unsigned experts, const void* x, const void* packed) {
   return bits == 4 && group_size == 64 && k % 64 == 0 && n % 2 == 0 && experts <= 4096 && reinterpret_cast<size_t>(x) % 16 == 0 && reinterpret_cast<size_t>(packed) % 16 == 0;
 }
 
+namespace {
+template <bool kPair, int BM>
+void launch_grouped(Ctx& ctx, const GroupedArgs& a, unsigned tiles) {
+  constexpr size_t smem = grouped_smem_bytes<kPair, BM>();
+  static bool configured[64] = {};
+  int device = 0;
+  cudaGetDevice(&device);
+  if (device >= 0 && device < 64 && !configured[device]) {
+    cudaFuncSetAttribute(grouped_q4_gemm_kernel<kPair, BM>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    configured[device] = true;
+  }
+  launch_pdl(grouped_q4_gemm_kernel<kPair, BM>, dim3((a.n + GT_BN - 1) / GT_BN, tiles), dim3(BM * 2), smem, ctx.stream, a);
+  ctx.launches++;
+}
+// tile_rows must be the value the plan was made with (64 or 128); the grid covers the most tiles such a plan can hold
+template <bool kPair>
+void run_grouped(Ctx& ctx, const GroupedArgs& a, unsigned tile_rows, unsigned total_routes, unsigned experts) {
+  const unsigned tiles = total_routes / tile_rows + experts + 1;
+  if (tile_rows == 128) launch_grouped<kPair, 128>(ctx, a, tiles);
+  else launch_grouped<kPair, 64>(ctx, a, tiles);
+}
+}  // namespace
+
 void launch_grouped_q4_pair(Ctx& ctx, const void* x, const unsigned* gate, const void* gate_scales, const void* gate_biases, const unsigned* up, const void* up_scales,
-                            const void* up_biases, const void* plan, unsigned total_routes, unsigned experts, unsigned src_div, void* act_out, unsigned k, unsigned n) {
+                            const void* up_biases, const void* plan, unsigned total_routes, unsigned experts, unsigned src_div, void* act_out, unsigned k, unsigned n, unsigned tile_rows) {
   const PlanLayout l = plan_layout(const_cast<void*>(plan), total_routes, experts);
   GroupedArgs a{static_cast<const unsigned short*>(x), {gate, up}, {static_cast<const unsigned short*>(gate_scales), static_cast<const unsigned short*>(up_scales)},
                 {static_cast<const unsigned short*>(gate_biases), static_cast<const unsigned short*>(up_biases)}, l.sorted, l.tiles, l.n_tiles, act_out, k, n, src_div, 1};
-  dim3 grid((n + GT_BN - 1) / GT_BN, l.tiles_cap);
-  launch_pdl(grouped_q4_gemm_kernel<true>, grid, dim3(GT_THREADS), 0, ctx.stream, a);
-  ctx.launches++;
+  run_grouped<true>(ctx, a, tile_rows, total_routes, experts);
 }
 
 void launch_grouped_q4_single(Ctx& ctx, const void* x, const unsigned* packed, const void* scales, const void* biases, const void* plan, unsigned total_routes, unsigned experts,
-                              unsigned src_div, void* out, bool out_bf16, unsigned k, unsigned n) {
+                              unsigned src_div, void* out, bool out_bf16, unsigned k, unsigned n, unsigned tile_rows) {
   const PlanLayout l = plan_layout(const_cast<void*>(plan), total_routes, experts);
   GroupedArgs a{static_cast<const unsigned short*>(x), {packed, packed}, {static_cast<const unsigned short*>(scales), static_cast<const unsigned short*>(scales)},
                 {static_cast<const unsigned short*>(biases), static_cast<const unsigned short*>(biases)}, l.sorted, l.tiles, l.n_tiles, out, k, n, src_div, out_bf16 ? 1 : 0};
-  dim3 grid((n + GT_BN - 1) / GT_BN, l.tiles_cap);
-  launch_pdl(grouped_q4_gemm_kernel<false>, grid, dim3(GT_THREADS), 0, ctx.stream, a);
-  ctx.launches++;
+  run_grouped<false>(ctx, a, tile_rows, total_routes, experts);
 }
 
 bool expert_stream_supported(unsigned k, unsigned n, unsigned bits, unsigned group_size, unsigned experts, const void* x, const void* packed, const void* scales, const void* biases) {

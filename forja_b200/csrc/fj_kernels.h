@@ -163,12 +163,15 @@ void launch_gather_quant_weighted_sum(Ctx& ctx, const void* act, int a_dt, const
 size_t route_plan_bytes(unsigned total_routes, unsigned experts);
 void launch_route_plan(Ctx& ctx, const unsigned* indices, unsigned total_routes, unsigned experts, void* plan, ErrorRecord* err, unsigned tile_rows = 64);
 bool grouped_q4_supported(unsigned k, unsigned n, unsigned bits, unsigned group_size, unsigned experts, const void* x, const void* packed);
+// Rows per tile (64 or 128) the tile GEMMs should use for this many routes; pass it to launch_route_plan and to both launchers.
+unsigned grouped_tile_rows(unsigned total_routes, unsigned experts);
 // act_out[route, :] = silu(x_r . gate_e) * (x_r . up_e) in bf16, x_r = x[route / src_div]; bf16 x, bf16 scales/biases, group 64.
 void launch_grouped_q4_pair(Ctx& ctx, const void* x, const unsigned* gate, const void* gate_scales, const void* gate_biases, const unsigned* up, const void* up_scales,
-                            const void* up_biases, const void* plan, unsigned total_routes, unsigned experts, unsigned src_div, void* act_out, unsigned k, unsigned n);
+                            const void* up_biases, const void* plan, unsigned total_routes, unsigned experts, unsigned src_div, void* act_out, unsigned k, unsigned n,
+                            unsigned tile_rows = 64);
 // out[route, :] = x[route / src_div] . W_e, f32 or (out_bf16) bf16.
 void launch_grouped_q4_single(Ctx& ctx, const void* x, const unsigned* packed, const void* scales, const void* biases, const void* plan, unsigned total_routes, unsigned experts,
-                              unsigned src_div, void* out, bool out_bf16, unsigned k, unsigned n);
+                              unsigned src_div, void* out, bool out_bf16, unsigned k, unsigned n, unsigned tile_rows = 64);
 // Streaming form of the two launchers above for few rows per expert; the plan must have been made with tile_rows = 16.
 // live_routes (only a hint for the grid): how many of the routes are expected to carry a valid expert id.
 // false: the kernel could not be configured on this device and nothing was launched.

@@ -597,9 +597,11 @@ extern "C" int32_t fj_moe_step(fj_moe_model* m, const uint32_t* token_ids, uint3
         return true;
       }
       if (!fj::grouped_q4_supported(H, I, 4, G, n_experts, x, L.gate.packed) || !fj::grouped_q4_supported(I, H, 4, G, n_experts, act, L.down.packed)) return false;
-      fj::launch_route_plan(ctx, ids, n_routes, n_experts, m->route_plan, nullptr);
-      fj::launch_grouped_q4_pair(ctx, x, L.gate.packed, L.gate.scales, L.gate.biases, L.up.packed, L.up.scales, L.up.biases, m->route_plan, n_routes, n_experts, src_div, act, H, I);
-      fj::launch_grouped_q4_single(ctx, act, L.down.packed, L.down.scales, L.down.biases, m->route_plan, n_routes, n_experts, 1, down_out, false, I, H);
+      const unsigned tile_rows = fj::grouped_tile_rows(live, n_experts);
+      fj::launch_route_plan(ctx, ids, n_routes, n_experts, m->route_plan, nullptr, tile_rows);
+      fj::launch_grouped_q4_pair(ctx, x, L.gate.packed, L.gate.scales, L.gate.biases, L.up.packed, L.up.scales, L.up.biases, m->route_plan, n_routes, n_experts, src_div, act, H, I,
+                                 tile_rows);
+      fj::launch_grouped_q4_single(ctx, act, L.down.packed, L.down.scales, L.down.biases, m->route_plan, n_routes, n_experts, 1, down_out, false, I, H, tile_rows);
       return true;
     };
     if (m->world == 1) {
