@@ -16,6 +16,7 @@
 // tile a row lands in, never its value.
 #include "fj_kernels.h"
 #include "fj_q4_i8.cuh"
+#include "fj_grouped.cuh"
 
 #include <algorithm>
 
@@ -24,10 +25,6 @@ namespace fj {
 namespace {
 
 constexpr int GT_BN = 64, GT_BK = 64;  // columns and k per tile step; rows per tile: 64 or 128 (template parameter)
-
-struct RouteTile {
-  unsigned expert, first, count;
-};
 
 // One CTA: histogram of routes per expert, exclusive scan, arrange, tile list.
 __global__ void __launch_bounds__(1024) route_plan_kernel(const unsigned* __restrict__ indices, unsigned total, unsigned experts, unsigned* offsets /*[experts + 1]*/,
@@ -78,19 +75,6 @@ __device__ inline void g_mma(float (&d)[4], const unsigned (&a)[4], unsigned b0,
 __device__ inline unsigned pack_bf16(float lo, float hi) {
   return static_cast<unsigned>(__bfloat16_as_ushort(__float2bfloat16_rn(lo))) | (static_cast<unsigned>(__bfloat16_as_ushort(__float2bfloat16_rn(hi))) << 16);
 }
-
-struct GroupedArgs {
-  const unsigned short* x;          // A source rows, bf16 [*, k]
-  const unsigned* packed[2];        // [experts][n][k / 8]
-  const unsigned short* scales[2];  // [experts][n][k / 64] bf16
-  const unsigned short* biases[2];
-  const unsigned* sorted;           // route ids bucketed by expert
-  const RouteTile* tiles;
-  const unsigned* n_tiles;
-  void* out;                        // pair: bf16 [routes][n]; single: f32 (or bf16 when out_bf16) [routes][n]
-  unsigned k, n, src_div;           // A row of a route = route / src_div
-  int out_bf16;
-};
 
 // Shared memory of one CTA: A stages, the expanded B tile(s), nibble stages, scales and biases, route ids.
 template <bool kPair, int BM>
@@ -486,7 +470,8 @@ void launch_grouped(Ctx& ctx, const GroupedArgs& a, unsigned tiles) {
 template <bool kPair>
 void run_grouped(Ctx& ctx, const GroupedArgs& a, unsigned tile_rows, unsigned total_routes, unsigned experts) {
   const unsigned tiles = total_routes / tile_rows + experts + 1;
-  if (tile_rows == 128) launch_grouped<kPair, 128>(ctx, a, tiles);
+  if (tile_rows == 128 && grouped_tc5_supported(a)) launch_grouped_tc5(ctx, a, kPair, tiles);  // tcgen05 tiles with TMEM accumulators
+  else if (tile_rows == 128) launch_grouped<kPair, 128>(ctx, a, tiles);
   else launch_grouped<kPair, 64>(ctx, a, tiles);
 }
 }  // namespace
@@ -531,6 +516,8 @@ bool launch_expert_stream_single(Ctx& ctx, const void* x, const unsigned* packed
                      {static_cast<const unsigned short*>(biases), static_cast<const unsigned short*>(biases)}, l.sorted, l.tiles, l.n_tiles, out, k, n, src_div, 0, out_bf16 ? 1 : 0};
   return run_expert_stream<false>(ctx, a, l.tiles_cap, std::min(experts, live_routes) + live_routes / 16);
 }
+
+unsigned grouped_tcgen05_giveups() { return grouped_tc5_giveups(); }
 
 namespace {
 // out[row] = (extra[row] +) sum_j weights[row, j] * per_route[slot(row, j)], j ascending, f32, each product rounded

@@ -135,6 +135,7 @@ void launch_gemm_nt(Ctx& ctx, const void* a, int a_dt, size_t lda, const void* w
 bool gemm_nt_tcgen05_supported(int a_dt, int w_dt, unsigned m, unsigned n, unsigned k, size_t lda, size_t ldw, const void* a, const void* w);
 void launch_gemm_nt_tcgen05(Ctx& ctx, const void* a, int a_dt, size_t lda, const void* w, size_t ldw, void* c, int c_dt, size_t ldc, unsigned m, unsigned n, unsigned k);
 unsigned gemm_tcgen05_giveups();  // bounded waits that ran out since the library was loaded (0 in a healthy run)
+unsigned grouped_tcgen05_giveups();  // the same for the expert-bucketed tcgen05 tiles
 // Fully strided fallback (any layout, batch): one thread per output element.
 void launch_matmul_generic(Ctx& ctx, const View& a, const View& b, const View& c, unsigned batch, unsigned m, unsigned n,
                            unsigned k);

@@ -185,8 +185,9 @@ def test_gather_quant_weighted_sum_known_answer():
 
 # 1 and 7 rows x 8 routes: one pass per route. 8 to 47 rows (64 to 376 routes, fewer than 24 per expert): routes bucketed by
 # expert into 16-row tiles that stream each expert once (8-row and 16-row forms, experts with more than one tile).
-# 200 rows: 64-row tile GEMMs.
-@pytest.mark.parametrize("rows", [1, 7, 8, 16, 33, 47, 200])
+# 100 rows (50 routes per expert): 64-row tile GEMMs on mma.sync. 200 and 300 rows (100 / 150 per expert): 128-row tiles
+# on the tcgen05 tensor cores, with experts that need a second, ragged tile.
+@pytest.mark.parametrize("rows", [1, 7, 8, 16, 33, 47, 100, 200, 300])
 def test_moe_expert_projections_match_oracle(rows):
     """Qwen3-30B-A3B expert shapes at a reduced expert count: gate/up pair 2048 -> 768 with the
     gate*sigmoid(gate)*up epilogue, then the weighted down projection 768 -> 2048 plus residual
@@ -221,7 +222,7 @@ def test_moe_expert_projections_match_oracle(rows):
     assert_close(down(out), fjo.decode(want, dt), QUANT_TOL)
 
 
-@pytest.mark.parametrize("rows", [40, 80])  # 160 routes: streamed 16-row tiles; 320 routes: 64-row tile GEMMs
+@pytest.mark.parametrize("rows", [40, 80, 200])  # 160 routes: streamed 16-row tiles; 320: 64-row tile GEMMs; 800: 128-row tcgen05 tiles
 def test_bucketed_expert_path_zeroes_bad_routes_and_reports_the_lowest_id(rows):
     """Bucketed routes with two out-of-range expert ids: their rows are zero, every other row is computed,
     and the submission fails with the lowest offending id (crates/forja-cpu/src/lib.rs:1078-1088)."""
