@@ -4,16 +4,19 @@
 //
 // One CTA owns a route tile (up to 128 rows of one expert) x 64 output columns, for the gate and up
 // matrices together in pair mode. Per 64-k step (= one quantisation group):
-//  * cp.async brings the 128 gathered activation rows into shared memory in the 128-byte-swizzle
-//    K-major layout, and 64 columns x 32 bytes of nibbles per matrix plus their scales and biases
-//    into a small staging ring, three steps ahead of the tensor core;
-//  * all 256 threads expand the nibbles to bf16 (pairs of nibbles OR-ed into the mantissa of bf16
+//  * 256 producer threads copy, with cp.async and two steps ahead, the 128 gathered activation rows
+//    into shared memory in the 128-byte-swizzle K-major layout, and each its own 8 bytes of nibbles
+//    per matrix (column c = thread / 4, quarter of the step = thread % 4) into a private slot; the
+//    column's scale and bias travel in registers, fetched one step ahead;
+//  * each producer expands its nibbles to bf16 (pairs of nibbles OR-ed into the mantissa of bf16
 //    128.0, minus 128, one bf16x2 fma = bf16(s * q + b) with a single rounding) straight into the
-//    swizzled B tile of the step's stage;
-//  * one elected thread issues tcgen05.mma.cta_group::1.kind::f16 (M 128, N 64, K 16, four per
-//    matrix) into f32 accumulators in tensor memory (64 columns per matrix) and commits to the
-//    stage's mbarrier; the expansion of the next step overlaps the tensor core's work.
-// Epilogue: the eight warps read their TMEM lanes (warp % 4 selects the 32 rows, warp / 4 the 32
+//    swizzled B tile of the step's stage and arrives on the stage's "filled" mbarrier: no CTA-wide
+//    barrier in the loop, warps may run up to two steps apart;
+//  * the elected thread of a ninth warp waits for "filled", issues tcgen05.mma.cta_group::1.kind::f16
+//    (M 128, N 64, K 16, four per matrix) into f32 accumulators in tensor memory (64 columns per
+//    matrix) and commits to the step's "done" mbarrier; a producer starts step it once the MMAs
+//    of step it - 2 are done (4 A slots, 2 B slots), so the tensor core always has a step queued.
+// Epilogue: the eight producer warps read their TMEM lanes (warp % 4 selects the 32 rows, warp / 4 the 32
 // columns) with tcgen05.ld; pair mode stores silu(gate) * up as bf16, single mode f32 or bf16 rows,
 // scattered to out[route].
 // Every mbarrier wait is bounded; a wait that runs out is counted, the CTA skips its output, frees
@@ -24,7 +27,10 @@ namespace fj {
 
 namespace {
 
-constexpr int G5_BM = 128, G5_BN = 64, G5_BK = 64, G5_STAGES = 3, G5_THREADS = 256, G5_PARAM_SLOTS = 2;
+constexpr int G5_BM = 128, G5_BN = 64, G5_BK = 64, G5_PRODUCERS = 256, G5_THREADS = G5_PRODUCERS + 32;
+// Copies run two steps ahead of their use; a producer may start step it once the MMAs of step it - 2 are done, which frees
+// A slot (it + 2) % 4 and B slot it % 2. The nibble slots are private to a thread (3: two in flight, one being read).
+constexpr int G5_A_STAGES = 4, G5_B_STAGES = 2, G5_RAW_STAGES = 3, G5_AHEAD = 2;
 constexpr int G5_A_BYTES = G5_BM * 128, G5_B_BYTES = G5_BN * 128, G5_RAW_BYTES = G5_BN * 32;
 constexpr unsigned kG5SpinLimit = 1u << 24;
 
@@ -33,28 +39,26 @@ __device__ unsigned g_grouped_tc5_giveups = 0;
 template <bool kPair>
 struct G5Layout {
   static constexpr int NW = kPair ? 2 : 1;
-  static constexpr int STAGE = G5_A_BYTES + NW * G5_B_BYTES;              // A tile, then the expanded B tile(s); all 1024-byte aligned
-  static constexpr int RAW = G5_STAGES * STAGE;                           // [STAGES][NW][64 x 32 B] nibbles
-  // [SLOTS][NW][2][64] x 4 B: scales / biases of two consecutive groups. Two slots are enough: the copy for steps it + 4, it + 5
-  // is issued at the end of step it + 2, after every thread has expanded step it + 1.
-  static constexpr int PARAMS = RAW + G5_STAGES * NW * G5_RAW_BYTES;
-  static constexpr int ROUTES = PARAMS + G5_PARAM_SLOTS * NW * 2 * G5_BN * 4;  // [128] route ids
-  static constexpr int TOTAL = ROUTES + G5_BM * 4 + 1024;                 // + slack to align the base to 1024 bytes
+  static constexpr int B = G5_A_STAGES * G5_A_BYTES;                       // [A_STAGES] A tiles, then [B_STAGES][NW] expanded B tiles; all 1024-byte aligned
+  static constexpr int RAW = B + G5_B_STAGES * NW * G5_B_BYTES;            // [RAW_STAGES][NW][256 threads x 8 B] nibbles, private to the thread that copied them
+  static constexpr int ROUTES = RAW + G5_RAW_STAGES * NW * G5_RAW_BYTES;   // [128] route ids
+  static constexpr int TOTAL = ROUTES + G5_BM * 4 + 1024;                  // + slack to align the base to 1024 bytes
 };
 
 __device__ inline void g5_cp_async_16(unsigned smem_addr, const void* gmem, unsigned src_bytes) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(smem_addr), "l"(gmem), "r"(src_bytes) : "memory");
 }
-__device__ inline void g5_cp_async_4(unsigned smem_addr, const void* gmem, unsigned src_bytes) {
-  asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;\n" ::"r"(smem_addr), "l"(gmem), "r"(src_bytes) : "memory");
+__device__ inline void g5_cp_async_8(unsigned smem_addr, const void* gmem, unsigned src_bytes) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 8, %2;\n" ::"r"(smem_addr), "l"(gmem), "r"(src_bytes) : "memory");
 }
 __device__ inline void g5_mbar_init(unsigned addr, unsigned count) { asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(addr), "r"(count) : "memory"); }
-// Polls until the phase with the given parity has completed; false when the limit ran out.
-__device__ inline bool g5_mbar_wait(unsigned addr, unsigned parity) {
+// Polls until the phase with the given parity has completed; false when the limit ran out or another thread of the CTA gave up.
+__device__ inline bool g5_mbar_wait(unsigned addr, unsigned parity, volatile int* gave_up) {
   for (unsigned spin = 0; spin < kG5SpinLimit; ++spin) {
     unsigned done;
     asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.b32 %0, 1, 0, p;\n}\n" : "=r"(done) : "r"(addr), "r"(parity) : "memory");
     if (done) return true;
+    if ((spin & 1023u) == 1023u && *gave_up != 0) return false;
   }
   return false;
 }
@@ -87,8 +91,9 @@ __global__ void __launch_bounds__(G5_THREADS, 2) grouped_q4_tc5_kernel(GroupedAr
   constexpr int NW = L::NW;
   constexpr unsigned TMEM_COLS = NW * G5_BN;
   extern __shared__ unsigned char g5_smem_raw[];
-  __shared__ __align__(8) unsigned long long s_bar[G5_STAGES + 1];  // stage released by the tensor core; [STAGES]: all MMAs done
+  __shared__ __align__(8) unsigned long long s_bar[2 * G5_B_STAGES + 1];  // [0, 2): step filled by the 256 producers; [2, 4): step's MMAs done; [4]: all MMAs done
   __shared__ unsigned s_tmem;
+  __shared__ volatile int s_failed;
   pdl_sync();  // the route plan and the rows come from the kernels before
   if (blockIdx.y >= *p.n_tiles) return;
   const RouteTile tile = p.tiles[blockIdx.y];
@@ -102,7 +107,9 @@ __global__ void __launch_bounds__(G5_THREADS, 2) grouped_q4_tc5_kernel(GroupedAr
   unsigned* s_route = reinterpret_cast<unsigned*>(smem + L::ROUTES);
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i <= G5_STAGES; ++i) g5_mbar_init(bar_base + 8 * i, 1);
+    for (int i = 0; i < G5_B_STAGES; ++i) g5_mbar_init(bar_base + 8 * i, G5_PRODUCERS);
+    for (int i = G5_B_STAGES; i <= 2 * G5_B_STAGES; ++i) g5_mbar_init(bar_base + 8 * i, 1);
+    s_failed = 0;
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
   }
   if (warp == 0) {
@@ -117,72 +124,78 @@ __global__ void __launch_bounds__(G5_THREADS, 2) grouped_q4_tc5_kernel(GroupedAr
   const unsigned tmem = s_tmem;
   const size_t expert_rows = static_cast<size_t>(tile.expert) * p.n;
 
-  // this thread's four A chunks per stage: rows r, r + 32, r + 64, r + 96, 16-byte chunk a_c8
-  const unsigned a_c8 = threadIdx.x & 7;
-  const unsigned short* a_src[4];
+  const bool producer = threadIdx.x < G5_PRODUCERS;
+  bool failed = false;
+  if (producer) {
+    // this thread's four A chunks per stage: rows r, r + 32, r + 64, r + 96, 16-byte chunk a_c8
+    const unsigned a_c8 = threadIdx.x & 7;
+    const unsigned short* a_src[4];
 #pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    const unsigned route = s_route[(threadIdx.x >> 3) + i * (G5_THREADS / 8)];
-    a_src[i] = route != 0xFFFFFFFFu ? p.x + static_cast<size_t>(route / p.src_div) * p.k + a_c8 * 8 : nullptr;
-  }
+    for (int i = 0; i < 4; ++i) {
+      const unsigned route = s_route[(threadIdx.x >> 3) + i * (G5_PRODUCERS / 8)];
+      a_src[i] = route != 0xFFFFFFFFu ? p.x + static_cast<size_t>(route / p.src_div) * p.k + a_c8 * 8 : nullptr;
+    }
+    // ... and its own slice of the weights: column c, quarter `part` of every 64-k step (8 bytes of nibbles per matrix)
+    const unsigned c = threadIdx.x >> 2, part = threadIdx.x & 3;
+    const bool col_ok = col0 + c < p.n;
+    const size_t w_row = expert_rows + (col_ok ? col0 + c : 0);
+    const unsigned own = threadIdx.x * 8;  // byte offset of this thread's private staging slot inside a stage's region
 
-  auto issue_loads = [&](unsigned it) {
-    if (it < k_iters) {
-      const unsigned slot = it % G5_STAGES, stage = smem_base + slot * L::STAGE, kk = it * G5_BK;
+    auto issue_loads = [&](unsigned it) {
+      if (it < k_iters) {
+        const unsigned a_tile = smem_base + (it % G5_A_STAGES) * G5_A_BYTES, slot = it % G5_RAW_STAGES, kk = it * G5_BK;
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const unsigned r = (threadIdx.x >> 3) + i * (G5_THREADS / 8);
-        const bool ok = a_src[i] != nullptr;
-        g5_cp_async_16(stage + r * 128 + ((a_c8 ^ (r & 7)) << 4), ok ? static_cast<const void*>(a_src[i] + kk) : static_cast<const void*>(p.x), ok ? 16u : 0u);
-      }
-      if (threadIdx.x < 128) {
-        // nibbles: 64 columns x 2 chunks of 16 bytes per matrix
-        const unsigned c = threadIdx.x >> 1, half = threadIdx.x & 1;
-        const bool ok = col0 + c < p.n;
-        const size_t row = expert_rows + (ok ? col0 + c : 0);
-#pragma unroll
-        for (int w = 0; w < NW; ++w)
-          g5_cp_async_16(smem_base + L::RAW + ((slot * NW + w) * G5_BN + c) * 32 + half * 16, p.packed[w] + row * words_per_row + (kk / 8) + half * 4, ok ? 16u : 0u);
-      } else if ((it & 1u) == 0) {
-        // scales and biases of groups it and it + 1 (4 bytes, aligned because the group count per row is even)
-        const unsigned idx = threadIdx.x - 128, c = idx & 63, which = idx >> 6;
-        const bool ok = col0 + c < p.n;
-        const size_t row = expert_rows + (ok ? col0 + c : 0);
-        const unsigned pslot = (it >> 1) % G5_PARAM_SLOTS;
+        for (int i = 0; i < 4; ++i) {
+          const unsigned r = (threadIdx.x >> 3) + i * (G5_PRODUCERS / 8);
+          const bool ok = a_src[i] != nullptr;
+          g5_cp_async_16(a_tile + r * 128 + ((a_c8 ^ (r & 7)) << 4), ok ? static_cast<const void*>(a_src[i] + kk) : static_cast<const void*>(p.x), ok ? 16u : 0u);
+        }
 #pragma unroll
         for (int w = 0; w < NW; ++w) {
-          const unsigned short* src = (which ? p.biases[w] : p.scales[w]) + row * groups_per_row + it;
-          g5_cp_async_4(smem_base + L::PARAMS + (((pslot * NW + w) * 2 + which) * G5_BN + c) * 4, src, ok ? 4u : 0u);
+          g5_cp_async_8(smem_base + L::RAW + (slot * NW + w) * (G5_PRODUCERS * 8) + own, p.packed[w] + w_row * words_per_row + (kk / 8) + part * 2, col_ok ? 8u : 0u);
         }
       }
-    }
-    asm volatile("cp.async.commit_group;\n" ::: "memory");
-  };
+      asm volatile("cp.async.commit_group;\n" ::: "memory");
+    };
 
 #pragma unroll
-  for (int s = 0; s < G5_STAGES - 1; ++s) issue_loads(s);
+    for (int s = 0; s < G5_AHEAD; ++s) issue_loads(s);
 
-  const unsigned idesc = g5_instr_desc();
-  bool failed = false;
-  for (unsigned it = 0; it < k_iters; ++it) {
-    asm volatile("cp.async.wait_group %0;\n" ::"n"(G5_STAGES - 2) : "memory");
-    __syncthreads();  // the nibbles, scales and biases of step `it` are visible to every thread
-    const unsigned slot = it % G5_STAGES;
-    {
-      // expand: thread -> (column, quarter of the 64-k step) = two packed words per matrix
-      const unsigned c = threadIdx.x >> 2, part = threadIdx.x & 3;
-      const unsigned pslot = (it >> 1) % G5_PARAM_SLOTS, shift = (it & 1u) * 16;
-      const unsigned offset_bits = 0x43004300u;
-      const __nv_bfloat162 offset2 = *reinterpret_cast<const __nv_bfloat162*>(&offset_bits);
+    const unsigned offset_bits = 0x43004300u;
+    const __nv_bfloat162 offset2 = *reinterpret_cast<const __nv_bfloat162*>(&offset_bits);
+    // scale and bias of this thread's column travel in registers, fetched one step ahead
+    unsigned sc_next[NW], bi_next[NW];
+#pragma unroll
+    for (int w = 0; w < NW; ++w) {
+      sc_next[w] = col_ok && k_iters != 0 ? __ldg(p.scales[w] + w_row * groups_per_row) : 0u;
+      bi_next[w] = col_ok && k_iters != 0 ? __ldg(p.biases[w] + w_row * groups_per_row) : 0u;
+    }
+    for (unsigned it = 0; it < k_iters; ++it) {
+      // A slot (it + 2) % 4 and B slot it % 2 were last read by the MMAs of step it - 2
+      if (it >= 2) {
+        const unsigned prev = it - 2;
+        if (!g5_mbar_wait(bar_base + 8 * (G5_B_STAGES + prev % G5_B_STAGES), (prev / G5_B_STAGES) & 1u, &s_failed)) { failed = true; break; }
+      }
+      issue_loads(it + G5_AHEAD);
+      unsigned sc_now[NW], bi_now[NW];
 #pragma unroll
       for (int w = 0; w < NW; ++w) {
-        const unsigned* params = reinterpret_cast<const unsigned*>(smem + L::PARAMS) + ((pslot * NW + w) * 2) * G5_BN;
-        const unsigned sc = (params[c] >> shift) & 0xFFFFu, bi = (params[G5_BN + c] >> shift) & 0xFFFFu;
+        sc_now[w] = sc_next[w];
+        bi_now[w] = bi_next[w];
+        const bool more = col_ok && it + 1 < k_iters;
+        sc_next[w] = more ? __ldg(p.scales[w] + w_row * groups_per_row + it + 1) : 0u;
+        bi_next[w] = more ? __ldg(p.biases[w] + w_row * groups_per_row + it + 1) : 0u;
+      }
+      asm volatile("cp.async.wait_group %0;\n" ::"n"(G5_AHEAD) : "memory");  // this thread's copies of step `it` have landed
+      const unsigned slot = it % G5_RAW_STAGES, b_slot = it % G5_B_STAGES;
+#pragma unroll
+      for (int w = 0; w < NW; ++w) {
+        const unsigned sc = sc_now[w], bi = bi_now[w];
         const unsigned s2 = sc | (sc << 16), b2 = bi | (bi << 16);
         const __nv_bfloat162 scale2 = *reinterpret_cast<const __nv_bfloat162*>(&s2), bias2 = *reinterpret_cast<const __nv_bfloat162*>(&b2);
-        const uint2 q = *reinterpret_cast<const uint2*>(smem + L::RAW + ((slot * NW + w) * G5_BN + c) * 32 + part * 8);
+        const uint2 q = *reinterpret_cast<const uint2*>(smem + L::RAW + (slot * NW + w) * (G5_PRODUCERS * 8) + own);
         const unsigned words[2] = {q.x, q.y};
-        unsigned char* b_tile = smem + slot * L::STAGE + G5_A_BYTES + w * G5_B_BYTES;
+        unsigned char* b_tile = smem + L::B + (b_slot * NW + w) * G5_B_BYTES;
 #pragma unroll
         for (int i = 0; i < 2; ++i) {
           unsigned r[4];
@@ -197,16 +210,22 @@ __global__ void __launch_bounds__(G5_THREADS, 2) grouped_q4_tc5_kernel(GroupedAr
               make_uint4(__byte_perm(r[0], r[1], 0x5410), __byte_perm(r[2], r[3], 0x5410), __byte_perm(r[0], r[1], 0x7632), __byte_perm(r[2], r[3], 0x7632));
         }
       }
+      // cp.async and st.shared wrote through the generic proxy; the tensor core reads through the async proxy
+      asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+      asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(bar_base + 8 * b_slot) : "memory");
     }
-    asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");  // cp.async and st.shared wrote through the generic proxy; the tensor core reads through the async proxy
-    if (__syncthreads_or(failed ? 1 : 0)) { failed = true; break; }
-    if (threadIdx.x == 0) {
+    asm volatile("cp.async.wait_group 0;\n" ::: "memory");
+  } else if (threadIdx.x == G5_PRODUCERS) {
+    // the elected thread of the extra warp feeds the tensor core as stages fill up
+    const unsigned idesc = g5_instr_desc();
+    for (unsigned it = 0; it < k_iters; ++it) {
+      const unsigned b_slot = it % G5_B_STAGES;
+      if (!g5_mbar_wait(bar_base + 8 * b_slot, (it / G5_B_STAGES) & 1u, &s_failed)) { failed = true; break; }
       asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-      const unsigned stage = smem_base + slot * L::STAGE;
-      const unsigned long long a_desc = g5_smem_desc(stage);
+      const unsigned long long a_desc = g5_smem_desc(smem_base + (it % G5_A_STAGES) * G5_A_BYTES);
 #pragma unroll
       for (int w = 0; w < NW; ++w) {
-        const unsigned long long b_desc = g5_smem_desc(stage + G5_A_BYTES + w * G5_B_BYTES);
+        const unsigned long long b_desc = g5_smem_desc(smem_base + L::B + (b_slot * NW + w) * G5_B_BYTES);
 #pragma unroll
         for (int ks = 0; ks < G5_BK / 16; ++ks) {
           const unsigned accumulate = (it != 0 || ks != 0) ? 1u : 0u;
@@ -215,26 +234,20 @@ __global__ void __launch_bounds__(G5_THREADS, 2) grouped_q4_tc5_kernel(GroupedAr
                        : "memory");
         }
       }
-      asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(bar_base + 8 * slot) : "memory");
-      if (it + 1 == k_iters) asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(bar_base + 8 * G5_STAGES) : "memory");
+      asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(bar_base + 8 * (G5_B_STAGES + b_slot)) : "memory");
+      if (it + 1 == k_iters) asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(bar_base + 8 * (2 * G5_B_STAGES)) : "memory");
     }
-    // refill the stage the previous step read, once the tensor core has released it
-    if (it >= 1) {
-      const unsigned prev = it - 1;
-      if (!g5_mbar_wait(bar_base + 8 * (prev % G5_STAGES), (prev / G5_STAGES) & 1u)) failed = true;
-    }
-    if (!failed) issue_loads(it + G5_STAGES - 1);
-    else asm volatile("cp.async.commit_group;\n" ::: "memory");
   }
-  asm volatile("cp.async.wait_group 0;\n" ::: "memory");
-  if (!failed && k_iters != 0 && !g5_mbar_wait(bar_base + 8 * G5_STAGES, 0)) failed = true;
+  if (failed) s_failed = 1;
+  // every thread waits for the last MMA (bounded), then the CTA agrees on whether anything gave up
+  if (!failed && k_iters != 0 && !g5_mbar_wait(bar_base + 8 * (2 * G5_B_STAGES), 0, &s_failed)) { failed = true; s_failed = 1; }
   if (__syncthreads_or(failed ? 1 : 0)) {
     failed = true;
     if (threadIdx.x == 0) atomicAdd(&g_grouped_tc5_giveups, 1u);
   }
   asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
 
-  if (!failed) {
+  if (!failed && producer) {
     const unsigned quarter = warp & 3, half = warp >> 2;  // TMEM lanes 32 * quarter .., columns 32 * half ..
     const unsigned route = s_route[quarter * 32 + lane];
     const unsigned c_first = col0 + half * 32;
@@ -305,11 +318,8 @@ void launch_g5(Ctx& ctx, const GroupedArgs& a, unsigned tiles) {
 
 }  // namespace
 
-// Group count per row even (4-byte scale / bias copies), 4-byte aligned scale and bias tables.
 bool grouped_tc5_supported(const GroupedArgs& a) {
-  bool ok = a.k % 128 == 0 && a.k >= 128 && a.n >= 1;
-  for (int w = 0; w < 2; ++w) ok = ok && reinterpret_cast<size_t>(a.scales[w]) % 4 == 0 && reinterpret_cast<size_t>(a.biases[w]) % 4 == 0;
-  return ok;
+  return a.k % 64 == 0 && a.k >= 64 && a.n >= 1 && reinterpret_cast<size_t>(a.packed[0]) % 8 == 0 && reinterpret_cast<size_t>(a.packed[1]) % 8 == 0;
 }
 
 void launch_grouped_tc5(Ctx& ctx, const GroupedArgs& a, bool pair, unsigned tiles) {
