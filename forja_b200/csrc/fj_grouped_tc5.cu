@@ -36,9 +36,11 @@ constexpr unsigned kG5SpinLimit = 1u << 24;
 
 __device__ unsigned g_grouped_tc5_giveups = 0;
 
-template <bool kPair>
+// kPair: gate and up matrices, 64 columns each. kWide (single matrix only): 128 columns, handled as two 64-column halves
+// so that a CTA reads its 128 activation rows once for twice the output.
+template <bool kPair, bool kWide>
 struct G5Layout {
-  static constexpr int NW = kPair ? 2 : 1;
+  static constexpr int NW = (kPair || kWide) ? 2 : 1;
   static constexpr int B = G5_A_STAGES * G5_A_BYTES;                       // [A_STAGES] A tiles, then [B_STAGES][NW] expanded B tiles; all 1024-byte aligned
   static constexpr int RAW = B + G5_B_STAGES * NW * G5_B_BYTES;            // [RAW_STAGES][NW][256 threads x 8 B] nibbles, private to the thread that copied them
   static constexpr int ROUTES = RAW + G5_RAW_STAGES * NW * G5_RAW_BYTES;   // [128] route ids
@@ -85,9 +87,9 @@ __device__ inline void g5_tmem_load32(unsigned taddr, unsigned (&v)[32]) {
   asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
 }
 
-template <bool kPair>
+template <bool kPair, bool kWide>
 __global__ void __launch_bounds__(G5_THREADS, 2) grouped_q4_tc5_kernel(GroupedArgs p) {
-  using L = G5Layout<kPair>;
+  using L = G5Layout<kPair, kWide>;
   constexpr int NW = L::NW;
   constexpr unsigned TMEM_COLS = NW * G5_BN;
   extern __shared__ unsigned char g5_smem_raw[];
@@ -98,7 +100,7 @@ __global__ void __launch_bounds__(G5_THREADS, 2) grouped_q4_tc5_kernel(GroupedAr
   if (blockIdx.y >= *p.n_tiles) return;
   const RouteTile tile = p.tiles[blockIdx.y];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const unsigned col0 = blockIdx.x * G5_BN;
+  const unsigned col0 = blockIdx.x * (kWide ? 2 * G5_BN : G5_BN);
   const unsigned k_iters = p.k / G5_BK, words_per_row = p.k / 8, groups_per_row = p.k / 64;
   const unsigned raw_addr = static_cast<unsigned>(__cvta_generic_to_shared(g5_smem_raw));
   const unsigned smem_base = (raw_addr + 1023u) & ~1023u;
@@ -137,8 +139,19 @@ __global__ void __launch_bounds__(G5_THREADS, 2) grouped_q4_tc5_kernel(GroupedAr
     }
     // ... and its own slice of the weights: column c, quarter `part` of every 64-k step (8 bytes of nibbles per matrix)
     const unsigned c = threadIdx.x >> 2, part = threadIdx.x & 3;
-    const bool col_ok = col0 + c < p.n;
-    const size_t w_row = expert_rows + (col_ok ? col0 + c : 0);
+    bool col_ok[NW];
+    size_t w_row[NW];
+    const unsigned* w_packed[NW];
+    const unsigned short *w_scales[NW], *w_biases[NW];
+#pragma unroll
+    for (int w = 0; w < NW; ++w) {
+      const unsigned col = col0 + (kWide ? w * G5_BN : 0) + c;
+      col_ok[w] = col < p.n;
+      w_row[w] = expert_rows + (col_ok[w] ? col : 0);
+      w_packed[w] = p.packed[kPair ? w : 0];
+      w_scales[w] = p.scales[kPair ? w : 0];
+      w_biases[w] = p.biases[kPair ? w : 0];
+    }
     const unsigned own = threadIdx.x * 8;  // byte offset of this thread's private staging slot inside a stage's region
 
     auto issue_loads = [&](unsigned it) {
@@ -152,7 +165,7 @@ __global__ void __launch_bounds__(G5_THREADS, 2) grouped_q4_tc5_kernel(GroupedAr
         }
 #pragma unroll
         for (int w = 0; w < NW; ++w) {
-          g5_cp_async_8(smem_base + L::RAW + (slot * NW + w) * (G5_PRODUCERS * 8) + own, p.packed[w] + w_row * words_per_row + (kk / 8) + part * 2, col_ok ? 8u : 0u);
+          g5_cp_async_8(smem_base + L::RAW + (slot * NW + w) * (G5_PRODUCERS * 8) + own, w_packed[w] + w_row[w] * words_per_row + (kk / 8) + part * 2, col_ok[w] ? 8u : 0u);
         }
       }
       asm volatile("cp.async.commit_group;\n" ::: "memory");
@@ -167,8 +180,8 @@ __global__ void __launch_bounds__(G5_THREADS, 2) grouped_q4_tc5_kernel(GroupedAr
     unsigned sc_next[NW], bi_next[NW];
 #pragma unroll
     for (int w = 0; w < NW; ++w) {
-      sc_next[w] = col_ok && k_iters != 0 ? __ldg(p.scales[w] + w_row * groups_per_row) : 0u;
-      bi_next[w] = col_ok && k_iters != 0 ? __ldg(p.biases[w] + w_row * groups_per_row) : 0u;
+      sc_next[w] = col_ok[w] && k_iters != 0 ? __ldg(w_scales[w] + w_row[w] * groups_per_row) : 0u;
+      bi_next[w] = col_ok[w] && k_iters != 0 ? __ldg(w_biases[w] + w_row[w] * groups_per_row) : 0u;
     }
     for (unsigned it = 0; it < k_iters; ++it) {
       // A slot (it + 2) % 4 and B slot it % 2 were last read by the MMAs of step it - 2
@@ -182,9 +195,9 @@ __global__ void __launch_bounds__(G5_THREADS, 2) grouped_q4_tc5_kernel(GroupedAr
       for (int w = 0; w < NW; ++w) {
         sc_now[w] = sc_next[w];
         bi_now[w] = bi_next[w];
-        const bool more = col_ok && it + 1 < k_iters;
-        sc_next[w] = more ? __ldg(p.scales[w] + w_row * groups_per_row + it + 1) : 0u;
-        bi_next[w] = more ? __ldg(p.biases[w] + w_row * groups_per_row + it + 1) : 0u;
+        const bool more = col_ok[w] && it + 1 < k_iters;
+        sc_next[w] = more ? __ldg(w_scales[w] + w_row[w] * groups_per_row + it + 1) : 0u;
+        bi_next[w] = more ? __ldg(w_biases[w] + w_row[w] * groups_per_row + it + 1) : 0u;
       }
       asm volatile("cp.async.wait_group %0;\n" ::"n"(G5_AHEAD) : "memory");  // this thread's copies of step `it` have landed
       const unsigned slot = it % G5_RAW_STAGES, b_slot = it % G5_B_STAGES;
@@ -248,10 +261,12 @@ __global__ void __launch_bounds__(G5_THREADS, 2) grouped_q4_tc5_kernel(GroupedAr
   asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
 
   if (!failed && producer) {
-    const unsigned quarter = warp & 3, half = warp >> 2;  // TMEM lanes 32 * quarter .., columns 32 * half ..
+    const unsigned quarter = warp & 3, half = warp >> 2;  // TMEM lanes 32 * quarter .., columns 32 * half .. of every 64-column block
     const unsigned route = s_route[quarter * 32 + lane];
-    const unsigned c_first = col0 + half * 32;
-    const unsigned taddr = tmem + ((quarter * 32) << 16) + half * 32;
+#pragma unroll 1
+    for (int pass = 0; pass < (kWide ? 2 : 1); ++pass) {
+    const unsigned c_first = col0 + pass * G5_BN + half * 32;
+    const unsigned taddr = tmem + ((quarter * 32) << 16) + pass * G5_BN + half * 32;
     unsigned v[32];
     g5_tmem_load32(taddr, v);
     if (kPair) {
@@ -296,23 +311,25 @@ __global__ void __launch_bounds__(G5_THREADS, 2) grouped_q4_tc5_kernel(GroupedAr
         }
       }
     }
+    }  // pass
   }
   asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
   __syncthreads();
   if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
 }
 
-template <bool kPair>
+template <bool kPair, bool kWide>
 void launch_g5(Ctx& ctx, const GroupedArgs& a, unsigned tiles) {
-  constexpr int smem = G5Layout<kPair>::TOTAL;
+  constexpr int smem = G5Layout<kPair, kWide>::TOTAL;
   static bool configured[64] = {};
   int device = 0;
   cudaGetDevice(&device);
   if (device >= 0 && device < 64 && !configured[device]) {
-    cudaFuncSetAttribute(grouped_q4_tc5_kernel<kPair>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    cudaFuncSetAttribute(grouped_q4_tc5_kernel<kPair, kWide>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     configured[device] = true;
   }
-  launch_pdl(grouped_q4_tc5_kernel<kPair>, dim3((a.n + G5_BN - 1) / G5_BN, tiles), dim3(G5_THREADS), smem, ctx.stream, a);
+  const unsigned width = kWide ? 2 * G5_BN : G5_BN;
+  launch_pdl(grouped_q4_tc5_kernel<kPair, kWide>, dim3((a.n + width - 1) / width, tiles), dim3(G5_THREADS), smem, ctx.stream, a);
   ctx.launches++;
 }
 
@@ -323,8 +340,9 @@ bool grouped_tc5_supported(const GroupedArgs& a) {
 }
 
 void launch_grouped_tc5(Ctx& ctx, const GroupedArgs& a, bool pair, unsigned tiles) {
-  if (pair) launch_g5<true>(ctx, a, tiles);
-  else launch_g5<false>(ctx, a, tiles);
+  if (pair) launch_g5<true, false>(ctx, a, tiles);
+  else if (a.n > G5_BN) launch_g5<false, true>(ctx, a, tiles);
+  else launch_g5<false, false>(ctx, a, tiles);
 }
 
 unsigned grouped_tc5_giveups() {

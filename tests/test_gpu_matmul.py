@@ -247,3 +247,22 @@ def test_bucketed_expert_path_zeroes_bad_routes_and_reports_the_lowest_id(rows):
     mask = np.ones((rows, top_k), bool)
     mask[3, 1] = mask[17, 0] = False
     assert_close(got[mask], want[mask], QUANT_TOL)
+
+
+@pytest.mark.parametrize("inter", [64, 96])  # one 64-column block; two blocks of which the second is ragged
+def test_bucketed_expert_path_narrow_and_ragged_column_blocks(inter):
+    """128-row tcgen05 tiles with an output narrower than, or not a multiple of, the column block."""
+    rng = np.random.default_rng(inter)
+    be = backend()
+    experts, hidden, top_k, rows = 4, 256, 4, 128
+    dt = fb.BF16
+    pk, sc, bi = quant_weights(rng, inter, hidden, 4, 64, fb.BF16, experts)
+    x, xh = up(rng.standard_normal((rows, hidden)), dt)
+    ids = rng.integers(0, experts, (rows, top_k)).astype(np.uint32)
+    idx, _ = up_u32(ids)
+    out = be.alloc(dt, (rows, top_k, inter))
+    be.run(Op.GatherQuantMatmul(4, 64), [x, be.tensor_from(pk, fb.U32), be.tensor_from(sc, fb.BF16), be.tensor_from(bi, fb.BF16), idx], [out])
+    fjo.set_threads(fjo.max_threads())
+    want = fjo.decode(fjo.gather_quant_matmul(xh, dt, pk, sc, bi, fjo.BF16, ids, 4, 64, dt), dt)
+    fjo.set_threads(1)
+    assert_close(down(out), want, QUANT_TOL)
