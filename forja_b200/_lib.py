@@ -79,7 +79,7 @@ EXPORTS = [
     "fj_sched_decode_bucket", "fj_sched_ready_prompt", "fj_sched_prompt_batch", "fj_sched_waiting", "fj_sched_active",
     "fj_prompt_chunk_work", "fj_prompt_chunk_merged_work", "fj_reservations_fit", "fj_prefill_plan",
     "fj_ep_load", "fj_ep_unique_id", "fj_ep_create", "fj_ep_destroy", "fj_ep_all_to_all", "fj_moe_model_create", "fj_moe_model_destroy",
-    "fj_moe_step", "fj_moe_step_stats", "fj_fill_random", "fj_tcgen05_wait_giveups", "fj_moe_capture_routes", "fj_moe_read_routes",
+    "fj_moe_step", "fj_moe_step_stats", "fj_fill_random", "fj_tcgen05_wait_giveups", "fj_moe_capture_routes", "fj_moe_read_routes", "fj_moe_phase_timing", "fj_moe_read_phase_ms",
 ]
 
 _lib = None
@@ -150,7 +150,7 @@ def load():
         "fj_ep_load": ([C.c_char_p], I32), "fj_ep_unique_id": ([P], I32), "fj_ep_create": ([P, P, U32, U32, P], I32), "fj_ep_destroy": ([P], None),
         "fj_ep_all_to_all": ([P, U64, U64, U64], I32), "fj_moe_model_create": ([P, P, P, U64, P, P, P, P, P], I32),
         "fj_moe_model_destroy": ([P], None), "fj_moe_step": ([P, P, P, U64], I32), "fj_moe_step_stats": ([P, P, P], I32),
-        "fj_fill_random": ([P, U64, U64, U64, U32, U64, C.c_float, C.c_float], I32), "fj_tcgen05_wait_giveups": ([P, P], I32), "fj_moe_capture_routes": ([P, U32], I32), "fj_moe_read_routes": ([P, U32, U32, P, P], I32),
+        "fj_fill_random": ([P, U64, U64, U64, U32, U64, C.c_float, C.c_float], I32), "fj_tcgen05_wait_giveups": ([P, P], I32), "fj_moe_capture_routes": ([P, U32], I32), "fj_moe_read_routes": ([P, U32, U32, P, P], I32), "fj_moe_phase_timing": ([P, U32], I32), "fj_moe_read_phase_ms": ([P, P], I32),
     }
     for name, (types, restype) in sched.items():
         fn = getattr(lib, name)

@@ -617,3 +617,12 @@ class MoeModel:
         k, w = C.c_uint64(0), C.c_uint64(0)
         _check(self._lib.fj_moe_step_stats(self._h, C.byref(k), C.byref(w)))
         return {"kernels": k.value, "attn_work_items": w.value}
+
+    def phase_timing(self, enabled: bool):
+        _check(self._lib.fj_moe_phase_timing(self._h, 1 if enabled else 0))
+
+    def phase_ms(self):
+        """Milliseconds of the last step summed over the layers: attention + router, dispatch, experts, return + combine."""
+        out = (C.c_float * 4)()
+        _check(self._lib.fj_moe_read_phase_ms(self._h, out))
+        return [float(v) for v in out]

@@ -147,6 +147,9 @@ def run_moe(args):
     t0, t1 = be.timer(), be.timer()
     processed = 0
     kernels = 0
+    phase_ms = [0.0] * 4
+    if args.phases:
+        model.phase_timing(True)
     for step in range(args.warmup + args.steps):
         if step == args.warmup:
             be.synchronize()
@@ -160,6 +163,8 @@ def run_moe(args):
         ids = rng.integers(0, cfg["vocab"], rows).astype(np.uint32) if rows else None
         model.step(ids, want_tokens=rows > 0, lanes=lanes)
         kernels += model.stats()["kernels"]
+        if args.phases and step >= args.warmup:
+            phase_ms = [a + b for a, b in zip(phase_ms, model.phase_ms())]
         state.advance(tokens)
         processed += rows
     be.timer_record(t1)
@@ -175,6 +180,9 @@ def run_moe(args):
         total = int(sum(float(g[1]) for g in gathered))
         kernels = int(sum(float(g[2]) for g in gathered))
         dist.barrier()
+    if args.phases:
+        print(json.dumps({"rank": rank, "ms_per_step_by_phase": {name: v / args.steps for name, v in zip(
+            ("attention_and_router", "dispatch", "experts", "return_and_combine"), phase_ms)}}), flush=True)
     if rank == 0:
         print(json.dumps({
             "metric": "moe step tok/s (prompt + generated tokens)", "value": total / elapsed, "unit": "tok/s", "n_gpus": world, "steps": args.steps,
@@ -326,6 +334,7 @@ def main():
     moe.add_argument("--prompt-budget", type=int, default=2048)
     moe.add_argument("--prefill-limit", type=int, default=4)
     moe.add_argument("--decode-only", action="store_true")
+    moe.add_argument("--phases", action="store_true", help="also print the time of the timed steps split by phase (CUDA events inside the step)")
     moe.add_argument("--grouped-min-routes", type=int, default=0, help="0 = library default")
     moe.add_argument("--stream-rows-per-expert", type=int, default=0, help="0 = library default")
     q4 = sub.add_parser("q4")

@@ -527,7 +527,31 @@ __global__ void routes_combine_kernel(const float* __restrict__ per_route, const
                                       const void* __restrict__ weights, int w_dt, const void* __restrict__ extra, int e_dt, void* out, int out_dt, unsigned rows, unsigned top_k,
                                       unsigned width) {
   pdl_sync();
+  // four columns per thread (16-byte loads of the per-route rows) when the row width and the pointer allow it
+  const bool wide = width % 4 == 0 && reinterpret_cast<size_t>(per_route) % 16 == 0;
   for (unsigned row = blockIdx.x; row < rows; row += gridDim.x) {
+    if (wide) {
+      for (unsigned c = (blockIdx.y * blockDim.x + threadIdx.x) * 4; c < width; c += gridDim.y * blockDim.x * 4) {
+        float total[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        for (unsigned j = 0; j < top_k; ++j) {
+          const unsigned slot = route_slot ? route_slot[row * top_k + j] : (expert_ids[row * top_k + j] < experts ? row * top_k + j : 0xFFFFFFFFu);
+          if (slot == 0xFFFFFFFFu) continue;
+          const float w = load_as_f32(weights, w_dt, row * top_k + j);
+          const float4 v = *reinterpret_cast<const float4*>(per_route + static_cast<size_t>(slot) * width + c);
+          total[0] = __fadd_rn(total[0], __fmul_rn(w, v.x));
+          total[1] = __fadd_rn(total[1], __fmul_rn(w, v.y));
+          total[2] = __fadd_rn(total[2], __fmul_rn(w, v.z));
+          total[3] = __fadd_rn(total[3], __fmul_rn(w, v.w));
+        }
+        const size_t o = static_cast<size_t>(row) * width + c;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          if (extra) total[i] = total[i] + load_as_f32(extra, e_dt, o + i);
+          store_from_f32(out, out_dt, o + i, total[i]);
+        }
+      }
+      continue;
+    }
     for (unsigned c = blockIdx.y * blockDim.x + threadIdx.x; c < width; c += gridDim.y * blockDim.x) {
       float total = 0.0f;
       for (unsigned j = 0; j < top_k; ++j) {
@@ -547,7 +571,7 @@ void launch_routes_combine(Ctx& ctx, const float* per_route, const unsigned* rou
                            int e_dt, void* out, int out_dt, unsigned rows, unsigned top_k, unsigned width) {
   if (rows == 0) return;
   // few rows: spread the columns of a row over several CTAs so that the grid still fills the GPU
-  const unsigned col_ctas = rows >= 1024u ? 1u : std::min((width + 255u) / 256u, (1024u + rows - 1) / rows);
+  const unsigned col_ctas = rows >= 1024u ? 1u : std::min((width + 1023u) / 1024u, (1024u + rows - 1) / rows);
   launch_pdl(routes_combine_kernel, dim3(rows < 1024u ? rows : 1024u, col_ctas), dim3(256), 0, ctx.stream, per_route, route_slot, expert_ids, experts, weights, w_dt, extra, e_dt, out, out_dt, rows,
              top_k, width);
   ctx.launches++;

@@ -275,6 +275,7 @@ struct fj_moe_model {
   const float* inv_freq = nullptr;
   uint64_t last_kernels = 0, last_work_items = 0;
   // optional record of every layer's routing of the last step (parity checks): [layers][max_rows * top_k]
+  std::vector<cudaEvent_t> phase_events;  // [layers][5] when phase timing is on
   unsigned* captured_experts = nullptr;
   float* captured_weights = nullptr;
 };
@@ -427,8 +428,39 @@ void fj_moe_model_destroy(fj_moe_model* m) {
   cudaSetDevice(m->be->device);
   cudaStreamSynchronize(m->be->stream);
   for (void* p : m->owned) cudaFree(p);
+  for (cudaEvent_t e : m->phase_events) cudaEventDestroy(e);
   if (m->ep_counts_host) cudaFreeHost(m->ep_counts_host);
   delete m;
+}
+
+int32_t fj_moe_phase_timing(fj_moe_model* m, uint32_t enabled) {
+  if (!m) return FJ_INVALID_INPUT;
+  std::lock_guard<std::mutex> lock(m->be->mutex);
+  cudaSetDevice(m->be->device);
+  cudaStreamSynchronize(m->be->stream);
+  for (cudaEvent_t e : m->phase_events) cudaEventDestroy(e);
+  m->phase_events.clear();
+  if (enabled) {
+    m->phase_events.resize(static_cast<size_t>(m->cfg.layers) * 5);
+    for (cudaEvent_t& e : m->phase_events)
+      if (cudaEventCreate(&e) != cudaSuccess) return FJ_ALLOCATION_FAILED;
+  }
+  return FJ_OK;
+}
+
+int32_t fj_moe_read_phase_ms(fj_moe_model* m, float* out4) {
+  if (!m || !out4 || m->phase_events.empty()) return FJ_INVALID_INPUT;
+  std::lock_guard<std::mutex> lock(m->be->mutex);
+  cudaSetDevice(m->be->device);
+  if (cudaStreamSynchronize(m->be->stream) != cudaSuccess) return FJ_DEVICE_EXECUTION_FAILED;
+  for (int i = 0; i < 4; ++i) out4[i] = 0.0f;
+  for (uint32_t l = 0; l < m->cfg.layers; ++l)
+    for (int i = 0; i < 4; ++i) {
+      float ms = 0.0f;
+      if (cudaEventElapsedTime(&ms, m->phase_events[l * 5 + i], m->phase_events[l * 5 + i + 1]) != cudaSuccess) { cudaGetLastError(); return FJ_INVALID_INPUT; }
+      out4[i] += ms;
+    }
+  return FJ_OK;
 }
 
 int32_t fj_moe_capture_routes(fj_moe_model* m, uint32_t enabled) {
@@ -544,6 +576,10 @@ extern "C" int32_t fj_moe_step(fj_moe_model* m, const uint32_t* token_ids, uint3
   int32_t status = FJ_OK;
   for (uint32_t l = 0; l < c.layers && status == FJ_OK; ++l) {
     const auto& L = m->layers[l];
+    auto mark = [&](int phase) {
+      if (!m->phase_events.empty()) cudaEventRecord(m->phase_events[static_cast<size_t>(l) * 5 + phase], be->stream);
+    };
+    mark(0);
     if (rows != 0) {
       q4(m->normed, L.qkv, m->qkv, dt, rows, H, qd + 2 * kd, 4);
       fj::launch_qknorm_rope_append(ctx, m->qkv, dt, L.q_norm, L.k_norm, pool->pack.positions, pool->pack.slot_mapping, m->q, L.k_plane, L.v_plane, rows, c.q_heads, c.kv_heads,
@@ -604,9 +640,12 @@ extern "C" int32_t fj_moe_step(fj_moe_model* m, const uint32_t* token_ids, uint3
       fj::launch_grouped_q4_single(ctx, act, L.down.packed, L.down.scales, L.down.biases, m->route_plan, n_routes, n_experts, 1, down_out, false, I, H, tile_rows);
       return true;
     };
+    mark(1);
     if (m->world == 1) {
       const unsigned routes = rows * K;
+      mark(2);
       if (bucketed(m->normed, K, m->route_experts, routes, routes, c.experts, m->act, m->down_routes)) {
+        mark(3);
         fj::launch_routes_combine(ctx, m->down_routes, nullptr, m->route_experts, c.experts, m->route_weights, FJ_F32, hidden, dt, other, dt, rows, K, H);
       } else {
         fj::launch_gather_quant_matmul(ctx, m->normed, dt, L.gate.packed, L.gate.scales, L.gate.biases, dt, L.up.packed, L.up.scales, L.up.biases, m->route_experts, m->act, dt, rows, H,
@@ -647,6 +686,7 @@ extern "C" int32_t fj_moe_step(fj_moe_model* m, const uint32_t* token_ids, uint3
       status = ep_all_to_all_rows(m->ep, m->send_rows, slab_at.data(), send_counts, m->recv_rows, packed_at.data(), recv_counts, static_cast<size_t>(H) * 2, m->send_experts,
                                   m->recv_experts, 4);
       if (status != FJ_OK) break;
+      mark(2);
       if (received) {
         // rows received for this rank's experts, densely packed by source: one route each
         if (!bucketed(m->recv_rows, 1, m->recv_experts, received, padded ? cap : received, m->experts_local, m->act_ep, m->down_ep)) {
@@ -657,12 +697,14 @@ extern "C" int32_t fj_moe_step(fj_moe_model* m, const uint32_t* token_ids, uint3
         }
       }
       if (status != FJ_OK) break;
+      mark(3);
       status = ep_all_to_all_rows(m->ep, m->down_ep, packed_at.data(), recv_counts, m->returned, slab_at.data(), send_counts, static_cast<size_t>(H) * 4);
       if (status != FJ_OK) break;
       if (rows) {
         fj::launch_routes_combine(ctx, m->returned, m->route_slot, nullptr, 0, m->route_weights, FJ_F32, hidden, dt, other, dt, rows, K, H);
       }
     }
+    mark(4);
     std::swap(hidden, other);
     if (rows != 0) {
       const void* next_norm = l + 1 < c.layers ? m->layers[l + 1].input_norm : m->final_norm;

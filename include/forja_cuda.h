@@ -406,6 +406,11 @@ void fj_moe_model_destroy(fj_moe_model* model);
  * the group must call it for the same step, even with no active lane of its own (pack zero tokens). */
 int32_t fj_moe_step(fj_moe_model* model, const uint32_t* token_ids, uint32_t* out_tokens, uint64_t logits_out);
 int32_t fj_moe_step_stats(fj_moe_model* model, uint64_t* kernels, uint64_t* attn_work_items);
+/* Measurement aid: while enabled, every layer of a step records CUDA events around its four phases; fj_moe_read_phase_ms
+ * waits for the step and returns the time summed over the layers: [0] attention block and router, [1] dispatch (slot plan,
+ * row scatter, exchange to the experts' owners; ~0 on one GPU), [2] expert projections, [3] exchange back and weighted combine. */
+int32_t fj_moe_phase_timing(fj_moe_model* model, uint32_t enabled);
+int32_t fj_moe_read_phase_ms(fj_moe_model* model, float* out4);
 /* Parity aid: while enabled, every layer's routing of a step (TopK output: expert ids and normalised
  * weights, [rows, top_k] in packed row order) is kept and can be read back after the step. */
 int32_t fj_moe_capture_routes(fj_moe_model* model, uint32_t enabled);
