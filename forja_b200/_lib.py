@@ -71,7 +71,7 @@ EXPORTS = [
     "fj_program_info", "fj_program_classify", "fj_submit", "fj_sub_wait", "fj_sub_gpu_time_ns", "fj_sub_completion_serial", "fj_sub_error",
     "fj_sub_kernel_launches", "fj_sub_profile", "fj_sub_destroy", "fj_synchronize", "fj_kernel_launch_count", "fj_timer_create",
     "fj_timer_record", "fj_timer_elapsed_ns", "fj_kvpool_create", "fj_kvpool_destroy", "fj_kvpool_reserve", "fj_kvpool_release",
-    "fj_kvpool_read_table", "fj_kvpool_read_generations", "fj_kvpool_read_free", "fj_kvpool_tables_buffer",
+    "fj_kvpool_read_table", "fj_kvpool_read_generations", "fj_kvpool_read_free", "fj_kvpool_read_refcounts", "fj_kvpool_fork", "fj_kvpool_cow_tail", "fj_dense_copy_page", "fj_kvpool_tables_buffer",
     "fj_kvpool_generations_buffer", "fj_pack_step", "fj_dense_model_create", "fj_dense_model_destroy", "fj_dense_step",
     "fj_dense_step_stats", "fj_dense_fill_kv", "fj_dense_profile_attention", "fj_dense_attention_time",
     "fj_paged_decode_attention_static", "fj_sched_create", "fj_sched_destroy", "fj_sched_set_prompt_chunk_multiple", "fj_sched_enqueue",
@@ -127,6 +127,7 @@ def load():
         "fj_synchronize": [P], "fj_timer_create": [P, P], "fj_timer_record": [P, U64], "fj_timer_elapsed_ns": [P, U64, U64, P],
         "fj_kvpool_create": [P, U32, U32, U32, U32, P], "fj_kvpool_reserve": [P, P, P, U32, P], "fj_kvpool_release": [P, P, U32],
         "fj_kvpool_read_table": [P, U32, P], "fj_kvpool_read_generations": [P, P], "fj_kvpool_read_free": [P, P, U32, P],
+        "fj_kvpool_read_refcounts": [P, P], "fj_kvpool_fork": [P, U32, U64, U32, U64, U64], "fj_kvpool_cow_tail": [P, U32, U64, P], "fj_dense_copy_page": [P, U32, U32, U32],
         "fj_pack_step": [P, P, P, U32, P], "fj_dense_model_create": [P, P, U64, U64, P, P, P], "fj_dense_step": [P, P, P, U64],
         "fj_dense_step_stats": [P, P, P], "fj_dense_fill_kv": [P, U64], "fj_dense_profile_attention": [P, U32],
         "fj_dense_attention_time": [P, P, P],

@@ -450,6 +450,21 @@ class KvPool:
         _check(self._lib.fj_kvpool_read_free(self._h, out.ctypes.data_as(C.c_void_p), self.physical_pages, C.byref(n)))
         return out[:n.value]
 
+    def refcounts(self) -> np.ndarray:
+        out = np.zeros(self.physical_pages, np.uint32)
+        _check(self._lib.fj_kvpool_read_refcounts(self._h, out.ctypes.data_as(C.c_void_p)))
+        return out
+
+    def fork(self, src_lane: int, src_logical_len: int, dst_lane: int, prefix_tokens: int, reserved_tokens: int) -> int:
+        """PagedSequence::fork_reserved on the device pool; returns the status (OK, QUOTA_EXCEEDED, INVALID_INPUT)."""
+        return int(self._lib.fj_kvpool_fork(self._h, src_lane, src_logical_len, dst_lane, prefix_tokens, reserved_tokens))
+
+    def cow_tail(self, lane: int, logical_len: int):
+        """PagedSequence::cow_tail; returns (status, copied, source page, destination page, rows to copy)."""
+        out = (C.c_uint32 * 4)()
+        status = int(self._lib.fj_kvpool_cow_tail(self._h, lane, logical_len, out))
+        return status, bool(out[0]), int(out[1]), int(out[2]), int(out[3])
+
     def tables_tensor(self) -> Tensor:
         return Tensor(self._lib.fj_kvpool_tables_buffer(self._h), Layout.contiguous(U32, (self.lanes, self.table_pages, 2)), self.lanes * self.table_pages * 8)
 
@@ -508,6 +523,9 @@ class DenseModel:
 
     def fill_kv(self, seed: int = 0):
         _check(self._lib.fj_dense_fill_kv(self._h, seed))
+
+    def copy_page(self, src_page: int, dst_page: int, tokens: int):
+        _check(self._lib.fj_dense_copy_page(self._h, src_page, dst_page, tokens))
 
     def profile_attention(self, enabled: bool):
         _check(self._lib.fj_dense_profile_attention(self._h, int(enabled)))

@@ -52,7 +52,7 @@ struct fj_backend {
 struct fj_kvpool {
   fj_backend* be = nullptr;
   fj::KvPoolDevice dev{};
-  uint64_t buf_free = 0, buf_count = 0, buf_gens = 0, buf_tables = 0, buf_lane_pages = 0;
+  uint64_t buf_free = 0, buf_count = 0, buf_gens = 0, buf_tables = 0, buf_lane_pages = 0, buf_refcounts = 0, buf_immutable = 0;
   // packer state
   uint64_t buf_lane_meta[5] = {0, 0, 0, 0, 0};  // logical_lengths, query_starts, absolute_positions, activity, cu_seqlens
   uint64_t buf_rows[3] = {0, 0, 0};             // positions, slot_mapping, row_lane

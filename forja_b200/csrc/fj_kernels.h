@@ -193,12 +193,18 @@ struct KvPoolDevice {
   unsigned* generations;  // [physical_pages]
   unsigned* tables;       // [lanes][table_pages][2]
   unsigned* lane_pages;   // [lanes] pages bound to each lane
+  unsigned* refcounts;    // [physical_pages] owners of each page (0 = free)
+  unsigned* immutable;    // [lanes][table_pages] 1 = this lane must not write the page (shared prefix)
   unsigned physical_pages, lanes, table_pages, page_tokens;
 };
 void launch_kvpool_init(Ctx& ctx, const KvPoolDevice& pool);
 void launch_kvpool_reserve(Ctx& ctx, const KvPoolDevice& pool, const unsigned* lanes, const unsigned* tokens, unsigned count,
                            int* status);
 void launch_kvpool_release(Ctx& ctx, const KvPoolDevice& pool, const unsigned* lanes, unsigned count);
+// args (device) = {src lane, dst lane, prefix tokens, reserved tokens}; *status (device) = 0 / 1 quota / 3 overflow / 7 invalid.
+void launch_kvpool_fork(Ctx& ctx, const KvPoolDevice& pool, const unsigned* args, int* status);
+// args (device) = {lane, logical length}; result (device) = {status, copied, src page, dst page, tokens to copy}.
+void launch_kvpool_cow_tail(Ctx& ctx, const KvPoolDevice& pool, const unsigned* args, int* result);
 struct PackOutputs {
   unsigned *logical_lengths, *query_starts, *absolute_positions, *activity, *cu_seqlens, *positions, *slot_mapping, *row_lane;
 };

@@ -7,6 +7,8 @@
 // is materialised here in the same dtype, so rounding points coincide.
 #include "fj_backend.h"
 
+#include <functional>
+
 #include <string.h>
 
 #include <algorithm>
@@ -60,6 +62,8 @@ int32_t fj_kvpool_create(fj_backend* be, uint32_t page_tokens, uint32_t physical
   need(static_cast<uint64_t>(physical_pages) * 4, &pool->buf_gens);
   need(static_cast<uint64_t>(lanes) * table_pages * 8, &pool->buf_tables);
   need(static_cast<uint64_t>(lanes) * 4, &pool->buf_lane_pages);
+  need(static_cast<uint64_t>(physical_pages) * 4, &pool->buf_refcounts);
+  need(static_cast<uint64_t>(lanes) * table_pages * 4, &pool->buf_immutable);
   for (int i = 0; i < 4; ++i) need(static_cast<uint64_t>(lanes) * 4, &pool->buf_lane_meta[i]);
   need(static_cast<uint64_t>(lanes + 1) * 4, &pool->buf_lane_meta[4]);
   need(static_cast<uint64_t>(lanes) * 8, &pool->buf_stage);
@@ -69,6 +73,8 @@ int32_t fj_kvpool_create(fj_backend* be, uint32_t page_tokens, uint32_t physical
   pool->dev.generations = static_cast<unsigned*>(buf_ptr(be, pool->buf_gens));
   pool->dev.tables = static_cast<unsigned*>(buf_ptr(be, pool->buf_tables));
   pool->dev.lane_pages = static_cast<unsigned*>(buf_ptr(be, pool->buf_lane_pages));
+  pool->dev.refcounts = static_cast<unsigned*>(buf_ptr(be, pool->buf_refcounts));
+  pool->dev.immutable = static_cast<unsigned*>(buf_ptr(be, pool->buf_immutable));
   pool->dev.physical_pages = physical_pages; pool->dev.lanes = lanes; pool->dev.table_pages = table_pages; pool->dev.page_tokens = page_tokens;
   pool->pack.logical_lengths = static_cast<unsigned*>(buf_ptr(be, pool->buf_lane_meta[0]));
   pool->pack.query_starts = static_cast<unsigned*>(buf_ptr(be, pool->buf_lane_meta[1]));
@@ -87,7 +93,7 @@ void fj_kvpool_destroy(fj_kvpool* pool) {
   std::lock_guard<std::mutex> lock(be->mutex);
   cudaSetDevice(be->device);
   cudaStreamSynchronize(be->stream);
-  uint64_t ids[] = {pool->buf_free, pool->buf_count, pool->buf_gens, pool->buf_tables, pool->buf_lane_pages, pool->buf_lane_meta[0], pool->buf_lane_meta[1],
+  uint64_t ids[] = {pool->buf_free, pool->buf_count, pool->buf_gens, pool->buf_tables, pool->buf_lane_pages, pool->buf_refcounts, pool->buf_immutable, pool->buf_lane_meta[0], pool->buf_lane_meta[1],
                     pool->buf_lane_meta[2], pool->buf_lane_meta[3], pool->buf_lane_meta[4], pool->buf_rows[0], pool->buf_rows[1], pool->buf_rows[2], pool->buf_stage};
   for (uint64_t id : ids) {
     fj_buffer_rec* r = id ? find_buffer(be, id) : nullptr;
@@ -148,6 +154,48 @@ int32_t fj_kvpool_read_free(fj_kvpool* pool, uint32_t* pages, uint32_t cap, uint
   if (pages && n) return fj_read(pool->be, pool->buf_free, 0, pages, static_cast<uint64_t>(std::min(n, cap)) * 4);
   return FJ_OK;
 }
+int32_t fj_kvpool_read_refcounts(fj_kvpool* pool, uint32_t* refcounts) {
+  if (!pool || !refcounts) return FJ_INVALID_INPUT;
+  return fj_read(pool->be, pool->buf_refcounts, 0, refcounts, static_cast<uint64_t>(pool->dev.physical_pages) * 4);
+}
+
+// Runs one single-CTA pool kernel on `words_in` staged argument words and reads `words_out` result words back.
+static int32_t pool_control_call(fj_kvpool* pool, const uint32_t* args, unsigned words_in, int32_t* result, unsigned words_out,
+                                 const std::function<void(fj::Ctx&, const unsigned*, int*)>& launch) {
+  fj_backend* be = pool->be;
+  std::lock_guard<std::mutex> lock(be->mutex);
+  cudaSetDevice(be->device);
+  unsigned* staged = nullptr;
+  if (cudaMallocAsync(reinterpret_cast<void**>(&staged), (words_in + words_out) * 4, be->stream) != cudaSuccess) { cudaGetLastError(); return FJ_ALLOCATION_FAILED; }
+  cudaMemcpyAsync(staged, args, words_in * 4, cudaMemcpyHostToDevice, be->stream);
+  launch(be->ctx, staged, reinterpret_cast<int*>(staged + words_in));
+  cudaMemcpyAsync(result, staged + words_in, words_out * 4, cudaMemcpyDeviceToHost, be->stream);
+  cudaFreeAsync(staged, be->stream);
+  return cuda_status(cudaStreamSynchronize(be->stream));
+}
+
+int32_t fj_kvpool_fork(fj_kvpool* pool, uint32_t src_lane, uint64_t src_logical_len, uint32_t dst_lane, uint64_t prefix_tokens, uint64_t reserved_tokens) {
+  if (!pool) return FJ_INVALID_INPUT;
+  // PagedSequence::fork_reserved refuses a prefix beyond what the source has committed and a reservation below the prefix
+  if (prefix_tokens > src_logical_len || reserved_tokens < prefix_tokens || reserved_tokens > 0xFFFFFFFFull - pool->dev.page_tokens) return FJ_INVALID_INPUT;
+  const uint32_t args[4] = {src_lane, dst_lane, static_cast<uint32_t>(prefix_tokens), static_cast<uint32_t>(reserved_tokens)};
+  int32_t status = FJ_OK;
+  const int32_t call = pool_control_call(pool, args, 4, &status, 1,
+                                         [&](fj::Ctx& ctx, const unsigned* a, int* r) { fj::launch_kvpool_fork(ctx, pool->dev, a, r); });
+  return call != FJ_OK ? call : status;
+}
+
+int32_t fj_kvpool_cow_tail(fj_kvpool* pool, uint32_t lane, uint64_t logical_len, uint32_t* out4) {
+  if (!pool || !out4 || logical_len > 0xFFFFFFFFull) return FJ_INVALID_INPUT;
+  const uint32_t args[2] = {lane, static_cast<uint32_t>(logical_len)};
+  int32_t result[5] = {0, 0, 0, 0, 0};
+  const int32_t call = pool_control_call(pool, args, 2, result, 5,
+                                         [&](fj::Ctx& ctx, const unsigned* a, int* r) { fj::launch_kvpool_cow_tail(ctx, pool->dev, a, r); });
+  if (call != FJ_OK) return call;
+  for (int i = 0; i < 4; ++i) out4[i] = static_cast<uint32_t>(result[1 + i]);
+  return result[0];
+}
+
 uint64_t fj_kvpool_tables_buffer(fj_kvpool* pool) { return pool ? pool->buf_tables : 0; }
 uint64_t fj_kvpool_generations_buffer(fj_kvpool* pool) { return pool ? pool->buf_gens : 0; }
 
@@ -508,6 +556,25 @@ int32_t fj_dense_step(fj_dense_model* m, const uint32_t* token_ids, uint32_t* ou
     return cuda_status(cudaStreamSynchronize(be->stream));
   }
   return FJ_OK;
+}
+
+// The data half of cow_tail for this model's planes: the first `tokens` K and V rows of page `src_page` are copied to
+// page `dst_page` in every layer (stream-ordered device copies).
+int32_t fj_dense_copy_page(fj_dense_model* m, uint32_t src_page, uint32_t dst_page, uint32_t tokens) {
+  if (!m) return FJ_INVALID_INPUT;
+  fj_backend* be = m->be;
+  const fj::KvPoolDevice& pool = m->pool->dev;
+  if (src_page >= pool.physical_pages || dst_page >= pool.physical_pages || tokens > pool.page_tokens) return FJ_INVALID_INPUT;
+  if (tokens == 0 || src_page == dst_page) return FJ_OK;
+  std::lock_guard<std::mutex> lock(be->mutex);
+  cudaSetDevice(be->device);
+  const size_t row = static_cast<size_t>(m->cfg.kv_heads) * m->cfg.head_dim * fj::dtype_size(static_cast<int>(m->cfg.dtype));
+  const size_t from = static_cast<size_t>(src_page) * pool.page_tokens * row, to = static_cast<size_t>(dst_page) * pool.page_tokens * row;
+  for (auto& L : m->layers) {
+    cudaMemcpyAsync(static_cast<char*>(L.k_plane) + to, static_cast<const char*>(L.k_plane) + from, tokens * row, cudaMemcpyDeviceToDevice, be->stream);
+    cudaMemcpyAsync(static_cast<char*>(L.v_plane) + to, static_cast<const char*>(L.v_plane) + from, tokens * row, cudaMemcpyDeviceToDevice, be->stream);
+  }
+  return cuda_status(cudaGetLastError());
 }
 
 int32_t fj_dense_step_stats(fj_dense_model* m, uint64_t* kernels, uint64_t* attn_work_items) {

@@ -3,6 +3,10 @@
 //  * allocator: LIFO free stack with page 0 on top after initialisation, generation + 1 on every
 //    allocation and never 0xFFFFFFFF, refusals change nothing (PagePool::reserve / release /
 //    add_slab / allocate_pages, crates/forja-core/src/paged_pool.rs:204-232, 308-327, 1229-1326);
+//    prefix sharing: a page carries a reference count, a fork retains the shared prefix pages and
+//    marks them immutable for both owners, a shared tail page is replaced by a private copy before it
+//    is written (fork_reserved :949-1018, cow_tail :1025-1054), a page returns to the free stack
+//    when its last reference goes;
 //  * packer: per-lane logical_length / query_start / absolute_position / activity
 //    (write_paged_lane_metadata, crates/forja-host/src/lib.rs:4977-5065) plus cu_seqlens, per-row
 //    positions, slot_mapping (= physical page * page_tokens + offset) and row_lane.
@@ -21,10 +25,12 @@ __global__ void kvpool_init_kernel(KvPoolDevice pool) {
   for (unsigned i = threadIdx.x; i < pool.physical_pages; i += blockDim.x) {
     pool.free_stack[i] = pool.physical_pages - 1 - i;  // (start..end).rev(): page 0 pops first
     pool.generations[i] = 0;
+    pool.refcounts[i] = 0;
   }
   for (size_t i = threadIdx.x; i < static_cast<size_t>(pool.lanes) * pool.table_pages; i += blockDim.x) {
     pool.tables[2 * i] = 0;
     pool.tables[2 * i + 1] = POISON;
+    pool.immutable[i] = 0;
   }
   for (unsigned i = threadIdx.x; i < pool.lanes; i += blockDim.x) pool.lane_pages[i] = 0;
   if (threadIdx.x == 0) *pool.free_count = pool.physical_pages;
@@ -60,6 +66,8 @@ __global__ void kvpool_reserve_kernel(KvPoolDevice pool, const unsigned* __restr
           const unsigned page = pool.free_stack[s_free - 1 - j];
           const unsigned g = pool.generations[page] + 1;
           pool.generations[page] = g;
+          pool.refcounts[page] = 1;
+          pool.immutable[static_cast<size_t>(lane) * pool.table_pages + j] = 0;
           pool.tables[(static_cast<size_t>(lane) * pool.table_pages + j) * 2] = page;
           pool.tables[(static_cast<size_t>(lane) * pool.table_pages + j) * 2 + 1] = g;
         }
@@ -68,26 +76,6 @@ __global__ void kvpool_reserve_kernel(KvPoolDevice pool, const unsigned* __restr
     }
     __syncthreads();
     if (threadIdx.x == 0 && status != nullptr) status[i] = s_status;
-    __syncthreads();
-  }
-}
-
-__global__ void kvpool_release_kernel(KvPoolDevice pool, const unsigned* __restrict__ lanes, unsigned count) {
-  __shared__ unsigned s_free, s_pages;
-  for (unsigned i = 0; i < count; ++i) {
-    const unsigned lane = lanes[i];
-    if (lane >= pool.lanes) continue;
-    if (threadIdx.x == 0) { s_free = *pool.free_count; s_pages = pool.lane_pages[lane]; }
-    __syncthreads();
-    const unsigned pages = s_pages;
-    for (unsigned j = threadIdx.x; j < pages; j += blockDim.x) {
-      const size_t e = (static_cast<size_t>(lane) * pool.table_pages + j) * 2;
-      pool.free_stack[s_free + j] = pool.tables[e];  // sequence order: the last page ends on top
-      pool.tables[e] = 0;
-      pool.tables[e + 1] = POISON;
-    }
-    __syncthreads();
-    if (threadIdx.x == 0) { *pool.free_count = s_free + pages; pool.lane_pages[lane] = 0; }
     __syncthreads();
   }
 }
@@ -113,6 +101,124 @@ __device__ inline unsigned block_exclusive_scan(unsigned value, unsigned* total,
   for (int w = 0; w < warps; ++w) sum_all += warp_sums[w];
   *total = sum_all;
   return offset + inclusive - value;
+}
+
+// Drops one reference of the page in table slot `slot`; true when that was the last one.
+__device__ inline bool drop_page_reference(const KvPoolDevice& pool, unsigned page) { return atomicSub(&pool.refcounts[page], 1u) == 1u; }
+
+__global__ void kvpool_release_kernel(KvPoolDevice pool, const unsigned* __restrict__ lanes, unsigned count) {
+  __shared__ unsigned s_free, s_pages, s_total;
+  __shared__ unsigned warp_sums[32];
+  for (unsigned i = 0; i < count; ++i) {
+    const unsigned lane = lanes[i];
+    if (lane >= pool.lanes) continue;
+    if (threadIdx.x == 0) { s_free = *pool.free_count; s_pages = pool.lane_pages[lane]; }
+    __syncthreads();
+    const unsigned pages = s_pages;
+    // sequence order: the pages whose last reference goes are appended in table order (the last one ends on top)
+    for (unsigned j0 = 0; j0 < pages; j0 += blockDim.x) {
+      const unsigned j = j0 + threadIdx.x;
+      unsigned page = 0, freed = 0;
+      if (j < pages) {
+        const size_t e = static_cast<size_t>(lane) * pool.table_pages + j;
+        page = pool.tables[2 * e];
+        freed = drop_page_reference(pool, page) ? 1u : 0u;
+        pool.tables[2 * e] = 0;
+        pool.tables[2 * e + 1] = POISON;
+        pool.immutable[e] = 0;
+      }
+      const unsigned at = block_exclusive_scan(freed, &s_total, warp_sums);
+      if (freed) pool.free_stack[s_free + at] = page;
+      __syncthreads();
+      if (threadIdx.x == 0) s_free += s_total;
+      __syncthreads();
+    }
+    if (threadIdx.x == 0) { *pool.free_count = s_free; pool.lane_pages[lane] = 0; }
+    __syncthreads();
+  }
+}
+
+// fork_reserved: lane `dst` (unbound) shares the first ceil(prefix / page_tokens) pages of lane `src` and gets private pages
+// up to `reserved` tokens. Refusals change nothing. args = {src, dst, prefix_tokens, reserved_tokens}.
+__global__ void kvpool_fork_kernel(KvPoolDevice pool, const unsigned* __restrict__ args, int* status) {
+  __shared__ int s_status;
+  __shared__ unsigned s_free;
+  const unsigned src = args[0], dst = args[1], prefix = args[2], reserved = args[3];
+  const unsigned shared = prefix == 0 ? 0 : (prefix + pool.page_tokens - 1) / pool.page_tokens;
+  const unsigned total = reserved == 0 ? 0 : (reserved + pool.page_tokens - 1) / pool.page_tokens;
+  if (threadIdx.x == 0) {
+    s_free = *pool.free_count;
+    int st = 0;
+    if (src >= pool.lanes || dst >= pool.lanes || src == dst || reserved < prefix || total > pool.table_pages || pool.lane_pages[dst] != 0 || shared > pool.lane_pages[src]) st = 7;
+    else if (total - shared > s_free) st = 1;
+    s_status = st;
+  }
+  __syncthreads();
+  if (s_status == 0) {
+    const unsigned fresh = total - shared;
+    int overflow = 0;
+    for (unsigned j = threadIdx.x; j < fresh; j += blockDim.x)
+      if (pool.generations[pool.free_stack[s_free - 1 - j]] >= POISON - 1) overflow = 1;
+    for (unsigned j = threadIdx.x; j < shared; j += blockDim.x)
+      if (pool.refcounts[pool.tables[(static_cast<size_t>(src) * pool.table_pages + j) * 2]] == 0xFFFFFFFFu) overflow = 1;
+    overflow = __syncthreads_or(overflow);
+    if (overflow) {
+      if (threadIdx.x == 0) s_status = 3;
+    } else {
+      for (unsigned j = threadIdx.x; j < total; j += blockDim.x) {
+        const size_t d = static_cast<size_t>(dst) * pool.table_pages + j;
+        if (j < shared) {
+          const size_t e = static_cast<size_t>(src) * pool.table_pages + j;
+          atomicAdd(&pool.refcounts[pool.tables[2 * e]], 1u);
+          pool.tables[2 * d] = pool.tables[2 * e];
+          pool.tables[2 * d + 1] = pool.tables[2 * e + 1];
+          pool.immutable[e] = 1;
+          pool.immutable[d] = 1;
+        } else {
+          const unsigned page = pool.free_stack[s_free - 1 - (j - shared)];
+          const unsigned g = pool.generations[page] + 1;
+          pool.generations[page] = g;
+          pool.refcounts[page] = 1;
+          pool.tables[2 * d] = page;
+          pool.tables[2 * d + 1] = g;
+          pool.immutable[d] = 0;
+        }
+      }
+      if (threadIdx.x == 0) { *pool.free_count = s_free - fresh; pool.lane_pages[dst] = total; }
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) *status = s_status;
+}
+
+// cow_tail: when the page that holds token logical_len - 1 of `lane` is shared (immutable for this lane or referenced by
+// another), a fresh page takes its place in the lane's table and the old reference is dropped; the caller then copies
+// `tokens` rows from page `src` to page `dst`. result = {status, copied, src, dst, tokens}. args = {lane, logical_len}.
+__global__ void kvpool_cow_tail_kernel(KvPoolDevice pool, const unsigned* __restrict__ args, int* result) {
+  if (threadIdx.x != 0) return;
+  const unsigned lane = args[0], length = args[1];
+  result[0] = 0; result[1] = 0; result[2] = 0; result[3] = 0; result[4] = 0;
+  if (lane >= pool.lanes) { result[0] = 7; return; }
+  if (length == 0 || length % pool.page_tokens == 0) return;
+  const unsigned tail = (length - 1) / pool.page_tokens;
+  if (tail >= pool.lane_pages[lane]) { result[0] = 7; return; }
+  const size_t e = static_cast<size_t>(lane) * pool.table_pages + tail;
+  const unsigned old = pool.tables[2 * e];
+  if (pool.immutable[e] == 0 && pool.refcounts[old] == 1) return;
+  unsigned free_count = *pool.free_count;
+  if (free_count == 0) { result[0] = 1; return; }
+  const unsigned fresh = pool.free_stack[free_count - 1];
+  if (pool.generations[fresh] >= POISON - 1) { result[0] = 3; return; }
+  --free_count;
+  const unsigned g = pool.generations[fresh] + 1;
+  pool.generations[fresh] = g;
+  pool.refcounts[fresh] = 1;
+  pool.tables[2 * e] = fresh;
+  pool.tables[2 * e + 1] = g;
+  pool.immutable[e] = 0;
+  if (--pool.refcounts[old] == 0) pool.free_stack[free_count++] = old;
+  *pool.free_count = free_count;
+  result[1] = 1; result[2] = static_cast<int>(old); result[3] = static_cast<int>(fresh); result[4] = static_cast<int>(length % pool.page_tokens);
 }
 
 __global__ void pack_step_kernel(KvPoolDevice pool, const unsigned* __restrict__ starts, const unsigned* __restrict__ tokens,
@@ -218,6 +324,14 @@ void launch_kvpool_reserve(Ctx& ctx, const KvPoolDevice& pool, const unsigned* l
 void launch_kvpool_release(Ctx& ctx, const KvPoolDevice& pool, const unsigned* lanes, unsigned count) {
   if (count == 0) return;
   kvpool_release_kernel<<<1, 256, 0, ctx.stream>>>(pool, lanes, count);
+  ctx.launches++;
+}
+void launch_kvpool_fork(Ctx& ctx, const KvPoolDevice& pool, const unsigned* args, int* status) {
+  kvpool_fork_kernel<<<1, 256, 0, ctx.stream>>>(pool, args, status);
+  ctx.launches++;
+}
+void launch_kvpool_cow_tail(Ctx& ctx, const KvPoolDevice& pool, const unsigned* args, int* result) {
+  kvpool_cow_tail_kernel<<<1, 32, 0, ctx.stream>>>(pool, args, result);
   ctx.launches++;
 }
 void launch_pack_step(Ctx& ctx, const KvPoolDevice& pool, const unsigned* starts, const unsigned* tokens, unsigned lanes,

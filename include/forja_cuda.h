@@ -207,6 +207,16 @@ int32_t fj_kvpool_release(fj_kvpool* pool, const uint32_t* lanes, uint32_t count
 int32_t fj_kvpool_read_table(fj_kvpool* pool, uint32_t lane, uint32_t* entries);
 int32_t fj_kvpool_read_generations(fj_kvpool* pool, uint32_t* generations);
 int32_t fj_kvpool_read_free(fj_kvpool* pool, uint32_t* pages, uint32_t cap, uint32_t* count);
+int32_t fj_kvpool_read_refcounts(fj_kvpool* pool, uint32_t* refcounts); /* [physical_pages]: owners of each page, 0 = free */
+/* Prefix sharing (PagedSequence::fork_reserved / cow_tail, crates/forja-core/src/paged_pool.rs:949-1054).
+ * fork: the unbound lane dst shares the first ceil(prefix_tokens / page_tokens) pages of src (reference counts + 1, the
+ * pages become immutable for both) and gets private pages up to reserved_tokens; src_logical_len = tokens src has
+ * committed. Returns FJ_OK, FJ_QUOTA_EXCEEDED (not enough free pages; nothing changed) or FJ_INVALID_INPUT.
+ * cow_tail: before a lane writes at logical_len, a shared page holding token logical_len - 1 is replaced in its table by
+ * a fresh private page; out4 = {copied (0/1), source page, destination page, rows to copy}; the caller copies the rows
+ * (fj_dense_copy_page). Both calls are synchronous control-path calls. */
+int32_t fj_kvpool_fork(fj_kvpool* pool, uint32_t src_lane, uint64_t src_logical_len, uint32_t dst_lane, uint64_t prefix_tokens, uint64_t reserved_tokens);
+int32_t fj_kvpool_cow_tail(fj_kvpool* pool, uint32_t lane, uint64_t logical_len, uint32_t* out4);
 uint64_t fj_kvpool_tables_buffer(fj_kvpool* pool);      /* buffer id: [lanes, table_pages, 2] u32 */
 uint64_t fj_kvpool_generations_buffer(fj_kvpool* pool); /* buffer id: [physical_pages] u32 */
 
@@ -296,6 +306,8 @@ void fj_dense_model_destroy(fj_dense_model* model);
  * returns after the step completed when out_tokens != NULL, else it only enqueues. */
 int32_t fj_dense_step(fj_dense_model* model, const uint32_t* token_ids, uint32_t* out_tokens, uint64_t logits_out);
 /* Launch count of the last step and the number of split-K work items of its attention launches. */
+/* Copies the first `tokens` K/V rows of page src_page to page dst_page in every layer (the data half of cow_tail). */
+int32_t fj_dense_copy_page(fj_dense_model* model, uint32_t src_page, uint32_t dst_page, uint32_t tokens);
 int32_t fj_dense_step_stats(fj_dense_model* model, uint64_t* kernels, uint64_t* attn_work_items);
 /* Fills every K/V plane of the model with seeded pseudo-random N(0, 1) values in the plane dtype
  * (synthetic contexts for benchmarks: any page a lane is given already holds finite random rows). */

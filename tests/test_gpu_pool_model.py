@@ -191,3 +191,134 @@ def test_smollm2_135m_f32_prompts_and_32_greedy_steps():
     prompts {7, 33, 128, 300}, then 32 greedy steps: logits within f32 rel 1e-4, identical tokens."""
     history, _ = run_generation(SMOLLM2, [7, 33, 128, 300], steps=32, logits_tol=1e-4)
     assert len(history) == 33
+
+
+def test_prefix_sharing_on_the_device_pool_is_bit_exact_against_the_host_pool():
+    """Random reserve / commit / fork / copy-on-write / release traffic: tables, generations, reference
+    counts, free-stack order, copy instructions and refusals equal PagePool / PagedSequence
+    (fork_reserved, cow_tail: crates/forja-core/src/paged_pool.rs:949-1054)."""
+    rng = np.random.default_rng(3)
+    be = backend()
+    page, physical, lanes, table_pages = 16, 64, 10, 12
+    dev = fb.KvPool(be, page, physical, lanes, table_pages)
+    ref = fjo.Pool(page, 64, physical, 1 << 40, fixed=True)
+    seqs, lengths = {}, {}
+    forks = copies = refused = 0
+
+    def check():
+        assert dev.free_list().tolist() == ref.free_list().tolist()
+        assert dev.generations().tolist() == ref.generations().tolist()
+        counts = dev.refcounts()
+        live = set()
+        for lane, seq in seqs.items():
+            want = seq.table()
+            got = dev.table(lane)
+            assert np.array_equal(got[:len(want)], want), f"lane {lane}"
+            assert np.all(got[len(want):, 1] == POISON)
+            assert counts[want[:, 0]].tolist() == seq.refcounts().tolist()
+            live.update(want[:, 0].tolist())
+        assert all(counts[p] == 0 for p in range(physical) if p not in live)
+
+    for step in range(400):
+        lane = int(rng.integers(0, lanes))
+        action = rng.random()
+        if lane not in seqs:
+            donors = [l for l in seqs if lengths[l] > 0]
+            if donors and action < 0.6:
+                src = donors[int(rng.integers(0, len(donors)))]
+                prefix = int(rng.integers(1, lengths[src] + 1))
+                reserved = min(prefix + int(rng.integers(0, 60)), table_pages * page)
+                status = dev.fork(src, lengths[src], lane, prefix, reserved)
+                try:
+                    seqs[lane] = seqs[src].fork_reserved(prefix, reserved)
+                    lengths[lane] = prefix
+                    assert status == fb.backend.OK
+                    forks += 1
+                except fjo.OracleError as e:
+                    assert e.status == fjo.QUOTA_EXCEEDED and status == fb.backend.QUOTA_EXCEEDED
+                    refused += 1
+            else:
+                tokens = int(rng.integers(1, table_pages * page))
+                status = dev.reserve([lane], [tokens])[0]
+                try:
+                    seqs[lane] = ref.reserve(tokens)
+                    assert status == fb.backend.OK
+                    lengths[lane] = int(rng.integers(0, tokens + 1))
+                    assert seqs[lane].commit_write(lengths[lane]) == 0
+                except fjo.OracleError as e:
+                    assert e.status == fjo.QUOTA_EXCEEDED and status == fb.backend.QUOTA_EXCEEDED
+                    refused += 1
+        elif action < 0.35:
+            dev.release([lane])
+            seqs.pop(lane).drop()
+            lengths.pop(lane)
+        else:
+            status, copied, src_page, dst_page, rows = dev.cow_tail(lane, lengths[lane])
+            try:
+                want = seqs[lane].cow_tail()
+                assert status == fb.backend.OK
+                assert (want is None and not copied) or want == (src_page, dst_page, rows)
+                copies += int(copied)
+                # a private tail may now take more tokens
+                room = seqs[lane].reserved_tokens - lengths[lane]
+                grow = int(rng.integers(0, min(room, 20) + 1))
+                if grow and seqs[lane].commit_write(grow) == 0:
+                    lengths[lane] += grow
+            except fjo.OracleError as e:
+                assert e.status == fjo.QUOTA_EXCEEDED and status == fb.backend.QUOTA_EXCEEDED
+                refused += 1
+        check()
+    assert forks > 20 and copies > 10
+    # refusals that the host entry point makes itself
+    assert dev.fork(0, 5, 1, 6, 10) == fb.backend.INVALID_INPUT  # prefix beyond the committed length
+    assert dev.fork(0, 5, 1, 4, 3) == fb.backend.INVALID_INPUT   # reservation below the prefix
+    for seq in seqs.values():
+        seq.drop()
+    dev.close()
+
+
+def test_forked_lane_decodes_like_a_lane_that_prefilled_the_prompt_itself():
+    """Lane 1 shares lane 0's prompt pages, gets a private copy of the partly filled tail page, and both lanes then decode
+    different tokens: every logit row must equal the oracle's, for which both lanes simply hold the same prompt."""
+    cfg, page, steps = TINY_F32, 16, 3
+    rng = np.random.default_rng(4)
+    be = backend()
+    prompt = 37  # two full pages and five rows of the third
+    pool = fb.KvPool(be, page, 12, 2, 4)
+    assert pool.reserve([0], [prompt + steps]) == [0]
+    weights = engine.random_dense_weights(cfg, 1)
+    model = build_model(cfg, weights, pool)
+    ref = engine.DenseOracle(cfg, weights, 12, page)
+    ids = rng.integers(0, cfg["vocab"], prompt).astype(np.uint32)
+    logits = be.alloc(cfg["dtype"], (2, cfg["vocab"]))
+    pool.pack_step([0, 0], [prompt, 0])
+    model.step(ids, lanes=2, logits=logits, want_tokens=False)
+    assert pool.fork(0, prompt, 1, prompt, prompt + steps) == fb.backend.OK
+    assert pool.refcounts()[pool.table(0)[:3, 0]].tolist() == [2, 2, 2]
+    # both lanes are about to write row 37: each needs the tail page for itself
+    for lane in (0, 1):
+        status, copied, src, dst, rows = pool.cow_tail(lane, prompt)
+        assert status == fb.backend.OK
+        if copied:
+            assert rows == prompt % page
+            model.copy_page(src, dst, rows)
+    tables = [pool.table(0), pool.table(1)]
+    assert tables[0][2, 0] != tables[1][2, 0] and np.array_equal(tables[0][:2], tables[1][:2])
+    generations = pool.generations()
+    fjo.set_threads(fjo.max_threads())
+    for lane in (0, 1):
+        ref.forward_lane(ids, 0, tables[lane], generations)
+    position = prompt
+    for step in range(steps):
+        feed = rng.integers(0, cfg["vocab"], 2).astype(np.uint32)
+        pool.pack_step([position, position], [1, 1])
+        model.step(feed, lanes=2, logits=logits, want_tokens=False)
+        got = down(logits)
+        for lane in (0, 1):
+            want, _ = ref.forward_lane([int(feed[lane])], position, tables[lane], generations)
+            err = max_abs_rel(got[lane], want)
+            assert err <= 1e-4, f"step {step} lane {lane}: {err:.3e}"
+        position += 1
+    fjo.set_threads(1)
+    model.close()
+    pool.close()
