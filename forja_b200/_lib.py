@@ -54,7 +54,7 @@ class FjQuantWeight(C.Structure):
 
 class FjMoeConfig(C.Structure):
     _fields_ = [(n, C.c_uint32) for n in ("layers", "hidden", "q_heads", "kv_heads", "head_dim", "experts", "top_k", "expert_intermediate", "vocab",
-                                          "group_size", "router_bits")] + [("eps", C.c_float), ("theta", C.c_float), ("max_rows", C.c_uint32), ("grouped_min_routes", C.c_uint32), ("stream_rows_per_expert", C.c_uint32)]
+                                          "group_size", "router_bits")] + [("eps", C.c_float), ("theta", C.c_float), ("max_rows", C.c_uint32), ("grouped_min_routes", C.c_uint32), ("stream_rows_per_expert", C.c_uint32), ("ep_return_bf16", C.c_uint32)]
 
 
 class FjMoeLayerWeights(C.Structure):

@@ -131,6 +131,7 @@ def run_moe(args):
     cfg["max_rows"] = lanes + (0 if args.decode_only else args.prompt_budget)
     cfg["grouped_min_routes"] = args.grouped_min_routes
     cfg["stream_rows_per_expert"] = args.stream_rows_per_expert
+    cfg["ep_return_bf16"] = int(args.ep_bf16_return)
     be = fb.CudaBackend(local_rank)
     ep = None
     if world > 1:
@@ -191,7 +192,7 @@ def run_moe(args):
             "config": {"workload": "qwen3-30b-a3b-arch q4 sparse-MoE continuous batching" + (" (decode only)" if args.decode_only else " (chunked prefill + decode)"),
                        "lanes_total": args.lanes, "lanes_per_gpu": lanes, "layers": cfg["layers"], "prompt_tokens": [args.prompt_min, args.prompt_max],
                        "prompt_budget_per_gpu_step": 0 if args.decode_only else args.prompt_budget,
-                       "parallelism": "experts sharded over %d GPUs, NCCL send/recv all-to-all per MoE layer; lanes data-parallel" % world if world > 1 else "single GPU"}}))
+                       "parallelism": ("experts sharded over %d GPUs, NCCL send/recv all-to-all per MoE layer (rows return as %s); lanes data-parallel" % (world, "bf16" if args.ep_bf16_return else "f32")) if world > 1 else "single GPU"}}))
     model.close()
     pool.close()
     if ep is not None:
@@ -334,6 +335,7 @@ def main():
     moe.add_argument("--prompt-budget", type=int, default=2048)
     moe.add_argument("--prefill-limit", type=int, default=4)
     moe.add_argument("--decode-only", action="store_true")
+    moe.add_argument("--ep-bf16-return", action="store_true", help="expert parallelism: per-route rows come back as bf16 instead of f32")
     moe.add_argument("--phases", action="store_true", help="also print the time of the timed steps split by phase (CUDA events inside the step)")
     moe.add_argument("--grouped-min-routes", type=int, default=0, help="0 = library default")
     moe.add_argument("--stream-rows-per-expert", type=int, default=0, help="0 = library default")

@@ -635,7 +635,7 @@ int32_t exec_gather_quant(Exec& x, const fj_dispatch& d, fj::ErrorRecord* err) {
         if (!fj::launch_expert_stream_single(x.be->ctx, ap, static_cast<const unsigned*>(pp), sp, bp, plan, static_cast<unsigned>(total), experts, 1, per_route, false, k, n))
           return FJ_DEVICE_EXECUTION_FAILED;
       } else fj::launch_grouped_q4_single(x.be->ctx, ap, static_cast<const unsigned*>(pp), sp, bp, plan, static_cast<unsigned>(total), experts, 1, per_route, false, k, n, tile_rows);
-      fj::launch_routes_combine(x.be->ctx, per_route, nullptr, static_cast<const unsigned*>(ip), experts, wp, wt.dtype, ex, epilogue == 2 ? d.inputs[6].dtype : 0, out,
+      fj::launch_routes_combine(x.be->ctx, per_route, FJ_F32, nullptr, static_cast<const unsigned*>(ip), experts, wp, wt.dtype, ex, epilogue == 2 ? d.inputs[6].dtype : 0, out,
                                 d.outputs[0].dtype, rows, routes, n);
       return FJ_OK;
     }

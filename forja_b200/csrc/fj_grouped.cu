@@ -523,12 +523,14 @@ namespace {
 // out[row] = (extra[row] +) sum_j weights[row, j] * per_route[slot(row, j)], j ascending, f32, each product rounded
 // before it is added: the arithmetic of the fused weighted-sum projection (lib.rs:1153-1199). route_slot == nullptr:
 // the result of route r sits in row r and routes whose expert id is out of range are skipped.
-__global__ void routes_combine_kernel(const float* __restrict__ per_route, const unsigned* __restrict__ route_slot, const unsigned* __restrict__ expert_ids, unsigned experts,
+__global__ void routes_combine_kernel(const void* __restrict__ per_route_any, int p_dt, const unsigned* __restrict__ route_slot, const unsigned* __restrict__ expert_ids, unsigned experts,
                                       const void* __restrict__ weights, int w_dt, const void* __restrict__ extra, int e_dt, void* out, int out_dt, unsigned rows, unsigned top_k,
                                       unsigned width) {
   pdl_sync();
-  // four columns per thread (16-byte loads of the per-route rows) when the row width and the pointer allow it
-  const bool wide = width % 4 == 0 && reinterpret_cast<size_t>(per_route) % 16 == 0;
+  // four columns per thread (16-byte loads of f32 per-route rows, 8-byte loads of bf16 ones) when the row width and the pointer allow it
+  const float* per_route = static_cast<const float*>(per_route_any);
+  const unsigned short* per_route_h = static_cast<const unsigned short*>(per_route_any);
+  const bool wide = width % 4 == 0 && reinterpret_cast<size_t>(per_route_any) % 16 == 0 && (p_dt == F32 || p_dt == BF16);
   for (unsigned row = blockIdx.x; row < rows; row += gridDim.x) {
     if (wide) {
       for (unsigned c = (blockIdx.y * blockDim.x + threadIdx.x) * 4; c < width; c += gridDim.y * blockDim.x * 4) {
@@ -537,7 +539,13 @@ __global__ void routes_combine_kernel(const float* __restrict__ per_route, const
           const unsigned slot = route_slot ? route_slot[row * top_k + j] : (expert_ids[row * top_k + j] < experts ? row * top_k + j : 0xFFFFFFFFu);
           if (slot == 0xFFFFFFFFu) continue;
           const float w = load_as_f32(weights, w_dt, row * top_k + j);
-          const float4 v = *reinterpret_cast<const float4*>(per_route + static_cast<size_t>(slot) * width + c);
+          float4 v;
+          if (p_dt == F32) {
+            v = *reinterpret_cast<const float4*>(per_route + static_cast<size_t>(slot) * width + c);
+          } else {
+            const uint2 h = *reinterpret_cast<const uint2*>(per_route_h + static_cast<size_t>(slot) * width + c);
+            v = make_float4(__uint_as_float(h.x << 16), __uint_as_float(h.x & 0xFFFF0000u), __uint_as_float(h.y << 16), __uint_as_float(h.y & 0xFFFF0000u));
+          }
           total[0] = __fadd_rn(total[0], __fmul_rn(w, v.x));
           total[1] = __fadd_rn(total[1], __fmul_rn(w, v.y));
           total[2] = __fadd_rn(total[2], __fmul_rn(w, v.z));
@@ -557,7 +565,7 @@ __global__ void routes_combine_kernel(const float* __restrict__ per_route, const
       for (unsigned j = 0; j < top_k; ++j) {
         const unsigned slot = route_slot ? route_slot[row * top_k + j] : (expert_ids[row * top_k + j] < experts ? row * top_k + j : 0xFFFFFFFFu);
         if (slot == 0xFFFFFFFFu) continue;
-        total = __fadd_rn(total, __fmul_rn(load_as_f32(weights, w_dt, row * top_k + j), per_route[static_cast<size_t>(slot) * width + c]));
+        total = __fadd_rn(total, __fmul_rn(load_as_f32(weights, w_dt, row * top_k + j), load_as_f32(per_route_any, p_dt, static_cast<size_t>(slot) * width + c)));
       }
       const size_t o = static_cast<size_t>(row) * width + c;
       if (extra) total = total + load_as_f32(extra, e_dt, o);
@@ -567,12 +575,12 @@ __global__ void routes_combine_kernel(const float* __restrict__ per_route, const
 }
 }  // namespace
 
-void launch_routes_combine(Ctx& ctx, const float* per_route, const unsigned* route_slot, const unsigned* expert_ids, unsigned experts, const void* weights, int w_dt, const void* extra,
+void launch_routes_combine(Ctx& ctx, const void* per_route, int p_dt, const unsigned* route_slot, const unsigned* expert_ids, unsigned experts, const void* weights, int w_dt, const void* extra,
                            int e_dt, void* out, int out_dt, unsigned rows, unsigned top_k, unsigned width) {
   if (rows == 0) return;
   // few rows: spread the columns of a row over several CTAs so that the grid still fills the GPU
   const unsigned col_ctas = rows >= 1024u ? 1u : std::min((width + 1023u) / 1024u, (1024u + rows - 1) / rows);
-  launch_pdl(routes_combine_kernel, dim3(rows < 1024u ? rows : 1024u, col_ctas), dim3(256), 0, ctx.stream, per_route, route_slot, expert_ids, experts, weights, w_dt, extra, e_dt, out, out_dt, rows,
+  launch_pdl(routes_combine_kernel, dim3(rows < 1024u ? rows : 1024u, col_ctas), dim3(256), 0, ctx.stream, per_route, p_dt, route_slot, expert_ids, experts, weights, w_dt, extra, e_dt, out, out_dt, rows,
              top_k, width);
   ctx.launches++;
 }

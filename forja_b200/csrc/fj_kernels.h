@@ -182,8 +182,9 @@ bool launch_expert_stream_pair(Ctx& ctx, const void* x, const unsigned* gate, co
                                unsigned live_routes = 0xFFFFFFFFu);
 bool launch_expert_stream_single(Ctx& ctx, const void* x, const unsigned* packed, const void* scales, const void* biases, const void* plan, unsigned total_routes, unsigned experts,
                                  unsigned src_div, void* out, bool out_bf16, unsigned k, unsigned n, unsigned live_routes = 0xFFFFFFFFu);
-// out[row] = (extra[row] +) sum_j weights[row, j] * per_route[slot], j ascending (slot = route_slot[row, j], or the route itself).
-void launch_routes_combine(Ctx& ctx, const float* per_route, const unsigned* route_slot, const unsigned* expert_ids, unsigned experts, const void* weights, int w_dt, const void* extra,
+// out[row] = (extra[row] +) sum_j weights[row, j] * per_route[slot], j ascending (slot = route_slot[row, j], or the route itself);
+// per_route rows are f32 or bf16 (p_dt).
+void launch_routes_combine(Ctx& ctx, const void* per_route, int p_dt, const unsigned* route_slot, const unsigned* expert_ids, unsigned experts, const void* weights, int w_dt, const void* extra,
                            int e_dt, void* out, int out_dt, unsigned rows, unsigned top_k, unsigned width);
 
 // ---- fj_pack.cu -----------------------------------------------------------------------------

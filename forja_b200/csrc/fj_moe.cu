@@ -618,7 +618,7 @@ extern "C" int32_t fj_moe_step(fj_moe_model* m, const uint32_t* token_ids, uint3
     const unsigned kGroupedRoutes = c.grouped_min_routes ? c.grouped_min_routes : 64;
     const unsigned kStreamRows = c.stream_rows_per_expert ? c.stream_rows_per_expert : 24;
     // `live`: how many of the n_routes ids are expected to be valid (a padded exchange carries whole slabs)
-    auto bucketed = [&](const void* x, unsigned src_div, const unsigned* ids, unsigned n_routes, unsigned live, unsigned n_experts, void* act, float* down_out) -> bool {
+    auto bucketed = [&](const void* x, unsigned src_div, const unsigned* ids, unsigned n_routes, unsigned live, unsigned n_experts, void* act, void* down_out, bool down_bf16) -> bool {
       if (live < kGroupedRoutes || G != 64) return false;
       const bool stream = live < static_cast<uint64_t>(kStreamRows) * n_experts &&
                           fj::expert_stream_supported(H, I, 4, G, n_experts, x, L.gate.packed, L.gate.scales, L.gate.biases) &&
@@ -628,7 +628,7 @@ extern "C" int32_t fj_moe_step(fj_moe_model* m, const uint32_t* token_ids, uint3
         fj::launch_route_plan(ctx, ids, n_routes, n_experts, m->route_plan, nullptr, 16);
         if (!fj::launch_expert_stream_pair(ctx, x, L.gate.packed, L.gate.scales, L.gate.biases, L.up.packed, L.up.scales, L.up.biases, m->route_plan, n_routes, n_experts, src_div, act, H,
                                            I, live) ||
-            !fj::launch_expert_stream_single(ctx, act, L.down.packed, L.down.scales, L.down.biases, m->route_plan, n_routes, n_experts, 1, down_out, false, I, H, live))
+            !fj::launch_expert_stream_single(ctx, act, L.down.packed, L.down.scales, L.down.biases, m->route_plan, n_routes, n_experts, 1, down_out, down_bf16, I, H, live))
           status = FJ_DEVICE_EXECUTION_FAILED;
         return true;
       }
@@ -637,16 +637,16 @@ extern "C" int32_t fj_moe_step(fj_moe_model* m, const uint32_t* token_ids, uint3
       fj::launch_route_plan(ctx, ids, n_routes, n_experts, m->route_plan, nullptr, tile_rows);
       fj::launch_grouped_q4_pair(ctx, x, L.gate.packed, L.gate.scales, L.gate.biases, L.up.packed, L.up.scales, L.up.biases, m->route_plan, n_routes, n_experts, src_div, act, H, I,
                                  tile_rows);
-      fj::launch_grouped_q4_single(ctx, act, L.down.packed, L.down.scales, L.down.biases, m->route_plan, n_routes, n_experts, 1, down_out, false, I, H, tile_rows);
+      fj::launch_grouped_q4_single(ctx, act, L.down.packed, L.down.scales, L.down.biases, m->route_plan, n_routes, n_experts, 1, down_out, down_bf16, I, H, tile_rows);
       return true;
     };
     mark(1);
     if (m->world == 1) {
       const unsigned routes = rows * K;
       mark(2);
-      if (bucketed(m->normed, K, m->route_experts, routes, routes, c.experts, m->act, m->down_routes)) {
+      if (bucketed(m->normed, K, m->route_experts, routes, routes, c.experts, m->act, m->down_routes, false)) {
         mark(3);
-        fj::launch_routes_combine(ctx, m->down_routes, nullptr, m->route_experts, c.experts, m->route_weights, FJ_F32, hidden, dt, other, dt, rows, K, H);
+        fj::launch_routes_combine(ctx, m->down_routes, FJ_F32, nullptr, m->route_experts, c.experts, m->route_weights, FJ_F32, hidden, dt, other, dt, rows, K, H);
       } else {
         fj::launch_gather_quant_matmul(ctx, m->normed, dt, L.gate.packed, L.gate.scales, L.gate.biases, dt, L.up.packed, L.up.scales, L.up.biases, m->route_experts, m->act, dt, rows, H,
                                        c.experts, I, K, 4, G, 1, nullptr);
@@ -655,6 +655,9 @@ extern "C" int32_t fj_moe_step(fj_moe_model* m, const uint32_t* token_ids, uint3
       }
     } else {
       const unsigned cap = m->capacity, routes = rows * K, W = m->world;
+      // rows come back from the experts' owners as f32 (bit-identical to one GPU) or, on request, rounded to bf16 (half the bytes)
+      const bool ret_bf16 = c.ep_return_bf16 != 0;
+      const int ret_dt = ret_bf16 ? FJ_BF16 : FJ_F32;
       // Small steps (decode): whole slabs of `cap` slots travel, padded with an out-of-range expert id, and
       // nothing has to come back to the host. Large steps: the row counts are exchanged and read back first
       // so that only live rows travel. The choice depends on the model's capacity only, so all ranks agree.
@@ -689,19 +692,19 @@ extern "C" int32_t fj_moe_step(fj_moe_model* m, const uint32_t* token_ids, uint3
       mark(2);
       if (received) {
         // rows received for this rank's experts, densely packed by source: one route each
-        if (!bucketed(m->recv_rows, 1, m->recv_experts, received, padded ? cap : received, m->experts_local, m->act_ep, m->down_ep)) {
+        if (!bucketed(m->recv_rows, 1, m->recv_experts, received, padded ? cap : received, m->experts_local, m->act_ep, m->down_ep, ret_bf16)) {
           fj::launch_gather_quant_matmul(ctx, m->recv_rows, dt, L.gate.packed, L.gate.scales, L.gate.biases, dt, L.up.packed, L.up.scales, L.up.biases, m->recv_experts, m->act_ep, dt,
                                          received, H, m->experts_local, I, 1, 4, G, 1, nullptr);
-          fj::launch_gather_quant_matmul(ctx, m->act_ep, dt, L.down.packed, L.down.scales, L.down.biases, dt, nullptr, nullptr, nullptr, m->recv_experts, m->down_ep, FJ_F32, received, I,
+          fj::launch_gather_quant_matmul(ctx, m->act_ep, dt, L.down.packed, L.down.scales, L.down.biases, dt, nullptr, nullptr, nullptr, m->recv_experts, m->down_ep, ret_dt, received, I,
                                          m->experts_local, H, 1, 4, G, 0, nullptr);
         }
       }
       if (status != FJ_OK) break;
       mark(3);
-      status = ep_all_to_all_rows(m->ep, m->down_ep, packed_at.data(), recv_counts, m->returned, slab_at.data(), send_counts, static_cast<size_t>(H) * 4);
+      status = ep_all_to_all_rows(m->ep, m->down_ep, packed_at.data(), recv_counts, m->returned, slab_at.data(), send_counts, static_cast<size_t>(H) * (ret_bf16 ? 2 : 4));
       if (status != FJ_OK) break;
       if (rows) {
-        fj::launch_routes_combine(ctx, m->returned, m->route_slot, nullptr, 0, m->route_weights, FJ_F32, hidden, dt, other, dt, rows, K, H);
+        fj::launch_routes_combine(ctx, m->returned, ret_dt, m->route_slot, nullptr, 0, m->route_weights, FJ_F32, hidden, dt, other, dt, rows, K, H);
       }
     }
     mark(4);

@@ -399,6 +399,9 @@ typedef struct fj_moe_config {
    * * experts (0 = 24), and as 64-row tile GEMMs (weights rounded to bf16) from there on. */
   uint32_t grouped_min_routes;
   uint32_t stream_rows_per_expert;
+  /* Expert parallelism only: nonzero = the experts' owners return their per-route rows rounded to bf16 instead of f32.
+   * Halves the larger of the two exchanges; the logits then agree with one GPU within the bf16 tolerance instead of bit for bit. */
+  uint32_t ep_return_bf16;
 } fj_moe_config;
 typedef struct fj_moe_layer_weights {
   uint64_t input_norm, q_norm, k_norm, post_norm; /* bf16 [hidden], [head_dim], [head_dim], [hidden] */

@@ -48,13 +48,15 @@ def main():
 
     for max_rows in (64, 300):  # slab capacity 256 (padded exchange, no host round trip) and 1200 (row counts exchanged first)
         run_case(be, ep, rank, dict(CFG, max_rows=max_rows), weights, local, prompts, steps, page, lanes, table_pages, physical, ids)
+    # rows returned as bf16: half the bytes on the way back, logits within the bf16 bound instead of bit-identical
+    run_case(be, ep, rank, dict(CFG, max_rows=300, ep_return_bf16=1), weights, local, prompts, steps, page, lanes, table_pages, physical, ids, exact=False)
     dist.barrier()
     ep.close()
     dist.destroy_process_group()
     print("EP_OK", rank)
 
 
-def run_case(be, ep, rank, cfg, weights, local, prompts, steps, page, lanes, table_pages, physical, ids):
+def run_case(be, ep, rank, cfg, weights, local, prompts, steps, page, lanes, table_pages, physical, ids, exact=True):
     def build(w, group):
         pool = fb.KvPool(be, page, physical, lanes, table_pages)
         assert all(s == 0 for s in pool.reserve(list(range(lanes)), [n + steps + 1 for n in prompts]))
@@ -71,9 +73,14 @@ def run_case(be, ep, rank, cfg, weights, local, prompts, steps, page, lanes, tab
         pool_one.pack_step(starts, counts)
         want = model_one.step(tokens, lanes=lanes, logits=logits_one)
         a, b = be.read(logits_ep), be.read(logits_one)
-        assert np.array_equal(a, b), f"rank {rank}: expert-parallel logits differ from the single-GPU path"
-        assert got.tolist() == want.tolist()
-        return got
+        if exact:
+            assert np.array_equal(a, b), f"rank {rank}: expert-parallel logits differ from the single-GPU path"
+            assert got.tolist() == want.tolist()
+        else:
+            fa, fb_ = (a.astype(np.uint32) << 16).view(np.float32), (b.astype(np.uint32) << 16).view(np.float32)
+            err = float(np.max(np.abs(fa - fb_)) / np.max(np.abs(fb_)))
+            assert err <= 2e-2, f"rank {rank}: bf16-return logits off by {err:.3e} (max-abs rel)"
+        return want
 
     tokens = both([0] * lanes, prompts, np.concatenate(ids))
     positions = list(prompts)
