@@ -117,6 +117,10 @@ class MoeLanes:
 
 
 def run_moe(args):
+    """With --micro-batches R > 1 every GPU runs R independent half-size (1/R) continuous batches, each on its own
+    backend (stream), pool, model and expert-parallel group and stepped by its own host thread, so that one batch's
+    exchange with the experts' owners overlaps the other batch's attention and expert work."""
+    import threading
     rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
     local_rank = int(os.environ.get("LOCAL_RANK", 0))
     dist = None
@@ -127,54 +131,80 @@ def run_moe(args):
     cfg = dict(MOE)
     if args.layers:
         cfg["layers"] = args.layers
-    lanes = args.lanes // world
-    cfg["max_rows"] = lanes + (0 if args.decode_only else args.prompt_budget)
+    R = max(1, args.micro_batches)
+    lanes = args.lanes // world // R
+    budget = args.prompt_budget // R
+    cfg["max_rows"] = lanes + (0 if args.decode_only else budget)
     cfg["grouped_min_routes"] = args.grouped_min_routes
     cfg["stream_rows_per_expert"] = args.stream_rows_per_expert
     cfg["ep_return_bf16"] = int(args.ep_bf16_return)
-    be = fb.CudaBackend(local_rank)
-    ep = None
-    if world > 1:
-        def exchange(mine):
-            box = [mine]
-            dist.broadcast_object_list(box, src=0)
-            return box[0]
-        ep = fb.ExpertParallel(be, rank, world, exchange)
+
+    def exchange(mine):
+        box = [mine]
+        dist.broadcast_object_list(box, src=0)
+        return box[0]
+
     table_pages = (args.prompt_max + 256 + 1 + PAGE - 1) // PAGE + 1
-    pool = fb.KvPool(be, PAGE, lanes * table_pages + 8, lanes, table_pages)
-    model = build_moe(be, pool, cfg, ep, rank, world)
-    state = MoeLanes(pool, lanes, args.seed + rank, args.prompt_budget, args.prefill_limit, (args.prompt_min, args.prompt_max), args.decode_only)
-    rng = np.random.default_rng(args.seed + 77 + rank)
-    t0, t1 = be.timer(), be.timer()
-    processed = 0
-    kernels = 0
-    phase_ms = [0.0] * 4
-    if args.phases:
-        model.phase_timing(True)
-    for step in range(args.warmup + args.steps):
-        if step == args.warmup:
+    parts = []
+    for r in range(R):  # built one after the other: the rendezvous of every expert-parallel group goes through the same gloo group
+        be = fb.CudaBackend(local_rank)
+        ep = fb.ExpertParallel(be, rank, world, exchange) if world > 1 else None
+        pool = fb.KvPool(be, PAGE, lanes * table_pages + 8, lanes, table_pages)
+        model = build_moe(be, pool, cfg, ep, rank, world)
+        state = MoeLanes(pool, lanes, args.seed + rank * R + r, budget, args.prefill_limit, (args.prompt_min, args.prompt_max), args.decode_only)
+        parts.append({"be": be, "ep": ep, "pool": pool, "model": model, "state": state, "rng": np.random.default_rng(args.seed + 77 + rank * R + r)})
+    gate = threading.Barrier(R)
+    results = [None] * R
+    failures = []
+
+    def worker(i):
+        try:
+            part = parts[i]
+            be, pool, model, state, rng = part["be"], part["pool"], part["model"], part["state"], part["rng"]
+            t0, t1 = be.timer(), be.timer()
+            processed = kernels = 0
+            phase_ms = [0.0] * 4
+            if args.phases:
+                model.phase_timing(True)
+            for step in range(args.warmup + args.steps):
+                if step == args.warmup:
+                    be.synchronize()
+                    gate.wait()
+                    if i == 0 and dist is not None:
+                        dist.barrier()
+                    gate.wait()
+                    be.timer_record(t0)
+                    processed, kernels = 0, 0
+                starts, tokens = state.plan()
+                rows = int(tokens.sum())
+                pool.pack_step(starts, tokens)
+                ids = rng.integers(0, cfg["vocab"], rows).astype(np.uint32) if rows else None
+                model.step(ids, want_tokens=rows > 0, lanes=lanes)
+                kernels += model.stats()["kernels"]
+                if args.phases and step >= args.warmup:
+                    phase_ms = [a + b for a, b in zip(phase_ms, model.phase_ms())]
+                state.advance(tokens)
+                processed += rows
+            be.timer_record(t1)
             be.synchronize()
-            if dist is not None:
-                dist.barrier()
-            be.timer_record(t0)
-            processed, kernels = 0, 0
-        starts, tokens = state.plan()
-        rows = int(tokens.sum())
-        pool.pack_step(starts, tokens)
-        ids = rng.integers(0, cfg["vocab"], rows).astype(np.uint32) if rows else None
-        model.step(ids, want_tokens=rows > 0, lanes=lanes)
-        kernels += model.stats()["kernels"]
-        if args.phases and step >= args.warmup:
-            phase_ms = [a + b for a, b in zip(phase_ms, model.phase_ms())]
-        state.advance(tokens)
-        processed += rows
-    be.timer_record(t1)
-    be.synchronize()
-    elapsed = be.timer_elapsed_ns(t0, t1) * 1e-9
-    total = processed
+            results[i] = (be.timer_elapsed_ns(t0, t1) * 1e-9, processed, kernels, phase_ms)
+        except BaseException as error:  # noqa: BLE001 - reported by the main thread
+            failures.append(error)
+            gate.abort()
+
+    threads = [threading.Thread(target=worker, args=(i,)) for i in range(R)]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join()
+    if failures:
+        raise failures[0]
+    elapsed = max(r[0] for r in results)
+    total = sum(r[1] for r in results)
+    kernels = sum(r[2] for r in results)
     if dist is not None:
         import torch
-        box = torch.tensor([elapsed, float(processed), float(kernels)], dtype=torch.float64)
+        box = torch.tensor([elapsed, float(total), float(kernels)], dtype=torch.float64)
         gathered = [torch.zeros_like(box) for _ in range(world)]
         dist.all_gather(gathered, box)
         elapsed = max(float(g[0]) for g in gathered)
@@ -182,21 +212,23 @@ def run_moe(args):
         kernels = int(sum(float(g[2]) for g in gathered))
         dist.barrier()
     if args.phases:
-        print(json.dumps({"rank": rank, "ms_per_step_by_phase": {name: v / args.steps for name, v in zip(
-            ("attention_and_router", "dispatch", "experts", "return_and_combine"), phase_ms)}}), flush=True)
+        for i, r in enumerate(results):
+            print(json.dumps({"rank": rank, "micro_batch": i, "ms_per_step_by_phase": {name: v / args.steps for name, v in zip(
+                ("attention_and_router", "dispatch", "experts", "return_and_combine"), r[3])}}), flush=True)
     if rank == 0:
         print(json.dumps({
             "metric": "moe step tok/s (prompt + generated tokens)", "value": total / elapsed, "unit": "tok/s", "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": elapsed / args.steps * 1e3, "higher_is_better": True, "scaling": "strong", "dtype": "bf16 activations, q4 weights",
             "data": "synthetic", "gpu_launches": kernels,
             "config": {"workload": "qwen3-30b-a3b-arch q4 sparse-MoE continuous batching" + (" (decode only)" if args.decode_only else " (chunked prefill + decode)"),
-                       "lanes_total": args.lanes, "lanes_per_gpu": lanes, "layers": cfg["layers"], "prompt_tokens": [args.prompt_min, args.prompt_max],
-                       "prompt_budget_per_gpu_step": 0 if args.decode_only else args.prompt_budget,
+                       "lanes_total": args.lanes, "lanes_per_gpu": lanes * R, "micro_batches_per_gpu": R, "layers": cfg["layers"], "prompt_tokens": [args.prompt_min, args.prompt_max],
+                       "prompt_budget_per_gpu_step": 0 if args.decode_only else budget * R,
                        "parallelism": ("experts sharded over %d GPUs, NCCL send/recv all-to-all per MoE layer (rows return as %s); lanes data-parallel" % (world, "bf16" if args.ep_bf16_return else "f32")) if world > 1 else "single GPU"}}))
-    model.close()
-    pool.close()
-    if ep is not None:
-        ep.close()
+    for part in parts:
+        part["model"].close()
+        part["pool"].close()
+        if part["ep"] is not None:
+            part["ep"].close()
     if dist is not None:
         dist.destroy_process_group()
 
@@ -336,6 +368,7 @@ def main():
     moe.add_argument("--prefill-limit", type=int, default=4)
     moe.add_argument("--decode-only", action="store_true")
     moe.add_argument("--ep-bf16-return", action="store_true", help="expert parallelism: per-route rows come back as bf16 instead of f32")
+    moe.add_argument("--micro-batches", type=int, default=1, help="independent continuous batches per GPU, stepped concurrently (each gets 1/R of the lanes and of the prompt budget)")
     moe.add_argument("--phases", action="store_true", help="also print the time of the timed steps split by phase (CUDA events inside the step)")
     moe.add_argument("--grouped-min-routes", type=int, default=0, help="0 = library default")
     moe.add_argument("--stream-rows-per-expert", type=int, default=0, help="0 = library default")
