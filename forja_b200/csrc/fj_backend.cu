@@ -595,10 +595,10 @@ int32_t exec_quant_matmul(Exec& x, const fj_dispatch& d) {
 }
 
 // From this many routes on, GatherQuantMatmul buckets the routes by expert: 16-row tiles that stream each active
-// expert once while the average expert has fewer than kStreamRowsPerExpert rows, 64-row tile GEMMs (weights rounded
-// to bf16) beyond that.
+// expert once while the average expert has fewer than kStreamRowsPerExpert rows, tile GEMMs (128 rows on tcgen05, weights
+// rounded to bf16) beyond that.
 constexpr uint64_t kGroupedRoutes = 64;
-constexpr uint64_t kStreamRowsPerExpert = 24;
+constexpr uint64_t kStreamRowsPerExpert = 72;
 
 int32_t exec_gather_quant(Exec& x, const fj_dispatch& d, fj::ErrorRecord* err) {
   if (d.n_outputs != 1 || !quant_params_ok(d.u0, d.u1)) return FJ_INVALID_INPUT;

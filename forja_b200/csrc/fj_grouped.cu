@@ -445,8 +445,8 @@ void launch_route_plan(Ctx& ctx, const unsigned* indices, unsigned total_routes,
   ctx.launches++;
 }
 
-// 128-row tiles once the average expert fills most of one (the nibble expansion is shared by twice the rows), else 64.
-unsigned grouped_tile_rows(unsigned total_routes, unsigned experts) { return total_routes >= 96ull * experts ? 128u : 64u; }
+// 128-row tiles (tcgen05) once the average expert fills half of one, else 64-row tiles.
+unsigned grouped_tile_rows(unsigned total_routes, unsigned experts) { return total_routes >= 64ull * experts ? 128u : 64u; }
 
 bool grouped_q4_supported(unsigned k, unsigned n, unsigned bits, unsigned group_size, unsigned experts, const void* x, const void* packed) {
   return bits == 4 && group_size == 64 && k % 64 == 0 && n % 2 == 0 && experts <= 4096 && reinterpret_cast<size_t>(x) % 16 == 0 && reinterpret_cast<size_t>(packed) % 16 == 0;

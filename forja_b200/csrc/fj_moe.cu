@@ -613,10 +613,10 @@ extern "C" int32_t fj_moe_step(fj_moe_model* m, const uint32_t* token_ids, uint3
       }
     }
     // Few routes: one GEMV-style pass per route. More: bucket by expert; while the average expert has few rows the
-    // 16-row tiles stream each active expert's nibbles once (int8 tensor cores), beyond that 64-row tile GEMMs
-    // (weights rounded to bf16) take over.
+    // 16-row tiles stream each active expert's nibbles (int8 tensor cores; measured faster up to 64 rows per expert),
+    // beyond that 128-row tile GEMMs on tcgen05 (weights rounded to bf16) take over.
     const unsigned kGroupedRoutes = c.grouped_min_routes ? c.grouped_min_routes : 64;
-    const unsigned kStreamRows = c.stream_rows_per_expert ? c.stream_rows_per_expert : 24;
+    const unsigned kStreamRows = c.stream_rows_per_expert ? c.stream_rows_per_expert : 72;
     // `live`: how many of the n_routes ids are expected to be valid (a padded exchange carries whole slabs)
     auto bucketed = [&](const void* x, unsigned src_div, const unsigned* ids, unsigned n_routes, unsigned live, unsigned n_experts, void* act, void* down_out, bool down_bf16) -> bool {
       if (live < kGroupedRoutes || G != 64) return false;

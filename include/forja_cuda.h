@@ -396,7 +396,7 @@ typedef struct fj_moe_config {
   /* Expert projections switch from one pass per route to expert-bucketed forms at this many routes
    * (0 = 64); a value above max_rows * top_k keeps the per-route path. Bucketed routes run as 16-row
    * tiles that stream each active expert once (int8 tensor cores) while routes < stream_rows_per_expert
-   * * experts (0 = 24), and as 64-row tile GEMMs (weights rounded to bf16) from there on. */
+   * * experts (0 = 72), and as tile GEMMs (128 rows on tcgen05, weights rounded to bf16) from there on. */
   uint32_t grouped_min_routes;
   uint32_t stream_rows_per_expert;
   /* Expert parallelism only: nonzero = the experts' owners return their per-route rows rounded to bf16 instead of f32.

@@ -183,10 +183,9 @@ def test_gather_quant_weighted_sum_known_answer():
     assert down(out).ravel().tolist() == [473.5, 582.0]
 
 
-# 1 and 7 rows x 8 routes: one pass per route. 8 to 47 rows (64 to 376 routes, fewer than 24 per expert): routes bucketed by
-# expert into 16-row tiles that stream each expert once (8-row and 16-row forms, experts with more than one tile).
-# 100 rows (50 routes per expert): 64-row tile GEMMs on mma.sync. 200 and 300 rows (100 / 150 per expert): 128-row tiles
-# on the tcgen05 tensor cores, with experts that need a second, ragged tile.
+# 1 and 7 rows x 8 routes: one pass per route. 8 to 100 rows (64 to 800 routes, fewer than 72 per expert): routes bucketed by
+# expert into 16-row tiles that stream the expert's weights (8-row and 16-row forms, experts with several tiles).
+# 200 and 300 rows (100 / 150 per expert): 128-row tiles on the tcgen05 tensor cores, with experts that need a second, ragged tile.
 @pytest.mark.parametrize("rows", [1, 7, 8, 16, 33, 47, 100, 200, 300])
 def test_moe_expert_projections_match_oracle(rows):
     """Qwen3-30B-A3B expert shapes at a reduced expert count: gate/up pair 2048 -> 768 with the
@@ -222,7 +221,7 @@ def test_moe_expert_projections_match_oracle(rows):
     assert_close(down(out), fjo.decode(want, dt), QUANT_TOL)
 
 
-@pytest.mark.parametrize("rows", [40, 80, 200])  # 160 routes: streamed 16-row tiles; 320: 64-row tile GEMMs; 800: 128-row tcgen05 tiles
+@pytest.mark.parametrize("rows", [40, 80, 200])  # 160 and 320 routes: streamed 16-row tiles; 800: 128-row tcgen05 tiles
 def test_bucketed_expert_path_zeroes_bad_routes_and_reports_the_lowest_id(rows):
     """Bucketed routes with two out-of-range expert ids: their rows are zero, every other row is computed,
     and the submission fails with the lowest offending id (crates/forja-cpu/src/lib.rs:1078-1088)."""
@@ -255,6 +254,25 @@ def test_bucketed_expert_path_narrow_and_ragged_column_blocks(inter):
     rng = np.random.default_rng(inter)
     be = backend()
     experts, hidden, top_k, rows = 4, 256, 4, 128
+    dt = fb.BF16
+    pk, sc, bi = quant_weights(rng, inter, hidden, 4, 64, fb.BF16, experts)
+    x, xh = up(rng.standard_normal((rows, hidden)), dt)
+    ids = rng.integers(0, experts, (rows, top_k)).astype(np.uint32)
+    idx, _ = up_u32(ids)
+    out = be.alloc(dt, (rows, top_k, inter))
+    be.run(Op.GatherQuantMatmul(4, 64), [x, be.tensor_from(pk, fb.U32), be.tensor_from(sc, fb.BF16), be.tensor_from(bi, fb.BF16), idx], [out])
+    fjo.set_threads(fjo.max_threads())
+    want = fjo.decode(fjo.gather_quant_matmul(xh, dt, pk, sc, bi, fjo.BF16, ids, 4, 64, dt), dt)
+    fjo.set_threads(1)
+    assert_close(down(out), want, QUANT_TOL)
+
+
+@pytest.mark.parametrize("rows", [48, 96])  # 48 / 96 routes per expert: 64-row mma.sync tiles; 128-row tcgen05 tiles
+def test_bucketed_expert_path_with_k_that_the_streamed_form_refuses(rows):
+    """hidden = 320 is a multiple of the group size but not of the 256-k unit of the streamed form."""
+    rng = np.random.default_rng(rows)
+    be = backend()
+    experts, hidden, inter, top_k = 4, 320, 128, 4
     dt = fb.BF16
     pk, sc, bi = quant_weights(rng, inter, hidden, 4, 64, fb.BF16, experts)
     x, xh = up(rng.standard_normal((rows, hidden)), dt)
