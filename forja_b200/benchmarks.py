@@ -138,6 +138,11 @@ def run_moe(args):
     cfg["grouped_min_routes"] = args.grouped_min_routes
     cfg["stream_rows_per_expert"] = args.stream_rows_per_expert
     cfg["ep_return_bf16"] = int(args.ep_bf16_return)
+    if R > 1 and world > 1 and cfg["max_rows"] * cfg["top_k"] <= 1024:
+        # Small steps exchange padded slabs without a host round trip, so each thread queues dozens of NCCL groups ahead; with two
+        # communicators per GPU issued in whatever order the threads happen to run, such a run stopped making progress on 8 GPUs
+        # (ended by its timeout). The exchange with a host round trip per layer keeps one group per communicator in flight.
+        raise SystemExit("--micro-batches > 1 needs steps of more than 1024 routes per micro-batch (row counts exchanged per layer); use it with prompt work, not with --decode-only at this size")
 
     def exchange(mine):
         box = [mine]
