@@ -45,7 +45,8 @@ def near_tie_flips(tokens, ref_tokens, got_logits):
     return flips
 
 
-# the long prompts put more than 128 routes into one step: expert-bucketed tile GEMMs; the rest: one pass per route
+# the long prompts put more than 64 routes into one step: routes bucketed by expert (streamed 16-row tiles, or tile GEMMs from
+# 72 rows per expert on); the rest: one pass per route
 @pytest.mark.parametrize("cfg,prompts,steps", [(TINY, [5, 23, 9], 5), (CODER_LIKE, [3, 17, 1, 8], 6), (TINY, [70, 40, 9], 3), (CODER_LIKE, [40, 33], 2)])
 def test_moe_step_matches_oracle(cfg, prompts, steps):
     """Two claims, checked separately. (1) Routing: every layer's top-k expert set on the GPU equals the oracle's,
