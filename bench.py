@@ -472,8 +472,14 @@ def run_reference(args):
 def main():
     args = parse_args()
     result = run_reference(args) if args.impl == "reference" else run_native(args)
+    try:  # leave the process group before the line is printed, so nothing follows it on the terminal
+        import torch.distributed as dist
+        if dist.is_available() and dist.is_initialized():
+            dist.destroy_process_group()
+    except Exception:  # noqa: BLE001 - teardown only
+        pass
     if result is not None:
-        print(json.dumps(result))
+        print(json.dumps(result), flush=True)
 
 
 if __name__ == "__main__":
