@@ -239,23 +239,29 @@ __global__ void pack_step_kernel(KvPoolDevice pool, const unsigned* __restrict__
       out.query_starts[lane] = t ? start : 0;
       out.absolute_positions[lane] = t ? start + t - 1 : 0;
       out.activity[lane] = t ? 1 : 0;
-      for (unsigned i = 0; i < t; ++i) {
-        const unsigned row = offset + i;
-        if (row >= rows_cap) break;
-        const unsigned position = start + i, lp = position / pool.page_tokens;
-        unsigned slot = POISON;
-        if (lp < pool.table_pages) {
-          const size_t e = (static_cast<size_t>(lane) * pool.table_pages + lp) * 2;
-          if (pool.tables[e + 1] != POISON) slot = pool.tables[e] * pool.page_tokens + position % pool.page_tokens;
-        }
-        out.positions[row] = position;
-        out.slot_mapping[row] = slot;
-        out.row_lane[row] = lane;
-      }
     }
     __syncthreads();
     if (threadIdx.x == 0) s_base += total;
     __syncthreads();
+  }
+  // per-row outputs: all threads share the rows; the lane of a row is found by bisection over cu_seqlens
+  const unsigned rows = min(s_base, rows_cap);
+  for (unsigned row = threadIdx.x; row < rows; row += blockDim.x) {
+    unsigned lo = 0, hi = lanes;  // cu_seqlens[lo] <= row < cu_seqlens[hi]
+    while (hi - lo > 1) {
+      const unsigned mid = (lo + hi) / 2;
+      if (out.cu_seqlens[mid] <= row) lo = mid; else hi = mid;
+    }
+    const unsigned lane = lo;
+    const unsigned position = starts[lane] + (row - out.cu_seqlens[lane]), lp = position / pool.page_tokens;
+    unsigned slot = POISON;
+    if (lp < pool.table_pages) {
+      const size_t e = (static_cast<size_t>(lane) * pool.table_pages + lp) * 2;
+      if (pool.tables[e + 1] != POISON) slot = pool.tables[e] * pool.page_tokens + position % pool.page_tokens;
+    }
+    out.positions[row] = position;
+    out.slot_mapping[row] = slot;
+    out.row_lane[row] = lane;
   }
 }
 
