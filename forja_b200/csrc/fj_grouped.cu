@@ -4,12 +4,17 @@
 // semantics: Op::GatherQuantMatmul, crates/forja-cpu/src/lib.rs:964-1204).
 //
 // The per-route kernels read an expert's whole matrix for every route, which is right for a few
-// decode rows and hopeless for prefill chunks. Here the routes are bucketed by expert (histogram,
-// scan, arrange; one CTA, like the reference), cut into tiles of 64 rows of one expert, and every
-// tile runs a 64 x 64 x K tensor-core GEMM whose B operand is dequantised on the fly: per 64-k
-// step (= one quantisation group) the CTA copies 64 columns x 32 bytes of nibbles with cp.async,
-// expands them to bf16 (w = s * q + b in f32, rounded once) into a swizzled shared tile and feeds
-// mma.sync m16n8k16 through ldmatrix. Rows of A are gathered through the sorted route list.
+// decode rows and hopeless beyond. Here the routes are bucketed by expert (histogram, scan,
+// arrange; one CTA, like the reference) and cut into tiles of one expert's rows; three forms run
+// the tiles, chosen by the average number of rows per expert:
+//  * 16-row tiles streamed through the int8 tensor-core q4 form (expert_q4_stream_kernel below):
+//    every active expert's nibbles are read once per tile, activations in block fixed point;
+//  * 128-row tiles on tcgen05 with TMEM accumulators (fj_grouped_tc5.cu);
+//  * 64- or 128-row mma.sync tiles (grouped_q4_gemm_kernel below) for shapes the other two refuse:
+//    per 64-k step (= one quantisation group) the CTA copies 64 columns x 32 bytes of nibbles with
+//    cp.async, expands them to bf16 (one bf16x2 fma per pair of weights) into a swizzled shared
+//    tile and feeds mma.sync m16n8k16 through ldmatrix; rows of A are gathered through the sorted
+//    route list.
 //  pair mode: gate and up tiles share the A tile; epilogue silu(gate) * up -> act[route] (bf16)
 //  single mode: f32 result per route (the weighted combine adds them in route order afterwards)
 // The order of rows inside an expert's bucket is whatever the atomics give; it only decides which

@@ -103,7 +103,7 @@ __device__ inline unsigned block_exclusive_scan(unsigned value, unsigned* total,
   return offset + inclusive - value;
 }
 
-// Drops one reference of the page in table slot `slot`; true when that was the last one.
+// Drops one reference of `page`; true when that was the last one.
 __device__ inline bool drop_page_reference(const KvPoolDevice& pool, unsigned page) { return atomicSub(&pool.refcounts[page], 1u) == 1u; }
 
 __global__ void kvpool_release_kernel(KvPoolDevice pool, const unsigned* __restrict__ lanes, unsigned count) {
