@@ -308,6 +308,25 @@ def run_gemm(args):
             be.release(t)
 
 
+def run_sample(args):
+    """Op::Sample on [rows, vocab] bf16 logits (N(0, spread)): device time per dispatch for a few parameter settings."""
+    from forja_b200.backend import CommandList, Op
+    be = fb.CudaBackend(0)
+    logits = be.alloc(fb.BF16, (args.rows, args.vocab))
+    be.fill_random(logits, 3, std=args.spread)
+    out = be.alloc(fb.U32, (args.rows,))
+    bits = lambda v: int(np.array([v], np.float32).view(np.uint32)[0])
+    for name, temperature, top_k, top_p in (("greedy", 0.0, 0, 1.0), ("top-k 40, top-p 0.95", 0.8, 40, 0.95), ("top-p 0.9 over the row", 1.0, 0, 0.9),
+                                            ("temperature only", 1.0, 0, 1.0)):
+        params = be.tensor_from(np.array([bits(temperature), top_k, bits(top_p), 11, 22], np.uint32), fb.U32)
+        cl = CommandList()
+        for rep in range(args.reps):
+            cl.dispatch(Op.Sample(rep), [logits, params], out)
+        ns = timed(be, cl, args.reps)
+        print(json.dumps({"workload": "Op::Sample, one CTA per row", "rows": args.rows, "vocab": args.vocab, "setting": name, "us_per_dispatch": ns / 1e3}), flush=True)
+        be.release(params)
+
+
 def run_attention(args):
     """Isolated paged GQA attention (config 3): 32 q / 4 kv heads, head_dim 128, page 16, permuted page tables, bf16 N(0, 1).
     decode: `lanes` sequences with kv lengths log-uniform 64-32768, one query token each (one ragged launch);
@@ -389,8 +408,13 @@ def main():
     attn.add_argument("--lanes", type=int, default=256)
     attn.add_argument("--kv-max", type=int, default=32768)
     attn.add_argument("--seed", type=int, default=0)
+    sample = sub.add_parser("sample")
+    sample.add_argument("--rows", type=int, default=128)
+    sample.add_argument("--vocab", type=int, default=151936)
+    sample.add_argument("--spread", type=float, default=3.0)
+    sample.add_argument("--reps", type=int, default=5)
     args = ap.parse_args()
-    {"moe": run_moe, "q4": run_q4, "gemm": run_gemm, "attention": run_attention}[args.command](args)
+    {"moe": run_moe, "q4": run_q4, "gemm": run_gemm, "attention": run_attention, "sample": run_sample}[args.command](args)
 
 
 if __name__ == "__main__":
