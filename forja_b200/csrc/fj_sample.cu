@@ -102,10 +102,20 @@ __device__ unsigned long long select_rank(const SampleArgs& a, size_t row_offset
     for (unsigned b = threadIdx.x; b < 256; b += SAMPLE_THREADS) s.hist[b] = 0;
     __syncthreads();
     const unsigned long long prefix = s.prefix;
-    for (unsigned i = threadIdx.x; i < a.width; i += SAMPLE_THREADS) {
-      if (!sample_allowed(a, i)) continue;
-      const unsigned long long key = sample_key(a, row_offset, i);
-      if (shift == 56 || (key >> (shift + 8)) == (prefix >> (shift + 8))) atomicAdd(&s.hist[(key >> shift) & 255u], 1u);
+    // eight rounds at a time: the loads of a batch are independent of each other, so they are in flight together
+    constexpr int kBatch = 8;
+    for (unsigned base = threadIdx.x; base < a.width; base += SAMPLE_THREADS * kBatch) {
+      unsigned long long keys[kBatch];
+      bool live[kBatch];
+#pragma unroll
+      for (int u = 0; u < kBatch; ++u) {
+        const unsigned i = base + u * SAMPLE_THREADS;
+        live[u] = i < a.width && sample_allowed(a, i);
+        keys[u] = live[u] ? sample_key(a, row_offset, i) : 0ULL;
+      }
+#pragma unroll
+      for (int u = 0; u < kBatch; ++u)
+        if (live[u] && (shift == 56 || (keys[u] >> (shift + 8)) == (prefix >> (shift + 8)))) atomicAdd(&s.hist[(keys[u] >> shift) & 255u], 1u);
     }
     __syncthreads();
     if (threadIdx.x == 0) {
@@ -211,7 +221,7 @@ __global__ void __launch_bounds__(SAMPLE_THREADS) sample_kernel(SampleArgs a) {
         for (unsigned c = 0; c < chunks; ++c) {
           const unsigned first = c * SAMPLE_CHUNK, last = min(first + SAMPLE_CHUNK, significant), count = last - first;
           if (!(chunks == 1 && phase == 1)) {
-            const unsigned long long low_key = last == n_allowed ? 0ULL : select_rank(a, row_offset, last, s);
+            const unsigned long long low_key = last == n_allowed ? 0ULL : (last == cap ? cap_key : select_rank(a, row_offset, last, s));  // rank cap is known already
             unsigned padded = 1;
             while (padded < count) padded <<= 1;
             __syncthreads();
