@@ -20,6 +20,7 @@ import json
 import os
 import subprocess
 import sys
+import tempfile
 import time
 
 import numpy as np
@@ -241,8 +242,8 @@ def run_native(args):
     # The clock sampler starts before the warm-up: nvidia-smi's own start-up (NVML initialisation) can stall
     # kernel launches for about a second, which must not land inside a timed region. It keeps sampling
     # through both timed regions.
-    clocks_path = os.path.join(ROOT, "gpurun_out", f"clocks_rank{rank}.csv")
-    os.makedirs(os.path.dirname(clocks_path), exist_ok=True)
+    clocks_dir = tempfile.mkdtemp(prefix="fj_bench_clocks_")
+    clocks_path = os.path.join(clocks_dir, f"clocks_rank{rank}.csv")
     sampler = start_clock_sampler(clocks_path, local)
     if sampler is not None:
         deadline = time.perf_counter() + 5.0
@@ -340,7 +341,7 @@ def run_native(args):
     result["step_roofline"] = {"algorithmic_gb_per_step": step_bytes / 1e9, "achieved_gbs": step_bytes / 1e9 / (elapsed / args.steps),
                                "frac_of_hbm_peak": step_bytes / 1e9 / (elapsed / args.steps) / peaks["hbm_gbs"]}
     if world == 1 and not args.no_cpu_baseline:
-        result["cpu_baseline"] = cpu_baseline(args, cfg, budget_s=20.0)
+        result["cpu_baseline"] = cpu_baseline(args, cfg)
     model.close()
     pool.close()
     return result
@@ -374,18 +375,18 @@ def ncu_traffic_per_launch(algorithmic_bytes):
     return None if NCU_TRAFFIC_RATIO is None else algorithmic_bytes * NCU_TRAFFIC_RATIO
 
 
-def cpu_sample(args, cfg, n_lanes, threads):
+def cpu_sample(args, cfg, n_lanes, threads, appended_tokens):
     """Builds the CPU port (the oracle engine, test infrastructure) on a sample of the workload:
-    `n_lanes` requests drawn from the same length distribution, synthetic N(0,1) KV contexts."""
+    `n_lanes` requests drawn from the same length distribution, synthetic N(0,1) KV contexts. Every
+    lane's page table has room for its context plus `appended_tokens` decode steps."""
     from oracle import engine, fjo
     fjo.set_threads(threads)
     requests = Requests(args.seed * 1000, args.ctx_max)
     sample = [requests.next() for _ in range(args.lanes)]
     pick = [sample[i] for i in np.linspace(0, args.lanes - 1, n_lanes).astype(int)]
-    pages = [(ctx + 2 + PAGE - 1) // PAGE for ctx, _ in pick]
+    pages = [(ctx + appended_tokens + PAGE - 1) // PAGE for ctx, _ in pick]
     physical = sum(pages) + 1
-    weights = engine.random_dense_weights(cfg, args.seed)
-    ref = engine.DenseOracle(cfg, weights, physical, PAGE)
+    ref = engine.DenseOracle(cfg, None, physical, PAGE, weight_bits=random_weights_bf16(cfg, args.seed))
     rng = np.random.default_rng(args.seed)
     block = f32_to_bf16_bits(rng.standard_normal(1 << 20, dtype=np.float32))
     for plane in ref.k_planes + ref.v_planes:
@@ -402,39 +403,58 @@ def cpu_sample(args, cfg, n_lanes, threads):
     return ref, pick, tables, generations
 
 
-def cpu_decode_step(ref, pick, tables, generations, offset):
+def cpu_decode_step(ref, pick, tables, generations, offset, n_lanes=None):
+    """One decode step of the sampled lanes on the CPU port: lane i appends one token at position
+    ctx_i + offset. Returns the tokens produced."""
     tokens = 0
-    for (ctx, _), table in zip(pick, tables):
+    for (ctx, _), table in list(zip(pick, tables))[:n_lanes]:
         ref.forward_lane([(ctx * 7 + offset) % ref.cfg["vocab"]], ctx + offset, table, generations)
         tokens += 1
     return tokens
 
 
-def cpu_baseline(args, cfg, budget_s):
-    """Times the CPU port on this box's host cores on a bounded sample (one decode step of a few
-    lanes of the same workload). A reported baseline, not the optimisation target."""
+CPU_BASELINE_STEPS = 5  # timed steps per thread count (median reported), after one untimed step
+
+
+def cpu_baseline(args, cfg):
+    """Times the CPU port on this box's host cores on a bounded sample of the workload: decode steps
+    of a few lanes of the same request stream through all layers, once with every host thread
+    (OpenMP over rows/columns; `value`) and once on one core (`one_core`: forja-cpu itself is
+    single-threaded, crates/forja-cpu/src/lib.rs:20-24). Median of CPU_BASELINE_STEPS steps each,
+    after one untimed step. A reported baseline, not the optimisation target."""
     from oracle import fjo
     threads = fjo.max_threads()
-    n_lanes = 2
-    ref, pick, tables, generations = cpu_sample(args, cfg, n_lanes, threads)
-    t0 = time.perf_counter()
-    tokens = cpu_decode_step(ref, pick, tables, generations, 0)
-    first = time.perf_counter() - t0
-    steps = 1
-    if first < budget_s / 2:
-        t0 = time.perf_counter()
-        tokens = cpu_decode_step(ref, pick, tables, generations, 1)
-        first = time.perf_counter() - t0
+    ref, pick, tables, generations = cpu_sample(args, cfg, 2, threads, 2 * (CPU_BASELINE_STEPS + 1))
+
+    def median_rate(n_lanes, first_offset):
+        cpu_decode_step(ref, pick, tables, generations, first_offset, n_lanes)
+        rates = []
+        for s in range(CPU_BASELINE_STEPS):
+            t0 = time.perf_counter()
+            tokens = cpu_decode_step(ref, pick, tables, generations, first_offset + 1 + s, n_lanes)
+            rates.append(tokens / (time.perf_counter() - t0))
+        return float(np.median(rates)), float(np.max(rates))
+
+    all_median, all_best = median_rate(2, 0)
     fjo.set_threads(1)
-    return {"value": tokens / first, "unit": "tok/s", "cores": threads, "kind": "port",
-            "sample": f"{steps} decode step of {n_lanes} lanes (contexts {[c for c, _ in pick]}) of the same request stream, all {cfg['layers']} layers, "
-                      f"C++ restatement of forja-cpu with OpenMP over rows/columns"}
+    one_median, one_best = median_rate(1, CPU_BASELINE_STEPS + 1)
+    contexts = [c for c, _ in pick]
+    return {"value": all_median, "unit": "tok/s", "cores": threads, "kind": "port", "best": all_best,
+            "one_core": {"value": one_median, "unit": "tok/s", "cores": 1, "best": one_best,
+                         "sample": f"median of {CPU_BASELINE_STEPS} decode steps of 1 lane (context {contexts[0]}) after 1 untimed step"},
+            "sample": f"median of {CPU_BASELINE_STEPS} decode steps of 2 lanes (contexts {contexts}) of the same request stream after 1 untimed step, all "
+                      f"{cfg['layers']} layers, C++ restatement of forja-cpu with OpenMP over rows/columns"}
+
+
+REFERENCE_BUDGET_S = 150.0
 
 
 def run_reference(args):
     """Reference arm: forja's own CPU backend cannot be built here (Rust, no toolchain), so the CPU
     port (oracle restatement of crates/forja-cpu) is timed on the host cores with every thread it
-    can use. Each step decodes a bounded sample of lanes of the same workload."""
+    can use. Each step decodes a bounded sample of the workload: one lane of the same request stream
+    through all layers. Steps and warm-up are the requested ones unless they would not fit in
+    REFERENCE_BUDGET_S seconds."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return None
@@ -444,25 +464,29 @@ def run_reference(args):
         cfg["layers"] = args.layers
     threads = fjo.max_threads()
     n_lanes = 1
-    ref, pick, tables, generations = cpu_sample(args, cfg, n_lanes, threads)
-    budget = 150.0
+    # positions used: ctx + 0 (probe), ctx + 1 .. ctx + warmup + steps; the table holds one more
+    ref, pick, tables, generations = cpu_sample(args, cfg, n_lanes, threads, 2 + args.warmup + args.steps)
     t0 = time.perf_counter()
     cpu_decode_step(ref, pick, tables, generations, 0)
-    one = time.perf_counter() - t0
-    steps = max(1, min(args.steps, int(budget / max(one, 1e-3)) - args.warmup))
-    warmup = min(args.warmup, max(0, int(budget / max(one, 1e-3)) - steps))
+    one = max(time.perf_counter() - t0, 1e-3)
+    fit = int(REFERENCE_BUDGET_S / one)
+    steps = max(1, min(args.steps, fit - args.warmup))
+    warmup = min(args.warmup, max(0, fit - steps))
     for w in range(warmup):
         cpu_decode_step(ref, pick, tables, generations, 1 + w)
-    t0 = time.perf_counter()
-    tokens = 0
+    tokens, durations = 0, []
+    t_all = time.perf_counter()
     for s in range(steps):
+        t0 = time.perf_counter()
         tokens += cpu_decode_step(ref, pick, tables, generations, 1 + warmup + s)
-    elapsed = time.perf_counter() - t0
+        durations.append(time.perf_counter() - t0)
+    elapsed = time.perf_counter() - t_all
     fjo.set_threads(1)
     value = tokens / elapsed
     sample = f"each step decodes {n_lanes} lane (context {pick[0][0]}) of the same request stream through all {cfg['layers']} layers; {steps} timed steps"
     return {"impl": "reference", "metric": "ragged decode tok/s", "value": value, "unit": "tok/s", "n_gpus": args.gpus, "steps": steps, "warmup": warmup,
-            "ms_per_step": elapsed / steps * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "ms_per_step": elapsed / steps * 1e3, "median_ms_per_step": float(np.median(durations)) * 1e3, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": {"workload": "qwen3-0.6b-arch bf16 continuous-batching decode, 128 lanes, ctx log-uniform 128-%d, page 16" % args.ctx_max,
                        "note": "forja-cpu restated in C++ (the Rust reference cannot be compiled on this box); steps requested %d" % args.steps},
             "cpu_baseline": {"value": value, "unit": "tok/s", "cores": threads, "kind": "port", "sample": sample},

@@ -40,11 +40,16 @@ def random_dense_weights(cfg: dict, seed: int = 0):
 class DenseOracle:
     """Reference-order forward step over paged KV. ``dt`` is the activation/weight/KV dtype code."""
 
-    def __init__(self, cfg: dict, weights: dict, physical_pages: int, page_tokens: int):
+    def __init__(self, cfg: dict, weights: dict, physical_pages: int, page_tokens: int, weight_bits: dict = None):
+        """``weights``: f32 arrays (encoded here to the storage dtype); or ``weight_bits``: the same
+        dictionary already in storage form (bf16 bit patterns as uint16), used as it is."""
         self.cfg, self.dt, self.page_tokens = cfg, cfg["dtype"], page_tokens
-        enc = lambda a: fjo.encode(a, self.dt)
-        self.w = {"embed": enc(weights["embed"]), "final_norm": enc(weights["final_norm"]),
-                  "layers": [{k: enc(v) for k, v in layer.items()} for layer in weights["layers"]]}
+        if weight_bits is not None:
+            self.w = weight_bits
+        else:
+            enc = lambda a: fjo.encode(a, self.dt)
+            self.w = {"embed": enc(weights["embed"]), "final_norm": enc(weights["final_norm"]),
+                      "layers": [{k: enc(v) for k, v in layer.items()} for layer in weights["layers"]]}
         kd = cfg["kv_heads"] * cfg["head_dim"]
         self.k_planes = [np.zeros((physical_pages, page_tokens, kd), fjo.NP_OF[self.dt]) for _ in range(cfg["layers"])]
         self.v_planes = [np.zeros((physical_pages, page_tokens, kd), fjo.NP_OF[self.dt]) for _ in range(cfg["layers"])]
