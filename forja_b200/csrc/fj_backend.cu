@@ -28,7 +28,9 @@ fj_buffer_rec* find_buffer(fj_backend* be, uint64_t id) {
 }
 
 int32_t alloc_buffer(fj_backend* be, uint64_t bytes, uint64_t* id) {
-  if (be->limit_bytes != 0 && be->used_bytes + bytes > be->limit_bytes) return FJ_QUOTA_EXCEEDED;
+  uint64_t total = 0;
+  if (__builtin_add_overflow(be->used_bytes, bytes, &total)) return FJ_QUOTA_EXCEEDED;
+  if (be->limit_bytes != 0 && total > be->limit_bytes) return FJ_QUOTA_EXCEEDED;
   void* ptr = nullptr;
   uint64_t alloc_bytes = bytes == 0 ? 16 : bytes;
   if (cudaMalloc(&ptr, alloc_bytes) != cudaSuccess) { cudaGetLastError(); return FJ_ALLOCATION_FAILED; }
@@ -56,18 +58,36 @@ bool is_contiguous(const fj_tensor& t) {
   return true;
 }
 
-void* tensor_ptr(fj_backend* be, const fj_tensor& t, bool for_write) {
-  fj_buffer_rec* rec = find_buffer(be, t.buffer);
-  if (rec == nullptr || t.rank > 8 || t.dtype > FJ_U32) return nullptr;
-  if (for_write && rec->readonly) return nullptr;
+// Byte range [lo, hi) a view can touch, with every product and sum overflow-checked like the
+// reference's layout arithmetic (crates/forja-core/src/layout.rs uses checked_mul / checked_add
+// throughout). An empty view spans [lo, lo). False: rank or dtype out of range, or the arithmetic
+// wraps 64 bits - such a view addresses nothing valid.
+bool tensor_byte_span(const fj_tensor& t, uint64_t* lo, uint64_t* hi) {
+  if (t.rank > 8 || t.dtype > FJ_U32) return false;
   const uint64_t esz = fj::dtype_size(static_cast<int>(t.dtype));
+  if (__builtin_mul_overflow(t.offset, esz, lo)) return false;
+  bool empty = false;
+  for (uint32_t a = 0; a < t.rank; ++a) empty = empty || t.shape[a] == 0;
+  if (empty) { *hi = *lo; return true; }
   uint64_t last = t.offset;
   for (uint32_t a = 0; a < t.rank; ++a) {
-    if (t.shape[a] == 0) return static_cast<char*>(rec->ptr) + t.offset * esz;  // empty tensor: never dereferenced
-    last += static_cast<uint64_t>(t.shape[a] - 1) * t.strides[a];
+    uint64_t step = 0;
+    if (__builtin_mul_overflow(static_cast<uint64_t>(t.shape[a] - 1), t.strides[a], &step)) return false;
+    if (__builtin_add_overflow(last, step, &last)) return false;
   }
-  if ((last + 1) * esz > rec->bytes) return nullptr;
-  return static_cast<char*>(rec->ptr) + t.offset * esz;
+  uint64_t count = 0;
+  if (__builtin_add_overflow(last, static_cast<uint64_t>(1), &count)) return false;
+  return !__builtin_mul_overflow(count, esz, hi);
+}
+
+void* tensor_ptr(fj_backend* be, const fj_tensor& t, bool for_write) {
+  fj_buffer_rec* rec = find_buffer(be, t.buffer);
+  if (rec == nullptr) return nullptr;
+  if (for_write && rec->readonly) return nullptr;
+  uint64_t lo = 0, hi = 0;
+  if (!tensor_byte_span(t, &lo, &hi)) return nullptr;
+  if (lo > rec->bytes || hi > rec->bytes) return nullptr;  // an empty view is never dereferenced but must still start inside
+  return static_cast<char*>(rec->ptr) + lo;
 }
 
 bool make_view(fj_backend* be, const fj_tensor& t, bool for_write, View* out) {
@@ -709,14 +729,10 @@ int32_t exec_paged_copy(Exec& x, const fj_dispatch& d, fj::ErrorRecord* err) {
 
 bool ranges_overlap(fj_backend* be, const fj_tensor& a, const fj_tensor& b) {
   if (a.buffer != b.buffer) return false;
-  auto span = [](const fj_tensor& t, uint64_t* lo, uint64_t* hi) {
-    uint64_t last = t.offset;
-    for (uint32_t i = 0; i < t.rank; ++i) last += static_cast<uint64_t>(t.shape[i] ? t.shape[i] - 1 : 0) * t.strides[i];
-    uint64_t esz = fj::dtype_size(t.dtype);
-    *lo = t.offset * esz; *hi = (last + 1) * esz;
-  };
   uint64_t al, ah, bl, bh;
-  span(a, &al, &ah); span(b, &bl, &bh);
+  // a view whose span cannot be computed is refused by tensor_ptr before anything runs; calling it
+  // a hazard here only keeps it out of a coalesced run
+  if (!tensor_byte_span(a, &al, &ah) || !tensor_byte_span(b, &bl, &bh)) return true;
   (void)be;
   return al < bh && bl < ah;
 }
@@ -1052,6 +1068,11 @@ int32_t fj_program_prepare(fj_backend* be, uint32_t kind, const uint32_t* insts,
   be->programs.push_back(rec);
   *handle = be->programs.size();
   return FJ_OK;
+}
+
+int32_t fj_tensor_byte_span(const fj_tensor* view, uint64_t* lo, uint64_t* hi) {
+  if (view == nullptr || lo == nullptr || hi == nullptr) return FJ_INVALID_INPUT;
+  return tensor_byte_span(*view, lo, hi) ? FJ_OK : FJ_INVALID_INPUT;
 }
 
 int32_t fj_program_classify(uint32_t kind, const uint32_t* insts, uint32_t n_insts, const uint32_t* outputs, uint32_t n_outputs, uint32_t* kernel, float consts[4]) {

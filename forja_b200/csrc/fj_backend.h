@@ -87,6 +87,7 @@ fj_buffer_rec* find_buffer(fj_backend* be, uint64_t id);
 // Allocates a zeroed device buffer and registers it (quota checked). Returns an fj_status.
 int32_t alloc_buffer(fj_backend* be, uint64_t bytes, uint64_t* id);
 // Device pointer of a tensor's first element after bounds validation; nullptr on failure.
+bool tensor_byte_span(const fj_tensor& t, uint64_t* lo, uint64_t* hi);
 void* tensor_ptr(fj_backend* be, const fj_tensor& t, bool for_write);
 bool make_view(fj_backend* be, const fj_tensor& t, bool for_write, fj::View* out);
 bool is_contiguous(const fj_tensor& t);

@@ -355,11 +355,8 @@ SplitPlan plan_gemm(unsigned m, unsigned n, unsigned k, int sm_count) {
 template <int BN, bool kBF16>
 void run_mma(Ctx& ctx, const GemmParams& p, unsigned tiles_m, unsigned tiles_n) {
   constexpr int smem = kPipelineDepth<BN> * (BM * BK * 2 + BN * BK * 2);
-  static bool configured = false;
-  if (!configured) {
-    cudaFuncSetAttribute(gemm_nt_mma_kernel<BN, kBF16>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-    configured = true;
-  }
+  static SmemOptIn opted;
+  opt_in_smem(opted, gemm_nt_mma_kernel<BN, kBF16>, smem);
   launch_pdl(gemm_nt_mma_kernel<BN, kBF16>, dim3(tiles_n, tiles_m, p.splits), dim3(GEMM_THREADS), smem, ctx.stream, p);
   ctx.launches++;
 }

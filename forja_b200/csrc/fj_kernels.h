@@ -2,6 +2,7 @@
 // and bumps ctx.launches by the number of kernels it started; none of them allocates.
 #pragma once
 
+#include <atomic>
 #include <cuda_runtime.h>
 #include <stdint.h>
 
@@ -30,6 +31,25 @@ inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, s
   config.attrs = attribute;
   config.numAttrs = 1;
   return cudaLaunchKernelEx(&config, kernel, KArgs(args)...);
+}
+
+// Raises a kernel's dynamic shared-memory limit once per device: cudaFuncAttributeMaxDynamicSharedMemorySize
+// belongs to the (function, device) pair, so a process that opens a second GPU has to opt in there too.
+// One SmemOptIn per kernel instantiation (a function-local static); safe to call from several host threads.
+// Returns false when the attribute call fails; the CUDA error is left pending, so the launch that follows
+// fails too and the submission reports FJ_DEVICE_EXECUTION_FAILED.
+struct SmemOptIn {
+  std::atomic<unsigned char> done[64] = {};
+};
+template <typename K>
+inline bool opt_in_smem(SmemOptIn& state, K kernel, int bytes) {
+  int device = 0;
+  if (cudaGetDevice(&device) != cudaSuccess) return false;
+  if (device < 0 || device >= 64) return cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) == cudaSuccess;
+  if (state.done[device].load(std::memory_order_acquire)) return true;
+  if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) != cudaSuccess) return false;
+  state.done[device].store(1, std::memory_order_release);
+  return true;
 }
 
 // ---- fj_elementwise.cu ----------------------------------------------------------------------

@@ -654,7 +654,8 @@ __global__ void __launch_bounds__(kWarps * 32, 2) attn_prefill_mma_kernel(Prefil
 #pragma unroll
     for (int i = 0; i < 16; ++i) {
       const float v0 = o[i][2 * r] * inv, v1 = o[i][2 * r + 1] * inv;
-      if (p.out_dtype == (kBF16 ? BF16 : F16) && (base % 2 == 0)) {
+      // the packed 4-byte store needs a 4-byte-aligned ADDRESS: a 16-bit output view may start at an odd element of its buffer
+      if (p.out_dtype == (kBF16 ? BF16 : F16) && (((reinterpret_cast<size_t>(seq.out) >> 1) + base) % 2 == 0)) {
         *reinterpret_cast<unsigned*>(static_cast<unsigned short*>(seq.out) + base + i * 8) = pack2<kBF16>(v0, v1);
       } else {
         store_from_f32(seq.out, p.out_dtype, base + i * 8, v0);
@@ -787,12 +788,9 @@ void launch_attn_decode_mma(Ctx& ctx, const AttnGeometry& g, const AttnSeq* seqs
   p.q_heads = g.q_heads; p.kv_heads = g.kv_heads; p.group = g.q_heads / g.kv_heads;
   p.scale = g.scale; p.out_dtype = g.out_dtype;
   p.part_o = scratch.part_o; p.part_ml = scratch.part_ml; p.counters = scratch.counters; p.err = err;
-  static bool configured = false;
-  if (!configured) {
-    cudaFuncSetAttribute(attn_decode_mma_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kDecodeSmem);
-    cudaFuncSetAttribute(attn_decode_mma_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kDecodeSmem);
-    configured = true;
-  }
+  static SmemOptIn opted_bf16, opted_f16;
+  if (g.kv_dtype == BF16) opt_in_smem(opted_bf16, attn_decode_mma_kernel<true>, kDecodeSmem);
+  else opt_in_smem(opted_f16, attn_decode_mma_kernel<false>, kDecodeSmem);
   if (g.kv_dtype == BF16) launch_pdl(attn_decode_mma_kernel<true>, dim3(n_work), dim3(kWarps * 32), kDecodeSmem, ctx.stream, p);
   else launch_pdl(attn_decode_mma_kernel<false>, dim3(n_work), dim3(kWarps * 32), kDecodeSmem, ctx.stream, p);
   ctx.launches++;

@@ -140,6 +140,11 @@ int32_t fj_write(fj_backend* be, uint64_t buffer, uint64_t byte_offset, const vo
 int32_t fj_read(fj_backend* be, uint64_t buffer, uint64_t byte_offset, void* dst, uint64_t len);
 /* read (backend.rs:762): gathers a strided view into contiguous logical bytes at dst. */
 int32_t fj_read_strided(fj_backend* be, const fj_tensor* view, void* dst);
+/* The byte range [lo, hi) of its allocation that a view can touch, with every product and sum
+ * overflow-checked (the checked layout arithmetic of crates/forja-core/src/layout.rs:165-330);
+ * FJ_INVALID_INPUT when rank or dtype is out of range or the arithmetic wraps 64 bits. Host logic,
+ * needs no device: it is the test every tensor of a submission passes before a kernel sees it. */
+int32_t fj_tensor_byte_span(const fj_tensor* view, uint64_t* lo, uint64_t* hi);
 /* Device address of a buffer, for callers that stage data with their own copies or kernels. */
 int32_t fj_buffer_device_ptr(fj_backend* be, uint64_t buffer, void** ptr, uint64_t* bytes);
 

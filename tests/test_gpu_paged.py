@@ -5,7 +5,7 @@ import numpy as np
 import pytest
 
 import forja_b200 as fb
-from forja_b200.backend import CommandList, Op
+from forja_b200.backend import CommandList, Layout, Op, Tensor
 from oracle import fjo
 from tests.gpu_util import TOL, assert_close, backend, down, down_raw, max_abs_rel, up, up_u32
 
@@ -333,3 +333,25 @@ def test_prefill_attention_non_causal_inactive_and_corrupt_lanes():
         be.run(Op.PagedSdpa(scale, True, 60, key_length, page), [q.permute([1, 0, 2]), kt, vt, up_u32(bad)[0], up_u32(generations)[0]], [out3.permute([1, 0, 2])])
     assert info.value.flag == 2 and info.value.index == 2
     assert np.all(down(out3) == 0.0)
+
+
+@pytest.mark.parametrize("q_len,q_start", [(70, 33), (1, 40)])
+def test_attention_output_view_at_an_odd_element_offset(q_len, q_start):
+    """A 16-bit output view may start at an odd element of its buffer (2-byte aligned): the
+    tensor-core kernels must not use packed 4-byte stores there."""
+    rng = np.random.default_rng(77 + q_len)
+    be = backend()
+    dt, page, hq, kvh, d = fb.BF16, 16, 16, 8, 128
+    key_length = q_start + q_len
+    physical = key_length // page + 4
+    table, generations = random_table(rng, key_length, page, physical)
+    kt, kh, vt, vh = fill_pools(rng, physical, page, kvh, d, dt)
+    q, qh = up(rng.standard_normal((q_len, hq, d)), dt)
+    flat = be.alloc(dt, (q_len * hq * d + 3,))
+    out = Tensor(flat.buffer, Layout.contiguous(dt, (q_len, hq, d), offset=1), flat.byte_len, True)
+    scale = 0.088388346
+    be.run(Op.PagedSdpa(scale, True, q_start, key_length, page), [q.permute([1, 0, 2]), kt, vt, up_u32(table)[0], up_u32(generations)[0]], [out.permute([1, 0, 2])])
+    want = fjo.paged_sdpa(np.ascontiguousarray(qh.transpose(1, 0, 2)), dt, kh, dt, vh, dt, table, generations, key_length, q_start, scale, True, page)
+    assert_close(down(out).transpose(1, 0, 2), fjo.decode(want, dt), TOL[dt])
+    raw = down_raw(flat)
+    assert raw[0] == 0 and not raw[-2:].any()

@@ -102,3 +102,31 @@ def test_layout_views_match_reference_semantics():
     assert b.strides == (0, 0, 1)
     with pytest.raises(fb.BackendError):
         base.slice([(0, 5, 1), (0, 6, 1), (0, 8, 1)])
+
+
+def _span(offset, shape, strides, dtype=fb.F32):
+    lib = _lib.load()
+    t = _lib.FjTensor()
+    t.buffer, t.dtype, t.rank, t.offset = 1, dtype, len(shape), offset
+    for a, (n, s) in enumerate(zip(shape, strides)):
+        t.shape[a], t.strides[a] = n, s
+    lo, hi = C.c_uint64(0), C.c_uint64(0)
+    st = lib.fj_tensor_byte_span(C.byref(t), C.byref(lo), C.byref(hi))
+    return st, lo.value, hi.value
+
+
+def test_tensor_byte_span_uses_checked_arithmetic():
+    """The one memory-safety re-check at the boundary must not wrap: a view whose strides or offset
+    overflow 64 bits addresses nothing valid and is refused (crates/forja-core/src/layout.rs uses
+    checked_mul / checked_add for the same arithmetic)."""
+    INVALID = fb.backend.INVALID_INPUT
+    assert _span(3, (4, 5), (5, 1)) == (0, 12, (3 + 19 + 1) * 4)
+    assert _span(0, (2, 3), (0, 1), fb.BF16) == (0, 0, 6)           # broadcast axis
+    assert _span(7, (4, 0, 2), (1 << 62, 1, 1)) == (0, 28, 28)       # empty view: nothing is addressed
+    assert _span(0, (3,), (1 << 63,))[0] == INVALID                  # 2 * 2^63 wraps to 0
+    assert _span(0, (2, 2), ((1 << 64) - 1, 2))[0] == INVALID        # sum of steps wraps
+    assert _span(1 << 62, (1,), (1,))[0] == INVALID                  # offset * 4 wraps
+    assert _span((1 << 64) - 1, (1,), (1,), fb.U32)[0] == INVALID    # last + 1 wraps
+    assert _span(0, (1 << 31, 1 << 31, 8), (1 << 33, 4, 1 << 60))[0] == INVALID
+    st, lo, hi = _span(0, (1,), (1,), 9)
+    assert st == INVALID                                              # dtype out of range
