@@ -341,10 +341,43 @@ def run_native(args):
     result["step_roofline"] = {"algorithmic_gb_per_step": step_bytes / 1e9, "achieved_gbs": step_bytes / 1e9 / (elapsed / args.steps),
                                "frac_of_hbm_peak": step_bytes / 1e9 / (elapsed / args.steps) / peaks["hbm_gbs"]}
     if world == 1 and not args.no_cpu_baseline:
+        result["parity_check"] = parity_check(args, cfg, be, pool, model, lanes, host_tokens)
         result["cpu_baseline"] = cpu_baseline(args, cfg)
     model.close()
     pool.close()
     return result
+
+
+def parity_check(args, cfg, be, pool, model, lanes, host_tokens):
+    """After the timed regions, outside them: one more decode step of the running batch on the GPU with the
+    logits kept, and the lane with the shortest context replayed on the CPU port from the very cache rows
+    the GPU holds for it (read back page by page) and the same bf16 weights. Reports the logits' max-abs
+    relative difference (bound 2e-2) and whether the greedy tokens agree. The oracle is the checker here,
+    not the thing measured."""
+    import forja_b200 as fb
+    from oracle import engine, fjo
+    starts, tokens = lanes.descriptors()
+    active = np.nonzero(tokens)[0]
+    if active.size == 0:
+        return None
+    lane = int(active[np.argmin(starts[active])])
+    start = int(starts[lane])
+    table = pool.table(lane)
+    bound = int((table[:, 1] != 0xFFFFFFFF).sum())
+    ref = engine.DenseOracle(cfg, None, bound + 1, PAGE, weight_bits=random_weights_bf16(cfg, args.seed))
+    own_table, generations = engine.copy_lane_cache(ref, model.kv_pages, table, start, compact=True)
+    logits = be.alloc(fb.BF16, (args.lanes, cfg["vocab"]))
+    pool.pack_step(starts, tokens)
+    got_tokens = model.step(host_tokens[tokens > 0], want_tokens=True, lanes=args.lanes, logits=logits)
+    lanes.advance()
+    got = fjo.decode(be.read(logits)[lane], fjo.BF16)
+    fjo.set_threads(fjo.max_threads())
+    want, want_token = ref.forward_lane([int(host_tokens[lane])], start, own_table, generations)
+    fjo.set_threads(1)
+    err = float(np.max(np.abs(got - want)) / np.max(np.abs(want)))
+    return {"lane": lane, "context": start, "max_abs_rel": err, "bound": 2e-2, "within_bound": bool(err <= 2e-2),
+            "token_equal": bool(int(got_tokens[lane]) == want_token), "gpu_token": int(got_tokens[lane]), "cpu_token": int(want_token),
+            "logit_gap_of_the_two_tokens_rel": float(abs(got[int(got_tokens[lane])] - got[want_token]) / np.max(np.abs(got)))}
 
 
 def sum_weight_params(cfg):

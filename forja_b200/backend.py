@@ -524,6 +524,15 @@ class DenseModel:
     def fill_kv(self, seed: int = 0):
         _check(self._lib.fj_dense_fill_kv(self._h, seed))
 
+    def kv_pages(self, layer: int, plane: int, first_page: int, count: int, data: Optional[np.ndarray] = None) -> np.ndarray:
+        """Reads (data None) or writes the rows of `count` consecutive physical pages of one layer's K (plane 0) or V (plane 1)
+        plane; storage values [count, page_tokens, kv_heads * head_dim] (bf16/f16 as uint16 bit patterns)."""
+        cfg = self.config
+        shape = (count, self.pool.page_tokens, cfg["kv_heads"] * cfg["head_dim"])
+        host = np.empty(shape, NP_OF[cfg["dtype"]]) if data is None else np.ascontiguousarray(data, NP_OF[cfg["dtype"]]).reshape(shape)
+        _check(self._lib.fj_dense_kv_pages(self._h, layer, plane, first_page, count, host.ctypes.data_as(C.c_void_p), 0 if data is None else 1))
+        return host
+
     def copy_page(self, src_page: int, dst_page: int, tokens: int):
         _check(self._lib.fj_dense_copy_page(self._h, src_page, dst_page, tokens))
 

@@ -577,6 +577,21 @@ int32_t fj_dense_copy_page(fj_dense_model* m, uint32_t src_page, uint32_t dst_pa
   return cuda_status(cudaGetLastError());
 }
 
+int32_t fj_dense_kv_pages(fj_dense_model* m, uint32_t layer, uint32_t plane, uint32_t first_page, uint32_t count, void* host, uint32_t to_device) {
+  if (!m || !host || layer >= m->layers.size() || plane > 1) return FJ_INVALID_INPUT;
+  fj_backend* be = m->be;
+  const fj::KvPoolDevice& pool = m->pool->dev;
+  if (first_page > pool.physical_pages || count > pool.physical_pages - first_page) return FJ_INVALID_INPUT;
+  if (count == 0) return FJ_OK;
+  std::lock_guard<std::mutex> lock(be->mutex);
+  cudaSetDevice(be->device);
+  const size_t page_bytes = static_cast<size_t>(pool.page_tokens) * m->cfg.kv_heads * m->cfg.head_dim * fj::dtype_size(static_cast<int>(m->cfg.dtype));
+  char* dev = static_cast<char*>(plane == 0 ? m->layers[layer].k_plane : m->layers[layer].v_plane) + first_page * page_bytes;
+  if (to_device) cudaMemcpyAsync(dev, host, count * page_bytes, cudaMemcpyHostToDevice, be->stream);
+  else cudaMemcpyAsync(host, dev, count * page_bytes, cudaMemcpyDeviceToHost, be->stream);
+  return cuda_status(cudaStreamSynchronize(be->stream));
+}
+
 int32_t fj_dense_step_stats(fj_dense_model* m, uint64_t* kernels, uint64_t* attn_work_items) {
   if (!m) return FJ_INVALID_INPUT;
   if (kernels) *kernels = m->last_kernels;

@@ -314,6 +314,13 @@ int32_t fj_dense_step(fj_dense_model* model, const uint32_t* token_ids, uint32_t
 /* Copies the first `tokens` K/V rows of page src_page to page dst_page in every layer (the data half of cow_tail). */
 int32_t fj_dense_copy_page(fj_dense_model* model, uint32_t src_page, uint32_t dst_page, uint32_t tokens);
 int32_t fj_dense_step_stats(fj_dense_model* model, uint64_t* kernels, uint64_t* attn_work_items);
+/* Host access to the model's KV planes (which the library owns, like the host-owned page planes of
+ * crates/forja-host/src/lib.rs:4323-4360): copies the rows of `count` consecutive physical pages of
+ * one layer's K plane (plane 0) or V plane (plane 1) to host memory (to_device 0) or from it
+ * (to_device 1); page_tokens * kv_heads * head_dim elements of the model dtype per page.
+ * Synchronous; for checkpointing a sequence's cache and for checkers that replay a lane elsewhere. */
+int32_t fj_dense_kv_pages(fj_dense_model* model, uint32_t layer, uint32_t plane, uint32_t first_page, uint32_t count,
+                          void* host, uint32_t to_device);
 /* Fills every K/V plane of the model with seeded pseudo-random N(0, 1) values in the plane dtype
  * (synthetic contexts for benchmarks: any page a lane is given already holds finite random rows). */
 int32_t fj_dense_fill_kv(fj_dense_model* model, uint64_t seed);

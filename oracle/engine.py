@@ -267,3 +267,34 @@ def ep_moe_layer(rank: int, world: int, cfg: dict, normed, residual, L_local: di
             total = (total + (weights[r, j] * returned[route_slot[r, j]]).astype(np.float32)).astype(np.float32)
         out[r] = fjo.encode((total + res[r]).astype(np.float32), fjo.BF16)
     return out
+
+
+def copy_lane_cache(oracle, read_pages, table: np.ndarray, tokens: int, compact: bool = False):
+    """Copies the K/V rows a lane holds on the device into ``oracle``'s planes, page by page, so that
+    the CPU replay of that lane starts from the very cache contents the device kernel reads.
+    ``read_pages(layer, plane, first_page, count)`` returns [count, page_tokens, kv_dim] storage values
+    (plane 0 = K, 1 = V); ``table`` is the lane's page table [table_pages, 2]; ``tokens`` = rows in use.
+    ``compact``: the oracle's planes hold only this lane (its i-th bound page becomes oracle page i), for
+    device pools too large to mirror on the host. Returns (table, generations) to replay the lane with."""
+    bound = int((table[:, 1] != 0xFFFFFFFF).sum())
+    used = (tokens + oracle.page_tokens - 1) // oracle.page_tokens
+    pages = [int(p) for p in table[:used, 0]]
+    runs, i = [], 0
+    while i < len(pages):  # runs of consecutive physical pages: one device read each
+        j = i
+        while j + 1 < len(pages) and pages[j + 1] == pages[j] + 1:
+            j += 1
+        runs.append((i, pages[i], j - i + 1))
+        i = j + 1
+    for layer in range(oracle.cfg["layers"]):
+        for plane, planes in ((0, oracle.k_planes), (1, oracle.v_planes)):
+            for index, first, count in runs:
+                dst = index if compact else first
+                planes[layer][dst:dst + count] = read_pages(layer, plane, first, count)
+    if not compact:
+        return table, None
+    own = table.copy()
+    own[:bound, 0] = np.arange(bound, dtype=np.uint32)
+    generations = np.zeros(oracle.k_planes[0].shape[0], np.uint32)
+    generations[:bound] = table[:bound, 1]
+    return own, generations

@@ -322,3 +322,56 @@ def test_forked_lane_decodes_like_a_lane_that_prefilled_the_prompt_itself():
     fjo.set_threads(1)
     model.close()
     pool.close()
+
+
+QWEN3_06B = dict(dtype=fb.BF16, layers=28, hidden=1024, q_heads=16, kv_heads=8, head_dim=128, intermediate=3072, vocab=151936, qk_norm=1, eps=1e-6, theta=1e6, max_rows=8)
+
+
+def test_qwen3_06b_shape_decode_matches_oracle_at_full_size():
+    """The benchmarked configuration at its real size (28 layers, hidden 1024, 16 q / 8 kv heads, vocabulary
+    151 936, bf16): four lanes whose synthetic contexts span the benchmark's range decode three steps. Both sides
+    start from the same cache contents (the device fills its planes with seeded N(0, 1) values, the lanes' pages are
+    copied into the oracle) and the same bf16 weights. Logits: max-abs rel <= 2e-2 for every lane and step. Greedy
+    tokens: equal, or the two candidates are a near-tie of the logits (bf16 rounding decides between them); the
+    oracle's token is fed back on both sides so that a flip does not change the next step's inputs."""
+    import bench
+    cfg, page, steps = QWEN3_06B, 16, 3
+    contexts = [130, 1141, 1810, 8000]
+    lanes = len(contexts)
+    be = backend()
+    table_pages = (max(contexts) + steps + page - 1) // page + 1
+    physical = sum((n + steps + page - 1) // page for n in contexts) + 3
+    pool = fb.KvPool(be, page, physical, lanes, table_pages)
+    assert all(s == 0 for s in pool.reserve(list(range(lanes)), [n + steps for n in contexts]))
+    bits = bench.random_weights_bf16(cfg, 0)
+    up = lambda a: be.tensor_from(a, fb.BF16)
+    model = fb.DenseModel(be, pool, cfg, up(bits["embed"]), up(bits["final_norm"]), [{k: up(v) for k, v in layer.items()} for layer in bits["layers"]])
+    model.fill_kv(5)
+    ref = engine.DenseOracle(cfg, None, physical, page, weight_bits=bits)
+    tables, generations = [pool.table(lane) for lane in range(lanes)], pool.generations()
+    for lane in range(lanes):
+        engine.copy_lane_cache(ref, model.kv_pages, tables[lane], contexts[lane])
+    rng = np.random.default_rng(9)
+    feed = rng.integers(0, cfg["vocab"], lanes).astype(np.uint32)
+    logits = be.alloc(fb.BF16, (lanes, cfg["vocab"]))
+    positions, worst, flips = list(contexts), 0.0, 0
+    fjo.set_threads(fjo.max_threads())
+    for step in range(steps):
+        pool.pack_step(positions, [1] * lanes)
+        tokens = model.step(feed, lanes=lanes, logits=logits)
+        got = down(logits)
+        want_tokens = []
+        for lane in range(lanes):
+            want, token = ref.forward_lane([int(feed[lane])], positions[lane], tables[lane], generations)
+            err = max_abs_rel(got[lane], want)
+            worst = max(worst, err)
+            assert err <= 2e-2, f"step {step} lane {lane} (context {contexts[lane]}): logits max-abs rel {err:.3e}"
+            want_tokens.append(token)
+        flips += check_tokens(tokens, want_tokens, got, strict=False)
+        feed = np.array(want_tokens, np.uint32)
+        positions = [p + 1 for p in positions]
+    fjo.set_threads(1)
+    print(f"qwen3-0.6b shape: worst logits max-abs rel {worst:.3e}, greedy flips {flips} of {lanes * steps}")
+    assert flips <= 1
+    model.close()
+    pool.close()
