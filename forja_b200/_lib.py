@@ -32,6 +32,11 @@ class FjDispatchProfile(C.Structure):
     _fields_ = [("op", C.c_uint32), ("kernels", C.c_uint32), ("ns", C.c_uint64)]
 
 
+class FjWeightTensor(C.Structure):
+    _fields_ = [("name", C.c_char_p), ("dtype", C.c_uint32), ("rank", C.c_uint32), ("shape", C.c_uint32 * 8), ("byte_offset", C.c_uint64),
+                ("byte_len", C.c_uint64), ("dtype_aligned", C.c_uint32)]
+
+
 class FjPackView(C.Structure):
     _fields_ = [("rows", C.c_uint32), ("lanes", C.c_uint32), ("logical_lengths", C.c_uint64), ("query_starts", C.c_uint64),
                 ("absolute_positions", C.c_uint64), ("activity", C.c_uint64), ("cu_seqlens", C.c_uint64), ("positions", C.c_uint64),
@@ -77,6 +82,9 @@ EXPORTS = [
     "fj_paged_decode_attention_static", "fj_sched_create", "fj_sched_destroy", "fj_sched_set_prompt_chunk_multiple", "fj_sched_enqueue",
     "fj_sched_reconcile_active", "fj_sched_complete", "fj_sched_retry_admission", "fj_sched_admit", "fj_sched_admit_pages",
     "fj_sched_decode_bucket", "fj_sched_ready_prompt", "fj_sched_prompt_batch", "fj_sched_waiting", "fj_sched_active",
+    "fj_safetensors_open", "fj_safetensors_open_all", "fj_safetensors_close", "fj_safetensors_tensor_count", "fj_safetensors_shard_name",
+    "fj_safetensors_file_len", "fj_safetensors_data_start", "fj_safetensors_tensor", "fj_safetensors_find", "fj_weights_last_error",
+    "fj_safetensors_import", "fj_safetensors_view", "fj_safetensors_quant_views",
     "fj_prompt_chunk_work", "fj_prompt_chunk_merged_work", "fj_reservations_fit", "fj_prefill_plan",
     "fj_ep_load", "fj_ep_unique_id", "fj_ep_create", "fj_ep_destroy", "fj_ep_all_to_all", "fj_moe_model_create", "fj_moe_model_destroy",
     "fj_moe_step", "fj_moe_step_stats", "fj_fill_random", "fj_tcgen05_wait_giveups", "fj_moe_capture_routes", "fj_moe_read_routes", "fj_moe_phase_timing", "fj_moe_read_phase_ms",
@@ -146,6 +154,11 @@ def load():
         "fj_sched_admit_pages": ([P, U32, P, P, U64], U64), "fj_sched_decode_bucket": ([P, P, U64], C.c_int64),
         "fj_sched_ready_prompt": ([P, U64, U32], None), "fj_sched_prompt_batch": ([P, I32, P, P, U64], U64),
         "fj_sched_waiting": ([P], U64), "fj_sched_active": ([P], U64),
+        "fj_safetensors_open": ([C.c_char_p, P], I32), "fj_safetensors_open_all": ([C.c_char_p, P, U32, P], I32), "fj_safetensors_close": ([P], None),
+        "fj_safetensors_tensor_count": ([P], U32), "fj_safetensors_shard_name": ([P], C.c_char_p), "fj_safetensors_file_len": ([P], U64),
+        "fj_safetensors_data_start": ([P], U64), "fj_safetensors_tensor": ([P, U32, P], I32), "fj_safetensors_find": ([P, C.c_char_p, P], I32),
+        "fj_weights_last_error": ([], C.c_char_p), "fj_safetensors_import": ([P, P, P], I32), "fj_safetensors_view": ([P, C.c_char_p, U64, P], I32),
+        "fj_safetensors_quant_views": ([P, C.c_char_p, U64, U32, U32, P, P, P], I32),
         "fj_prompt_chunk_work": ([U32, U32, U32], U32), "fj_prompt_chunk_merged_work": ([U32, U32, U32], U32),
         "fj_reservations_fit": ([U32, U32, P, U64], I32), "fj_prefill_plan": ([U32, U32, U32, P, U64], U64),
         "fj_ep_load": ([C.c_char_p], I32), "fj_ep_unique_id": ([P], I32), "fj_ep_create": ([P, P, U32, U32, P], I32), "fj_ep_destroy": ([P], None),

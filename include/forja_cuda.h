@@ -35,7 +35,18 @@ typedef enum fj_status {
   FJ_TIMEOUT = 6,
   FJ_INVALID_INPUT = 7,
   FJ_UNSUPPORTED_OPERATION = 8,
-  FJ_INDEX_OUT_OF_RANGE = 9       /* fj_device_error.value = lowest offending index */
+  FJ_INDEX_OUT_OF_RANGE = 9,      /* fj_device_error.value = lowest offending index */
+  /* WeightError, crates/forja-host/src/weights.rs:337-358 (returned by the fj_safetensors_* calls only) */
+  FJ_WEIGHTS_IO = 20,
+  FJ_WEIGHTS_NOT_REGULAR_FILE = 21,
+  FJ_WEIGHTS_MAPPING = 22,
+  FJ_WEIGHTS_TRUNCATED = 23,
+  FJ_WEIGHTS_INVALID_HEADER = 24,
+  FJ_WEIGHTS_INVALID_INDEX = 25,
+  FJ_WEIGHTS_HEADER_TOO_LARGE = 26,
+  FJ_WEIGHTS_UNSUPPORTED_DTYPE = 27,
+  FJ_WEIGHTS_INVALID_RANGE = 28,
+  FJ_WEIGHTS_OVERLAPPING_RANGES = 29
 } fj_status;
 
 /* dtype, wit/compute.wit:4-10 */
@@ -189,6 +200,51 @@ uint64_t fj_kernel_launch_count(fj_backend* be);
 int32_t fj_timer_create(fj_backend* be, uint64_t* timer);
 int32_t fj_timer_record(fj_backend* be, uint64_t timer);
 int32_t fj_timer_elapsed_ns(fj_backend* be, uint64_t start_timer, uint64_t stop_timer, uint64_t* ns);
+
+/* ---- weight sources: safetensors import, crates/forja-host/src/weights.rs ------------------- */
+
+/* WeightTensor, weights.rs:27-84. `name` points into the source and lives as long as it. */
+typedef struct fj_weight_tensor {
+  const char* name;
+  uint32_t dtype;        /* fj_dtype: F32, F16, BF16 or U32 (anything else is FJ_WEIGHTS_UNSUPPORTED_DTYPE at open) */
+  uint32_t rank;
+  uint32_t shape[8];
+  uint64_t byte_offset;  /* from the start of the data region */
+  uint64_t byte_len;
+  uint32_t dtype_aligned; /* is_dtype_aligned, weights.rs:72 */
+} fj_weight_tensor;
+typedef struct fj_safetensors fj_safetensors;
+
+/* Safetensors::open (weights.rs:175-226): validates one file - regular file, 8-byte length prefix, header of at
+ * most 100 MiB, JSON object without duplicate names (nesting deeper than 128 is refused), supported dtypes, byte
+ * ranges equal to shape x element size, inside the file and non-overlapping. Tensors are kept sorted by offset.
+ * Host-only: needs no device. On failure fj_weights_last_error() holds the message for the calling thread. */
+int32_t fj_safetensors_open(const char* path, fj_safetensors** out);
+/* Safetensors::open_all (weights.rs:114-168): `path` ending in .json is a shard index {"weight_map": {tensor: file}}
+ * (at most 100 MiB, at most 1024 shards, shard names without separators ending in .safetensors, resolving inside the
+ * index's directory, each shard holding exactly the tensors the map assigns to it); shards come back ordered by
+ * file name. Any other path opens as a single file. *count receives the number of sources; FJ_QUOTA_EXCEEDED when
+ * `cap` is too small (nothing is returned then). */
+int32_t fj_safetensors_open_all(const char* path, fj_safetensors** out, uint32_t cap, uint32_t* count);
+void fj_safetensors_close(fj_safetensors* source);
+uint32_t fj_safetensors_tensor_count(const fj_safetensors* source);
+const char* fj_safetensors_shard_name(const fj_safetensors* source); /* NULL for an unsharded file (weights.rs:235) */
+uint64_t fj_safetensors_file_len(const fj_safetensors* source);      /* weights.rs:241 */
+uint64_t fj_safetensors_data_start(const fj_safetensors* source);
+int32_t fj_safetensors_tensor(const fj_safetensors* source, uint32_t index, fj_weight_tensor* out);
+int32_t fj_safetensors_find(const fj_safetensors* source, const char* name, fj_weight_tensor* out);
+const char* fj_weights_last_error(void);
+/* mapped_region + import_readonly (weights.rs:326-333, crates/forja-host/src/lib.rs:5885-5900): maps the file,
+ * refuses it when its length changed since validation, and copies the data region into one read-only buffer. */
+int32_t fj_safetensors_import(fj_backend* be, const fj_safetensors* source, uint64_t* buffer);
+/* WeightTensor::layout (weights.rs:76-83): the named tensor as a contiguous view of the imported buffer. */
+int32_t fj_safetensors_view(const fj_safetensors* source, const char* name, uint64_t buffer, fj_tensor* out);
+/* An MLX affine-quantised matrix (or stack of expert matrices) by checkpoint prefix: `<prefix>.weight` u32
+ * [.., out, in * bits / 32], `<prefix>.scales` and `<prefix>.biases` f16/bf16 [.., out, in / group_size]
+ * (engines/qwen3-coder/src/lib.rs:174-188, 430-437); shapes and dtypes are cross-checked like
+ * QuantizedMatrix::new (crates/forja-core/src/quantized.rs:78-121). */
+int32_t fj_safetensors_quant_views(const fj_safetensors* source, const char* prefix, uint64_t buffer, uint32_t bits,
+                                   uint32_t group_size, fj_tensor* packed, fj_tensor* scales, fj_tensor* biases);
 
 /* ---- fast path: device-resident ragged batching -------------------------------------------- */
 
