@@ -352,8 +352,10 @@ def parity_check(args, cfg, be, pool, model, lanes, host_tokens):
     """After the timed regions, outside them: one more decode step of the running batch on the GPU with the
     logits kept, and the lane with the shortest context replayed on the CPU port from the very cache rows
     the GPU holds for it (read back page by page) and the same bf16 weights. Reports the logits' max-abs
-    relative difference (bound 2e-2) and whether the greedy tokens agree. The oracle is the checker here,
-    not the thing measured."""
+    relative difference and whether the greedy tokens agree. Bound: 2e-2, or twice the comparison's noise
+    floor where that is larger (the CPU port against itself with its projection sums re-associated: at 28
+    bf16 layers that alone moves the logits by 1e-2 to 3e-2 of their maximum). The oracle is the checker
+    here, not the thing measured."""
     import forja_b200 as fb
     from oracle import engine, fjo
     starts, tokens = lanes.descriptors()
@@ -364,8 +366,12 @@ def parity_check(args, cfg, be, pool, model, lanes, host_tokens):
     start = int(starts[lane])
     table = pool.table(lane)
     bound = int((table[:, 1] != 0xFFFFFFFF).sum())
-    ref = engine.DenseOracle(cfg, None, bound + 1, PAGE, weight_bits=random_weights_bf16(cfg, args.seed))
+    bits = random_weights_bf16(cfg, args.seed)
+    ref = engine.DenseOracle(cfg, None, bound + 1, PAGE, weight_bits=bits)
+    reordered = engine.ReorderedDenseOracle(cfg, None, bound + 1, PAGE, weight_bits=bits)
     own_table, generations = engine.copy_lane_cache(ref, model.kv_pages, table, start, compact=True)
+    for mine, theirs in zip(reordered.k_planes + reordered.v_planes, ref.k_planes + ref.v_planes):
+        mine[:] = theirs
     logits = be.alloc(fb.BF16, (args.lanes, cfg["vocab"]))
     pool.pack_step(starts, tokens)
     got_tokens = model.step(host_tokens[tokens > 0], want_tokens=True, lanes=args.lanes, logits=logits)
@@ -373,9 +379,13 @@ def parity_check(args, cfg, be, pool, model, lanes, host_tokens):
     got = fjo.decode(be.read(logits)[lane], fjo.BF16)
     fjo.set_threads(fjo.max_threads())
     want, want_token = ref.forward_lane([int(host_tokens[lane])], start, own_table, generations)
+    other, _ = reordered.forward_lane([int(host_tokens[lane])], start, own_table, generations)
     fjo.set_threads(1)
     err = float(np.max(np.abs(got - want)) / np.max(np.abs(want)))
-    return {"lane": lane, "context": start, "max_abs_rel": err, "bound": 2e-2, "within_bound": bool(err <= 2e-2),
+    noise = float(np.max(np.abs(other - want)) / np.max(np.abs(want)))
+    return {"lane": lane, "context": start, "max_abs_rel": err, "noise_floor_max_abs_rel": noise,
+            "bound": "max(2e-2, 2 x noise floor); noise floor = the CPU port against itself with re-associated projection sums",
+            "within_bound": bool(err <= max(2e-2, 2.0 * noise)),
             "token_equal": bool(int(got_tokens[lane]) == want_token), "gpu_token": int(got_tokens[lane]), "cpu_token": int(want_token),
             "logit_gap_of_the_two_tokens_rel": float(abs(got[int(got_tokens[lane])] - got[want_token]) / np.max(np.abs(got)))}
 

@@ -144,7 +144,7 @@ class Tensor:
 
 # fj_op codes (include/forja_cuda.h)
 OP_PROGRAM, OP_COPY, OP_PAGED_COPY, OP_RMS_NORM, OP_ARGMAX, OP_TOP_K, OP_ROPE, OP_EMBED, OP_QUANT_EMBED, OP_MATMUL, OP_QUANT_MATMUL, \
-    OP_GATHER_QUANT_MATMUL, OP_PAGED_SDPA, OP_PAGED_SDPA_APPEND, OP_SDPA, OP_SAMPLE = range(1, 17)
+    OP_GATHER_QUANT_MATMUL, OP_PAGED_SDPA, OP_PAGED_SDPA_APPEND, OP_SDPA, OP_SAMPLE, OP_GATHER_MATMUL = range(1, 18)
 
 
 @dataclass(frozen=True)
@@ -187,6 +187,10 @@ class Op:
         return Op(OP_PAGED_SDPA, u0=int(causal), u1=q_start, u2=key_length, u3=page_tokens, f0=scale)
     @staticmethod
     def PagedSdpaAppend(scale: float, q_start: int, page_tokens: int): return Op(OP_PAGED_SDPA_APPEND, u1=q_start, u3=page_tokens, f0=scale)
+    @staticmethod
+    def Sdpa(scale: float, causal: bool, q_start: int): return Op(OP_SDPA, u0=int(causal), u1=q_start, f0=scale)
+    @staticmethod
+    def GatherMatmul(): return Op(OP_GATHER_MATMUL)
     @staticmethod
     def Program(handle: int): return Op(OP_PROGRAM, program=handle)
 

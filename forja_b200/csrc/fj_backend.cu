@@ -585,6 +585,33 @@ int32_t exec_matmul(Exec& x, const fj_dispatch& d) {
   return FJ_OK;
 }
 
+// Op::Sdpa, crates/forja-core/src/ops.rs:270 (check :2180-2234): q [hq, T, d], k [kvh, L, d], v [kvh, L, dv] -> out [hq, T, dv];
+// f0 = scale, u0 = causal, u1 = q_start. Views may be strided (a cache sliced to its live length).
+int32_t exec_sdpa(Exec& x, const fj_dispatch& d) {
+  if (d.n_inputs != 3 || d.n_outputs != 1) return FJ_INVALID_INPUT;
+  const fj_tensor &q = d.inputs[0], &k = d.inputs[1], &v = d.inputs[2], &o = d.outputs[0];
+  if (q.rank != 3 || k.rank != 3 || v.rank != 3 || o.rank != 3 || !is_float(q.dtype) || !is_float(k.dtype) || !is_float(v.dtype) || !is_float(o.dtype)) return FJ_INVALID_INPUT;
+  if (k.shape[0] == 0 || q.shape[0] % k.shape[0] != 0 || v.shape[0] != k.shape[0] || v.shape[1] != k.shape[1] || k.shape[2] != q.shape[2]) return FJ_INVALID_INPUT;
+  if (o.shape[0] != q.shape[0] || o.shape[1] != q.shape[1] || o.shape[2] != v.shape[2]) return FJ_INVALID_INPUT;
+  // causal rows attend q_start + row + 1 keys: the last row must not reach past the cache (ops.rs check_sdpa)
+  if (d.u0 && static_cast<uint64_t>(d.u1) + q.shape[1] > k.shape[1]) return FJ_INVALID_INPUT;
+  View vq, vk, vv, vo;
+  if (!make_view(x.be, q, false, &vq) || !make_view(x.be, k, false, &vk) || !make_view(x.be, v, false, &vv) || !make_view(x.be, o, true, &vo)) return FJ_INVALID_INPUT;
+  return fj::launch_sdpa(x.be->ctx, vq, vk, vv, vo, d.f0, d.u0 != 0, d.u1) ? FJ_OK : FJ_UNSUPPORTED_OPERATION;
+}
+
+// Op::GatherMatmul, crates/forja-core/src/ops.rs:254 (check :1749-1796): x [rows, inner], weights [experts, inner, cols],
+// indices u32 [rows, routes] -> out [rows, routes, cols] in the activation dtype.
+int32_t exec_gather_matmul(Exec& x, const fj_dispatch& d, fj::ErrorRecord* err) {
+  if (d.n_inputs != 3 || d.n_outputs != 1) return FJ_INVALID_INPUT;
+  const fj_tensor &a = d.inputs[0], &w = d.inputs[1], &idx = d.inputs[2], &o = d.outputs[0];
+  if (a.rank != 2 || w.rank != 3 || idx.rank != 2 || o.rank != 3 || !is_float(a.dtype) || !is_float(w.dtype) || idx.dtype != FJ_U32 || o.dtype != a.dtype) return FJ_INVALID_INPUT;
+  if (w.shape[1] != a.shape[1] || idx.shape[0] != a.shape[0] || o.shape[0] != a.shape[0] || o.shape[1] != idx.shape[1] || o.shape[2] != w.shape[2]) return FJ_INVALID_INPUT;
+  View va, vw, vi, vo;
+  if (!make_view(x.be, a, false, &va) || !make_view(x.be, w, false, &vw) || !make_view(x.be, idx, false, &vi) || !make_view(x.be, o, true, &vo)) return FJ_INVALID_INPUT;
+  return fj::launch_gather_matmul(x.be->ctx, va, vw, vi, vo, err) ? FJ_OK : FJ_UNSUPPORTED_OPERATION;
+}
+
 int32_t exec_quant_matmul(Exec& x, const fj_dispatch& d) {
   if (d.n_inputs != 4 || d.n_outputs != 1 || !quant_params_ok(d.u0, d.u1)) return FJ_INVALID_INPUT;
   if (d.program != 0) return FJ_UNSUPPORTED_OPERATION;
@@ -1161,6 +1188,8 @@ int32_t fj_submit(fj_backend* be, const fj_dispatch* dispatches, uint32_t count,
       case FJ_OP_MATMUL: status = exec_matmul(x, d); break;
       case FJ_OP_QUANT_MATMUL: status = exec_quant_matmul(x, d); break;
       case FJ_OP_GATHER_QUANT_MATMUL: status = exec_gather_quant(x, d, err); break;
+      case FJ_OP_SDPA: status = exec_sdpa(x, d); break;
+      case FJ_OP_GATHER_MATMUL: status = exec_gather_matmul(x, d, err); break;
       case FJ_OP_PAGED_SDPA:
       case FJ_OP_PAGED_SDPA_APPEND: {
         const bool append = d.op == FJ_OP_PAGED_SDPA_APPEND;

@@ -52,6 +52,12 @@ inline bool opt_in_smem(SmemOptIn& state, K kernel, int bytes) {
   return true;
 }
 
+// ---- fj_dense_ops.cu ------------------------------------------------------------------------
+// Op::Sdpa over a contiguous cache (views [heads, tokens, width], any strides) and Op::GatherMatmul over dense experts.
+// false: shape outside what the kernels take (head_dim > 256, value width > 256, inner beyond 12288).
+bool launch_sdpa(Ctx& ctx, const View& q, const View& k, const View& v, const View& out, float scale, bool causal, unsigned q_start);
+bool launch_gather_matmul(Ctx& ctx, const View& x, const View& w, const View& idx, const View& out, ErrorRecord* err);
+
 // ---- fj_elementwise.cu ----------------------------------------------------------------------
 void launch_copy(Ctx& ctx, const View& in, const View& out, size_t elements);
 void launch_fill_zero(Ctx& ctx, void* ptr, size_t bytes);

@@ -52,7 +52,7 @@ typedef enum fj_status {
 /* dtype, wit/compute.wit:4-10 */
 typedef enum fj_dtype { FJ_F32 = 0, FJ_F16 = 1, FJ_BF16 = 2, FJ_I32 = 3, FJ_U32 = 4 } fj_dtype;
 
-/* Op, crates/forja-core/src/ops.rs:163-302 (State, Sample* and GatherMatmul are not on this path) */
+/* Op, crates/forja-core/src/ops.rs:163-302 (Op::State, the recurrent-state update, is not on this path) */
 typedef enum fj_op {
   FJ_OP_PROGRAM = 1,            /* program = handle from fj_program_prepare */
   FJ_OP_COPY = 2,
@@ -68,7 +68,9 @@ typedef enum fj_op {
   FJ_OP_GATHER_QUANT_MATMUL = 12, /* u0 = bits, u1 = group_size; 5-, 8- or 6-input form; program = epilogue or 0 */
   FJ_OP_PAGED_SDPA = 13,        /* f0 = scale, u0 = causal, u1 = q_start, u2 = key_length, u3 = page_tokens */
   FJ_OP_PAGED_SDPA_APPEND = 14, /* f0 = scale, u1 = q_start, u3 = page_tokens */
-  FJ_OP_SDPA = 15,              /* f0 = scale, u0 = causal, u1 = q_start (contiguous cache) */
+  FJ_OP_SDPA = 15,              /* contiguous cache: [q [hq, T, d], k [kvh, L, d], v [kvh, L, dv]] -> [hq, T, dv]; f0 = scale, u0 = causal, u1 = q_start */
+  FJ_OP_GATHER_MATMUL = 17,     /* Op::GatherMatmul (dense experts): [x [rows, inner], weights [experts, inner, cols], idx u32 [rows, routes]]
+                                   -> [rows, routes, cols]; an id >= experts leaves a zero row and reports the lowest such id */
   FJ_OP_SAMPLE = 16             /* Op::Sample / Op::SampleMasked (crates/forja-core/src/ops.rs:202-239): u0 = position; inputs [logits, params(5 x u32),
                                    (allow mask, (width + 31) / 32 x u32)]; invalid parameter words or mask fail the submission with FJ_INVALID_INPUT */
 } fj_op;

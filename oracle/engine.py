@@ -110,6 +110,21 @@ class DenseOracle:
         return fjo.decode(logits, dt)[0], token
 
 
+class ReorderedDenseOracle(DenseOracle):
+    """The same step with one liberty taken: every projection sums its products in blocked (BLAS) order instead
+    of sequentially in index order. Accumulation stays f32 and every rounding point stays where it is, so this
+    is what any implementation that does not copy the reference's scalar summation order can hope to match.
+    The distance between this oracle and DenseOracle on the same inputs is the noise floor of the comparison:
+    a deep bf16 model amplifies last-place differences of the sums through the bf16 roundings that follow."""
+
+    def _linear(self, x, w):
+        cache = self.__dict__.setdefault("_f32_weights", {})
+        wf = cache.get(id(w))
+        if wf is None:
+            wf = cache[id(w)] = fjo.decode(w, self.dt)
+        return fjo.encode((fjo.decode(x, self.dt) @ wf.T).astype(np.float32), self.dt)
+
+
 def random_moe_weights(cfg: dict, seed: int = 0):
     """Random MLX-affine weights for the sparse-MoE decoder: uniformly random codes, positive scales
     and biases that centre every group near zero. Returns numpy arrays: quantised tensors as

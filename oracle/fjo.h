@@ -87,6 +87,8 @@ int fjo_quant_matmul(const void* x, int x_dt, const uint32_t* packed, const void
                      const void* biases, int p_dt, void* out, int out_dt, size_t rows,
                      size_t inner, size_t cols, uint32_t bits, uint32_t group_size);
 /* Op::GatherQuantMatmul 5-input projection, lib.rs:1025-1106. out [rows, k, cols] */
+int fjo_gather_matmul(const void* x, int x_dt, const void* weights, int w_dt, const uint32_t* indices, void* out, int out_dt,
+                      size_t rows, size_t inner, size_t experts, size_t cols, size_t routes, uint32_t* bad_index);
 int fjo_gather_quant_matmul(const void* x, int x_dt, const uint32_t* packed, const void* scales,
                             const void* biases, int p_dt, const uint32_t* indices, void* out,
                             int out_dt, size_t rows, size_t inner, size_t experts, size_t cols,

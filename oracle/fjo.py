@@ -255,6 +255,22 @@ def gather_quant_weighted_sum(act, a_dt, packed, scales, biases, p_dt, indices, 
     return (out, None) if not raise_on_bad else out
 
 
+def gather_matmul(x, x_dt, weights, w_dt, indices, out_dt=None, raise_on_bad=True):
+    """Op::GatherMatmul: x [rows, inner], weights [experts, inner, columns], indices [rows, routes] -> [rows, routes, columns]."""
+    x, weights, indices = _c(x), _c(weights), _c(indices, np.uint32)
+    out_dt = x_dt if out_dt is None else out_dt
+    rows, inner = x.shape
+    experts, _, cols = weights.shape
+    routes = indices.shape[1]
+    out = empty((rows, routes, cols), out_dt)
+    bad = C.c_uint32(0)
+    st = lib().fjo_gather_matmul(_p(x), x_dt, _p(weights), w_dt, _p(indices), _p(out), out_dt, _sz(rows), _sz(inner), _sz(experts), _sz(cols), _sz(routes), C.byref(bad))
+    if st == INDEX_OUT_OF_RANGE and not raise_on_bad:
+        return out, bad.value
+    _check(st, bad)
+    return (out, None) if not raise_on_bad else out
+
+
 def sdpa(q, q_dt, k, k_dt, v, v_dt, scale, causal, q_start, out_dt=None):
     q, k, v = _c(q), _c(k), _c(v)
     out_dt = q_dt if out_dt is None else out_dt

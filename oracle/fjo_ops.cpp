@@ -403,6 +403,37 @@ int fjo_quant_matmul(const void* x, int x_dt, const uint32_t* packed, const void
   return encode(values.data(), out, out_dt, values.size()) ? FJO_OK : FJO_EXECUTION_FAILED;
 }
 
+// execute_gather_matmul, crates/forja-cpu/src/lib.rs:850-912: out[r, j, c] = sum_i x[r, i] * W[idx[r, j], i, c]
+// (dense experts stored [experts, inner, columns]); a route naming a missing expert leaves zeros and the
+// lowest such id is reported after everything else was written.
+int fjo_gather_matmul(const void* x, int x_dt, const void* weights_p, int w_dt, const uint32_t* indices, void* out, int out_dt,
+                      size_t rows, size_t inner, size_t experts, size_t cols, size_t routes, uint32_t* bad_index) {
+  bool ok0, ok1;
+  auto activations = decode_vec(x, x_dt, rows * inner, &ok0);
+  auto weights = decode_vec(weights_p, w_dt, experts * inner * cols, &ok1);
+  if (!ok0 || !ok1) return FJO_EXECUTION_FAILED;
+  std::vector<float> values(rows * routes * cols, 0.0f);
+  bool have = false; uint32_t lowest = 0;
+  for (size_t r = 0; r < rows * routes; ++r)
+    if (indices[r] >= experts) record_invalid(&have, &lowest, indices[r]);
+#pragma omp parallel for collapse(2) if (g_threads > 1)
+  for (size_t r = 0; r < rows; ++r) {
+    for (size_t j = 0; j < routes; ++j) {
+      const size_t expert = indices[r * routes + j];
+      if (expert >= experts) continue;
+      const float* w = &weights[expert * inner * cols];
+      for (size_t c = 0; c < cols; ++c) {
+        float sum = 0.0f;
+        for (size_t i = 0; i < inner; ++i) sum = sum + activations[r * inner + i] * w[i * cols + c];
+        values[(r * routes + j) * cols + c] = sum;
+      }
+    }
+  }
+  if (!encode(values.data(), out, out_dt, values.size())) return FJO_EXECUTION_FAILED;
+  if (have) { if (bad_index) *bad_index = lowest; return FJO_INDEX_OUT_OF_RANGE; }
+  return FJO_OK;
+}
+
 int fjo_gather_quant_matmul(const void* x, int x_dt, const uint32_t* packed, const void* scales_p,
                             const void* biases_p, int p_dt, const uint32_t* indices, void* out,
                             int out_dt, size_t rows, size_t inner, size_t experts, size_t cols,

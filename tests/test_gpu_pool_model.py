@@ -331,9 +331,14 @@ def test_qwen3_06b_shape_decode_matches_oracle_at_full_size():
     """The benchmarked configuration at its real size (28 layers, hidden 1024, 16 q / 8 kv heads, vocabulary
     151 936, bf16): four lanes whose synthetic contexts span the benchmark's range decode three steps. Both sides
     start from the same cache contents (the device fills its planes with seeded N(0, 1) values, the lanes' pages are
-    copied into the oracle) and the same bf16 weights. Logits: max-abs rel <= 2e-2 for every lane and step. Greedy
-    tokens: equal, or the two candidates are a near-tie of the logits (bf16 rounding decides between them); the
-    oracle's token is fed back on both sides so that a flip does not change the next step's inputs."""
+    copied into the oracle) and the same bf16 weights.
+
+    Bound on the logits (max-abs rel): 2e-2, or twice the noise floor of the comparison where that is larger. The
+    noise floor is measured here, per lane and step: the distance between the oracle and the same oracle with its
+    projection sums re-associated (ReorderedDenseOracle). At 28 bf16 layers that legal re-association alone moves the
+    logits by 1e-2 to 3e-2 of their maximum, so 2e-2 cannot be asked of anything that does not sum in the reference's
+    scalar order. Greedy tokens: equal, or the two candidates are a near-tie of the logits; the oracle's token is fed
+    back on every side so that a flip does not change the next step's inputs."""
     import bench
     cfg, page, steps = QWEN3_06B, 16, 3
     contexts = [130, 1141, 1810, 8000]
@@ -348,13 +353,16 @@ def test_qwen3_06b_shape_decode_matches_oracle_at_full_size():
     model = fb.DenseModel(be, pool, cfg, up(bits["embed"]), up(bits["final_norm"]), [{k: up(v) for k, v in layer.items()} for layer in bits["layers"]])
     model.fill_kv(5)
     ref = engine.DenseOracle(cfg, None, physical, page, weight_bits=bits)
+    reordered = engine.ReorderedDenseOracle(cfg, None, physical, page, weight_bits=bits)
     tables, generations = [pool.table(lane) for lane in range(lanes)], pool.generations()
     for lane in range(lanes):
         engine.copy_lane_cache(ref, model.kv_pages, tables[lane], contexts[lane])
+    for mine, theirs in zip(reordered.k_planes + reordered.v_planes, ref.k_planes + ref.v_planes):
+        mine[:] = theirs
     rng = np.random.default_rng(9)
     feed = rng.integers(0, cfg["vocab"], lanes).astype(np.uint32)
     logits = be.alloc(fb.BF16, (lanes, cfg["vocab"]))
-    positions, worst, flips = list(contexts), 0.0, 0
+    positions, flips, report = list(contexts), 0, []
     fjo.set_threads(fjo.max_threads())
     for step in range(steps):
         pool.pack_step(positions, [1] * lanes)
@@ -363,15 +371,18 @@ def test_qwen3_06b_shape_decode_matches_oracle_at_full_size():
         want_tokens = []
         for lane in range(lanes):
             want, token = ref.forward_lane([int(feed[lane])], positions[lane], tables[lane], generations)
-            err = max_abs_rel(got[lane], want)
-            worst = max(worst, err)
-            assert err <= 2e-2, f"step {step} lane {lane} (context {contexts[lane]}): logits max-abs rel {err:.3e}"
+            other, _ = reordered.forward_lane([int(feed[lane])], positions[lane], tables[lane], generations)
+            err, noise = max_abs_rel(got[lane], want), max_abs_rel(other, want)
+            report.append((step, contexts[lane], err, noise))
+            assert err <= max(2e-2, 2.0 * noise), f"step {step} lane {lane} (context {contexts[lane]}): logits max-abs rel {err:.3e}, noise floor {noise:.3e}"
             want_tokens.append(token)
         flips += check_tokens(tokens, want_tokens, got, strict=False)
         feed = np.array(want_tokens, np.uint32)
         positions = [p + 1 for p in positions]
     fjo.set_threads(1)
-    print(f"qwen3-0.6b shape: worst logits max-abs rel {worst:.3e}, greedy flips {flips} of {lanes * steps}")
+    for step, context, err, noise in report:
+        print(f"qwen3-0.6b shape, step {step}, context {context}: logits max-abs rel {err:.3e} (noise floor {noise:.3e})")
+    print(f"greedy flips {flips} of {lanes * steps}")
     assert flips <= 1
     model.close()
     pool.close()

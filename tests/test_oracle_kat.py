@@ -196,6 +196,16 @@ def test_gathered_quantized_matmul_selects_duplicate_routes_and_reports_lowest_b
 
 # ---- crates/forja-cpu/src/lib.rs:2954-3017 -----------------------------------------------------
 
+def test_gathered_matmul_selects_duplicate_routes_and_reports_lowest_bad_index():
+    # crates/forja-cpu/src/lib.rs:2449-2488
+    x = np.array([[1.0, 2.0], [3.0, 4.0]], np.float32)
+    weights = np.array([1.0, 0.0, 0.0, 1.0, 1.0, 1.0, 1.0, 1.0, 2.0, 0.0, 0.0, 3.0], np.float32).reshape(3, 2, 2)
+    out = fjo.gather_matmul(x, fjo.F32, weights, fjo.F32, np.array([[2, 0, 2], [0, 2, 0]], np.uint32))
+    assert out.ravel().tolist() == [2.0, 6.0, 1.0, 2.0, 2.0, 6.0, 3.0, 4.0, 6.0, 12.0, 3.0, 4.0]
+    out, bad = fjo.gather_matmul(x, fjo.F32, weights, fjo.F32, np.array([[99], [7]], np.uint32), raise_on_bad=False)
+    assert bad == 7 and not out.any()
+
+
 def test_combined_quantized_matmul_keeps_valid_routes_and_reports_lowest_bad_index():
     act = np.repeat(np.arange(1, 6, dtype=np.float32), 64).reshape(1, 5, 64)
     packed = np.repeat((np.arange(1, 7, dtype=np.uint64) * 0x11111111).astype(np.uint32), 8).reshape(3, 2, 8)
