@@ -49,6 +49,7 @@ def parse_args():
     ap.add_argument("--ctx-max", type=int, default=CTX_MAX, help="largest context length (lower it for profiler captures)")
     ap.add_argument("--layers", type=int, default=0, help="override the layer count (profiler captures only; 0 = the model's 28)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-graph-replay", action="store_true", help="launch every decode step kernel by kernel instead of replaying its recorded CUDA graph")
     return ap.parse_args()
 
 
@@ -231,6 +232,7 @@ def run_native(args):
     model = fb.DenseModel(be, pool, cfg, up(weights["embed"]), up(weights["final_norm"]), [{k: up(v) for k, v in layer.items()} for layer in weights["layers"]])
     del weights
     model.fill_kv(args.seed + 17 * rank)
+    model.graph_replay(not args.no_graph_replay)
     lanes = Lanes(pool, Requests(args.seed * 1000 + rank, args.ctx_max), args.lanes, args.pool_pages)
 
     def step_device():
@@ -331,6 +333,7 @@ def run_native(args):
                 "ms_per_step": e2e_elapsed / e2e_steps * 1e3, "mean_kv_tokens_per_step": e2e_kv_tokens / e2e_steps},
         "gpu_launches": int(launches),
         "health": {"tcgen05_wait_giveups": int(be.tcgen05_wait_giveups())},
+        "graph_replay": model.graph_stats(),
         "roofline": {"kernel": "attn_decode_mma_kernel (paged GQA decode attention, split-K)", "bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"],
                      "unit": "GB/s", "frac": (achieved / peaks["hbm_gbs"]) if achieved else None, "peak_source": peaks["source"],
                      "algorithmic_bytes_per_launch": per_launch_bytes, "launches": int(attn_launches), "avg_launch_us": attn_ns / max(attn_launches, 1) * 1e-3,

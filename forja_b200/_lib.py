@@ -78,7 +78,7 @@ EXPORTS = [
     "fj_timer_record", "fj_timer_elapsed_ns", "fj_kvpool_create", "fj_kvpool_destroy", "fj_kvpool_reserve", "fj_kvpool_release",
     "fj_kvpool_read_table", "fj_kvpool_read_generations", "fj_kvpool_read_free", "fj_kvpool_read_refcounts", "fj_kvpool_fork", "fj_kvpool_cow_tail", "fj_dense_copy_page", "fj_kvpool_tables_buffer",
     "fj_kvpool_generations_buffer", "fj_pack_step", "fj_dense_model_create", "fj_dense_model_destroy", "fj_dense_step",
-    "fj_dense_step_stats", "fj_dense_kv_pages", "fj_dense_fill_kv", "fj_dense_profile_attention", "fj_dense_attention_time",
+    "fj_dense_step_stats", "fj_dense_graph_replay", "fj_dense_graph_stats", "fj_dense_kv_pages", "fj_dense_fill_kv", "fj_dense_profile_attention", "fj_dense_attention_time",
     "fj_paged_decode_attention_static", "fj_sched_create", "fj_sched_destroy", "fj_sched_set_prompt_chunk_multiple", "fj_sched_enqueue",
     "fj_sched_reconcile_active", "fj_sched_complete", "fj_sched_retry_admission", "fj_sched_admit", "fj_sched_admit_pages",
     "fj_sched_decode_bucket", "fj_sched_ready_prompt", "fj_sched_prompt_batch", "fj_sched_waiting", "fj_sched_active",
@@ -137,7 +137,7 @@ def load():
         "fj_kvpool_read_table": [P, U32, P], "fj_kvpool_read_generations": [P, P], "fj_kvpool_read_free": [P, P, U32, P],
         "fj_kvpool_read_refcounts": [P, P], "fj_kvpool_fork": [P, U32, U64, U32, U64, U64], "fj_kvpool_cow_tail": [P, U32, U64, P], "fj_dense_copy_page": [P, U32, U32, U32],
         "fj_pack_step": [P, P, P, U32, P], "fj_dense_model_create": [P, P, U64, U64, P, P, P], "fj_dense_step": [P, P, P, U64],
-        "fj_dense_step_stats": [P, P, P], "fj_dense_kv_pages": [P, U32, U32, U32, U32, P, U32], "fj_dense_fill_kv": [P, U64], "fj_dense_profile_attention": [P, U32],
+        "fj_dense_step_stats": [P, P, P], "fj_dense_graph_replay": [P, U32], "fj_dense_graph_stats": [P, P, P, P], "fj_dense_kv_pages": [P, U32, U32, U32, U32, P, U32], "fj_dense_fill_kv": [P, U64], "fj_dense_profile_attention": [P, U32],
         "fj_dense_attention_time": [P, P, P],
         "fj_paged_decode_attention_static": [P, P, P, P, P, P, P, P, U32, U32, U32, U32, U32, U32, C.c_float, P],
     }

@@ -528,6 +528,15 @@ class DenseModel:
     def fill_kv(self, seed: int = 0):
         _check(self._lib.fj_dense_fill_kv(self._h, seed))
 
+    def graph_replay(self, enabled: bool = True):
+        """Decode-only steps are recorded once per launch-geometry bucket as a CUDA graph and replayed (fj_dense_graph_replay)."""
+        _check(self._lib.fj_dense_graph_replay(self._h, int(enabled)))
+
+    def graph_stats(self):
+        a, b, c = C.c_uint64(0), C.c_uint64(0), C.c_uint64(0)
+        _check(self._lib.fj_dense_graph_stats(self._h, C.byref(a), C.byref(b), C.byref(c)))
+        return {"recordings": a.value, "replays": b.value, "failures": c.value}
+
     def kv_pages(self, layer: int, plane: int, first_page: int, count: int, data: Optional[np.ndarray] = None) -> np.ndarray:
         """Reads (data None) or writes the rows of `count` consecutive physical pages of one layer's K (plane 0) or V (plane 1)
         plane; storage values [count, page_tokens, kv_heads * head_dim] (bf16/f16 as uint16 bit patterns)."""

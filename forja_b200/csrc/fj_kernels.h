@@ -133,7 +133,9 @@ size_t attn_part_ml_bytes(unsigned slots);
 bool attn_decode_mma_supported(const AttnGeometry& g, unsigned max_q_len);
 void launch_attn_decode_mma(Ctx& ctx, const AttnGeometry& g, const AttnSeq* seqs, const AttnWork* work, unsigned n_work,
                             const void* kpool, const void* vpool, const unsigned* generations, const AttnScratch& scratch,
-                            ErrorRecord* err);
+                            ErrorRecord* err, const unsigned* n_work_dev = nullptr);
+// n_work_dev: optional device word holding the live item count; CTAs beyond it return at once, so a launch recorded
+// once with a rounded-up grid (a replayed CUDA graph) serves steps whose work lists differ in length.
 // Chunked-prefill attention on tensor cores for any q_len: same shape limits as the decode kernel and
 // q_heads / kv_heads in {1, 2, 4, 8, 16}. One CTA per item {sequence, first token of a block of
 // attn_prefill_tokens_per_block tokens} and KV head; the caller lists every block of every sequence.

@@ -260,6 +260,16 @@ struct fj_dense_model {
   std::vector<std::pair<cudaEvent_t, cudaEvent_t>> pending;    // recorded, not yet measured
   uint64_t attention_ns = 0, attention_launches = 0;
   size_t plane_bytes = 0;
+  // Recorded decode steps (CUDA graphs), one per bucket of the step's launch geometry; see fj_dense_graph_replay.
+  struct StepGraph {
+    uint64_t key[8];
+    cudaGraphExec_t exec;
+    uint64_t kernels;  // kernel launches one replay stands for
+    uint64_t last_use;
+  };
+  bool graph_replay = false;
+  std::vector<StepGraph> graphs;
+  uint64_t graph_captures = 0, graph_replays = 0, graph_failures = 0, direct_decode_steps = 0, graph_clock = 0;
   cudaEvent_t take_event() {
     if (!event_pool.empty()) { cudaEvent_t e = event_pool.back(); event_pool.pop_back(); return e; }
     cudaEvent_t e = nullptr;
@@ -432,77 +442,53 @@ void fj_dense_model_destroy(fj_dense_model* m) {
   std::lock_guard<std::mutex> lock(m->be->mutex);
   cudaSetDevice(m->be->device);
   cudaStreamSynchronize(m->be->stream);
+  for (auto& g : m->graphs) cudaGraphExecDestroy(g.exec);
   for (void* p : m->owned) cudaFree(p);
   for (auto& pair : m->pending) { cudaEventDestroy(pair.first); cudaEventDestroy(pair.second); }
   for (auto e : m->event_pool) cudaEventDestroy(e);
   delete m;
 }
 
-int32_t fj_dense_step(fj_dense_model* m, const uint32_t* token_ids, uint32_t* out_tokens, uint64_t logits_out) {
-  if (!m) return FJ_INVALID_INPUT;
+}  // extern "C"
+
+namespace {
+
+// Launch geometry of one step, fixed before anything is enqueued.
+struct StepPlan {
+  unsigned rows;          // rows every row-wise kernel runs (the packed rows, or the lane count when padded for replay)
+  unsigned lanes;
+  bool feedback;          // tokens come from the previous step's device-resident greedy tokens
+  bool mma;               // split-K tensor-core decode attention
+  unsigned max_q_len;
+  unsigned chunk;         // tokens per split-K work item
+  unsigned work_grid;     // CTAs of the decode attention launch (>= the live item count)
+  const unsigned* n_work_dev;  // live item count on the device when work_grid is a rounded-up bound, else nullptr
+  unsigned n_blocks;      // 64-row blocks of the chunked-prefill attention
+  fj::AttnScratch scratch;
+  void* logits;
+};
+
+// The launch sequence of one forward step (reference op order: engines/qwen3/src/lib.rs:391-452, 734-811;
+// engines/smollm2/src/optimized.rs:97-245). Everything it touches is device-resident and every pointer it
+// passes outlives the call, so the same sequence can be recorded into a CUDA graph and replayed.
+void enqueue_dense_step(fj_dense_model* m, const StepPlan& plan) {
   fj_backend* be = m->be;
   fj_kvpool* pool = m->pool;
-  std::lock_guard<std::mutex> lock(be->mutex);
-  cudaSetDevice(be->device);
   const fj_dense_config& c = m->cfg;
-  const unsigned rows = pool->rows, lanes = pool->lanes_packed;
-  if (rows == 0 || lanes == 0) return FJ_INVALID_INPUT;
-  if (rows > c.max_rows) return FJ_INVALID_INPUT;
   const int dt = static_cast<int>(c.dtype);
   const size_t esz = fj::dtype_size(dt);
   const unsigned qd = c.q_heads * c.head_dim, kd = c.kv_heads * c.head_dim, H = c.hidden, I = c.intermediate;
+  const unsigned rows = plan.rows, lanes = plan.lanes;
   fj::Ctx& ctx = be->ctx;
-  const unsigned long long launches_before = ctx.launches;
-
-  if (token_ids) cudaMemcpyAsync(m->tokens_in, token_ids, static_cast<size_t>(rows) * 4, cudaMemcpyHostToDevice, be->stream);
-  else launch_feedback_tokens(ctx, pool->pack.cu_seqlens, m->tokens_out, m->tokens_in, lanes);
-
-  // attention plan for this step (shared by all layers: q and attn buffers do not move)
-  const unsigned group = c.q_heads / c.kv_heads;
-  unsigned max_q_len = 0;
-  uint64_t total_keys = 0;
-  for (unsigned l = 0; l < lanes; ++l) {
-    max_q_len = std::max(max_q_len, pool->host_tokens[l]);
-    if (pool->host_tokens[l]) total_keys += static_cast<uint64_t>(pool->host_starts[l]) + pool->host_tokens[l];
-  }
   fj::AttnGeometry g;
   g.q_heads = c.q_heads; g.kv_heads = c.kv_heads; g.head_dim = c.head_dim; g.value_dim = c.head_dim; g.page_tokens = pool->dev.page_tokens;
   g.physical_pages = pool->dev.physical_pages; g.q_dtype = dt; g.kv_dtype = dt; g.out_dtype = dt;
   g.scale = 1.0f / sqrtf(static_cast<float>(c.head_dim));
-  const bool mma = fj::attn_decode_mma_supported(g, max_q_len) && max_q_len * group <= 16;
-  uint64_t chunk = 64, n_work = 0;
-  if (mma) {
-    const uint64_t target_items = static_cast<uint64_t>(ctx.sm_count) * 2 * 4;
-    chunk = (total_keys * c.kv_heads + target_items - 1) / std::max<uint64_t>(target_items, 1);
-    chunk = std::min<uint64_t>(std::max<uint64_t>((chunk + 63) / 64 * 64, 64), 1024);
-    for (unsigned l = 0; l < lanes; ++l)
-      if (pool->host_tokens[l]) n_work += ((static_cast<uint64_t>(pool->host_starts[l]) + pool->host_tokens[l] + chunk - 1) / chunk) * c.kv_heads;
-    if (n_work > m->work_cap) return FJ_QUOTA_EXCEEDED;
-  }
-  fj::launch_build_attn_lists(ctx, pool->dev, pool->pack, lanes, c.kv_heads, static_cast<unsigned>(chunk), m->q, m->attn, c.q_heads, c.head_dim, static_cast<int>(esz), m->seqs,
-                              m->work, m->n_work_dev, m->work_cap);
-  // query runs too long for the decode kernel: 64-row tensor-core blocks, listed by the host from the packed step
-  unsigned n_blocks = 0;
-  if (!mma && fj::attn_prefill_mma_supported(g)) {
-    const unsigned per_block = fj::attn_prefill_tokens_per_block(g);
-    std::vector<uint2> items;
-    for (unsigned l = 0; l < lanes; ++l)
-      for (unsigned t = 0; t < pool->host_tokens[l]; t += per_block) items.push_back(make_uint2(l, t));
-    if (items.size() > m->prefill_items_cap) return FJ_QUOTA_EXCEEDED;
-    n_blocks = static_cast<unsigned>(items.size());
-    cudaMemcpyAsync(m->prefill_items, items.data(), items.size() * sizeof(uint2), cudaMemcpyHostToDevice, be->stream);  // pageable source: staged before the call returns
-  }
-  fj::AttnScratch scratch{nullptr, nullptr, nullptr};
-  if (mma) {
-    const size_t groups = static_cast<size_t>(lanes) * c.kv_heads;
-    const size_t counter_bytes = (groups * sizeof(unsigned) + 255) / 256 * 256;
-    const size_t o_bytes = fj::attn_part_o_bytes(static_cast<unsigned>(n_work), c.head_dim), ml_bytes = fj::attn_part_ml_bytes(static_cast<unsigned>(n_work));
-    if (!ensure_attn_scratch(be, counter_bytes + o_bytes + ml_bytes)) return FJ_ALLOCATION_FAILED;
-    scratch.counters = static_cast<unsigned*>(be->attn_scratch);
-    scratch.part_o = reinterpret_cast<float*>(static_cast<char*>(be->attn_scratch) + counter_bytes);
-    scratch.part_ml = reinterpret_cast<float*>(static_cast<char*>(be->attn_scratch) + counter_bytes + o_bytes);
-  }
 
+  if (plan.feedback) launch_feedback_tokens(ctx, pool->pack.cu_seqlens, m->tokens_out, m->tokens_in, lanes);
+  // attention plan for this step (shared by all layers: q and attn buffers do not move)
+  fj::launch_build_attn_lists(ctx, pool->dev, pool->pack, lanes, c.kv_heads, plan.chunk, m->q, m->attn, c.q_heads, c.head_dim, static_cast<int>(esz), m->seqs,
+                              m->work, m->n_work_dev, m->work_cap);
   fj::launch_embed(ctx, m->embed, dt, m->tokens_in, m->hidden, dt, c.vocab, H, rows, nullptr);
   void* hidden = m->hidden;
   void* other = m->hidden2;
@@ -515,9 +501,9 @@ int32_t fj_dense_step(fj_dense_model* m, const uint32_t* token_ids, uint32_t* ou
                                   c.head_dim, c.eps, m->inv_freq, c.qk_norm ? 1 : 0, plane_slots);
     cudaEvent_t attn_begin = nullptr, attn_end = nullptr;
     if (m->profile_attention) { attn_begin = m->take_event(); attn_end = m->take_event(); cudaEventRecord(attn_begin, be->stream); }
-    if (mma) fj::launch_attn_decode_mma(ctx, g, m->seqs, m->work, static_cast<unsigned>(n_work), L.k_plane, L.v_plane, pool->dev.generations, scratch, nullptr);
-    else if (n_blocks) fj::launch_attn_prefill_mma(ctx, g, m->seqs, m->prefill_items, n_blocks, L.k_plane, L.v_plane, pool->dev.generations, nullptr);
-    else fj::launch_attn_generic(ctx, g, m->seqs, lanes, max_q_len, L.k_plane, L.v_plane, pool->dev.generations, nullptr);
+    if (plan.mma) fj::launch_attn_decode_mma(ctx, g, m->seqs, m->work, plan.work_grid, L.k_plane, L.v_plane, pool->dev.generations, plan.scratch, nullptr, plan.n_work_dev);
+    else if (plan.n_blocks) fj::launch_attn_prefill_mma(ctx, g, m->seqs, m->prefill_items, plan.n_blocks, L.k_plane, L.v_plane, pool->dev.generations, nullptr);
+    else fj::launch_attn_generic(ctx, g, m->seqs, lanes, plan.max_q_len, L.k_plane, L.v_plane, pool->dev.generations, nullptr);
     if (m->profile_attention) { cudaEventRecord(attn_end, be->stream); m->pending.emplace_back(attn_begin, attn_end); }
     fj::launch_gemm_nt(ctx, m->attn, dt, qd, L.wo, dt, qd, m->proj, dt, H, rows, H, qd, be->gemm_scratch, be->gemm_scratch_bytes);
     // hidden' = hidden + attention ; normed = rms(hidden') * post_norm
@@ -539,14 +525,150 @@ int32_t fj_dense_step(fj_dense_model* m, const uint32_t* token_ids, uint32_t* ou
   // last row of every lane -> final norm -> tied lm_head -> greedy token
   launch_gather_last_rows(ctx, hidden, dt, pool->pack.cu_seqlens, m->last_hidden, lanes, H);
   fj::launch_rms_norm(ctx, dense_view(m->last_hidden, dt, lanes, H, H), weight_view(m->final_norm, dt, lanes, H), dense_view(m->last_normed, dt, lanes, H, H), lanes, H, c.eps);
-  void* logits = m->logits;
+  fj::launch_gemm_nt(ctx, m->last_normed, dt, H, m->embed, dt, H, plan.logits, dt, c.vocab, lanes, c.vocab, H, be->gemm_scratch, be->gemm_scratch_bytes);
+  fj::launch_argmax(ctx, plan.logits, dt, c.vocab, m->tokens_out, lanes, c.vocab, m->argmax_scratch);
+}
+
+constexpr unsigned kWorkGridStep = 256;   // recorded decode steps round their attention grid up to a multiple of this
+constexpr size_t kMaxStepGraphs = 24;     // least recently used recordings beyond this are dropped
+
+// Replays the recorded launch sequence of this step's bucket, recording it first when the bucket is new.
+// false: nothing was enqueued (recording failed or is not possible); the caller runs the step directly.
+bool replay_dense_step(fj_dense_model* m, const StepPlan& plan) {
+  fj_backend* be = m->be;
+  fj_dense_model::StepGraph wanted{};
+  const uint64_t key[8] = {plan.lanes, plan.chunk, plan.work_grid, plan.feedback ? 1u : 0u, reinterpret_cast<uint64_t>(plan.logits),
+                           reinterpret_cast<uint64_t>(be->gemm_scratch), reinterpret_cast<uint64_t>(plan.scratch.counters), reinterpret_cast<uint64_t>(m->pool->pack.positions)};
+  ++m->graph_clock;
+  for (auto& g : m->graphs) {
+    if (memcmp(g.key, key, sizeof(key)) != 0) continue;
+    if (cudaGraphLaunch(g.exec, be->stream) != cudaSuccess) { cudaGetLastError(); return false; }
+    g.last_use = m->graph_clock;
+    be->ctx.launches += g.kernels;
+    ++m->graph_replays;
+    return true;
+  }
+  if (m->graph_failures >= 3) return false;  // recording does not work here: stay on the direct path
+  const unsigned long long before = be->ctx.launches;
+  if (cudaStreamBeginCapture(be->stream, cudaStreamCaptureModeThreadLocal) != cudaSuccess) { cudaGetLastError(); ++m->graph_failures; return false; }
+  enqueue_dense_step(m, plan);
+  cudaGraph_t graph = nullptr;
+  const cudaError_t ended = cudaStreamEndCapture(be->stream, &graph);
+  const uint64_t kernels = be->ctx.launches - before;
+  be->ctx.launches = before;  // nothing ran yet
+  cudaGraphExec_t exec = nullptr;
+  if (ended != cudaSuccess || graph == nullptr || cudaGraphInstantiate(&exec, graph, 0) != cudaSuccess) {
+    cudaGetLastError();
+    if (graph) cudaGraphDestroy(graph);
+    ++m->graph_failures;
+    return false;
+  }
+  cudaGraphDestroy(graph);
+  if (m->graphs.size() >= kMaxStepGraphs) {
+    auto oldest = std::min_element(m->graphs.begin(), m->graphs.end(), [](const fj_dense_model::StepGraph& a, const fj_dense_model::StepGraph& b) { return a.last_use < b.last_use; });
+    cudaGraphExecDestroy(oldest->exec);
+    m->graphs.erase(oldest);
+  }
+  memcpy(wanted.key, key, sizeof(key));
+  wanted.exec = exec; wanted.kernels = kernels; wanted.last_use = m->graph_clock;
+  m->graphs.push_back(wanted);
+  ++m->graph_captures;
+  if (cudaGraphLaunch(exec, be->stream) != cudaSuccess) { cudaGetLastError(); return false; }
+  be->ctx.launches += kernels;
+  ++m->graph_replays;
+  return true;
+}
+
+}  // namespace
+
+extern "C" {
+
+int32_t fj_dense_step(fj_dense_model* m, const uint32_t* token_ids, uint32_t* out_tokens, uint64_t logits_out) {
+  if (!m) return FJ_INVALID_INPUT;
+  fj_backend* be = m->be;
+  fj_kvpool* pool = m->pool;
+  std::lock_guard<std::mutex> lock(be->mutex);
+  cudaSetDevice(be->device);
+  const fj_dense_config& c = m->cfg;
+  const unsigned rows = pool->rows, lanes = pool->lanes_packed;
+  if (rows == 0 || lanes == 0) return FJ_INVALID_INPUT;
+  if (rows > c.max_rows) return FJ_INVALID_INPUT;
+  const int dt = static_cast<int>(c.dtype);
+  const size_t esz = fj::dtype_size(dt);
+  fj::Ctx& ctx = be->ctx;
+  const unsigned long long launches_before = ctx.launches;
+
+  StepPlan plan{};
+  plan.rows = rows; plan.lanes = lanes; plan.feedback = token_ids == nullptr;
+  const unsigned group = c.q_heads / c.kv_heads;
+  unsigned max_q_len = 0;
+  uint64_t total_keys = 0;
+  bool decode_only = true;
+  for (unsigned l = 0; l < lanes; ++l) {
+    max_q_len = std::max(max_q_len, pool->host_tokens[l]);
+    decode_only = decode_only && pool->host_tokens[l] <= 1;
+    if (pool->host_tokens[l]) total_keys += static_cast<uint64_t>(pool->host_starts[l]) + pool->host_tokens[l];
+  }
+  plan.max_q_len = max_q_len;
+  fj::AttnGeometry g;
+  g.q_heads = c.q_heads; g.kv_heads = c.kv_heads; g.head_dim = c.head_dim; g.value_dim = c.head_dim; g.page_tokens = pool->dev.page_tokens;
+  g.physical_pages = pool->dev.physical_pages; g.q_dtype = dt; g.kv_dtype = dt; g.out_dtype = dt;
+  plan.mma = fj::attn_decode_mma_supported(g, max_q_len) && max_q_len * group <= 16;
+  uint64_t chunk = 64, n_work = 0;
+  if (plan.mma) {
+    const uint64_t target_items = static_cast<uint64_t>(ctx.sm_count) * 2 * 4;
+    chunk = (total_keys * c.kv_heads + target_items - 1) / std::max<uint64_t>(target_items, 1);
+    chunk = std::min<uint64_t>(std::max<uint64_t>((chunk + 63) / 64 * 64, 64), 1024);
+    for (unsigned l = 0; l < lanes; ++l)
+      if (pool->host_tokens[l]) n_work += ((static_cast<uint64_t>(pool->host_starts[l]) + pool->host_tokens[l] + chunk - 1) / chunk) * c.kv_heads;
+    if (n_work > m->work_cap) return FJ_QUOTA_EXCEEDED;
+  }
+  plan.chunk = static_cast<unsigned>(chunk);
+  plan.work_grid = static_cast<unsigned>(n_work);
+  // A decode-only step can be replayed from a recording: every row-wise kernel then runs `lanes` rows (the packer pads the
+  // rows past the packed count with refused slots) and the attention grid is rounded up, with the live count read on the device.
+  const bool replay = m->graph_replay && plan.mma && decode_only && !m->profile_attention && lanes <= c.max_rows && lanes <= pool->rows_cap &&
+                      m->direct_decode_steps > 0 && m->graph_failures < 3;
+  if (replay) {
+    plan.rows = lanes;
+    plan.work_grid = static_cast<unsigned>(std::min<uint64_t>((n_work + kWorkGridStep - 1) / kWorkGridStep * kWorkGridStep, m->work_cap));
+    plan.n_work_dev = m->n_work_dev;
+  }
+  // query runs too long for the decode kernel: 64-row tensor-core blocks, listed by the host from the packed step
+  if (!plan.mma && fj::attn_prefill_mma_supported(g)) {
+    const unsigned per_block = fj::attn_prefill_tokens_per_block(g);
+    std::vector<uint2> items;
+    for (unsigned l = 0; l < lanes; ++l)
+      for (unsigned t = 0; t < pool->host_tokens[l]; t += per_block) items.push_back(make_uint2(l, t));
+    if (items.size() > m->prefill_items_cap) return FJ_QUOTA_EXCEEDED;
+    plan.n_blocks = static_cast<unsigned>(items.size());
+    cudaMemcpyAsync(m->prefill_items, items.data(), items.size() * sizeof(uint2), cudaMemcpyHostToDevice, be->stream);  // pageable source: staged before the call returns
+  }
+  plan.scratch = fj::AttnScratch{nullptr, nullptr, nullptr};
+  if (plan.mma) {
+    const size_t groups = static_cast<size_t>(lanes) * c.kv_heads;
+    const size_t counter_bytes = (groups * sizeof(unsigned) + 255) / 256 * 256;
+    const size_t o_bytes = fj::attn_part_o_bytes(plan.work_grid, c.head_dim), ml_bytes = fj::attn_part_ml_bytes(plan.work_grid);
+    if (!ensure_attn_scratch(be, counter_bytes + o_bytes + ml_bytes)) return FJ_ALLOCATION_FAILED;
+    plan.scratch.counters = static_cast<unsigned*>(be->attn_scratch);
+    plan.scratch.part_o = reinterpret_cast<float*>(static_cast<char*>(be->attn_scratch) + counter_bytes);
+    plan.scratch.part_ml = reinterpret_cast<float*>(static_cast<char*>(be->attn_scratch) + counter_bytes + o_bytes);
+  }
+  plan.logits = m->logits;
   if (logits_out) {
     fj_buffer_rec* r = find_buffer(be, logits_out);
     if (!r || r->readonly || r->bytes < static_cast<uint64_t>(lanes) * c.vocab * esz) return FJ_INVALID_INPUT;
-    logits = r->ptr;
+    plan.logits = r->ptr;
   }
-  fj::launch_gemm_nt(ctx, m->last_normed, dt, H, m->embed, dt, H, logits, dt, c.vocab, lanes, c.vocab, H, be->gemm_scratch, be->gemm_scratch_bytes);
-  fj::launch_argmax(ctx, logits, dt, c.vocab, m->tokens_out, lanes, c.vocab, m->argmax_scratch);
+
+  if (token_ids) cudaMemcpyAsync(m->tokens_in, token_ids, static_cast<size_t>(rows) * 4, cudaMemcpyHostToDevice, be->stream);
+  if (!(replay && replay_dense_step(m, plan))) {
+    if (replay) {  // the recording could not be made: run this step with its exact geometry
+      plan.rows = rows; plan.work_grid = static_cast<unsigned>(n_work); plan.n_work_dev = nullptr;
+    }
+    enqueue_dense_step(m, plan);
+    if (plan.mma && decode_only) ++m->direct_decode_steps;
+  }
   m->last_kernels = ctx.launches - launches_before;
   m->last_work_items = n_work;
   cudaError_t e = cudaGetLastError();
@@ -555,6 +677,26 @@ int32_t fj_dense_step(fj_dense_model* m, const uint32_t* token_ids, uint32_t* ou
     cudaMemcpyAsync(out_tokens, m->tokens_out, static_cast<size_t>(lanes) * 4, cudaMemcpyDeviceToHost, be->stream);
     return cuda_status(cudaStreamSynchronize(be->stream));
   }
+  return FJ_OK;
+}
+
+// Graph replay for the decode step (the backend-specific tier behind Backend::prepare_graph / replay,
+// crates/forja-core/src/backend.rs:858-967): with replay enabled, decode-only steps are recorded once per bucket
+// {lanes, split-K chunk, attention grid rounded up to 256 items, token source, logits target} as a CUDA graph and
+// replayed, so a step costs one graph launch on the host instead of one launch per kernel.
+int32_t fj_dense_graph_replay(fj_dense_model* m, uint32_t enabled) {
+  if (!m) return FJ_INVALID_INPUT;
+  std::lock_guard<std::mutex> lock(m->be->mutex);
+  m->graph_replay = enabled != 0;
+  return FJ_OK;
+}
+
+int32_t fj_dense_graph_stats(fj_dense_model* m, uint64_t* recordings, uint64_t* replays, uint64_t* failures) {
+  if (!m) return FJ_INVALID_INPUT;
+  std::lock_guard<std::mutex> lock(m->be->mutex);
+  if (recordings) *recordings = m->graph_captures;
+  if (replays) *replays = m->graph_replays;
+  if (failures) *failures = m->graph_failures;
   return FJ_OK;
 }
 

@@ -263,6 +263,13 @@ __global__ void pack_step_kernel(KvPoolDevice pool, const unsigned* __restrict__
     out.slot_mapping[row] = slot;
     out.row_lane[row] = lane;
   }
+  // Rows between the packed count and the lane count are padding for callers that always run `lanes` rows (a
+  // recorded launch sequence replayed with fixed grids): position 0 and a refused slot, so nothing is appended for them.
+  for (unsigned row = rows + threadIdx.x; row < min(lanes, rows_cap); row += blockDim.x) {
+    out.positions[row] = 0;
+    out.slot_mapping[row] = POISON;
+    out.row_lane[row] = 0;
+  }
 }
 
 __global__ void build_attn_lists_kernel(KvPoolDevice pool, PackOutputs pack, unsigned lanes, unsigned kv_heads, unsigned chunk_tokens,

@@ -80,6 +80,7 @@ struct DecodeParams {
   float* part_ml;
   unsigned* counters;
   ErrorRecord* err;
+  const unsigned* n_work_dev;  // when set: the live item count on the device; the grid may be larger (a replayed graph)
 };
 
 __device__ inline void cp_async_16(unsigned smem_addr, const void* gmem, unsigned src_bytes) {
@@ -133,7 +134,7 @@ __global__ void __launch_bounds__(kWarps * 32, 2) attn_decode_mma_kernel(DecodeP
   __shared__ unsigned s_ticket;
   pdl_sync();
   const unsigned item = blockIdx.x;
-  if (item >= p.n_work) return;
+  if (item >= p.n_work || (p.n_work_dev != nullptr && item >= *p.n_work_dev)) return;
   const AttnWork work = p.work[item];
   const AttnSeq seq = p.seqs[work.seq];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -779,9 +780,10 @@ bool attn_decode_mma_supported(const AttnGeometry& g, unsigned max_q_len) {
 
 void launch_attn_decode_mma(Ctx& ctx, const AttnGeometry& g, const AttnSeq* seqs, const AttnWork* work, unsigned n_work,
                             const void* kpool, const void* vpool, const unsigned* generations, const AttnScratch& scratch,
-                            ErrorRecord* err) {
+                            ErrorRecord* err, const unsigned* n_work_dev) {
   if (n_work == 0) return;
   DecodeParams p;
+  p.n_work_dev = n_work_dev;
   p.seqs = seqs; p.work = work; p.n_work = n_work;
   p.kpool = static_cast<const char*>(kpool); p.vpool = static_cast<const char*>(vpool);
   p.generations = generations; p.physical_pages = g.physical_pages;

@@ -372,6 +372,17 @@ int32_t fj_dense_step(fj_dense_model* model, const uint32_t* token_ids, uint32_t
 /* Copies the first `tokens` K/V rows of page src_page to page dst_page in every layer (the data half of cow_tail). */
 int32_t fj_dense_copy_page(fj_dense_model* model, uint32_t src_page, uint32_t dst_page, uint32_t tokens);
 int32_t fj_dense_step_stats(fj_dense_model* model, uint64_t* kernels, uint64_t* attn_work_items);
+/* Graph replay of the decode step: the backend-specific tier behind Backend::prepare_graph / replay
+ * (crates/forja-core/src/backend.rs:858-967; the reference's default tier re-instantiates and re-submits the
+ * template). With replay enabled, a decode-only step (every active lane appends one token) is recorded once per
+ * bucket {lanes, split-K chunk, attention grid rounded up to 256 work items, token source, logits target} as a
+ * CUDA graph and replayed afterwards: one graph launch on the host instead of one launch per kernel. Every
+ * row-wise kernel of a replayed step runs `lanes` rows (rows past the packed count are padding whose appends are
+ * refused), the attention kernel reads the live work-item count on the device. Steps that mix prompt pieces, or
+ * run while attention profiling is on, take the direct path. Results are identical on both paths.
+ * fj_dense_graph_stats: recordings made, steps replayed, recordings that failed (after 3 the model stays direct). */
+int32_t fj_dense_graph_replay(fj_dense_model* model, uint32_t enabled);
+int32_t fj_dense_graph_stats(fj_dense_model* model, uint64_t* recordings, uint64_t* replays, uint64_t* failures);
 /* Host access to the model's KV planes (which the library owns, like the host-owned page planes of
  * crates/forja-host/src/lib.rs:4323-4360): copies the rows of `count` consecutive physical pages of
  * one layer's K plane (plane 0) or V plane (plane 1) to host memory (to_device 0) or from it

@@ -386,3 +386,55 @@ def test_qwen3_06b_shape_decode_matches_oracle_at_full_size():
     assert flips <= 1
     model.close()
     pool.close()
+
+
+def test_replayed_decode_steps_equal_directly_launched_ones():
+    """Graph replay (fj_dense_graph_replay): decode-only steps recorded once per bucket and replayed give bit-identical
+    logits, tokens and cache contents to the same steps launched kernel by kernel - also with an idle lane in the batch
+    (its rows are padding in the recorded launch), with host-fed and with device-fed tokens."""
+    cfg, page, steps = dict(TINY_BF16, max_rows=64), 16, 9
+    prompts = [5, 40, 17, 3, 29]
+    lanes = len(prompts)
+    be = backend()
+    rng = np.random.default_rng(12)
+    weights = engine.random_dense_weights(cfg, 2)
+    ids = [rng.integers(0, cfg["vocab"], n).astype(np.uint32) for n in prompts]
+    feed_at_5 = rng.integers(0, cfg["vocab"], lanes - 1).astype(np.uint32)
+
+    def generate(replay):
+        physical = sum((n + steps + page - 1) // page for n in prompts) + 3
+        pool = fb.KvPool(be, page, physical, lanes, 8)
+        assert all(s == 0 for s in pool.reserve(list(range(lanes)), [n + steps for n in prompts]))
+        model = build_model(cfg, weights, pool)
+        model.graph_replay(replay)
+        logits = be.alloc(cfg["dtype"], (lanes, cfg["vocab"]))
+        pool.pack_step([0] * lanes, prompts)
+        history = [model.step(np.concatenate(ids), lanes=lanes, logits=logits).tolist()]
+        rows = [be.read(logits).copy()]
+        positions = list(prompts)
+        for step in range(steps):
+            idle = 2 if 3 <= step < 6 else None  # lane 2 sits out three steps
+            tokens = [0 if lane == idle else 1 for lane in range(lanes)]
+            pool.pack_step(positions, tokens)
+            feed = feed_at_5 if step == 5 else None  # one step takes its tokens from the host
+            history.append(model.step(feed, lanes=lanes, logits=logits).tolist())
+            rows.append(be.read(logits).copy())
+            positions = [p + t for p, t in zip(positions, tokens)]
+        cache = [model.kv_pages(layer, plane, 0, physical) for layer in range(cfg["layers"]) for plane in (0, 1)]
+        stats = model.graph_stats()
+        model.close()
+        pool.close()
+        return history, rows, cache, stats
+
+    direct = generate(False)
+    replayed = generate(True)
+    assert direct[3] == {"recordings": 0, "replays": 0, "failures": 0}
+    assert replayed[3]["failures"] == 0
+    # the first decode step runs directly (it warms every kernel up), the others replay; host-fed and device-fed
+    # tokens are different recordings
+    assert replayed[3]["replays"] == steps - 1 and 2 <= replayed[3]["recordings"] <= 4
+    assert direct[0] == replayed[0]
+    for a, b in zip(direct[1], replayed[1]):
+        assert np.array_equal(a, b)
+    for a, b in zip(direct[2], replayed[2]):
+        assert np.array_equal(a, b)
