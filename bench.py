@@ -48,6 +48,7 @@ def parse_args():
     ap.add_argument("--pool-pages", type=int, default=36000, help="physical KV pages per GPU (36000 pages = 66 GB of planes)")
     ap.add_argument("--ctx-max", type=int, default=CTX_MAX, help="largest context length (lower it for profiler captures)")
     ap.add_argument("--layers", type=int, default=0, help="override the layer count (profiler captures only; 0 = the model's 28)")
+    ap.add_argument("--repeats", type=int, default=0, help="how often the block of --steps steps is timed (the median block is reported); 0 = 9 for blocks up to 64 steps, else 3, else 1")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-graph-replay", action="store_true", help="launch every decode step kernel by kernel instead of replaying its recorded CUDA graph")
     return ap.parse_args()
@@ -73,35 +74,45 @@ class Requests:
 
 
 class Lanes:
-    """Host bookkeeping of the continuous batch: which request sits in which lane, its current
-    length and remaining budget, and the free-page count (the device allocator is deterministic,
-    so the host knows it without reading anything back)."""
+    """Host bookkeeping of the continuous batch. Admission runs through the product scheduler
+    (SchedulerPolicy over fj_sched_*: FIFO with at most 8 bypasses by smaller requests, page
+    reservation = ceil((context + budget) / page), crates/forja-serve/src/scheduler.rs:109-152):
+    every request that finishes is replaced in the waiting line by the next one of the seeded
+    stream, and whatever the scheduler admits against the free pages takes the lowest free lanes.
+    The device allocator is deterministic, so the host knows the free-page count without reading
+    anything back."""
 
     def __init__(self, pool, requests, lanes, pool_pages):
+        import forja_b200 as fb
         self.pool, self.requests, self.n = pool, requests, lanes
         self.free_pages = pool_pages
         self.length = np.zeros(lanes, np.uint32)
         self.remaining = np.zeros(lanes, np.int64)
         self.pages = np.zeros(lanes, np.int64)
-        self.waiting = [None] * lanes
+        self.request_of = [None] * lanes
+        self.waiting = {}
+        self.next_id = 0
         self.admitted = 0
-        for lane in range(lanes):
-            self.waiting[lane] = requests.next()
+        buckets = sorted({1 << i for i in range(lanes.bit_length())} | {lanes})
+        self.sched = fb.SchedulerPolicy(buckets, active_limit=lanes, prefill_limit=lanes, prompt_budget=PAGE, idle_prompt_budget=PAGE)
+        for _ in range(lanes):
+            self.enqueue()
         self.admit()
 
+    def enqueue(self):
+        ctx, budget = self.requests.next()
+        self.waiting[self.next_id] = (ctx, budget)
+        self.sched.enqueue(self.next_id, ctx + budget)
+        self.next_id += 1
+
     def admit(self):
+        ids, self.free_pages = self.sched.admit_pages(PAGE, self.free_pages)
+        free_lanes = [lane for lane in range(self.n) if self.request_of[lane] is None]
         lanes, tokens = [], []
-        for lane in range(self.n):
-            req = self.waiting[lane]
-            if req is None:
-                continue
-            ctx, budget = req
-            need = (ctx + budget + PAGE - 1) // PAGE
-            if need > self.free_pages:
-                continue  # page reservation does not fit yet: the lane idles this step
-            self.free_pages -= need
-            self.pages[lane], self.length[lane], self.remaining[lane] = need, ctx, budget
-            self.waiting[lane] = None
+        for rid, lane in zip(ids, free_lanes):
+            ctx, budget = self.waiting.pop(rid)
+            self.pages[lane], self.length[lane], self.remaining[lane] = (ctx + budget + PAGE - 1) // PAGE, ctx, budget
+            self.request_of[lane] = rid
             lanes.append(lane)
             tokens.append(ctx + budget)
             self.admitted += 1
@@ -123,7 +134,9 @@ class Lanes:
             for lane in done.tolist():
                 self.free_pages += int(self.pages[lane])
                 self.pages[lane] = 0
-                self.waiting[lane] = self.requests.next()
+                self.sched.complete(self.request_of[lane])
+                self.request_of[lane] = None
+                self.enqueue()
             self.admit()
         return int(active.sum())
 
@@ -235,6 +248,8 @@ def run_native(args):
     model.graph_replay(not args.no_graph_replay)
     lanes = Lanes(pool, Requests(args.seed * 1000 + rank, args.ctx_max), args.lanes, args.pool_pages)
 
+    repeats = args.repeats if args.repeats > 0 else (9 if args.steps <= 64 else (3 if args.steps <= 256 else 1))
+
     def step_device():
         starts, tokens = lanes.descriptors()
         pool.pack_step(starts, tokens)
@@ -263,28 +278,40 @@ def run_native(args):
         lanes.advance()
 
     # ---- timed region 1: device-resident decode --------------------------------------------
+    # The block of `steps` steps is timed `repeats` times back to back on the running batch (each
+    # bracketed by barrier + synchronise, CUDA events on the backend's stream, max over ranks);
+    # the line reports the median block, so one disturbed block does not decide the number.
     t_begin, t_end = be.timer(), be.timer()
     model.attention_time()
-    barrier(dist, be)
-    launches0 = be.kernel_launch_count()
-    be.timer_record(t_begin)
-    total_tokens, attn_bytes, kv_tokens, profiled_steps = 0, 0, 0, 0
-    for step in range(args.steps):
-        # the attention launches of every 8th step are bracketed by CUDA events on the kernel's
-        # stream; bracketing all of them costs about a millisecond per step in pipeline bubbles
-        sampled = step % 8 == 0
-        model.profile_attention(sampled)
-        starts, tokens = step_device()
-        active = starts[tokens > 0] + 1
-        if sampled:
-            attn_bytes += attention_bytes(active, cfg)
-            profiled_steps += 1
-        kv_tokens += int(active.sum())
-        total_tokens += lanes.advance()
-    be.timer_record(t_end)
-    barrier(dist, be)
-    elapsed = be.timer_elapsed_ns(t_begin, t_end) * 1e-9
-    launches = be.kernel_launch_count() - launches0
+    blocks = []
+    launches = 0
+    attn_bytes, profiled_steps = 0, 0
+    for rep in range(repeats):
+        barrier(dist, be)
+        launches0 = be.kernel_launch_count()
+        be.timer_record(t_begin)
+        block_tokens, block_kv = 0, 0
+        for step in range(args.steps):
+            # the attention launches of every 8th step are bracketed by CUDA events on the kernel's
+            # stream; bracketing all of them costs about a millisecond per step in pipeline bubbles
+            sampled = step % 8 == 0
+            model.profile_attention(sampled)
+            starts, tokens = step_device()
+            active = starts[tokens > 0] + 1
+            if sampled:
+                attn_bytes += attention_bytes(active, cfg)
+                profiled_steps += 1
+            block_kv += int(active.sum())
+            block_tokens += lanes.advance()
+        be.timer_record(t_end)
+        barrier(dist, be)
+        block_elapsed = be.timer_elapsed_ns(t_begin, t_end) * 1e-9
+        launches = be.kernel_launch_count() - launches0
+        block_elapsed, block_tokens_all, (block_kv_all,) = reduce_max_sum(dist, local, block_elapsed, block_tokens, [block_kv])
+        blocks.append((block_elapsed, block_tokens_all, block_kv_all))
+    order = sorted(range(repeats), key=lambda i: blocks[i][1] / blocks[i][0])
+    elapsed, total_tokens, kv_tokens = blocks[order[repeats // 2]]
+    kv_tokens /= world
     attn_ns, attn_launches = model.attention_time()
     model.profile_attention(False)
     stats = model.stats()
@@ -292,6 +319,11 @@ def run_native(args):
     # ---- timed region 2: end to end through the C ABI with host buffers ----------------------
     e2e_steps = args.steps
     host_tokens = np.zeros(args.lanes, np.uint32)
+    for _ in range(min(args.warmup, 3)):  # the host-fed form of the step warms up outside the timed region
+        starts, tokens = lanes.descriptors()
+        pool.pack_step(starts, tokens)
+        host_tokens = model.step(host_tokens[tokens > 0], want_tokens=True, lanes=args.lanes)
+        lanes.advance()
     barrier(dist, be)
     h2d = d2h = 0
     e2e_tokens = e2e_kv_tokens = 0
@@ -313,8 +345,7 @@ def run_native(args):
         sampler.wait()
     clocks = read_clock_samples(clocks_path)
 
-    elapsed, total_tokens, (e2e_tok_sum, attn_bytes_sum) = reduce_max_sum(dist, local, elapsed, total_tokens, [e2e_tokens, attn_bytes])
-    e2e_elapsed, _, _ = reduce_max_sum(dist, local, e2e_elapsed, 0, [])
+    e2e_elapsed, _, (e2e_tok_sum,) = reduce_max_sum(dist, local, e2e_elapsed, 0, [e2e_tokens])
     if rank != 0:
         return None
     peaks = load_peaks()
@@ -322,7 +353,8 @@ def run_native(args):
     achieved = (attn_bytes * cfg["layers"] / 1e9) / (attn_ns * 1e-9) if attn_ns else None
     per_launch_bytes = attn_bytes / max(profiled_steps, 1)
     result = {
-        "metric": "ragged decode tok/s", "value": total_tokens / elapsed, "unit": "tok/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "metric": "ragged decode tok/s", "value": total_tokens / elapsed, "unit": "tok/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "repeats": repeats,
+        "block_tok_s": [round(b[1] / b[0], 1) for b in blocks],
         "ms_per_step": elapsed / args.steps * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": {"workload": "qwen3-0.6b-arch bf16 continuous-batching decode, 128 lanes, ctx log-uniform 128-%d, page 16" % args.ctx_max,
                    "lanes_per_gpu": args.lanes, "layers": cfg["layers"], "pool_pages": args.pool_pages, "admitted_requests": lanes.admitted,

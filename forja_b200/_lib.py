@@ -32,6 +32,10 @@ class FjDispatchProfile(C.Structure):
     _fields_ = [("op", C.c_uint32), ("kernels", C.c_uint32), ("ns", C.c_uint64)]
 
 
+class FjGraphBinding(C.Structure):
+    _fields_ = [("dispatch", C.c_uint32), ("field", C.c_uint32), ("param", C.c_uint32), ("scale", C.c_uint32), ("offset", C.c_uint64)]
+
+
 class FjWeightTensor(C.Structure):
     _fields_ = [("name", C.c_char_p), ("dtype", C.c_uint32), ("rank", C.c_uint32), ("shape", C.c_uint32 * 8), ("byte_offset", C.c_uint64),
                 ("byte_len", C.c_uint64), ("dtype_aligned", C.c_uint32)]
@@ -73,7 +77,7 @@ SCHED_RESERVE_FN = C.CFUNCTYPE(C.c_int32, C.c_void_p, C.c_uint64, C.c_uint64)
 EXPORTS = [
     "fj_backend_create", "fj_backend_destroy", "fj_device_info", "fj_set_memory_limit", "fj_memory_usage", "fj_alloc",
     "fj_import_readonly", "fj_release", "fj_write", "fj_read", "fj_read_strided", "fj_buffer_device_ptr", "fj_program_prepare",
-    "fj_program_info", "fj_program_classify", "fj_tensor_byte_span", "fj_submit", "fj_sub_wait", "fj_sub_gpu_time_ns", "fj_sub_completion_serial", "fj_sub_error",
+    "fj_program_info", "fj_program_classify", "fj_tensor_byte_span", "fj_submit", "fj_graph_prepare", "fj_graph_replay", "fj_graph_destroy", "fj_sub_wait", "fj_sub_gpu_time_ns", "fj_sub_completion_serial", "fj_sub_error",
     "fj_sub_kernel_launches", "fj_sub_profile", "fj_sub_destroy", "fj_synchronize", "fj_kernel_launch_count", "fj_timer_create",
     "fj_timer_record", "fj_timer_elapsed_ns", "fj_kvpool_create", "fj_kvpool_destroy", "fj_kvpool_reserve", "fj_kvpool_release",
     "fj_kvpool_read_table", "fj_kvpool_read_generations", "fj_kvpool_read_free", "fj_kvpool_read_refcounts", "fj_kvpool_fork", "fj_kvpool_cow_tail", "fj_dense_copy_page", "fj_kvpool_tables_buffer",
@@ -121,6 +125,8 @@ def load():
     lib.fj_backend_destroy.restype = None
     lib.fj_sub_destroy.restype = None
     lib.fj_kvpool_destroy.restype = None
+    lib.fj_graph_destroy.restype = None
+    lib.fj_graph_destroy.argtypes = [C.c_void_p]
     lib.fj_dense_model_destroy.restype = None
     for name in ("fj_backend_destroy", "fj_sub_destroy", "fj_kvpool_destroy", "fj_dense_model_destroy", "fj_sub_completion_serial",
                  "fj_kernel_launch_count", "fj_sub_kernel_launches", "fj_kvpool_tables_buffer", "fj_kvpool_generations_buffer"):
@@ -130,7 +136,7 @@ def load():
         "fj_backend_create": [I32, U64, P], "fj_device_info": [P, P], "fj_set_memory_limit": [P, U64], "fj_memory_usage": [P, P, P],
         "fj_alloc": [P, U64, P], "fj_import_readonly": [P, P, U64, P], "fj_release": [P, U64], "fj_write": [P, U64, U64, P, U64],
         "fj_read": [P, U64, U64, P, U64], "fj_read_strided": [P, P, P], "fj_buffer_device_ptr": [P, U64, P, P],
-        "fj_program_prepare": [P, U32, P, U32, P, U32, P], "fj_program_info": [P, U64, P, P], "fj_program_classify": [U32, P, U32, P, U32, P, P], "fj_tensor_byte_span": [P, P, P], "fj_submit": [P, P, U32, U32, P],
+        "fj_program_prepare": [P, U32, P, U32, P, U32, P], "fj_program_info": [P, U64, P, P], "fj_program_classify": [U32, P, U32, P, U32, P, P], "fj_tensor_byte_span": [P, P, P], "fj_submit": [P, P, U32, U32, P], "fj_graph_prepare": [P, P, U32, P, U32, U32, P], "fj_graph_replay": [P, P, U32, U32, P],
         "fj_sub_wait": [P, U64], "fj_sub_gpu_time_ns": [P, P], "fj_sub_error": [P, P], "fj_sub_profile": [P, P, U32, P],
         "fj_synchronize": [P], "fj_timer_create": [P, P], "fj_timer_record": [P, U64], "fj_timer_elapsed_ns": [P, U64, U64, P],
         "fj_kvpool_create": [P, U32, U32, U32, U32, P], "fj_kvpool_reserve": [P, P, P, U32, P], "fj_kvpool_release": [P, P, U32],

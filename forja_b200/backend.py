@@ -254,6 +254,34 @@ class Submission:
             self._h = None
 
 
+GRAPH_FIELD_U0, GRAPH_FIELD_U1, GRAPH_FIELD_U2, GRAPH_FIELD_U3 = 0, 1, 2, 3
+GRAPH_FIELD_INPUT_OFFSET, GRAPH_FIELD_OUTPUT_OFFSET, GRAPH_FIELD_INPUT_EXTENT, GRAPH_FIELD_OUTPUT_EXTENT = 0x100, 0x200, 0x300, 0x400
+
+
+class PreparedGraph:
+    """forja_core::PreparedGraph (crates/forja-core/src/graph.rs:1077-1160): a retained command template replayed with parameter values."""
+
+    def __init__(self, lib, handle, n_params: int):
+        self._lib, self._h, self.n_params = lib, handle, n_params
+
+    def replay(self, values: Sequence[int], profiled: bool = False) -> Submission:
+        raw = (C.c_uint32 * max(len(values), 1))(*values)
+        handle = C.c_void_p()
+        _check(self._lib.fj_graph_replay(self._h, raw, len(values), int(profiled), C.byref(handle)))
+        return Submission(self._lib, handle, [])
+
+    def close(self):
+        if self._h:
+            self._lib.fj_graph_destroy(self._h)
+        self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:  # noqa: BLE001 - interpreter shutdown
+            pass
+
+
 class CudaBackend:
     """The `forja-cuda` backend: one CUDA device, one stream, hand-written sm_100a kernels."""
 
@@ -337,7 +365,8 @@ class CudaBackend:
         _check(self._lib.fj_program_info(self._h, handle, C.byref(kernel), consts))
         return kernel.value, tuple(consts)
 
-    def submit(self, commands: CommandList, profiled: bool = False) -> Submission:
+    @staticmethod
+    def _encode(commands: CommandList):
         n = len(commands.dispatches)
         arr = (_lib.FjDispatch * max(n, 1))()
         keep = []
@@ -348,9 +377,24 @@ class CudaBackend:
             arr[i].op, arr[i].n_inputs, arr[i].n_outputs = d.op.code, len(d.inputs), len(d.outputs)
             arr[i].u0, arr[i].u1, arr[i].u2, arr[i].u3, arr[i].f0, arr[i].program = d.op.u0, d.op.u1, d.op.u2, d.op.u3, d.op.f0, d.op.program
             arr[i].inputs, arr[i].outputs = ins, outs
+        return arr, n, keep
+
+    def submit(self, commands: CommandList, profiled: bool = False) -> Submission:
+        arr, n, keep = self._encode(commands)
         handle = C.c_void_p()
         _check(self._lib.fj_submit(self._h, arr, n, int(profiled), C.byref(handle)))
         return Submission(self._lib, handle, keep)
+
+    def prepare_graph(self, commands: CommandList, bindings: Sequence[Tuple[int, int, int, int, int]], n_params: int) -> "PreparedGraph":
+        """Backend::prepare_graph: ``bindings`` are (dispatch, field code, parameter, scale, offset) with the field codes of
+        include/forja_cuda.h (GRAPH_FIELD_*); the bound field becomes offset + scale * values[parameter] at every replay."""
+        arr, n, _ = self._encode(commands)
+        raw = (_lib.FjGraphBinding * max(len(bindings), 1))()
+        for i, (dispatch, field_code, param, scale, offset) in enumerate(bindings):
+            raw[i].dispatch, raw[i].field, raw[i].param, raw[i].scale, raw[i].offset = dispatch, field_code, param, scale, offset
+        handle = C.c_void_p()
+        _check(self._lib.fj_graph_prepare(self._h, arr, n, raw, len(bindings), n_params, C.byref(handle)))
+        return PreparedGraph(self._lib, handle, n_params)
 
     # -- helpers for tests and benchmarks -----------------------------------------------------
     def tensor_from(self, array: np.ndarray, dtype: int) -> Tensor:

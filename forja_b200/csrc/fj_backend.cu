@@ -1239,6 +1239,82 @@ int32_t fj_submit(fj_backend* be, const fj_dispatch* dispatches, uint32_t count,
   return FJ_OK;
 }
 
+// ---- graph templates: Backend::prepare_graph / replay, crates/forja-core/src/backend.rs:858-967 ----
+
+struct fj_graph {
+  fj_backend* be = nullptr;
+  std::vector<fj_dispatch> dispatches;
+  std::vector<std::vector<fj_tensor>> inputs, outputs;  // storage the dispatches point into
+  std::vector<fj_graph_binding> bindings;
+  uint32_t n_params = 0;
+};
+
+// Where a binding lands, or nullptr for a field code / operand index the template does not have.
+// u32 fields come back through `narrow`, 64-bit tensor offsets through `wide`.
+static bool graph_field(fj_graph* g, const fj_graph_binding& b, uint32_t** narrow, uint64_t** wide) {
+  *narrow = nullptr; *wide = nullptr;
+  if (b.dispatch >= g->dispatches.size()) return false;
+  fj_dispatch& d = g->dispatches[b.dispatch];
+  if (b.field <= FJ_GRAPH_FIELD_U3) { uint32_t* u[4] = {&d.u0, &d.u1, &d.u2, &d.u3}; *narrow = u[b.field]; return true; }
+  const uint32_t kind = b.field & 0xF00u, operand = (b.field >> 4) & 0xFu, axis = b.field & 0xFu;
+  const bool is_input = kind == FJ_GRAPH_FIELD_INPUT_OFFSET || kind == FJ_GRAPH_FIELD_INPUT_EXTENT;
+  const bool is_output = kind == FJ_GRAPH_FIELD_OUTPUT_OFFSET || kind == FJ_GRAPH_FIELD_OUTPUT_EXTENT;
+  if (!is_input && !is_output) return false;
+  std::vector<fj_tensor>& tensors = is_input ? g->inputs[b.dispatch] : g->outputs[b.dispatch];
+  if (operand >= tensors.size()) return false;
+  fj_tensor& t = tensors[operand];
+  if (kind == FJ_GRAPH_FIELD_INPUT_OFFSET || kind == FJ_GRAPH_FIELD_OUTPUT_OFFSET) { if (axis != 0) return false; *wide = &t.offset; return true; }
+  if (axis >= t.rank) return false;
+  *narrow = &t.shape[axis];
+  return true;
+}
+
+int32_t fj_graph_prepare(fj_backend* be, const fj_dispatch* dispatches, uint32_t count, const fj_graph_binding* bindings, uint32_t n_bindings,
+                         uint32_t n_params, fj_graph** out) {
+  if (!be || !out || (count && !dispatches) || (n_bindings && !bindings) || n_params > 16) return FJ_INVALID_INPUT;  // ParamSpace holds at most 16 parameters
+  auto* g = new fj_graph();
+  g->be = be; g->n_params = n_params;
+  g->dispatches.assign(dispatches, dispatches + count);
+  g->inputs.resize(count); g->outputs.resize(count);
+  for (uint32_t i = 0; i < count; ++i) {
+    const fj_dispatch& d = dispatches[i];
+    if ((d.n_inputs && !d.inputs) || (d.n_outputs && !d.outputs) || d.n_inputs > 16 || d.n_outputs > 16) { delete g; return FJ_INVALID_INPUT; }
+    g->inputs[i].assign(d.inputs, d.inputs + d.n_inputs);
+    g->outputs[i].assign(d.outputs, d.outputs + d.n_outputs);
+  }
+  for (uint32_t i = 0; i < count; ++i) { g->dispatches[i].inputs = g->inputs[i].data(); g->dispatches[i].outputs = g->outputs[i].data(); }
+  g->bindings.assign(bindings, bindings + n_bindings);
+  for (const fj_graph_binding& b : g->bindings) {
+    uint32_t* narrow; uint64_t* wide;
+    if (b.param >= n_params || !graph_field(g, b, &narrow, &wide)) { delete g; return FJ_INVALID_INPUT; }
+  }
+  *out = g;
+  return FJ_OK;
+}
+
+// replay: every bound field becomes offset + scale * values[param], evaluated in checked 64-bit arithmetic and,
+// for 32-bit fields, refused when it does not fit (Affine::evaluate, crates/forja-core/src/symbolic.rs:249-262);
+// the instantiated commands then go through fj_submit, which validates them like any other submission.
+int32_t fj_graph_replay(fj_graph* g, const uint32_t* values, uint32_t n_values, uint32_t profiled, fj_submission** out) {
+  if (!g || !out || n_values != g->n_params || (n_values && !values)) return FJ_INVALID_INPUT;
+  // instantiate into a private copy so that concurrent replays of one template do not see each other's values
+  fj_graph copy;
+  copy.be = g->be; copy.n_params = g->n_params;
+  copy.dispatches = g->dispatches; copy.inputs = g->inputs; copy.outputs = g->outputs;
+  for (size_t i = 0; i < copy.dispatches.size(); ++i) { copy.dispatches[i].inputs = copy.inputs[i].data(); copy.dispatches[i].outputs = copy.outputs[i].data(); }
+  for (const fj_graph_binding& b : g->bindings) {
+    uint32_t* narrow; uint64_t* wide;
+    if (!graph_field(&copy, b, &narrow, &wide)) return FJ_INVALID_INPUT;
+    uint64_t v = 0;
+    if (__builtin_mul_overflow(static_cast<uint64_t>(b.scale), static_cast<uint64_t>(values[b.param]), &v) || __builtin_add_overflow(v, b.offset, &v)) return FJ_INVALID_INPUT;
+    if (narrow) { if (v > 0xFFFFFFFFull) return FJ_INVALID_INPUT; *narrow = static_cast<uint32_t>(v); }
+    else *wide = v;
+  }
+  return fj_submit(g->be, copy.dispatches.data(), static_cast<uint32_t>(copy.dispatches.size()), profiled, out);
+}
+
+void fj_graph_destroy(fj_graph* g) { delete g; }
+
 int32_t fj_sub_wait(fj_submission* sub, uint64_t timeout_ns) {
   if (!sub) return FJ_INVALID_INPUT;
   if (sub->done) return sub->result;

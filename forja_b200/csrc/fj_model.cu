@@ -529,7 +529,7 @@ void enqueue_dense_step(fj_dense_model* m, const StepPlan& plan) {
   fj::launch_argmax(ctx, plan.logits, dt, c.vocab, m->tokens_out, lanes, c.vocab, m->argmax_scratch);
 }
 
-constexpr unsigned kWorkGridStep = 256;   // recorded decode steps round their attention grid up to a multiple of this
+constexpr unsigned kWorkGridStep = 1024;  // recorded decode steps round their attention grid up to a multiple of this (a recording costs tens of ms)
 constexpr size_t kMaxStepGraphs = 24;     // least recently used recordings beyond this are dropped
 
 // Replays the recorded launch sequence of this step's bucket, recording it first when the bucket is new.
@@ -682,7 +682,7 @@ int32_t fj_dense_step(fj_dense_model* m, const uint32_t* token_ids, uint32_t* ou
 
 // Graph replay for the decode step (the backend-specific tier behind Backend::prepare_graph / replay,
 // crates/forja-core/src/backend.rs:858-967): with replay enabled, decode-only steps are recorded once per bucket
-// {lanes, split-K chunk, attention grid rounded up to 256 items, token source, logits target} as a CUDA graph and
+// {lanes, split-K chunk, attention grid rounded up to 1024 items, token source, logits target} as a CUDA graph and
 // replayed, so a step costs one graph launch on the host instead of one launch per kernel.
 int32_t fj_dense_graph_replay(fj_dense_model* m, uint32_t enabled) {
   if (!m) return FJ_INVALID_INPUT;

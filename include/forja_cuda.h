@@ -184,6 +184,33 @@ int32_t fj_program_info(fj_backend* be, uint64_t handle, uint32_t* kernel, float
  * ragged launch. */
 int32_t fj_submit(fj_backend* be, const fj_dispatch* dispatches, uint32_t count, uint32_t profiled,
                   fj_submission** out);
+/* Graph templates: prepare_graph / replay / replay_profiled (backend.rs:858-920; GraphTemplate,
+ * crates/forja-core/src/graph.rs:1062-1617). A template is a validated command list in which scalar operation
+ * parameters (TemplateOp: q_start, key_length, copy start, sample position) and tensor layouts (TemplateTensor::
+ * Symbolic: element offset, extents) may be affine in up to 16 replay parameters: value = offset + scale *
+ * values[param] (Affine, crates/forja-core/src/symbolic.rs:207-262, checked arithmetic). fj_graph_prepare copies
+ * the dispatches; fj_graph_replay instantiates them with this call's values and submits them - the reference's
+ * own default tier - so a replay answers exactly like the equivalent fj_submit (fj_dense_graph_replay below is
+ * the device-side tier for whole decode steps). Field codes: */
+enum {
+  FJ_GRAPH_FIELD_U0 = 0, FJ_GRAPH_FIELD_U1 = 1, FJ_GRAPH_FIELD_U2 = 2, FJ_GRAPH_FIELD_U3 = 3, /* fj_dispatch.u0 .. u3 */
+  FJ_GRAPH_FIELD_INPUT_OFFSET = 0x100,  /* | operand << 4 : element offset of input `operand` */
+  FJ_GRAPH_FIELD_OUTPUT_OFFSET = 0x200, /* | operand << 4 */
+  FJ_GRAPH_FIELD_INPUT_EXTENT = 0x300,  /* | operand << 4 | axis : shape[axis] of input `operand` */
+  FJ_GRAPH_FIELD_OUTPUT_EXTENT = 0x400  /* | operand << 4 | axis */
+};
+typedef struct fj_graph_binding {
+  uint32_t dispatch; /* index into the template's dispatches */
+  uint32_t field;    /* one of the codes above */
+  uint32_t param;    /* index into the replay values */
+  uint32_t scale;
+  uint64_t offset;
+} fj_graph_binding;
+typedef struct fj_graph fj_graph;
+int32_t fj_graph_prepare(fj_backend* be, const fj_dispatch* dispatches, uint32_t count, const fj_graph_binding* bindings,
+                         uint32_t n_bindings, uint32_t n_params, fj_graph** out);
+int32_t fj_graph_replay(fj_graph* graph, const uint32_t* values, uint32_t n_values, uint32_t profiled, fj_submission** out);
+void fj_graph_destroy(fj_graph* graph);
 /* Submission, backend.rs:609-647 */
 int32_t fj_sub_wait(fj_submission* sub, uint64_t timeout_ns); /* 0 = wait forever; FJ_TIMEOUT leaves the submission alive */
 int32_t fj_sub_gpu_time_ns(fj_submission* sub, uint64_t* ns);
@@ -375,7 +402,7 @@ int32_t fj_dense_step_stats(fj_dense_model* model, uint64_t* kernels, uint64_t* 
 /* Graph replay of the decode step: the backend-specific tier behind Backend::prepare_graph / replay
  * (crates/forja-core/src/backend.rs:858-967; the reference's default tier re-instantiates and re-submits the
  * template). With replay enabled, a decode-only step (every active lane appends one token) is recorded once per
- * bucket {lanes, split-K chunk, attention grid rounded up to 256 work items, token source, logits target} as a
+ * bucket {lanes, split-K chunk, attention grid rounded up to 1024 work items, token source, logits target} as a
  * CUDA graph and replayed afterwards: one graph launch on the host instead of one launch per kernel. Every
  * row-wise kernel of a replayed step runs `lanes` rows (rows past the packed count are padding whose appends are
  * refused), the attention kernel reads the live work-item count on the device. Steps that mix prompt pieces, or

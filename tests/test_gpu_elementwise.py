@@ -252,7 +252,7 @@ def test_submission_reports_time_serial_and_launches():
     prof = a.profile()
     assert [p[0] for p in prof] == [fb.backend.OP_COPY] * 2 and all(p[1] == 1 for p in prof)
     with pytest.raises(fb.BackendError) as e:  # unsupported operations are refused, not emulated
-        be.run(Op(fb.backend.OP_SDPA), [x], [out])
+        be.run(Op(18), [x], [out])  # Op::State, the recurrent-state update, is not on this path
     assert e.value.status == fb.backend.UNSUPPORTED_OPERATION
     with pytest.raises(fb.BackendError):  # read-only imports cannot be written
         ro = be.import_readonly(np.ones(4, np.float32), fb.F32)

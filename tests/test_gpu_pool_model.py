@@ -392,7 +392,7 @@ def test_replayed_decode_steps_equal_directly_launched_ones():
     """Graph replay (fj_dense_graph_replay): decode-only steps recorded once per bucket and replayed give bit-identical
     logits, tokens and cache contents to the same steps launched kernel by kernel - also with an idle lane in the batch
     (its rows are padding in the recorded launch), with host-fed and with device-fed tokens."""
-    cfg, page, steps = dict(TINY_BF16, max_rows=64), 16, 9
+    cfg, page, steps = dict(TINY_BF16, max_rows=128), 16, 9
     prompts = [5, 40, 17, 3, 29]
     lanes = len(prompts)
     be = backend()
