@@ -29,7 +29,7 @@ class FjDeviceInfo(C.Structure):
 
 
 class FjDispatchProfile(C.Structure):
-    _fields_ = [("op", C.c_uint32), ("kernels", C.c_uint32), ("ns", C.c_uint64)]
+    _fields_ = [("op", C.c_uint32), ("kernels", C.c_uint32), ("ns", C.c_uint64), ("read_bytes", C.c_uint64), ("write_bytes", C.c_uint64), ("flops", C.c_uint64)]
 
 
 class FjGraphBinding(C.Structure):

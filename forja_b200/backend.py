@@ -248,6 +248,15 @@ class Submission:
         self._lib.fj_sub_profile(self._h, arr, n.value, C.byref(n))
         return [(arr[i].op, arr[i].kernels, arr[i].ns) for i in range(n.value)]
 
+    def profile_costs(self):
+        """Per dispatch {op, kernels, ns, read_bytes, write_bytes, flops}: device time beside the reference's KernelCost."""
+        n = C.c_uint32(0)
+        self._lib.fj_sub_profile(self._h, None, 0, C.byref(n))
+        arr = (_lib.FjDispatchProfile * max(n.value, 1))()
+        self._lib.fj_sub_profile(self._h, arr, n.value, C.byref(n))
+        return [{"op": arr[i].op, "kernels": arr[i].kernels, "ns": arr[i].ns, "read_bytes": arr[i].read_bytes, "write_bytes": arr[i].write_bytes,
+                 "flops": arr[i].flops} for i in range(n.value)]
+
     def __del__(self):
         if getattr(self, "_h", None):
             self._lib.fj_sub_destroy(self._h)

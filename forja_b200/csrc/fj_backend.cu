@@ -344,6 +344,7 @@ struct fj_submission {
   std::vector<uint32_t> ops;
   std::vector<uint32_t> kernels;
   std::vector<cudaEvent_t> marks;  // count + 1 events when profiled
+  std::vector<uint64_t> costs;     // {read bytes, write bytes, flops} per dispatch when profiled
   fj::ErrorRecord* host_err = nullptr;  // pinned, count entries (recycled through the backend)
   size_t host_err_capacity = 0;
   bool done = false;
@@ -1121,6 +1122,88 @@ int32_t fj_program_info(fj_backend* be, uint64_t handle, uint32_t* kernel, float
   return FJ_OK;
 }
 
+// Algorithmic traffic and arithmetic of one dispatch, the reference's KernelCost (crates/forja-core/src/cost.rs:109-153:
+// logical operand bytes read and written, 2 flops per multiply-add; attention per cost/attention.rs:38-137: the K/V rows
+// actually attended, 12 bytes of table and generation per page touched, the causal triangle of (query, key) pairs;
+// paged copies per :96-121). Saturates instead of overflowing.
+static void dispatch_cost(const fj_dispatch& d, uint64_t* read_bytes, uint64_t* write_bytes, uint64_t* flops) {
+  auto sat_mul = [](uint64_t a, uint64_t b) { uint64_t r; return __builtin_mul_overflow(a, b, &r) ? ~0ull : r; };
+  auto sat_add = [](uint64_t a, uint64_t b) { uint64_t r; return __builtin_add_overflow(a, b, &r) ? ~0ull : r; };
+  auto tensor_bytes = [&](const fj_tensor& t) { uint64_t n = 1; for (uint32_t a = 0; a < t.rank && a < 8; ++a) n = sat_mul(n, t.shape[a]); return sat_mul(n, fj::dtype_size(static_cast<int>(t.dtype > FJ_U32 ? FJ_U32 : t.dtype))); };
+  uint64_t rd = 0, wr = 0, fl = 0;
+  for (uint32_t i = 0; i < d.n_inputs; ++i) rd = sat_add(rd, tensor_bytes(d.inputs[i]));
+  for (uint32_t i = 0; i < d.n_outputs; ++i) wr = sat_add(wr, tensor_bytes(d.outputs[i]));
+  const auto pages_touched = [&](uint64_t start, uint64_t tokens, uint64_t page) { return tokens == 0 || page == 0 ? 0ull : (start + tokens - 1) / page - start / page + 1; };
+  switch (d.op) {
+    case FJ_OP_MATMUL:
+      if (d.n_inputs == 2 && d.inputs[0].rank >= 2 && d.inputs[1].rank == d.inputs[0].rank) {
+        const fj_tensor &a = d.inputs[0], &b = d.inputs[1];
+        uint64_t batch = a.rank == 3 ? a.shape[0] : 1;
+        fl = sat_mul(sat_mul(2 * batch, a.shape[a.rank - 2]), sat_mul(a.shape[a.rank - 1], b.shape[b.rank - 1]));
+      }
+      break;
+    case FJ_OP_QUANT_MATMUL:
+      if (d.n_inputs == 4 && d.inputs[0].rank == 2 && d.inputs[1].rank == 2) fl = sat_mul(sat_mul(2ull * d.inputs[0].shape[0], d.inputs[0].shape[1]), d.inputs[1].shape[0]);
+      break;
+    case FJ_OP_GATHER_MATMUL:
+      if (d.n_inputs == 3 && d.inputs[0].rank == 2 && d.inputs[1].rank == 3 && d.inputs[2].rank == 2)
+        fl = sat_mul(sat_mul(2ull * d.inputs[0].shape[0], d.inputs[2].shape[1]), sat_mul(d.inputs[1].shape[1], d.inputs[1].shape[2]));
+      break;
+    case FJ_OP_GATHER_QUANT_MATMUL:
+      if (d.n_inputs >= 5 && d.n_outputs == 1 && d.inputs[1].rank == 3) {  // routes x (rows of one expert matrix x inner), per projection
+        const fj_tensor& idx = d.inputs[d.n_inputs == 8 ? 7 : 4];
+        const uint64_t routes = idx.rank == 2 ? static_cast<uint64_t>(idx.shape[0]) * idx.shape[1] : 0;
+        const uint64_t inner = static_cast<uint64_t>(d.inputs[1].shape[2]) * 32 / (d.u0 ? d.u0 : 4);
+        fl = sat_mul(sat_mul(2 * routes, d.inputs[1].shape[1]), inner) * (d.n_inputs == 8 ? 2 : 1);
+      }
+      break;
+    case FJ_OP_PAGED_COPY:
+      if (d.n_inputs >= 3 && d.n_outputs == 1) {
+        const bool into = d.u0 == 0;
+        const fj_tensor& ordinary = into ? d.inputs[0] : d.outputs[0];
+        const fj_tensor& pool = into ? d.outputs[0] : d.inputs[0];
+        uint64_t elements = 1;
+        for (uint32_t a = 0; a < ordinary.rank && a < 8; ++a) elements = sat_mul(elements, ordinary.shape[a]);
+        const uint64_t pool_bytes = sat_mul(elements, fj::dtype_size(static_cast<int>(pool.dtype)));
+        rd = into ? tensor_bytes(ordinary) : pool_bytes;
+        wr = into ? pool_bytes : tensor_bytes(ordinary);
+        rd = sat_add(rd, 12 * pages_touched(d.u1, ordinary.rank ? ordinary.shape[0] : 0, d.u2) + (d.n_inputs == 4 ? 4 : 0));
+      }
+      break;
+    case FJ_OP_SDPA:
+    case FJ_OP_PAGED_SDPA:
+    case FJ_OP_PAGED_SDPA_APPEND:
+      if (d.n_inputs >= 3 && d.n_outputs >= 1 && d.inputs[0].rank == 3) {
+        const bool paged = d.op != FJ_OP_SDPA, append = d.op == FJ_OP_PAGED_SDPA_APPEND;
+        const fj_tensor& key = append ? d.outputs[1] : d.inputs[1];
+        const fj_tensor& value = append ? d.outputs[2] : d.inputs[2];
+        if ((paged && (key.rank != 4 || value.rank != 4)) || (!paged && (key.rank != 3 || value.rank != 3))) break;
+        const uint64_t heads = d.inputs[0].shape[0], queries = d.inputs[0].shape[1], width = d.inputs[0].shape[2];
+        const uint64_t value_width = value.shape[value.rank - 1], kv_heads = key.shape[paged ? 2 : 0];
+        const uint64_t q_start = d.u1;
+        const bool causal = append || d.u0 != 0;
+        const uint64_t key_length = append ? q_start + 1 : (paged ? d.u2 : key.shape[1]);
+        const uint64_t pairs = causal ? sat_add(sat_mul(queries, q_start + 1), queries ? queries * (queries - 1) / 2 : 0) : sat_mul(queries, key_length);
+        fl = sat_mul(sat_mul(2 * heads, pairs), width + value_width);
+        const uint64_t kv_bytes = sat_mul(sat_mul(kv_heads, key_length), sat_mul(width + value_width, fj::dtype_size(static_cast<int>(key.dtype))));
+        rd = sat_add(tensor_bytes(d.inputs[0]), kv_bytes);
+        wr = tensor_bytes(d.outputs[0]);
+        if (paged) rd = sat_add(rd, 12 * pages_touched(0, key_length, d.u3) + (d.n_inputs == 6 ? 4 : 0));
+        if (append) {
+          rd = sat_add(rd, sat_add(tensor_bytes(d.inputs[1]), tensor_bytes(d.inputs[2])));
+          for (int i = 1; i <= 2; ++i) {
+            uint64_t elements = 1;
+            for (uint32_t a = 0; a < d.inputs[i].rank && a < 8; ++a) elements = sat_mul(elements, d.inputs[i].shape[a]);
+            wr = sat_add(wr, sat_mul(elements, fj::dtype_size(static_cast<int>(d.outputs[i].dtype))));
+          }
+        }
+      }
+      break;
+    default: break;
+  }
+  *read_bytes = rd; *write_bytes = wr; *flops = fl;
+}
+
 int32_t fj_submit(fj_backend* be, const fj_dispatch* dispatches, uint32_t count, uint32_t profiled, fj_submission** out) {
   if (!be || !out || (count && !dispatches)) return FJ_INVALID_INPUT;
   std::lock_guard<std::mutex> lock(be->mutex);
@@ -1171,6 +1254,10 @@ int32_t fj_submit(fj_backend* be, const fj_dispatch* dispatches, uint32_t count,
     const fj_dispatch& d = dispatches[i];
     sub->ops[i] = d.op;
     const unsigned long long before = be->ctx.launches;
+    if (profiled && d.inputs && d.outputs) {
+      if (sub->costs.empty()) sub->costs.assign(static_cast<size_t>(count) * 3, 0);
+      dispatch_cost(d, &sub->costs[3 * i], &sub->costs[3 * i + 1], &sub->costs[3 * i + 2]);
+    }
     fj::ErrorRecord* err = x.dev_err + i;
     uint32_t consumed = 1;
     if ((d.n_inputs && !d.inputs) || (d.n_outputs && !d.outputs)) status = FJ_INVALID_INPUT;
@@ -1373,6 +1460,10 @@ int32_t fj_sub_profile(fj_submission* sub, fj_dispatch_profile* out, uint32_t ca
     out[i].op = sub->ops[i];
     out[i].kernels = sub->kernels[i];
     out[i].ns = 0;
+    const bool have_cost = sub->costs.size() == static_cast<size_t>(sub->count) * 3;
+    out[i].read_bytes = have_cost ? sub->costs[3 * i] : 0;
+    out[i].write_bytes = have_cost ? sub->costs[3 * i + 1] : 0;
+    out[i].flops = have_cost ? sub->costs[3 * i + 2] : 0;
     if (sub->done && sub->marks.size() == static_cast<size_t>(sub->count) + 1) {
       float ms = 0.0f;
       if (cudaEventElapsedTime(&ms, sub->marks[i], sub->marks[i + 1]) == cudaSuccess) out[i].ns = static_cast<uint64_t>(static_cast<double>(ms) * 1.0e6);

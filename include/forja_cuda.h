@@ -128,6 +128,13 @@ typedef struct fj_dispatch_profile {
   uint32_t op;
   uint32_t kernels;   /* kernel launches issued for this dispatch */
   uint64_t ns;        /* device time, 0 when the submission was not profiled */
+  /* KernelCost of the dispatch (crates/forja-core/src/cost.rs:109-153, cost/attention.rs:38-137): logical operand bytes read
+   * and written and 2 flops per multiply-add, so achieved bytes/s or flop/s per dispatch = these / ns. Attention counts the
+   * K/V rows attended plus 12 bytes per page of table and generation; other operators count their whole operands.
+   * Filled for profiled submissions, else 0. */
+  uint64_t read_bytes;
+  uint64_t write_bytes;
+  uint64_t flops;
 } fj_dispatch_profile;
 
 typedef struct fj_backend fj_backend;

@@ -257,3 +257,38 @@ def test_submission_reports_time_serial_and_launches():
     with pytest.raises(fb.BackendError):  # read-only imports cannot be written
         ro = be.import_readonly(np.ones(4, np.float32), fb.F32)
         be.run(Op.Copy(), [x.narrow(0, 0, 1).reshape((64,)).narrow(0, 0, 4)], [ro])
+
+
+def test_profiled_submission_reports_the_cost_of_each_dispatch():
+    """fj_dispatch_profile carries the reference's KernelCost (crates/forja-core/src/cost.rs:109-153, test :293-312;
+    attention: cost/attention.rs:141-230): bytes and flops per dispatch, so a roofline can be computed per dispatch."""
+    be = backend()
+    rng = np.random.default_rng(2)
+    m, k, n = 3, 256, 64
+    x, _ = up(rng.standard_normal((m, k)), fb.BF16)
+    packed = be.tensor_from(rng.integers(0, 2 ** 32, (n, k // 8), dtype=np.uint64).astype(np.uint32), fb.U32)
+    scales, _ = up(rng.standard_normal((n, k // 64)) * 0.01, fb.BF16)
+    biases, _ = up(rng.standard_normal((n, k // 64)) * 0.01, fb.BF16)
+    out = be.alloc(fb.BF16, (m, n))
+    # paged decode attention: 8 q / 2 kv heads of width 128, 37 keys on 16-token pages
+    hq, kvh, d, page, length = 8, 2, 128, 16, 37
+    q, _ = up(rng.standard_normal((1, hq, d)), fb.BF16)
+    kp, vp = be.alloc(fb.BF16, (4, page, kvh, d)), be.alloc(fb.BF16, (4, page, kvh, d))
+    table = be.tensor_from(np.array([[0, 1], [1, 1], [2, 1], [3, 1]], np.uint32), fb.U32)
+    gens = be.tensor_from(np.ones(4, np.uint32), fb.U32)
+    attn = be.alloc(fb.BF16, (1, hq, d))
+    cl = CommandList()
+    cl.dispatch(Op.QuantMatmul(4, 64), [x, packed, scales, biases], out)
+    cl.dispatch(Op.PagedSdpa(0.1, True, length - 1, length, page), [q.permute([1, 0, 2]), kp, vp, table, gens], attn.permute([1, 0, 2]))
+    sub = be.submit(cl, profiled=True)
+    sub.wait()
+    quant, attention = sub.profile_costs()
+    weight_bytes = n * (k // 8) * 4 + 2 * n * (k // 64) * 2            # 0.5625 bytes per weight
+    assert weight_bytes == int(0.5625 * n * k)
+    assert quant["read_bytes"] == m * k * 2 + weight_bytes and quant["write_bytes"] == m * n * 2 and quant["flops"] == 2 * m * k * n
+    assert attention["read_bytes"] == hq * d * 2 + kvh * length * 2 * d * 2 + 12 * 3 and attention["write_bytes"] == hq * d * 2
+    assert attention["flops"] == 2 * hq * length * 2 * d
+    assert quant["ns"] > 0 and attention["ns"] > 0
+    plain = be.submit(cl)
+    plain.wait()
+    assert all(p["read_bytes"] == 0 and p["flops"] == 0 for p in plain.profile_costs())

@@ -1,7 +1,6 @@
 """Op::Sample / Op::SampleMasked on the GPU against the oracle's restatement of
 crates/forja-cpu/src/lib.rs:1553-1700 (parameter words, top-k / top-p truncation, counter-based
-Gumbel-max). Indices must be identical; the only tolerated difference is a choice that flips at a
-last-place difference between the device's and the host's expf/logf, bounded below at 2 per 1000."""
+Gumbel-max). Indices must be identical to the oracle's on every draw of the fixed seeds used here."""
 import numpy as np
 import pytest
 
@@ -65,7 +64,9 @@ def test_sampled_indices_equal_the_oracle(dt):
             if temperature == 0.0 or top_k == 1:
                 assert np.array_equal(got, want), f"greedy case {case} differs"
             assert np.array_equal(got, run_sample(x, params, position)), "same seed and position must reproduce"
-    assert different <= max(1, total // 500), f"{different} of {total} sampled indices differ from the oracle"
+    # Bit-exact given equal logits. A draw could only flip where the device's expf/logf and glibc's differ in the last place
+    # of a deciding key; on these fixed seeds (3 168 draws per dtype) none does, so the test demands zero differences.
+    assert different == 0, f"{different} of {total} sampled indices differ from the oracle"
 
 
 def test_masked_sampling_and_non_finite_logits():
@@ -90,7 +91,7 @@ def test_masked_sampling_and_non_finite_logits():
             if mask is not None:
                 assert all((allow[t // 32] >> (t % 32)) & 1 for t in got.tolist())
             assert got[2] == want[2] and got[4] == want[4] and got[6] == want[6]
-    assert different <= 1, f"{different} of {total} differ"
+    assert different == 0, f"{different} of {total} differ"
     only = np.zeros((width + 31) // 32, np.uint32)
     only[3] = 1 << 5
     assert set(run_sample(x, [bits(1.0), 0, bits(0.9), 1, 1], 0, only).tolist()) == {3 * 32 + 5}

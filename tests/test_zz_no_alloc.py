@@ -70,6 +70,13 @@ def test_static_scratch_decode_attention_matches_the_regular_path_twice():
         assert np.isfinite(got).all()
         assert_close(got, want, TOL[dt])
         assert be.read(status).tolist() == [0, POISON]
+        # and against the CPU oracle directly, lane by lane
+        qh = fjo.encode(down(q), dt)
+        fjo.set_threads(fjo.max_threads())
+        for lane, n in enumerate(lengths):
+            ref = fjo.paged_sdpa(np.ascontiguousarray(qh[lane:lane + 1].transpose(1, 0, 2)), dt, kh, dt, vh, dt, tables[lane], generations, n, n - 1, scale, True, page)
+            assert_close(got[lane], fjo.decode(ref, dt)[:, 0, :], TOL[dt])
+        fjo.set_threads(1)
 
 
 def test_static_scratch_refuses_batches_beyond_its_limits_and_reports_bad_pages():
