@@ -49,6 +49,10 @@ def parse_args():
     ap.add_argument("--ctx-max", type=int, default=CTX_MAX, help="largest context length (lower it for profiler captures)")
     ap.add_argument("--layers", type=int, default=0, help="override the layer count (profiler captures only; 0 = the model's 28)")
     ap.add_argument("--repeats", type=int, default=0, help="how often the block of --steps steps is timed (the median block is reported); 0 = 9 for blocks up to 64 steps, else 3, else 1")
+    ap.add_argument("--no-moe", action="store_true", help="skip the sharded sparse-MoE block")
+    ap.add_argument("--moe-lanes", type=int, default=256, help="lanes of the sparse-MoE block, in total over all GPUs")
+    ap.add_argument("--moe-steps", type=int, default=8)
+    ap.add_argument("--moe-layers", type=int, default=0, help="0 = the model's 48")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-graph-replay", action="store_true", help="launch every decode step kernel by kernel instead of replaying its recorded CUDA graph")
     return ap.parse_args()
@@ -346,6 +350,13 @@ def run_native(args):
     clocks = read_clock_samples(clocks_path)
 
     e2e_elapsed, _, (e2e_tok_sum,) = reduce_max_sum(dist, local, e2e_elapsed, 0, [e2e_tokens])
+    graph_stats = model.graph_stats()
+    giveups = int(be.tcgen05_wait_giveups())
+    parity = parity_check(args, cfg, be, pool, model, lanes, host_tokens) if world == 1 and not args.no_cpu_baseline else None
+    # the dense model and its 66 GB of KV planes go before the sparse model comes
+    model.close()
+    pool.close()
+    moe = None if args.no_moe else moe_ep(args, rank, world, local, dist)
     if rank != 0:
         return None
     peaks = load_peaks()
@@ -364,8 +375,8 @@ def run_native(args):
         "e2e": {"value": e2e_tok_sum / e2e_elapsed, "unit": "tok/s", "h2d_bytes_per_step": h2d / e2e_steps, "d2h_bytes_per_step": d2h / e2e_steps,
                 "ms_per_step": e2e_elapsed / e2e_steps * 1e3, "mean_kv_tokens_per_step": e2e_kv_tokens / e2e_steps},
         "gpu_launches": int(launches),
-        "health": {"tcgen05_wait_giveups": int(be.tcgen05_wait_giveups())},
-        "graph_replay": model.graph_stats(),
+        "health": {"tcgen05_wait_giveups": giveups},
+        "graph_replay": graph_stats,
         "roofline": {"kernel": "attn_decode_mma_kernel (paged GQA decode attention, split-K)", "bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"],
                      "unit": "GB/s", "frac": (achieved / peaks["hbm_gbs"]) if achieved else None, "peak_source": peaks["source"],
                      "algorithmic_bytes_per_launch": per_launch_bytes, "launches": int(attn_launches), "avg_launch_us": attn_ns / max(attn_launches, 1) * 1e-3,
@@ -375,12 +386,45 @@ def run_native(args):
     step_bytes = 2 * sum_weight_params(cfg) + (kv_tokens / args.steps) * cfg["layers"] * cfg["kv_heads"] * cfg["head_dim"] * 2 * 2
     result["step_roofline"] = {"algorithmic_gb_per_step": step_bytes / 1e9, "achieved_gbs": step_bytes / 1e9 / (elapsed / args.steps),
                                "frac_of_hbm_peak": step_bytes / 1e9 / (elapsed / args.steps) / peaks["hbm_gbs"]}
+    if moe is not None:
+        result["moe_ep"] = moe
+    if parity is not None:
+        result["parity_check"] = parity
     if world == 1 and not args.no_cpu_baseline:
-        result["parity_check"] = parity_check(args, cfg, be, pool, model, lanes, host_tokens)
         result["cpu_baseline"] = cpu_baseline(args, cfg)
-    model.close()
-    pool.close()
     return result
+
+
+def moe_ep(args, rank, world, local, dist):
+    """The sharded sparse-MoE step (Qwen3-30B-A3B shape) beside the headline: 256 lanes in total, experts sharded over
+    the ranks with an NCCL all-to-all per MoE layer (fj_ep_* / fj_moe_step), so that the scaling run carries its
+    1/2/4/8-GPU numbers. Every rank takes part; the block reports whole-job tokens per second (maximum over ranks of the
+    device time) and the step's phases."""
+    from forja_b200 import benchmarks
+
+    def exchange(mine):
+        box = [mine]
+        dist.broadcast_object_list(box, src=0)
+        return box[0]
+
+    def barrier_all():
+        if dist is not None:
+            dist.barrier()
+
+    def reduce(value, op):
+        if dist is None:
+            return value
+        import torch
+        t = torch.tensor([value], dtype=torch.float64, device=f"cuda:{local}")
+        dist.all_reduce(t, op=op)
+        return float(t.item())
+
+    try:
+        return benchmarks.moe_ep_block(rank, world, local, exchange, barrier_all, lambda v: reduce(v, dist.ReduceOp.MAX if dist else None),
+                                       lambda v: reduce(v, dist.ReduceOp.SUM if dist else None), lanes_total=args.moe_lanes, steps=args.moe_steps, warmup=3,
+                                       layers=args.moe_layers, seed=args.seed)
+    except Exception as error:  # noqa: BLE001 - the headline line is still printed; the failure is reported in the block
+        return {"error": f"{type(error).__name__}: {error}"}
 
 
 def parity_check(args, cfg, be, pool, model, lanes, host_tokens):

@@ -32,6 +32,11 @@ class FjDispatchProfile(C.Structure):
     _fields_ = [("op", C.c_uint32), ("kernels", C.c_uint32), ("ns", C.c_uint64), ("read_bytes", C.c_uint64), ("write_bytes", C.c_uint64), ("flops", C.c_uint64)]
 
 
+class FjKvCheckpoint(C.Structure):
+    _fields_ = [("pool", C.c_uint64), ("lane_epoch", C.c_uint64), ("logical_len", C.c_uint64)] + \
+               [(n, C.c_uint32) for n in ("lane", "active", "has_tail", "index", "page", "immutable", "retained", "reserved")]
+
+
 class FjGraphBinding(C.Structure):
     _fields_ = [("dispatch", C.c_uint32), ("field", C.c_uint32), ("param", C.c_uint32), ("scale", C.c_uint32), ("offset", C.c_uint64)]
 
@@ -80,7 +85,7 @@ EXPORTS = [
     "fj_program_info", "fj_program_classify", "fj_tensor_byte_span", "fj_submit", "fj_graph_prepare", "fj_graph_replay", "fj_graph_destroy", "fj_sub_wait", "fj_sub_gpu_time_ns", "fj_sub_completion_serial", "fj_sub_error",
     "fj_sub_kernel_launches", "fj_sub_profile", "fj_sub_destroy", "fj_synchronize", "fj_kernel_launch_count", "fj_timer_create",
     "fj_timer_record", "fj_timer_elapsed_ns", "fj_kvpool_create", "fj_kvpool_destroy", "fj_kvpool_reserve", "fj_kvpool_release",
-    "fj_kvpool_read_table", "fj_kvpool_read_generations", "fj_kvpool_read_free", "fj_kvpool_read_refcounts", "fj_kvpool_fork", "fj_kvpool_cow_tail", "fj_dense_copy_page", "fj_kvpool_tables_buffer",
+    "fj_kvpool_read_table", "fj_kvpool_read_generations", "fj_kvpool_read_free", "fj_kvpool_read_refcounts", "fj_kvpool_fork", "fj_kvpool_cow_tail", "fj_kvpool_rewind_private", "fj_kvpool_checkpoint", "fj_kvpool_rollback", "fj_kvpool_checkpoint_drop", "fj_dense_copy_page", "fj_kvpool_tables_buffer",
     "fj_kvpool_generations_buffer", "fj_pack_step", "fj_dense_model_create", "fj_dense_model_destroy", "fj_dense_step",
     "fj_dense_step_stats", "fj_dense_graph_replay", "fj_dense_graph_stats", "fj_dense_kv_pages", "fj_dense_fill_kv", "fj_dense_profile_attention", "fj_dense_attention_time",
     "fj_paged_decode_attention_static", "fj_sched_create", "fj_sched_destroy", "fj_sched_set_prompt_chunk_multiple", "fj_sched_enqueue",
@@ -90,7 +95,7 @@ EXPORTS = [
     "fj_safetensors_file_len", "fj_safetensors_data_start", "fj_safetensors_tensor", "fj_safetensors_find", "fj_weights_last_error",
     "fj_safetensors_import", "fj_safetensors_view", "fj_safetensors_quant_views",
     "fj_prompt_chunk_work", "fj_prompt_chunk_merged_work", "fj_reservations_fit", "fj_prefill_plan",
-    "fj_ep_load", "fj_ep_unique_id", "fj_ep_create", "fj_ep_destroy", "fj_ep_all_to_all", "fj_moe_model_create", "fj_moe_model_destroy",
+    "fj_ep_load", "fj_ep_unique_id", "fj_ep_create", "fj_ep_destroy", "fj_ep_all_to_all", "fj_ep_set_timeout", "fj_ep_poll_selftest", "fj_moe_model_create", "fj_moe_model_destroy",
     "fj_moe_step", "fj_moe_step_stats", "fj_fill_random", "fj_tcgen05_wait_giveups", "fj_moe_capture_routes", "fj_moe_read_routes", "fj_moe_phase_timing", "fj_moe_read_phase_ms",
 ]
 
@@ -141,7 +146,7 @@ def load():
         "fj_synchronize": [P], "fj_timer_create": [P, P], "fj_timer_record": [P, U64], "fj_timer_elapsed_ns": [P, U64, U64, P],
         "fj_kvpool_create": [P, U32, U32, U32, U32, P], "fj_kvpool_reserve": [P, P, P, U32, P], "fj_kvpool_release": [P, P, U32],
         "fj_kvpool_read_table": [P, U32, P], "fj_kvpool_read_generations": [P, P], "fj_kvpool_read_free": [P, P, U32, P],
-        "fj_kvpool_read_refcounts": [P, P], "fj_kvpool_fork": [P, U32, U64, U32, U64, U64], "fj_kvpool_cow_tail": [P, U32, U64, P], "fj_dense_copy_page": [P, U32, U32, U32],
+        "fj_kvpool_read_refcounts": [P, P], "fj_kvpool_fork": [P, U32, U64, U32, U64, U64], "fj_kvpool_cow_tail": [P, U32, U64, P], "fj_kvpool_rewind_private": [P, U32, U64, U64], "fj_kvpool_checkpoint": [P, U32, U64, P], "fj_kvpool_rollback": [P, U32, P, P], "fj_kvpool_checkpoint_drop": [P, P], "fj_dense_copy_page": [P, U32, U32, U32],
         "fj_pack_step": [P, P, P, U32, P], "fj_dense_model_create": [P, P, U64, U64, P, P, P], "fj_dense_step": [P, P, P, U64],
         "fj_dense_step_stats": [P, P, P], "fj_dense_graph_replay": [P, U32], "fj_dense_graph_stats": [P, P, P, P], "fj_dense_kv_pages": [P, U32, U32, U32, U32, P, U32], "fj_dense_fill_kv": [P, U64], "fj_dense_profile_attention": [P, U32],
         "fj_dense_attention_time": [P, P, P],
@@ -168,7 +173,7 @@ def load():
         "fj_prompt_chunk_work": ([U32, U32, U32], U32), "fj_prompt_chunk_merged_work": ([U32, U32, U32], U32),
         "fj_reservations_fit": ([U32, U32, P, U64], I32), "fj_prefill_plan": ([U32, U32, U32, P, U64], U64),
         "fj_ep_load": ([C.c_char_p], I32), "fj_ep_unique_id": ([P], I32), "fj_ep_create": ([P, P, U32, U32, P], I32), "fj_ep_destroy": ([P], None),
-        "fj_ep_all_to_all": ([P, U64, U64, U64], I32), "fj_moe_model_create": ([P, P, P, U64, P, P, P, P, P], I32),
+        "fj_ep_all_to_all": ([P, U64, U64, U64], I32), "fj_ep_set_timeout": ([P, U64], I32), "fj_ep_poll_selftest": ([U64, U64, U64, P], I32), "fj_moe_model_create": ([P, P, P, U64, P, P, P, P, P], I32),
         "fj_moe_model_destroy": ([P], None), "fj_moe_step": ([P, P, P, U64], I32), "fj_moe_step_stats": ([P, P, P], I32),
         "fj_fill_random": ([P, U64, U64, U64, U32, U64, C.c_float, C.c_float], I32), "fj_tcgen05_wait_giveups": ([P, P], I32), "fj_moe_capture_routes": ([P, U32], I32), "fj_moe_read_routes": ([P, U32, U32, P, P], I32), "fj_moe_phase_timing": ([P, U32], I32), "fj_moe_read_phase_ms": ([P, P], I32),
     }

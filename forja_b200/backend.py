@@ -25,6 +25,7 @@ STATUS_NAMES = ["Ok", "QuotaExceeded", "AllocationFailed", "ExecutionFailed", "D
                 "Timeout", "InvalidInput", "UnsupportedOperation", "IndexOutOfRange"]
 OK, QUOTA_EXCEEDED, ALLOCATION_FAILED, EXECUTION_FAILED, DEVICE_EXECUTION_FAILED, DEVICE_ERROR_FLAG, TIMEOUT, INVALID_INPUT, \
     UNSUPPORTED_OPERATION, INDEX_OUT_OF_RANGE = range(10)
+POOL_SHARED_TAIL, POOL_INVALID_CHECKPOINT, POOL_CORRUPT_STATE = 30, 31, 32
 
 
 class BackendError(RuntimeError):
@@ -521,6 +522,24 @@ class KvPool:
         out = (C.c_uint32 * 4)()
         status = int(self._lib.fj_kvpool_cow_tail(self._h, lane, logical_len, out))
         return status, bool(out[0]), int(out[1]), int(out[2]), int(out[3])
+
+    def rewind_private(self, lane: int, current_len: int, new_len: int) -> int:
+        """PagedSequence::rewind_private as a check: OK, POOL_INVALID_CHECKPOINT or POOL_SHARED_TAIL (the length itself lives with the caller)."""
+        return self._lib.fj_kvpool_rewind_private(self._h, lane, current_len, new_len)
+
+    def checkpoint(self, lane: int, logical_len: int) -> "_lib.FjKvCheckpoint":
+        cp = _lib.FjKvCheckpoint()
+        _check(self._lib.fj_kvpool_checkpoint(self._h, lane, logical_len, C.byref(cp)))
+        return cp
+
+    def rollback(self, lane: int, checkpoint) -> Tuple[int, int]:
+        """Consumes the checkpoint; returns (status, restored logical length)."""
+        length = C.c_uint64(0)
+        status = self._lib.fj_kvpool_rollback(self._h, lane, C.byref(checkpoint), C.byref(length))
+        return status, length.value
+
+    def drop_checkpoint(self, checkpoint) -> int:
+        return self._lib.fj_kvpool_checkpoint_drop(self._h, C.byref(checkpoint))
 
     def tables_tensor(self) -> Tensor:
         return Tensor(self._lib.fj_kvpool_tables_buffer(self._h), Layout.contiguous(U32, (self.lanes, self.table_pages, 2)), self.lanes * self.table_pages * 8)

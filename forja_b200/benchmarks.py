@@ -238,6 +238,82 @@ def run_moe(args):
         dist.destroy_process_group()
 
 
+def moe_ep_block(rank, world, local_rank, exchange, barrier, max_over_ranks, sum_over_ranks, lanes_total=256, steps=8, warmup=3, layers=0, seed=0,
+                 prompt_budget=2048, prompt_range=(512, 4096), prefill_limit=4):
+    """One measurement of the sparse-MoE continuous-batching step (Qwen3-30B-A3B shape, q4 weights, bf16 activations) with the
+    experts sharded over `world` ranks: `lanes_total` lanes split evenly over the ranks (strong scaling over the lanes), every
+    rank prefilling up to `prompt_budget` prompt tokens per step beside its decode rows. `exchange(obj)` broadcasts rank 0's
+    object (the NCCL id of the expert-parallel group), `barrier()` aligns the ranks, `max_over_ranks(x)` / `sum_over_ranks(x)`
+    reduce a float. Timed with CUDA events on the backend's stream between barriers, maximum over ranks; two further steps
+    run with per-phase events for the split. Returns the block on every rank."""
+    cfg = dict(MOE)
+    if layers:
+        cfg["layers"] = layers
+    lanes = max(1, lanes_total // world)
+    cfg["max_rows"] = lanes + prompt_budget
+    cfg["grouped_min_routes"] = 0
+    cfg["stream_rows_per_expert"] = 0
+    cfg["ep_return_bf16"] = 0
+    be = fb.CudaBackend(local_rank)
+    ep = fb.ExpertParallel(be, rank, world, exchange) if world > 1 else None
+    table_pages = (prompt_range[1] + 256 + 1 + PAGE - 1) // PAGE + 1
+    pool = fb.KvPool(be, PAGE, lanes * table_pages + 8, lanes, table_pages)
+    model = build_moe(be, pool, cfg, ep, rank, world)
+    state = MoeLanes(pool, lanes, seed + rank, prompt_budget, prefill_limit, prompt_range, False)
+    rng = np.random.default_rng(seed + 77 + rank)
+    t0, t1 = be.timer(), be.timer()
+
+    def one_step():
+        starts, tokens = state.plan()
+        rows = int(tokens.sum())
+        pool.pack_step(starts, tokens)
+        ids = rng.integers(0, cfg["vocab"], rows).astype(np.uint32) if rows else None
+        model.step(ids, want_tokens=rows > 0, lanes=lanes)
+        state.advance(tokens)
+        return rows, model.stats()["kernels"]
+
+    for _ in range(warmup):
+        one_step()
+    be.synchronize()
+    barrier()
+    be.timer_record(t0)
+    processed = kernels = 0
+    for _ in range(steps):
+        rows, launched = one_step()
+        processed += rows
+        kernels += launched
+    be.timer_record(t1)
+    be.synchronize()
+    barrier()
+    elapsed = max_over_ranks(be.timer_elapsed_ns(t0, t1) * 1e-9)
+    total = sum_over_ranks(float(processed))
+    model.phase_timing(True)
+    phase_ms, phase_steps = [0.0] * 4, 2
+    for _ in range(phase_steps):
+        one_step()
+        phase_ms = [a + b for a, b in zip(phase_ms, model.phase_ms())]
+    model.phase_timing(False)
+    phases = {name: max_over_ranks(v / phase_steps) for name, v in zip(("attention_and_router", "dispatch", "experts", "return_and_combine"), phase_ms)}
+    rows_per_step = total / steps / world
+    remote = (world - 1) / world
+    block = {
+        "workload": "qwen3-30b-a3b-arch q4 sparse-MoE continuous batching (chunked prefill + decode), %d layers, 128 experts top-8" % cfg["layers"],
+        "n_gpus": world, "scaling": "strong over the lanes (%d lanes in total, %d per GPU); prompt budget %d tokens per GPU and step" % (lanes_total, lanes, prompt_budget),
+        "tok_s": total / elapsed, "ms_per_step": elapsed / steps * 1e3, "steps": steps, "warmup": warmup, "rows_per_gpu_step": rows_per_step,
+        "phase_ms_per_step_max_over_ranks": phases,
+        "exchange_mb_per_layer_and_gpu": {"dispatch_bf16": rows_per_step * cfg["top_k"] * remote * cfg["hidden"] * 2 / 1e6,
+                                          "return_f32": rows_per_step * cfg["top_k"] * remote * cfg["hidden"] * 4 / 1e6},
+        "gpu_launches": int(sum_over_ranks(float(kernels))),
+        "parallelism": ("experts sharded over %d GPUs, NCCL send/recv all-to-all per MoE layer, lanes data-parallel" % world) if world > 1 else "single GPU",
+    }
+    model.close()
+    pool.close()
+    if ep is not None:
+        ep.close()
+    be.close()
+    return block
+
+
 def load_peaks():
     try:
         with open(os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "MEASURED_PEAKS.json")) as f:

@@ -61,6 +61,7 @@ struct fj_kvpool {
   fj::PackOutputs pack{};
   std::vector<uint32_t> host_starts, host_tokens;  // last packed step (host copy for grid sizing)
   uint32_t rows = 0, lanes_packed = 0;
+  std::vector<uint64_t> lane_epoch;  // bumped when a lane is released: identity of the sequence a checkpoint was taken from
 };
 
 namespace fjb {

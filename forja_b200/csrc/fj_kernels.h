@@ -237,6 +237,8 @@ void launch_kvpool_cow_tail(Ctx& ctx, const KvPoolDevice& pool, const unsigned* 
 struct PackOutputs {
   unsigned *logical_lengths, *query_starts, *absolute_positions, *activity, *cu_seqlens, *positions, *slot_mapping, *row_lane;
 };
+// rewind check / checkpoint / rollback / checkpoint drop on the device pool; see kvpool_boundary_kernel for the argument words.
+void launch_kvpool_boundary(Ctx& ctx, const KvPoolDevice& pool, const unsigned* args, int* result);
 void launch_pack_step(Ctx& ctx, const KvPoolDevice& pool, const unsigned* starts, const unsigned* tokens, unsigned lanes,
                       const PackOutputs& out, unsigned rows_cap);
 // Builds AttnSeq / AttnWork lists for the dense step from packed metadata (one CTA).

@@ -133,6 +133,9 @@ int32_t fj_kvpool_release(fj_kvpool* pool, const uint32_t* lanes, uint32_t count
   if (cudaMallocAsync(reinterpret_cast<void**>(&staged), static_cast<size_t>(count) * 4, be->stream) != cudaSuccess) { cudaGetLastError(); return FJ_ALLOCATION_FAILED; }
   cudaMemcpyAsync(staged, lanes, count * 4, cudaMemcpyHostToDevice, be->stream);
   fj::launch_kvpool_release(be->ctx, pool->dev, staged, count);
+  if (pool->lane_epoch.size() < pool->dev.lanes) pool->lane_epoch.resize(pool->dev.lanes, 0);
+  for (uint32_t i = 0; i < count; ++i)
+    if (lanes[i] < pool->dev.lanes) ++pool->lane_epoch[lanes[i]];  // whatever binds this lane next is another sequence
   cudaFreeAsync(staged, be->stream);
   return FJ_OK;
 }
@@ -194,6 +197,67 @@ int32_t fj_kvpool_cow_tail(fj_kvpool* pool, uint32_t lane, uint64_t logical_len,
   if (call != FJ_OK) return call;
   for (int i = 0; i < 4; ++i) out4[i] = static_cast<uint32_t>(result[1 + i]);
   return result[0];
+}
+
+// ---- sequence boundaries: rewind_private / checkpoint / rollback, crates/forja-core/src/paged_pool.rs:864-883, 1061-1123 ----
+
+int32_t fj_kvpool_rewind_private(fj_kvpool* pool, uint32_t lane, uint64_t current_len, uint64_t new_len) {
+  if (!pool || current_len > 0xFFFFFFFFull || new_len > 0xFFFFFFFFull) return FJ_INVALID_INPUT;
+  const uint32_t args[4] = {0, lane, static_cast<uint32_t>(current_len), static_cast<uint32_t>(new_len)};
+  int32_t result[6] = {0, 0, 0, 0, 0, 0};
+  const int32_t call = pool_control_call(pool, args, 4, result, 6, [&](fj::Ctx& ctx, const unsigned* a, int* r) { fj::launch_kvpool_boundary(ctx, pool->dev, a, r); });
+  return call != FJ_OK ? call : result[0];
+}
+
+int32_t fj_kvpool_checkpoint(fj_kvpool* pool, uint32_t lane, uint64_t logical_len, fj_kv_checkpoint* out) {
+  if (!pool || !out || logical_len > 0xFFFFFFFFull || lane >= pool->dev.lanes) return FJ_INVALID_INPUT;
+  const uint32_t args[3] = {1, lane, static_cast<uint32_t>(logical_len)};
+  int32_t result[6] = {0, 0, 0, 0, 0, 0};
+  const int32_t call = pool_control_call(pool, args, 3, result, 6, [&](fj::Ctx& ctx, const unsigned* a, int* r) { fj::launch_kvpool_boundary(ctx, pool->dev, a, r); });
+  if (call != FJ_OK) return call;
+  if (result[0] != 0) return result[0];
+  memset(out, 0, sizeof(*out));
+  out->pool = reinterpret_cast<uint64_t>(pool);
+  out->lane_epoch = pool->lane_epoch.size() > lane ? pool->lane_epoch[lane] : 0;
+  out->logical_len = logical_len;
+  out->lane = lane; out->active = 1;
+  out->has_tail = static_cast<uint32_t>(result[1]); out->index = static_cast<uint32_t>(result[2]); out->page = static_cast<uint32_t>(result[3]);
+  out->immutable = static_cast<uint32_t>(result[4]); out->retained = static_cast<uint32_t>(result[5]);
+  return FJ_OK;
+}
+
+// SequenceCheckpoint::belongs_to: live, made by this pool, and the lane still holds the sequence it held then.
+static bool checkpoint_belongs_to(fj_kvpool* pool, uint32_t lane, const fj_kv_checkpoint* cp) {
+  return cp->active != 0 && cp->pool == reinterpret_cast<uint64_t>(pool) && cp->lane == lane && lane < pool->dev.lanes &&
+         (pool->lane_epoch.size() > lane ? pool->lane_epoch[lane] : 0) == cp->lane_epoch;
+}
+
+int32_t fj_kvpool_checkpoint_drop(fj_kvpool* pool, fj_kv_checkpoint* cp) {
+  if (!pool || !cp) return FJ_INVALID_INPUT;
+  if (cp->active == 0 && cp->retained == 0) return FJ_OK;
+  const bool owes = cp->has_tail && cp->retained && cp->pool == reinterpret_cast<uint64_t>(pool);
+  cp->active = 0; cp->retained = 0;
+  if (!owes) return FJ_OK;
+  const uint32_t args[3] = {3, cp->page, 1};
+  int32_t result[6] = {0, 0, 0, 0, 0, 0};
+  const int32_t call = pool_control_call(pool, args, 3, result, 6, [&](fj::Ctx& ctx, const unsigned* a, int* r) { fj::launch_kvpool_boundary(ctx, pool->dev, a, r); });
+  return call != FJ_OK ? call : result[0];
+}
+
+int32_t fj_kvpool_rollback(fj_kvpool* pool, uint32_t lane, fj_kv_checkpoint* cp, uint64_t* logical_len) {
+  if (!pool || !cp) return FJ_INVALID_INPUT;
+  if (!checkpoint_belongs_to(pool, lane, cp)) {  // a foreign or stale checkpoint is refused and dropped
+    fj_kvpool_checkpoint_drop(pool, cp);
+    return FJ_POOL_INVALID_CHECKPOINT;
+  }
+  const uint32_t args[7] = {2, lane, cp->has_tail, cp->index, cp->page, cp->immutable, cp->retained};
+  int32_t result[6] = {0, 0, 0, 0, 0, 0};
+  const int32_t call = pool_control_call(pool, args, 7, result, 6, [&](fj::Ctx& ctx, const unsigned* a, int* r) { fj::launch_kvpool_boundary(ctx, pool->dev, a, r); });
+  cp->active = 0; cp->retained = 0;  // consumed: the kernel has settled every reference the checkpoint held
+  if (call != FJ_OK) return call;
+  if (result[0] != 0) return result[0];
+  if (logical_len) *logical_len = cp->logical_len;
+  return FJ_OK;
 }
 
 uint64_t fj_kvpool_tables_buffer(fj_kvpool* pool) { return pool ? pool->buf_tables : 0; }

@@ -23,6 +23,9 @@
 // identical bits. Received rows land in local memory before any kernel reads them.
 #include "fj_backend.h"
 
+#include <chrono>
+#include <thread>
+
 #include <dlfcn.h>
 #include <string.h>
 
@@ -43,6 +46,7 @@ struct NcclApi {
   int (*Recv)(void* buf, size_t count, int dtype, int peer, void* comm, cudaStream_t stream) = nullptr;
   int (*GroupStart)() = nullptr;
   int (*GroupEnd)() = nullptr;
+  int (*CommAbort)(void* comm) = nullptr;
 };
 NcclApi g_nccl;
 std::mutex g_nccl_mutex;
@@ -54,10 +58,30 @@ constexpr int kNcclInt8 = 0;  // ncclInt8 / ncclChar
 
 }  // namespace
 
+// Polls `done()` until it answers true or `timeout_ms` has passed (0 = no limit); sleeps briefly between polls once the
+// first millisecond is over. Returns false on expiry. The clock is injectable so that the expiry path can be exercised
+// on the host without a device (fj_ep_poll_selftest).
+template <typename Done, typename Clock>
+bool poll_until(Done done, uint64_t timeout_ms, Clock now_ms) {
+  const uint64_t begin = now_ms();
+  for (;;) {
+    if (done()) return true;
+    const uint64_t waited = now_ms() - begin;
+    if (timeout_ms != 0 && waited >= timeout_ms) return false;
+    if (waited >= 1) std::this_thread::sleep_for(std::chrono::microseconds(50));
+  }
+}
+inline uint64_t steady_ms() {
+  return static_cast<uint64_t>(std::chrono::duration_cast<std::chrono::milliseconds>(std::chrono::steady_clock::now().time_since_epoch()).count());
+}
+
 struct fj_ep {
   fj_backend* be = nullptr;
   void* comm = nullptr;
   uint32_t rank = 0, world = 1;
+  uint64_t wait_timeout_ms = 60000;  // host waits on an exchange give up after this long (fj_ep_set_timeout)
+  bool aborted = false;              // the communicator was aborted after a wait ran out: every later exchange answers FJ_TIMEOUT
+  cudaEvent_t wait_event = nullptr;
 };
 
 extern "C" {
@@ -76,6 +100,7 @@ int32_t fj_ep_load(const char* libnccl_path) {
   api.Recv = reinterpret_cast<int (*)(void*, size_t, int, int, void*, cudaStream_t)>(dlsym(h, "ncclRecv"));
   api.GroupStart = reinterpret_cast<int (*)()>(dlsym(h, "ncclGroupStart"));
   api.GroupEnd = reinterpret_cast<int (*)()>(dlsym(h, "ncclGroupEnd"));
+  api.CommAbort = reinterpret_cast<int (*)(void*)>(dlsym(h, "ncclCommAbort"));  // optional: only the watchdog uses it
   if (!api.GetUniqueId || !api.CommInitRank || !api.CommDestroy || !api.Send || !api.Recv || !api.GroupStart || !api.GroupEnd) { dlclose(h); return FJ_UNSUPPORTED_OPERATION; }
   g_nccl = api;
   return FJ_OK;
@@ -109,19 +134,55 @@ void fj_ep_destroy(fj_ep* ep) {
   {
     std::lock_guard<std::mutex> lock(ep->be->mutex);
     cudaSetDevice(ep->be->device);
-    cudaStreamSynchronize(ep->be->stream);
+    if (!ep->aborted) cudaStreamSynchronize(ep->be->stream);
     if (ep->comm) g_nccl.CommDestroy(ep->comm);
+    if (ep->wait_event) cudaEventDestroy(ep->wait_event);
   }
   delete ep;
+}
+
+int32_t fj_ep_set_timeout(fj_ep* ep, uint64_t timeout_ms) {
+  if (!ep) return FJ_INVALID_INPUT;
+  std::lock_guard<std::mutex> lock(ep->be->mutex);
+  ep->wait_timeout_ms = timeout_ms;
+  return FJ_OK;
+}
+
+// Host-only check of the bounded wait: a condition that turns true after `ready_after_polls` polls (0 = never) is polled
+// against a simulated clock that advances `tick_ms` per reading. Returns 1 when the wait saw the condition, 0 when it gave
+// up at the deadline; *polls receives how often the condition was asked.
+int32_t fj_ep_poll_selftest(uint64_t timeout_ms, uint64_t ready_after_polls, uint64_t tick_ms, uint64_t* polls) {
+  uint64_t asked = 0, clock = 0;
+  const bool ok = poll_until([&]() { ++asked; return ready_after_polls != 0 && asked >= ready_after_polls; }, timeout_ms, [&]() { clock += tick_ms; return clock; });
+  if (polls) *polls = asked;
+  return ok ? 1 : 0;
 }
 
 }  // extern "C"
 
 namespace {
 
+// Waits for everything enqueued on the backend's stream, but only so long: a peer that never posts its half of an exchange
+// leaves the NCCL kernel waiting on the device for ever, and a plain stream synchronisation would hang the host with it.
+// On expiry the communicator is aborted (ncclCommAbort ends its kernels), the group is marked dead and FJ_TIMEOUT comes back.
+int32_t ep_wait_stream(fj_ep* ep) {
+  cudaStream_t stream = ep->be->stream;
+  if (ep->aborted) return FJ_TIMEOUT;
+  if (!ep->wait_event && cudaEventCreateWithFlags(&ep->wait_event, cudaEventDisableTiming) != cudaSuccess) { cudaGetLastError(); return FJ_DEVICE_EXECUTION_FAILED; }
+  if (cudaEventRecord(ep->wait_event, stream) != cudaSuccess) { cudaGetLastError(); return FJ_DEVICE_EXECUTION_FAILED; }
+  cudaError_t last = cudaSuccess;
+  const bool finished = poll_until([&]() { last = cudaEventQuery(ep->wait_event); return last != cudaErrorNotReady; }, ep->wait_timeout_ms, steady_ms);
+  if (finished) { if (last != cudaSuccess) { cudaGetLastError(); return FJ_DEVICE_EXECUTION_FAILED; } return FJ_OK; }
+  cudaGetLastError();
+  ep->aborted = true;
+  if (g_nccl.CommAbort && ep->comm) { g_nccl.CommAbort(ep->comm); ep->comm = nullptr; }
+  return FJ_TIMEOUT;
+}
+
 // Every rank sends bytes_per_peer to each peer and receives as much from each, on the backend's
 // stream; the block for the rank itself is a device copy. Caller holds the backend mutex.
 int32_t ep_all_to_all(fj_ep* ep, const void* send, void* recv, size_t bytes_per_peer) {
+  if (ep->aborted || !ep->comm) return FJ_TIMEOUT;
   cudaStream_t stream = ep->be->stream;
   if (g_nccl.GroupStart() != 0) return FJ_DEVICE_EXECUTION_FAILED;
   int failed = 0;
@@ -140,6 +201,7 @@ int32_t ep_all_to_all(fj_ep* ep, const void* send, void* recv, size_t bytes_per_
 // its recv_counts[p] rows land at recv + recv_rows_at[p] rows. Counts are host values.
 int32_t ep_all_to_all_rows(fj_ep* ep, const void* send, const unsigned* send_rows_at, const unsigned* send_counts, void* recv, const unsigned* recv_rows_at,
                            const unsigned* recv_counts, size_t row_bytes, const void* send2 = nullptr, void* recv2 = nullptr, size_t row_bytes2 = 0) {
+  if (ep->aborted || !ep->comm) return FJ_TIMEOUT;
   cudaStream_t stream = ep->be->stream;
   if (g_nccl.GroupStart() != 0) return FJ_DEVICE_EXECUTION_FAILED;
   int failed = 0;
@@ -680,7 +742,8 @@ extern "C" int32_t fj_moe_step(fj_moe_model* m, const uint32_t* token_ids, uint3
         status = ep_all_to_all(m->ep, m->ep_counts, m->ep_counts + W, 4);
         if (status != FJ_OK) break;
         cudaMemcpyAsync(m->ep_counts_host, m->ep_counts, 2 * W * 4, cudaMemcpyDeviceToHost, be->stream);
-        if (cudaStreamSynchronize(be->stream) != cudaSuccess) { status = FJ_DEVICE_EXECUTION_FAILED; break; }
+        status = ep_wait_stream(m->ep);  // bounded: a rank that never joins must not hang the others' hosts
+        if (status != FJ_OK) break;
         send_counts = m->ep_counts_host;
         recv_counts = m->ep_counts_host + W;
         for (unsigned p = 0; p < W; ++p) { slab_at[p] = p * cap; packed_at[p] = received; received += recv_counts[p]; }
@@ -732,6 +795,7 @@ extern "C" int32_t fj_moe_step(fj_moe_model* m, const uint32_t* token_ids, uint3
   if (cudaGetLastError() != cudaSuccess) return FJ_DEVICE_EXECUTION_FAILED;
   if (out_tokens && rows != 0) {
     cudaMemcpyAsync(out_tokens, m->tokens_out, static_cast<size_t>(lanes) * 4, cudaMemcpyDeviceToHost, be->stream);
+    if (m->ep) return ep_wait_stream(m->ep);  // the step's exchanges are still in flight: wait for them with the group's deadline
     return cuda_status(cudaStreamSynchronize(be->stream));
   }
   return FJ_OK;

@@ -221,6 +221,82 @@ __global__ void kvpool_cow_tail_kernel(KvPoolDevice pool, const unsigned* __rest
   result[1] = 1; result[2] = static_cast<int>(old); result[3] = static_cast<int>(fresh); result[4] = static_cast<int>(length % pool.page_tokens);
 }
 
+// Drops one reference of `page` and returns it to the free stack when that was the last one; false when the page holds
+// no reference to drop (PagePool::release answers CorruptState there, crates/forja-core/src/paged_pool.rs:308-327).
+__device__ inline bool release_page(const KvPoolDevice& pool, unsigned page) {
+  if (page >= pool.physical_pages || pool.refcounts[page] == 0) return false;
+  if (--pool.refcounts[page] == 0) pool.free_stack[(*pool.free_count)++] = page;
+  return true;
+}
+
+// Sequence boundaries on the device pool (PagedSequence::rewind_private / checkpoint / rollback and the checkpoint's Drop,
+// crates/forja-core/src/paged_pool.rs:864-883, 1061-1123, 1167-1175). One thread; args[0] selects the operation:
+//   0 rewind check  {0, lane, current_len, new_len}                       -> {status}
+//   1 checkpoint    {1, lane, logical_len}                                -> {status, has_tail, index, page, immutable, retained}
+//   2 rollback      {2, lane, has_tail, index, page, immutable, retained} -> {status}
+//   3 drop          {3, page, retained}                                   -> {status}
+// Status: 0 ok, 7 invalid input, 30 shared tail, 31 invalid checkpoint, 32 corrupt state, 3 reference count would overflow.
+// Rollback follows the reference as written: when the tail page is unchanged and the checkpoint had retained it, the
+// reference taken at the checkpoint is released by rollback and once more when the consumed checkpoint is dropped.
+__global__ void kvpool_boundary_kernel(KvPoolDevice pool, const unsigned* __restrict__ args, int* result) {
+  if (threadIdx.x != 0) return;
+  for (int i = 0; i < 6; ++i) result[i] = 0;
+  const unsigned op = args[0];
+  if (op == 3) {
+    if (args[2] && !release_page(pool, args[1])) result[0] = 32;
+    return;
+  }
+  const unsigned lane = args[1];
+  if (lane >= pool.lanes) { result[0] = 7; return; }
+  const unsigned bound = pool.lane_pages[lane];
+  if (op == 0) {
+    const unsigned current = args[2], target = args[3];
+    if (target >= current) { result[0] = 31; return; }
+    const unsigned first = target / pool.page_tokens, last = (current + pool.page_tokens - 1) / pool.page_tokens;
+    if (last > bound) { result[0] = 32; return; }
+    for (unsigned j = first; j < last; ++j) {
+      const size_t e = static_cast<size_t>(lane) * pool.table_pages + j;
+      if (pool.immutable[e] != 0 || pool.refcounts[pool.tables[2 * e]] != 1) { result[0] = 30; return; }
+    }
+    return;
+  }
+  if (op == 1) {
+    const unsigned length = args[2];
+    if (length == 0) return;
+    const unsigned tail = (length - 1) / pool.page_tokens;
+    if (tail >= bound) { result[0] = 32; return; }
+    const size_t e = static_cast<size_t>(lane) * pool.table_pages + tail;
+    const unsigned page = pool.tables[2 * e], immutable = pool.immutable[e] != 0 ? 1u : 0u;
+    const unsigned retained = (immutable || pool.refcounts[page] > 1) ? 1u : 0u;
+    if (retained) {
+      if (pool.refcounts[page] == 0xFFFFFFFFu) { result[0] = 3; return; }
+      pool.refcounts[page] += 1;
+    }
+    result[1] = 1; result[2] = static_cast<int>(tail); result[3] = static_cast<int>(page); result[4] = static_cast<int>(immutable); result[5] = static_cast<int>(retained);
+    return;
+  }
+  if (op == 2) {
+    if (args[2] == 0) return;  // checkpoint of an empty sequence: only the length goes back
+    const unsigned index = args[3], page = args[4], immutable = args[5];
+    unsigned retained = args[6];
+    if (index >= bound) { if (retained) release_page(pool, page); result[0] = 32; return; }
+    const size_t e = static_cast<size_t>(lane) * pool.table_pages + index;
+    const unsigned current = pool.tables[2 * e];
+    if (current == page) {
+      if (retained && !release_page(pool, page)) { result[0] = 32; return; }
+    } else {
+      if (!release_page(pool, current)) { if (retained) release_page(pool, page); result[0] = 32; return; }
+      pool.tables[2 * e] = page;
+      pool.tables[2 * e + 1] = pool.generations[page];
+      retained = 0;
+    }
+    pool.immutable[e] = immutable;
+    if (retained && !release_page(pool, page)) result[0] = 32;  // the consumed checkpoint is dropped
+    return;
+  }
+  result[0] = 7;
+}
+
 __global__ void pack_step_kernel(KvPoolDevice pool, const unsigned* __restrict__ starts, const unsigned* __restrict__ tokens,
                                  unsigned lanes, PackOutputs out, unsigned rows_cap) {
   __shared__ unsigned warp_sums[kPackThreads / 32];
@@ -345,6 +421,10 @@ void launch_kvpool_fork(Ctx& ctx, const KvPoolDevice& pool, const unsigned* args
 }
 void launch_kvpool_cow_tail(Ctx& ctx, const KvPoolDevice& pool, const unsigned* args, int* result) {
   kvpool_cow_tail_kernel<<<1, 32, 0, ctx.stream>>>(pool, args, result);
+  ctx.launches++;
+}
+void launch_kvpool_boundary(Ctx& ctx, const KvPoolDevice& pool, const unsigned* args, int* result) {
+  kvpool_boundary_kernel<<<1, 32, 0, ctx.stream>>>(pool, args, result);
   ctx.launches++;
 }
 void launch_pack_step(Ctx& ctx, const KvPoolDevice& pool, const unsigned* starts, const unsigned* tokens, unsigned lanes,

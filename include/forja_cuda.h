@@ -46,7 +46,11 @@ typedef enum fj_status {
   FJ_WEIGHTS_HEADER_TOO_LARGE = 26,
   FJ_WEIGHTS_UNSUPPORTED_DTYPE = 27,
   FJ_WEIGHTS_INVALID_RANGE = 28,
-  FJ_WEIGHTS_OVERLAPPING_RANGES = 29
+  FJ_WEIGHTS_OVERLAPPING_RANGES = 29,
+  /* PagePoolError, crates/forja-core/src/paged_pool.rs:30-70 (returned by the fj_kvpool_* boundary calls only) */
+  FJ_POOL_SHARED_TAIL = 30,
+  FJ_POOL_INVALID_CHECKPOINT = 31,
+  FJ_POOL_CORRUPT_STATE = 32
 } fj_status;
 
 /* dtype, wit/compute.wit:4-10 */
@@ -314,6 +318,25 @@ int32_t fj_kvpool_read_refcounts(fj_kvpool* pool, uint32_t* refcounts); /* [phys
  * (fj_dense_copy_page). Both calls are synchronous control-path calls. */
 int32_t fj_kvpool_fork(fj_kvpool* pool, uint32_t src_lane, uint64_t src_logical_len, uint32_t dst_lane, uint64_t prefix_tokens, uint64_t reserved_tokens);
 int32_t fj_kvpool_cow_tail(fj_kvpool* pool, uint32_t lane, uint64_t logical_len, uint32_t* out4);
+/* Sequence boundaries on the device pool (PagedSequence::rewind_private / checkpoint / rollback and SequenceCheckpoint,
+ * crates/forja-core/src/paged_pool.rs:864-883, 1061-1175). The logical length of a lane lives with the caller, as
+ * everywhere in this interface.
+ * rewind_private: may the lane go back from current_len to new_len? FJ_POOL_INVALID_CHECKPOINT unless new_len < current_len;
+ *   FJ_POOL_SHARED_TAIL when a page between the two boundaries is immutable for the lane or referenced by another owner.
+ * checkpoint: records the lane's length and tail page; a tail that is shared is retained (reference count + 1) so that a
+ *   later copy-on-write cannot free it.
+ * rollback: consumes a checkpoint of this lane: the recorded tail page goes back into the table (a private copy made since
+ *   is released), the immutable mark is restored and *logical_len receives the recorded length. A checkpoint of another
+ *   pool or lane, or one whose lane was released since, is refused with FJ_POOL_INVALID_CHECKPOINT and dropped.
+ * checkpoint_drop: gives up a checkpoint that was not rolled back (releases the retained tail). */
+typedef struct fj_kv_checkpoint {
+  uint64_t pool, lane_epoch, logical_len;
+  uint32_t lane, active, has_tail, index, page, immutable, retained, reserved;
+} fj_kv_checkpoint;
+int32_t fj_kvpool_rewind_private(fj_kvpool* pool, uint32_t lane, uint64_t current_len, uint64_t new_len);
+int32_t fj_kvpool_checkpoint(fj_kvpool* pool, uint32_t lane, uint64_t logical_len, fj_kv_checkpoint* out);
+int32_t fj_kvpool_rollback(fj_kvpool* pool, uint32_t lane, fj_kv_checkpoint* checkpoint, uint64_t* logical_len);
+int32_t fj_kvpool_checkpoint_drop(fj_kvpool* pool, fj_kv_checkpoint* checkpoint);
 uint64_t fj_kvpool_tables_buffer(fj_kvpool* pool);      /* buffer id: [lanes, table_pages, 2] u32 */
 uint64_t fj_kvpool_generations_buffer(fj_kvpool* pool); /* buffer id: [physical_pages] u32 */
 
@@ -491,6 +514,14 @@ void fj_ep_destroy(fj_ep* ep);
 /* Every rank sends bytes_per_peer bytes of `send` to each rank and receives as many from each into
  * `recv` (buffer ids; world * bytes_per_peer bytes each), ordered on the backend's stream. */
 int32_t fj_ep_all_to_all(fj_ep* ep, uint64_t send, uint64_t recv, uint64_t bytes_per_peer);
+/* Every host wait on an exchange of this group (the per-layer row counts of large steps, the tokens of a step) polls with a
+ * deadline, 60 s unless set here (0 = none). When it runs out - a peer never posted its half - the communicator is aborted
+ * (ncclCommAbort), the call and every later exchange of the group answer FJ_TIMEOUT, and the backend stays usable. */
+int32_t fj_ep_set_timeout(fj_ep* ep, uint64_t timeout_ms);
+/* Host-only check of that bounded wait against a simulated clock (needs no device): a condition that turns true at its
+ * ready_after_polls-th poll (0 = never) is waited for with a clock that advances tick_ms per reading; returns 1 when the
+ * condition was seen, 0 when the wait gave up at timeout_ms; *polls = how often the condition was asked. */
+int32_t fj_ep_poll_selftest(uint64_t timeout_ms, uint64_t ready_after_polls, uint64_t tick_ms, uint64_t* polls);
 
 /* Sparse-MoE decoder (Qwen3-Coder-30B-A3B shape family; reference op order:
  * engines/qwen3-coder/src/lib.rs:886-947 forward_batch, :505-603 SparseMoe::route / forward_decode,

@@ -14,7 +14,7 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
 def small_args(**over):
-    base = dict(gpus=1, steps=20, warmup=5, impl="reference", lanes=128, seed=0, pool_pages=36000, ctx_max=8192, layers=2, no_cpu_baseline=False, no_graph_replay=False)
+    base = dict(gpus=1, steps=20, warmup=5, impl="reference", lanes=128, seed=0, pool_pages=36000, ctx_max=8192, layers=2, no_cpu_baseline=False, no_graph_replay=False, no_moe=True, moe_lanes=256, moe_steps=8, moe_layers=0, repeats=0)
     base.update(over)
     return argparse.Namespace(**base)
 

@@ -438,3 +438,154 @@ def test_replayed_decode_steps_equal_directly_launched_ones():
         assert np.array_equal(a, b)
     for a, b in zip(direct[2], replayed[2]):
         assert np.array_equal(a, b)
+
+
+def test_sequence_boundaries_on_the_device_pool_are_bit_exact_against_the_host_pool():
+    """rewind_private / checkpoint / rollback / checkpoint drop (crates/forja-core/src/paged_pool.rs:864-883, 1061-1175)
+    mixed into reserve / fork / copy-on-write / release traffic: statuses, tables, generations, reference counts and the
+    free-stack order equal the host pool after every operation."""
+    rng = np.random.default_rng(11)
+    be = backend()
+    page, physical, lanes, table_pages = 16, 72, 8, 10
+    dev = fb.KvPool(be, page, physical, lanes, table_pages)
+    ref = fjo.Pool(page, 64, physical, 1 << 40, fixed=True)
+    seqs, lengths, marks = {}, {}, {}   # marks[lane] = (device checkpoint, oracle checkpoint, copied since?, retained)
+    counts = {"checkpoint": 0, "rollback": 0, "rollback_after_cow": 0, "drop": 0, "rewind_ok": 0, "rewind_shared": 0, "stale": 0}
+    stale = []
+
+    def check():
+        assert dev.free_list().tolist() == ref.free_list().tolist()
+        assert dev.generations().tolist() == ref.generations().tolist()
+        refcounts = dev.refcounts()
+        for lane, seq in seqs.items():
+            want = seq.table()
+            assert np.array_equal(dev.table(lane)[:len(want)], want), f"lane {lane}"
+            assert refcounts[want[:, 0]].tolist() == seq.refcounts().tolist(), f"lane {lane}"
+            assert seq.logical_len == lengths[lane]
+
+    def cow(lane):
+        status, copied, src_page, dst_page, rows = dev.cow_tail(lane, lengths[lane])
+        try:
+            want = seqs[lane].cow_tail()
+            assert status == fb.backend.OK and ((want is None and not copied) or want == (src_page, dst_page, rows))
+            if lane in marks and copied:
+                marks[lane][2] = True
+            return True
+        except fjo.OracleError as e:
+            assert e.status == fjo.QUOTA_EXCEEDED and status == fb.backend.QUOTA_EXCEEDED
+            return False
+
+    for step in range(500):
+        lane = int(rng.integers(0, lanes))
+        action = rng.random()
+        if lane not in seqs:
+            donors = [l for l in seqs if lengths[l] > 0]
+            if donors and action < 0.5:
+                src = donors[int(rng.integers(0, len(donors)))]
+                prefix = int(rng.integers(1, lengths[src] + 1))
+                reserved = min(prefix + int(rng.integers(0, 50)), table_pages * page)
+                status = dev.fork(src, lengths[src], lane, prefix, reserved)
+                try:
+                    seqs[lane] = seqs[src].fork_reserved(prefix, reserved)
+                    lengths[lane] = prefix
+                    assert status == fb.backend.OK
+                except fjo.OracleError as e:
+                    assert e.status == fjo.QUOTA_EXCEEDED and status == fb.backend.QUOTA_EXCEEDED
+            else:
+                tokens = int(rng.integers(1, table_pages * page))
+                status = dev.reserve([lane], [tokens])[0]
+                try:
+                    seqs[lane] = ref.reserve(tokens)
+                    assert status == fb.backend.OK
+                    lengths[lane] = int(rng.integers(0, tokens + 1))
+                    assert seqs[lane].commit_write(lengths[lane]) == 0
+                except fjo.OracleError as e:
+                    assert e.status == fjo.QUOTA_EXCEEDED and status == fb.backend.QUOTA_EXCEEDED
+        elif action < 0.12:
+            if lane in marks:   # its checkpoint outlives the sequence: rolling it back later must be refused
+                stale.append(marks.pop(lane))
+            dev.release([lane])
+            seqs.pop(lane).drop()
+            lengths.pop(lane)
+        elif action < 0.35 and lane not in marks:
+            dev_cp = dev.checkpoint(lane, lengths[lane])
+            ora_cp = seqs[lane].checkpoint()
+            marks[lane] = [dev_cp, ora_cp, False, bool(dev_cp.retained)]
+            assert dev_cp.logical_len == lengths[lane]
+            counts["checkpoint"] += 1
+        elif action < 0.55 and lane in marks:
+            dev_cp, ora_cp, copied, retained = marks[lane]
+            if retained and not copied:
+                # the reference releases a retained, unchanged tail twice on rollback; the traffic keeps to the engine's own
+                # order (checkpoint, copy-on-write, write, rollback), the directed test below covers the other one
+                if not cow(lane):
+                    check()
+                    continue
+                copied = marks[lane][2]
+            if retained and not copied:
+                dev.drop_checkpoint(dev_cp)
+                fjo.lib().fjo_checkpoint_drop(ora_cp)
+                counts["drop"] += 1
+            else:
+                status, restored = dev.rollback(lane, dev_cp)
+                assert seqs[lane].rollback(ora_cp) == 0 and status == fb.backend.OK
+                lengths[lane] = restored
+                counts["rollback"] += 1
+                counts["rollback_after_cow"] += int(copied)
+            marks.pop(lane)
+        elif action < 0.7 and lengths[lane] > 0:
+            target = int(rng.integers(0, lengths[lane] + 2))
+            status = dev.rewind_private(lane, lengths[lane], target)
+            want = seqs[lane].rewind_private(target)
+            assert (status, want) in ((fb.backend.OK, 0), (fb.backend.POOL_SHARED_TAIL, fjo.SHARED_TAIL), (fb.backend.POOL_INVALID_CHECKPOINT, fjo.INVALID_CHECKPOINT)), (status, want)
+            if status == fb.backend.OK:
+                lengths[lane] = target
+                counts["rewind_ok"] += 1
+            counts["rewind_shared"] += int(status == fb.backend.POOL_SHARED_TAIL)
+        elif stale and action < 0.75:
+            dev_cp, ora_cp, _, _ = stale.pop()
+            status, _ = dev.rollback(lane, dev_cp)
+            assert status == fb.backend.POOL_INVALID_CHECKPOINT and seqs[lane].rollback(ora_cp) == fjo.INVALID_CHECKPOINT
+            counts["stale"] += 1
+        else:
+            if cow(lane):
+                room = seqs[lane].reserved_tokens - lengths[lane]
+                grow = int(rng.integers(0, min(room, 20) + 1))
+                if grow and seqs[lane].commit_write(grow) == 0:
+                    lengths[lane] += grow
+        check()
+    assert counts["checkpoint"] > 30 and counts["rollback"] > 10 and counts["rollback_after_cow"] > 3 and counts["rewind_ok"] > 10 and counts["rewind_shared"] > 3, counts
+    assert counts["stale"] > 0, counts
+    for dev_cp, ora_cp, _, _ in list(marks.values()) + stale:
+        dev.drop_checkpoint(dev_cp)
+        fjo.lib().fjo_checkpoint_drop(ora_cp)
+    check()
+    for seq in seqs.values():
+        seq.drop()
+    dev.close()
+
+
+def test_rollback_of_an_unchanged_shared_tail_follows_the_reference_as_written():
+    """PagedSequence::rollback releases a retained tail that is still in place once itself and once more when the consumed
+    checkpoint is dropped (paged_pool.rs:1109-1113 with :1167-1175). The device pool does the same, so its reference counts
+    stay equal to the host pool's: three owners of the tail page, checkpoint (+1 = 4), rollback (-2 = 2)."""
+    be = backend()
+    page = 16
+    dev = fb.KvPool(be, page, 16, 3, 4)
+    ref = fjo.Pool(page, 64, 16, 1 << 40, fixed=True)
+    assert dev.reserve([0], [40]) == [0]
+    a = ref.reserve(40)
+    assert a.commit_write(20) == 0
+    assert dev.fork(0, 20, 1, 20, 40) == 0 and dev.fork(0, 20, 2, 20, 40) == 0
+    b, c = a.fork_reserved(20, 40), a.fork_reserved(20, 40)
+    tail = int(a.table()[1, 0])
+    assert dev.refcounts()[tail] == 3 == a.refcounts()[1]
+    dev_cp, ora_cp = dev.checkpoint(1, 20), b.checkpoint()
+    assert dev_cp.retained == 1 and dev.refcounts()[tail] == 4 == a.refcounts()[1]
+    status, restored = dev.rollback(1, dev_cp)
+    assert status == 0 and restored == 20 and b.rollback(ora_cp) == 0
+    assert dev.refcounts()[tail] == 2 == a.refcounts()[1]
+    assert dev.free_list().tolist() == ref.free_list().tolist()
+    for seq in (a, b, c):
+        seq.drop()
+    dev.close()

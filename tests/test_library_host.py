@@ -130,3 +130,19 @@ def test_tensor_byte_span_uses_checked_arithmetic():
     assert _span(0, (1 << 31, 1 << 31, 8), (1 << 33, 4, 1 << 60))[0] == INVALID
     st, lo, hi = _span(0, (1,), (1,), 9)
     assert st == INVALID                                              # dtype out of range
+
+
+def test_bounded_exchange_wait_gives_up_at_its_deadline():
+    """The host waits of the expert-parallel exchange poll with a deadline (a peer that never posts must not hang the other
+    ranks' hosts). Exercised here against a simulated clock: no device, no NCCL."""
+    lib = _lib.load()
+    polls = C.c_uint64(0)
+    # the condition turns true at the 5th poll, well inside the deadline
+    assert lib.fj_ep_poll_selftest(1000, 5, 1, C.byref(polls)) == 1 and polls.value == 5
+    # a condition that never turns true: the wait ends once the clock has passed the deadline
+    assert lib.fj_ep_poll_selftest(100, 0, 7, C.byref(polls)) == 0
+    assert 100 // 7 <= polls.value <= 100 // 7 + 2
+    # true only after the deadline: not seen
+    assert lib.fj_ep_poll_selftest(10, 50, 1, C.byref(polls)) == 0 and polls.value < 50
+    # no deadline: waits as long as it takes
+    assert lib.fj_ep_poll_selftest(0, 300, 1000, C.byref(polls)) == 1 and polls.value == 300
