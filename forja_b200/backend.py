@@ -178,9 +178,9 @@ class Op:
     @staticmethod
     def QuantEmbed(bits: int, group_size: int): return Op(OP_QUANT_EMBED, u0=bits, u1=group_size)
     @staticmethod
-    def Matmul(): return Op(OP_MATMUL)
+    def Matmul(epilogue: int = 0): return Op(OP_MATMUL, program=epilogue)  # with an epilogue: inputs [a, b, extra]
     @staticmethod
-    def QuantMatmul(bits: int, group_size: int): return Op(OP_QUANT_MATMUL, u0=bits, u1=group_size)
+    def QuantMatmul(bits: int, group_size: int, epilogue: int = 0): return Op(OP_QUANT_MATMUL, u0=bits, u1=group_size, program=epilogue)
     @staticmethod
     def GatherQuantMatmul(bits: int, group_size: int, epilogue: int = 0): return Op(OP_GATHER_QUANT_MATMUL, u0=bits, u1=group_size, program=epilogue)
     @staticmethod

@@ -243,6 +243,9 @@ bool recognise(uint32_t kind, const uint32_t* insts, uint32_t n, const uint32_t*
     uint32_t inner, sig, x;
     if (p.binary_with(o0, B_MUL, [&](uint32_t q) { return p.is_input(q, 1); }, &inner) &&
         p.binary_with(inner, B_MUL, [&](uint32_t q) { return p.is_input(q, 0); }, &sig) && p.unary(sig, U_SIGMOID, &x) && p.is_input(x, 0)) { rec->kernel = 2; return true; }
+    // gated up, the matmul epilogue of engines/smollm2/src/optimized.rs:249-252: (gate * sigmoid(gate)) * up with up = Input0 (the accumulator), gate = Input1
+    if (p.binary_with(o0, B_MUL, [&](uint32_t q) { return p.is_input(q, 0); }, &inner) &&
+        p.binary_with(inner, B_MUL, [&](uint32_t q) { return p.is_input(q, 1); }, &sig) && p.unary(sig, U_SIGMOID, &x) && p.is_input(x, 1)) { rec->kernel = 7; return true; }
     return false;
   }
   if (kind == 1 && n_out == 1) {
@@ -558,9 +561,48 @@ int32_t exec_quant_embed(Exec& x, const fj_dispatch& d, fj::ErrorRecord* err) {
   return FJ_OK;
 }
 
+// Scalar epilogue of a matrix product (apply_epilogue_accumulators, crates/forja-cpu/src/lib.rs:443-493): the Map program sees the
+// f32 accumulator as input 0 and the extra operands after it; its output is rounded once to the output dtype. Recognised
+// forms: accumulator + extra (bias or residual add), silu(extra) * accumulator (gated up), silu(accumulator) * extra.
+// Runs the product into an f32 temporary via `product(temp tensor)`, then one element-wise pass.
+template <typename Product>
+int32_t with_epilogue(Exec& x, const fj_dispatch& d, uint32_t primitive_inputs, Product product) {
+  if (d.program == 0 || d.program > x.be->programs.size()) return FJ_INVALID_INPUT;
+  const uint32_t kernel = x.be->programs[d.program - 1].kernel;
+  if (kernel != 1 && kernel != 2 && kernel != 7) return FJ_UNSUPPORTED_OPERATION;
+  if (d.n_inputs != primitive_inputs + 1 || d.n_outputs != 1) return FJ_INVALID_INPUT;
+  const fj_tensor &extra = d.inputs[primitive_inputs], &out = d.outputs[0];
+  if (!same_shape(extra, out) || !is_float(extra.dtype) || !is_float(out.dtype) || out.rank != 2) return FJ_INVALID_INPUT;
+  const uint64_t elements = element_count(out);
+  float* acc = static_cast<float*>(x.temp(std::max<uint64_t>(elements, 1) * sizeof(float)));
+  if (!acc) return FJ_ALLOCATION_FAILED;
+  const int32_t status = product(acc);
+  if (status != FJ_OK || elements == 0) return status;
+  View ve, vo;
+  if (!make_view(x.be, extra, false, &ve) || !make_view(x.be, out, true, &vo)) return FJ_INVALID_INPUT;
+  View va = dense_view(acc, FJ_F32, out.shape[0], out.shape[1], out.shape[1]);
+  if (kernel == 1) fj::launch_add(x.be->ctx, va, ve, vo, elements);
+  else if (kernel == 7) fj::launch_silu_mul(x.be->ctx, ve, va, vo, elements);  // gate = extra, up = accumulator
+  else fj::launch_silu_mul(x.be->ctx, va, ve, vo, elements);                    // gate = accumulator, up = extra
+  return FJ_OK;
+}
+
+int32_t exec_matmul_plain(Exec& x, const fj_dispatch& d, float* acc_out);
+
 int32_t exec_matmul(Exec& x, const fj_dispatch& d) {
-  if (d.n_inputs != 2 || d.n_outputs != 1 || d.program != 0) return d.program ? FJ_UNSUPPORTED_OPERATION : FJ_INVALID_INPUT;
-  const fj_tensor &a = d.inputs[0], &b = d.inputs[1], &c = d.outputs[0];
+  if (d.program != 0) {
+    if (d.n_inputs < 2 || d.inputs[0].rank != 2) return FJ_UNSUPPORTED_OPERATION;  // epilogues are used on rank-2 products
+    return with_epilogue(x, d, 2, [&](float* acc) { return exec_matmul_plain(x, d, acc); });
+  }
+  return exec_matmul_plain(x, d, nullptr);
+}
+
+// acc_out != nullptr: the product goes to that contiguous f32 [m, n] area instead of the dispatch's output.
+int32_t exec_matmul_plain(Exec& x, const fj_dispatch& d, float* acc_out) {
+  if (d.n_inputs < 2 || d.n_outputs != 1 || (acc_out == nullptr && d.n_inputs != 2)) return FJ_INVALID_INPUT;
+  const fj_tensor &a = d.inputs[0], &b = d.inputs[1];
+  fj_tensor c = d.outputs[0];
+  if (acc_out != nullptr) { c.dtype = FJ_F32; c.strides[0] = c.shape[1]; c.strides[1] = 1; }
   if (a.rank != b.rank || a.rank != c.rank || (a.rank != 2 && a.rank != 3)) return FJ_INVALID_INPUT;
   const uint32_t r = a.rank;
   const unsigned m = a.shape[r - 2], k = a.shape[r - 1], n = b.shape[r - 1];
@@ -572,7 +614,7 @@ int32_t exec_matmul(Exec& x, const fj_dispatch& d) {
   if (nt) {
     const void* ap = tensor_ptr(x.be, a, false);
     const void* bp = tensor_ptr(x.be, b, false);
-    void* cp = tensor_ptr(x.be, c, true);
+    void* cp = acc_out != nullptr ? static_cast<void*>(acc_out) : tensor_ptr(x.be, c, true);
     if (!ap || !bp || !cp) return FJ_INVALID_INPUT;
     size_t need = fj::gemm_scratch_bytes(m, n, k);
     void* scratch = nullptr; size_t scratch_bytes = 0;
@@ -581,7 +623,9 @@ int32_t exec_matmul(Exec& x, const fj_dispatch& d) {
     return FJ_OK;
   }
   View va, vb, vc;
-  if (!make_view(x.be, a, false, &va) || !make_view(x.be, b, false, &vb) || !make_view(x.be, c, true, &vc)) return FJ_INVALID_INPUT;
+  if (!make_view(x.be, a, false, &va) || !make_view(x.be, b, false, &vb)) return FJ_INVALID_INPUT;
+  if (acc_out != nullptr) vc = dense_view(acc_out, FJ_F32, m, n, n);
+  else if (!make_view(x.be, c, true, &vc)) return FJ_INVALID_INPUT;
   fj::launch_matmul_generic(x.be->ctx, va, vb, vc, batch, m, n, k);
   return FJ_OK;
 }
@@ -613,15 +657,23 @@ int32_t exec_gather_matmul(Exec& x, const fj_dispatch& d, fj::ErrorRecord* err) 
   return fj::launch_gather_matmul(x.be->ctx, va, vw, vi, vo, err) ? FJ_OK : FJ_UNSUPPORTED_OPERATION;
 }
 
+int32_t exec_quant_matmul_plain(Exec& x, const fj_dispatch& d, float* acc_out);
+
 int32_t exec_quant_matmul(Exec& x, const fj_dispatch& d) {
-  if (d.n_inputs != 4 || d.n_outputs != 1 || !quant_params_ok(d.u0, d.u1)) return FJ_INVALID_INPUT;
-  if (d.program != 0) return FJ_UNSUPPORTED_OPERATION;
+  if (d.program != 0) return with_epilogue(x, d, 4, [&](float* acc) { return exec_quant_matmul_plain(x, d, acc); });
+  return exec_quant_matmul_plain(x, d, nullptr);
+}
+
+// acc_out != nullptr: the product goes to that contiguous f32 [m, n] area instead of the dispatch's output.
+int32_t exec_quant_matmul_plain(Exec& x, const fj_dispatch& d, float* acc_out) {
+  if (d.n_inputs < 4 || d.n_outputs != 1 || (acc_out == nullptr && d.n_inputs != 4) || !quant_params_ok(d.u0, d.u1)) return FJ_INVALID_INPUT;
   const fj_tensor &xt = d.inputs[0], &pk = d.inputs[1];
   if (xt.rank != 2 || pk.rank != 2 || pk.dtype != FJ_U32 || d.inputs[2].dtype != d.inputs[3].dtype || !is_float(xt.dtype)) return FJ_INVALID_INPUT;
   const unsigned m = xt.shape[0], k = xt.shape[1], n = pk.shape[0];
   if (pk.shape[1] != k * d.u0 / 32 || k % d.u1 != 0 || element_count(d.inputs[2]) != static_cast<uint64_t>(n) * (k / d.u1) || element_count(d.outputs[0]) != static_cast<uint64_t>(m) * n) return FJ_INVALID_INPUT;
   const void *xp = x.input(xt), *pp = x.input(pk), *sp = x.input(d.inputs[2]), *bp = x.input(d.inputs[3]);
-  void* out = x.output(d.outputs[0]);
+  void* out = acc_out != nullptr ? static_cast<void*>(acc_out) : x.output(d.outputs[0]);
+  const uint32_t out_dtype = acc_out != nullptr ? static_cast<uint32_t>(FJ_F32) : d.outputs[0].dtype;
   if (!xp || !pp || !sp || !bp || !out) return FJ_INVALID_INPUT;
   void* workspace = nullptr;
   size_t workspace_bytes = 0;
@@ -637,7 +689,7 @@ int32_t exec_quant_matmul(Exec& x, const fj_dispatch& d) {
     size_t need = fj::gemm_scratch_bytes(m, slab_cols, k);
     if (need <= (size_t(1) << 30) && ensure_gemm_scratch(x.be, need)) { gemm_scratch = x.be->gemm_scratch; gemm_scratch_bytes = x.be->gemm_scratch_bytes; }
   }
-  fj::launch_quant_matmul(x.be->ctx, xp, xt.dtype, static_cast<const unsigned*>(pp), sp, bp, d.inputs[2].dtype, out, d.outputs[0].dtype, m, k, n, d.u0, d.u1, workspace,
+  fj::launch_quant_matmul(x.be->ctx, xp, xt.dtype, static_cast<const unsigned*>(pp), sp, bp, d.inputs[2].dtype, out, out_dtype, m, k, n, d.u0, d.u1, workspace,
                           workspace_bytes, gemm_scratch, gemm_scratch_bytes);
   return FJ_OK;
 }

@@ -155,14 +155,17 @@ void launch_paged_copy(Ctx& ctx, bool into_pages, void* ordinary, int o_dt, size
 
 // ---- fj_gemm.cu -----------------------------------------------------------------------------
 // C[M,N] = A[M,K] * W[N,K]^T ("NT": both operands K-major), f32 accumulation, output rounded once.
-// lda/ldw/ldc in elements. 16-bit path: mma.sync tiles for M > 16, warp-per-column GEMV below.
+// lda/ldw/ldc in elements. 16-bit path: the TMA-fed tcgen05 kernel for M > 16 (mma.sync split-K tiles when its
+// alignment rules are not met), warp-per-column GEMV at 16 rows or fewer.
 size_t gemm_scratch_bytes(unsigned m, unsigned n, unsigned k);
 void launch_gemm_nt(Ctx& ctx, const void* a, int a_dt, size_t lda, const void* w, int w_dt, size_t ldw, void* c, int c_dt,
                     size_t ldc, unsigned m, unsigned n, unsigned k, void* scratch, size_t scratch_bytes);
-// tcgen05 form (TMEM accumulators, 128 x 128 x 64 tiles, no split-K): bf16/f16, K % 64 == 0, 16-byte aligned rows.
-bool gemm_nt_tcgen05_supported(int a_dt, int w_dt, unsigned m, unsigned n, unsigned k, size_t lda, size_t ldw, const void* a, const void* w);
-void launch_gemm_nt_tcgen05(Ctx& ctx, const void* a, int a_dt, size_t lda, const void* w, size_t ldw, void* c, int c_dt, size_t ldc, unsigned m, unsigned n, unsigned k);
-unsigned gemm_tcgen05_giveups();  // bounded waits that ran out since the library was loaded (0 in a healthy run)
+// TMA-fed, warp-specialised tcgen05 GEMM (fj_gemm_tma.cu): 128 x {32, 64, 128, 256} tiles, one producer thread issuing
+// cp.async.bulk.tensor loads, one thread issuing the MMAs, four epilogue warps. false from the launcher: no tensor map
+// could be made (the caller takes another kernel).
+bool gemm_nt_tma_supported(int a_dt, int w_dt, unsigned m, unsigned n, unsigned k, size_t lda, size_t ldw, const void* a, const void* w);
+bool launch_gemm_nt_tma(Ctx& ctx, const void* a, int a_dt, size_t lda, const void* w, size_t ldw, void* c, int c_dt, size_t ldc, unsigned m, unsigned n, unsigned k);
+unsigned gemm_tma_giveups();  // bounded waits that ran out since the library was loaded (0 in a healthy run)
 unsigned grouped_tcgen05_giveups();  // the same for the expert-bucketed tcgen05 tiles
 // Fully strided fallback (any layout, batch): one thread per output element.
 void launch_matmul_generic(Ctx& ctx, const View& a, const View& b, const View& c, unsigned batch, unsigned m, unsigned n,

@@ -636,6 +636,178 @@ bool run_q4_stream(Ctx& ctx, const Q4MmaArgs& a, int x_dt) {
   return a.m <= 8 ? run_q4_i8_config<false, 1>(ctx, a, sms) : run_q4_i8_config<false, 2>(ctx, a, sms);
 }
 
+// ---- one or two rows: integer dot products from registers ---------------------------------------------------
+// q4, group 64, bf16 activations, k a multiple of 1024 up to 4096. A warp owns whole weight rows (output columns): lane l
+// takes the four packed words l*4 .. l*4+3 of every 1024-k slice (one 16-byte load, 32 weights, half a group), so a warp
+// reads a row as contiguous 512-byte pieces. The lane's activations never leave its registers: converted once per CTA
+// pass to the same block fixed point as the tensor-core form above (per 64-k block a power-of-two step, 13-bit integers
+// split into a signed high and an unsigned low byte), packed in the byte order of the nibble masks (`w & 0x0F0F0F0F`
+// holds k = 0,2,4,6 of a word, `(w >> 4) & 0x0F0F0F0F` k = 1,3,5,7) and multiplied with dp4a: 3 mask/shift and 4 dp4a
+// instructions per packed word and row, no shared memory, no tensor-core tile that is 15/16 zero rows.
+// y = sum over the lane's half groups of (s * S) * (256 * hi + lo) + b * (sum of the lane's 32 activations), then a warp sum.
+// The loads of the two rows after the current one are in flight while it is reduced.
+__device__ inline int dp4a_us(unsigned a, unsigned b, int c) {  // unsigned bytes of a x signed bytes of b
+  int d;
+  asm("dp4a.u32.s32 %0, %1, %2, %3;\n" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+  return d;
+}
+__device__ inline int dp4a_uu(unsigned a, unsigned b, int c) {  // unsigned x unsigned
+  int d;
+  asm("dp4a.u32.u32 %0, %1, %2, %3;\n" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+  return d;
+}
+
+template <int SLICES, int ROWS>
+__global__ void __launch_bounds__(256) q4_dp4a_gemv_kernel(Q4MmaArgs a) {
+  const unsigned lane = threadIdx.x & 31;
+  const unsigned warps_total = gridDim.x * (blockDim.x >> 5), warp_global = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const unsigned groups_per_row = a.k / 64;
+  const uint4* packed = reinterpret_cast<const uint4*>(a.packed);
+  const size_t row_vectors = a.k / 32;  // 16-byte vectors per weight row
+
+  // the first row's weights are requested before the activations are touched (they do not depend on the previous kernel)
+  unsigned n = warp_global;
+  constexpr int SP = (SLICES + 1) / 2;  // a lane keeps the scale and bias of groups lane and lane + 32
+  uint4 q[SLICES], q_next[SLICES], q_after[SLICES];  // the row being reduced and the two rows behind it, already requested
+  unsigned short scale_raw[SP], bias_raw[SP], scale_next[SP], bias_next[SP], scale_after[SP], bias_after[SP];
+#pragma unroll
+  for (int i = 0; i < SP; ++i) scale_raw[i] = bias_raw[i] = scale_next[i] = bias_next[i] = scale_after[i] = bias_after[i] = 0;
+  auto request = [&](unsigned row, uint4 (&dst)[SLICES], unsigned short (&sr)[SP], unsigned short (&br)[SP]) {
+    if (row < a.n) {
+#pragma unroll
+      for (int it = 0; it < SLICES; ++it) dst[it] = __ldcs(packed + static_cast<size_t>(row) * row_vectors + it * 32 + lane);
+#pragma unroll
+      for (int i = 0; i < SP; ++i) {
+        if (lane + 32 * i < groups_per_row) {
+          sr[i] = __ldcs(a.scales + static_cast<size_t>(row) * groups_per_row + lane + 32 * i);
+          br[i] = __ldcs(a.biases + static_cast<size_t>(row) * groups_per_row + lane + 32 * i);
+        }
+      }
+    }
+  };
+  request(n, q, scale_raw, bias_raw);
+  request(n + warps_total, q_next, scale_next, bias_next);
+  pdl_sync();
+
+  // activations of this lane: k = it * 1024 + lane * 32 .. + 31 for every slice
+  unsigned xh[ROWS][SLICES][8], xl[ROWS][SLICES][8];  // [word][even | odd] packed bytes
+  float xsum[ROWS][SLICES], xstep[ROWS][SLICES];
+#pragma unroll
+  for (int r = 0; r < ROWS; ++r) {
+#pragma unroll
+    for (int it = 0; it < SLICES; ++it) {
+      float f[32];
+      float sum = 0.0f, biggest = 0.0f;
+      if (static_cast<unsigned>(r) < a.m) {
+        const uint4* src = reinterpret_cast<const uint4*>(a.x + static_cast<size_t>(r) * a.x_row_stride + it * 1024 + lane * 32);
+#pragma unroll
+        for (int v = 0; v < 4; ++v) {
+          const uint4 raw = src[v];
+          const unsigned words[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            f[v * 8 + 2 * i] = __uint_as_float(words[i] << 16);
+            f[v * 8 + 2 * i + 1] = __uint_as_float(words[i] & 0xFFFF0000u);
+          }
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) f[i] = 0.0f;
+      }
+#pragma unroll
+      for (int i = 0; i < 32; ++i) { sum += f[i]; biggest = fmaxf(biggest, fabsf(f[i])); }
+      biggest = fmaxf(biggest, __shfl_xor_sync(0xffffffffu, biggest, 1));  // the 64-k block spans this lane and its neighbour
+      const unsigned exponent = __float_as_uint(biggest) & 0x7F800000u;
+      const bool usable = exponent >= (12u << 23) && exponent < (255u << 23);
+      const float inv_step = usable ? __uint_as_float((254u << 23) - (exponent - (11u << 23))) : 1.0f;
+      xstep[r][it] = usable ? __uint_as_float(exponent - (11u << 23)) : 0.0f;  // a block without a usable step keeps only its bias term
+      xsum[r][it] = sum;
+#pragma unroll
+      for (int w = 0; w < 4; ++w) {
+        unsigned he = 0, ho = 0, le = 0, lo = 0;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int even = usable ? __float2int_rn(f[w * 8 + 2 * j] * inv_step) : 0, odd = usable ? __float2int_rn(f[w * 8 + 2 * j + 1] * inv_step) : 0;
+          he |= (static_cast<unsigned>(even >> 8) & 0xFFu) << (8 * j);
+          le |= (static_cast<unsigned>(even) & 0xFFu) << (8 * j);
+          ho |= (static_cast<unsigned>(odd >> 8) & 0xFFu) << (8 * j);
+          lo |= (static_cast<unsigned>(odd) & 0xFFu) << (8 * j);
+        }
+        xh[r][it][2 * w] = he; xh[r][it][2 * w + 1] = ho;
+        xl[r][it][2 * w] = le; xl[r][it][2 * w + 1] = lo;
+      }
+    }
+  }
+
+  for (; n < a.n; n += warps_total) {
+    request(n + 2 * warps_total, q_after, scale_after, bias_after);
+    float y[ROWS];
+#pragma unroll
+    for (int r = 0; r < ROWS; ++r) y[r] = 0.0f;
+#pragma unroll
+    for (int it = 0; it < SLICES; ++it) {
+      // scale and bias of this lane's group g = it * 16 + lane / 2 sit in lane g % 32, slot g / 32
+      const unsigned holder = (it * 16 + (lane >> 1)) & 31u;
+      const float s = __uint_as_float(__shfl_sync(0xffffffffu, static_cast<unsigned>(scale_raw[it / 2]), holder) << 16);
+      const float b = __uint_as_float(__shfl_sync(0xffffffffu, static_cast<unsigned>(bias_raw[it / 2]), holder) << 16);
+      const unsigned words[4] = {q[it].x, q[it].y, q[it].z, q[it].w};
+      int hi[ROWS], lo[ROWS];
+#pragma unroll
+      for (int r = 0; r < ROWS; ++r) { hi[r] = 0; lo[r] = 0; }
+#pragma unroll
+      for (int w = 0; w < 4; ++w) {
+        const unsigned even = words[w] & 0x0F0F0F0Fu, odd = (words[w] >> 4) & 0x0F0F0F0Fu;
+#pragma unroll
+        for (int r = 0; r < ROWS; ++r) {
+          hi[r] = dp4a_us(even, xh[r][it][2 * w], hi[r]);
+          hi[r] = dp4a_us(odd, xh[r][it][2 * w + 1], hi[r]);
+          lo[r] = dp4a_uu(even, xl[r][it][2 * w], lo[r]);
+          lo[r] = dp4a_uu(odd, xl[r][it][2 * w + 1], lo[r]);
+        }
+      }
+#pragma unroll
+      for (int r = 0; r < ROWS; ++r) y[r] += (s * xstep[r][it]) * static_cast<float>(hi[r] * 256 + lo[r]) + b * xsum[r][it];
+    }
+#pragma unroll
+    for (int r = 0; r < ROWS; ++r) {
+      const float total = warp_sum(y[r]);
+      if (lane == 0 && static_cast<unsigned>(r) < a.m) store_from_f32(a.out, a.out_dt, static_cast<size_t>(r) * a.out_row_stride + n, total);
+    }
+#pragma unroll
+    for (int it = 0; it < SLICES; ++it) { q[it] = q_next[it]; q_next[it] = q_after[it]; }
+#pragma unroll
+    for (int i = 0; i < SP; ++i) { scale_raw[i] = scale_next[i]; bias_raw[i] = bias_next[i]; scale_next[i] = scale_after[i]; bias_next[i] = bias_after[i]; }
+  }
+}
+
+template <int SLICES, int ROWS>
+void launch_q4_dp4a(Ctx& ctx, const Q4MmaArgs& a) {
+  const unsigned sms = static_cast<unsigned>(ctx.sm_count > 0 ? ctx.sm_count : 148);
+  const unsigned row_warps = (a.n + 7) / 8;  // CTAs if every warp took a single row
+  // CTAs per SM that the register file holds at once (256 threads each), so that the whole grid is resident and the rows stay interleaved
+  constexpr unsigned per_sm = ROWS > 1 ? 2u : (SLICES == 1 ? 4u : (SLICES == 2 ? 3u : (SLICES == 3 ? 2u : 1u)));
+  const unsigned grid = std::min(row_warps, sms * per_sm);
+  launch_pdl(q4_dp4a_gemv_kernel<SLICES, ROWS>, dim3(grid), dim3(256), 0, ctx.stream, a);
+  ctx.launches++;
+}
+
+// A single row of bf16 activations against a large q4 / group-64 matrix whose k is 1024, 2048, 3072 or 4096. Measured
+// against the tensor-core streaming form: 2048 x 151936 (an lm_head) 38.2 us against 41.9 with one row in flight fewer; on
+// matrices of a few MB (5 us either way, launch and one DRAM round trip) and with two rows (54 against 44 us: the dp4a count
+// doubles while the loads stay) it is not faster, so those stay with the tensor-core form.
+constexpr uint64_t kDp4aMinWeights = 32ull << 20;
+bool run_q4_dp4a(Ctx& ctx, const Q4MmaArgs& a, int x_dt) {
+  if (x_dt != BF16 || a.group_size != 64 || a.m != 1 || a.k % 1024 != 0 || a.k > 4096 || static_cast<uint64_t>(a.n) * a.k < kDp4aMinWeights) return false;
+  if (reinterpret_cast<size_t>(a.packed) % 16 != 0 || reinterpret_cast<size_t>(a.x) % 16 != 0 || (a.x_row_stride * 2) % 16 != 0) return false;
+  switch (a.k / 1024) {
+    case 1: launch_q4_dp4a<1, 1>(ctx, a); break;
+    case 2: launch_q4_dp4a<2, 1>(ctx, a); break;
+    case 3: launch_q4_dp4a<3, 1>(ctx, a); break;
+    default: launch_q4_dp4a<4, 1>(ctx, a); break;
+  }
+  return true;
+}
+
 // Dequantises `cols` weight rows (columns of the projection) starting at absolute row `row0` of
 // the scale/bias tables into a dense [cols, k] matrix of dtype out_dt; one thread per packed word.
 __global__ void dequant_rows_kernel(const unsigned* __restrict__ packed, const void* scales, const void* biases, int p_dt, void* out, int out_dt,
@@ -759,6 +931,7 @@ void launch_quant_matmul(Ctx& ctx, const void* x, int x_dt, const unsigned* pack
   if (q4_mma_supported(x_dt, p_dt, m, k, bits, group_size, x, k, packed)) {
     Q4MmaArgs a{static_cast<const unsigned short*>(x), k, packed, static_cast<const unsigned short*>(scales), static_cast<const unsigned short*>(biases),
                 out, out_dt, n, m, k, n, group_size};
+    if (run_q4_dp4a(ctx, a, x_dt)) return;
     if (!run_q4_stream(ctx, a, x_dt)) run_q4_mma(ctx, a, x_dt);
     return;
   }

@@ -187,7 +187,11 @@ int32_t fj_program_prepare(fj_backend* be, uint32_t kind, const uint32_t* insts,
 int32_t fj_program_classify(uint32_t kind, const uint32_t* insts, uint32_t n_insts, const uint32_t* outputs,
                             uint32_t n_outputs, uint32_t* kernel, float consts[4]);
 /* Which fused kernel a prepared program maps to: 1 add, 2 silu_mul, 3 rms_norm, 4 residual_norm,
- * 5 qk_norm_rope, 6 rope_pairs; consts receives the captured constants (eps, theta, head_dim). */
+ * 5 qk_norm_rope, 6 rope_pairs, 7 gated up (input 0 * silu(input 1), the matmul epilogue of
+ * engines/smollm2/src/optimized.rs:249-252); consts receives the captured constants (eps, theta, head_dim).
+ * As the epilogue of FJ_OP_MATMUL / FJ_OP_QUANT_MATMUL (fj_dispatch.program, one extra input of the output's shape after
+ * the primitive inputs; crates/forja-cpu/src/lib.rs:443-493) the Map programs 1, 2 and 7 are taken: the program sees the
+ * f32 accumulator as input 0 and the extra operand as input 1, and its result is rounded once to the output dtype. */
 int32_t fj_program_info(fj_backend* be, uint64_t handle, uint32_t* kernel, float consts[4]);
 
 /* submit (backend.rs:783) / submit_profiled (backend.rs:800). Work is enqueued and the call

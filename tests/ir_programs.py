@@ -65,6 +65,15 @@ def silu_mul():
     return p
 
 
+def gated_up():
+    """The matmul epilogue of engines/smollm2/src/optimized.rs:249-252: gate * sigmoid(gate) * up with up = input 0
+    (the accumulator) and gate = input 1 (the extra operand)."""
+    p = fjo.Program(fjo.MAP)
+    up, gate = p.input(0), p.input(1)
+    p.output(0, p.binary(fjo.B_MUL, p.binary(fjo.B_MUL, gate, p.unary(fjo.U_SIGMOID, gate)), up))
+    return p
+
+
 def add():
     p = fjo.Program(fjo.MAP)
     p.output(0, p.binary(fjo.B_ADD, p.input(0), p.input(1)))

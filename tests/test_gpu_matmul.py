@@ -284,3 +284,44 @@ def test_bucketed_expert_path_with_k_that_the_streamed_form_refuses(rows):
     want = fjo.decode(fjo.gather_quant_matmul(xh, dt, pk, sc, bi, fjo.BF16, ids, 4, 64, dt), dt)
     fjo.set_threads(1)
     assert_close(down(out), want, QUANT_TOL)
+
+
+@pytest.mark.parametrize("dt,m,k,n", [(fb.F32, 7, 576, 1536), (fb.BF16, 33, 256, 192), (fb.BF16, 128, 1024, 3072), (fb.F32, 1, 64, 48)])
+def test_matmul_epilogues_see_the_f32_accumulator(dt, m, k, n):
+    """Op::Matmul with a scalar epilogue (crates/forja-cpu/src/lib.rs:443-493; SmolLM2's fused-epilogues tuning,
+    engines/smollm2/src/optimized.rs:190-204): the Map program gets the unrounded accumulator and the extra operand and
+    its result is rounded once. Oracle: matmul to f32, then the interpreted program."""
+    rng = np.random.default_rng(m + n)
+    be = backend()
+    x, xh = up(rng.standard_normal((m, k)), dt)
+    w, wh = up(rng.standard_normal((n, k)) * 0.05, dt)
+    extra, eh = up(rng.standard_normal((m, n)), dt)
+    fjo.set_threads(fjo.max_threads())
+    acc = fjo.matmul(xh, dt, wh, dt, fjo.F32, right_transposed=True)
+    fjo.set_threads(1)
+    for name, prog in (("gated_up", ir.gated_up()), ("add", ir.add()), ("silu_mul", ir.silu_mul())):
+        out = be.alloc(dt, (m, n))
+        be.run(Op.Matmul(epilogue=prepare(prog)), [x, w.permute([1, 0]), extra], [out])
+        want = fjo.program(prog, (m, n), [acc, eh], [fjo.F32, dt], [dt])[0]
+        if dt == fb.F32:
+            assert_close(down(out), want, 1e-5)
+        else:
+            assert_close(down(out), fjo.decode(want, dt), TOL[dt])
+    # an epilogue the library does not know is refused, not emulated
+    with pytest.raises(fb.BackendError) as e:
+        be.run(Op.Matmul(epilogue=prepare(ir.rms_norm(1e-5))), [x, w.permute([1, 0]), extra], [be.alloc(dt, (m, n))])
+    assert e.value.status in (fb.backend.UNSUPPORTED_OPERATION, fb.backend.INVALID_INPUT)
+
+
+def test_quant_matmul_epilogue_adds_a_residual():
+    rng = np.random.default_rng(12)
+    be = backend()
+    m, k, n = 5, 512, 256
+    pk, sc, bi = quant_weights(rng, n, k, 4, 64, fb.BF16)
+    x, xh = up(rng.standard_normal((m, k)), fb.BF16)
+    res, rh = up(rng.standard_normal((m, n)), fb.BF16)
+    out = be.alloc(fb.BF16, (m, n))
+    be.run(Op.QuantMatmul(4, 64, epilogue=prepare(ir.add())), [x, be.tensor_from(pk, fb.U32), be.tensor_from(sc, fb.BF16), be.tensor_from(bi, fb.BF16), res], [out])
+    acc = fjo.quant_matmul(xh, fb.BF16, pk, sc, bi, fb.BF16, 4, 64, fjo.F32)
+    want = fjo.program(ir.add(), (m, n), [acc, rh], [fjo.F32, fb.BF16], [fb.BF16])[0]
+    assert_close(down(out), fjo.decode(want, fb.BF16), QUANT_TOL)
