@@ -838,6 +838,7 @@ int32_t exec_paged_attention_run(Exec& x, const fj_dispatch* ds, uint32_t count,
   if (!gp || gens0.dtype != FJ_U32 || element_count(gens0) != g.physical_pages || !is_contiguous(gens0)) return FJ_INVALID_INPUT;
 
   std::vector<fj::AttnSeq> seqs(count);
+  std::vector<fj::AppendLane> appends(append ? count : 0);
   unsigned max_q_len = 0;
   for (uint32_t i = 0; i < count; ++i) {
     const fj_dispatch& d = ds[i];
@@ -863,7 +864,7 @@ int32_t exec_paged_attention_run(Exec& x, const fj_dispatch* ds, uint32_t count,
       s.key_length = d.u2;
     }
     s.q_tok_stride = q.strides[1]; s.q_head_stride = q.strides[0]; s.o_tok_stride = out.strides[1]; s.o_head_stride = out.strides[0];
-    s.pad = 0;
+    s.err_index = i;  // every lane reports to the record of its own dispatch
     max_q_len = std::max(max_q_len, s.q_len);
     if (append) {
       // PagedCopy of the new K and V rows at q_start (crates/forja-cpu/src/lib.rs:272-290)
@@ -871,11 +872,15 @@ int32_t exec_paged_attention_run(Exec& x, const fj_dispatch* ds, uint32_t count,
       const void* knp = x.input(kn);
       const void* vnp = x.input(vn);
       if (!knp || !vnp || element_count(kn) != static_cast<uint64_t>(g.kv_heads) * g.head_dim || element_count(vn) != static_cast<uint64_t>(g.kv_heads) * g.value_dim) return FJ_INVALID_INPUT;
-      fj::launch_paged_copy(x.be->ctx, true, const_cast<void*>(knp), kn.dtype, g.kv_heads * g.head_dim, kp, kpool.dtype, s.table, s.table_pages, gp, g.physical_pages, d.u1, 1,
-                            g.page_tokens, g.kv_heads * g.head_dim, s.activity, err);
-      fj::launch_paged_copy(x.be->ctx, true, const_cast<void*>(vnp), vn.dtype, g.kv_heads * g.value_dim, vp, vpool.dtype, s.table, s.table_pages, gp, g.physical_pages, d.u1, 1,
-                            g.page_tokens, g.kv_heads * g.value_dim, s.activity, err);
+      if (!is_float(kn.dtype) || !is_float(vn.dtype)) return FJ_INVALID_INPUT;
+      appends[i] = fj::AppendLane{knp, vnp, s.table, s.activity, s.table_pages, d.u1, i, static_cast<int>(kn.dtype), static_cast<int>(vn.dtype)};
     }
+  }
+  if (append) {
+    // the new K and V rows of every lane go into their pages in one launch (one validate + copy pair per lane before)
+    fj::AppendLane* dev_appends = x.upload(appends);
+    if (!dev_appends) return FJ_ALLOCATION_FAILED;
+    fj::launch_paged_append_batch(x.be->ctx, dev_appends, count, kp, vp, kpool.dtype, gp, g.physical_pages, g.page_tokens, g.kv_heads * g.head_dim, g.kv_heads * g.value_dim, err);
   }
   fj::AttnSeq* dev_seqs = x.upload(seqs);
   if (!dev_seqs) return FJ_ALLOCATION_FAILED;
@@ -911,31 +916,25 @@ int32_t exec_paged_attention_run(Exec& x, const fj_dispatch* ds, uint32_t count,
   const uint64_t target_items = static_cast<uint64_t>(x.be->ctx.sm_count) * 2 * 4;
   uint64_t chunk = (total_tokens * g.kv_heads + target_items - 1) / std::max<uint64_t>(target_items, 1);
   chunk = std::min<uint64_t>(std::max<uint64_t>((chunk + 63) / 64 * 64, 64), 1024);
-  std::vector<fj::AttnWork> work;
-  unsigned groups = 0;
+  // the work list itself is built on the device from the lane descriptors; the host only needs its length
+  uint64_t n_work = 0;
   for (uint32_t i = 0; i < count; ++i) {
     const unsigned len = seqs[i].key_length;
-    const unsigned splits = len == 0 ? 1 : static_cast<unsigned>((len + chunk - 1) / chunk);
-    for (unsigned h = 0; h < g.kv_heads; ++h) {
-      for (unsigned sp = 0; sp < splits; ++sp) {
-        fj::AttnWork w;
-        w.seq = i; w.kv_head = h; w.t_begin = static_cast<unsigned>(sp * chunk); w.t_end = static_cast<unsigned>(std::min<uint64_t>(len, (sp + 1) * chunk));
-        w.split = sp; w.n_splits = splits; w.slot = static_cast<unsigned>(work.size()); w.group_index = groups;
-        work.push_back(w);
-      }
-      ++groups;
-    }
+    n_work += (len == 0 ? 1 : (len + chunk - 1) / chunk) * g.kv_heads;
   }
-  const size_t o_bytes = fj::attn_part_o_bytes(static_cast<unsigned>(work.size()), g.head_dim), ml_bytes = fj::attn_part_ml_bytes(static_cast<unsigned>(work.size()));
+  if (n_work > (1u << 24)) return FJ_QUOTA_EXCEEDED;
+  const unsigned groups = count * g.kv_heads;
+  const size_t o_bytes = fj::attn_part_o_bytes(static_cast<unsigned>(n_work), g.head_dim), ml_bytes = fj::attn_part_ml_bytes(static_cast<unsigned>(n_work));
   const size_t counter_bytes = (static_cast<size_t>(groups) * sizeof(unsigned) + 255) / 256 * 256;
   if (!ensure_attn_scratch(x.be, counter_bytes + o_bytes + ml_bytes)) return FJ_ALLOCATION_FAILED;
   fj::AttnScratch scratch;
   scratch.counters = static_cast<unsigned*>(x.be->attn_scratch);
   scratch.part_o = reinterpret_cast<float*>(static_cast<char*>(x.be->attn_scratch) + counter_bytes);
   scratch.part_ml = reinterpret_cast<float*>(static_cast<char*>(x.be->attn_scratch) + counter_bytes + o_bytes);
-  fj::AttnWork* dev_work = x.upload(work);
+  fj::AttnWork* dev_work = static_cast<fj::AttnWork*>(x.temp(static_cast<size_t>(n_work) * sizeof(fj::AttnWork)));
   if (!dev_work) return FJ_ALLOCATION_FAILED;
-  fj::launch_attn_decode_mma(x.be->ctx, g, dev_seqs, dev_work, static_cast<unsigned>(work.size()), kp, vp, gp, scratch, err);
+  fj::launch_build_work_from_seqs(x.be->ctx, dev_seqs, count, g.kv_heads, static_cast<unsigned>(chunk), dev_work, static_cast<unsigned>(n_work));
+  fj::launch_attn_decode_mma(x.be->ctx, g, dev_seqs, dev_work, static_cast<unsigned>(n_work), kp, vp, gp, scratch, err);
   return FJ_OK;
 }
 
@@ -1334,15 +1333,33 @@ int32_t fj_submit(fj_backend* be, const fj_dispatch* dispatches, uint32_t count,
         const bool append = d.op == FJ_OP_PAGED_SDPA_APPEND;
         const uint32_t want_in = append ? 5 : 5, want_out = append ? 3 : 1;
         if ((d.n_inputs != want_in && d.n_inputs != want_in + 1) || d.n_outputs != want_out) { status = FJ_INVALID_INPUT; break; }
-        // extend the run while the next dispatch shares planes/geometry and does not read what the run writes
+        // extend the run while the next dispatch shares planes/geometry and does not touch what the run writes. The bytes the
+        // run has written so far are kept as one hull per buffer (conservative: a gap inside the hull counts as written), so
+        // the test is one comparison per operand instead of one per earlier lane.
         uint32_t end = i + 1;
-        while (end < count && (dispatches[end].n_inputs == d.n_inputs) && dispatches[end].inputs && dispatches[end].outputs && paged_run_compatible(be, d, dispatches[end])) {
-          bool hazard = false;
-          for (uint32_t j = i; j < end && !hazard; ++j) {
-            hazard = ranges_overlap(be, dispatches[j].outputs[0], dispatches[end].inputs[0]) || ranges_overlap(be, dispatches[j].outputs[0], dispatches[end].outputs[0]);
-            if (append) hazard = hazard || ranges_overlap(be, dispatches[j].outputs[0], dispatches[end].inputs[1]) || ranges_overlap(be, dispatches[j].outputs[0], dispatches[end].inputs[2]);
-          }
-          if (hazard) break;
+        struct Hull { uint64_t buffer, lo, hi; };
+        std::vector<Hull> written;
+        auto note_output = [&](const fj_tensor& t) {
+          uint64_t lo = 0, hi = 0;
+          if (!tensor_byte_span(t, &lo, &hi)) return false;
+          for (Hull& h : written)
+            if (h.buffer == t.buffer) { h.lo = std::min(h.lo, lo); h.hi = std::max(h.hi, hi); return true; }
+          written.push_back(Hull{t.buffer, lo, hi});
+          return true;
+        };
+        auto touches_written = [&](const fj_tensor& t) {
+          uint64_t lo = 0, hi = 0;
+          if (!tensor_byte_span(t, &lo, &hi)) return true;
+          for (const Hull& h : written)
+            if (h.buffer == t.buffer && lo < h.hi && h.lo < hi) return true;
+          return false;
+        };
+        bool spans_ok = note_output(d.outputs[0]);
+        while (spans_ok && end < count && (dispatches[end].n_inputs == d.n_inputs) && dispatches[end].inputs && dispatches[end].outputs && paged_run_compatible(be, d, dispatches[end])) {
+          const fj_dispatch& next = dispatches[end];
+          bool hazard = touches_written(next.inputs[0]) || touches_written(next.outputs[0]);
+          if (append) hazard = hazard || touches_written(next.inputs[1]) || touches_written(next.inputs[2]);
+          if (hazard || !note_output(next.outputs[0])) break;
           ++end;
         }
         consumed = end - i;

@@ -84,7 +84,24 @@ struct TmaGemmParams {
   void* c; int c_dt; size_t ldc;
   unsigned m, n, k;
   int bf16;
+  unsigned splits, k_per_split;  // the CTAs of a cluster (blockIdx.z = rank in the cluster) share a tile along K; k_per_split is a multiple of 64
 };
+
+// 32 consecutive accumulator columns of this thread's TMEM lane, as f32 bit patterns.
+__device__ inline void tmem_load_32(unsigned taddr, unsigned (&v)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];\n"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]),
+        "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]),
+        "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+      : "r"(taddr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+}
+// All threads of all CTAs of the cluster meet; writes to shared memory before it are visible to cluster-wide reads after it.
+__device__ inline void cluster_sync() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;\n" ::: "memory");
+}
 
 // 32 consecutive columns of one output row, from their f32 bit patterns: rounded once, 64-byte rows when aligned.
 __device__ inline void store_row_chunk(const TmaGemmParams& p, unsigned row, unsigned c_first, const unsigned (&v)[32]) {
@@ -125,7 +142,8 @@ __global__ void __launch_bounds__(TM_THREADS, 1) gemm_nt_tma_kernel(const __grid
   __shared__ int s_failed;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const unsigned row0 = blockIdx.y * TM_BM, col0 = blockIdx.x * BN;
-  const unsigned k_iters = p.k / TM_BK;
+  const unsigned k_begin = blockIdx.z * p.k_per_split;
+  const unsigned k_iters = (min(p.k, k_begin + p.k_per_split) - k_begin) / TM_BK;
   const unsigned raw = static_cast<unsigned>(__cvta_generic_to_shared(tma_smem_raw));
   const unsigned smem_base = (raw + 1023u) & ~1023u;
   const unsigned full_base = static_cast<unsigned>(__cvta_generic_to_shared(&s_full[0]));
@@ -156,8 +174,8 @@ __global__ void __launch_bounds__(TM_THREADS, 1) gemm_nt_tma_kernel(const __grid
         if (it >= STAGES && !mbar_wait(empty_base + 8 * stage, ((it / STAGES) - 1) & 1u)) { s_failed = 1; break; }
         const unsigned dst = smem_base + stage * STAGE_BYTES;
         mbar_expect_tx(full_base + 8 * stage, STAGE_BYTES);
-        tma_load_2d(dst, &map_a, static_cast<int>(it * TM_BK), static_cast<int>(row0), full_base + 8 * stage);
-        tma_load_2d(dst + TM_A_BYTES, &map_w, static_cast<int>(it * TM_BK), static_cast<int>(col0), full_base + 8 * stage);
+        tma_load_2d(dst, &map_a, static_cast<int>(k_begin + it * TM_BK), static_cast<int>(row0), full_base + 8 * stage);
+        tma_load_2d(dst + TM_A_BYTES, &map_w, static_cast<int>(k_begin + it * TM_BK), static_cast<int>(col0), full_base + 8 * stage);
       }
     }
   } else if (warp == 1) {
@@ -188,21 +206,52 @@ __global__ void __launch_bounds__(TM_THREADS, 1) gemm_nt_tma_kernel(const __grid
     if (!ready) s_failed = 1;
     asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
     const unsigned row = row0 + quarter * 32 + lane;
-    if (ready) {
+    const unsigned tile_row = quarter * 32 + lane;
+    // Split K inside a cluster: ranks above 0 park their f32 partial tile in their own shared memory (the pipeline stages
+    // are free by now; 16-byte pieces of a row are XOR-ed with the row number so that a warp's stores spread over the banks),
+    // rank 0 adds them in rank order to its own accumulator through distributed shared memory and writes the tile.
+    if (ready && blockIdx.z != 0) {
+      asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");  // the stages were last touched through the async proxy (TMA writes, tensor-core reads)
 #pragma unroll 1
       for (int cb = 0; cb < (BN + 31) / 32; ++cb) {
         unsigned v[32];
-        const unsigned taddr = tmem + ((quarter * 32u) << 16) + cb * 32;
-        asm volatile(
-            "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];\n"
-            : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]),
-              "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]),
-              "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
-            : "r"(taddr));
-        asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+        tmem_load_32(tmem + ((quarter * 32u) << 16) + cb * 32, v);
+        const unsigned row_base = smem_base + tile_row * (BN * 4);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const unsigned piece = static_cast<unsigned>(cb * 8 + j) ^ (tile_row & 7u);
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};\n" ::"r"(row_base + piece * 16), "r"(v[4 * j]), "r"(v[4 * j + 1]), "r"(v[4 * j + 2]), "r"(v[4 * j + 3]) : "memory");
+        }
+      }
+    }
+    if (p.splits > 1) cluster_sync();  // partials are in place
+    if (ready && blockIdx.z == 0) {
+#pragma unroll 1
+      for (int cb = 0; cb < (BN + 31) / 32; ++cb) {
+        unsigned v[32];
+        tmem_load_32(tmem + ((quarter * 32u) << 16) + cb * 32, v);
+        for (unsigned rank = 1; rank < p.splits; ++rank) {
+          const unsigned local = smem_base + tile_row * (BN * 4);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const unsigned piece = static_cast<unsigned>(cb * 8 + j) ^ (tile_row & 7u);
+            unsigned remote, t0, t1, t2, t3;
+            asm volatile("mapa.shared::cluster.u32 %0, %1, %2;\n" : "=r"(remote) : "r"(local + piece * 16), "r"(rank));
+            asm volatile("ld.shared::cluster.v4.b32 {%0, %1, %2, %3}, [%4];\n" : "=r"(t0), "=r"(t1), "=r"(t2), "=r"(t3) : "r"(remote) : "memory");
+            v[4 * j] = __float_as_uint(__uint_as_float(v[4 * j]) + __uint_as_float(t0));
+            v[4 * j + 1] = __float_as_uint(__uint_as_float(v[4 * j + 1]) + __uint_as_float(t1));
+            v[4 * j + 2] = __float_as_uint(__uint_as_float(v[4 * j + 2]) + __uint_as_float(t2));
+            v[4 * j + 3] = __float_as_uint(__uint_as_float(v[4 * j + 3]) + __uint_as_float(t3));
+          }
+        }
         if (row < p.m) store_row_chunk(p, row, col0 + cb * 32, v);
       }
     }
+  }
+  // every thread of every CTA of the cluster: nobody leaves (and frees its shared memory) while rank 0 may still read it
+  if (p.splits > 1) {
+    if (warp < 2) cluster_sync();  // the two main-loop warps take part in the first meeting as well
+    cluster_sync();
   }
   asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
   __syncthreads();
@@ -270,8 +319,24 @@ template <int BN>
 bool run_tma(Ctx& ctx, const CUtensorMap& map_a, const CUtensorMap& map_w, const TmaGemmParams& p) {
   static SmemOptIn opted;
   if (!opt_in_smem(opted, gemm_nt_tma_kernel<BN>, kSmemBytes<BN>)) { cudaGetLastError(); return false; }
-  dim3 grid((p.n + BN - 1) / BN, (p.m + TM_BM - 1) / TM_BM);
-  launch_pdl(gemm_nt_tma_kernel<BN>, grid, dim3(TM_THREADS), kSmemBytes<BN>, ctx.stream, map_a, map_w, p);
+  cudaLaunchConfig_t config = {};
+  config.gridDim = dim3((p.n + BN - 1) / BN, (p.m + TM_BM - 1) / TM_BM, p.splits);
+  config.blockDim = dim3(TM_THREADS);
+  config.dynamicSmemBytes = kSmemBytes<BN>;
+  config.stream = ctx.stream;
+  cudaLaunchAttribute attributes[2];
+  attributes[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attributes[0].val.programmaticStreamSerializationAllowed = 1;
+  config.attrs = attributes;
+  config.numAttrs = 1;
+  if (p.splits > 1) {  // the CTAs that share a tile along K form a cluster
+    attributes[1].id = cudaLaunchAttributeClusterDimension;
+    attributes[1].val.clusterDim.x = 1;
+    attributes[1].val.clusterDim.y = 1;
+    attributes[1].val.clusterDim.z = p.splits;
+    config.numAttrs = 2;
+  }
+  if (cudaLaunchKernelEx(&config, gemm_nt_tma_kernel<BN>, map_a, map_w, p) != cudaSuccess) return false;  // the error stays pending for the submission
   ctx.launches++;
   return true;
 }
@@ -283,24 +348,37 @@ bool gemm_nt_tma_supported(int a_dt, int w_dt, unsigned m, unsigned n, unsigned 
          (reinterpret_cast<size_t>(a) | reinterpret_cast<size_t>(w)) % 16 == 0 && encode_tiled_entry() != nullptr;
 }
 
-// Tile width: the widest tile that still gives every SM a CTA; grids that cannot fill the GPU take 64 columns, the narrowest
-// outputs 32 (so that a 1024-column decode projection still spreads over 32 SMs). K is not split: measured on the decode
-// projections (128 rows), f32 partials plus a last-CTA reduction cost more than the shorter main loop saves
-// (1024 x 4096: 7.6 us unsplit, 12.5 us in two splits; 2048 x 1024: 11.5 against 20.1 us in eight).
-unsigned gemm_nt_tma_tile_n(unsigned m, unsigned n, int sm_count) {
+// Tile width and K split. Width: the widest tile that still gives every SM a CTA; grids that cannot fill the GPU take 64
+// columns, the narrowest outputs 32. Such grids with 2048 k or more are also split along K, 2 or 4 ways, while the grid stays
+// within one wave and every split keeps at least eight k steps: the CTAs of a split form a thread-block cluster and meet
+// through distributed shared memory (no partials in global memory, no atomics). What the split buys is less operand traffic
+// per SM: every CTA of an unsplit 128-row tile pulls the whole 128 x K activation block through its SM's L2 port. Measured on
+// the 128-row decode projections: 2048 x 1024 in 9.2 us instead of 11.5, 3072 x 1024 in 10.7 instead of 15.8; 1024 x 4096 is
+// faster unsplit (7.9 against 9.2 us).
+void gemm_nt_tma_plan(unsigned m, unsigned n, unsigned k, int sm_count, unsigned* tile_n, unsigned* splits, unsigned* k_per_split) {
   const unsigned row_blocks = (m + TM_BM - 1) / TM_BM;
   const unsigned sms = static_cast<unsigned>(sm_count > 0 ? sm_count : 148);
-  for (unsigned bn : {256u, 128u, 64u}) {
-    if (row_blocks * ((n + bn - 1) / bn) >= sms) return bn;
+  unsigned bn = row_blocks * ((n + 63) / 64) >= sms / 4 ? 64 : 32;
+  for (unsigned candidate : {256u, 128u, 64u}) {
+    if (row_blocks * ((n + candidate - 1) / candidate) >= sms) { bn = candidate; break; }
   }
-  return row_blocks * ((n + 63) / 64) >= sms / 4 ? 64 : 32;
+  const unsigned tiles = row_blocks * ((n + bn - 1) / bn), k_iters = k / TM_BK;
+  unsigned parts = 1;
+  if (k_iters >= 32) {  // a cluster launch costs about 1.5 us more than a plain one: below 2048 k the shorter main loop does not pay for it
+    while (parts < 4 && tiles * parts * 2 <= sms && k_iters / (parts * 2) >= 8) parts *= 2;
+  }
+  const unsigned iters_per = (k_iters + parts - 1) / parts;
+  *tile_n = bn;
+  *k_per_split = iters_per * TM_BK;
+  *splits = (k_iters + iters_per - 1) / iters_per;
 }
 
 bool launch_gemm_nt_tma(Ctx& ctx, const void* a, int a_dt, size_t lda, const void* w, size_t ldw, void* c, int c_dt, size_t ldc, unsigned m, unsigned n, unsigned k) {
-  const unsigned bn = gemm_nt_tma_tile_n(m, n, ctx.sm_count);
+  unsigned bn = 64, splits = 1, k_per_split = k;
+  gemm_nt_tma_plan(m, n, k, ctx.sm_count, &bn, &splits, &k_per_split);
   CUtensorMap map_a, map_w;
   if (!tensor_map_2d(a, m, k, lda, TM_BM, a_dt == BF16, &map_a) || !tensor_map_2d(w, n, k, ldw, bn, a_dt == BF16, &map_w)) return false;
-  TmaGemmParams p{c, c_dt, ldc, m, n, k, a_dt == BF16 ? 1 : 0};
+  TmaGemmParams p{c, c_dt, ldc, m, n, k, a_dt == BF16 ? 1 : 0, splits, k_per_split};
   switch (bn) {
     case 256: return run_tma<256>(ctx, map_a, map_w, p);
     case 128: return run_tma<128>(ctx, map_a, map_w, p);

@@ -110,7 +110,16 @@ struct AttnSeq {
   unsigned q_len, q_start, key_length, table_pages;
   unsigned long long q_tok_stride, q_head_stride, o_tok_stride, o_head_stride;  // elements
   unsigned causal;
-  unsigned pad;
+  unsigned err_index;           // which record of the launch's error array this lane reports to (its dispatch within a coalesced run)
+};
+// One lane of a batched single-token append (PagedSdpaAppend's copy half, crates/forja-cpu/src/lib.rs:262-307).
+struct AppendLane {
+  const void* k_new;            // [kv_heads * head_dim] and [kv_heads * value_dim] rows of the new token
+  const void* v_new;
+  const unsigned* table;
+  const unsigned* activity;     // one word or nullptr (= active)
+  unsigned table_pages, q_start, err_index;
+  int k_dtype, v_dtype;
 };
 struct AttnWork {
   unsigned seq, kv_head, t_begin, t_end, split, n_splits, slot, group_index;
@@ -147,6 +156,13 @@ void launch_attn_prefill_mma(Ctx& ctx, const AttnGeometry& g, const AttnSeq* seq
 // (sequence, head, query row)); used for f32 models and odd shapes.
 void launch_attn_generic(Ctx& ctx, const AttnGeometry& g, const AttnSeq* seqs, unsigned n_seqs, unsigned max_q_len,
                          const void* kpool, const void* vpool, const unsigned* generations, ErrorRecord* err);
+// Single-token appends of many lanes in one launch: lane i writes its new K and V rows at logical position q_start through its
+// authenticated page table, or reports ERR_PAGE to err[err_index] and writes nothing.
+void launch_paged_append_batch(Ctx& ctx, const AppendLane* lanes, unsigned count, void* kpool, void* vpool, int pool_dt, const unsigned* generations,
+                               unsigned physical_pages, unsigned page_tokens, unsigned k_elements, unsigned v_elements, ErrorRecord* err);
+// Split-K work list of a ragged decode launch, built on the device from the lanes' descriptors: chunks of `chunk` tokens per
+// (lane, kv head), in lane-major, head, split order (the order the host loop used to upload).
+void launch_build_work_from_seqs(Ctx& ctx, const AttnSeq* seqs, unsigned count, unsigned kv_heads, unsigned chunk, AttnWork* work, unsigned work_cap);
 // Paged copy of `tokens` rows between an ordinary [tokens, elements] tensor and a plane.
 void launch_paged_copy(Ctx& ctx, bool into_pages, void* ordinary, int o_dt, size_t o_row_stride, void* pool, int p_dt,
                        const unsigned* table, unsigned table_pages, const unsigned* generations, unsigned physical_pages,

@@ -371,7 +371,7 @@ __global__ void build_attn_lists_kernel(KvPoolDevice pool, PackOutputs pack, uns
       s.activity = nullptr;
       s.q_len = q_len; s.q_start = start; s.key_length = key_length; s.table_pages = pool.table_pages;
       s.q_tok_stride = row_elems; s.q_head_stride = head_dim; s.o_tok_stride = row_elems; s.o_head_stride = head_dim;
-      s.causal = 1; s.pad = 0;
+      s.causal = 1; s.err_index = 0;
       seqs[lane] = s;
     }
     unsigned total_items, total_groups;

@@ -210,7 +210,7 @@ __global__ void __launch_bounds__(kWarps * 32, 2) attn_decode_mma_kernel(DecodeP
       }
       if (!ok) {
         bad = 1;
-        report_error(p.err, ERR_PAGE, lp);
+        report_error(p.err != nullptr ? p.err + seq.err_index : nullptr, ERR_PAGE, lp);
         page = 0;
       }
       ent_page = page;
@@ -523,7 +523,7 @@ __global__ void __launch_bounds__(kWarps * 32, 2) attn_prefill_mma_kernel(Prefil
       }
       if (!ok) {
         bad = 1;
-        report_error(p.err, ERR_PAGE, lp);
+        report_error(p.err != nullptr ? p.err + seq.err_index : nullptr, ERR_PAGE, lp);
         page = 0;
       }
       ent_page = page;
@@ -720,7 +720,7 @@ __global__ void __launch_bounds__(kGenThreads) attn_generic_kernel(GenericParams
       if (ok) { page = seq.table[2 * lp]; ok = authenticate(page, seq.table[2 * lp + 1], p.generations, p.physical_pages); }
       float sc = -INFINITY;
       if (!ok) {
-        report_error(p.err, ERR_PAGE, lp);
+        report_error(p.err != nullptr ? p.err + seq.err_index : nullptr, ERR_PAGE, lp);
         s_bad = 1;
         row_base[i] = ~0ull;
       } else {
@@ -838,6 +838,84 @@ void launch_attn_generic(Ctx& ctx, const AttnGeometry& g, const AttnSeq* seqs, u
   ctx.launches++;
 }
 
+namespace {
+
+__global__ void __launch_bounds__(128) paged_append_batch_kernel(const AppendLane* __restrict__ lanes, unsigned count, void* kpool, void* vpool, int pool_dt,
+                                                                 const unsigned* __restrict__ generations, unsigned physical_pages, unsigned page_tokens,
+                                                                 unsigned k_elements, unsigned v_elements, ErrorRecord* err) {
+  pdl_sync();
+  const unsigned i = blockIdx.x;
+  if (i >= count) return;
+  const AppendLane lane = lanes[i];
+  if (lane.activity != nullptr && *lane.activity == 0) return;  // inactive lane: nothing is copied, its table is not read
+  const unsigned lp = lane.q_start / page_tokens;
+  bool ok = lp < lane.table_pages;
+  unsigned page = 0;
+  if (ok) { page = lane.table[2 * lp]; ok = authenticate(page, lane.table[2 * lp + 1], generations, physical_pages); }
+  if (!ok) {
+    if (threadIdx.x == 0) report_error(err != nullptr ? err + lane.err_index : nullptr, ERR_PAGE, lp);
+    return;
+  }
+  const size_t row = static_cast<size_t>(page) * page_tokens + lane.q_start % page_tokens;
+  for (unsigned e = threadIdx.x; e < k_elements; e += blockDim.x) store_from_f32(kpool, pool_dt, row * k_elements + e, load_as_f32(lane.k_new, lane.k_dtype, e));
+  for (unsigned e = threadIdx.x; e < v_elements; e += blockDim.x) store_from_f32(vpool, pool_dt, row * v_elements + e, load_as_f32(lane.v_new, lane.v_dtype, e));
+}
+
+// One CTA: exclusive scan of the lanes' item counts, then every lane writes its items.
+__global__ void __launch_bounds__(256) build_work_from_seqs_kernel(const AttnSeq* __restrict__ seqs, unsigned count, unsigned kv_heads, unsigned chunk, AttnWork* work,
+                                                                   unsigned work_cap) {
+  __shared__ unsigned warp_totals[8];
+  __shared__ unsigned s_base;
+  pdl_sync();
+  if (threadIdx.x == 0) s_base = 0;
+  __syncthreads();
+  for (unsigned l0 = 0; l0 < count; l0 += blockDim.x) {
+    const unsigned lane = l0 + threadIdx.x;
+    unsigned len = 0, splits = 0;
+    if (lane < count) { len = seqs[lane].key_length; splits = len == 0 ? 1u : (len + chunk - 1) / chunk; }
+    const unsigned items = splits * kv_heads;
+    // block-wide exclusive scan of `items`
+    unsigned inclusive = items;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) { const unsigned t = __shfl_up_sync(0xffffffffu, inclusive, o); if ((threadIdx.x & 31) >= static_cast<unsigned>(o)) inclusive += t; }
+    if ((threadIdx.x & 31) == 31) warp_totals[threadIdx.x >> 5] = inclusive;
+    __syncthreads();
+    unsigned before = s_base, total = 0;
+    for (unsigned w = 0; w < blockDim.x / 32; ++w) { if (w < (threadIdx.x >> 5)) before += warp_totals[w]; total += warp_totals[w]; }
+    const unsigned first = before + inclusive - items;
+    if (lane < count) {
+      for (unsigned h = 0; h < kv_heads; ++h) {
+        for (unsigned sp = 0; sp < splits; ++sp) {
+          const unsigned idx = first + h * splits + sp;
+          if (idx >= work_cap) continue;
+          AttnWork w;
+          w.seq = lane; w.kv_head = h; w.t_begin = sp * chunk; w.t_end = min(len, (sp + 1) * chunk);
+          w.split = sp; w.n_splits = splits; w.slot = idx; w.group_index = lane * kv_heads + h;
+          work[idx] = w;
+        }
+      }
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) s_base += total;
+    __syncthreads();
+  }
+}
+
+}  // namespace
+
+void launch_paged_append_batch(Ctx& ctx, const AppendLane* lanes, unsigned count, void* kpool, void* vpool, int pool_dt, const unsigned* generations,
+                               unsigned physical_pages, unsigned page_tokens, unsigned k_elements, unsigned v_elements, ErrorRecord* err) {
+  if (count == 0) return;
+  launch_pdl(paged_append_batch_kernel, dim3(count), dim3(128), 0, ctx.stream, lanes, count, kpool, vpool, pool_dt, generations, physical_pages, page_tokens, k_elements, v_elements, err);
+  ctx.launches++;
+}
+
+void launch_build_work_from_seqs(Ctx& ctx, const AttnSeq* seqs, unsigned count, unsigned kv_heads, unsigned chunk, AttnWork* work, unsigned work_cap) {
+  if (count == 0) return;
+  launch_pdl(build_work_from_seqs_kernel, dim3(1), dim3(256), 0, ctx.stream, seqs, count, kv_heads, chunk, work, work_cap);
+  ctx.launches++;
+}
+
 void launch_paged_copy(Ctx& ctx, bool into_pages, void* ordinary, int o_dt, size_t o_row_stride, void* pool, int p_dt,
                        const unsigned* table, unsigned table_pages, const unsigned* generations, unsigned physical_pages,
                        unsigned start, unsigned tokens, unsigned page_tokens, unsigned elements, const unsigned* activity,
@@ -910,7 +988,7 @@ __global__ void static_attention_plan_kernel(StaticPlan plan, unsigned char* scr
     s.activity = nullptr;
     s.q_len = 1; s.q_start = len ? len - 1 : 0; s.key_length = len; s.table_pages = plan.table_pages;
     s.q_tok_stride = row_elems; s.q_head_stride = kHeadDim; s.o_tok_stride = row_elems; s.o_head_stride = kHeadDim;
-    s.causal = 1; s.pad = 0;
+    s.causal = 1; s.err_index = 0;
     seqs[lane] = s;
     // items of this lane start after those of the lanes before it
     unsigned first = 0;

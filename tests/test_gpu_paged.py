@@ -226,8 +226,8 @@ def test_batched_append_attention_equals_single_lane_and_is_one_ragged_launch():
         return down_raw(out), down_raw(kp), down_raw(vp), subs
 
     got, got_k, got_v, subs = run(True)
-    # lanes * 2 single-row appends (one validate + one copy kernel each) + ONE attention kernel
-    assert subs[0].kernel_launches() == lanes * 4 + 1
+    # one append kernel for every lane's new K and V rows, one that builds the split-K work list, ONE attention kernel
+    assert subs[0].kernel_launches() == 3
     one, one_k, one_v, _ = run(False)
     assert np.array_equal(got, one) and np.array_equal(got_k, one_k) and np.array_equal(got_v, one_v)
     want_k, want_v = kh.copy(), vh.copy()
@@ -355,3 +355,47 @@ def test_attention_output_view_at_an_odd_element_offset(q_len, q_start):
     assert_close(down(out).transpose(1, 0, 2), fjo.decode(want, dt), TOL[dt])
     raw = down_raw(flat)
     assert raw[0] == 0 and not raw[-2:].any()
+
+
+def test_coalesced_run_reports_a_bad_lane_under_its_own_dispatch():
+    """Per-lane attention dispatches over shared planes run as one launch, but a refused page entry is still reported with
+    the index of the dispatch it belongs to (the reference runs the dispatches one by one), for decode and append runs."""
+    rng = np.random.default_rng(31)
+    be = backend()
+    dt, page, hq, kvh, d, lanes = fb.BF16, 16, 16, 8, 128, 5
+    lengths = [40, 300, 17, 1000, 64]
+    physical = sum((n + page) // page + 1 for n in lengths) + 2
+    generations = rng.integers(1, 50, physical).astype(np.uint32)
+    perm = rng.permutation(physical).astype(np.uint32)
+    tables, cursor = [], 0
+    for n in lengths:
+        pages = (n + page) // page + 1
+        t = np.zeros((pages, 2), np.uint32)
+        t[:, 0] = perm[cursor:cursor + pages]
+        t[:, 1] = generations[t[:, 0]]
+        cursor += pages
+        tables.append(t)
+    bad_lane = 3
+    tables[bad_lane][lengths[bad_lane] // page, 1] ^= 1  # the page that holds the newest token is stale
+    kt, _, vt, _ = fill_pools(rng, physical, page, kvh, d, dt)
+    q, _ = up(rng.standard_normal((lanes, hq, d)), dt)
+    kn, _ = up(rng.standard_normal((lanes, kvh, d)), dt)
+    gn = up_u32(generations)[0]
+    for append in (False, True):
+        out = be.tensor_from(np.full((lanes, hq, d), 0x3F80, np.uint16), dt)
+        cl = CommandList()
+        cl.dispatch(Op.Copy(), [q], be.alloc(dt, (lanes, hq, d)))  # dispatch 0 is something else
+        for lane, n in enumerate(lengths):
+            row = [(lane, 1, 1), (0, hq, 1), (0, d, 1)]
+            if append:
+                cl.dispatch_many(Op.PagedSdpaAppend(0.0884, n, page), [q.slice(row).permute([1, 0, 2]), kn.narrow(0, lane, 1), kn.narrow(0, lane, 1), up_u32(tables[lane])[0], gn],
+                                 [out.slice(row).permute([1, 0, 2]), kt, vt])
+            else:
+                cl.dispatch(Op.PagedSdpa(0.0884, True, n, n + 1, page), [q.slice(row).permute([1, 0, 2]), kt, vt, up_u32(tables[lane])[0], gn], out.slice(row).permute([1, 0, 2]))
+        with pytest.raises(fb.BackendError) as e:
+            be.submit(cl).wait()
+        assert e.value.status == fb.backend.DEVICE_ERROR_FLAG and e.value.flag == 2 and e.value.index == lengths[bad_lane] // page
+        assert e.value.dispatch == 1 + bad_lane
+        got = down_raw(out)
+        assert not got[bad_lane].any()
+        assert all(got[lane].any() for lane in range(lanes) if lane != bad_lane)
