@@ -236,6 +236,29 @@ class MoeOracle:
         return fjo.decode(logits, dt)[0], int(fjo.argmax(logits, dt)[0])
 
 
+class Bf16WeightMoeOracle(MoeOracle):
+    """MoeOracle with one liberty taken in the 4-bit projections of the attention block and the lm_head: the
+    dequantised weight s * q + b (f32, as the reference forms it, crates/forja-cpu/src/lib.rs:878-962) is rounded
+    to bf16 before the products, which is what a tensor-core GEMM over 16-bit operands has to do, and the sums run
+    in blocked (BLAS) order. Accumulation stays f32 and every other rounding point stays in place. The distance
+    between this oracle and MoeOracle on the same inputs and routing is the floor of a comparison against such a
+    GEMM: each projection moves by about 2e-3 normwise, and a layer amplifies that."""
+
+    def _q(self, x, triple, bits=4, out_dt=None):
+        if bits != 4:
+            return super()._q(x, triple, bits, out_dt)
+        cache = self.__dict__.setdefault("_bf16_weights", {})
+        wf = cache.get(id(triple[0]))
+        if wf is None:
+            packed, G = triple[0], self.cfg["group_size"]
+            q = ((packed[..., None] >> (np.arange(8, dtype=np.uint32) * 4)) & 15).reshape(packed.shape[0], -1).astype(np.float32)
+            s = np.repeat(fjo.decode(triple[1], fjo.BF16), G, axis=-1)
+            b = np.repeat(fjo.decode(triple[2], fjo.BF16), G, axis=-1)
+            wf = cache[id(triple[0])] = fjo.decode(fjo.encode((s * q).astype(np.float32) + b, fjo.BF16), fjo.BF16)
+        y = (fjo.decode(x, fjo.BF16) @ wf.T).astype(np.float32)
+        return y if out_dt == fjo.F32 else fjo.encode(y, fjo.BF16)
+
+
 def ep_moe_layer(rank: int, world: int, cfg: dict, normed, residual, L_local: dict, router, exchange):
     """Expert-parallel form of MoeOracle.moe for one rank, restating the device algorithm in numpy:
     slots are handed out per destination in (row, j) order, slabs of capacity rows * top_k are
