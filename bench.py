@@ -53,6 +53,7 @@ def parse_args():
     ap.add_argument("--moe-lanes", type=int, default=256, help="lanes of the sparse-MoE block, in total over all GPUs")
     ap.add_argument("--moe-steps", type=int, default=8)
     ap.add_argument("--moe-layers", type=int, default=0, help="0 = the model's 48")
+    ap.add_argument("--moe-nccl", action="store_true", help="sharded MoE block: exchange through NCCL send/recv instead of peer stores over NVLink")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-graph-replay", action="store_true", help="launch every decode step kernel by kernel instead of replaying its recorded CUDA graph")
     return ap.parse_args()
@@ -411,6 +412,11 @@ def moe_ep(args, rank, world, local, dist):
         if dist is not None:
             dist.barrier()
 
+    def gather(obj):
+        out = [None] * world
+        dist.all_gather_object(out, obj)
+        return out
+
     def reduce(value, op):
         if dist is None:
             return value
@@ -422,7 +428,7 @@ def moe_ep(args, rank, world, local, dist):
     try:
         return benchmarks.moe_ep_block(rank, world, local, exchange, barrier_all, lambda v: reduce(v, dist.ReduceOp.MAX if dist else None),
                                        lambda v: reduce(v, dist.ReduceOp.SUM if dist else None), lanes_total=args.moe_lanes, steps=args.moe_steps, warmup=3,
-                                       layers=args.moe_layers, seed=args.seed)
+                                       layers=args.moe_layers, seed=args.seed, all_gather=None if (dist is None or args.moe_nccl) else gather)
     except Exception as error:  # noqa: BLE001 - the headline line is still printed; the failure is reported in the block
         return {"error": f"{type(error).__name__}: {error}"}
 

@@ -703,8 +703,36 @@ class MoeModel:
                                              C.byref(handle)))
         self._h = handle
 
+    def connect_peers(self, all_gather) -> bool:
+        """Switches an expert-parallel model to the direct exchange (peer stores over NVLink instead of NCCL, no host
+        round trip; fj_moe_ep_*). ``all_gather(obj) -> list`` returns every rank's object in rank order (e.g.
+        torch.distributed.all_gather_object); it is called three times here and once more by close(). Returns whether
+        the direct exchange is in use: every rank must have mapped every peer, otherwise all stay on NCCL."""
+        mine = (C.c_uint8 * 256)()
+        status = self._lib.fj_moe_ep_export(self._h, mine)
+        table = all_gather(bytes(mine) if status == 0 else None)
+        if status == 0 and all(t is not None and len(t) == 256 for t in table):
+            status = self._lib.fj_moe_ep_connect(self._h, (C.c_uint8 * (256 * len(table))).from_buffer_copy(b"".join(table)))
+        else:
+            status = status or 1
+        self._peer_gather = all_gather
+        everyone = all(s == 0 for s in all_gather(int(status)))
+        if everyone:
+            _check(self._lib.fj_moe_ep_direct(self._h, 1))
+        all_gather(None)  # nobody steps before everybody has switched
+        return everyone
+
+    def set_wait_polls(self, polls: int):
+        _check(self._lib.fj_moe_ep_wait_polls(self._h, polls))
+
     def close(self):
         if getattr(self, "_h", None) and getattr(self.backend, "_h", None):
+            gather = getattr(self, "_peer_gather", None)
+            if gather is not None:
+                # mappings of the peers' buffers are closed everywhere before anyone frees
+                self._lib.fj_moe_ep_disconnect(self._h)
+                gather(None)
+                self._peer_gather = None
             self._lib.fj_moe_model_destroy(self._h)
         self._h = None
 

@@ -239,13 +239,14 @@ def run_moe(args):
 
 
 def moe_ep_block(rank, world, local_rank, exchange, barrier, max_over_ranks, sum_over_ranks, lanes_total=256, steps=8, warmup=3, layers=0, seed=0,
-                 prompt_budget=2048, prompt_range=(512, 4096), prefill_limit=4):
+                 prompt_budget=2048, prompt_range=(512, 4096), prefill_limit=4, all_gather=None):
     """One measurement of the sparse-MoE continuous-batching step (Qwen3-30B-A3B shape, q4 weights, bf16 activations) with the
     experts sharded over `world` ranks: `lanes_total` lanes split evenly over the ranks (strong scaling over the lanes), every
     rank prefilling up to `prompt_budget` prompt tokens per step beside its decode rows. `exchange(obj)` broadcasts rank 0's
     object (the NCCL id of the expert-parallel group), `barrier()` aligns the ranks, `max_over_ranks(x)` / `sum_over_ranks(x)`
-    reduce a float. Timed with CUDA events on the backend's stream between barriers, maximum over ranks; two further steps
-    run with per-phase events for the split. Returns the block on every rank."""
+    reduce a float; `all_gather(obj) -> list`, when given, lets the ranks map each other's buffers so that the exchange runs as
+    peer stores over NVLink instead of NCCL (MoeModel.connect_peers). Timed with CUDA events on the backend's stream between
+    barriers, maximum over ranks; two further steps run with per-phase events for the split. Returns the block on every rank."""
     cfg = dict(MOE)
     if layers:
         cfg["layers"] = layers
@@ -259,6 +260,7 @@ def moe_ep_block(rank, world, local_rank, exchange, barrier, max_over_ranks, sum
     table_pages = (prompt_range[1] + 256 + 1 + PAGE - 1) // PAGE + 1
     pool = fb.KvPool(be, PAGE, lanes * table_pages + 8, lanes, table_pages)
     model = build_moe(be, pool, cfg, ep, rank, world)
+    direct = bool(world > 1 and all_gather is not None and model.connect_peers(all_gather))
     state = MoeLanes(pool, lanes, seed + rank, prompt_budget, prefill_limit, prompt_range, False)
     rng = np.random.default_rng(seed + 77 + rank)
     t0, t1 = be.timer(), be.timer()
@@ -293,18 +295,24 @@ def moe_ep_block(rank, world, local_rank, exchange, barrier, max_over_ranks, sum
         one_step()
         phase_ms = [a + b for a, b in zip(phase_ms, model.phase_ms())]
     model.phase_timing(False)
-    phases = {name: max_over_ranks(v / phase_steps) for name, v in zip(("attention_and_router", "dispatch", "experts", "return_and_combine"), phase_ms)}
+    names = ("attention_and_router", "dispatch", "experts", "return_and_combine")
+    phases = {name: max_over_ranks(v / phase_steps) for name, v in zip(names, phase_ms)}
+    # the smallest value over the ranks: a rank that arrives early at an exchange waits there for the others, so the spread of
+    # the two exchange phases is mostly the imbalance of the compute phases before them
+    phases_min = {name: -max_over_ranks(-v / phase_steps) for name, v in zip(names, phase_ms)}
     rows_per_step = total / steps / world
     remote = (world - 1) / world
     block = {
         "workload": "qwen3-30b-a3b-arch q4 sparse-MoE continuous batching (chunked prefill + decode), %d layers, 128 experts top-8" % cfg["layers"],
         "n_gpus": world, "scaling": "strong over the lanes (%d lanes in total, %d per GPU); prompt budget %d tokens per GPU and step" % (lanes_total, lanes, prompt_budget),
         "tok_s": total / elapsed, "ms_per_step": elapsed / steps * 1e3, "steps": steps, "warmup": warmup, "rows_per_gpu_step": rows_per_step,
-        "phase_ms_per_step_max_over_ranks": phases,
+        "phase_ms_per_step_max_over_ranks": phases, "phase_ms_per_step_min_over_ranks": phases_min,
         "exchange_mb_per_layer_and_gpu": {"dispatch_bf16": rows_per_step * cfg["top_k"] * remote * cfg["hidden"] * 2 / 1e6,
                                           "return_f32": rows_per_step * cfg["top_k"] * remote * cfg["hidden"] * 4 / 1e6},
         "gpu_launches": int(sum_over_ranks(float(kernels))),
-        "parallelism": ("experts sharded over %d GPUs, NCCL send/recv all-to-all per MoE layer, lanes data-parallel" % world) if world > 1 else "single GPU",
+        "parallelism": ("experts sharded over %d GPUs, %s per MoE layer, lanes data-parallel" %
+                        (world, "rows stored straight into the owner's memory over NVLink by the producing kernels, flags instead of a host round trip" if direct
+                         else "NCCL send/recv all-to-all")) if world > 1 else "single GPU",
     }
     model.close()
     pool.close()

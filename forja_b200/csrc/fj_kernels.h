@@ -209,7 +209,8 @@ void launch_gather_quant_weighted_sum(Ctx& ctx, const void* act, int a_dt, const
 // Routes bucketed by expert and cut into tiles of tile_rows rows (64 for the tile GEMMs, 16 for the streaming form); `plan` is caller-owned device memory of
 // route_plan_bytes(total_routes, experts). Ids >= experts are left out of every bucket.
 size_t route_plan_bytes(unsigned total_routes, unsigned experts);
-void launch_route_plan(Ctx& ctx, const unsigned* indices, unsigned total_routes, unsigned experts, void* plan, ErrorRecord* err, unsigned tile_rows = 64);
+void launch_route_plan(Ctx& ctx, const unsigned* indices, unsigned total_routes, unsigned experts, void* plan, ErrorRecord* err, unsigned tile_rows = 64,
+                       const unsigned* slab_counts = nullptr, unsigned slab_cap = 0);
 bool grouped_q4_supported(unsigned k, unsigned n, unsigned bits, unsigned group_size, unsigned experts, const void* x, const void* packed);
 // Rows per tile (64 or 128) the tile GEMMs should use for this many routes; pass it to launch_route_plan and to both launchers.
 unsigned grouped_tile_rows(unsigned total_routes, unsigned experts);

@@ -234,7 +234,7 @@ __global__ void ep_plan_kernel(const unsigned* __restrict__ indices, unsigned ro
     if (dest >= world) { route_slot[r] = 0xFFFFFFFFu; continue; }  // bad expert id: contributes nothing
     const unsigned slot = dest * capacity + atomicAdd(&send_counts[dest], 1u);
     route_slot[r] = slot;
-    send_experts[slot] = expert - dest * experts_local;
+    if (send_experts) send_experts[slot] = expert - dest * experts_local;
   }
 }
 
@@ -284,6 +284,208 @@ __global__ void ep_scatter_rows_kernel(const unsigned short* __restrict__ normed
   }
 }
 
+// ---- direct exchange: rows are stored straight into the owner's memory over NVLink ----------------
+// Ranks of one node map each other's receive buffers (CUDA IPC) and a layer's exchange becomes plain peer
+// stores plus one 64-bit flag per (source, destination): {exchange number, row count}. The kernel that wrote
+// the rows publishes the flag after a system-scope fence from its last block; the receiver polls its own
+// memory, with a bound, and hands the counts to the kernels that follow on its stream. No host round trip,
+// no staging copy, no multicast. Why no back-pressure flag is needed: a rank overwrites a peer's slab for
+// exchange e + 1 only after it received that peer's results of exchange e, which the peer sent after it
+// finished reading the slab.
+struct EpPeers {
+  unsigned short* const* rows;        // [world] every rank's recv_rows
+  unsigned* const* experts;           // [world] every rank's recv_experts
+  unsigned long long* const* flags;   // [world] every rank's flag words: [world] dispatch | [world] return
+  const unsigned char* const* results;  // [world] every rank's per-route results (down_ep), read by the origin's combine
+};
+
+__device__ inline void st_release_sys(unsigned long long* p, unsigned long long v) { asm volatile("st.release.sys.global.u64 [%0], %1;\n" ::"l"(p), "l"(v) : "memory"); }
+__device__ inline unsigned long long ld_acquire_sys(const unsigned long long* p) {
+  unsigned long long v;
+  asm volatile("ld.acquire.sys.global.u64 %0, [%1];\n" : "=l"(v) : "l"(p) : "memory");
+  return v;
+}
+
+// The last block to finish publishes what the whole grid stored: true in exactly one block, after every block's
+// stores were fenced at system scope. `ticket` returns to zero for the next launch.
+__device__ inline bool ep_last_block(unsigned* ticket) {
+  __shared__ bool s_last;
+  __syncthreads();  // orders the block's stores before thread 0's fence: one system fence per block, not one per thread
+  if (threadIdx.x == 0) {
+    __threadfence_system();
+    s_last = atomicAdd(ticket, 1u) == gridDim.x - 1;
+    if (s_last) *ticket = 0;
+    __threadfence_system();
+  }
+  __syncthreads();
+  return s_last;
+}
+
+// Dispatch: every route takes a slot of its destination's slab (which one does not matter, results are read back by slot):
+// a block counts its routes per destination in shared memory and reserves the ranges with one atomic per destination, so the
+// global counters see a few hundred atomics instead of one per route. Each route's activation row and local expert id then go
+// into slot (rank * capacity + slot) of the owner's buffers, one warp per row with eight 16-byte pieces in flight per lane;
+// finally flag[rank] of every peer = {exchange, rows sent to it}. Zeroes the send counters for the next layer.
+__global__ void __launch_bounds__(256) ep_push_dispatch_kernel(const unsigned short* __restrict__ normed, const unsigned* __restrict__ route_experts, unsigned routes, unsigned top_k,
+                                                               unsigned width, unsigned capacity, unsigned rank, unsigned world, unsigned experts_local, EpPeers peers,
+                                                               unsigned* route_slot, unsigned* send_counts, unsigned* ticket, unsigned exchange) {
+  __shared__ unsigned s_count[64], s_base[64], s_slot[256];
+  const unsigned vecs = width / 8, lane = threadIdx.x & 31u, warp = threadIdx.x / 32, warps = blockDim.x / 32;
+  const unsigned per_block = (routes + gridDim.x - 1) / gridDim.x;
+  const unsigned begin = min(routes, blockIdx.x * per_block), end = min(routes, begin + per_block);
+  for (unsigned chunk = begin; chunk < end; chunk += blockDim.x) {
+    if (threadIdx.x < 64) s_count[threadIdx.x] = 0;
+    __syncthreads();
+    const unsigned r = chunk + threadIdx.x;
+    unsigned expert = 0, dest = 0xFFFFFFFFu, local = 0;
+    if (r < end) {
+      expert = route_experts[r];
+      dest = expert / experts_local;
+      if (dest < world) local = atomicAdd(&s_count[dest], 1u);
+    }
+    __syncthreads();
+    if (threadIdx.x < world) s_base[threadIdx.x] = s_count[threadIdx.x] ? atomicAdd(&send_counts[threadIdx.x], s_count[threadIdx.x]) : 0u;
+    __syncthreads();
+    if (r < end) {
+      unsigned slot = 0xFFFFFFFFu;  // bad expert id: contributes nothing
+      if (dest < world) {
+        const unsigned in = s_base[dest] + local;
+        if (in < capacity) {
+          slot = dest * capacity + in;
+          peers.experts[dest][rank * capacity + in] = expert - dest * experts_local;
+        }
+      }
+      route_slot[r] = slot;
+      s_slot[threadIdx.x] = slot;
+    }
+    __syncthreads();
+    const unsigned n = min(blockDim.x, end - chunk);
+    for (unsigned i = warp; i < n; i += warps) {
+      const unsigned slot = s_slot[i];
+      if (slot == 0xFFFFFFFFu) continue;
+      const unsigned to = slot / capacity, at = rank * capacity + slot % capacity;
+      const uint4* src = reinterpret_cast<const uint4*>(normed + static_cast<size_t>((chunk + i) / top_k) * width);
+      uint4* dst = reinterpret_cast<uint4*>(peers.rows[to] + static_cast<size_t>(at) * width);
+      for (unsigned base = 0; base < vecs; base += 256) {
+        uint4 v[8];
+#pragma unroll
+        for (unsigned u = 0; u < 8; ++u) {
+          const unsigned k = base + u * 32 + lane;
+          if (k < vecs) v[u] = src[k];
+        }
+#pragma unroll
+        for (unsigned u = 0; u < 8; ++u) {
+          const unsigned k = base + u * 32 + lane;
+          if (k < vecs) dst[k] = v[u];
+        }
+      }
+    }
+    __syncthreads();
+  }
+  if (ep_last_block(ticket) && threadIdx.x < world) {
+    const unsigned count = min(send_counts[threadIdx.x], capacity);
+    send_counts[threadIdx.x] = 0;
+    st_release_sys(peers.flags[threadIdx.x] + rank, (static_cast<unsigned long long>(exchange) << 32) | count);
+  }
+}
+
+// Waits, with a bound, until every source's flag carries this exchange number; stores the row counts for the
+// kernels that follow. A wait that runs out sets *wait_err (and every later wait returns at once): the step then
+// computes on zero rows and the host answers FJ_TIMEOUT; the context stays usable.
+// signal_flags != nullptr: before waiting, publish {exchange, 0} in word signal_at of every peer's flags (the owner's "results
+// of this exchange are ready": everything earlier on the stream has completed and the fence orders it before the flag).
+__global__ void ep_wait_kernel(const unsigned long long* flags, unsigned world, unsigned exchange, unsigned capacity, unsigned* counts_out, unsigned* stale_counts, unsigned* recv_experts,
+                               unsigned* live_total_host, unsigned* wait_err, unsigned max_polls, unsigned long long* const* signal_flags = nullptr, unsigned signal_at = 0) {
+  __shared__ unsigned s_counts[64];
+  const unsigned src = threadIdx.x;
+  unsigned count = 0;
+  if (signal_flags && src < world) {
+    __threadfence_system();
+    st_release_sys(signal_flags[src] + signal_at, static_cast<unsigned long long>(exchange) << 32);
+  }
+  if (src < world) {
+    bool seen = false;
+    for (unsigned poll = 0; poll < max_polls && *reinterpret_cast<volatile unsigned*>(wait_err) == 0; ++poll) {
+      const unsigned long long v = ld_acquire_sys(flags + src);
+      if (static_cast<unsigned>(v >> 32) == exchange) { count = min(static_cast<unsigned>(v), capacity); seen = true; break; }
+      __nanosleep(poll < 64 ? 20 : 500);
+    }
+    if (!seen) atomicExch(wait_err, exchange ? exchange : 1u);
+    if (counts_out) counts_out[src] = count;
+  }
+  if (src < 64) s_counts[src] = src < world ? count : 0;
+  __syncthreads();
+  if (recv_experts) {
+    // ids left over from an earlier, longer slab must not look valid to kernels that read the whole slab
+    for (unsigned s = 0; s < world; ++s) {
+      const unsigned now = s_counts[s], before = stale_counts[s];
+      for (unsigned i = now + threadIdx.x; i < before; i += blockDim.x) recv_experts[static_cast<size_t>(s) * capacity + i] = 0xFFFFFFFFu;
+    }
+    __syncthreads();
+    if (src < world) stale_counts[src] = count;
+  }
+  if (threadIdx.x == 0 && live_total_host) {
+    unsigned total = 0;
+    for (unsigned s = 0; s < world; ++s) total += s_counts[s];
+    *live_total_host = total;
+  }
+}
+
+// Return by reading instead of writing: the owner only publishes "results of this exchange are ready" (ep_wait_kernel's
+// signal), and the origin's
+// combine reads each route's result row from the owner's memory (peer loads over NVLink; all top_k rows of a column group are
+// in flight before the first is used). Same arithmetic as routes_combine_kernel: sum over j ascending of the rounded products
+// w_j * row_j, then the residual. Nothing is staged on either side. The owner overwrites its results for exchange e + 1 only
+// after every peer's dispatch of e + 1 arrived, which each peer issues after this kernel of exchange e.
+template <bool kBf16>
+__global__ void __launch_bounds__(256) ep_pull_combine_kernel(const unsigned char* const* __restrict__ results /*[world] every rank's per-route results*/,
+                                                              const unsigned* __restrict__ route_slot, const float* __restrict__ weights, const void* __restrict__ extra, int e_dt, void* out,
+                                                              int out_dt, unsigned rows, unsigned top_k, unsigned width, unsigned capacity, unsigned rank) {
+  constexpr unsigned kBatch = 8;
+  for (unsigned row = blockIdx.x; row < rows; row += gridDim.x) {
+    for (unsigned c = threadIdx.x * 4; c < width; c += blockDim.x * 4) {
+      float total[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+      for (unsigned j0 = 0; j0 < top_k; j0 += kBatch) {
+        float4 v[kBatch];
+        float w[kBatch];
+        unsigned valid = 0;
+#pragma unroll
+        for (unsigned b = 0; b < kBatch; ++b) {
+          const unsigned j = j0 + b;
+          const unsigned slot = j < top_k ? route_slot[row * top_k + j] : 0xFFFFFFFFu;
+          w[b] = 0.0f;
+          v[b] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+          if (slot == 0xFFFFFFFFu) continue;
+          valid |= 1u << b;
+          w[b] = weights[row * top_k + j];
+          const size_t at = (static_cast<size_t>(rank) * capacity + slot % capacity) * width + c;
+          const unsigned char* base = results[slot / capacity];
+          if (kBf16) {
+            const uint2 h = *reinterpret_cast<const uint2*>(base + at * 2);
+            v[b] = make_float4(__uint_as_float(h.x << 16), __uint_as_float(h.x & 0xFFFF0000u), __uint_as_float(h.y << 16), __uint_as_float(h.y & 0xFFFF0000u));
+          } else {
+            v[b] = *reinterpret_cast<const float4*>(base + at * 4);
+          }
+        }
+#pragma unroll
+        for (unsigned b = 0; b < kBatch; ++b) {
+          if (!(valid >> b & 1u)) continue;
+          total[0] = __fadd_rn(total[0], __fmul_rn(w[b], v[b].x));
+          total[1] = __fadd_rn(total[1], __fmul_rn(w[b], v[b].y));
+          total[2] = __fadd_rn(total[2], __fmul_rn(w[b], v[b].z));
+          total[3] = __fadd_rn(total[3], __fmul_rn(w[b], v[b].w));
+        }
+      }
+      const size_t o = static_cast<size_t>(row) * width + c;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        if (extra) total[i] = total[i] + fj::load_as_f32(extra, e_dt, o + i);
+        fj::store_from_f32(out, out_dt, o + i, total[i]);
+      }
+    }
+  }
+}
+
 }  // namespace
 
 // ---- the model ------------------------------------------------------------------------------------
@@ -325,6 +527,16 @@ struct fj_moe_model {
   float *down_ep = nullptr, *returned = nullptr;
   unsigned *ep_counts = nullptr;       // device: send counts [world] | receive counts [world]
   unsigned* ep_counts_host = nullptr;  // pinned copy of both
+  // direct exchange (peer stores; fj_moe_ep_connect): tables of every rank's buffers, this rank's flag words
+  bool ep_direct = false;
+  std::vector<void*> ep_opened;        // peer mappings to close
+  void** ep_tables = nullptr;          // device: [4][world] pointers (rows | experts | flags | per-route results)
+  unsigned long long* ep_flags = nullptr;  // device: [2 * world], written by the peers
+  unsigned* ep_state = nullptr;        // device: tickets [2] | wait_err [1] | pad [1] | stale counts [world]
+  unsigned* ep_live_host = nullptr;    // mapped pinned: rows received per layer in the previous step [layers], then wait_err copy [1]
+  unsigned* ep_live_dev = nullptr;     // the same memory as the device sees it
+  uint32_t ep_exchange = 0;            // exchanges done so far (all ranks count alike)
+  uint32_t ep_max_polls = 1u << 24;    // about ten seconds of polling before a wait gives up (fj_moe_ep_wait_polls)
   // grouped expert path (many routes): route plan and per-route f32 down projections
   void* route_plan = nullptr;
   float* down_routes = nullptr;
@@ -464,6 +676,18 @@ int32_t fj_moe_model_create(fj_backend* be, const fj_moe_config* config, const f
     m->returned = static_cast<float*>(dev_alloc(slots * H * 4));
     m->ep_counts = static_cast<unsigned*>(dev_alloc(2 * world * 4));
     if (cudaMallocHost(reinterpret_cast<void**>(&m->ep_counts_host), 2 * world * 4) != cudaSuccess) { cudaGetLastError(); ok = false; }
+    m->ep_flags = static_cast<unsigned long long*>(dev_alloc(2 * world * 8));
+    m->ep_state = static_cast<unsigned*>(dev_alloc((4 + world) * 4));
+    m->ep_tables = static_cast<void**>(dev_alloc(4 * world * sizeof(void*)));
+    if (ok) {
+      cudaMemsetAsync(m->ep_flags, 0, 2 * world * 8, be->stream);
+      cudaMemsetAsync(m->ep_state, 0, (4 + world) * 4, be->stream);
+      cudaMemsetAsync(m->recv_experts, 0xFF, slots * 4, be->stream);
+      const size_t words = static_cast<size_t>(c.layers) + 1;
+      if (cudaHostAlloc(reinterpret_cast<void**>(&m->ep_live_host), words * 4, cudaHostAllocMapped) != cudaSuccess ||
+          cudaHostGetDevicePointer(reinterpret_cast<void**>(&m->ep_live_dev), m->ep_live_host, 0) != cudaSuccess) { cudaGetLastError(); ok = false; }
+      else memset(m->ep_live_host, 0, words * 4);
+    }
     m->route_plan = dev_alloc(fj::route_plan_bytes(static_cast<unsigned>(slots), m->experts_local));
   } else {
     m->route_plan = dev_alloc(fj::route_plan_bytes(static_cast<unsigned>(R * K), c.experts));
@@ -477,6 +701,7 @@ int32_t fj_moe_model_create(fj_backend* be, const fj_moe_config* config, const f
   if (!ok || cudaStreamSynchronize(be->stream) != cudaSuccess) {
     for (void* p : m->owned) { cudaFree(p); }
     if (m->ep_counts_host) cudaFreeHost(m->ep_counts_host);
+    if (m->ep_live_host) cudaFreeHost(m->ep_live_host);
     delete m;
     return ok ? FJ_ALLOCATION_FAILED : FJ_INVALID_INPUT;
   }
@@ -489,10 +714,107 @@ void fj_moe_model_destroy(fj_moe_model* m) {
   std::lock_guard<std::mutex> lock(m->be->mutex);
   cudaSetDevice(m->be->device);
   cudaStreamSynchronize(m->be->stream);
+  for (void* p : m->ep_opened) cudaIpcCloseMemHandle(p);  // normally closed earlier by fj_moe_ep_disconnect, before any rank frees
   for (void* p : m->owned) cudaFree(p);
   for (cudaEvent_t e : m->phase_events) cudaEventDestroy(e);
   if (m->ep_counts_host) cudaFreeHost(m->ep_counts_host);
+  if (m->ep_live_host) cudaFreeHost(m->ep_live_host);
   delete m;
+}
+
+// ---- direct exchange: connecting the ranks of one node -------------------------------------------------
+// fj_moe_ep_export writes this rank's four buffer handles (4 x 64 bytes: received rows, received expert ids,
+// flag words, per-route results); the caller gathers every rank's 256 bytes in rank order (any host channel) and
+// hands the whole table to fj_moe_ep_connect, which maps the peers' buffers. Every rank then passes whether its
+// connect succeeded through the same channel and calls fj_moe_ep_direct(model, 1) only if all did: the choice
+// between this exchange and the NCCL one must be the same on all ranks. Before any rank destroys its model,
+// all call fj_moe_ep_disconnect and meet at a host barrier: a mapping must be closed before its owner frees.
+int32_t fj_moe_ep_export(fj_moe_model* m, uint8_t* out256) {
+  if (!m || !out256 || m->world < 2) return FJ_INVALID_INPUT;
+  std::lock_guard<std::mutex> lock(m->be->mutex);
+  cudaSetDevice(m->be->device);
+  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "handle size");
+  void* bufs[4] = {m->recv_rows, m->recv_experts, m->ep_flags, m->down_ep};
+  for (int i = 0; i < 4; ++i) {
+    cudaIpcMemHandle_t h;
+    if (cudaIpcGetMemHandle(&h, bufs[i]) != cudaSuccess) { cudaGetLastError(); return FJ_UNSUPPORTED_OPERATION; }
+    memcpy(out256 + 64 * i, &h, 64);
+  }
+  return FJ_OK;
+}
+
+int32_t fj_moe_ep_connect(fj_moe_model* m, const uint8_t* table /*[world][256]*/) {
+  if (!m || !table || m->world < 2 || m->world > 64 || !m->ep) return FJ_INVALID_INPUT;
+  std::lock_guard<std::mutex> lock(m->be->mutex);
+  cudaSetDevice(m->be->device);
+  if (!m->ep_opened.empty() || m->ep_direct) return FJ_INVALID_INPUT;
+  const uint32_t W = m->world, rank = m->ep->rank;
+  std::vector<void*> host(4 * static_cast<size_t>(W), nullptr);
+  void* own[4] = {m->recv_rows, m->recv_experts, m->ep_flags, m->down_ep};
+  for (uint32_t p = 0; p < W; ++p)
+    for (int i = 0; i < 4; ++i) {
+      if (p == rank) { host[static_cast<size_t>(i) * W + p] = own[i]; continue; }
+      cudaIpcMemHandle_t h;
+      memcpy(&h, table + 256 * static_cast<size_t>(p) + 64 * i, 64);
+      void* mapped = nullptr;
+      if (cudaIpcOpenMemHandle(&mapped, h, cudaIpcMemLazyEnablePeerAccess) != cudaSuccess) {
+        cudaGetLastError();
+        for (void* q : m->ep_opened) cudaIpcCloseMemHandle(q);
+        m->ep_opened.clear();
+        return FJ_UNSUPPORTED_OPERATION;
+      }
+      m->ep_opened.push_back(mapped);
+      host[static_cast<size_t>(i) * W + p] = mapped;
+    }
+  if (cudaMemcpyAsync(m->ep_tables, host.data(), host.size() * sizeof(void*), cudaMemcpyHostToDevice, m->be->stream) != cudaSuccess ||
+      cudaStreamSynchronize(m->be->stream) != cudaSuccess) { cudaGetLastError(); return FJ_DEVICE_EXECUTION_FAILED; }
+  return FJ_OK;
+}
+
+int32_t fj_moe_ep_direct(fj_moe_model* m, uint32_t enabled) {
+  if (!m || m->world < 2) return FJ_INVALID_INPUT;
+  std::lock_guard<std::mutex> lock(m->be->mutex);
+  if (enabled && m->ep_opened.size() != 4 * static_cast<size_t>(m->world - 1)) return FJ_INVALID_INPUT;
+  m->ep_direct = enabled != 0;
+  return FJ_OK;
+}
+
+int32_t fj_moe_ep_disconnect(fj_moe_model* m) {
+  if (!m) return FJ_INVALID_INPUT;
+  std::lock_guard<std::mutex> lock(m->be->mutex);
+  cudaSetDevice(m->be->device);
+  cudaStreamSynchronize(m->be->stream);
+  m->ep_direct = false;
+  for (void* p : m->ep_opened) cudaIpcCloseMemHandle(p);
+  m->ep_opened.clear();
+  return FJ_OK;
+}
+
+// Bound of the device-side waits of the direct exchange, in polls (about half a microsecond each).
+int32_t fj_moe_ep_wait_polls(fj_moe_model* m, uint32_t polls) {
+  if (!m || polls == 0) return FJ_INVALID_INPUT;
+  m->ep_max_polls = polls;
+  return FJ_OK;
+}
+
+// Self-test of the bounded wait (no peer involved): waits on a flag that nothing sets, with `polls` polls,
+// and answers FJ_TIMEOUT when the kernel gave up and reported it, FJ_OK if it did not. The context stays usable.
+int32_t fj_ep_wait_selftest(fj_backend* be, uint32_t polls) {
+  if (!be || polls == 0) return FJ_INVALID_INPUT;
+  std::lock_guard<std::mutex> lock(be->mutex);
+  cudaSetDevice(be->device);
+  void* mem = nullptr;
+  if (cudaMalloc(&mem, 64) != cudaSuccess) { cudaGetLastError(); return FJ_ALLOCATION_FAILED; }
+  cudaMemsetAsync(mem, 0, 64, be->stream);
+  unsigned long long* flag = static_cast<unsigned long long*>(mem);
+  unsigned* err = reinterpret_cast<unsigned*>(flag + 2);
+  ep_wait_kernel<<<1, 64, 0, be->stream>>>(flag, 1, 7, 1, nullptr, nullptr, nullptr, nullptr, err, polls);
+  unsigned host_err = 0;
+  cudaMemcpyAsync(&host_err, err, 4, cudaMemcpyDeviceToHost, be->stream);
+  const cudaError_t e = cudaStreamSynchronize(be->stream);
+  cudaFree(mem);
+  if (e != cudaSuccess) { cudaGetLastError(); return FJ_DEVICE_EXECUTION_FAILED; }
+  return host_err == 7 ? FJ_TIMEOUT : FJ_OK;
 }
 
 int32_t fj_moe_phase_timing(fj_moe_model* m, uint32_t enabled) {
@@ -680,14 +1002,15 @@ extern "C" int32_t fj_moe_step(fj_moe_model* m, const uint32_t* token_ids, uint3
     const unsigned kGroupedRoutes = c.grouped_min_routes ? c.grouped_min_routes : 64;
     const unsigned kStreamRows = c.stream_rows_per_expert ? c.stream_rows_per_expert : 72;
     // `live`: how many of the n_routes ids are expected to be valid (a padded exchange carries whole slabs)
-    auto bucketed = [&](const void* x, unsigned src_div, const unsigned* ids, unsigned n_routes, unsigned live, unsigned n_experts, void* act, void* down_out, bool down_bf16) -> bool {
+    auto bucketed = [&](const void* x, unsigned src_div, const unsigned* ids, unsigned n_routes, unsigned live, unsigned n_experts, void* act, void* down_out, bool down_bf16,
+                        const unsigned* slab_counts = nullptr, unsigned slab_cap = 0) -> bool {
       if (live < kGroupedRoutes || G != 64) return false;
       const bool stream = live < static_cast<uint64_t>(kStreamRows) * n_experts &&
                           fj::expert_stream_supported(H, I, 4, G, n_experts, x, L.gate.packed, L.gate.scales, L.gate.biases) &&
                           fj::expert_stream_supported(H, I, 4, G, n_experts, x, L.up.packed, L.up.scales, L.up.biases) &&
                           fj::expert_stream_supported(I, H, 4, G, n_experts, act, L.down.packed, L.down.scales, L.down.biases);
       if (stream) {
-        fj::launch_route_plan(ctx, ids, n_routes, n_experts, m->route_plan, nullptr, 16);
+        fj::launch_route_plan(ctx, ids, n_routes, n_experts, m->route_plan, nullptr, 16, slab_counts, slab_cap);
         if (!fj::launch_expert_stream_pair(ctx, x, L.gate.packed, L.gate.scales, L.gate.biases, L.up.packed, L.up.scales, L.up.biases, m->route_plan, n_routes, n_experts, src_div, act, H,
                                            I, live) ||
             !fj::launch_expert_stream_single(ctx, act, L.down.packed, L.down.scales, L.down.biases, m->route_plan, n_routes, n_experts, 1, down_out, down_bf16, I, H, live))
@@ -696,7 +1019,7 @@ extern "C" int32_t fj_moe_step(fj_moe_model* m, const uint32_t* token_ids, uint3
       }
       if (!fj::grouped_q4_supported(H, I, 4, G, n_experts, x, L.gate.packed) || !fj::grouped_q4_supported(I, H, 4, G, n_experts, act, L.down.packed)) return false;
       const unsigned tile_rows = fj::grouped_tile_rows(live, n_experts);
-      fj::launch_route_plan(ctx, ids, n_routes, n_experts, m->route_plan, nullptr, tile_rows);
+      fj::launch_route_plan(ctx, ids, n_routes, n_experts, m->route_plan, nullptr, tile_rows, slab_counts, slab_cap);
       fj::launch_grouped_q4_pair(ctx, x, L.gate.packed, L.gate.scales, L.gate.biases, L.up.packed, L.up.scales, L.up.biases, m->route_plan, n_routes, n_experts, src_div, act, H, I,
                                  tile_rows);
       fj::launch_grouped_q4_single(ctx, act, L.down.packed, L.down.scales, L.down.biases, m->route_plan, n_routes, n_experts, 1, down_out, down_bf16, I, H, tile_rows);
@@ -714,6 +1037,44 @@ extern "C" int32_t fj_moe_step(fj_moe_model* m, const uint32_t* token_ids, uint3
                                        c.experts, I, K, 4, G, 1, nullptr);
         fj::launch_gather_quant_weighted_sum(ctx, m->act, dt, L.down.packed, L.down.scales, L.down.biases, dt, m->route_experts, m->route_weights, FJ_F32, hidden, dt, other, dt, rows, K,
                                              I, c.experts, H, 4, G, 2, nullptr);
+      }
+    } else if (m->ep_direct) {
+      // Direct exchange: peer stores and flags instead of NCCL, no host round trip (kernels above).
+      const unsigned cap = m->capacity, routes = rows * K, W = m->world, rank = m->ep->rank;
+      const bool ret_bf16 = c.ep_return_bf16 != 0;
+      const int ret_dt = ret_bf16 ? FJ_BF16 : FJ_F32;
+      const unsigned exchange = ++m->ep_exchange;
+      void** t = m->ep_tables;
+      const EpPeers peers{reinterpret_cast<unsigned short* const*>(t), reinterpret_cast<unsigned* const*>(t + W), reinterpret_cast<unsigned long long* const*>(t + 2 * W),
+                          reinterpret_cast<const unsigned char* const*>(t + 3 * W)};
+      unsigned *tickets = m->ep_state, *wait_err = m->ep_state + 2, *stale = m->ep_state + 4, *recv_counts = m->ep_counts + W;
+      ep_push_dispatch_kernel<<<std::max(1u, std::min((routes + 7) / 8, 4u * static_cast<unsigned>(ctx.sm_count > 0 ? ctx.sm_count : 148))), 256, 0, be->stream>>>(static_cast<const unsigned short*>(m->normed), m->route_experts, routes, K, H, cap, rank, W,
+                                                                                          m->experts_local, peers, m->route_slot, m->ep_counts, tickets, exchange);
+      ep_wait_kernel<<<1, 128, 0, be->stream>>>(m->ep_flags, W, exchange, cap, recv_counts, stale, m->recv_experts, m->ep_live_dev + l, wait_err, m->ep_max_polls);
+      ctx.launches += 2;
+      mark(2);
+      // how many rows arrive is known on the device only; the kernels are chosen from what this layer received in the previous step
+      const unsigned seen_before = m->ep_live_host[l];
+      unsigned live = seen_before ? seen_before : std::max(routes, 1u);
+      if (c.grouped_min_routes == 0) live = std::max(live, kGroupedRoutes);  // slabs are mostly empty: the bucketed kernels skip what the per-route ones would visit
+      if (!bucketed(m->recv_rows, 1, m->recv_experts, W * cap, live, m->experts_local, m->act_ep, m->down_ep, ret_bf16, recv_counts, cap)) {
+        fj::launch_gather_quant_matmul(ctx, m->recv_rows, dt, L.gate.packed, L.gate.scales, L.gate.biases, dt, L.up.packed, L.up.scales, L.up.biases, m->recv_experts, m->act_ep, dt,
+                                       W * cap, H, m->experts_local, I, 1, 4, G, 1, nullptr);
+        fj::launch_gather_quant_matmul(ctx, m->act_ep, dt, L.down.packed, L.down.scales, L.down.biases, dt, nullptr, nullptr, nullptr, m->recv_experts, m->down_ep, ret_dt, W * cap, I,
+                                       m->experts_local, H, 1, 4, G, 0, nullptr);
+      }
+      if (status != FJ_OK) break;
+      mark(3);
+      // "my results are ready" to every peer, then wait for theirs; the combine reads the rows where they are
+      ep_wait_kernel<<<1, 128, 0, be->stream>>>(m->ep_flags + W, W, exchange, cap, nullptr, nullptr, nullptr, nullptr, wait_err, m->ep_max_polls, peers.flags, W + rank);
+      ctx.launches++;
+      if (rows) {
+        const unsigned grid = std::min(rows, 16u * static_cast<unsigned>(ctx.sm_count > 0 ? ctx.sm_count : 148));
+        if (ret_bf16)
+          ep_pull_combine_kernel<true><<<grid, 256, 0, be->stream>>>(peers.results, m->route_slot, m->route_weights, hidden, dt, other, dt, rows, K, H, cap, rank);
+        else
+          ep_pull_combine_kernel<false><<<grid, 256, 0, be->stream>>>(peers.results, m->route_slot, m->route_weights, hidden, dt, other, dt, rows, K, H, cap, rank);
+        ctx.launches++;
       }
     } else {
       const unsigned cap = m->capacity, routes = rows * K, W = m->world;
@@ -793,9 +1154,14 @@ extern "C" int32_t fj_moe_step(fj_moe_model* m, const uint32_t* token_ids, uint3
   m->last_kernels = ctx.launches - launches_before;
   m->last_work_items = n_work;
   if (cudaGetLastError() != cudaSuccess) return FJ_DEVICE_EXECUTION_FAILED;
+  if (m->ep_direct) cudaMemcpyAsync(m->ep_live_host + c.layers, m->ep_state + 2, 4, cudaMemcpyDeviceToHost, be->stream);
   if (out_tokens && rows != 0) {
     cudaMemcpyAsync(out_tokens, m->tokens_out, static_cast<size_t>(lanes) * 4, cudaMemcpyDeviceToHost, be->stream);
-    if (m->ep) return ep_wait_stream(m->ep);  // the step's exchanges are still in flight: wait for them with the group's deadline
+    if (m->ep) {
+      const int32_t waited = ep_wait_stream(m->ep);  // the step's exchanges are still in flight: wait for them with the group's deadline
+      if (waited == FJ_OK && m->ep_direct && m->ep_live_host[c.layers] != 0) return FJ_TIMEOUT;  // a device-side wait of the direct exchange ran out
+      return waited;
+    }
     return cuda_status(cudaStreamSynchronize(be->stream));
   }
   return FJ_OK;

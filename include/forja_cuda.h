@@ -571,6 +571,29 @@ void fj_moe_model_destroy(fj_moe_model* model);
  * the group must call it for the same step, even with no active lane of its own (pack zero tokens). */
 int32_t fj_moe_step(fj_moe_model* model, const uint32_t* token_ids, uint32_t* out_tokens, uint64_t logits_out);
 int32_t fj_moe_step_stats(fj_moe_model* model, uint64_t* kernels, uint64_t* attn_work_items);
+/* Direct exchange between the ranks of one node (no counterpart in the single-GPU reference): instead of NCCL sends and
+ * receives with a host round trip for the row counts, every rank maps four of the others' buffers (CUDA IPC). A layer's
+ * dispatch is plain peer stores over NVLink by the kernel that assigns the slots, followed by one flag per (source,
+ * destination) carrying the row count, which the receiver polls in its own memory with a bound; on the way back the owner
+ * only publishes "results ready" and the origin's combine reads the per-route rows from the owner's memory. Nothing is
+ * staged, no multicast is used. Results are bit-identical to the NCCL exchange and to one GPU (same slots, same arithmetic).
+ *   fj_moe_ep_export     writes this rank's 4 x 64-byte buffer handles to out256.
+ *   fj_moe_ep_connect    takes every rank's 256 bytes in rank order ([world][256]; gathered by the caller over any host
+ *                        channel) and maps the peers' buffers; FJ_UNSUPPORTED_OPERATION when a mapping is refused.
+ *   fj_moe_ep_direct     switches the model's steps to this exchange (1) or back to NCCL (0). All ranks must choose alike:
+ *                        enable only after every rank reported a successful connect.
+ *   fj_moe_ep_disconnect unmaps the peers' buffers. Every rank calls it and then meets the others at a host barrier before
+ *                        any of them destroys its model: a mapping has to be closed before its owner frees the memory.
+ *   fj_moe_ep_wait_polls bound of the device-side waits in polls (default 2^24, about ten seconds). A wait that runs out
+ *                        makes the step compute on zero rows, fj_moe_step answer FJ_TIMEOUT from then on, and leaves the
+ *                        context usable; the model has to be rebuilt.
+ *   fj_ep_wait_selftest  runs that wait on a flag nothing sets and returns FJ_TIMEOUT when the kernel gave up and said so. */
+int32_t fj_moe_ep_export(fj_moe_model* model, uint8_t* out256);
+int32_t fj_moe_ep_connect(fj_moe_model* model, const uint8_t* table);
+int32_t fj_moe_ep_direct(fj_moe_model* model, uint32_t enabled);
+int32_t fj_moe_ep_disconnect(fj_moe_model* model);
+int32_t fj_moe_ep_wait_polls(fj_moe_model* model, uint32_t polls);
+int32_t fj_ep_wait_selftest(fj_backend* be, uint32_t polls);
 /* Measurement aid: while enabled, every layer of a step records CUDA events around its four phases; fj_moe_read_phase_ms
  * waits for the step and returns the time summed over the layers: [0] attention block and router, [1] dispatch (slot plan,
  * row scatter, exchange to the experts' owners; ~0 on one GPU), [2] expert projections, [3] exchange back and weighted combine. */

@@ -46,17 +46,28 @@ def main():
     rng = np.random.default_rng(100 + rank)
     ids = [rng.integers(0, CFG["vocab"], n).astype(np.uint32) for n in prompts]
 
+    def gather(obj):
+        out = [None] * world
+        dist.all_gather_object(out, obj)
+        return out
+
     for max_rows in (64, 300):  # slab capacity 256 (padded exchange, no host round trip) and 1200 (row counts exchanged first)
         run_case(be, ep, rank, dict(CFG, max_rows=max_rows), weights, local, prompts, steps, page, lanes, table_pages, physical, ids)
     # rows returned as bf16: half the bytes on the way back, logits within the bf16 bound instead of bit-identical
     run_case(be, ep, rank, dict(CFG, max_rows=300, ep_return_bf16=1), weights, local, prompts, steps, page, lanes, table_pages, physical, ids, exact=False)
+    # the direct exchange (peer stores over NVLink and flags instead of NCCL): the same three cases, then one with the
+    # bucketed expert kernels reading the slabs through the per-source row counts
+    for max_rows in (64, 300):
+        run_case(be, ep, rank, dict(CFG, max_rows=max_rows), weights, local, prompts, steps, page, lanes, table_pages, physical, ids, gather=gather)
+    run_case(be, ep, rank, dict(CFG, max_rows=300, ep_return_bf16=1), weights, local, prompts, steps, page, lanes, table_pages, physical, ids, exact=False, gather=gather)
+    run_case(be, ep, rank, dict(CFG, max_rows=300, grouped_min_routes=0), weights, local, prompts, steps, page, lanes, table_pages, physical, ids, exact=False, gather=gather)
     dist.barrier()
     ep.close()
     dist.destroy_process_group()
     print("EP_OK", rank)
 
 
-def run_case(be, ep, rank, cfg, weights, local, prompts, steps, page, lanes, table_pages, physical, ids, exact=True):
+def run_case(be, ep, rank, cfg, weights, local, prompts, steps, page, lanes, table_pages, physical, ids, exact=True, gather=None):
     def build(w, group):
         pool = fb.KvPool(be, page, physical, lanes, table_pages)
         assert all(s == 0 for s in pool.reserve(list(range(lanes)), [n + steps + 1 for n in prompts]))
@@ -65,6 +76,9 @@ def run_case(be, ep, rank, cfg, weights, local, prompts, steps, page, lanes, tab
 
     pool_ep, model_ep = build(local, ep)
     pool_one, model_one = build(weights, None)
+    if gather is not None:
+        assert model_ep.connect_peers(gather), f"rank {rank}: the peers' buffers could not be mapped"
+        model_ep.set_wait_polls(1 << 23)  # a few seconds: the other rank also runs its single-GPU twin between steps
     logits_ep, logits_one = be.alloc(fb.BF16, (lanes, cfg["vocab"])), be.alloc(fb.BF16, (lanes, cfg["vocab"]))
 
     def both(starts, counts, tokens):

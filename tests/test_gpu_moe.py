@@ -116,6 +116,15 @@ def test_moe_step_matches_oracle(cfg, prompts, steps):
     pool.close()
 
 
+def test_device_wait_of_the_direct_exchange_gives_up_and_reports():
+    """The receiver of the direct exchange polls a flag in its own memory with a bound. Here nothing ever sets the flag:
+    the kernel has to return by itself, report the exchange number it waited for, and leave the context usable."""
+    be = backend()
+    assert be._lib.fj_ep_wait_selftest(be._h, 3000) == fb.backend.TIMEOUT
+    x = be.tensor_from(np.arange(8, dtype=np.float32), fb.F32)
+    assert be.read(x).tolist() == list(range(8))
+
+
 def test_expert_parallel_step_equals_single_gpu_bits():
     """Two ranks, one GPU each, experts split in half: every rank's logits must equal, bit for bit,
     what one GPU computes for the same lanes (each route runs the same arithmetic either way)."""
