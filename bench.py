@@ -398,7 +398,8 @@ def run_native(args):
 
 def moe_ep(args, rank, world, local, dist):
     """The sharded sparse-MoE step (Qwen3-30B-A3B shape) beside the headline: 256 lanes in total, experts sharded over
-    the ranks with an NCCL all-to-all per MoE layer (fj_ep_* / fj_moe_step), so that the scaling run carries its
+    the ranks and the rows exchanged per MoE layer by peer stores and loads over NVLink (fj_moe_ep_* / fj_moe_step; NCCL
+    send/recv with --moe-nccl), so that the scaling run carries its
     1/2/4/8-GPU numbers. Every rank takes part; the block reports whole-job tokens per second (maximum over ranks of the
     device time) and the step's phases."""
     from forja_b200 import benchmarks

@@ -68,7 +68,7 @@ class FjQuantWeight(C.Structure):
 
 class FjMoeConfig(C.Structure):
     _fields_ = [(n, C.c_uint32) for n in ("layers", "hidden", "q_heads", "kv_heads", "head_dim", "experts", "top_k", "expert_intermediate", "vocab",
-                                          "group_size", "router_bits")] + [("eps", C.c_float), ("theta", C.c_float), ("max_rows", C.c_uint32), ("grouped_min_routes", C.c_uint32), ("stream_rows_per_expert", C.c_uint32), ("ep_return_bf16", C.c_uint32)]
+                                          "group_size", "router_bits")] + [("eps", C.c_float), ("theta", C.c_float), ("max_rows", C.c_uint32), ("grouped_min_routes", C.c_uint32), ("stream_rows_per_expert", C.c_uint32), ("ep_return_bf16", C.c_uint32), ("ep_chunks", C.c_uint32)]
 
 
 class FjMoeLayerWeights(C.Structure):
@@ -95,7 +95,7 @@ EXPORTS = [
     "fj_safetensors_file_len", "fj_safetensors_data_start", "fj_safetensors_tensor", "fj_safetensors_find", "fj_weights_last_error",
     "fj_safetensors_import", "fj_safetensors_view", "fj_safetensors_quant_views",
     "fj_prompt_chunk_work", "fj_prompt_chunk_merged_work", "fj_reservations_fit", "fj_prefill_plan",
-    "fj_ep_load", "fj_ep_unique_id", "fj_ep_create", "fj_ep_destroy", "fj_ep_all_to_all", "fj_ep_set_timeout", "fj_ep_poll_selftest", "fj_moe_ep_export", "fj_moe_ep_connect", "fj_moe_ep_direct", "fj_moe_ep_disconnect", "fj_moe_ep_wait_polls",
+    "fj_ep_load", "fj_ep_unique_id", "fj_ep_create", "fj_ep_destroy", "fj_ep_all_to_all", "fj_ep_set_timeout", "fj_ep_poll_selftest", "fj_moe_ep_export", "fj_moe_ep_connect", "fj_moe_ep_direct", "fj_moe_ep_disconnect", "fj_moe_ep_wait_polls", "fj_moe_ep_return_mode", "fj_moe_ep_received", "fj_moe_uniform_routing",
     "fj_ep_wait_selftest", "fj_moe_model_create", "fj_moe_model_destroy",
     "fj_moe_step", "fj_moe_step_stats", "fj_fill_random", "fj_tcgen05_wait_giveups", "fj_moe_capture_routes", "fj_moe_read_routes", "fj_moe_phase_timing", "fj_moe_read_phase_ms",
 ]
@@ -120,6 +120,11 @@ def load():
                 raise RuntimeError(f"{path} is missing and FORJA_B200_NO_BUILD is set")
         else:
             _build.build()
+    # Kernels are loaded when the context is created, not at their first launch: a first launch that has to load its module
+    # synchronises the whole device, and with two streams of one GPU in flight (two micro-batches of an expert-parallel model)
+    # that load would wait for the other stream's bounded wait on a peer, which in turn waits for this rank. The setting only
+    # takes effect if CUDA has not been initialised in this process yet.
+    os.environ.setdefault("CUDA_MODULE_LOADING", "EAGER")
     lib = C.CDLL(path)
     for name in EXPORTS:
         getattr(lib, name)
@@ -175,7 +180,7 @@ def load():
         "fj_reservations_fit": ([U32, U32, P, U64], I32), "fj_prefill_plan": ([U32, U32, U32, P, U64], U64),
         "fj_ep_load": ([C.c_char_p], I32), "fj_ep_unique_id": ([P], I32), "fj_ep_create": ([P, P, U32, U32, P], I32), "fj_ep_destroy": ([P], None),
         "fj_ep_all_to_all": ([P, U64, U64, U64], I32), "fj_ep_set_timeout": ([P, U64], I32), "fj_ep_poll_selftest": ([U64, U64, U64, P], I32), "fj_moe_ep_export": ([P, P], I32), "fj_moe_ep_connect": ([P, P], I32), "fj_moe_ep_direct": ([P, U32], I32),
-        "fj_moe_ep_disconnect": ([P], I32), "fj_moe_ep_wait_polls": ([P, U32], I32), "fj_ep_wait_selftest": ([P, U32], I32), "fj_moe_model_create": ([P, P, P, U64, P, P, P, P, P], I32),
+        "fj_moe_ep_disconnect": ([P], I32), "fj_moe_ep_wait_polls": ([P, U32], I32), "fj_moe_ep_return_mode": ([P, U32], I32), "fj_moe_ep_received": ([P, P, U32], I32), "fj_moe_uniform_routing": ([P, U32], I32), "fj_ep_wait_selftest": ([P, U32], I32), "fj_moe_model_create": ([P, P, P, U64, P, P, P, P, P], I32),
         "fj_moe_model_destroy": ([P], None), "fj_moe_step": ([P, P, P, U64], I32), "fj_moe_step_stats": ([P, P, P], I32),
         "fj_fill_random": ([P, U64, U64, U64, U32, U64, C.c_float, C.c_float], I32), "fj_tcgen05_wait_giveups": ([P, P], I32), "fj_moe_capture_routes": ([P, U32], I32), "fj_moe_read_routes": ([P, U32, U32, P, P], I32), "fj_moe_phase_timing": ([P, U32], I32), "fj_moe_read_phase_ms": ([P, P], I32),
     }

@@ -708,11 +708,11 @@ class MoeModel:
         round trip; fj_moe_ep_*). ``all_gather(obj) -> list`` returns every rank's object in rank order (e.g.
         torch.distributed.all_gather_object); it is called three times here and once more by close(). Returns whether
         the direct exchange is in use: every rank must have mapped every peer, otherwise all stay on NCCL."""
-        mine = (C.c_uint8 * 256)()
+        mine = (C.c_uint8 * 320)()
         status = self._lib.fj_moe_ep_export(self._h, mine)
         table = all_gather(bytes(mine) if status == 0 else None)
-        if status == 0 and all(t is not None and len(t) == 256 for t in table):
-            status = self._lib.fj_moe_ep_connect(self._h, (C.c_uint8 * (256 * len(table))).from_buffer_copy(b"".join(table)))
+        if status == 0 and all(t is not None and len(t) == 320 for t in table):
+            status = self._lib.fj_moe_ep_connect(self._h, (C.c_uint8 * (320 * len(table))).from_buffer_copy(b"".join(table)))
         else:
             status = status or 1
         self._peer_gather = all_gather
@@ -724,6 +724,21 @@ class MoeModel:
 
     def set_wait_polls(self, polls: int):
         _check(self._lib.fj_moe_ep_wait_polls(self._h, polls))
+
+    def uniform_routing(self, enabled: bool):
+        """Measurement aid: replace the router's choice by an even spread over the experts (fj_moe_uniform_routing)."""
+        _check(self._lib.fj_moe_uniform_routing(self._h, int(enabled)))
+
+    def received_rows(self) -> np.ndarray:
+        """Direct exchange: rows this rank received for its experts in the last step, [layers, chunks]."""
+        chunks = max(1, int(self.config.get("ep_chunks", 0) or 1))
+        out = np.zeros(self.config["layers"] * chunks, np.uint32)
+        _check(self._lib.fj_moe_ep_received(self._h, out.ctypes.data_as(C.c_void_p), out.size))
+        return out.reshape(self.config["layers"], chunks)
+
+    def set_return_mode(self, mode: int):
+        """Direct exchange: 0 or 1 = the origin reads the results from the owner (default), 2 = the owner writes them."""
+        _check(self._lib.fj_moe_ep_return_mode(self._h, mode))
 
     def close(self):
         if getattr(self, "_h", None) and getattr(self.backend, "_h", None):

@@ -138,7 +138,8 @@ def run_moe(args):
     cfg["grouped_min_routes"] = args.grouped_min_routes
     cfg["stream_rows_per_expert"] = args.stream_rows_per_expert
     cfg["ep_return_bf16"] = int(args.ep_bf16_return)
-    if R > 1 and world > 1 and cfg["max_rows"] * cfg["top_k"] <= 1024:
+    cfg["ep_chunks"] = args.ep_chunks
+    if R > 1 and world > 1 and args.nccl and cfg["max_rows"] * cfg["top_k"] <= 1024:
         # Small steps exchange padded slabs without a host round trip, so each thread queues dozens of NCCL groups ahead; with two
         # communicators per GPU issued in whatever order the threads happen to run, such a run stopped making progress on 8 GPUs
         # (ended by its timeout). The exchange with a host round trip per layer keeps one group per communicator in flight.
@@ -149,6 +150,12 @@ def run_moe(args):
         dist.broadcast_object_list(box, src=0)
         return box[0]
 
+    def gather(obj):
+        out = [None] * world
+        dist.all_gather_object(out, obj)
+        return out
+
+    direct = False
     table_pages = (args.prompt_max + 256 + 1 + PAGE - 1) // PAGE + 1
     parts = []
     for r in range(R):  # built one after the other: the rendezvous of every expert-parallel group goes through the same gloo group
@@ -156,6 +163,11 @@ def run_moe(args):
         ep = fb.ExpertParallel(be, rank, world, exchange) if world > 1 else None
         pool = fb.KvPool(be, PAGE, lanes * table_pages + 8, lanes, table_pages)
         model = build_moe(be, pool, cfg, ep, rank, world)
+        if world > 1 and not args.nccl:
+            direct = model.connect_peers(gather)
+            model.set_return_mode(args.ep_return_mode)
+        if args.uniform_routing:
+            model.uniform_routing(True)
         state = MoeLanes(pool, lanes, args.seed + rank * R + r, budget, args.prefill_limit, (args.prompt_min, args.prompt_max), args.decode_only)
         parts.append({"be": be, "ep": ep, "pool": pool, "model": model, "state": state, "rng": np.random.default_rng(args.seed + 77 + rank * R + r)})
     gate = threading.Barrier(R)
@@ -192,6 +204,8 @@ def run_moe(args):
                 processed += rows
             be.timer_record(t1)
             be.synchronize()
+            if args.phases and direct:
+                print(json.dumps({"rank": rank, "micro_batch": i, "rows_received_per_layer_last_step": model.received_rows().sum(axis=1).tolist()}), flush=True)
             results[i] = (be.timer_elapsed_ns(t0, t1) * 1e-9, processed, kernels, phase_ms)
         except BaseException as error:  # noqa: BLE001 - reported by the main thread
             failures.append(error)
@@ -228,7 +242,8 @@ def run_moe(args):
             "config": {"workload": "qwen3-30b-a3b-arch q4 sparse-MoE continuous batching" + (" (decode only)" if args.decode_only else " (chunked prefill + decode)"),
                        "lanes_total": args.lanes, "lanes_per_gpu": lanes * R, "micro_batches_per_gpu": R, "layers": cfg["layers"], "prompt_tokens": [args.prompt_min, args.prompt_max],
                        "prompt_budget_per_gpu_step": 0 if args.decode_only else budget * R,
-                       "parallelism": ("experts sharded over %d GPUs, NCCL send/recv all-to-all per MoE layer (rows return as %s); lanes data-parallel" % (world, "bf16" if args.ep_bf16_return else "f32")) if world > 1 else "single GPU"}}))
+                       "parallelism": ("experts sharded over %d GPUs, %s per MoE layer (rows return as %s); lanes data-parallel" % (
+                           world, "peer stores and loads over NVLink with flags" if direct else "NCCL send/recv all-to-all", "bf16" if args.ep_bf16_return else "f32")) if world > 1 else "single GPU"}}))
     for part in parts:
         part["model"].close()
         part["pool"].close()
@@ -300,6 +315,33 @@ def moe_ep_block(rank, world, local_rank, exchange, barrier, max_over_ranks, sum
     # the smallest value over the ranks: a rank that arrives early at an exchange waits there for the others, so the spread of
     # the two exchange phases is mostly the imbalance of the compute phases before them
     phases_min = {name: -max_over_ranks(-v / phase_steps) for name, v in zip(names, phase_ms)}
+    # how evenly the router of this random-weight model spreads the rows over the ranks: per layer, the busiest rank's
+    # received rows over the mean (every rank waits for the busiest one at that layer's return)
+    imbalance = None
+    if direct:
+        mine = model.received_rows().sum(axis=1).astype(np.float64)
+        busiest = np.array([max_over_ranks(float(v)) for v in mine])
+        mean = np.array([sum_over_ranks(float(v)) for v in mine]) / world
+        ratio = busiest / np.maximum(mean, 1.0)
+        imbalance = {"mean": float(ratio.mean()), "max": float(ratio.max())}
+    # the same steps with the router's choice replaced by an even spread over the experts (what a trained, load-balanced
+    # router approximates): separates the cost of the exchange from the cost of waiting for the busiest rank
+    model.uniform_routing(True)
+    for _ in range(2):
+        one_step()
+    be.synchronize()
+    barrier()
+    be.timer_record(t0)
+    even_rows = 0
+    for _ in range(steps):
+        rows, _ = one_step()
+        even_rows += rows
+    be.timer_record(t1)
+    be.synchronize()
+    barrier()
+    even_elapsed = max_over_ranks(be.timer_elapsed_ns(t0, t1) * 1e-9)
+    even_total = sum_over_ranks(float(even_rows))
+    model.uniform_routing(False)
     rows_per_step = total / steps / world
     remote = (world - 1) / world
     block = {
@@ -309,9 +351,12 @@ def moe_ep_block(rank, world, local_rank, exchange, barrier, max_over_ranks, sum
         "phase_ms_per_step_max_over_ranks": phases, "phase_ms_per_step_min_over_ranks": phases_min,
         "exchange_mb_per_layer_and_gpu": {"dispatch_bf16": rows_per_step * cfg["top_k"] * remote * cfg["hidden"] * 2 / 1e6,
                                           "return_f32": rows_per_step * cfg["top_k"] * remote * cfg["hidden"] * 4 / 1e6},
+        "rows_received_busiest_rank_over_mean_per_layer": imbalance,
+        "with_even_routing": {"tok_s": even_total / even_elapsed, "ms_per_step": even_elapsed / steps * 1e3,
+                              "what": "router's choice replaced by an even spread over the experts (fj_moe_uniform_routing); not the headline"},
         "gpu_launches": int(sum_over_ranks(float(kernels))),
         "parallelism": ("experts sharded over %d GPUs, %s per MoE layer, lanes data-parallel" %
-                        (world, "rows stored straight into the owner's memory over NVLink by the producing kernels, flags instead of a host round trip" if direct
+                        (world, "rows stored straight into the owner's memory over NVLink by the dispatching kernel, results read from the owner's memory by the combine, flags instead of a host round trip" if direct
                          else "NCCL send/recv all-to-all")) if world > 1 else "single GPU",
     }
     model.close()
@@ -476,6 +521,10 @@ def main():
     moe.add_argument("--prefill-limit", type=int, default=4)
     moe.add_argument("--decode-only", action="store_true")
     moe.add_argument("--ep-bf16-return", action="store_true", help="expert parallelism: per-route rows come back as bf16 instead of f32")
+    moe.add_argument("--ep-chunks", type=int, default=1, help="direct exchange: chunks per layer that overlap their transfers with each other's expert work")
+    moe.add_argument("--ep-return-mode", type=int, default=0, help="direct exchange: 0 or 1 = origins read the results, 2 = owners write them")
+    moe.add_argument("--uniform-routing", action="store_true", help="measurement aid: spread every row's experts evenly instead of using the (random-weight) router's choice")
+    moe.add_argument("--nccl", action="store_true", help="expert parallelism through NCCL send/recv instead of the direct exchange over NVLink")
     moe.add_argument("--micro-batches", type=int, default=1, help="independent continuous batches per GPU, stepped concurrently (each gets 1/R of the lanes and of the prompt budget)")
     moe.add_argument("--phases", action="store_true", help="also print the time of the timed steps split by phase (CUDA events inside the step)")
     moe.add_argument("--grouped-min-routes", type=int, default=0, help="0 = library default")

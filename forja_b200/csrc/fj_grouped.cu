@@ -32,11 +32,11 @@ namespace {
 constexpr int GT_BN = 64, GT_BK = 64;  // columns and k per tile step; rows per tile: 64 or 128 (template parameter)
 
 // One CTA: histogram of routes per expert, exclusive scan, arrange, tile list.
-// slab_counts != nullptr: the routes come in slabs of slab_cap entries of which only the first slab_counts[s] are in use
-// (rows received from peer s); the rest of each slab is not read.
+// slab_counts != nullptr: the routes come in slabs that start slab_cap entries apart; of slab s only the slab_counts[s]
+// entries (at most slab_limit) from slab_offset on are in use (the rows one chunk received from peer s); nothing else is read.
 __global__ void __launch_bounds__(1024) route_plan_kernel(const unsigned* __restrict__ indices, unsigned total, unsigned experts, unsigned* offsets /*[experts + 1]*/,
                                                           unsigned* sorted /*[total]*/, RouteTile* tiles, unsigned* n_tiles, unsigned tiles_cap, unsigned tile_rows, ErrorRecord* err,
-                                                          const unsigned* __restrict__ slab_counts, unsigned slab_cap) {
+                                                          const unsigned* __restrict__ slab_counts, unsigned slab_cap, unsigned slab_offset, unsigned slab_limit) {
   extern __shared__ unsigned plan_smem[];
   pdl_sync();
   unsigned* count = plan_smem;           // [experts]
@@ -45,9 +45,9 @@ __global__ void __launch_bounds__(1024) route_plan_kernel(const unsigned* __rest
   __syncthreads();
   const unsigned slabs = slab_counts ? total / slab_cap : 1u, slab_len = slab_counts ? slab_cap : total;
   for (unsigned s = 0; s < slabs; ++s) {
-    const unsigned used = slab_counts ? min(slab_counts[s], slab_cap) : total;
+    const unsigned used = slab_counts ? min(slab_counts[s], slab_limit) : total;
     for (unsigned i = threadIdx.x; i < used; i += blockDim.x) {
-      const unsigned e = indices[s * slab_len + i];
+      const unsigned e = indices[s * slab_len + slab_offset + i];
       if (e < experts) atomicAdd(&count[e], 1u);
       else report_error(err, ERR_INDEX, e);  // left out of every bucket; the lowest bad id is reported (lib.rs:1078-1088)
     }
@@ -69,9 +69,9 @@ __global__ void __launch_bounds__(1024) route_plan_kernel(const unsigned* __rest
   }
   __syncthreads();
   for (unsigned s = 0; s < slabs; ++s) {
-    const unsigned used = slab_counts ? min(slab_counts[s], slab_cap) : total;
+    const unsigned used = slab_counts ? min(slab_counts[s], slab_limit) : total;
     for (unsigned i = threadIdx.x; i < used; i += blockDim.x) {
-      const unsigned r = s * slab_len + i, e = indices[r];
+      const unsigned r = s * slab_len + slab_offset + i, e = indices[r];
       if (e < experts) sorted[atomicAdd(&cursor[e], 1u)] = r;
     }
   }
@@ -454,11 +454,12 @@ PlanLayout plan_layout(void* plan, unsigned total_routes, unsigned experts) {
 }  // namespace
 
 void launch_route_plan(Ctx& ctx, const unsigned* indices, unsigned total_routes, unsigned experts, void* plan, ErrorRecord* err, unsigned tile_rows, const unsigned* slab_counts,
-                       unsigned slab_cap) {
+                       unsigned slab_cap, unsigned slab_offset, unsigned slab_limit) {
   const PlanLayout l = plan_layout(plan, total_routes, experts);
-  if (slab_counts && (slab_cap == 0 || total_routes % slab_cap != 0)) slab_counts = nullptr;
+  if (slab_counts && (slab_cap == 0 || total_routes % slab_cap != 0 || slab_offset >= slab_cap)) slab_counts = nullptr;
+  if (slab_limit == 0 || slab_limit > slab_cap - slab_offset) slab_limit = slab_cap - slab_offset;
   launch_pdl(route_plan_kernel, dim3(1), dim3(1024), 2 * experts * sizeof(unsigned), ctx.stream, indices, total_routes, experts, l.offsets, l.sorted, l.tiles, l.n_tiles, l.tiles_cap,
-             tile_rows, err, slab_counts, slab_cap);
+             tile_rows, err, slab_counts, slab_cap, slab_counts ? slab_offset : 0u, slab_limit);
   ctx.launches++;
 }
 

@@ -210,7 +210,7 @@ void launch_gather_quant_weighted_sum(Ctx& ctx, const void* act, int a_dt, const
 // route_plan_bytes(total_routes, experts). Ids >= experts are left out of every bucket.
 size_t route_plan_bytes(unsigned total_routes, unsigned experts);
 void launch_route_plan(Ctx& ctx, const unsigned* indices, unsigned total_routes, unsigned experts, void* plan, ErrorRecord* err, unsigned tile_rows = 64,
-                       const unsigned* slab_counts = nullptr, unsigned slab_cap = 0);
+                       const unsigned* slab_counts = nullptr, unsigned slab_cap = 0, unsigned slab_offset = 0, unsigned slab_limit = 0);
 bool grouped_q4_supported(unsigned k, unsigned n, unsigned bits, unsigned group_size, unsigned experts, const void* x, const void* packed);
 // Rows per tile (64 or 128) the tile GEMMs should use for this many routes; pass it to launch_route_plan and to both launchers.
 unsigned grouped_tile_rows(unsigned total_routes, unsigned experts);

@@ -271,6 +271,20 @@ __global__ void router_sum_kernel(const float* __restrict__ halves /*[rows][2 * 
   }
 }
 
+// Measurement aid: replaces a step's routing by an even spread: row r of layer l takes top_k distinct experts
+// (start + j * stride) mod experts from a hash of (l, r), each with weight 1 / top_k.
+__global__ void route_uniform_kernel(unsigned* route_experts, float* route_weights, unsigned rows, unsigned top_k, unsigned experts, unsigned layer) {
+  const unsigned r = blockIdx.x * blockDim.x + threadIdx.x;
+  if (r >= rows) return;
+  unsigned h = (r + 1u) * 2654435761u ^ (layer + 1u) * 40503u;
+  h ^= h >> 15; h *= 2246822519u; h ^= h >> 13;
+  const unsigned start = h % experts, stride = experts > 1 ? 1u + 2u * ((h >> 8) % max(experts / 2, 1u)) : 0u;  // odd: no repeat within a power-of-two expert count
+  for (unsigned j = 0; j < top_k; ++j) {
+    route_experts[r * top_k + j] = static_cast<unsigned>((start + static_cast<unsigned long long>(j) * stride) % experts);
+    route_weights[r * top_k + j] = 1.0f / static_cast<float>(top_k);
+  }
+}
+
 // Copies each route's activation row (bf16, width % 8 == 0) into its slot, 16 bytes per thread step.
 __global__ void ep_scatter_rows_kernel(const unsigned short* __restrict__ normed, const unsigned* __restrict__ route_slot, unsigned routes, unsigned top_k,
                                        unsigned width, unsigned short* send_rows) {
@@ -297,6 +311,7 @@ struct EpPeers {
   unsigned* const* experts;           // [world] every rank's recv_experts
   unsigned long long* const* flags;   // [world] every rank's flag words: [world] dispatch | [world] return
   const unsigned char* const* results;  // [world] every rank's per-route results (down_ep), read by the origin's combine
+  unsigned char* const* returned;       // [world] every rank's `returned`, written by the owners when results are pushed
 };
 
 __device__ inline void st_release_sys(unsigned long long* p, unsigned long long v) { asm volatile("st.release.sys.global.u64 [%0], %1;\n" ::"l"(p), "l"(v) : "memory"); }
@@ -326,13 +341,17 @@ __device__ inline bool ep_last_block(unsigned* ticket) {
 // global counters see a few hundred atomics instead of one per route. Each route's activation row and local expert id then go
 // into slot (rank * capacity + slot) of the owner's buffers, one warp per row with eight 16-byte pieces in flight per lane;
 // finally flag[rank] of every peer = {exchange, rows sent to it}. Zeroes the send counters for the next layer.
-__global__ void __launch_bounds__(256) ep_push_dispatch_kernel(const unsigned short* __restrict__ normed, const unsigned* __restrict__ route_experts, unsigned routes, unsigned top_k,
-                                                               unsigned width, unsigned capacity, unsigned rank, unsigned world, unsigned experts_local, EpPeers peers,
-                                                               unsigned* route_slot, unsigned* send_counts, unsigned* ticket, unsigned exchange) {
+// A chunk covers routes [route_begin, route_end) and owns slots [chunk_base, chunk_base + chunk_capacity) of every slab, its own
+// counters, ticket and flag words (flag_base): chunks of one layer travel independently of each other.
+__global__ void __launch_bounds__(256) ep_push_dispatch_kernel(const unsigned short* __restrict__ normed, const unsigned* __restrict__ route_experts, unsigned route_begin,
+                                                               unsigned route_end, unsigned top_k, unsigned width, unsigned capacity, unsigned chunk_base, unsigned chunk_capacity,
+                                                               unsigned rank, unsigned world, unsigned experts_local, EpPeers peers, unsigned* route_slot, unsigned* send_counts,
+                                                               unsigned* ticket, unsigned flag_base, unsigned exchange) {
   __shared__ unsigned s_count[64], s_base[64], s_slot[256];
   const unsigned vecs = width / 8, lane = threadIdx.x & 31u, warp = threadIdx.x / 32, warps = blockDim.x / 32;
+  const unsigned routes = route_end - route_begin;
   const unsigned per_block = (routes + gridDim.x - 1) / gridDim.x;
-  const unsigned begin = min(routes, blockIdx.x * per_block), end = min(routes, begin + per_block);
+  const unsigned begin = route_begin + min(routes, blockIdx.x * per_block), end = min(route_end, begin + per_block);
   for (unsigned chunk = begin; chunk < end; chunk += blockDim.x) {
     if (threadIdx.x < 64) s_count[threadIdx.x] = 0;
     __syncthreads();
@@ -350,9 +369,9 @@ __global__ void __launch_bounds__(256) ep_push_dispatch_kernel(const unsigned sh
       unsigned slot = 0xFFFFFFFFu;  // bad expert id: contributes nothing
       if (dest < world) {
         const unsigned in = s_base[dest] + local;
-        if (in < capacity) {
-          slot = dest * capacity + in;
-          peers.experts[dest][rank * capacity + in] = expert - dest * experts_local;
+        if (in < chunk_capacity) {
+          slot = dest * capacity + chunk_base + in;
+          peers.experts[dest][rank * capacity + chunk_base + in] = expert - dest * experts_local;
         }
       }
       route_slot[r] = slot;
@@ -383,9 +402,9 @@ __global__ void __launch_bounds__(256) ep_push_dispatch_kernel(const unsigned sh
     __syncthreads();
   }
   if (ep_last_block(ticket) && threadIdx.x < world) {
-    const unsigned count = min(send_counts[threadIdx.x], capacity);
+    const unsigned count = min(send_counts[threadIdx.x], chunk_capacity);
     send_counts[threadIdx.x] = 0;
-    st_release_sys(peers.flags[threadIdx.x] + rank, (static_cast<unsigned long long>(exchange) << 32) | count);
+    st_release_sys(peers.flags[threadIdx.x] + flag_base + rank, (static_cast<unsigned long long>(exchange) << 32) | count);
   }
 }
 
@@ -394,8 +413,10 @@ __global__ void __launch_bounds__(256) ep_push_dispatch_kernel(const unsigned sh
 // computes on zero rows and the host answers FJ_TIMEOUT; the context stays usable.
 // signal_flags != nullptr: before waiting, publish {exchange, 0} in word signal_at of every peer's flags (the owner's "results
 // of this exchange are ready": everything earlier on the stream has completed and the fence orders it before the flag).
+// `capacity` bounds a count (the chunk's share of a slab); the chunk's ids of source s start at recv_experts[s * slab_stride].
 __global__ void ep_wait_kernel(const unsigned long long* flags, unsigned world, unsigned exchange, unsigned capacity, unsigned* counts_out, unsigned* stale_counts, unsigned* recv_experts,
-                               unsigned* live_total_host, unsigned* wait_err, unsigned max_polls, unsigned long long* const* signal_flags = nullptr, unsigned signal_at = 0) {
+                               unsigned* live_total_host, unsigned* wait_err, unsigned max_polls, unsigned long long* const* signal_flags = nullptr, unsigned signal_at = 0,
+                               unsigned slab_stride = 0) {
   __shared__ unsigned s_counts[64];
   const unsigned src = threadIdx.x;
   unsigned count = 0;
@@ -419,7 +440,7 @@ __global__ void ep_wait_kernel(const unsigned long long* flags, unsigned world, 
     // ids left over from an earlier, longer slab must not look valid to kernels that read the whole slab
     for (unsigned s = 0; s < world; ++s) {
       const unsigned now = s_counts[s], before = stale_counts[s];
-      for (unsigned i = now + threadIdx.x; i < before; i += blockDim.x) recv_experts[static_cast<size_t>(s) * capacity + i] = 0xFFFFFFFFu;
+      for (unsigned i = now + threadIdx.x; i < before; i += blockDim.x) recv_experts[static_cast<size_t>(s) * slab_stride + i] = 0xFFFFFFFFu;
     }
     __syncthreads();
     if (src < world) stale_counts[src] = count;
@@ -429,6 +450,41 @@ __global__ void ep_wait_kernel(const unsigned long long* flags, unsigned world, 
     for (unsigned s = 0; s < world; ++s) total += s_counts[s];
     *live_total_host = total;
   }
+}
+
+// Return by writing: the result row of slot (src * capacity + chunk_base + i), i < counts[src], goes to slot
+// (rank * capacity + chunk_base + i) of src's `returned`; then return-flag[rank] of every peer = {exchange, 0}. The alternative to
+// the reading combine below; it costs an extra pass over local memory on both sides and measured slower on 2 and on 8 GPUs
+// (57.7 against 54.8 ms and 71.3 against 68.2 ms per step of the sparse-MoE benchmark), so it is not the default.
+__global__ void ep_push_return_kernel(const unsigned char* __restrict__ results, unsigned row_bytes, unsigned capacity, unsigned chunk_base, unsigned chunk_capacity, unsigned rank,
+                                      unsigned world, const unsigned* __restrict__ counts, EpPeers peers, unsigned* ticket, unsigned flag_base, unsigned exchange) {
+  const unsigned vecs = row_bytes / 16, lane = threadIdx.x & 31u, warp = threadIdx.x / 32, warps = blockDim.x / 32;
+  unsigned most = 0;
+  for (unsigned src = 0; src < world; ++src) most = max(most, min(counts[src], chunk_capacity));
+  // consecutive warps write to consecutive destinations, starting behind this rank: at any moment every destination is being
+  // written by every source, instead of all sources converging on one destination after the other
+  for (unsigned item = blockIdx.x * warps + warp; item < most * world; item += gridDim.x * warps) {
+    const unsigned src = (rank + 1 + item % world) % world, i = item / world;
+    if (i >= min(counts[src], chunk_capacity)) continue;
+    {
+      const uint4* from = reinterpret_cast<const uint4*>(results + (static_cast<size_t>(src) * capacity + chunk_base + i) * row_bytes);
+      uint4* to = reinterpret_cast<uint4*>(peers.returned[src] + (static_cast<size_t>(rank) * capacity + chunk_base + i) * row_bytes);
+      for (unsigned base = 0; base < vecs; base += 256) {
+        uint4 v[8];
+#pragma unroll
+        for (unsigned u = 0; u < 8; ++u) {
+          const unsigned k = base + u * 32 + lane;
+          if (k < vecs) v[u] = from[k];
+        }
+#pragma unroll
+        for (unsigned u = 0; u < 8; ++u) {
+          const unsigned k = base + u * 32 + lane;
+          if (k < vecs) to[k] = v[u];
+        }
+      }
+    }
+  }
+  if (ep_last_block(ticket) && threadIdx.x < world) st_release_sys(peers.flags[threadIdx.x] + flag_base + rank, static_cast<unsigned long long>(exchange) << 32);
 }
 
 // Return by reading instead of writing: the owner only publishes "results of this exchange are ready" (ep_wait_kernel's
@@ -525,15 +581,20 @@ struct fj_moe_model {
   unsigned short *send_rows = nullptr, *recv_rows = nullptr, *act_ep = nullptr;
   unsigned *send_experts = nullptr, *recv_experts = nullptr, *route_slot = nullptr;
   float *down_ep = nullptr, *returned = nullptr;
-  unsigned *ep_counts = nullptr;       // device: send counts [world] | receive counts [world]
+  unsigned *ep_counts = nullptr;       // device: per chunk, send counts [world] | receive counts [world]
   unsigned* ep_counts_host = nullptr;  // pinned copy of both
   // direct exchange (peer stores; fj_moe_ep_connect): tables of every rank's buffers, this rank's flag words
   bool ep_direct = false;
   std::vector<void*> ep_opened;        // peer mappings to close
-  void** ep_tables = nullptr;          // device: [4][world] pointers (rows | experts | flags | per-route results)
-  unsigned long long* ep_flags = nullptr;  // device: [2 * world], written by the peers
-  unsigned* ep_state = nullptr;        // device: tickets [2] | wait_err [1] | pad [1] | stale counts [world]
-  unsigned* ep_live_host = nullptr;    // mapped pinned: rows received per layer in the previous step [layers], then wait_err copy [1]
+  void** ep_tables = nullptr;          // device: [5][world] pointers (rows | experts | flags | per-route results | returned)
+  unsigned long long* ep_flags = nullptr;  // device: [chunks][2 * world] (dispatch | return), written by the peers
+  unsigned* ep_state = nullptr;        // device: wait_err [1] | dispatch tickets [chunks] | return tickets [chunks] | stale counts [chunks][world]
+  uint32_t ep_return_mode = 0;         // 0 or 1 = the origin reads the results, 2 = the owner writes them
+  uint32_t ep_chunks = 1, ep_chunk_capacity = 0;  // chunks per layer and each chunk's share of a slab (capacity = chunks * share)
+  std::vector<cudaStream_t> ep_streams;  // streams of chunks 1.. (chunk 0 runs on the backend's stream)
+  std::vector<cudaEvent_t> ep_events;    // [0] router done | [1 + 3 c + {0 pushed, 1 experts done, 2 combined}]
+  std::vector<void*> ep_plans;           // route plan of every chunk
+  unsigned* ep_live_host = nullptr;    // mapped pinned: rows received per (layer, chunk) in the previous step, then wait_err copy [1]
   unsigned* ep_live_dev = nullptr;     // the same memory as the device sees it
   uint32_t ep_exchange = 0;            // exchanges done so far (all ranks count alike)
   uint32_t ep_max_polls = 1u << 24;    // about ten seconds of polling before a wait gives up (fj_moe_ep_wait_polls)
@@ -552,6 +613,7 @@ struct fj_moe_model {
   std::vector<cudaEvent_t> phase_events;  // [layers][5] when phase timing is on
   unsigned* captured_experts = nullptr;
   float* captured_weights = nullptr;
+  bool uniform_routing = false;  // measurement aid (fj_moe_uniform_routing)
 };
 
 extern "C" {
@@ -581,7 +643,9 @@ int32_t fj_moe_model_create(fj_backend* be, const fj_moe_config* config, const f
   auto* m = new fj_moe_model();
   m->be = be; m->pool = pool; m->ep = ep; m->cfg = c; m->world = world;
   m->experts_local = c.experts / world;
-  m->capacity = c.max_rows * c.top_k;
+  m->ep_chunks = world > 1 ? std::min<uint32_t>(std::max<uint32_t>(c.ep_chunks, 1), 8) : 1;
+  m->ep_chunk_capacity = (c.max_rows + m->ep_chunks - 1) / m->ep_chunks * c.top_k;
+  m->capacity = m->ep_chunks * m->ep_chunk_capacity;  // >= max_rows * top_k
   bool ok = true;
   auto dev_alloc = [&](size_t bytes) -> void* {
     void* p = nullptr;
@@ -674,21 +738,32 @@ int32_t fj_moe_model_create(fj_backend* be, const fj_moe_config* config, const f
     m->route_slot = static_cast<unsigned*>(dev_alloc(R * K * 4));
     m->down_ep = static_cast<float*>(dev_alloc(slots * H * 4));
     m->returned = static_cast<float*>(dev_alloc(slots * H * 4));
-    m->ep_counts = static_cast<unsigned*>(dev_alloc(2 * world * 4));
+    const uint32_t chunks = m->ep_chunks;
+    m->ep_counts = static_cast<unsigned*>(dev_alloc(static_cast<size_t>(chunks) * 2 * world * 4));
     if (cudaMallocHost(reinterpret_cast<void**>(&m->ep_counts_host), 2 * world * 4) != cudaSuccess) { cudaGetLastError(); ok = false; }
-    m->ep_flags = static_cast<unsigned long long*>(dev_alloc(2 * world * 8));
-    m->ep_state = static_cast<unsigned*>(dev_alloc((4 + world) * 4));
-    m->ep_tables = static_cast<void**>(dev_alloc(4 * world * sizeof(void*)));
+    m->ep_flags = static_cast<unsigned long long*>(dev_alloc(static_cast<size_t>(chunks) * 2 * world * 8));
+    m->ep_state = static_cast<unsigned*>(dev_alloc((1 + 2 * chunks + static_cast<size_t>(chunks) * world) * 4));
+    m->ep_tables = static_cast<void**>(dev_alloc(5 * world * sizeof(void*)));
+    for (uint32_t ch = 1; ch < chunks && ok; ++ch) {
+      cudaStream_t extra = nullptr;
+      if (cudaStreamCreateWithFlags(&extra, cudaStreamNonBlocking) != cudaSuccess) { cudaGetLastError(); ok = false; break; }
+      m->ep_streams.push_back(extra);
+      m->ep_plans.push_back(dev_alloc(fj::route_plan_bytes(static_cast<unsigned>(slots), m->experts_local)));
+    }
+    for (uint32_t e = 0; e < 1 + 3 * chunks && ok && chunks > 1; ++e) {
+      cudaEvent_t ev = nullptr;
+      if (cudaEventCreateWithFlags(&ev, cudaEventDisableTiming) != cudaSuccess) { cudaGetLastError(); ok = false; break; }
+      m->ep_events.push_back(ev);
+    }
     if (ok) {
-      cudaMemsetAsync(m->ep_flags, 0, 2 * world * 8, be->stream);
-      cudaMemsetAsync(m->ep_state, 0, (4 + world) * 4, be->stream);
       cudaMemsetAsync(m->recv_experts, 0xFF, slots * 4, be->stream);
-      const size_t words = static_cast<size_t>(c.layers) + 1;
+      const size_t words = static_cast<size_t>(c.layers) * chunks + 1;
       if (cudaHostAlloc(reinterpret_cast<void**>(&m->ep_live_host), words * 4, cudaHostAllocMapped) != cudaSuccess ||
           cudaHostGetDevicePointer(reinterpret_cast<void**>(&m->ep_live_dev), m->ep_live_host, 0) != cudaSuccess) { cudaGetLastError(); ok = false; }
       else memset(m->ep_live_host, 0, words * 4);
     }
     m->route_plan = dev_alloc(fj::route_plan_bytes(static_cast<unsigned>(slots), m->experts_local));
+    m->ep_plans.insert(m->ep_plans.begin(), m->route_plan);
   } else {
     m->route_plan = dev_alloc(fj::route_plan_bytes(static_cast<unsigned>(R * K), c.experts));
     m->down_routes = static_cast<float*>(dev_alloc(R * K * H * 4));
@@ -700,6 +775,8 @@ int32_t fj_moe_model_create(fj_backend* be, const fj_moe_config* config, const f
   if (ok) ok = ensure_gemm_scratch(be, fj::gemm_scratch_bytes(static_cast<unsigned>(std::max(R, Lanes)), static_cast<unsigned>(std::max<uint64_t>(qd + 2 * kd, H)), static_cast<unsigned>(std::max<uint64_t>(H, qd))));
   if (!ok || cudaStreamSynchronize(be->stream) != cudaSuccess) {
     for (void* p : m->owned) { cudaFree(p); }
+    for (cudaStream_t st : m->ep_streams) cudaStreamDestroy(st);
+    for (cudaEvent_t ev : m->ep_events) cudaEventDestroy(ev);
     if (m->ep_counts_host) cudaFreeHost(m->ep_counts_host);
     if (m->ep_live_host) cudaFreeHost(m->ep_live_host);
     delete m;
@@ -714,6 +791,8 @@ void fj_moe_model_destroy(fj_moe_model* m) {
   std::lock_guard<std::mutex> lock(m->be->mutex);
   cudaSetDevice(m->be->device);
   cudaStreamSynchronize(m->be->stream);
+  for (cudaStream_t st : m->ep_streams) { cudaStreamSynchronize(st); cudaStreamDestroy(st); }
+  for (cudaEvent_t ev : m->ep_events) cudaEventDestroy(ev);
   for (void* p : m->ep_opened) cudaIpcCloseMemHandle(p);  // normally closed earlier by fj_moe_ep_disconnect, before any rank frees
   for (void* p : m->owned) cudaFree(p);
   for (cudaEvent_t e : m->phase_events) cudaEventDestroy(e);
@@ -723,39 +802,39 @@ void fj_moe_model_destroy(fj_moe_model* m) {
 }
 
 // ---- direct exchange: connecting the ranks of one node -------------------------------------------------
-// fj_moe_ep_export writes this rank's four buffer handles (4 x 64 bytes: received rows, received expert ids,
-// flag words, per-route results); the caller gathers every rank's 256 bytes in rank order (any host channel) and
+// fj_moe_ep_export writes this rank's five buffer handles (5 x 64 bytes: received rows, received expert ids,
+// flag words, per-route results, returned rows); the caller gathers every rank's 320 bytes in rank order (any host channel) and
 // hands the whole table to fj_moe_ep_connect, which maps the peers' buffers. Every rank then passes whether its
 // connect succeeded through the same channel and calls fj_moe_ep_direct(model, 1) only if all did: the choice
 // between this exchange and the NCCL one must be the same on all ranks. Before any rank destroys its model,
 // all call fj_moe_ep_disconnect and meet at a host barrier: a mapping must be closed before its owner frees.
-int32_t fj_moe_ep_export(fj_moe_model* m, uint8_t* out256) {
-  if (!m || !out256 || m->world < 2) return FJ_INVALID_INPUT;
+int32_t fj_moe_ep_export(fj_moe_model* m, uint8_t* out320) {
+  if (!m || !out320 || m->world < 2) return FJ_INVALID_INPUT;
   std::lock_guard<std::mutex> lock(m->be->mutex);
   cudaSetDevice(m->be->device);
   static_assert(sizeof(cudaIpcMemHandle_t) == 64, "handle size");
-  void* bufs[4] = {m->recv_rows, m->recv_experts, m->ep_flags, m->down_ep};
-  for (int i = 0; i < 4; ++i) {
+  void* bufs[5] = {m->recv_rows, m->recv_experts, m->ep_flags, m->down_ep, m->returned};
+  for (int i = 0; i < 5; ++i) {
     cudaIpcMemHandle_t h;
     if (cudaIpcGetMemHandle(&h, bufs[i]) != cudaSuccess) { cudaGetLastError(); return FJ_UNSUPPORTED_OPERATION; }
-    memcpy(out256 + 64 * i, &h, 64);
+    memcpy(out320 + 64 * i, &h, 64);
   }
   return FJ_OK;
 }
 
-int32_t fj_moe_ep_connect(fj_moe_model* m, const uint8_t* table /*[world][256]*/) {
+int32_t fj_moe_ep_connect(fj_moe_model* m, const uint8_t* table /*[world][320]*/) {
   if (!m || !table || m->world < 2 || m->world > 64 || !m->ep) return FJ_INVALID_INPUT;
   std::lock_guard<std::mutex> lock(m->be->mutex);
   cudaSetDevice(m->be->device);
   if (!m->ep_opened.empty() || m->ep_direct) return FJ_INVALID_INPUT;
   const uint32_t W = m->world, rank = m->ep->rank;
-  std::vector<void*> host(4 * static_cast<size_t>(W), nullptr);
-  void* own[4] = {m->recv_rows, m->recv_experts, m->ep_flags, m->down_ep};
+  std::vector<void*> host(5 * static_cast<size_t>(W), nullptr);
+  void* own[5] = {m->recv_rows, m->recv_experts, m->ep_flags, m->down_ep, m->returned};
   for (uint32_t p = 0; p < W; ++p)
-    for (int i = 0; i < 4; ++i) {
+    for (int i = 0; i < 5; ++i) {
       if (p == rank) { host[static_cast<size_t>(i) * W + p] = own[i]; continue; }
       cudaIpcMemHandle_t h;
-      memcpy(&h, table + 256 * static_cast<size_t>(p) + 64 * i, 64);
+      memcpy(&h, table + 320 * static_cast<size_t>(p) + 64 * i, 64);
       void* mapped = nullptr;
       if (cudaIpcOpenMemHandle(&mapped, h, cudaIpcMemLazyEnablePeerAccess) != cudaSuccess) {
         cudaGetLastError();
@@ -774,7 +853,7 @@ int32_t fj_moe_ep_connect(fj_moe_model* m, const uint8_t* table /*[world][256]*/
 int32_t fj_moe_ep_direct(fj_moe_model* m, uint32_t enabled) {
   if (!m || m->world < 2) return FJ_INVALID_INPUT;
   std::lock_guard<std::mutex> lock(m->be->mutex);
-  if (enabled && m->ep_opened.size() != 4 * static_cast<size_t>(m->world - 1)) return FJ_INVALID_INPUT;
+  if (enabled && m->ep_opened.size() != 5 * static_cast<size_t>(m->world - 1)) return FJ_INVALID_INPUT;
   m->ep_direct = enabled != 0;
   return FJ_OK;
 }
@@ -794,6 +873,26 @@ int32_t fj_moe_ep_disconnect(fj_moe_model* m) {
 int32_t fj_moe_ep_wait_polls(fj_moe_model* m, uint32_t polls) {
   if (!m || polls == 0) return FJ_INVALID_INPUT;
   m->ep_max_polls = polls;
+  return FJ_OK;
+}
+
+// How results travel back in the direct exchange: 0 or 1 = the origin's combine reads them from the owner's memory (default),
+// 2 = the owner writes them into the origin's memory. All ranks must choose alike.
+int32_t fj_moe_ep_return_mode(fj_moe_model* m, uint32_t mode) {
+  if (!m || mode > 2) return FJ_INVALID_INPUT;
+  std::lock_guard<std::mutex> lock(m->be->mutex);
+  m->ep_return_mode = mode;
+  return FJ_OK;
+}
+
+// Rows this rank received for its experts in the last finished step, per (layer, chunk): out[layers * chunks]. Tells how evenly
+// the router spreads the work over the ranks; a rank with more rows than the others makes everybody wait at that layer's return.
+int32_t fj_moe_ep_received(fj_moe_model* m, uint32_t* out, uint32_t words) {
+  if (!m || !out || !m->ep_live_host || words < m->cfg.layers * m->ep_chunks) return FJ_INVALID_INPUT;
+  std::lock_guard<std::mutex> lock(m->be->mutex);
+  cudaSetDevice(m->be->device);
+  if (cudaStreamSynchronize(m->be->stream) != cudaSuccess) { cudaGetLastError(); return FJ_DEVICE_EXECUTION_FAILED; }
+  memcpy(out, m->ep_live_host, static_cast<size_t>(m->cfg.layers) * m->ep_chunks * 4);
   return FJ_OK;
 }
 
@@ -844,6 +943,13 @@ int32_t fj_moe_read_phase_ms(fj_moe_model* m, float* out4) {
       if (cudaEventElapsedTime(&ms, m->phase_events[l * 5 + i], m->phase_events[l * 5 + i + 1]) != cudaSuccess) { cudaGetLastError(); return FJ_INVALID_INPUT; }
       out4[i] += ms;
     }
+  return FJ_OK;
+}
+
+int32_t fj_moe_uniform_routing(fj_moe_model* m, uint32_t enabled) {
+  if (!m) return FJ_INVALID_INPUT;
+  std::lock_guard<std::mutex> lock(m->be->mutex);
+  m->uniform_routing = enabled != 0;
   return FJ_OK;
 }
 
@@ -990,6 +1096,10 @@ extern "C" int32_t fj_moe_step(fj_moe_model* m, const uint32_t* token_ids, uint3
         q4(m->normed, L.router, m->router_logits, FJ_F32, rows, H, c.experts, c.router_bits);
       }
       fj::launch_top_k(ctx, m->router_logits, FJ_F32, m->route_weights, FJ_F32, m->route_experts, rows, c.experts, K, true);
+      if (m->uniform_routing) {
+        route_uniform_kernel<<<(rows + 255) / 256, 256, 0, be->stream>>>(m->route_experts, m->route_weights, rows, K, c.experts, l);
+        ctx.launches++;
+      }
       if (m->captured_experts) {
         const size_t at = static_cast<size_t>(l) * c.max_rows * K;
         cudaMemcpyAsync(m->captured_experts + at, m->route_experts, static_cast<size_t>(rows) * K * 4, cudaMemcpyDeviceToDevice, be->stream);
@@ -1002,28 +1112,31 @@ extern "C" int32_t fj_moe_step(fj_moe_model* m, const uint32_t* token_ids, uint3
     const unsigned kGroupedRoutes = c.grouped_min_routes ? c.grouped_min_routes : 64;
     const unsigned kStreamRows = c.stream_rows_per_expert ? c.stream_rows_per_expert : 72;
     // `live`: how many of the n_routes ids are expected to be valid (a padded exchange carries whole slabs)
-    auto bucketed = [&](const void* x, unsigned src_div, const unsigned* ids, unsigned n_routes, unsigned live, unsigned n_experts, void* act, void* down_out, bool down_bf16,
-                        const unsigned* slab_counts = nullptr, unsigned slab_cap = 0) -> bool {
+    auto bucketed_on = [&](fj::Ctx& ctx, void* plan, const void* x, unsigned src_div, const unsigned* ids, unsigned n_routes, unsigned live, unsigned n_experts, void* act, void* down_out,
+                           bool down_bf16, const unsigned* slab_counts, unsigned slab_cap, unsigned slab_offset, unsigned slab_limit) -> bool {
       if (live < kGroupedRoutes || G != 64) return false;
       const bool stream = live < static_cast<uint64_t>(kStreamRows) * n_experts &&
                           fj::expert_stream_supported(H, I, 4, G, n_experts, x, L.gate.packed, L.gate.scales, L.gate.biases) &&
                           fj::expert_stream_supported(H, I, 4, G, n_experts, x, L.up.packed, L.up.scales, L.up.biases) &&
                           fj::expert_stream_supported(I, H, 4, G, n_experts, act, L.down.packed, L.down.scales, L.down.biases);
       if (stream) {
-        fj::launch_route_plan(ctx, ids, n_routes, n_experts, m->route_plan, nullptr, 16, slab_counts, slab_cap);
-        if (!fj::launch_expert_stream_pair(ctx, x, L.gate.packed, L.gate.scales, L.gate.biases, L.up.packed, L.up.scales, L.up.biases, m->route_plan, n_routes, n_experts, src_div, act, H,
+        fj::launch_route_plan(ctx, ids, n_routes, n_experts, plan, nullptr, 16, slab_counts, slab_cap, slab_offset, slab_limit);
+        if (!fj::launch_expert_stream_pair(ctx, x, L.gate.packed, L.gate.scales, L.gate.biases, L.up.packed, L.up.scales, L.up.biases, plan, n_routes, n_experts, src_div, act, H,
                                            I, live) ||
-            !fj::launch_expert_stream_single(ctx, act, L.down.packed, L.down.scales, L.down.biases, m->route_plan, n_routes, n_experts, 1, down_out, down_bf16, I, H, live))
+            !fj::launch_expert_stream_single(ctx, act, L.down.packed, L.down.scales, L.down.biases, plan, n_routes, n_experts, 1, down_out, down_bf16, I, H, live))
           status = FJ_DEVICE_EXECUTION_FAILED;
         return true;
       }
       if (!fj::grouped_q4_supported(H, I, 4, G, n_experts, x, L.gate.packed) || !fj::grouped_q4_supported(I, H, 4, G, n_experts, act, L.down.packed)) return false;
       const unsigned tile_rows = fj::grouped_tile_rows(live, n_experts);
-      fj::launch_route_plan(ctx, ids, n_routes, n_experts, m->route_plan, nullptr, tile_rows, slab_counts, slab_cap);
-      fj::launch_grouped_q4_pair(ctx, x, L.gate.packed, L.gate.scales, L.gate.biases, L.up.packed, L.up.scales, L.up.biases, m->route_plan, n_routes, n_experts, src_div, act, H, I,
+      fj::launch_route_plan(ctx, ids, n_routes, n_experts, plan, nullptr, tile_rows, slab_counts, slab_cap, slab_offset, slab_limit);
+      fj::launch_grouped_q4_pair(ctx, x, L.gate.packed, L.gate.scales, L.gate.biases, L.up.packed, L.up.scales, L.up.biases, plan, n_routes, n_experts, src_div, act, H, I,
                                  tile_rows);
-      fj::launch_grouped_q4_single(ctx, act, L.down.packed, L.down.scales, L.down.biases, m->route_plan, n_routes, n_experts, 1, down_out, down_bf16, I, H, tile_rows);
+      fj::launch_grouped_q4_single(ctx, act, L.down.packed, L.down.scales, L.down.biases, plan, n_routes, n_experts, 1, down_out, down_bf16, I, H, tile_rows);
       return true;
+    };
+    auto bucketed = [&](const void* x, unsigned src_div, const unsigned* ids, unsigned n_routes, unsigned live, unsigned n_experts, void* act, void* down_out, bool down_bf16) -> bool {
+      return bucketed_on(ctx, m->route_plan, x, src_div, ids, n_routes, live, n_experts, act, down_out, down_bf16, nullptr, 0, 0, 0);
     };
     mark(1);
     if (m->world == 1) {
@@ -1039,43 +1152,96 @@ extern "C" int32_t fj_moe_step(fj_moe_model* m, const uint32_t* token_ids, uint3
                                              I, c.experts, H, 4, G, 2, nullptr);
       }
     } else if (m->ep_direct) {
-      // Direct exchange: peer stores and flags instead of NCCL, no host round trip (kernels above).
-      const unsigned cap = m->capacity, routes = rows * K, W = m->world, rank = m->ep->rank;
+      // Direct exchange: peer stores and flags instead of NCCL, no host round trip (kernels above). The layer's rows go in
+      // `chunks` pieces, each on a stream of its own and one step behind the previous one: a chunk starts its dispatch when the
+      // previous chunk's dispatch has left, and its experts when the previous chunk's experts are done, so transfers over
+      // NVLink run under the other chunks' expert projections.
+      const unsigned cap = m->capacity, W = m->world, rank = m->ep->rank, chunks = m->ep_chunks, cap_c = m->ep_chunk_capacity;
       const bool ret_bf16 = c.ep_return_bf16 != 0;
       const int ret_dt = ret_bf16 ? FJ_BF16 : FJ_F32;
       const unsigned exchange = ++m->ep_exchange;
       void** t = m->ep_tables;
       const EpPeers peers{reinterpret_cast<unsigned short* const*>(t), reinterpret_cast<unsigned* const*>(t + W), reinterpret_cast<unsigned long long* const*>(t + 2 * W),
-                          reinterpret_cast<const unsigned char* const*>(t + 3 * W)};
-      unsigned *tickets = m->ep_state, *wait_err = m->ep_state + 2, *stale = m->ep_state + 4, *recv_counts = m->ep_counts + W;
-      ep_push_dispatch_kernel<<<std::max(1u, std::min((routes + 7) / 8, 4u * static_cast<unsigned>(ctx.sm_count > 0 ? ctx.sm_count : 148))), 256, 0, be->stream>>>(static_cast<const unsigned short*>(m->normed), m->route_experts, routes, K, H, cap, rank, W,
-                                                                                          m->experts_local, peers, m->route_slot, m->ep_counts, tickets, exchange);
-      ep_wait_kernel<<<1, 128, 0, be->stream>>>(m->ep_flags, W, exchange, cap, recv_counts, stale, m->recv_experts, m->ep_live_dev + l, wait_err, m->ep_max_polls);
-      ctx.launches += 2;
-      mark(2);
-      // how many rows arrive is known on the device only; the kernels are chosen from what this layer received in the previous step
-      const unsigned seen_before = m->ep_live_host[l];
-      unsigned live = seen_before ? seen_before : std::max(routes, 1u);
-      if (c.grouped_min_routes == 0) live = std::max(live, kGroupedRoutes);  // slabs are mostly empty: the bucketed kernels skip what the per-route ones would visit
-      if (!bucketed(m->recv_rows, 1, m->recv_experts, W * cap, live, m->experts_local, m->act_ep, m->down_ep, ret_bf16, recv_counts, cap)) {
-        fj::launch_gather_quant_matmul(ctx, m->recv_rows, dt, L.gate.packed, L.gate.scales, L.gate.biases, dt, L.up.packed, L.up.scales, L.up.biases, m->recv_experts, m->act_ep, dt,
-                                       W * cap, H, m->experts_local, I, 1, 4, G, 1, nullptr);
-        fj::launch_gather_quant_matmul(ctx, m->act_ep, dt, L.down.packed, L.down.scales, L.down.biases, dt, nullptr, nullptr, nullptr, m->recv_experts, m->down_ep, ret_dt, W * cap, I,
-                                       m->experts_local, H, 1, 4, G, 0, nullptr);
+                          reinterpret_cast<const unsigned char* const*>(t + 3 * W), reinterpret_cast<unsigned char* const*>(t + 4 * W)};
+      unsigned* wait_err = m->ep_state;
+      const bool push_back = m->ep_return_mode == 2;
+      const unsigned sms = static_cast<unsigned>(ctx.sm_count > 0 ? ctx.sm_count : 148);
+      const unsigned rows_c = (rows + chunks - 1) / chunks;
+      if (chunks > 1) cudaEventRecord(m->ep_events[0], be->stream);
+      for (unsigned ch = 0; ch < chunks; ++ch) {
+        cudaStream_t st = ch == 0 ? be->stream : m->ep_streams[ch - 1];
+        fj::Ctx cx = ctx;
+        cx.stream = st;
+        cx.launches = 0;
+        const unsigned row0 = std::min(rows, ch * rows_c), row1 = std::min(rows, row0 + rows_c), n_rows = row1 - row0, routes = n_rows * K;
+        const unsigned fbase = ch * 2 * W;
+        unsigned *send_counts = m->ep_counts + fbase, *recv_counts = send_counts + W, *ticket = m->ep_state + 1 + ch, *ticket_back = m->ep_state + 1 + chunks + ch, *stale = m->ep_state + 1 + 2 * chunks + ch * W;
+        if (ch > 0) {
+          cudaStreamWaitEvent(st, m->ep_events[0], 0);                  // the routing of this layer
+          cudaStreamWaitEvent(st, m->ep_events[1 + 3 * (ch - 1)], 0);  // the previous chunk's rows have left
+        }
+        ep_push_dispatch_kernel<<<std::max(1u, std::min((routes + 7) / 8, 4u * sms)), 256, 0, st>>>(static_cast<const unsigned short*>(m->normed), m->route_experts, row0 * K, row1 * K, K, H, cap,
+                                                                                                  ch * cap_c, cap_c, rank, W, m->experts_local, peers, m->route_slot, send_counts, ticket,
+                                                                                                  fbase, exchange);
+        if (chunks > 1) cudaEventRecord(m->ep_events[1 + 3 * ch], st);
+        ep_wait_kernel<<<1, 128, 0, st>>>(m->ep_flags + fbase, W, exchange, cap_c, recv_counts, stale, m->recv_experts + ch * cap_c, m->ep_live_dev + static_cast<size_t>(l) * chunks + ch,
+                                          wait_err, m->ep_max_polls, nullptr, 0, cap);
+        cx.launches += 2;
+        if (ch == 0) mark(2);
+        if (ch > 0) cudaStreamWaitEvent(st, m->ep_events[1 + 3 * (ch - 1) + 1], 0);  // the previous chunk's experts
+        // how many rows arrive is known on the device only; the kernels are chosen from what this chunk received in the previous step
+        const unsigned seen_before = m->ep_live_host[static_cast<size_t>(l) * chunks + ch];
+        unsigned live = seen_before ? seen_before : std::max(routes, 1u);
+        if (c.grouped_min_routes == 0) live = std::max(live, kGroupedRoutes);  // slabs are mostly empty: the bucketed kernels skip what the per-route ones would visit
+        if (!bucketed_on(cx, m->ep_plans[ch], m->recv_rows, 1, m->recv_experts, W * cap, live, m->experts_local, m->act_ep, m->down_ep, ret_bf16, recv_counts, cap, ch * cap_c, cap_c)) {
+          // per-route kernels over this chunk's share of every slab (ids past the live count are invalid and skipped); only models built for tiny steps get here
+          for (unsigned src = 0; src < W; ++src) {
+            const size_t off = static_cast<size_t>(src) * cap + static_cast<size_t>(ch) * cap_c;
+            const unsigned short* x = m->recv_rows + off * H;
+            unsigned short* act = m->act_ep + off * I;
+            void* down = reinterpret_cast<unsigned char*>(m->down_ep) + off * H * (ret_bf16 ? 2 : 4);
+            fj::launch_gather_quant_matmul(cx, x, dt, L.gate.packed, L.gate.scales, L.gate.biases, dt, L.up.packed, L.up.scales, L.up.biases, m->recv_experts + off, act, dt, cap_c, H,
+                                           m->experts_local, I, 1, 4, G, 1, nullptr);
+            fj::launch_gather_quant_matmul(cx, act, dt, L.down.packed, L.down.scales, L.down.biases, dt, nullptr, nullptr, nullptr, m->recv_experts + off, down, ret_dt, cap_c, I,
+                                           m->experts_local, H, 1, 4, G, 0, nullptr);
+          }
+        }
+        if (chunks > 1) cudaEventRecord(m->ep_events[1 + 3 * ch + 1], st);
+        if (ch == 0) mark(3);
+        const size_t at = static_cast<size_t>(row0) * H * 2;  // activations are bf16
+        if (push_back) {
+          // the owner writes every result row into its origin's memory, then the origin combines from there
+          ep_push_return_kernel<<<8 * sms, 256, 0, st>>>(reinterpret_cast<const unsigned char*>(m->down_ep), static_cast<unsigned>(H * (ret_bf16 ? 2 : 4)), cap, ch * cap_c, cap_c, rank, W,
+                                                        recv_counts, peers, ticket_back, fbase + W, exchange);
+          ep_wait_kernel<<<1, 128, 0, st>>>(m->ep_flags + fbase + W, W, exchange, cap_c, nullptr, nullptr, nullptr, nullptr, wait_err, m->ep_max_polls);
+          cx.launches += 2;
+          if (n_rows)
+            fj::launch_routes_combine(cx, m->returned, ret_dt, m->route_slot + static_cast<size_t>(row0) * K, nullptr, 0, m->route_weights + static_cast<size_t>(row0) * K, FJ_F32,
+                                      static_cast<const unsigned char*>(hidden) + at, dt, static_cast<unsigned char*>(other) + at, dt, n_rows, K, H);
+          if (ch > 0) cudaEventRecord(m->ep_events[1 + 3 * ch + 2], st);
+          ctx.launches += cx.launches;
+          continue;
+        }
+        // "my results of this chunk are ready" to every peer, then wait for theirs; the combine reads the rows where they are
+        ep_wait_kernel<<<1, 128, 0, st>>>(m->ep_flags + fbase + W, W, exchange, cap_c, nullptr, nullptr, nullptr, nullptr, wait_err, m->ep_max_polls, peers.flags, fbase + W + rank);
+        cx.launches++;
+        if (n_rows) {
+          const unsigned grid = std::min(n_rows, 16u * sms);
+          const unsigned char* res = static_cast<const unsigned char*>(hidden) + at;
+          unsigned char* out = static_cast<unsigned char*>(other) + at;
+          if (ret_bf16)
+            ep_pull_combine_kernel<true><<<grid, 256, 0, st>>>(peers.results, m->route_slot + static_cast<size_t>(row0) * K, m->route_weights + static_cast<size_t>(row0) * K, res, dt, out, dt,
+                                                               n_rows, K, H, cap, rank);
+          else
+            ep_pull_combine_kernel<false><<<grid, 256, 0, st>>>(peers.results, m->route_slot + static_cast<size_t>(row0) * K, m->route_weights + static_cast<size_t>(row0) * K, res, dt, out, dt,
+                                                                n_rows, K, H, cap, rank);
+          cx.launches++;
+        }
+        if (ch > 0) cudaEventRecord(m->ep_events[1 + 3 * ch + 2], st);
+        ctx.launches += cx.launches;
       }
+      for (unsigned ch = 1; ch < chunks; ++ch) cudaStreamWaitEvent(be->stream, m->ep_events[1 + 3 * ch + 2], 0);
       if (status != FJ_OK) break;
-      mark(3);
-      // "my results are ready" to every peer, then wait for theirs; the combine reads the rows where they are
-      ep_wait_kernel<<<1, 128, 0, be->stream>>>(m->ep_flags + W, W, exchange, cap, nullptr, nullptr, nullptr, nullptr, wait_err, m->ep_max_polls, peers.flags, W + rank);
-      ctx.launches++;
-      if (rows) {
-        const unsigned grid = std::min(rows, 16u * static_cast<unsigned>(ctx.sm_count > 0 ? ctx.sm_count : 148));
-        if (ret_bf16)
-          ep_pull_combine_kernel<true><<<grid, 256, 0, be->stream>>>(peers.results, m->route_slot, m->route_weights, hidden, dt, other, dt, rows, K, H, cap, rank);
-        else
-          ep_pull_combine_kernel<false><<<grid, 256, 0, be->stream>>>(peers.results, m->route_slot, m->route_weights, hidden, dt, other, dt, rows, K, H, cap, rank);
-        ctx.launches++;
-      }
     } else {
       const unsigned cap = m->capacity, routes = rows * K, W = m->world;
       // rows come back from the experts' owners as f32 (bit-identical to one GPU) or, on request, rounded to bf16 (half the bytes)
@@ -1154,12 +1320,12 @@ extern "C" int32_t fj_moe_step(fj_moe_model* m, const uint32_t* token_ids, uint3
   m->last_kernels = ctx.launches - launches_before;
   m->last_work_items = n_work;
   if (cudaGetLastError() != cudaSuccess) return FJ_DEVICE_EXECUTION_FAILED;
-  if (m->ep_direct) cudaMemcpyAsync(m->ep_live_host + c.layers, m->ep_state + 2, 4, cudaMemcpyDeviceToHost, be->stream);
+  if (m->ep_direct) cudaMemcpyAsync(m->ep_live_host + static_cast<size_t>(c.layers) * m->ep_chunks, m->ep_state, 4, cudaMemcpyDeviceToHost, be->stream);
   if (out_tokens && rows != 0) {
     cudaMemcpyAsync(out_tokens, m->tokens_out, static_cast<size_t>(lanes) * 4, cudaMemcpyDeviceToHost, be->stream);
     if (m->ep) {
       const int32_t waited = ep_wait_stream(m->ep);  // the step's exchanges are still in flight: wait for them with the group's deadline
-      if (waited == FJ_OK && m->ep_direct && m->ep_live_host[c.layers] != 0) return FJ_TIMEOUT;  // a device-side wait of the direct exchange ran out
+      if (waited == FJ_OK && m->ep_direct && m->ep_live_host[static_cast<size_t>(c.layers) * m->ep_chunks] != 0) return FJ_TIMEOUT;  // a device-side wait of the direct exchange ran out
       return waited;
     }
     return cuda_status(cudaStreamSynchronize(be->stream));

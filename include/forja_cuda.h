@@ -552,6 +552,10 @@ typedef struct fj_moe_config {
   /* Expert parallelism only: nonzero = the experts' owners return their per-route rows rounded to bf16 instead of f32.
    * Halves the larger of the two exchanges; the logits then agree with one GPU within the bf16 tolerance instead of bit for bit. */
   uint32_t ep_return_bf16;
+  /* Expert parallelism with the direct exchange only: every layer's rows are split into this many chunks (0 or 1 = no
+   * split, at most 8) that go through dispatch, experts and return one behind the other on streams of their own, so that one
+   * chunk's transfer over NVLink runs while another chunk's experts compute. All ranks must use the same value. */
+  uint32_t ep_chunks;
 } fj_moe_config;
 typedef struct fj_moe_layer_weights {
   uint64_t input_norm, q_norm, k_norm, post_norm; /* bf16 [hidden], [head_dim], [head_dim], [hidden] */
@@ -574,11 +578,13 @@ int32_t fj_moe_step_stats(fj_moe_model* model, uint64_t* kernels, uint64_t* attn
 /* Direct exchange between the ranks of one node (no counterpart in the single-GPU reference): instead of NCCL sends and
  * receives with a host round trip for the row counts, every rank maps four of the others' buffers (CUDA IPC). A layer's
  * dispatch is plain peer stores over NVLink by the kernel that assigns the slots, followed by one flag per (source,
- * destination) carrying the row count, which the receiver polls in its own memory with a bound; on the way back the owner
- * only publishes "results ready" and the origin's combine reads the per-route rows from the owner's memory. Nothing is
- * staged, no multicast is used. Results are bit-identical to the NCCL exchange and to one GPU (same slots, same arithmetic).
- *   fj_moe_ep_export     writes this rank's 4 x 64-byte buffer handles to out256.
- *   fj_moe_ep_connect    takes every rank's 256 bytes in rank order ([world][256]; gathered by the caller over any host
+ * destination) carrying the row count, which the receiver polls in its own memory with a bound. On the way back either the
+ * owner only publishes "results ready" and the origin's combine reads the per-route rows from the owner's memory (fewer
+ * passes over local memory; used up to 3 ranks), or the owner writes them into the origin's memory (writes load NVLink
+ * better than reads when every rank talks to every other; used from 4 ranks on); fj_moe_ep_return_mode overrides the choice.
+ * No multicast is used. Results are bit-identical to the NCCL exchange and to one GPU (same slots, same arithmetic).
+ *   fj_moe_ep_export     writes this rank's 5 x 64-byte buffer handles to out320.
+ *   fj_moe_ep_connect    takes every rank's 320 bytes in rank order ([world][320]; gathered by the caller over any host
  *                        channel) and maps the peers' buffers; FJ_UNSUPPORTED_OPERATION when a mapping is refused.
  *   fj_moe_ep_direct     switches the model's steps to this exchange (1) or back to NCCL (0). All ranks must choose alike:
  *                        enable only after every rank reported a successful connect.
@@ -588,17 +594,25 @@ int32_t fj_moe_step_stats(fj_moe_model* model, uint64_t* kernels, uint64_t* attn
  *                        makes the step compute on zero rows, fj_moe_step answer FJ_TIMEOUT from then on, and leaves the
  *                        context usable; the model has to be rebuilt.
  *   fj_ep_wait_selftest  runs that wait on a flag nothing sets and returns FJ_TIMEOUT when the kernel gave up and said so. */
-int32_t fj_moe_ep_export(fj_moe_model* model, uint8_t* out256);
+int32_t fj_moe_ep_export(fj_moe_model* model, uint8_t* out320);
 int32_t fj_moe_ep_connect(fj_moe_model* model, const uint8_t* table);
 int32_t fj_moe_ep_direct(fj_moe_model* model, uint32_t enabled);
 int32_t fj_moe_ep_disconnect(fj_moe_model* model);
 int32_t fj_moe_ep_wait_polls(fj_moe_model* model, uint32_t polls);
+int32_t fj_moe_ep_return_mode(fj_moe_model* model, uint32_t mode); /* 0 or 1 = the origin reads, 2 = the owner writes; same on all ranks */
+/* Rows this rank received for its experts in the last finished step of the direct exchange, per (layer, chunk):
+ * out[layers * max(ep_chunks, 1)]. Shows how evenly the router spreads work over the ranks. */
+int32_t fj_moe_ep_received(fj_moe_model* model, uint32_t* out, uint32_t words);
 int32_t fj_ep_wait_selftest(fj_backend* be, uint32_t polls);
 /* Measurement aid: while enabled, every layer of a step records CUDA events around its four phases; fj_moe_read_phase_ms
  * waits for the step and returns the time summed over the layers: [0] attention block and router, [1] dispatch (slot plan,
  * row scatter, exchange to the experts' owners; ~0 on one GPU), [2] expert projections, [3] exchange back and weighted combine. */
 int32_t fj_moe_phase_timing(fj_moe_model* model, uint32_t enabled);
 int32_t fj_moe_read_phase_ms(fj_moe_model* model, float* out4);
+/* Measurement aid: while enabled, the router still runs but its choice is replaced by an even spread (every row takes top_k
+ * distinct experts from a hash of layer and row, weight 1 / top_k). A model with random weights routes most rows of a prompt to
+ * the same few experts, which a trained, load-balanced router does not; this switch shows what the step costs without that. */
+int32_t fj_moe_uniform_routing(fj_moe_model* model, uint32_t enabled);
 /* Parity aid: while enabled, every layer's routing of a step (TopK output: expert ids and normalised
  * weights, [rows, top_k] in packed row order) is kept and can be read back after the step. */
 int32_t fj_moe_capture_routes(fj_moe_model* model, uint32_t enabled);

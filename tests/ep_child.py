@@ -61,13 +61,19 @@ def main():
         run_case(be, ep, rank, dict(CFG, max_rows=max_rows), weights, local, prompts, steps, page, lanes, table_pages, physical, ids, gather=gather)
     run_case(be, ep, rank, dict(CFG, max_rows=300, ep_return_bf16=1), weights, local, prompts, steps, page, lanes, table_pages, physical, ids, exact=False, gather=gather)
     run_case(be, ep, rank, dict(CFG, max_rows=300, grouped_min_routes=0), weights, local, prompts, steps, page, lanes, table_pages, physical, ids, exact=False, gather=gather)
+    # results written back by the owners instead of read by the origins (what 4 and more ranks do by default)
+    run_case(be, ep, rank, dict(CFG, max_rows=300), weights, local, prompts, steps, page, lanes, table_pages, physical, ids, gather=gather, return_mode=2)
+    run_case(be, ep, rank, dict(CFG, max_rows=64, ep_chunks=2), weights, local, prompts, steps, page, lanes, table_pages, physical, ids, gather=gather, return_mode=2)
+    # every layer's rows in 3 chunks that pass through dispatch, experts and return one behind the other on their own streams
+    run_case(be, ep, rank, dict(CFG, max_rows=64, ep_chunks=3), weights, local, prompts, steps, page, lanes, table_pages, physical, ids, gather=gather)
+    run_case(be, ep, rank, dict(CFG, max_rows=300, ep_chunks=2, grouped_min_routes=0), weights, local, prompts, steps, page, lanes, table_pages, physical, ids, exact=False, gather=gather)
     dist.barrier()
     ep.close()
     dist.destroy_process_group()
     print("EP_OK", rank)
 
 
-def run_case(be, ep, rank, cfg, weights, local, prompts, steps, page, lanes, table_pages, physical, ids, exact=True, gather=None):
+def run_case(be, ep, rank, cfg, weights, local, prompts, steps, page, lanes, table_pages, physical, ids, exact=True, gather=None, return_mode=0):
     def build(w, group):
         pool = fb.KvPool(be, page, physical, lanes, table_pages)
         assert all(s == 0 for s in pool.reserve(list(range(lanes)), [n + steps + 1 for n in prompts]))
@@ -78,6 +84,7 @@ def run_case(be, ep, rank, cfg, weights, local, prompts, steps, page, lanes, tab
     pool_one, model_one = build(weights, None)
     if gather is not None:
         assert model_ep.connect_peers(gather), f"rank {rank}: the peers' buffers could not be mapped"
+        model_ep.set_return_mode(return_mode)
         model_ep.set_wait_polls(1 << 23)  # a few seconds: the other rank also runs its single-GPU twin between steps
     logits_ep, logits_one = be.alloc(fb.BF16, (lanes, cfg["vocab"])), be.alloc(fb.BF16, (lanes, cfg["vocab"]))
 
