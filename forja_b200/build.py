@@ -12,7 +12,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 INCLUDE = os.path.join(os.path.dirname(HERE), "include")
 OUTPUT = os.path.join(HERE, "libforja_cuda.so")
-SOURCES = ["fj_backend.cu", "fj_model.cu", "fj_elementwise.cu", "fj_paged.cu", "fj_gemm.cu", "fj_gemm_tma.cu", "fj_quant.cu", "fj_pack.cu", "fj_moe.cu", "fj_grouped.cu", "fj_grouped_tc5.cu", "fj_sample.cu", "fj_dense_ops.cu", "fj_sched.cpp", "fj_weights.cpp"]
+SOURCES = ["fj_backend.cu", "fj_model.cu", "fj_elementwise.cu", "fj_paged.cu", "fj_gemm.cu", "fj_gemm_tma.cu", "fj_attn_tc5.cu", "fj_quant.cu", "fj_pack.cu", "fj_moe.cu", "fj_grouped.cu", "fj_grouped_tc5.cu", "fj_sample.cu", "fj_dense_ops.cu", "fj_sched.cpp", "fj_weights.cpp"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-Xcompiler", "-fPIC",
               "--expt-relaxed-constexpr", "-I", INCLUDE, "-I", CSRC]
 

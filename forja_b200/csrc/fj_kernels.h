@@ -150,6 +150,13 @@ void launch_attn_decode_mma(Ctx& ctx, const AttnGeometry& g, const AttnSeq* seqs
 // attn_prefill_tokens_per_block tokens} and KV head; the caller lists every block of every sequence.
 bool attn_prefill_mma_supported(const AttnGeometry& g);
 unsigned attn_prefill_tokens_per_block(const AttnGeometry& g);
+// The same blocks on tcgen05 (128 rows per block, accumulators in tensor memory); taken by launch_attn_prefill_mma when the
+// shape allows (16-bit q/kv of one type, head_dim 128, 16-token pages, group dividing 128).
+bool attn_prefill_tc5_supported(const AttnGeometry& g);
+unsigned attn_prefill_tc5_tokens_per_block(const AttnGeometry& g);
+void launch_attn_prefill_tc5(Ctx& ctx, const AttnGeometry& g, const AttnSeq* seqs, const uint2* items, unsigned n_items, const void* kpool, const void* vpool,
+                             const unsigned* generations, ErrorRecord* err);
+unsigned attn_prefill_tc5_giveups();
 void launch_attn_prefill_mma(Ctx& ctx, const AttnGeometry& g, const AttnSeq* seqs, const uint2* items, unsigned n_items, const void* kpool, const void* vpool,
                              const unsigned* generations, ErrorRecord* err);
 // Generic f32-math attention for any float dtypes, head_dim <= 256, any q_len (one CTA per

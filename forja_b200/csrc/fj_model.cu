@@ -825,7 +825,7 @@ int32_t fj_tcgen05_wait_giveups(fj_backend* be, uint32_t* out) {
   std::lock_guard<std::mutex> lock(be->mutex);
   cudaSetDevice(be->device);
   cudaStreamSynchronize(be->stream);
-  *out = fj::gemm_tma_giveups() + fj::grouped_tcgen05_giveups();
+  *out = fj::gemm_tma_giveups() + fj::grouped_tcgen05_giveups() + fj::attn_prefill_tc5_giveups();
   return FJ_OK;
 }
 

@@ -804,11 +804,16 @@ bool attn_prefill_mma_supported(const AttnGeometry& g) {
          g.kv_heads != 0 && g.q_heads % g.kv_heads == 0 && (group == 1 || group == 2 || group == 4 || group == 8 || group == 16);
 }
 
-unsigned attn_prefill_tokens_per_block(const AttnGeometry& g) { return kPrefillRows / (g.q_heads / g.kv_heads); }
+unsigned attn_prefill_tokens_per_block(const AttnGeometry& g) {
+  if (attn_prefill_tc5_supported(g)) return attn_prefill_tc5_tokens_per_block(g);
+  return kPrefillRows / (g.q_heads / g.kv_heads);
+}
 
 void launch_attn_prefill_mma(Ctx& ctx, const AttnGeometry& g, const AttnSeq* seqs, const uint2* items, unsigned n_items, const void* kpool, const void* vpool,
                              const unsigned* generations, ErrorRecord* err) {
   if (n_items == 0) return;
+  // the items were listed with attn_prefill_tokens_per_block, which makes the same choice
+  if (attn_prefill_tc5_supported(g)) { launch_attn_prefill_tc5(ctx, g, seqs, items, n_items, kpool, vpool, generations, err); return; }
   static bool configured[64] = {};
   int device = 0;
   cudaGetDevice(&device);
