@@ -33,7 +33,7 @@ constexpr int A5_KV_HALF = A5_KEYS * 128;                 // [64 keys][64 d]
 constexpr int A5_V_BYTES = 2 * A5_KV_HALF;                // one V tile; two of them, used in turn
 constexpr int A5_Q = 0, A5_K = A5_Q + 2 * A5_Q_HALF, A5_V = A5_K + 2 * A5_KV_HALF, A5_P = A5_V + 2 * A5_V_BYTES, A5_BAR = A5_P + A5_ROWS * 128;
 constexpr int A5_SMEM = A5_BAR + 64 + 1024;               // + barriers, + slack to align the base to 1024 bytes
-constexpr unsigned A5_TMEM_COLS = 256, A5_S_COL = 0, A5_O_COL = 64;
+constexpr unsigned A5_TMEM_COLS = 256, A5_S_COL = 0, A5_O_COL = 128;  // S twice (64 columns each, used in turn), then O
 constexpr unsigned kA5SpinLimit = 1u << 24;
 constexpr unsigned A5_PAGE_CACHE = 1024;  // authenticated page-table entries kept in shared memory: 256 tiles
 constexpr unsigned kPoison = 0xFFFFFFFFu;
@@ -114,6 +114,12 @@ __device__ inline void a5_tmem_store32(unsigned taddr, const float (&v)[32]) {
       "r"(__float_as_uint(v[24])), "r"(__float_as_uint(v[25])), "r"(__float_as_uint(v[26])), "r"(__float_as_uint(v[27])), "r"(__float_as_uint(v[28])), "r"(__float_as_uint(v[29])),
       "r"(__float_as_uint(v[30])), "r"(__float_as_uint(v[31]))
       : "memory");
+}
+// 2^x for x <= 8 or so; flushes results below 2^-126 to zero (a probability that small adds nothing to an f32 sum)
+__device__ inline float a5_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+  return y;
 }
 template <bool kBF16>
 __device__ inline unsigned a5_pack2(float lo, float hi) {
@@ -234,15 +240,20 @@ __global__ void __launch_bounds__(A5_THREADS, 2) attn_prefill_tc5_kernel(A5Param
     for (int q = 0; q < 4; ++q) pg[q] = tile < n_tiles ? s_pages[(tile * (A5_KEYS / A5_PAGE) + q) % A5_PAGE_CACHE] : kPoison;
   };
   // One cp.async group with this thread's 8 pieces of a tile of one plane (rows past key_end and refused pages are zero-filled).
+  // Piece i is row t / 16 + 8 i of the tile: row (t / 16 + 8 (i & 1)) of page i / 2, and it lands 1024 bytes after piece i - 1.
+  const unsigned c16 = threadIdx.x & 15, r0 = threadIdx.x >> 4;
+  const size_t page_bytes = static_cast<size_t>(A5_PAGE) * plane_row_bytes;
+  const size_t src_even = static_cast<size_t>(kv_head) * A5_ROW_BYTES + r0 * plane_row_bytes + c16 * 16, src_odd = src_even + 8 * plane_row_bytes;
+  const unsigned dst0 = (c16 >> 3) * A5_KV_HALF + r0 * 128 + (((c16 & 7) ^ (r0 & 7)) << 4);
   auto issue = [&](unsigned tile, const unsigned (&pg)[4], const char* pool, unsigned region) {
     if (tile < n_tiles) {
+      const unsigned rows_left = key_end - tile * A5_KEYS;  // rows of this tile that exist (>= 1)
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
-        const unsigned r = (threadIdx.x >> 4) + 8 * i, c16 = threadIdx.x & 15;
         const unsigned page = pg[i >> 1];
-        const bool ok = page != kPoison && tile * A5_KEYS + r < key_end;
-        const size_t src = ok ? (static_cast<size_t>(page) * A5_PAGE * p.kv_heads + kv_head) * A5_ROW_BYTES + (r & 15) * plane_row_bytes + c16 * 16 : 0;
-        a5_cp_async_16(smem + region + (c16 >> 3) * A5_KV_HALF + r * 128 + (((c16 & 7) ^ (r & 7)) << 4), pool + src, ok ? 16u : 0u);
+        const bool ok = page != kPoison && r0 + 8 * i < rows_left;
+        const size_t src = ok ? page * page_bytes + ((i & 1) ? src_odd : src_even) : 0;
+        a5_cp_async_16(smem + region + dst0 + i * 1024, pool + src, ok ? 16u : 0u);
       }
     }
     asm volatile("cp.async.commit_group;\n" ::: "memory");
@@ -255,42 +266,60 @@ __global__ void __launch_bounds__(A5_THREADS, 2) attn_prefill_tc5_kernel(A5Param
   issue(0, pg, p.vpool, A5_V);
   entries(1, pg);
 
+  // S = Q K^T of one tile into S buffer (tile & 1): reduction over the head dimension, 4 steps of 16 in each half. One thread issues.
+  auto issue_scores = [&](unsigned tile) {
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      const unsigned long long a_desc = a5_desc(smem + A5_Q + half * A5_Q_HALF, 16), b_desc = a5_desc(smem + A5_K + half * A5_KV_HALF, 16);
+#pragma unroll
+      for (int ks = 0; ks < 4; ++ks) a5_mma(tmem + A5_S_COL + (tile & 1u) * A5_KEYS, a_desc + 2ull * ks, b_desc + 2ull * ks, idesc_s, (half != 0 || ks != 0) ? 1u : 0u);
+    }
+    a5_commit(bar_s);
+  };
+  if (n_tiles != 0) {
+    asm volatile("cp.async.wait_group 1;\n" ::: "memory");  // K of the first tile has landed
+    asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+    asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+      issue_scores(0);
+    }
+  }
+
   // The accumulator O stays in tensor memory over all tiles (P V accumulates into it). It is scaled by 2^-m like the stored
   // probabilities; m follows the row maximum only when that has grown by more than 2^8 since m was set, so the accumulator has
   // to be rescaled (read, multiplied, written back) a few times per row at most, instead of once per tile. Probabilities are
   // at most 2^8 in that scale, exact enough in bf16 and far from any overflow in the f32 sums.
+  // One barrier per tile: after it the issuing thread queues O += P V of this tile and S of the next one, which then run while
+  // the threads come round to wait for that S.
   constexpr float kSlack = 8.0f;
   for (unsigned tile = 0; tile < n_tiles && !failed; ++tile) {
     const unsigned key_base = tile * A5_KEYS;
-    asm volatile("cp.async.wait_group 1;\n" ::: "memory");  // K of this tile has landed (the newest group is V of this tile)
-    asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
-    asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
-    __syncthreads();  // K is in shared memory for everyone
-
-    // ---- S = Q K^T: reduction over the head dimension, 4 steps of 16 in each half (queued behind the previous tile's P V)
-    if (threadIdx.x == 0) {
-      asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-#pragma unroll
-      for (int half = 0; half < 2; ++half) {
-        const unsigned long long a_desc = a5_desc(smem + A5_Q + half * A5_Q_HALF, 16), b_desc = a5_desc(smem + A5_K + half * A5_KV_HALF, 16);
-#pragma unroll
-        for (int ks = 0; ks < 4; ++ks) a5_mma(tmem + A5_S_COL, a_desc + 2ull * ks, b_desc + 2ull * ks, idesc_s, (half != 0 || ks != 0) ? 1u : 0u);
-      }
-      a5_commit(bar_s);
-    }
     if (!a5_mbar_wait(bar_s, tile & 1u, &s_gave_up)) { failed = true; break; }
     asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
-    issue(tile + 1, pg, p.kpool, A5_K);  // the tensor core is done with K: the next tile's K travels under the softmax and P V
+    issue(tile + 1, pg, p.kpool, A5_K);  // the tensor core is done with K: the next tile's K travels under the softmax
+    const unsigned s_addr = lane_base + A5_S_COL + (tile & 1u) * A5_KEYS;
 
-    // ---- this thread's row of S, first pass: the maximum over the keys it may see
+    // ---- this thread's row of S, first pass: the maximum over the keys it may see (all 64 unless the row's limit cuts the tile)
+    const unsigned visible = limit > key_base ? min(limit - key_base, static_cast<unsigned>(A5_KEYS)) : 0u;
     float row_max = -INFINITY;
+    {
+      float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-    for (int h = 0; h < 2; ++h) {
-      float part[32];
-      a5_tmem_load32(lane_base + A5_S_COL + h * 32, part);
+      for (int h = 0; h < 2; ++h) {
+        float part[32];
+        a5_tmem_load32(s_addr + h * 32, part);
+        if (visible == A5_KEYS) {
 #pragma unroll
-      for (int i = 0; i < 32; ++i)
-        if (key_base + h * 32 + i < limit) row_max = fmaxf(row_max, part[i] * scale2);
+          for (int i = 0; i < 32; ++i) mx[i & 3] = fmaxf(mx[i & 3], part[i]);
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            if (static_cast<unsigned>(h * 32 + i) < visible) mx[i & 3] = fmaxf(mx[i & 3], part[i]);
+        }
+      }
+      row_max = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * scale2;  // scale2 > 0: the maximum commutes with the scaling
     }
     // the previous tile's P V is complete: P and the other V buffer are free, O is stable
     if (tile != 0 && !a5_mbar_wait(bar_o, (tile - 1) & 1u, &s_gave_up)) { failed = true; break; }
@@ -304,7 +333,7 @@ __global__ void __launch_bounds__(A5_THREADS, 2) attn_prefill_tc5_kernel(A5Param
     entries(tile + 2, pg);
     float alpha = 1.0f;
     if (row_max > m + kSlack || (m == -INFINITY && row_max != -INFINITY)) {
-      alpha = m == -INFINITY ? 0.0f : exp2f(m - row_max);
+      alpha = m == -INFINITY ? 0.0f : a5_exp2(m - row_max);
       m = row_max;
       l *= alpha;
     }
@@ -321,31 +350,36 @@ __global__ void __launch_bounds__(A5_THREADS, 2) attn_prefill_tc5_kernel(A5Param
     }
     // ---- second pass: P = 2^(s - m) goes to shared memory as the next A operand
     const float m_safe = m == -INFINITY ? 0.0f : m;
-    float sum = 0.0f;
+    float sums[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
       float part[32];
-      a5_tmem_load32(lane_base + A5_S_COL + h * 32, part);
+      a5_tmem_load32(s_addr + h * 32, part);
+      if (visible == A5_KEYS) {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) part[i] = a5_exp2(fmaf(part[i], scale2, -m_safe));
+      } else {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) part[i] = static_cast<unsigned>(h * 32 + i) < visible ? a5_exp2(fmaf(part[i], scale2, -m_safe)) : 0.0f;
+      }
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
         unsigned packed[4];
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-          const unsigned k0 = key_base + h * 32 + c * 8 + 2 * j;
-          const float p0 = k0 < limit ? exp2f(part[c * 8 + 2 * j] * scale2 - m_safe) : 0.0f;
-          const float p1 = k0 + 1 < limit ? exp2f(part[c * 8 + 2 * j + 1] * scale2 - m_safe) : 0.0f;
-          sum += p0 + p1;
-          packed[j] = a5_pack2<kBF16>(p0, p1);
+          sums[j] += part[c * 8 + 2 * j] + part[c * 8 + 2 * j + 1];
+          packed[j] = a5_pack2<kBF16>(part[c * 8 + 2 * j], part[c * 8 + 2 * j + 1]);
         }
         const unsigned chunk = h * 4 + c;
         *reinterpret_cast<uint4*>(smem_ptr + A5_P + row * 128 + ((chunk ^ (row & 7)) << 4)) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
       }
     }
+    const float sum = (sums[0] + sums[1]) + (sums[2] + sums[3]);
     l += sum;
-    asm volatile("cp.async.wait_group 2;\n" ::: "memory");  // V of this tile has landed (two newer groups: the next tile's K and V)
+    asm volatile("cp.async.wait_group 1;\n" ::: "memory");  // V of this tile and K of the next have landed (the newest group is the next tile's V)
     asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
     asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
-    __syncthreads();  // every row of P is written, V is in shared memory for everyone, O is rescaled; every thread has read its row of S
+    __syncthreads();  // every row of P is written, V and the next K are in shared memory for everyone, O is rescaled, S has been read
 
     // ---- O += P V: reduction over the 64 keys in 4 steps of 16; V is MN-major (the two 64-wide halves of the head dimension 8 KB apart)
     if (threadIdx.x == 0) {
@@ -355,6 +389,7 @@ __global__ void __launch_bounds__(A5_THREADS, 2) attn_prefill_tc5_kernel(A5Param
 #pragma unroll
       for (int ks = 0; ks < 4; ++ks) a5_mma(tmem + A5_O_COL, a_desc + 2ull * ks, a5_desc(v_tile + ks * 16 * 128, A5_KV_HALF), idesc_o, (tile != 0 || ks != 0) ? 1u : 0u);
       a5_commit(bar_o);
+      if (tile + 1 < n_tiles) issue_scores(tile + 1);
     }
   }
   asm volatile("cp.async.wait_group 0;\n" ::: "memory");
