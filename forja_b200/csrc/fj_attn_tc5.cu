@@ -301,23 +301,29 @@ __global__ void __launch_bounds__(A5_THREADS, 2) attn_prefill_tc5_kernel(A5Param
     issue(tile + 1, pg, p.kpool, A5_K);  // the tensor core is done with K: the next tile's K travels under the softmax
     const unsigned s_addr = lane_base + A5_S_COL + (tile & 1u) * A5_KEYS;
 
-    // ---- this thread's row of S, first pass: the maximum over the keys it may see (all 64 unless the row's limit cuts the tile)
+    // ---- this thread's row of S: the maximum over the keys it may see (all 64 unless the row's limit cuts the tile)
     const unsigned visible = limit > key_base ? min(limit - key_base, static_cast<unsigned>(A5_KEYS)) : 0u;
+    // the row is read from tensor memory once and kept in registers for both passes
+    float sc[A5_KEYS];
+    {
+      float part[32];
+      a5_tmem_load32(s_addr, part);
+#pragma unroll
+      for (int i = 0; i < 32; ++i) sc[i] = part[i];
+      a5_tmem_load32(s_addr + 32, part);
+#pragma unroll
+      for (int i = 0; i < 32; ++i) sc[32 + i] = part[i];
+    }
     float row_max = -INFINITY;
     {
       float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+      if (visible == A5_KEYS) {
 #pragma unroll
-      for (int h = 0; h < 2; ++h) {
-        float part[32];
-        a5_tmem_load32(s_addr + h * 32, part);
-        if (visible == A5_KEYS) {
+        for (int i = 0; i < A5_KEYS; ++i) mx[i & 3] = fmaxf(mx[i & 3], sc[i]);
+      } else {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) mx[i & 3] = fmaxf(mx[i & 3], part[i]);
-        } else {
-#pragma unroll
-          for (int i = 0; i < 32; ++i)
-            if (static_cast<unsigned>(h * 32 + i) < visible) mx[i & 3] = fmaxf(mx[i & 3], part[i]);
-        }
+        for (int i = 0; i < A5_KEYS; ++i)
+          if (static_cast<unsigned>(i) < visible) mx[i & 3] = fmaxf(mx[i & 3], sc[i]);
       }
       row_max = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * scale2;  // scale2 > 0: the maximum commutes with the scaling
     }
@@ -351,28 +357,22 @@ __global__ void __launch_bounds__(A5_THREADS, 2) attn_prefill_tc5_kernel(A5Param
     // ---- second pass: P = 2^(s - m) goes to shared memory as the next A operand
     const float m_safe = m == -INFINITY ? 0.0f : m;
     float sums[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    if (visible == A5_KEYS) {
 #pragma unroll
-    for (int h = 0; h < 2; ++h) {
-      float part[32];
-      a5_tmem_load32(s_addr + h * 32, part);
-      if (visible == A5_KEYS) {
+      for (int i = 0; i < A5_KEYS; ++i) sc[i] = a5_exp2(fmaf(sc[i], scale2, -m_safe));
+    } else {
 #pragma unroll
-        for (int i = 0; i < 32; ++i) part[i] = a5_exp2(fmaf(part[i], scale2, -m_safe));
-      } else {
+      for (int i = 0; i < A5_KEYS; ++i) sc[i] = static_cast<unsigned>(i) < visible ? a5_exp2(fmaf(sc[i], scale2, -m_safe)) : 0.0f;
+    }
 #pragma unroll
-        for (int i = 0; i < 32; ++i) part[i] = static_cast<unsigned>(h * 32 + i) < visible ? a5_exp2(fmaf(part[i], scale2, -m_safe)) : 0.0f;
+    for (int chunk = 0; chunk < 8; ++chunk) {
+      unsigned packed[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        sums[j] += sc[chunk * 8 + 2 * j] + sc[chunk * 8 + 2 * j + 1];
+        packed[j] = a5_pack2<kBF16>(sc[chunk * 8 + 2 * j], sc[chunk * 8 + 2 * j + 1]);
       }
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        unsigned packed[4];
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          sums[j] += part[c * 8 + 2 * j] + part[c * 8 + 2 * j + 1];
-          packed[j] = a5_pack2<kBF16>(part[c * 8 + 2 * j], part[c * 8 + 2 * j + 1]);
-        }
-        const unsigned chunk = h * 4 + c;
-        *reinterpret_cast<uint4*>(smem_ptr + A5_P + row * 128 + ((chunk ^ (row & 7)) << 4)) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
-      }
+      *reinterpret_cast<uint4*>(smem_ptr + A5_P + row * 128 + ((chunk ^ (row & 7)) << 4)) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
     }
     const float sum = (sums[0] + sums[1]) + (sums[2] + sums[3]);
     l += sum;
