@@ -892,7 +892,7 @@ int32_t exec_paged_attention_run(Exec& x, const fj_dispatch* ds, uint32_t count,
     }
   }
   if (!mma) {
-    // longer query runs (prefill chunks): 64-row tensor-core blocks when the shape allows, else the f32 kernel
+    // longer query runs (prefill chunks): 128-row tensor-core blocks when the shape allows, else the f32 kernel
     bool blocks = fj::attn_prefill_mma_supported(g);
     for (auto& s : seqs) {
       if ((reinterpret_cast<size_t>(s.q) & 3) || (s.q_tok_stride & 1) || (s.q_head_stride & 1)) blocks = false;

@@ -145,13 +145,12 @@ void launch_attn_decode_mma(Ctx& ctx, const AttnGeometry& g, const AttnSeq* seqs
                             ErrorRecord* err, const unsigned* n_work_dev = nullptr);
 // n_work_dev: optional device word holding the live item count; CTAs beyond it return at once, so a launch recorded
 // once with a rounded-up grid (a replayed CUDA graph) serves steps whose work lists differ in length.
-// Chunked-prefill attention on tensor cores for any q_len: same shape limits as the decode kernel and
-// q_heads / kv_heads in {1, 2, 4, 8, 16}. One CTA per item {sequence, first token of a block of
-// attn_prefill_tokens_per_block tokens} and KV head; the caller lists every block of every sequence.
+// Chunked-prefill attention on tensor cores for any q_len (tcgen05, fj_attn_tc5.cu): 16-bit q/kv of one type, head_dim ==
+// value_dim == 128, 16-token pages, q_heads / kv_heads dividing 128. One CTA per item {sequence, first token of a block of
+// attn_prefill_tokens_per_block tokens} and KV head (128 rows = tokens x query heads of the group); the caller lists every
+// block of every sequence. The *_mma names are the entry points the callers use; they forward to the tcgen05 kernel.
 bool attn_prefill_mma_supported(const AttnGeometry& g);
 unsigned attn_prefill_tokens_per_block(const AttnGeometry& g);
-// The same blocks on tcgen05 (128 rows per block, accumulators in tensor memory); taken by launch_attn_prefill_mma when the
-// shape allows (16-bit q/kv of one type, head_dim 128, 16-token pages, group dividing 128).
 bool attn_prefill_tc5_supported(const AttnGeometry& g);
 unsigned attn_prefill_tc5_tokens_per_block(const AttnGeometry& g);
 void launch_attn_prefill_tc5(Ctx& ctx, const AttnGeometry& g, const AttnSeq* seqs, const uint2* items, unsigned n_items, const void* kpool, const void* vpool,

@@ -527,7 +527,7 @@ struct StepPlan {
   unsigned chunk;         // tokens per split-K work item
   unsigned work_grid;     // CTAs of the decode attention launch (>= the live item count)
   const unsigned* n_work_dev;  // live item count on the device when work_grid is a rounded-up bound, else nullptr
-  unsigned n_blocks;      // 64-row blocks of the chunked-prefill attention
+  unsigned n_blocks;      // 128-row blocks of the chunked-prefill attention
   fj::AttnScratch scratch;
   void* logits;
 };
@@ -698,7 +698,7 @@ int32_t fj_dense_step(fj_dense_model* m, const uint32_t* token_ids, uint32_t* ou
     plan.work_grid = static_cast<unsigned>(std::min<uint64_t>((n_work + kWorkGridStep - 1) / kWorkGridStep * kWorkGridStep, m->work_cap));
     plan.n_work_dev = m->n_work_dev;
   }
-  // query runs too long for the decode kernel: 64-row tensor-core blocks, listed by the host from the packed step
+  // query runs too long for the decode kernel: 128-row tensor-core blocks, listed by the host from the packed step
   if (!plan.mma && fj::attn_prefill_mma_supported(g)) {
     const unsigned per_block = fj::attn_prefill_tokens_per_block(g);
     std::vector<uint2> items;

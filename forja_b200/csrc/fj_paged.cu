@@ -415,256 +415,7 @@ __global__ void __launch_bounds__(kWarps * 32, 2) attn_decode_mma_kernel(DecodeP
   if (threadIdx.x == 0) p.counters[work.group_index] = 0;  // leave the counter ready for the next launch
 }
 
-// ---------------------------------------------------------------------------------------------
-// chunked-prefill attention on tensor cores: 64 query rows per CTA over pages of K/V
-// ---------------------------------------------------------------------------------------------
-// One CTA owns 64 query rows of one (sequence, KV head): 64 / group consecutive tokens times the
-// group's query heads (row r -> token r / group, head r % group), 16 rows per warp. All four warps
-// walk the same keys, 4 pages (64 keys) per pipeline stage, copied with cp.async by the warp that
-// owns the page; per stage a warp computes S = Q K^T (16 x 64), one online-softmax update and
-// O += P V with P rounded to the KV dtype. Keys beyond a row's causal limit are masked, and the
-// walk stops at the largest limit of the CTA's rows, so the work per chunk is the causal triangle.
-constexpr int kPrefillRows = 64;
-constexpr int kPrefillPages = 4;                                   // pages per stage
-constexpr int kPrefillStageBytes = kPrefillPages * kStageBytes;    // 32 KB
-constexpr int kPrefillStages = 3;
-constexpr int kPrefillSmem = kPrefillStages * kPrefillStageBytes;  // 96 KB
-
-struct PrefillParams {
-  const AttnSeq* seqs;
-  const uint2* items;  // {sequence, first token of the block}
-  unsigned n_items;
-  const char* kpool;
-  const char* vpool;
-  const unsigned* generations;
-  unsigned physical_pages, q_heads, kv_heads, group;
-  float scale;
-  int out_dtype;
-  ErrorRecord* err;
-};
-
-template <bool kBF16>
-__global__ void __launch_bounds__(kWarps * 32, 2) attn_prefill_mma_kernel(PrefillParams p) {
-  extern __shared__ __align__(128) unsigned char smem[];
-  pdl_sync();
-  if (blockIdx.x >= p.n_items) return;
-  const uint2 item = p.items[blockIdx.x];
-  const AttnSeq seq = p.seqs[item.x];
-  const unsigned kv_head = blockIdx.y, token0 = item.y;
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const unsigned tokens_per_block = kPrefillRows / p.group;
-  const unsigned block_tokens = min(tokens_per_block, seq.q_len - token0);
-  const bool inactive = seq.activity != nullptr && *seq.activity == 0;
-
-  // this lane's two rows of the warp's 16-row tile
-  const unsigned row[2] = {static_cast<unsigned>(warp) * 16 + (lane >> 2), static_cast<unsigned>(warp) * 16 + (lane >> 2) + 8};
-  unsigned tok[2], head[2], limit[2];
-  bool live[2];
-#pragma unroll
-  for (int r = 0; r < 2; ++r) {
-    tok[r] = token0 + row[r] / p.group;
-    head[r] = kv_head * p.group + row[r] % p.group;
-    live[r] = row[r] / p.group < block_tokens;
-    limit[r] = !live[r] ? 0u : (seq.causal ? min(seq.key_length, seq.q_start + tok[r] + 1) : seq.key_length);
-  }
-  const unsigned c0 = (lane & 3) * 2;
-  if (inactive) {  // zeros, no reads (lib.rs:319-328)
-#pragma unroll
-    for (int r = 0; r < 2; ++r)
-      if (live[r])
-        for (int i = 0; i < 16; ++i) {
-          const size_t off = static_cast<size_t>(tok[r]) * seq.o_tok_stride + static_cast<size_t>(head[r]) * seq.o_head_stride + i * 8 + c0;
-          store_from_f32(seq.out, p.out_dtype, off, 0.0f);
-          store_from_f32(seq.out, p.out_dtype, off + 1, 0.0f);
-        }
-    return;
-  }
-  // keys this CTA has to visit: the largest limit of its rows
-  const unsigned last_token = token0 + block_tokens - 1;
-  const unsigned key_end = seq.causal ? min(seq.key_length, seq.q_start + last_token + 1) : seq.key_length;
-  const unsigned n_pages = (key_end + kPageTokens - 1) / kPageTokens;
-  const unsigned n_stages = (n_pages + kPrefillPages - 1) / kPrefillPages;
-
-  unsigned qf[8][4];
-  {
-    const unsigned short* qbase = static_cast<const unsigned short*>(seq.q);
-    const size_t off0 = static_cast<size_t>(tok[0]) * seq.q_tok_stride + static_cast<size_t>(head[0]) * seq.q_head_stride;
-    const size_t off1 = static_cast<size_t>(tok[1]) * seq.q_tok_stride + static_cast<size_t>(head[1]) * seq.q_head_stride;
-#pragma unroll
-    for (int ks = 0; ks < 8; ++ks) {
-      const unsigned col = ks * 16 + c0;
-      qf[ks][0] = live[0] ? *reinterpret_cast<const unsigned*>(qbase + off0 + col) : 0u;
-      qf[ks][1] = live[1] ? *reinterpret_cast<const unsigned*>(qbase + off1 + col) : 0u;
-      qf[ks][2] = live[0] ? *reinterpret_cast<const unsigned*>(qbase + off0 + col + 8) : 0u;
-      qf[ks][3] = live[1] ? *reinterpret_cast<const unsigned*>(qbase + off1 + col + 8) : 0u;
-    }
-  }
-  float o[16][4];
-#pragma unroll
-  for (int i = 0; i < 16; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f; }
-  float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.0f, 0.0f};
-  int bad = 0;
-
-  const unsigned smem_base = static_cast<unsigned>(__cvta_generic_to_shared(smem));
-  const size_t plane_row_bytes = static_cast<size_t>(p.kv_heads) * kRowBytes;
-  // warp w copies page 4 s + w of stage s; its table entries are authenticated 32 stages at a time
-  unsigned ent_page = 0;
-  int ent_ok = 0;
-  auto fetch_entries = [&](unsigned base_stage) {
-    const unsigned lp = (base_stage + lane) * kPrefillPages + warp;
-    ent_page = 0;
-    ent_ok = 0;
-    if (lp < n_pages) {
-      bool ok = lp < seq.table_pages;
-      unsigned page = 0;
-      if (ok) {
-        page = seq.table[2 * lp];
-        ok = authenticate(page, seq.table[2 * lp + 1], p.generations, p.physical_pages);
-      }
-      if (!ok) {
-        bad = 1;
-        report_error(p.err != nullptr ? p.err + seq.err_index : nullptr, ERR_PAGE, lp);
-        page = 0;
-      }
-      ent_page = page;
-      ent_ok = ok ? 1 : 0;
-    }
-  };
-  fetch_entries(0);
-  auto issue = [&](unsigned s) {
-    if (s < n_stages) {
-      if (s != 0 && (s & 31) == 0) fetch_entries(s);
-      const unsigned lp = s * kPrefillPages + warp;
-      const unsigned page = __shfl_sync(0xffffffffu, ent_page, s & 31);
-      const bool ok = __shfl_sync(0xffffffffu, ent_ok, s & 31) != 0 && lp < n_pages;
-      const unsigned tile = smem_base + (s % kPrefillStages) * kPrefillStageBytes + warp * kStageBytes;
-      const size_t page_off = (static_cast<size_t>(page) * kPageTokens * p.kv_heads + kv_head) * kRowBytes;
-#pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const unsigned chunk = lane + 32 * i;  // 256 chunks of 16 B per tile
-        const unsigned r = chunk >> 4, c16 = chunk & 15;
-        const unsigned bytes = (ok && lp * kPageTokens + r < key_end) ? 16u : 0u;
-        const size_t src = page_off + r * plane_row_bytes + c16 * 16;
-        const unsigned dst = r * kRowBytes + ((c16 ^ (r & 7)) << 4);
-        cp_async_16(tile + dst, p.kpool + src, bytes);
-        cp_async_16(tile + kTileBytes + dst, p.vpool + src, bytes);
-      }
-    }
-    cp_async_commit();
-  };
-#pragma unroll
-  for (int s = 0; s < kPrefillStages - 1; ++s) issue(s);
-
-  for (unsigned s = 0; s < n_stages; ++s) {
-    cp_async_wait<kPrefillStages - 2>();
-    __syncthreads();  // stage s is complete for all warps; everyone is done with stage s - 1
-    issue(s + kPrefillStages - 1);
-    const unsigned stage = smem_base + (s % kPrefillStages) * kPrefillStageBytes;
-    const unsigned key_base = s * (kPrefillPages * kPageTokens);
-    // a warp whose rows all end before this stage has nothing to add
-    if (__all_sync(0xffffffffu, key_base >= max(limit[0], limit[1]))) continue;
-
-    float sc[kPrefillPages][2][4];
-#pragma unroll
-    for (int pg = 0; pg < kPrefillPages; ++pg) {
-#pragma unroll
-      for (int nt = 0; nt < 2; ++nt) sc[pg][nt][0] = sc[pg][nt][1] = sc[pg][nt][2] = sc[pg][nt][3] = 0.0f;
-      const unsigned mi = lane >> 3, rr = lane & 7;
-      const unsigned token = (mi >> 1) * 8 + rr;
-#pragma unroll
-      for (int ks = 0; ks < 8; ++ks) {
-        const unsigned chunk = ks * 2 + (mi & 1);
-        unsigned b0, b1, b2, b3;
-        ldmatrix_x4(b0, b1, b2, b3, stage + pg * kStageBytes + token * kRowBytes + ((chunk ^ (token & 7)) << 4));
-        mma_16816<kBF16>(sc[pg][0], qf[ks], b0, b1);
-        mma_16816<kBF16>(sc[pg][1], qf[ks], b2, b3);
-      }
-    }
-    // scale, mask, one online-softmax update for the 64 keys (rows: regs 0,1 and 2,3)
-    float row_max[2] = {-INFINITY, -INFINITY};
-#pragma unroll
-    for (int pg = 0; pg < kPrefillPages; ++pg)
-#pragma unroll
-      for (int nt = 0; nt < 2; ++nt)
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const unsigned key = key_base + pg * kPageTokens + nt * 8 + (lane & 3) * 2 + (e & 1);
-          const int r = e >> 1;
-          float v = sc[pg][nt][e] * p.scale;
-          v = key < limit[r] ? v : -INFINITY;
-          sc[pg][nt][e] = v;
-          row_max[r] = fmaxf(row_max[r], v);
-        }
-    float alpha[2];
-#pragma unroll
-    for (int r = 0; r < 2; ++r) {
-      row_max[r] = fmaxf(row_max[r], __shfl_xor_sync(0xffffffffu, row_max[r], 1));
-      row_max[r] = fmaxf(row_max[r], __shfl_xor_sync(0xffffffffu, row_max[r], 2));
-      const float m_new = fmaxf(m[r], row_max[r]);
-      const float m_safe = m_new == -INFINITY ? 0.0f : m_new;
-      alpha[r] = m[r] == -INFINITY ? 0.0f : expf(m[r] - m_safe);
-      m[r] = m_new;
-      float sum = 0.0f;
-#pragma unroll
-      for (int pg = 0; pg < kPrefillPages; ++pg)
-#pragma unroll
-        for (int nt = 0; nt < 2; ++nt) {
-          const float p0 = expf(sc[pg][nt][2 * r] - m_safe), p1 = expf(sc[pg][nt][2 * r + 1] - m_safe);
-          sc[pg][nt][2 * r] = p0;
-          sc[pg][nt][2 * r + 1] = p1;
-          sum += p0 + p1;
-        }
-      l[r] = l[r] * alpha[r] + sum;
-    }
-#pragma unroll
-    for (int i = 0; i < 16; ++i) {
-      o[i][0] *= alpha[0]; o[i][1] *= alpha[0];
-      o[i][2] *= alpha[1]; o[i][3] *= alpha[1];
-    }
-#pragma unroll
-    for (int pg = 0; pg < kPrefillPages; ++pg) {
-      unsigned pf[4];
-      pf[0] = pack2<kBF16>(sc[pg][0][0], sc[pg][0][1]);
-      pf[1] = pack2<kBF16>(sc[pg][0][2], sc[pg][0][3]);
-      pf[2] = pack2<kBF16>(sc[pg][1][0], sc[pg][1][1]);
-      pf[3] = pack2<kBF16>(sc[pg][1][2], sc[pg][1][3]);
-      const unsigned mi = lane >> 3, rr = lane & 7;
-      const unsigned token = (mi & 1) * 8 + rr;
-#pragma unroll
-      for (int jn = 0; jn < 8; ++jn) {
-        const unsigned chunk = jn * 2 + (mi >> 1);
-        unsigned b0, b1, b2, b3;
-        ldmatrix_x4_trans(b0, b1, b2, b3, stage + pg * kStageBytes + kTileBytes + token * kRowBytes + ((chunk ^ (token & 7)) << 4));
-        mma_16816<kBF16>(o[2 * jn], pf, b0, b1);
-        mma_16816<kBF16>(o[2 * jn + 1], pf, b2, b3);
-      }
-    }
-  }
-  cp_async_wait<0>();
-#pragma unroll
-  for (int r = 0; r < 2; ++r) {
-    l[r] += __shfl_xor_sync(0xffffffffu, l[r], 1);
-    l[r] += __shfl_xor_sync(0xffffffffu, l[r], 2);
-  }
-  const int any_bad = __syncthreads_or(bad);  // a refused page zeroes the rows of this block
-#pragma unroll
-  for (int r = 0; r < 2; ++r) {
-    if (!live[r]) continue;
-    const float inv = (any_bad || l[r] <= 0.0f) ? 0.0f : 1.0f / l[r];
-    const size_t base = static_cast<size_t>(tok[r]) * seq.o_tok_stride + static_cast<size_t>(head[r]) * seq.o_head_stride + c0;
-#pragma unroll
-    for (int i = 0; i < 16; ++i) {
-      const float v0 = o[i][2 * r] * inv, v1 = o[i][2 * r + 1] * inv;
-      // the packed 4-byte store needs a 4-byte-aligned ADDRESS: a 16-bit output view may start at an odd element of its buffer
-      if (p.out_dtype == (kBF16 ? BF16 : F16) && (((reinterpret_cast<size_t>(seq.out) >> 1) + base) % 2 == 0)) {
-        *reinterpret_cast<unsigned*>(static_cast<unsigned short*>(seq.out) + base + i * 8) = pack2<kBF16>(v0, v1);
-      } else {
-        store_from_f32(seq.out, p.out_dtype, base + i * 8, v0);
-        store_from_f32(seq.out, p.out_dtype, base + i * 8 + 1, v1);
-      }
-    }
-  }
-}
+// Chunked-prefill attention on tensor cores lives in fj_attn_tc5.cu (tcgen05, 128 query rows per CTA).
 
 // ---------------------------------------------------------------------------------------------
 // generic attention: one CTA per (sequence, head, query row), f32 math, any float dtypes
@@ -798,36 +549,13 @@ void launch_attn_decode_mma(Ctx& ctx, const AttnGeometry& g, const AttnSeq* seqs
   ctx.launches++;
 }
 
-bool attn_prefill_mma_supported(const AttnGeometry& g) {
-  const unsigned group = g.kv_heads ? g.q_heads / g.kv_heads : 0;
-  return g.head_dim == kHeadDim && g.value_dim == kHeadDim && g.page_tokens == kPageTokens && (g.kv_dtype == BF16 || g.kv_dtype == F16) && g.q_dtype == g.kv_dtype &&
-         g.kv_heads != 0 && g.q_heads % g.kv_heads == 0 && (group == 1 || group == 2 || group == 4 || group == 8 || group == 16);
-}
+bool attn_prefill_mma_supported(const AttnGeometry& g) { return attn_prefill_tc5_supported(g); }
 
-unsigned attn_prefill_tokens_per_block(const AttnGeometry& g) {
-  if (attn_prefill_tc5_supported(g)) return attn_prefill_tc5_tokens_per_block(g);
-  return kPrefillRows / (g.q_heads / g.kv_heads);
-}
+unsigned attn_prefill_tokens_per_block(const AttnGeometry& g) { return attn_prefill_tc5_tokens_per_block(g); }
 
 void launch_attn_prefill_mma(Ctx& ctx, const AttnGeometry& g, const AttnSeq* seqs, const uint2* items, unsigned n_items, const void* kpool, const void* vpool,
                              const unsigned* generations, ErrorRecord* err) {
-  if (n_items == 0) return;
-  // the items were listed with attn_prefill_tokens_per_block, which makes the same choice
-  if (attn_prefill_tc5_supported(g)) { launch_attn_prefill_tc5(ctx, g, seqs, items, n_items, kpool, vpool, generations, err); return; }
-  static bool configured[64] = {};
-  int device = 0;
-  cudaGetDevice(&device);
-  if (device >= 0 && device < 64 && !configured[device]) {
-    cudaFuncSetAttribute(attn_prefill_mma_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kPrefillSmem);
-    cudaFuncSetAttribute(attn_prefill_mma_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kPrefillSmem);
-    configured[device] = true;
-  }
-  PrefillParams p{seqs, items, n_items, static_cast<const char*>(kpool), static_cast<const char*>(vpool), generations, g.physical_pages, g.q_heads, g.kv_heads,
-                  g.q_heads / g.kv_heads, g.scale, g.out_dtype, err};
-  dim3 grid(n_items, g.kv_heads);
-  if (g.kv_dtype == BF16) launch_pdl(attn_prefill_mma_kernel<true>, grid, dim3(kWarps * 32), kPrefillSmem, ctx.stream, p);
-  else launch_pdl(attn_prefill_mma_kernel<false>, grid, dim3(kWarps * 32), kPrefillSmem, ctx.stream, p);
-  ctx.launches++;
+  launch_attn_prefill_tc5(ctx, g, seqs, items, n_items, kpool, vpool, generations, err);
 }
 
 void launch_attn_generic(Ctx& ctx, const AttnGeometry& g, const AttnSeq* seqs, unsigned n_seqs, unsigned max_q_len,
