@@ -717,7 +717,11 @@ int32_t fj_moe_model_create(fj_backend* be, const fj_moe_config* config, const f
   m->tokens_out = static_cast<unsigned*>(dev_alloc(Lanes * 4));
   m->seqs = static_cast<fj::AttnSeq*>(dev_alloc(Lanes * sizeof(fj::AttnSeq)));
   const uint64_t token_capacity = static_cast<uint64_t>(pool->dev.physical_pages) * pool->dev.page_tokens;
-  m->work_cap = static_cast<uint32_t>(std::min<uint64_t>((token_capacity / 64 + Lanes) * c.kv_heads, 1u << 22));
+  // Split-K work items of a step: at most ceil(length / chunk) per lane and KV head with chunk >= 64 and a length that the lane's
+  // page table bounds, whatever prefixes are shared between lanes. Sized for that bound, the per-step check against work_cap
+  // cannot fail on one rank only (it still can where the bound exceeds 2^22 items and is clipped).
+  const uint64_t lane_items = (static_cast<uint64_t>(pool->dev.table_pages) * pool->dev.page_tokens + 63) / 64 + 1;
+  m->work_cap = static_cast<uint32_t>(std::min<uint64_t>(std::max<uint64_t>((token_capacity / 64 + Lanes) * c.kv_heads, Lanes * lane_items * c.kv_heads), 1u << 22));
   m->work = static_cast<fj::AttnWork*>(dev_alloc(static_cast<size_t>(m->work_cap) * sizeof(fj::AttnWork)));
   m->n_work_dev = static_cast<unsigned*>(dev_alloc(16));
   m->prefill_items_cap = static_cast<uint32_t>(R + Lanes);
