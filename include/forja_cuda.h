@@ -495,9 +495,10 @@ int32_t fj_paged_decode_attention_static(fj_backend* be, const void* q, void* ou
                                          uint32_t lanes, uint32_t table_pages, uint32_t physical_pages, uint32_t q_heads,
                                          uint32_t kv_heads, uint32_t dtype, float scale, uint32_t* status);
 
-/* Health counter of the tcgen05 GEMM (no counterpart in the reference): how many of its bounded
- * mbarrier waits ran out since the library was loaded. 0 in a healthy run; a nonzero value means a
- * kernel gave up, freed its tensor memory and left its output tile unwritten. Synchronises the stream. */
+/* Health counter of the tcgen05 kernels (dense GEMM, grouped expert GEMM, prefill attention; no counterpart in the
+ * reference): how many of their bounded mbarrier waits ran out since the library was loaded. 0 in a healthy run; a
+ * nonzero value means a kernel gave up, freed its tensor memory and left its output tile unwritten (the attention kernel
+ * writes zeros for its rows). Synchronises the stream. */
 int32_t fj_tcgen05_wait_giveups(fj_backend* be, uint32_t* out);
 
 /* Synthetic contents for benchmarks (no counterpart in the reference, whose weights come from
