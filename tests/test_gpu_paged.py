@@ -286,7 +286,7 @@ def test_long_context_split_k_matches_oracle():
 @pytest.mark.parametrize("q_len,q_start", [(512, 0), (512, 1536), (70, 33), (9, 1000), (257, 15)])
 def test_chunked_prefill_attention_on_tensor_cores_matches_oracle(hq, kvh, q_len, q_start):
     """Prefill chunks (config 3: 32 q / 4 kv heads, d 128, 512-token chunks) and ragged tails through
-    the 64-row tensor-core blocks: permuted pages, causal limit per row, chunk start inside a page."""
+    the 128-row tcgen05 blocks: permuted pages, causal limit per row, chunk start inside a page."""
     rng = np.random.default_rng(q_len * 7 + q_start + hq)
     be = backend()
     dt, page, d = fb.BF16, 16, 128
@@ -298,6 +298,30 @@ def test_chunked_prefill_attention_on_tensor_cores_matches_oracle(hq, kvh, q_len
     out = be.alloc(dt, (q_len, hq, d))
     scale = float(np.float32(1.0) / np.sqrt(np.float32(d)))
     be.run(Op.PagedSdpa(scale, True, q_start, key_length, page), [q.permute([1, 0, 2]), kt, vt, up_u32(table)[0], up_u32(generations)[0]], [out.permute([1, 0, 2])])
+    fjo.set_threads(fjo.max_threads())
+    want = fjo.paged_sdpa(np.ascontiguousarray(qh.transpose(1, 0, 2)), dt, kh, dt, vh, dt, table, generations, key_length, q_start, scale, True, page)
+    fjo.set_threads(1)
+    got = down(out).transpose(1, 0, 2)
+    assert_close(got, fjo.decode(want, dt), TOL[dt])
+    assert max_abs_rel(got, fjo.decode(want, dt)) <= 2e-2
+
+
+@pytest.mark.parametrize("dt,hq,kvh,q_len,q_start", [(fb.BF16, 32, 4, 16, 20000), (fb.BF16, 16, 8, 20, 33000), (fb.F16, 32, 4, 200, 100), (fb.F16, 8, 8, 33, 17000)])
+def test_prefill_attention_beyond_one_page_table_window_and_in_f16(dt, hq, kvh, q_len, q_start):
+    """The tcgen05 prefill kernel authenticates the lane's page table into shared memory 1024 pages (16384 keys) at a time:
+    contexts past that refill the window inside the tile loop. f16 runs the same kernel with the other operand format."""
+    rng = np.random.default_rng(q_len + q_start + hq)
+    be = backend()
+    page, d = 16, 128
+    key_length = q_start + q_len
+    physical = (key_length + page - 1) // page + 3
+    table, generations = random_table(rng, key_length, page, physical)
+    kt, kh, vt, vh = fill_pools(rng, physical, page, kvh, d, dt)
+    q, qh = up(rng.standard_normal((q_len, hq, d)), dt)
+    out = be.alloc(dt, (q_len, hq, d))
+    scale = float(np.float32(1.0) / np.sqrt(np.float32(d)))
+    be.run(Op.PagedSdpa(scale, True, q_start, key_length, page), [q.permute([1, 0, 2]), kt, vt, up_u32(table)[0], up_u32(generations)[0]], [out.permute([1, 0, 2])])
+    assert be.tcgen05_wait_giveups() == 0
     fjo.set_threads(fjo.max_threads())
     want = fjo.paged_sdpa(np.ascontiguousarray(qh.transpose(1, 0, 2)), dt, kh, dt, vh, dt, table, generations, key_length, q_start, scale, True, page)
     fjo.set_threads(1)
