@@ -259,43 +259,55 @@ class Bf16WeightMoeOracle(MoeOracle):
         return y if out_dt == fjo.F32 else fjo.encode(y, fjo.BF16)
 
 
-def ep_moe_layer(rank: int, world: int, cfg: dict, normed, residual, L_local: dict, router, exchange):
+def ep_moe_layer(rank: int, world: int, cfg: dict, normed, residual, L_local: dict, router, exchange, chunks: int = 1):
     """Expert-parallel form of MoeOracle.moe for one rank, restating the device algorithm in numpy:
-    slots are handed out per destination in (row, j) order, slabs of capacity rows * top_k are
-    exchanged, the owner computes gate/up/silu/down for every received slot, results return as f32
-    and the origin adds residual + sum_j w_j * down_j in ascending j (product rounded, then added).
+    slots are handed out per destination in (row, j) order, slabs are exchanged, the owner computes
+    gate/up/silu/down for every received slot, results return as f32 and the origin adds
+    residual + sum_j w_j * down_j in ascending j (product rounded, then added).
     ``L_local`` holds this rank's expert slice; ``exchange(array)`` takes [world, ...] slabs and
-    returns the slabs addressed to this rank, [world, ...] indexed by source."""
+    returns the slabs addressed to this rank, [world, ...] indexed by source.
+    ``chunks`` > 1 restates the layout of the direct exchange with a layer's rows in several chunks:
+    chunk c covers rows [c * ceil(rows / chunks), ...) of this rank, owns slots
+    [c * cap_c, (c + 1) * cap_c) of every slab (cap_c = ceil(max_rows / chunks) * top_k) and announces
+    how many of them it filled per destination (the payload of the device's flags); the owner visits
+    exactly the announced slots of every (chunk, source)."""
     G, K, H, I = cfg["group_size"], cfg["top_k"], cfg["hidden"], cfg["expert_intermediate"]
     per = cfg["experts"] // world
     rows = normed.shape[0]
-    cap = cfg["max_rows"] * K
+    chunks = max(1, int(chunks))
+    cap_c = (cfg["max_rows"] + chunks - 1) // chunks * K
+    cap = chunks * cap_c
+    rows_c = (rows + chunks - 1) // chunks
     logits = fjo.quant_matmul(normed, fjo.BF16, *router, fjo.BF16, cfg["router_bits"], G, fjo.F32)
     weights, experts = fjo.top_k(logits, fjo.F32, K, True) if rows else (np.zeros((0, K), np.float32), np.zeros((0, K), np.uint32))
     send_rows = np.zeros((world, cap, H), np.uint16)
     send_experts = np.full((world, cap), per, np.uint32)
-    next_slot = [0] * world
+    send_counts = np.zeros((world, chunks), np.uint32)  # [destination][chunk]
     route_slot = np.zeros((rows, K), np.int64)
     for r in range(rows):
+        c = r // rows_c
         for j in range(K):
             dest = int(experts[r, j]) // per
-            slot = next_slot[dest]
-            next_slot[dest] += 1
+            slot = c * cap_c + int(send_counts[dest, c])
+            assert send_counts[dest, c] < cap_c
+            send_counts[dest, c] += 1
             route_slot[r, j] = dest * cap + slot
             send_rows[dest, slot] = normed[r]
             send_experts[dest, slot] = int(experts[r, j]) - dest * per
-    recv_rows, recv_experts = exchange(send_rows), exchange(send_experts)
+    recv_rows, recv_experts, recv_counts = exchange(send_rows), exchange(send_experts), exchange(send_counts)
     down = np.zeros((world, cap, H), np.float32)
-    for src in range(world):
-        live = np.nonzero(recv_experts[src] < per)[0]
-        if live.size == 0:
-            continue
-        x = np.ascontiguousarray(recv_rows[src, live])
-        ids = np.ascontiguousarray(recv_experts[src, live]).reshape(-1, 1)
-        gate = fjo.gather_quant_matmul(x, fjo.BF16, *L_local["gate"], fjo.BF16, ids, 4, G, out_dt=fjo.F32)
-        up = fjo.gather_quant_matmul(x, fjo.BF16, *L_local["up"], fjo.BF16, ids, 4, G, out_dt=fjo.F32)
-        act = fjo.prog_silu_mul(gate, up, fjo.F32, out_dt=fjo.BF16).reshape(live.size, I)
-        down[src, live] = fjo.gather_quant_matmul(act, fjo.BF16, *L_local["down"], fjo.BF16, ids, 4, G, out_dt=fjo.F32).reshape(live.size, H)
+    for c in range(chunks):
+        for src in range(world):
+            live = c * cap_c + np.arange(int(recv_counts[src, c]))
+            if live.size == 0:
+                continue
+            assert np.all(recv_experts[src, live] < per)
+            x = np.ascontiguousarray(recv_rows[src, live])
+            ids = np.ascontiguousarray(recv_experts[src, live]).reshape(-1, 1)
+            gate = fjo.gather_quant_matmul(x, fjo.BF16, *L_local["gate"], fjo.BF16, ids, 4, G, out_dt=fjo.F32)
+            up = fjo.gather_quant_matmul(x, fjo.BF16, *L_local["up"], fjo.BF16, ids, 4, G, out_dt=fjo.F32)
+            act = fjo.prog_silu_mul(gate, up, fjo.F32, out_dt=fjo.BF16).reshape(live.size, I)
+            down[src, live] = fjo.gather_quant_matmul(act, fjo.BF16, *L_local["down"], fjo.BF16, ids, 4, G, out_dt=fjo.F32).reshape(live.size, H)
     returned = exchange(down).reshape(world * cap, H)
     out = np.zeros((rows, H), np.uint16)
     res = fjo.decode(residual, fjo.BF16) if rows else np.zeros((0, H), np.float32)

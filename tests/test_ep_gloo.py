@@ -1,5 +1,6 @@
 """Expert-parallel routing on two CPU ranks over gloo: the numpy restatement of the device
-algorithm (slot plan, slab exchange, owner-side expert projections, ordered combine) must give
+algorithm (slot plan, slab exchange, owner-side expert projections, ordered combine; also with a layer's
+rows in 2 and 3 chunks, each with its own share of every slab and its own announced row counts) must give
 each rank exactly the bits the single-rank MoE block gives for the same rows."""
 import os
 import subprocess
@@ -35,10 +36,11 @@ rng = np.random.default_rng(40 + rank)
 for rows in ([5, 8][rank], [3, 0][rank]):                            # the second round leaves rank 1 without rows
     normed = fjo.encode(rng.standard_normal((rows, cfg["hidden"])).astype(np.float32), fjo.BF16)
     residual = fjo.encode(rng.standard_normal((rows, cfg["hidden"])).astype(np.float32), fjo.BF16)
-    got = engine.ep_moe_layer(rank, world, cfg, normed, residual, local, L["router"], exchange)
-    if rows:
-        want, _, _, _ = engine.MoeOracle(cfg, weights, 2, 16).moe(normed, residual, L)
-        assert np.array_equal(got, want), f"rank {rank}: expert-parallel block differs from the single-rank block"
+    want = engine.MoeOracle(cfg, weights, 2, 16).moe(normed, residual, L)[0] if rows else None
+    for chunks in (1, 2, 3):                                         # 2 and 3: the chunked slot layout of the direct exchange
+        got = engine.ep_moe_layer(rank, world, cfg, normed, residual, local, L["router"], exchange, chunks=chunks)
+        if rows:
+            assert np.array_equal(got, want), f"rank {rank}: expert-parallel block ({chunks} chunks) differs from the single-rank block"
 dist.barrier()
 dist.destroy_process_group()
 print("EP_GLOO_OK", rank)
