@@ -1,23 +1,26 @@
 // Chunked-prefill paged attention on the 5th-generation tensor cores (tcgen05.mma, accumulators in tensor memory).
 //
-// Same contract as the mma.sync block kernel in fj_paged.cu (reference: crates/forja-cpu/src/lib.rs:309-433 paged_sdpa and
-// crates/forja-metal/src/paged.metal:206-298 for the role): one CTA takes one {sequence, first token} item and one KV head and
-// computes 128 rows = (128 / group) query tokens x group query heads against the lane's pages, causal by absolute position.
+// Contract (reference: crates/forja-cpu/src/lib.rs:309-433 paged_sdpa; crates/forja-metal/src/paged.metal:206-298 for the
+// role): one CTA takes one {sequence, first token} item and one KV head and computes 128 rows = (128 / group) query tokens x
+// group query heads against the lane's pages, causal by absolute position; refused pages zero the block's rows and are reported.
 //
 // Per 64-key tile:
 //   * K and V pages are copied with cp.async into shared memory in the 128-byte swizzle, two 64-wide halves of the head
-//     dimension each ([keys][64] bf16 = 128 bytes per row). For S = Q K^T that layout is a K-major B operand (reduction over
-//     the head dimension); for O = P V the very same bytes are an MN-major B operand (reduction over the keys, the head
-//     dimension contiguous), so V is never transposed.
-//   * S (128 x 64, f32) is produced by 8 tcgen05.mma of K = 16 into tensor memory; every thread owns one row, reads it back
-//     with tcgen05.ld, applies scale, causal limit and the online-softmax update in registers and writes its row of P (bf16)
-//     into shared memory in the swizzled K-major layout.
-//   * the tile's contribution P V (128 x 128, f32) is produced by 4 tcgen05.mma into a second tensor-memory region; the thread
-//     reads its row and folds it into its running output row in registers (o = o * alpha + tile), so nothing in tensor memory
-//     ever has to be rescaled.
-// Two CTAs share an SM (80 KB of shared memory, 256 tensor-memory columns each): while one runs its softmax the other's
-// MMAs and copies proceed. Every wait on an mbarrier is bounded; a wait that runs out is counted (attn_prefill_tc5_giveups)
-// and the CTA writes zeros for its rows.
+//     dimension each ([keys][64] bf16 = 128 bytes per row), a tile ahead of their use (V in two buffers). For S = Q K^T that
+//     layout is a K-major B operand (reduction over the head dimension); for O += P V the very same bytes are an MN-major B
+//     operand (reduction over the keys, the head dimension contiguous), so V is never transposed.
+//   * S (128 x 64, f32) is produced by 8 tcgen05.mma of K = 16 into one of two tensor-memory buffers; every thread owns one
+//     row, reads it back with tcgen05.ld, applies scale and causal limit, and writes its row of P = 2^(s - m) (bf16) into
+//     shared memory in the swizzled K-major layout.
+//   * O += P V (128 x 128, f32) is 4 tcgen05.mma accumulating in tensor memory over all tiles. The scale m follows the row
+//     maximum only when that has grown by more than 2^8, so the accumulator is read, multiplied and written back
+//     (tcgen05.ld / tcgen05.st) a few times per row at most instead of once per tile; the row sum uses the same scale.
+//   * one __syncthreads per tile; after it a single thread queues O += P V of this tile and S of the next, which run while
+//     the threads come round to wait for that S.
+// The lane's page table is authenticated into shared memory 1024 pages at a time, off the tile loop's critical path.
+// Two CTAs share an SM (about 104 KB of shared memory, 256 tensor-memory columns each): while one runs its softmax the
+// other's MMAs and copies proceed. Every wait on an mbarrier is bounded; a wait that runs out is counted
+// (attn_prefill_tc5_giveups) and the CTA writes zeros for its rows.
 #include "fj_kernels.h"
 
 #include <cuda_bf16.h>
