@@ -516,6 +516,8 @@ int fjo_sdpa(const void* q, int q_dt, const void* k, int k_dt, const void* v, in
   auto key = decode_vec(k, k_dt, kv_heads * kv_len * width, &ok1);
   auto value = decode_vec(v, v_dt, kv_heads * kv_len * value_width, &ok2);
   if (!ok0 || !ok1 || !ok2 || kv_heads == 0 || q_heads % kv_heads != 0) return FJO_EXECUTION_FAILED;
+  // a causal window must end inside the cache (crates/forja-core/src/ops.rs check_sdpa: q_start + q_len <= kv_len)
+  if (causal && static_cast<uint64_t>(q_start) + q_len > kv_len) return FJO_INVALID_INPUT;
   size_t group = q_heads / kv_heads;
   std::vector<float> result(q_heads * q_len * value_width);
   for (size_t h = 0; h < q_heads; ++h) {

@@ -447,3 +447,71 @@ def test_greedy_sample_equals_argmax_and_seeded_sampling_is_reproducible():
     assert set(masked.tolist()) <= {1, 3}
     with pytest.raises(fjo.OracleError):
         fjo.sample(logits, fjo.F32, [bits(-1.0), 0, bits(1.0), 0, 0], position=0)
+
+
+# ---- further known answers of the reference's backend tests -------------------------------------------------------------
+
+def test_copies_permuted_attention_heads_to_contiguous_bf16():  # lib.rs:2345-2371
+    values = np.arange(7 * 16 * 128, dtype=np.float32).reshape(7, 16, 128)
+    got = fjo.copy(np.ascontiguousarray(values.transpose(1, 0, 2)), fjo.F32, fjo.BF16)
+    want = fjo.encode(np.ascontiguousarray(values.transpose(1, 0, 2)), fjo.BF16)
+    assert got.shape == (16, 7, 128) and np.array_equal(got, want)
+    # index (sequence * 16 + head) * 128 + column, rounded to bf16 with ties to even: 257 -> 256, 259 -> 260
+    assert fjo.decode(got, fjo.BF16)[2, 0, 1] == 256.0 and fjo.decode(got, fjo.BF16)[2, 0, 3] == 260.0
+
+
+def test_matmul_handles_unit_contraction_and_row_dimensions():  # lib.rs:3080-3092
+    got = fjo.matmul(np.array([[2.0], [3.0]], np.float32), fjo.F32, np.array([[4.0, 5.0, 6.0]], np.float32), fjo.F32, fjo.F32)
+    assert got.ravel().tolist() == [8.0, 10.0, 12.0, 12.0, 15.0, 18.0]
+    left = np.array([1.0, 2.0, 3.0, 4.0], np.float32).reshape(2, 1, 2)
+    right = np.array([5.0, 6.0, 7.0, 8.0], np.float32).reshape(2, 2, 1)
+    assert fjo.matmul(left, fjo.F32, right, fjo.F32, fjo.F32).ravel().tolist() == [17.0, 53.0]
+
+
+def test_matmul_with_bias_epilogue_inputs_sums_in_index_order():  # lib.rs:1985-2070 (the fused and the decomposed form share this sum)
+    left = (np.arange(7 * 33, dtype=np.float32) / np.float32(97.0) - np.float32(1.0)).reshape(7, 33)
+    right = (np.arange(33 * 17, dtype=np.float32) / np.float32(113.0) - np.float32(2.0)).reshape(33, 17)
+    bias = np.arange(17, dtype=np.float32) / np.float32(17.0)
+    acc = fjo.matmul(left, fjo.F32, right, fjo.F32, fjo.F32)
+    want = np.zeros((7, 17), np.float32)
+    for k in range(33):  # k ascending, product rounded, then added
+        want = (want + (left[:, k:k + 1] * right[k:k + 1, :]).astype(np.float32)).astype(np.float32)
+    assert np.array_equal(acc.view(np.uint32), want.view(np.uint32))
+    fused = fjo.prog_add(acc, np.broadcast_to(bias, (7, 17)).copy(), fjo.F32)
+    assert np.array_equal(fused.view(np.uint32), (want + bias).astype(np.float32).view(np.uint32))
+
+
+def test_embeds_rows_near_both_ends_of_a_1024_wide_table():  # lib.rs:2760-2783
+    values = (np.arange(1000 * 1024) % 251).astype(np.float32).reshape(1000, 1024)
+    ids = np.array([0, 1, 998, 999], np.uint32)
+    assert np.array_equal(fjo.embed(values, fjo.F32, ids), values[ids])
+
+
+def test_sdpa_hand_checked_two_key_case_and_grouped_heads():  # lib.rs:3095-3153
+    q = np.array([1.0, 0.0], np.float32).reshape(1, 1, 2)
+    k = np.array([1.0, 0.0, 0.0, 1.0], np.float32).reshape(1, 2, 2)
+    v = np.array([10.0, 20.0], np.float32).reshape(1, 2, 1)
+    e = np.exp(np.float32(1.0))
+    got = fjo.sdpa(q, fjo.F32, k, fjo.F32, v, fjo.F32, 1.0, False, 0)
+    assert abs(float(got.ravel()[0]) - float((10.0 * e + 20.0) / (e + 1.0))) <= 1e-5 * 20
+    # 16 query heads over 8 cache heads, 7 keys of width 128, all-zero keys: every query head returns its cache head's value
+    keys = np.zeros((8, 7, 128), np.float32)
+    values = np.repeat(np.arange(8, dtype=np.float32), 7 * 128).reshape(8, 7, 128)
+    got = fjo.sdpa(np.zeros((16, 1, 128), np.float32), fjo.F32, keys, fjo.F32, values, fjo.F32, float(1.0 / np.sqrt(np.float32(128.0))), True, 6)
+    assert np.allclose(got.ravel(), np.repeat(np.arange(8, dtype=np.float32), 2 * 128), rtol=1e-5)
+    # a causal window that would reach past the cache is refused
+    key = np.array([1.0, 0.0, 0.0, 1.0, 1.0, 1.0, -1.0, 1.0], np.float32).reshape(1, 4, 2)
+    with pytest.raises(fjo.OracleError):
+        fjo.sdpa(np.array([7.0, 8.0], np.float32).reshape(1, 1, 2), fjo.F32, key, fjo.F32, key, fjo.F32, 0.5, True, 4)
+
+
+def test_paged_lane_activity_defaults_active_and_reads_u32():  # lib.rs:1973-1982
+    """No activity word = active; 0 = inactive (zeros out, nothing copied); any other value (7) = active."""
+    page = 16
+    table = np.array([[0, 0]], np.uint32)
+    generations = np.zeros(2, np.uint32)
+    rows = fjo.encode(np.arange(4 * 8, dtype=np.float32).reshape(4, 8), fjo.F32)
+    for activity, written in ((None, True), (0, False), (7, True)):
+        pool = np.zeros((2, page, 8), np.float32)
+        fjo.paged_copy_in(rows, fjo.F32, pool, fjo.F32, table, generations, 0, page, activity=activity)
+        assert bool(np.any(pool != 0.0)) == written
