@@ -331,3 +331,21 @@ def test_pack_step_reference_metadata():
     assert out["absolute_positions"].tolist() == [20, 0, 16]
     assert out["query_starts"].tolist() == [20, 0, 14]
     assert out["activity"].tolist() == [1, 0, 1]
+
+
+def test_cow_copy_preserves_shared_prefix_bytes():
+    """crates/forja-cpu/src/paged.rs:422-455: seven rows are written, the sequence is forked at seven, the original copies its
+    shared tail page (three rows) on write; both sequences still read the same seven rows through their own tables."""
+    p = pool(4096, slab=4)
+    original = p.reserve(8)
+    assert original.commit_write(7) == 0
+    storage = np.zeros((p.physical_pages(), 4, 2), np.float32)  # page of 4 tokens x one plane of 2 elements
+    prefix = np.arange(14, dtype=np.float32).reshape(7, 2)
+    fjo.paged_copy_in(prefix, fjo.F32, storage, fjo.F32, original.table(), p.generations(), 0, 4)
+    sibling = original.fork(7)
+    src, dst, count = original.cow_tail()
+    assert count == 3
+    tail = fjo.paged_copy_out(storage, fjo.F32, sibling.table(), p.generations(), 4, 3, 4, fjo.F32)
+    fjo.paged_copy_in(tail, fjo.F32, storage, fjo.F32, original.table(), p.generations(), 4, 4)
+    for sequence in (original, sibling):
+        assert np.array_equal(fjo.paged_copy_out(storage, fjo.F32, sequence.table(), p.generations(), 0, 7, 4, fjo.F32), prefix)
